@@ -1,0 +1,141 @@
+/*
+ * nvq.h -- C ABI of the B200 (sm_100a) cast / quantise / quantised-GEMM library.
+ *
+ * NovaNN (the reference framework) is pure Python over NumPy and has no native
+ * boundary of its own; what this library replaces are the NumPy calls on its hot
+ * path.  Each entry point names the reference call it stands in for as
+ * file:line inside the reference project.  The Python package novann_b200 binds
+ * these symbols with ctypes and presents the reference's Layer / functional API.
+ *
+ * Conventions
+ *  - every function returns an nvq_status (0 = ok, negative = failure); nothing
+ *    throws or aborts.  nvq_last_error() gives a thread-local message.
+ *  - all pointers named d_* are DEVICE pointers on `device`; h_* are host pointers.
+ *  - compute calls are asynchronous on `stream` (a cudaStream_t passed as void*,
+ *    NULL = the default stream of `device`); the caller synchronises.
+ *  - the library allocates nothing inside compute calls except where a function
+ *    says otherwise; buffers come from nvq_malloc or any other CUDA allocator.
+ *  - there is no CPU fallback anywhere: without a CUDA device every call fails.
+ */
+#ifndef NVQ_H
+#define NVQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int32_t nvq_status;
+enum {
+    NVQ_OK = 0,
+    NVQ_ERR_INVALID = -1,     /* bad argument (null, size, alignment, dtype, scale) */
+    NVQ_ERR_CUDA = -2,        /* a CUDA runtime / driver call failed */
+    NVQ_ERR_UNSUPPORTED = -3, /* valid request this build cannot serve (shape rule) */
+    NVQ_ERR_TIMEOUT = -4,     /* a bounded device-side wait gave up (kernel self check) */
+    NVQ_ERR_NCCL = -5         /* an NCCL call failed */
+};
+
+typedef enum {
+    NVQ_F32 = 0,
+    NVQ_F16 = 1,
+    NVQ_BF16 = 2,
+    NVQ_E4M3 = 3,     /* FP8 E4M3 "fn": bias 7, no inf, NaN 0x7f/0xff, max 448 */
+    NVQ_E5M2 = 4,     /* FP8 E5M2: bias 15, max finite 57344 */
+    NVQ_E2M1_B32 = 5  /* FP4 E2M1, two codes per byte (low nibble first), one fp32
+                         scale per 32 consecutive elements of a row */
+} nvq_dtype;
+
+typedef enum {
+    NVQ_PAD_ZEROS = 0,
+    NVQ_PAD_REFLECT = 1,
+    NVQ_PAD_REPLICATE = 2,
+    NVQ_PAD_CIRCULAR = 3
+} nvq_pad_mode;
+
+/* ---------------------------------------------------------------- runtime */
+
+const char* nvq_last_error(void);
+const char* nvq_version(void);
+nvq_status nvq_device_count(int* count);
+/* SM count and total memory of a device (grid sizing / shard sizing). */
+nvq_status nvq_device_info(int device, int* sm_count, size_t* total_bytes, int* cc_major,
+                           int* cc_minor);
+
+nvq_status nvq_malloc(int device, size_t bytes, void** d_ptr);
+nvq_status nvq_free(int device, void* d_ptr);
+nvq_status nvq_host_alloc(size_t bytes, void** h_ptr); /* pinned */
+nvq_status nvq_host_free(void* h_ptr);
+nvq_status nvq_memcpy_h2d(void* d_dst, const void* h_src, size_t bytes, int device, void* stream);
+nvq_status nvq_memcpy_d2h(void* h_dst, const void* d_src, size_t bytes, int device, void* stream);
+nvq_status nvq_memcpy_d2d(void* d_dst, const void* d_src, size_t bytes, int device, void* stream);
+nvq_status nvq_memset(void* d_dst, int value, size_t bytes, int device, void* stream);
+
+nvq_status nvq_stream_create(int device, void** stream);
+nvq_status nvq_stream_destroy(int device, void* stream);
+nvq_status nvq_stream_sync(int device, void* stream);
+nvq_status nvq_device_sync(int device);
+nvq_status nvq_event_create(int device, void** event);
+nvq_status nvq_event_destroy(int device, void* event);
+nvq_status nvq_event_record(int device, void* event, void* stream);
+nvq_status nvq_event_sync(int device, void* event);
+nvq_status nvq_event_elapsed_ms(void* start, void* stop, float* ms);
+
+/* Number of kernels this library has launched in the calling process so far. */
+uint64_t nvq_launch_count(void);
+
+/* ---------------------------------------------------------------- casts
+ * Replaces ndarray.astype at novann/layers/linear/linear.py:81,96 and
+ * novann/layers/convolutional/conv2d.py:159,188 (NumPy round-to-nearest-even
+ * narrowing, overflow to +-inf, exact widening), extended to bf16.
+ *   f32->f16: bit-identical to NumPy astype(float16), NaN payload rule included.
+ *   f32->bf16: RNE, any NaN -> sign|0x7fc0.   f16/bf16->f32: exact.
+ * Supported pairs: {f32}<->{f16,bf16}.  n elements, any alignment (16-byte
+ * aligned pointers take the vectorised path).
+ */
+nvq_status nvq_cast(void* d_dst, nvq_dtype dst_dtype, const void* d_src, nvq_dtype src_dtype,
+                    size_t n, int device, void* stream);
+
+/* Host-buffer variant of nvq_cast: h_src/h_dst are host arrays (pinned memory
+ * gives full PCIe rate); the data is streamed through device staging buffers in
+ * chunks with H2D, kernel and D2H overlapped.  Synchronous.  This is the call that
+ * sits exactly where ndarray.astype sat (host array in, host array out). */
+nvq_status nvq_cast_host(void* h_dst, nvq_dtype dst_dtype, const void* h_src,
+                         nvq_dtype src_dtype, size_t n, int device);
+
+/* ---------------------------------------------------------------- FP8, per tensor
+ * No reference counterpart (NovaNN has no quantisation); semantics follow the
+ * written rules: amax exact with NaNs ignored; scale = amax/FMAX and
+ * inv_scale = FMAX/amax, one fp32 division each (both 1 when amax == 0);
+ * q = cvt_sat_rne(x * inv_scale) with one fp32 multiply; x' = float(q) * scale.
+ */
+/* *d_amax = max|x| (fp32).  d_amax is written, not accumulated. */
+nvq_status nvq_amax_f32(const float* d_src, size_t n, float* d_amax, int device, void* stream);
+/* fmt = NVQ_E4M3 or NVQ_E5M2; inv_scale must be finite and > 0. */
+nvq_status nvq_quantize_fp8(uint8_t* d_dst, const float* d_src, size_t n, nvq_dtype fmt,
+                            float inv_scale, int device, void* stream);
+nvq_status nvq_dequantize_fp8(float* d_dst, const uint8_t* d_src, size_t n, nvq_dtype fmt,
+                              float scale, int device, void* stream);
+/* amax + scale computation + quantise without a host round trip.
+ * d_amax_scale_inv: 3 floats written {amax, scale, inv_scale}.  If d_amax_in is not
+ * NULL it holds an already combined amax (e.g. the max over all row shards) and the
+ * reduction over d_src is skipped. */
+nvq_status nvq_quantize_fp8_tensor(uint8_t* d_dst, float* d_amax_scale_inv, const float* d_src,
+                                   size_t n, nvq_dtype fmt, const float* d_amax_in, int device,
+                                   void* stream);
+
+/* ---------------------------------------------------------------- FP4 E2M1, block 32
+ * No reference counterpart.  rows x cols bf16, cols % 32 == 0.
+ * d_packed: rows x cols/2 bytes; d_scales: rows x cols/32 fp32.
+ */
+nvq_status nvq_quantize_fp4_b32(uint8_t* d_packed, float* d_scales, const uint16_t* d_src_bf16,
+                                size_t rows, size_t cols, int device, void* stream);
+nvq_status nvq_dequantize_fp4_b32(uint16_t* d_dst_bf16, const uint8_t* d_packed,
+                                  const float* d_scales, size_t rows, size_t cols, int device,
+                                  void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NVQ_H */

@@ -1,0 +1,91 @@
+"""ctypes binding of ``libnvq.so`` (the C ABI declared in ``include/nvq.h``).
+
+There is no fallback of any kind: if the library is missing, or a call fails, an
+exception is raised.  ``lib()`` loads lazily so that the package can be imported on
+a machine without a GPU (the library itself loads there too; only calls fail).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.environ.get("NVQ_LIB", os.path.join(_HERE, "libnvq.so"))
+
+# dtype ids of nvq_dtype
+F32, F16, BF16, E4M3, E5M2, E2M1_B32 = 0, 1, 2, 3, 4, 5
+DTYPE_IDS = {"f32": F32, "f16": F16, "bf16": BF16, "e4m3": E4M3, "e5m2": E5M2, "e2m1_b32": E2M1_B32}
+DTYPE_SIZE = {F32: 4, F16: 2, BF16: 2, E4M3: 1, E5M2: 1}
+PAD_MODES = {"zeros": 0, "reflect": 1, "replicate": 2, "circular": 3}
+
+OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_NCCL = 0, -1, -2, -3, -4, -5
+
+vp, sz, i32, f32c, u64 = C.c_void_p, C.c_size_t, C.c_int, C.c_float, C.c_uint64
+pvp = C.POINTER(C.c_void_p)
+
+# name -> (restype, argtypes).  Every symbol declared in include/nvq.h is listed here;
+# tests/test_abi.py checks the two against each other and against the built library.
+SIGNATURES = {
+    "nvq_last_error": (C.c_char_p, []),
+    "nvq_version": (C.c_char_p, []),
+    "nvq_device_count": (i32, [C.POINTER(i32)]),
+    "nvq_device_info": (i32, [i32, C.POINTER(i32), C.POINTER(sz), C.POINTER(i32), C.POINTER(i32)]),
+    "nvq_malloc": (i32, [i32, sz, pvp]),
+    "nvq_free": (i32, [i32, vp]),
+    "nvq_host_alloc": (i32, [sz, pvp]),
+    "nvq_host_free": (i32, [vp]),
+    "nvq_memcpy_h2d": (i32, [vp, vp, sz, i32, vp]),
+    "nvq_memcpy_d2h": (i32, [vp, vp, sz, i32, vp]),
+    "nvq_memcpy_d2d": (i32, [vp, vp, sz, i32, vp]),
+    "nvq_memset": (i32, [vp, i32, sz, i32, vp]),
+    "nvq_stream_create": (i32, [i32, pvp]),
+    "nvq_stream_destroy": (i32, [i32, vp]),
+    "nvq_stream_sync": (i32, [i32, vp]),
+    "nvq_device_sync": (i32, [i32]),
+    "nvq_event_create": (i32, [i32, pvp]),
+    "nvq_event_destroy": (i32, [i32, vp]),
+    "nvq_event_record": (i32, [i32, vp, vp]),
+    "nvq_event_sync": (i32, [i32, vp]),
+    "nvq_event_elapsed_ms": (i32, [vp, vp, C.POINTER(f32c)]),
+    "nvq_launch_count": (u64, []),
+    "nvq_cast": (i32, [vp, i32, vp, i32, sz, i32, vp]),
+    "nvq_cast_host": (i32, [vp, i32, vp, i32, sz, i32]),
+    "nvq_amax_f32": (i32, [vp, sz, vp, i32, vp]),
+    "nvq_quantize_fp8": (i32, [vp, vp, sz, i32, f32c, i32, vp]),
+    "nvq_dequantize_fp8": (i32, [vp, vp, sz, i32, f32c, i32, vp]),
+    "nvq_quantize_fp8_tensor": (i32, [vp, vp, vp, sz, i32, vp, i32, vp]),
+    "nvq_quantize_fp4_b32": (i32, [vp, vp, vp, sz, sz, i32, vp]),
+    "nvq_dequantize_fp4_b32": (i32, [vp, vp, vp, sz, sz, i32, vp]),
+}
+
+
+class NvqError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"nvq status {status}: {message}")
+        self.status = status
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """The loaded library.  Raises if it has not been built (no CPU fallback)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} not found: build it with `python -m novann_b200.build` "
+                "(there is no CPU fallback)")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != OK:
+        msg = lib().nvq_last_error()
+        raise NvqError(status, msg.decode() if msg else "")

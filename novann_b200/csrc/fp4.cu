@@ -1,0 +1,254 @@
+// FP4 E2M1 quantisation with one fp32 scale per 32 consecutive elements of a row,
+// two codes per byte (low nibble first), and the inverse.  NovaNN has no
+// quantisation; the rules are:
+//   amax_b = max|x| over the block (NaN ignored);  scale_b = amax_b / 6
+//   inv_b  = amax_b > 0 ? 6 / amax_b : 0
+//   code   = cvt_sat_rne_e2m1(float(x) * inv_b);   byte j = code[2j] | code[2j+1] << 4
+//   x'     = bf16_rne(e2m1_value(code) * scale_b)
+// One thread owns one block: 64 bytes of bf16 in, 16 bytes of codes + one scale out
+// (2.625 bytes per element either way), no shuffles, every access full-sector.
+#include <math.h>
+
+#include "nvq_common.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 2;
+
+struct Block32 { u32x8 a, b; };  // 32 bf16 values
+
+// two fp32 -> one byte holding two E2M1 codes (lo in the low nibble)
+__device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {
+    uint16_t r;
+    asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; mov.b16 %0, {t, 0}; }"
+        : "=h"(r)
+        : "f"(hi), "f"(lo));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t quant_word_fast(uint32_t w0, uint32_t w1, uint32_t w2,
+                                                    uint32_t w3, float inv) {
+    // 8 bf16 values (four words) -> 8 codes (one word)
+    const uint32_t w[4] = {w0, w1, w2, w3};
+    uint32_t out = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        float lo = __fmul_rn(__uint_as_float(w[i] << 16), inv);
+        float hi = __fmul_rn(__uint_as_float(w[i] & 0xFFFF0000u), inv);
+        out |= cvt_e2m1x2(lo, hi) << (8 * i);
+    }
+    return out;
+}
+
+__device__ __forceinline__ uint32_t quant_one_spec(uint32_t xu, uint32_t invu) {
+    return spec_f32_to_e2m1(spec_mul_bits(xu, invu));
+}
+
+__device__ __forceinline__ uint32_t quant_word_spec(uint32_t w0, uint32_t w1, uint32_t w2,
+                                                    uint32_t w3, uint32_t invu) {
+    const uint32_t w[4] = {w0, w1, w2, w3};
+    uint32_t out = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        uint32_t lo = quant_one_spec(w[i] << 16, invu);
+        uint32_t hi = quant_one_spec(w[i] & 0xFFFF0000u, invu);
+        out |= (lo | (hi << 4)) << (8 * i);
+    }
+    return out;
+}
+
+__device__ __forceinline__ void quant_block(const Block32& in, uint4& codes, float& scale) {
+    float amax = 0.f, probe = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        float a0 = __uint_as_float(in.a.v[i] << 16), a1 = __uint_as_float(in.a.v[i] & 0xFFFF0000u);
+        float b0 = __uint_as_float(in.b.v[i] << 16), b1 = __uint_as_float(in.b.v[i] & 0xFFFF0000u);
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(a0), fabsf(a1)), fmaxf(fabsf(b0), fabsf(b1))));
+        probe = fmaf(a0, 0.f, probe);
+        probe = fmaf(a1, 0.f, probe);
+        probe = fmaf(b0, 0.f, probe);
+        probe = fmaf(b1, 0.f, probe);
+    }
+    scale = __fdiv_rn(amax, 6.0f);
+    float inv = amax > 0.f ? __fdiv_rn(6.0f, amax) : 0.f;
+    // a block with inf / NaN, or whose reciprocal scale overflowed, takes the integer path
+    bool slow = (probe != probe) || (__float_as_uint(inv) >= 0x7F800000u);
+    if (!slow) {
+        codes.x = quant_word_fast(in.a.v[0], in.a.v[1], in.a.v[2], in.a.v[3], inv);
+        codes.y = quant_word_fast(in.a.v[4], in.a.v[5], in.a.v[6], in.a.v[7], inv);
+        codes.z = quant_word_fast(in.b.v[0], in.b.v[1], in.b.v[2], in.b.v[3], inv);
+        codes.w = quant_word_fast(in.b.v[4], in.b.v[5], in.b.v[6], in.b.v[7], inv);
+    } else {
+        uint32_t iu = __float_as_uint(inv);
+        codes.x = quant_word_spec(in.a.v[0], in.a.v[1], in.a.v[2], in.a.v[3], iu);
+        codes.y = quant_word_spec(in.a.v[4], in.a.v[5], in.a.v[6], in.a.v[7], iu);
+        codes.z = quant_word_spec(in.b.v[0], in.b.v[1], in.b.v[2], in.b.v[3], iu);
+        codes.w = quant_word_spec(in.b.v[4], in.b.v[5], in.b.v[6], in.b.v[7], iu);
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+fp4_quant_kernel(const uint16_t* __restrict__ src, uint8_t* __restrict__ packed,
+                 float* __restrict__ scales, size_t n_blocks) {
+    const size_t stride = (size_t)gridDim.x * kThreads;
+    const size_t tid = (size_t)blockIdx.x * kThreads + threadIdx.x;
+    for (size_t base = tid; base < n_blocks; base += stride * kUnroll) {
+        Block32 in[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; u++) {
+            size_t b = base + (size_t)u * stride;
+            if (b < n_blocks) {
+                in[u].a = ldg_stream_256((const char*)src + b * 64);
+                in[u].b = ldg_stream_256((const char*)src + b * 64 + 32);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; u++) {
+            size_t b = base + (size_t)u * stride;
+            if (b < n_blocks) {
+                uint4 codes;
+                float scale;
+                quant_block(in[u], codes, scale);
+                stg_stream_128(packed + b * 16, codes);
+                __stcs(scales + b, scale);
+            }
+        }
+    }
+}
+
+// ---- dequantise -------------------------------------------------------------------
+__device__ __forceinline__ float e2m1_value(uint32_t c) {
+    // {0,.5,1,1.5,2,3,4,6}: magnitudes as fp32 patterns from a 3-bit code
+    uint32_t m = c & 7u;
+    uint32_t bits = m == 0 ? 0u : m == 1 ? 0x3F000000u : (((m >> 1) + 126u) << 23) | ((m & 1u) << 22);
+    return __uint_as_float(bits | ((c & 8u) << 28));
+}
+
+__device__ __forceinline__ uint32_t dequant_one_spec(uint32_t c, uint32_t su) {
+    return spec_f32_to_bf16(spec_mul_bits(__float_as_uint(e2m1_value(c)), su));
+}
+
+// 8 codes (one word) -> 8 bf16 (four words)
+__device__ __forceinline__ void dequant_word_fast(uint32_t w, float s, uint32_t* o) {
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        uint16_t h = (uint16_t)(w >> (16 * i));
+        uint32_t f01, f23;  // two f16x2: codes 0,1 and 2,3 of this half word
+        asm("{ .reg .b8 lo, hi; mov.b16 {lo, hi}, %2; cvt.rn.f16x2.e2m1x2 %0, lo; "
+            "cvt.rn.f16x2.e2m1x2 %1, hi; }"
+            : "=r"(f01), "=r"(f23)
+            : "h"(h));
+        float v0, v1, v2, v3;
+        asm("cvt.f32.f16 %0, %1;" : "=f"(v0) : "h"((uint16_t)(f01 & 0xFFFFu)));
+        asm("cvt.f32.f16 %0, %1;" : "=f"(v1) : "h"((uint16_t)(f01 >> 16)));
+        asm("cvt.f32.f16 %0, %1;" : "=f"(v2) : "h"((uint16_t)(f23 & 0xFFFFu)));
+        asm("cvt.f32.f16 %0, %1;" : "=f"(v3) : "h"((uint16_t)(f23 >> 16)));
+        uint32_t r0, r1;
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r0) : "f"(__fmul_rn(v1, s)), "f"(__fmul_rn(v0, s)));
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r1) : "f"(__fmul_rn(v3, s)), "f"(__fmul_rn(v2, s)));
+        o[2 * i] = r0;
+        o[2 * i + 1] = r1;
+    }
+}
+
+__device__ __forceinline__ void dequant_word_spec(uint32_t w, uint32_t su, uint32_t* o) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        uint32_t lo = dequant_one_spec((w >> (8 * i)) & 0xFu, su);
+        uint32_t hi = dequant_one_spec((w >> (8 * i + 4)) & 0xFu, su);
+        o[i] = lo | (hi << 16);
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+fp4_dequant_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ scales,
+                   uint16_t* __restrict__ dst, size_t n_blocks) {
+    const size_t stride = (size_t)gridDim.x * kThreads;
+    const size_t tid = (size_t)blockIdx.x * kThreads + threadIdx.x;
+    for (size_t base = tid; base < n_blocks; base += stride * kUnroll) {
+        uint4 in[kUnroll];
+        float sc[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; u++) {
+            size_t b = base + (size_t)u * stride;
+            if (b < n_blocks) {
+                in[u] = ldg_stream_128(packed + b * 16);
+                sc[u] = __ldcs(scales + b);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; u++) {
+            size_t b = base + (size_t)u * stride;
+            if (b < n_blocks) {
+                u32x8 lo, hi;
+                uint32_t su = __float_as_uint(sc[u]);
+                if ((su & 0x7F800000u) != 0x7F800000u) {
+                    dequant_word_fast(in[u].x, sc[u], lo.v);
+                    dequant_word_fast(in[u].y, sc[u], lo.v + 4);
+                    dequant_word_fast(in[u].z, sc[u], hi.v);
+                    dequant_word_fast(in[u].w, sc[u], hi.v + 4);
+                } else {
+                    dequant_word_spec(in[u].x, su, lo.v);
+                    dequant_word_spec(in[u].y, su, lo.v + 4);
+                    dequant_word_spec(in[u].z, su, hi.v);
+                    dequant_word_spec(in[u].w, su, hi.v + 4);
+                }
+                stg_stream_256((char*)dst + b * 64, lo);
+                stg_stream_256((char*)dst + b * 64 + 32, hi);
+            }
+        }
+    }
+}
+
+template <class K>
+unsigned pick_grid(K kernel, size_t n_blocks, int device, int* per_sm_cache) {
+    if (*per_sm_cache == 0) {
+        int b = 0;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, kernel, kThreads, 0);
+        *per_sm_cache = b > 0 ? b : 1;
+    }
+    size_t want = (n_blocks + (size_t)kThreads * kUnroll - 1) / ((size_t)kThreads * kUnroll);
+    size_t cap = (size_t)nvq_sm_count(device) * *per_sm_cache;
+    return (unsigned)(want < 1 ? 1 : (want < cap ? want : cap));
+}
+
+}  // namespace
+
+extern "C" nvq_status nvq_quantize_fp4_b32(uint8_t* d_packed, float* d_scales,
+                                           const uint16_t* d_src_bf16, size_t rows, size_t cols,
+                                           int device, void* stream) {
+    NVQ_REQUIRE(cols % 32 == 0, "nvq_quantize_fp4_b32: cols (%zu) must be a multiple of 32", cols);
+    size_t n_blocks = rows * (cols / 32);
+    if (n_blocks == 0) return NVQ_OK;
+    NVQ_REQUIRE(d_packed && d_scales && d_src_bf16, "nvq_quantize_fp4_b32: null buffer");
+    NVQ_REQUIRE(nvq_aligned(d_src_bf16, 32) && nvq_aligned(d_packed, 16) && nvq_aligned(d_scales, 4),
+                "nvq_quantize_fp4_b32: src must be 32-byte, packed 16-byte, scales 4-byte aligned");
+    nvq_status s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    static int per_sm = 0;
+    unsigned grid = pick_grid(fp4_quant_kernel, n_blocks, device, &per_sm);
+    fp4_quant_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>(d_src_bf16, d_packed, d_scales,
+                                                                  n_blocks);
+    NVQ_LAUNCHED();
+    return NVQ_OK;
+}
+
+extern "C" nvq_status nvq_dequantize_fp4_b32(uint16_t* d_dst_bf16, const uint8_t* d_packed,
+                                             const float* d_scales, size_t rows, size_t cols,
+                                             int device, void* stream) {
+    NVQ_REQUIRE(cols % 32 == 0, "nvq_dequantize_fp4_b32: cols (%zu) must be a multiple of 32", cols);
+    size_t n_blocks = rows * (cols / 32);
+    if (n_blocks == 0) return NVQ_OK;
+    NVQ_REQUIRE(d_packed && d_scales && d_dst_bf16, "nvq_dequantize_fp4_b32: null buffer");
+    NVQ_REQUIRE(nvq_aligned(d_dst_bf16, 32) && nvq_aligned(d_packed, 16) && nvq_aligned(d_scales, 4),
+                "nvq_dequantize_fp4_b32: dst must be 32-byte, packed 16-byte, scales 4-byte aligned");
+    nvq_status s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    static int per_sm = 0;
+    unsigned grid = pick_grid(fp4_dequant_kernel, n_blocks, device, &per_sm);
+    fp4_dequant_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>(d_packed, d_scales, d_dst_bf16,
+                                                                    n_blocks);
+    NVQ_LAUNCHED();
+    return NVQ_OK;
+}
