@@ -129,26 +129,26 @@ __device__ __forceinline__ uint32_t dequant_one_spec(uint32_t c, uint32_t su) {
     return spec_f32_to_bf16(spec_mul_bits(__float_as_uint(e2m1_value(c)), su));
 }
 
+// one byte (two codes, low nibble first) -> f16x2 holding their exact values
+__device__ __forceinline__ uint32_t cvt_f16x2_e2m1x2(uint32_t byte) {
+    uint32_t r;
+    asm("{ .reg .b8 t, z; mov.b16 {t, z}, %1; cvt.rn.f16x2.e2m1x2 %0, t; }"
+        : "=r"(r)
+        : "h"((uint16_t)byte));
+    return r;
+}
+
 // 8 codes (one word) -> 8 bf16 (four words)
 __device__ __forceinline__ void dequant_word_fast(uint32_t w, float s, uint32_t* o) {
 #pragma unroll
-    for (int i = 0; i < 2; i++) {
-        uint16_t h = (uint16_t)(w >> (16 * i));
-        uint32_t f01, f23;  // two f16x2: codes 0,1 and 2,3 of this half word
-        asm("{ .reg .b8 lo, hi; mov.b16 {lo, hi}, %2; cvt.rn.f16x2.e2m1x2 %0, lo; "
-            "cvt.rn.f16x2.e2m1x2 %1, hi; }"
-            : "=r"(f01), "=r"(f23)
-            : "h"(h));
-        float v0, v1, v2, v3;
+    for (int i = 0; i < 4; i++) {
+        uint32_t f01 = cvt_f16x2_e2m1x2((w >> (8 * i)) & 0xFFu);
+        float v0, v1;
         asm("cvt.f32.f16 %0, %1;" : "=f"(v0) : "h"((uint16_t)(f01 & 0xFFFFu)));
         asm("cvt.f32.f16 %0, %1;" : "=f"(v1) : "h"((uint16_t)(f01 >> 16)));
-        asm("cvt.f32.f16 %0, %1;" : "=f"(v2) : "h"((uint16_t)(f23 & 0xFFFFu)));
-        asm("cvt.f32.f16 %0, %1;" : "=f"(v3) : "h"((uint16_t)(f23 >> 16)));
-        uint32_t r0, r1;
-        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r0) : "f"(__fmul_rn(v1, s)), "f"(__fmul_rn(v0, s)));
-        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r1) : "f"(__fmul_rn(v3, s)), "f"(__fmul_rn(v2, s)));
-        o[2 * i] = r0;
-        o[2 * i + 1] = r1;
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;"
+            : "=r"(o[i])
+            : "f"(__fmul_rn(v1, s)), "f"(__fmul_rn(v0, s)));
     }
 }
 
