@@ -135,6 +135,28 @@ nvq_status nvq_dequantize_fp4_b32(uint16_t* d_dst_bf16, const uint8_t* d_packed,
                                   const float* d_scales, size_t rows, size_t cols, int device,
                                   void* stream);
 
+/* ---------------------------------------------------------------- quantised Linear
+ * Replaces F.linear, novann/functional.py:147-163 (out = input @ weight.T; out +=
+ * bias) for a weight stored as FP8 / FP4 codes:
+ *   Y[m,n] = bf16_rne( s_n * sum_k X[m,k] * dequant(Wq[n,k]) + b_n )
+ * X: M x K bf16 row-major.  Wq: N x K codes.  E4M3 / E5M2: one byte per weight and
+ * d_w_scales holds N per-output-channel fp32 scales.  E2M1_B32: N x K/2 packed bytes
+ * and d_w_scales holds N x K/32 block scales (K % 32 == 0).  d_bias: N fp32 or NULL.
+ * Y: M x N bf16, 32-byte aligned.  K % 8 == 0, N % 8 == 0; M, N, K tails are handled.
+ * fp32 accumulation on the tcgen05 tensor cores.
+ * d_workspace: scratch of nvq_linear_workspace_bytes(N, K, fmt) bytes (32-byte
+ * aligned) that receives the weight expanded to 16-bit tensor-core operands; it is
+ * rewritten by every call, so calls that share a workspace must be stream ordered.
+ */
+nvq_status nvq_linear_workspace_bytes(size_t N, size_t K, nvq_dtype w_fmt, size_t* bytes);
+nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf16, const uint8_t* d_wq,
+                          nvq_dtype w_fmt, const float* d_w_scales, const float* d_bias,
+                          size_t M, size_t N, size_t K, void* d_workspace, size_t workspace_bytes,
+                          int device, void* stream);
+/* Tensor-core kernels bound every device-side wait; a wait that gives up records a
+ * non-zero code here (read and cleared by this call) instead of hanging. */
+nvq_status nvq_device_error_flag(int device, int* flag);
+
 #ifdef __cplusplus
 }
 #endif

@@ -56,6 +56,9 @@ SIGNATURES = {
     "nvq_quantize_fp8_tensor": (i32, [vp, vp, vp, sz, i32, vp, i32, vp]),
     "nvq_quantize_fp4_b32": (i32, [vp, vp, vp, sz, sz, i32, vp]),
     "nvq_dequantize_fp4_b32": (i32, [vp, vp, vp, sz, sz, i32, vp]),
+    "nvq_linear_workspace_bytes": (i32, [sz, sz, i32, C.POINTER(sz)]),
+    "nvq_linear_fwd": (i32, [vp, vp, vp, i32, vp, vp, sz, sz, sz, vp, sz, i32, vp]),
+    "nvq_device_error_flag": (i32, [i32, C.POINTER(i32)]),
 }
 
 

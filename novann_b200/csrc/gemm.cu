@@ -1,0 +1,404 @@
+// Quantised-weight Linear forward on the tcgen05 tensor cores (the replacement for
+// F.linear, novann/functional.py:147-163, when the weight is stored as FP8 / FP4):
+//   Y[m,n] = bf16( s_n * sum_k X[m,k] * Wd[n,k] + b_n )
+// X is M x K bf16 (K contiguous); Wd is the N x K weight whose codes were expanded to
+// 16-bit values that represent them exactly (every E4M3 / E5M2 / E2M1 value is a bf16
+// value), so the per-channel scale factors out of the K sum and is applied in the
+// epilogue together with the bias and the bf16 rounding.
+//
+// Kernel: persistent, one CTA per SM, warp specialised.
+//   warp 0      TMA producer: A (128 x 64) and B (BN x 64) tiles, 128-byte swizzle,
+//               STAGES-deep ring of shared-memory slots guarded by full/empty mbarriers
+//   warp 1      TMEM allocation, then one lane issues tcgen05.mma (128 x BN x 16, bf16 in,
+//               fp32 accumulators in TMEM); tcgen05.commit frees the slot / publishes the tile
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (each warp its own 32 TMEM lanes),
+//               scale, bias, round, 32-byte global stores.  Two accumulators (2 x 256
+//               TMEM columns) let the epilogue of tile i overlap the main loop of tile i+1.
+// No TMA multicast and no peer memory anywhere: each CTA fetches its own tiles.
+#include "tc_common.cuh"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;          // 64 bf16 = one 128-byte swizzled row
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512;  // two BN-column accumulators
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 8192 /*barriers, scales*/;
+
+enum { ERR_PRODUCER = 1, ERR_MMA_FULL = 2, ERR_MMA_TMEM = 3, ERR_EPILOGUE = 4 };
+
+struct Shared {            // lives after the tile ring
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+    float scale[2][BN];
+    float bias[2][BN];
+};
+
+struct Params {
+    uint16_t* y;
+    const float* scales;   // N or nullptr (= 1)
+    const float* bias;     // N or nullptr (= 0)
+    int M, N, K;
+    int m_blocks, n_blocks;
+    int* status;           // mapped host word: first non-zero give-up code
+};
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// AND-reduction + barrier over the 128 epilogue threads (named barrier 1)
+__device__ __forceinline__ bool epilogue_all(bool ok) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "bar.red.and.pred p, 1, 128, q;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"((uint32_t)ok)
+        : "memory");
+    return r != 0;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = tc::smem_u32(smem_raw);
+    const uint32_t tiles = (raw + 1023u) & ~1023u;          // 1024-byte aligned tile ring
+    Shared* sh = (Shared*)(smem_raw + (tiles - raw) + STAGES * STAGE_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_tiles = p.m_blocks * p.n_blocks;
+    const int num_kb = (p.K + BK - 1) / BK;
+    volatile int* abort_flag = &sh->abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            tc::mbar_init(tc::smem_u32(&sh->full[s]), 1);
+            tc::mbar_init(tc::smem_u32(&sh->empty[s]), 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            tc::mbar_init(tc::smem_u32(&sh->tmem_full[a]), 1);
+            tc::mbar_init(tc::smem_u32(&sh->tmem_empty[a]), 4);
+        }
+        sh->abort_flag = 0;
+        tc::mbar_fence_init();
+        tc::tma_prefetch_desc(&map_a);
+        tc::tma_prefetch_desc(&map_b);
+    }
+    if (warp == 1) {
+        tc::tmem_alloc(tc::smem_u32(&sh->tmem_base), TMEM_COLS);
+        tc::tmem_relinquish();
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::tc_fence_after();
+    const uint32_t tmem_base = sh->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const int m0 = (t % p.m_blocks) * BM, n0 = (t / p.m_blocks) * BN;
+                for (int kb = 0; kb < num_kb; kb++) {
+                    ok = tc::mbar_wait(tc::smem_u32(&sh->empty[stage]), phase ^ 1, abort_flag, ERR_PRODUCER);
+                    if (!ok) break;
+                    const uint32_t bar = tc::smem_u32(&sh->full[stage]);
+                    const uint32_t a_dst = tiles + stage * STAGE_BYTES;
+                    tc::mbar_arrive_expect_tx(bar, STAGE_BYTES);
+                    tc::tma_load_2d(a_dst, &map_a, bar, kb * BK, m0);
+                    tc::tma_load_2d(a_dst + A_BYTES, &map_b, bar, kb * BK, n0);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = tc::idesc_f16(BM, BN, 1, 1);
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            int it = 0;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, it++) {
+                const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+                ok = tc::mbar_wait(tc::smem_u32(&sh->tmem_empty[acc]), acc_phase ^ 1, abort_flag, ERR_MMA_TMEM);
+                if (!ok) break;
+                tc::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < num_kb; kb++) {
+                    ok = tc::mbar_wait(tc::smem_u32(&sh->full[stage]), phase, abort_flag, ERR_MMA_FULL);
+                    if (!ok) break;
+                    tc::tc_fence_after();
+                    const uint32_t a_addr = tiles + stage * STAGE_BYTES;
+                    const uint64_t a_desc = tc::smem_desc_k_sw128(a_addr);
+                    const uint64_t b_desc = tc::smem_desc_k_sw128(a_addr + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        // advancing 16 elements along K = 32 bytes = 2 units of the address field
+                        tc::tc_mma_f16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+                    }
+                    tc::tc_commit(tc::smem_u32(&sh->empty[stage]));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) tc::tc_commit(tc::smem_u32(&sh->tmem_full[acc]));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const int quarter = warp & 3;               // the 32 TMEM lanes this warp may read
+        const int et = threadIdx.x - 64;            // 0..127
+        const bool vec32 = (p.N % 16) == 0;         // rows then start on 32-byte boundaries
+        bool ok = true;
+        int it = 0;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, it++) {
+            const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+            const int m0 = (t % p.m_blocks) * BM, n0 = (t / p.m_blocks) * BN;
+            // per-tile scale / bias into shared memory (two columns per thread)
+            for (int c = et; c < BN; c += 128) {
+                int n = n0 + c;
+                sh->scale[acc][c] = (p.scales && n < p.N) ? p.scales[n] : 1.f;
+                sh->bias[acc][c] = (p.bias && n < p.N) ? p.bias[n] : 0.f;
+            }
+            ok = tc::mbar_wait(tc::smem_u32(&sh->tmem_full[acc]), acc_phase, abort_flag, ERR_EPILOGUE);
+            // barrier over the four epilogue warps: publishes scale/bias and makes the
+            // go / give-up decision the same for all of them
+            ok = epilogue_all(ok);
+            if (!ok) break;
+            tc::tc_fence_after();
+            const int row = m0 + quarter * 32 + lane;
+            uint16_t* yrow = p.y + (size_t)row * p.N + n0;
+            const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                tc::tmem_ld_32x32(taddr + c, r);
+                tc::tmem_ld_wait();
+                if (row < p.M) {
+#pragma unroll
+                    for (int g = 0; g < 2; g++) {      // two groups of 16 columns
+                        const int col = c + g * 16;
+                        u32x8 o;
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            const int cc = col + 2 * j;
+                            float v0 = fmaf(__uint_as_float(r[g * 16 + 2 * j]), sh->scale[acc][cc], sh->bias[acc][cc]);
+                            float v1 = fmaf(__uint_as_float(r[g * 16 + 2 * j + 1]), sh->scale[acc][cc + 1], sh->bias[acc][cc + 1]);
+                            o.v[j] = pack_bf16(v0, v1);
+                        }
+                        const int n = n0 + col;
+                        if (vec32 && n + 16 <= p.N) {
+                            stg_stream_256(yrow + col, o);
+                        } else {
+                            if (n + 8 <= p.N)
+                                stg_stream_128(yrow + col, make_uint4(o.v[0], o.v[1], o.v[2], o.v[3]));
+                            if (n + 16 <= p.N)
+                                stg_stream_128(yrow + col + 8, make_uint4(o.v[4], o.v[5], o.v[6], o.v[7]));
+                        }
+                    }
+                }
+            }
+            tc::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(tc::smem_u32(&sh->tmem_empty[acc]));
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    if (*abort_flag) {
+        // a role gave up: let copies still in flight land before the CTA retires
+        for (int i = 0; i < 64; i++) __nanosleep(20000);
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::tc_fence_after();
+    if (warp == 1) tc::tmem_dealloc(tmem_base, TMEM_COLS);
+    if (threadIdx.x == 0 && *abort_flag && p.status) atomicCAS(p.status, 0, *abort_flag);
+}
+
+// ---- exact expansion of weight codes to bf16 (workspace fill) -------------------------
+// 16 codes -> 16 bf16 per thread step; E4M3 / E5M2 values have at most 3 mantissa bits, so the
+// conversion through fp16 -> fp32 -> bf16 is exact.
+template <int FMT>
+__global__ void __launch_bounds__(256)
+expand_fp8_to_bf16_kernel(const uint8_t* __restrict__ src, uint16_t* __restrict__ dst, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const size_t packets = n / 16;
+    for (size_t pk = (size_t)blockIdx.x * blockDim.x + threadIdx.x; pk < packets; pk += stride) {
+        uint4 in = ldg_stream_128(src + pk * 16);
+        const uint32_t w[4] = {in.x, in.y, in.z, in.w};
+        u32x8 o;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            uint32_t h01, h23;
+            if (FMT == NVQ_E4M3) {
+                asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h01) : "h"((uint16_t)(w[i] & 0xFFFFu)));
+                asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h23) : "h"((uint16_t)(w[i] >> 16)));
+            } else {
+                h01 = __byte_perm(w[i], 0u, 0x1404);
+                h23 = __byte_perm(w[i], 0u, 0x3424);
+            }
+            float f0, f1, f2, f3;
+            asm("cvt.f32.f16 %0, %1;" : "=f"(f0) : "h"((uint16_t)(h01 & 0xFFFFu)));
+            asm("cvt.f32.f16 %0, %1;" : "=f"(f1) : "h"((uint16_t)(h01 >> 16)));
+            asm("cvt.f32.f16 %0, %1;" : "=f"(f2) : "h"((uint16_t)(h23 & 0xFFFFu)));
+            asm("cvt.f32.f16 %0, %1;" : "=f"(f3) : "h"((uint16_t)(h23 >> 16)));
+            o.v[2 * i] = pack_bf16(f0, f1);
+            o.v[2 * i + 1] = pack_bf16(f2, f3);
+        }
+        stg_stream_256(dst + pk * 16, o);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+int* g_status_host[64];   // mapped pinned words, one per device
+int* g_status_dev[64];
+
+nvq_status status_word(int device, int** dev_ptr) {
+    if (!g_status_host[device]) {
+        NVQ_CUDA(cudaHostAlloc((void**)&g_status_host[device], sizeof(int), cudaHostAllocMapped));
+        *g_status_host[device] = 0;
+        NVQ_CUDA(cudaHostGetDevicePointer((void**)&g_status_dev[device], g_status_host[device], 0));
+    }
+    *dev_ptr = g_status_dev[device];
+    return NVQ_OK;
+}
+
+}  // namespace
+
+nvq_status nvq_make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                            uint32_t box_rows, uint32_t box_cols, int elem_bytes) {
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        NVQ_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+        if (!fn || q != cudaDriverEntryPointSuccess)
+            NVQ_FAIL(NVQ_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+        g_encode = (EncodeTiledFn)fn;
+    }
+    NVQ_REQUIRE(nvq_aligned(base, 16), "tensor base must be 16-byte aligned");
+    NVQ_REQUIRE((cols * elem_bytes) % 16 == 0, "row pitch (%llu bytes) must be a multiple of 16",
+                (unsigned long long)(cols * elem_bytes));
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * (uint64_t)elem_bytes};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                             : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    CUresult r = g_encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) NVQ_FAIL(NVQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    return NVQ_OK;
+}
+
+// Y = bf16(scale_n * X @ Wd^T + bias_n) with Wd already expanded to bf16 (N x K).
+nvq_status nvq_linear_bf16_launch(uint16_t* d_y, const uint16_t* d_x, const uint16_t* d_w_bf16,
+                                  const float* d_scales, const float* d_bias, size_t M, size_t N,
+                                  size_t K, int device, cudaStream_t st) {
+    NVQ_REQUIRE(K % 8 == 0 && N % 8 == 0, "nvq_linear_fwd: K (%zu) and N (%zu) must be multiples of 8", K, N);
+    NVQ_REQUIRE(nvq_aligned(d_y, 32), "nvq_linear_fwd: Y must be 32-byte aligned");
+    NVQ_REQUIRE(M < (1u << 31) && N < (1u << 31) && K < (1u << 31), "nvq_linear_fwd: dimension too large");
+    CUtensorMap map_a, map_b;
+    nvq_status s = nvq_make_tmap_2d(&map_a, d_x, M, K, BM, BK, 2);
+    if (s != NVQ_OK) return s;
+    s = nvq_make_tmap_2d(&map_b, d_w_bf16, N, K, BN, BK, 2);
+    if (s != NVQ_OK) return s;
+    static bool attr_set[64];
+    if (!attr_set[device]) {
+        NVQ_CUDA(cudaFuncSetAttribute(linear_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        attr_set[device] = true;
+    }
+    Params p;
+    p.y = d_y;
+    p.scales = d_scales;
+    p.bias = d_bias;
+    p.M = (int)M;
+    p.N = (int)N;
+    p.K = (int)K;
+    p.m_blocks = (int)((M + BM - 1) / BM);
+    p.n_blocks = (int)((N + BN - 1) / BN);
+    s = status_word(device, &p.status);
+    if (s != NVQ_OK) return s;
+    int tiles = p.m_blocks * p.n_blocks;
+    int sms = nvq_sm_count(device);
+    int grid = tiles < sms ? tiles : sms;
+    linear_tc_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+    NVQ_LAUNCHED();
+    return NVQ_OK;
+}
+
+extern "C" nvq_status nvq_linear_workspace_bytes(size_t N, size_t K, nvq_dtype w_fmt, size_t* bytes) {
+    NVQ_REQUIRE(bytes, "null out pointer");
+    NVQ_REQUIRE(w_fmt == NVQ_E4M3 || w_fmt == NVQ_E5M2 || w_fmt == NVQ_E2M1_B32,
+                "nvq_linear_workspace_bytes: unsupported weight format %d", (int)w_fmt);
+    *bytes = N * K * 2;
+    return NVQ_OK;
+}
+
+extern "C" nvq_status nvq_device_error_flag(int device, int* flag) {
+    NVQ_REQUIRE(flag && device >= 0 && device < 64, "bad argument");
+    *flag = 0;
+    if (g_status_host[device]) {
+        *flag = *(volatile int*)g_status_host[device];
+        *(volatile int*)g_status_host[device] = 0;
+    }
+    return NVQ_OK;
+}
+
+extern "C" nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf16,
+                                     const uint8_t* d_wq, nvq_dtype w_fmt, const float* d_w_scales,
+                                     const float* d_bias, size_t M, size_t N, size_t K,
+                                     void* d_workspace, size_t workspace_bytes, int device,
+                                     void* stream) {
+    NVQ_REQUIRE(d_y_bf16 && d_x_bf16 && d_wq && d_w_scales, "nvq_linear_fwd: null buffer");
+    NVQ_REQUIRE(M > 0 && N > 0 && K > 0, "nvq_linear_fwd: empty problem");
+    NVQ_REQUIRE(w_fmt == NVQ_E4M3 || w_fmt == NVQ_E5M2 || w_fmt == NVQ_E2M1_B32,
+                "nvq_linear_fwd: unsupported weight format %d", (int)w_fmt);
+    NVQ_REQUIRE(d_workspace && workspace_bytes >= N * K * 2 && nvq_aligned(d_workspace, 32),
+                "nvq_linear_fwd: workspace of %zu bytes (32-byte aligned) required", N * K * 2);
+    nvq_status s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    cudaStream_t st = (cudaStream_t)stream;
+    uint16_t* wd = (uint16_t*)d_workspace;
+    const float* chan_scales = d_w_scales;
+    if (w_fmt == NVQ_E2M1_B32) {
+        // block scales vary along K, so they are folded into the expanded weight:
+        // Wd = bf16(e2m1_value * scale_block); no per-channel factor is left
+        NVQ_REQUIRE(K % 32 == 0, "nvq_linear_fwd: K (%zu) must be a multiple of 32 for E2M1_B32", K);
+        s = nvq_dequantize_fp4_b32(wd, d_wq, d_w_scales, N, K, device, stream);
+        if (s != NVQ_OK) return s;
+        chan_scales = nullptr;
+    } else {
+        NVQ_REQUIRE((N * K) % 16 == 0 && nvq_aligned(d_wq, 16),
+                    "nvq_linear_fwd: weight codes must be 16-byte aligned, N*K a multiple of 16");
+        size_t packets = N * K / 16;
+        size_t want = (packets + 255) / 256, cap = (size_t)nvq_sm_count(device) * 8;
+        unsigned grid = (unsigned)(want < cap ? want : cap);
+        if (w_fmt == NVQ_E4M3)
+            expand_fp8_to_bf16_kernel<NVQ_E4M3><<<grid, 256, 0, st>>>(d_wq, wd, N * K);
+        else
+            expand_fp8_to_bf16_kernel<NVQ_E5M2><<<grid, 256, 0, st>>>(d_wq, wd, N * K);
+        NVQ_LAUNCHED();
+    }
+    return nvq_linear_bf16_launch(d_y_bf16, d_x_bf16, wd, chan_scales, d_bias, M, N, K, device, st);
+}

@@ -1,0 +1,95 @@
+"""FP8 / FP4-weight Linear forward on the tensor cores against the oracle.
+
+Parity metric (written here because the spec only says "max-abs-rel"):
+``max|y - y_ref| / max|y_ref|`` <= 1e-2 for FP8 weights and <= 5e-2 for FP4, where
+y_ref is the oracle's bf16 output from a float64 contraction of the same codes.
+In practice the only differences are fp32 accumulation order and one bf16 rounding,
+so the tests also assert a much tighter bound (a few bf16 ulps of the largest output).
+"""
+import numpy as np
+import pytest
+
+from novann_b200 import functional as F, workloads
+from oracle import oracle_np as o
+
+pytestmark = pytest.mark.gpu
+
+FP8_TOL = 1e-2
+FP4_TOL = 5e-2
+
+
+def _run_fp8(gpu, m, n, k, fmt="e4m3", seed=0, bias=True):
+    xb, w, b = workloads.linear_inputs(m, n, k, seed=seed)
+    wq, sc = o.quantize_weight_per_channel(w, fmt)
+    y = F.linear_q_host(xb, wq, sc, b if bias else None, fmt, gpu)
+    want_bits, want_f32 = o.linear_fwd_qweight(xb, wq, sc, b if bias else None, fmt)
+    err = o.max_abs_rel(o.bf16_bits_to_f32(y), o.bf16_bits_to_f32(want_bits))
+    return err, y, want_bits
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 256), (256, 512, 512),
+                                   (384, 768, 1024)])
+def test_linear_fp8_tile_multiples(gpu, m, n, k):
+    err, y, want = _run_fp8(gpu, m, n, k)
+    assert err <= FP8_TOL
+    assert err <= 2.0 ** -7, err  # two bf16 ulps of the largest output
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 8, 8), (5, 24, 40), (130, 264, 72), (200, 1000, 328),
+                                   (1024, 16, 144), (77, 4096, 512)])
+def test_linear_fp8_ragged_shapes(gpu, m, n, k):
+    err, y, want = _run_fp8(gpu, m, n, k, seed=m)
+    assert y.shape == (m, n)
+    assert err <= 2.0 ** -7, err
+
+
+def test_linear_e5m2_and_no_bias(gpu):
+    err, _, _ = _run_fp8(gpu, 256, 256, 512, fmt="e5m2", bias=False)
+    assert err <= 2.0 ** -7
+
+
+def test_linear_matches_reference_path_tolerance(gpu):
+    """Against what the reference itself would compute: F.linear in fp32 on the
+    dequantised weight (NumPy sgemm), rounded to bf16."""
+    xb, w, b = workloads.linear_inputs(512, 1024, 2048, seed=3)
+    wq, sc = o.quantize_weight_per_channel(w, "e4m3")
+    y = o.bf16_bits_to_f32(F.linear_q_host(xb, wq, sc, b, "e4m3", gpu))
+    wd = o.E4M3_TABLE[wq] * sc[:, None]
+    ref = o.linear_fwd_f32(o.bf16_bits_to_f32(xb), wd, b)
+    assert o.max_abs_rel(y, ref) <= FP8_TOL
+
+
+def test_linear_fp4_block_scaled_weight(gpu):
+    xb, w, b = workloads.linear_inputs(256, 512, 1024, seed=5)
+    w_bits = o.f32_to_bf16_bits(w).reshape(w.shape)
+    packed, scales = o.quantize_fp4_b32(w_bits)
+    y = o.bf16_bits_to_f32(F.linear_q_host(xb, packed, scales, b, "e2m1_b32", gpu))
+    wd = o.dequantize_fp4_weight(packed, scales)
+    ref = o.bf16_bits_to_f32(xb).astype(np.float64) @ wd.astype(np.float64).T + b
+    assert o.max_abs_rel(y, ref) <= FP4_TOL
+    assert o.max_abs_rel(y, ref) <= 2.0 ** -6
+
+
+def test_linear_config_size(gpu):
+    """M = N = K = 4096, the benchmark configuration, checked on sampled rows against a
+    float64 contraction (a full CPU GEMM of this size takes too long for a test)."""
+    m = n = k = 4096
+    xb, w, b = workloads.linear_inputs(m, n, k, seed=0)
+    wq, sc = o.quantize_weight_per_channel(w, "e4m3")
+    y = F.linear_q_host(xb, wq, sc, b, "e4m3", gpu)
+    rows = np.array([0, 1, 127, 128, 1000, 2047, 2048, 4095])
+    want_bits, _ = o.linear_fwd_qweight(xb[rows], wq, sc, b, "e4m3")
+    err = o.max_abs_rel(o.bf16_bits_to_f32(y[rows]), o.bf16_bits_to_f32(want_bits))
+    assert err <= 2.0 ** -7, err
+    # linearity in the bias: a second run with bias 0 differs by ~b (bf16 rounding aside)
+    y0 = F.linear_q_host(xb[:128], wq, sc, None, "e4m3", gpu)
+    d = o.bf16_bits_to_f32(y[:128]) - o.bf16_bits_to_f32(y0)
+    assert np.max(np.abs(d - b[None, :])) <= 2.0 ** -6 * np.max(np.abs(o.bf16_bits_to_f32(y0)))
+
+
+def test_linear_argument_validation(gpu):
+    from novann_b200 import _lib
+    xb, w, b = workloads.linear_inputs(16, 12, 64, seed=0)   # N = 12 is not a multiple of 8
+    wq, sc = o.quantize_weight_per_channel(w, "e4m3")
+    with pytest.raises(_lib.NvqError):
+        F.linear_q_host(xb, wq, sc, b, "e4m3", gpu)
