@@ -50,8 +50,27 @@ struct Params {
     const float* bias;     // N or nullptr (= 0)
     int M, N, K;
     int m_blocks, n_blocks;
+    int num_big;           // work items [0, num_big) are 128 x 256 tiles
+    int num_items;         // items [num_big, num_items) are 128 x 128 halves of the remaining tiles
     int* status;           // mapped host word: first non-zero give-up code
 };
+
+// Work item -> tile.  The tiles that would form a partial last wave are cut into two
+// 128-column halves so that wave spreads over (almost) every SM instead of half of them.
+struct Tile { int m0, n0, bn; };
+__device__ __forceinline__ Tile tile_of(const Params& p, int item) {
+    int big = item, half = 0, bn = BN;
+    if (item >= p.num_big) {
+        big = p.num_big + ((item - p.num_big) >> 1);
+        half = (item - p.num_big) & 1;
+        bn = BN / 2;
+    }
+    Tile t;
+    t.m0 = (big % p.m_blocks) * BM;
+    t.n0 = (big / p.m_blocks) * BN + half * (BN / 2);
+    t.bn = bn;
+    return t;
+}
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     uint32_t r;
@@ -81,7 +100,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const uint32_t tiles = (raw + 1023u) & ~1023u;          // 1024-byte aligned tile ring
     Shared* sh = (Shared*)(smem_raw + (tiles - raw) + STAGES * STAGE_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_tiles = p.m_blocks * p.n_blocks;
+    const int num_tiles = p.num_items;
     const int num_kb = (p.K + BK - 1) / BK;
     volatile int* abort_flag = &sh->abort_flag;
 
@@ -114,15 +133,19 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-                const int m0 = (t % p.m_blocks) * BM, n0 = (t / p.m_blocks) * BN;
+                const Tile tl = tile_of(p, t);
                 for (int kb = 0; kb < num_kb; kb++) {
                     ok = tc::mbar_wait(tc::smem_u32(&sh->empty[stage]), phase ^ 1, abort_flag, ERR_PRODUCER);
                     if (!ok) break;
                     const uint32_t bar = tc::smem_u32(&sh->full[stage]);
                     const uint32_t a_dst = tiles + stage * STAGE_BYTES;
-                    tc::mbar_arrive_expect_tx(bar, STAGE_BYTES);
-                    tc::tma_load_2d(a_dst, &map_a, bar, kb * BK, m0);
-                    tc::tma_load_2d(a_dst + A_BYTES, &map_b, bar, kb * BK, n0);
+                    // B arrives as 128-row boxes; 256 rows are two boxes back to back, which is
+                    // the same shared-memory image as one 256-row tile
+                    tc::mbar_arrive_expect_tx(bar, A_BYTES + (tl.bn / 128) * (B_BYTES / 2));
+                    tc::tma_load_2d(a_dst, &map_a, bar, kb * BK, tl.m0);
+                    tc::tma_load_2d(a_dst + A_BYTES, &map_b, bar, kb * BK, tl.n0);
+                    if (tl.bn == BN)
+                        tc::tma_load_2d(a_dst + A_BYTES + B_BYTES / 2, &map_b, bar, kb * BK, tl.n0 + 128);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -130,7 +153,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = tc::idesc_f16(BM, BN, 1, 1);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             int it = 0;
@@ -140,6 +162,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (!ok) break;
                 tc::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
+                const uint32_t idesc = tc::idesc_f16(BM, tile_of(p, t).bn, 1, 1);
                 for (int kb = 0; kb < num_kb; kb++) {
                     ok = tc::mbar_wait(tc::smem_u32(&sh->full[stage]), phase, abort_flag, ERR_MMA_FULL);
                     if (!ok) break;
@@ -167,9 +190,10 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         int it = 0;
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, it++) {
             const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
-            const int m0 = (t % p.m_blocks) * BM, n0 = (t / p.m_blocks) * BN;
+            const Tile tl = tile_of(p, t);
+            const int m0 = tl.m0, n0 = tl.n0;
             // per-tile scale / bias into shared memory (two columns per thread)
-            for (int c = et; c < BN; c += 128) {
+            for (int c = et; c < tl.bn; c += 128) {
                 int n = n0 + c;
                 sh->scale[acc][c] = (p.scales && n < p.N) ? p.scales[n] : 1.f;
                 sh->bias[acc][c] = (p.bias && n < p.N) ? p.bias[n] : 0.f;
@@ -184,7 +208,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             uint16_t* yrow = p.y + (size_t)row * p.N + n0;
             const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
+            for (int c = 0; c < tl.bn; c += 32) {
                 uint32_t r[32];
                 tc::tmem_ld_32x32(taddr + c, r);
                 tc::tmem_ld_wait();
@@ -321,7 +345,7 @@ nvq_status nvq_linear_bf16_launch(uint16_t* d_y, const uint16_t* d_x, const uint
     CUtensorMap map_a, map_b;
     nvq_status s = nvq_make_tmap_2d(&map_a, d_x, M, K, BM, BK, 2);
     if (s != NVQ_OK) return s;
-    s = nvq_make_tmap_2d(&map_b, d_w_bf16, N, K, BN, BK, 2);
+    s = nvq_make_tmap_2d(&map_b, d_w_bf16, N, K, BN / 2, BK, 2);
     if (s != NVQ_OK) return s;
     static bool attr_set[64];
     if (!attr_set[device]) {
@@ -342,6 +366,11 @@ nvq_status nvq_linear_bf16_launch(uint16_t* d_y, const uint16_t* d_x, const uint
     int tiles = p.m_blocks * p.n_blocks;
     int sms = nvq_sm_count(device);
     int grid = tiles < sms ? tiles : sms;
+    // a partial last wave that would occupy at most half of the CTAs is cut into halves
+    int rem = tiles % grid;
+    int split = (tiles > grid && rem > 0 && 2 * rem <= grid) ? rem : 0;
+    p.num_big = tiles - split;
+    p.num_items = p.num_big + 2 * split;
     linear_tc_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
     NVQ_LAUNCHED();
     return NVQ_OK;

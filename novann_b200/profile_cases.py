@@ -1,0 +1,99 @@
+"""Small, self-ending cases of each kernel for profiler captures.
+
+    python -m novann_b200.profile_cases cast   [log2_elems=26]
+    python -m novann_b200.profile_cases fp8    [rows=8192]
+    python -m novann_b200.profile_cases fp4    [rows=8192]
+    python -m novann_b200.profile_cases linear [M=4096 N=4096 K=4096]
+
+Each case uploads seeded inputs, launches the kernels a few times and exits; sizes are
+larger than the 126 MB L2 (so DRAM counters mean something) but hold at most a few GB.
+"""
+from __future__ import annotations
+
+import sys
+
+import numpy as np
+
+from . import functional as F, quant, workloads
+from .device import DeviceBuffer, Stream, device_sync
+
+
+def case_cast(log2n: int = 26, reps: int = 3) -> None:
+    n = 1 << log2n
+    st = Stream(0)
+    x = workloads.cast_input(n, seed=0)
+    d32 = DeviceBuffer.from_numpy(x, 0)
+    d16 = DeviceBuffer(n * 2, 0)
+    for _ in range(reps):
+        quant.cast_device(d16, "bf16", d32, "f32", n, stream=st)
+        quant.cast_device(d32, "f32", d16, "bf16", n, stream=st)
+        quant.cast_device(d16, "f16", d32, "f32", n, stream=st)
+        quant.cast_device(d32, "f32", d16, "f16", n, stream=st)
+    st.sync()
+
+
+def case_fp8(rows: int = 8192, reps: int = 3) -> None:
+    cols = 8192
+    n = rows * cols
+    st = Stream(0)
+    x = workloads.fp8_input(rows, cols, seed=0)
+    d = DeviceBuffer.from_numpy(x, 0)
+    q = DeviceBuffer(n, 0)
+    asi = DeviceBuffer(12, 0)
+    for _ in range(reps):
+        quant.quantize_fp8_tensor_device(q, asi, d, n, "e4m3", stream=st)
+        quant.dequantize_fp8_device(d, q, n, "e4m3", 0.01, stream=st)
+    st.sync()
+
+
+def case_fp4(rows: int = 8192, reps: int = 3) -> None:
+    cols = 8192
+    st = Stream(0)
+    xb = workloads.fp4_input_bits(rows, cols, seed=0)
+    d = DeviceBuffer.from_numpy(xb, 0)
+    p = DeviceBuffer(rows * cols // 2, 0)
+    s = DeviceBuffer(rows * cols // 32 * 4, 0)
+    for _ in range(reps):
+        quant.quantize_fp4_b32_device(p, s, d, rows, cols, stream=st)
+        quant.dequantize_fp4_b32_device(d, p, s, rows, cols, stream=st)
+    st.sync()
+
+
+def case_linear(m: int = 4096, n: int = 4096, k: int = 4096, reps: int = 3) -> None:
+    st = Stream(0)
+    xb, w, b = workloads.linear_inputs(m, n, k, seed=0)
+    # weight codes straight from a seeded generator (no oracle in the product path)
+    rng = np.random.default_rng(1)
+    wq = rng.integers(0, 0x7F, (n, k), dtype=np.uint64).astype(np.uint8)
+    wq |= (rng.integers(0, 2, (n, k), dtype=np.uint64).astype(np.uint8) << 7)
+    sc = np.full(n, 1e-3, np.float32)
+    dx = DeviceBuffer.from_numpy(xb, 0)
+    dw = DeviceBuffer.from_numpy(wq, 0)
+    ds = DeviceBuffer.from_numpy(sc, 0)
+    db = DeviceBuffer.from_numpy(b, 0)
+    dy = DeviceBuffer(m * n * 2, 0)
+    ws = DeviceBuffer(F.linear_workspace_bytes(n, k, "e4m3"), 0)
+    for _ in range(reps):
+        F.linear_q_device(dy, dx, dw, "e4m3", ds, db, m, n, k, ws, stream=st)
+    st.sync()
+    F.check_device_errors(0)
+
+
+def main(argv) -> None:
+    what = argv[1] if len(argv) > 1 else "cast"
+    args = [int(a) for a in argv[2:]]
+    if what == "cast":
+        case_cast(*args)
+    elif what == "fp8":
+        case_fp8(*args)
+    elif what == "fp4":
+        case_fp4(*args)
+    elif what == "linear":
+        case_linear(*args)
+    else:
+        raise SystemExit(f"unknown case {what}")
+    device_sync(0)
+
+
+if __name__ == "__main__":
+    main(sys.argv)
