@@ -15,7 +15,9 @@
 //               scale, bias, round, 32-byte global stores.  Two accumulators (2 x 256
 //               TMEM columns) let the epilogue of tile i overlap the main loop of tile i+1.
 // No TMA multicast and no peer memory anywhere: each CTA fetches its own tiles.
-#include "tc_common.cuh"
+#include <stdlib.h>
+
+#include "gemm_common.cuh"
 
 namespace {
 
@@ -44,57 +46,9 @@ struct Shared {            // lives after the tile ring
     float bias[2][BN];
 };
 
-struct Params {
-    uint16_t* y;
-    const float* scales;   // N or nullptr (= 1)
-    const float* bias;     // N or nullptr (= 0)
-    int M, N, K;
-    int m_blocks, n_blocks;
-    int num_big;           // work items [0, num_big) are 128 x 256 tiles
-    int num_items;         // items [num_big, num_items) are 128 x 128 halves of the remaining tiles
-    int* status;           // mapped host word: first non-zero give-up code
-};
-
-// Work item -> tile.  The tiles that would form a partial last wave are cut into two
-// 128-column halves so that wave spreads over (almost) every SM instead of half of them.
-struct Tile { int m0, n0, bn; };
-__device__ __forceinline__ Tile tile_of(const Params& p, int item) {
-    int big = item, half = 0, bn = BN;
-    if (item >= p.num_big) {
-        big = p.num_big + ((item - p.num_big) >> 1);
-        half = (item - p.num_big) & 1;
-        bn = BN / 2;
-    }
-    Tile t;
-    t.m0 = (big % p.m_blocks) * BM;
-    t.n0 = (big / p.m_blocks) * BN + half * (BN / 2);
-    t.bn = bn;
-    return t;
-}
-
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    uint32_t r;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
-}
-
-// AND-reduction + barrier over the 128 epilogue threads (named barrier 1)
-__device__ __forceinline__ bool epilogue_all(bool ok) {
-    uint32_t r;
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\t"
-        "setp.ne.b32 q, %1, 0;\n\t"
-        "bar.red.and.pred p, 1, 128, q;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(r)
-        : "r"((uint32_t)ok)
-        : "memory");
-    return r != 0;
-}
-
 __global__ void __launch_bounds__(THREADS, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 const Params p) {
+                 const LinearParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = tc::smem_u32(smem_raw);
     const uint32_t tiles = (raw + 1023u) & ~1023u;          // 1024-byte aligned tile ring
@@ -133,7 +87,9 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-                const Tile tl = tile_of(p, t);
+                const TileRef tr = tile_ref(p, t);
+                const int bn = tr.is_half ? BN / 2 : BN;
+                const int m0 = tr.m_blk * BM, n0 = tr.n_blk * BN + tr.half * (BN / 2);
                 for (int kb = 0; kb < num_kb; kb++) {
                     ok = tc::mbar_wait(tc::smem_u32(&sh->empty[stage]), phase ^ 1, abort_flag, ERR_PRODUCER);
                     if (!ok) break;
@@ -141,11 +97,11 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const uint32_t a_dst = tiles + stage * STAGE_BYTES;
                     // B arrives as 128-row boxes; 256 rows are two boxes back to back, which is
                     // the same shared-memory image as one 256-row tile
-                    tc::mbar_arrive_expect_tx(bar, A_BYTES + (tl.bn / 128) * (B_BYTES / 2));
-                    tc::tma_load_2d(a_dst, &map_a, bar, kb * BK, tl.m0);
-                    tc::tma_load_2d(a_dst + A_BYTES, &map_b, bar, kb * BK, tl.n0);
-                    if (tl.bn == BN)
-                        tc::tma_load_2d(a_dst + A_BYTES + B_BYTES / 2, &map_b, bar, kb * BK, tl.n0 + 128);
+                    tc::mbar_arrive_expect_tx(bar, A_BYTES + (bn / 128) * (B_BYTES / 2));
+                    tc::tma_load_2d(a_dst, &map_a, bar, kb * BK, m0);
+                    tc::tma_load_2d(a_dst + A_BYTES, &map_b, bar, kb * BK, n0);
+                    if (bn == BN)
+                        tc::tma_load_2d(a_dst + A_BYTES + B_BYTES / 2, &map_b, bar, kb * BK, n0 + 128);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -162,7 +118,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (!ok) break;
                 tc::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                const uint32_t idesc = tc::idesc_f16(BM, tile_of(p, t).bn, 1, 1);
+                const uint32_t idesc = tc::idesc_f16(BM, tile_ref(p, t).is_half ? BN / 2 : BN, 1, 1);
                 for (int kb = 0; kb < num_kb; kb++) {
                     ok = tc::mbar_wait(tc::smem_u32(&sh->full[stage]), phase, abort_flag, ERR_MMA_FULL);
                     if (!ok) break;
@@ -190,10 +146,11 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         int it = 0;
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, it++) {
             const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
-            const Tile tl = tile_of(p, t);
-            const int m0 = tl.m0, n0 = tl.n0;
+            const TileRef tr = tile_ref(p, t);
+            const int bn = tr.is_half ? BN / 2 : BN;
+            const int m0 = tr.m_blk * BM, n0 = tr.n_blk * BN + tr.half * (BN / 2);
             // per-tile scale / bias into shared memory (two columns per thread)
-            for (int c = et; c < tl.bn; c += 128) {
+            for (int c = et; c < bn; c += 128) {
                 int n = n0 + c;
                 sh->scale[acc][c] = (p.scales && n < p.N) ? p.scales[n] : 1.f;
                 sh->bias[acc][c] = (p.bias && n < p.N) ? p.bias[n] : 0.f;
@@ -208,33 +165,12 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             uint16_t* yrow = p.y + (size_t)row * p.N + n0;
             const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
-            for (int c = 0; c < tl.bn; c += 32) {
+            for (int c = 0; c < bn; c += 32) {
                 uint32_t r[32];
                 tc::tmem_ld_32x32(taddr + c, r);
                 tc::tmem_ld_wait();
-                if (row < p.M) {
-#pragma unroll
-                    for (int g = 0; g < 2; g++) {      // two groups of 16 columns
-                        const int col = c + g * 16;
-                        u32x8 o;
-#pragma unroll
-                        for (int j = 0; j < 8; j++) {
-                            const int cc = col + 2 * j;
-                            float v0 = fmaf(__uint_as_float(r[g * 16 + 2 * j]), sh->scale[acc][cc], sh->bias[acc][cc]);
-                            float v1 = fmaf(__uint_as_float(r[g * 16 + 2 * j + 1]), sh->scale[acc][cc + 1], sh->bias[acc][cc + 1]);
-                            o.v[j] = pack_bf16(v0, v1);
-                        }
-                        const int n = n0 + col;
-                        if (vec32 && n + 16 <= p.N) {
-                            stg_stream_256(yrow + col, o);
-                        } else {
-                            if (n + 8 <= p.N)
-                                stg_stream_128(yrow + col, make_uint4(o.v[0], o.v[1], o.v[2], o.v[3]));
-                            if (n + 16 <= p.N)
-                                stg_stream_128(yrow + col + 8, make_uint4(o.v[4], o.v[5], o.v[6], o.v[7]));
-                        }
-                    }
-                }
+                if (row < p.M)
+                    store_chunk(r, &sh->scale[acc][c], &sh->bias[acc][c], yrow + c, n0 + c, p.N, vec32);
             }
             tc::tc_fence_before();
             __syncwarp();
@@ -297,7 +233,9 @@ EncodeTiledFn g_encode = nullptr;
 int* g_status_host[64];   // mapped pinned words, one per device
 int* g_status_dev[64];
 
-nvq_status status_word(int device, int** dev_ptr) {
+}  // namespace
+
+nvq_status nvq_status_word(int device, int** dev_ptr) {
     if (!g_status_host[device]) {
         NVQ_CUDA(cudaHostAlloc((void**)&g_status_host[device], sizeof(int), cudaHostAllocMapped));
         *g_status_host[device] = 0;
@@ -306,8 +244,6 @@ nvq_status status_word(int device, int** dev_ptr) {
     *dev_ptr = g_status_dev[device];
     return NVQ_OK;
 }
-
-}  // namespace
 
 nvq_status nvq_make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
                             uint32_t box_rows, uint32_t box_cols, int elem_bytes) {
@@ -335,13 +271,9 @@ nvq_status nvq_make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, u
     return NVQ_OK;
 }
 
-// Y = bf16(scale_n * X @ Wd^T + bias_n) with Wd already expanded to bf16 (N x K).
-nvq_status nvq_linear_bf16_launch(uint16_t* d_y, const uint16_t* d_x, const uint16_t* d_w_bf16,
-                                  const float* d_scales, const float* d_bias, size_t M, size_t N,
-                                  size_t K, int device, cudaStream_t st) {
-    NVQ_REQUIRE(K % 8 == 0 && N % 8 == 0, "nvq_linear_fwd: K (%zu) and N (%zu) must be multiples of 8", K, N);
-    NVQ_REQUIRE(nvq_aligned(d_y, 32), "nvq_linear_fwd: Y must be 32-byte aligned");
-    NVQ_REQUIRE(M < (1u << 31) && N < (1u << 31) && K < (1u << 31), "nvq_linear_fwd: dimension too large");
+nvq_status nvq_linear_launch_single(uint16_t* d_y, const uint16_t* d_x, const uint16_t* d_w_bf16,
+                                    const float* d_scales, const float* d_bias, size_t M, size_t N,
+                                    size_t K, int device, cudaStream_t st) {
     CUtensorMap map_a, map_b;
     nvq_status s = nvq_make_tmap_2d(&map_a, d_x, M, K, BM, BK, 2);
     if (s != NVQ_OK) return s;
@@ -352,7 +284,7 @@ nvq_status nvq_linear_bf16_launch(uint16_t* d_y, const uint16_t* d_x, const uint
         NVQ_CUDA(cudaFuncSetAttribute(linear_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         attr_set[device] = true;
     }
-    Params p;
+    LinearParams p;
     p.y = d_y;
     p.scales = d_scales;
     p.bias = d_bias;
@@ -361,7 +293,8 @@ nvq_status nvq_linear_bf16_launch(uint16_t* d_y, const uint16_t* d_x, const uint
     p.K = (int)K;
     p.m_blocks = (int)((M + BM - 1) / BM);
     p.n_blocks = (int)((N + BN - 1) / BN);
-    s = status_word(device, &p.status);
+    p.group_m = 16;
+    s = nvq_status_word(device, &p.status);
     if (s != NVQ_OK) return s;
     int tiles = p.m_blocks * p.n_blocks;
     int sms = nvq_sm_count(device);
@@ -374,6 +307,24 @@ nvq_status nvq_linear_bf16_launch(uint16_t* d_y, const uint16_t* d_x, const uint
     linear_tc_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
     NVQ_LAUNCHED();
     return NVQ_OK;
+}
+
+// Y = bf16(scale_n * X @ Wd^T + bias_n) with Wd already expanded to bf16 (N x K).
+// More than 128 rows: CTA pairs on 256 x 256 tiles; otherwise one CTA per 128 x 256 tile.
+// NVQ_LINEAR_MODE=single|pair overrides the choice (for measurements).
+nvq_status nvq_linear_bf16_launch(uint16_t* d_y, const uint16_t* d_x, const uint16_t* d_w_bf16,
+                                  const float* d_scales, const float* d_bias, size_t M, size_t N,
+                                  size_t K, int device, cudaStream_t st) {
+    NVQ_REQUIRE(K % 8 == 0 && N % 8 == 0, "nvq_linear_fwd: K (%zu) and N (%zu) must be multiples of 8", K, N);
+    NVQ_REQUIRE(nvq_aligned(d_y, 32), "nvq_linear_fwd: Y must be 32-byte aligned");
+    NVQ_REQUIRE(M < (1u << 31) && N < (1u << 31) && K < (1u << 31), "nvq_linear_fwd: dimension too large");
+    bool pair = M > 128;
+    if (const char* mode = getenv("NVQ_LINEAR_MODE")) {
+        if (mode[0] == 's') pair = false;
+        if (mode[0] == 'p') pair = true;
+    }
+    if (pair) return nvq_linear_launch_pair(d_y, d_x, d_w_bf16, d_scales, d_bias, M, N, K, device, st);
+    return nvq_linear_launch_single(d_y, d_x, d_w_bf16, d_scales, d_bias, M, N, K, device, st);
 }
 
 extern "C" nvq_status nvq_linear_workspace_bytes(size_t N, size_t K, nvq_dtype w_fmt, size_t* bytes) {

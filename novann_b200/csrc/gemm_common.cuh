@@ -1,0 +1,97 @@
+// Pieces shared by the single-CTA and the CTA-pair Linear kernels.
+#pragma once
+
+#include "tc_common.cuh"
+
+struct LinearParams {
+    uint16_t* y;
+    const float* scales;   // N per-output-channel factors or nullptr (= 1)
+    const float* bias;     // N or nullptr (= 0)
+    int M, N, K;
+    int m_blocks, n_blocks;   // in units of the kernel's own tile
+    int num_big;              // work items [0, num_big) are full tiles
+    int num_items;            // items [num_big, num_items) are half-width tiles
+    int group_m;              // rasterisation: m-blocks per group
+    int* status;              // mapped host word: first non-zero give-up code
+};
+
+nvq_status nvq_status_word(int device, int** dev_ptr);
+
+// launchers (gemm.cu: one CTA per 128 x 256 tile; gemm_pair.cu: CTA pair per 256 x 256 tile)
+nvq_status nvq_linear_launch_single(uint16_t* d_y, const uint16_t* d_x, const uint16_t* d_w,
+                                    const float* d_scales, const float* d_bias, size_t M, size_t N,
+                                    size_t K, int device, cudaStream_t st);
+nvq_status nvq_linear_launch_pair(uint16_t* d_y, const uint16_t* d_x, const uint16_t* d_w,
+                                  const float* d_scales, const float* d_bias, size_t M, size_t N,
+                                  size_t K, int device, cudaStream_t st);
+
+#ifdef __CUDACC__
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// AND-reduction + barrier over the 128 epilogue threads (named barrier 1)
+__device__ __forceinline__ bool epilogue_all(bool ok) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "bar.red.and.pred p, 1, 128, q;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"((uint32_t)ok)
+        : "memory");
+    return r != 0;
+}
+
+// Work item -> tile origin.  Full tiles are walked in groups of `group_m` row blocks (all
+// column blocks of a group before the next group) so that the tiles in flight at any time
+// form a roughly square patch and share their A and B panels through L2.  The tiles that
+// would form a partial last wave are cut into two half-width tiles so that the wave
+// spreads over (almost) every CTA.
+struct TileRef { int m_blk, n_blk, half, is_half; };
+__device__ __forceinline__ TileRef tile_ref(const LinearParams& p, int item) {
+    TileRef t;
+    int big = item;
+    t.half = 0;
+    t.is_half = 0;
+    if (item >= p.num_big) {
+        big = p.num_big + ((item - p.num_big) >> 1);
+        t.half = (item - p.num_big) & 1;
+        t.is_half = 1;
+    }
+    const int per_group = p.group_m * p.n_blocks;
+    const int g = big / per_group, r = big % per_group;
+    const int first = g * p.group_m;
+    const int gsize = min(p.group_m, p.m_blocks - first);
+    t.m_blk = first + r % gsize;
+    t.n_blk = r / gsize;
+    return t;
+}
+
+// Epilogue of one 32-column chunk: 32 fp32 accumulators of this thread's row -> scale,
+// bias, bf16, global stores.  `vec32` = rows start on 32-byte boundaries.
+__device__ __forceinline__ void store_chunk(const uint32_t* r, const float* scale, const float* bias,
+                                            uint16_t* yrow, int n_base, int N, bool vec32) {
+#pragma unroll
+    for (int g = 0; g < 2; g++) {
+        u32x8 o;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int cc = g * 16 + 2 * j;
+            float v0 = fmaf(__uint_as_float(r[cc]), scale[cc], bias[cc]);
+            float v1 = fmaf(__uint_as_float(r[cc + 1]), scale[cc + 1], bias[cc + 1]);
+            o.v[j] = pack_bf16(v0, v1);
+        }
+        const int n = n_base + g * 16;
+        if (vec32 && n + 16 <= N) {
+            stg_stream_256(yrow + g * 16, o);
+        } else {
+            if (n + 8 <= N) stg_stream_128(yrow + g * 16, make_uint4(o.v[0], o.v[1], o.v[2], o.v[3]));
+            if (n + 16 <= N) stg_stream_128(yrow + g * 16 + 8, make_uint4(o.v[4], o.v[5], o.v[6], o.v[7]));
+        }
+    }
+}
+#endif
