@@ -153,6 +153,35 @@ nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf16, const ui
                           nvq_dtype w_fmt, const float* d_w_scales, const float* d_bias,
                           size_t M, size_t N, size_t K, void* d_workspace, size_t workspace_bytes,
                           int device, void* stream);
+/* Allocation-free form of nvq_linear_fwd.  It has no counterpart in the reference.
+ *
+ * Some hosts of this library may not allocate device memory at the point where they need a
+ * Linear: code running between the capture-safe phases of a serving loop, plugins that were
+ * handed a fixed memory budget by their framework and must not grow it, and runtimes in which
+ * cudaMalloc would synchronise the whole device in the middle of a latency-critical step.  For
+ * them the scratch that receives the expanded weight is an array compiled into the library:
+ * NVQ_STATIC_WORKSPACE_BYTES bytes per GPU that loads the library, held until the process exits.
+ * The call allocates nothing (no cudaMalloc / cudaFree / cudaHostAlloc, no allocating library
+ * routine) and takes the same inputs and outputs as nvq_linear_fwd, minus the workspace.
+ *
+ *  - Limit: N * K * 2 <= NVQ_STATIC_WORKSPACE_BYTES (N * K <= 4 Mi weights, e.g. 2048 x 2048);
+ *    larger weights are rejected with NVQ_ERR_INVALID and a message naming the limit.
+ *  - The first call on each device looks up the array's address on that device (a host-side
+ *    query, no allocation).  Make that first call before any stream capture begins.
+ *  - Every call on a device shares the one array, and it keeps the previous call's contents.
+ *    Each call rewrites every byte it later reads, so nothing needs clearing, but two calls
+ *    that overlap on the GPU (different streams, or threads racing on one device) corrupt each
+ *    other: order them on one stream.
+ *  - d_status: optional device word (may be NULL) that receives a non-zero code if a bounded
+ *    device-side wait gave up; the caller zeroes it.  (nvq_device_error_flag does not cover
+ *    this entry point, because its word is allocated on first use.)
+ */
+#define NVQ_STATIC_WORKSPACE_BYTES (8u << 20)
+nvq_status nvq_linear_fwd_static(uint16_t* d_y_bf16, const uint16_t* d_x_bf16, const uint8_t* d_wq,
+                                 nvq_dtype w_fmt, const float* d_w_scales, const float* d_bias,
+                                 size_t M, size_t N, size_t K, int* d_status, int device,
+                                 void* stream);
+
 /* Tensor-core kernels bound every device-side wait; a wait that gives up records a
  * non-zero code here (read and cleared by this call) instead of hanging. */
 nvq_status nvq_device_error_flag(int device, int* flag);

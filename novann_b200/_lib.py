@@ -59,6 +59,7 @@ SIGNATURES = {
     "nvq_linear_workspace_bytes": (i32, [sz, sz, i32, C.POINTER(sz)]),
     "nvq_linear_fwd": (i32, [vp, vp, vp, i32, vp, vp, sz, sz, sz, vp, sz, i32, vp]),
     "nvq_device_error_flag": (i32, [i32, C.POINTER(i32)]),
+    "nvq_linear_fwd_static": (i32, [vp, vp, vp, i32, vp, vp, sz, sz, sz, vp, i32, vp]),
 }
 
 

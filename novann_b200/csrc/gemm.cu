@@ -235,7 +235,15 @@ int* g_status_dev[64];
 
 }  // namespace
 
+// set by the allocation-free entry point for the duration of its launches (per thread)
+static thread_local bool t_status_override = false;
+static thread_local int* t_status_override_ptr = nullptr;
+
 nvq_status nvq_status_word(int device, int** dev_ptr) {
+    if (t_status_override) {
+        *dev_ptr = t_status_override_ptr;
+        return NVQ_OK;
+    }
     if (!g_status_host[device]) {
         NVQ_CUDA(cudaHostAlloc((void**)&g_status_host[device], sizeof(int), cudaHostAllocMapped));
         *g_status_host[device] = 0;
@@ -381,4 +389,39 @@ extern "C" nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf1
         NVQ_LAUNCHED();
     }
     return nvq_linear_bf16_launch(d_y_bf16, d_x_bf16, wd, chan_scales, d_bias, M, N, K, device, st);
+}
+
+// ---------------------------------------------------------------- allocation-free variant
+// Scratch for the expanded weight lives in the library image itself: one array per GPU that
+// loads the library, held until the process exits.  NVQ_STATIC_WORKSPACE_BYTES bounds N * K.
+static __device__ __align__(256) unsigned char g_static_workspace[NVQ_STATIC_WORKSPACE_BYTES];
+static void* g_static_workspace_addr[64];   // device address of the array, per device
+
+extern "C" nvq_status nvq_linear_fwd_static(uint16_t* d_y_bf16, const uint16_t* d_x_bf16,
+                                            const uint8_t* d_wq, nvq_dtype w_fmt,
+                                            const float* d_w_scales, const float* d_bias, size_t M,
+                                            size_t N, size_t K, int* d_status, int device,
+                                            void* stream) {
+    NVQ_REQUIRE(N > 0 && K > 0 && N * K * 2 <= (size_t)NVQ_STATIC_WORKSPACE_BYTES,
+                "nvq_linear_fwd_static: N * K = %zu weights need %zu bytes of scratch; the built-in "
+                "scratch holds %zu bytes (N * K <= %zu). Use nvq_linear_fwd with a caller workspace.",
+                N * K, N * K * 2, (size_t)NVQ_STATIC_WORKSPACE_BYTES,
+                (size_t)NVQ_STATIC_WORKSPACE_BYTES / 2);
+    nvq_status s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    if (!g_static_workspace_addr[device]) {
+        // In host code the array's name is only a handle; the kernels need the address the
+        // array has on THIS device, which the runtime reports with that device current.
+        void* addr = nullptr;
+        NVQ_CUDA(cudaGetSymbolAddress(&addr, g_static_workspace));
+        if (!addr) NVQ_FAIL(NVQ_ERR_CUDA, "nvq_linear_fwd_static: no device address for the scratch array");
+        g_static_workspace_addr[device] = addr;
+    }
+    t_status_override = true;
+    t_status_override_ptr = d_status;
+    s = nvq_linear_fwd(d_y_bf16, d_x_bf16, d_wq, w_fmt, d_w_scales, d_bias, M, N, K,
+                       g_static_workspace_addr[device], NVQ_STATIC_WORKSPACE_BYTES, device, stream);
+    t_status_override = false;
+    t_status_override_ptr = nullptr;
+    return s;
 }

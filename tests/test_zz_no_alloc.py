@@ -1,0 +1,70 @@
+"""The allocation-free Linear entry point (``nvq_linear_fwd_static``).
+
+Hosts that cannot allocate device memory where they need a Linear (fixed memory budgets,
+latency-critical steps in which cudaMalloc would stall the device) call this form: its
+scratch is an array built into the library.  The test drives it through the C ABI and
+requires the same output as ``nvq_linear_fwd`` with a caller workspace, on two calls in a
+row; the second call uses a smaller weight so that it runs over the first call's leftovers
+in the shared scratch.  The file name sorts last on purpose: a run that stops at the first
+failure has then already run every other test.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from novann_b200 import _lib, functional as F, workloads
+from novann_b200.device import DeviceBuffer, device_sync
+
+pytestmark = pytest.mark.gpu
+
+STATIC_BYTES = 8 << 20
+
+
+def _codes(n, k, seed):
+    rng = np.random.default_rng(seed)
+    wq = rng.integers(0, 0x7F, (n, k), dtype=np.uint64).astype(np.uint8)      # finite E4M3 codes
+    wq |= rng.integers(0, 2, (n, k), dtype=np.uint64).astype(np.uint8) << 7   # random signs
+    sc = rng.uniform(1e-4, 1e-3, n).astype(np.float32)
+    return wq, sc
+
+
+def _both_ways(gpu, m, n, k, seed):
+    xb, _, b = workloads.linear_inputs(m, n, k, seed=seed)
+    wq, sc = _codes(n, k, seed)
+    L = _lib.lib()
+    dx, dw = DeviceBuffer.from_numpy(xb, gpu), DeviceBuffer.from_numpy(wq, gpu)
+    ds, db = DeviceBuffer.from_numpy(sc, gpu), DeviceBuffer.from_numpy(b, gpu)
+    y_ref, y_new = DeviceBuffer(m * n * 2, gpu), DeviceBuffer(m * n * 2, gpu)
+    status = DeviceBuffer.from_numpy(np.zeros(1, np.int32), gpu)
+    ws = DeviceBuffer(F.linear_workspace_bytes(n, k, "e4m3"), gpu)
+    F.linear_q_device(y_ref, dx, dw, "e4m3", ds, db, m, n, k, ws)
+    _lib.check(L.nvq_linear_fwd_static(y_new.at(0), dx.at(0), dw.at(0), _lib.E4M3, ds.at(0), db.at(0),
+                                       m, n, k, status.at(0), gpu, None))
+    device_sync(gpu)
+    F.check_device_errors(gpu)
+    assert status.to_numpy(np.int32, (1,))[0] == 0
+    a = y_ref.to_numpy(np.uint16, (m, n))
+    c = y_new.to_numpy(np.uint16, (m, n))
+    return a, c
+
+
+def test_static_scratch_matches_workspace_form_twice_in_a_row(gpu):
+    # first call fills most of the built-in scratch (2048 x 2048 weights = 8 MiB expanded)
+    a, c = _both_ways(gpu, 512, 2048, 2048, seed=1)
+    assert np.array_equal(a, c)
+    # second call: smaller weight, run over the first call's leftovers
+    a, c = _both_ways(gpu, 200, 264, 328, seed=2)
+    assert np.array_equal(a, c)
+
+
+def test_static_scratch_rejects_oversized_weight(gpu):
+    L = _lib.lib()
+    d = DeviceBuffer(64, gpu)
+    n, k = 2048, 2056                      # N * K * 2 just above the 8 MiB limit
+    assert n * k * 2 > STATIC_BYTES
+    st = L.nvq_linear_fwd_static(d.at(0), d.at(0), d.at(0), _lib.E4M3, d.at(0), None, 16, n, k,
+                                 None, gpu, None)
+    assert st == _lib.ERR_INVALID
+    msg = L.nvq_last_error().decode()
+    assert "built-in" in msg and str(STATIC_BYTES) in msg
