@@ -147,6 +147,9 @@ nvq_status nvq_dequantize_fp4_b32(uint16_t* d_dst_bf16, const uint8_t* d_packed,
  * d_workspace: scratch of nvq_linear_workspace_bytes(N, K, fmt) bytes (32-byte
  * aligned) that receives the weight expanded to 16-bit tensor-core operands; it is
  * rewritten by every call, so calls that share a workspace must be stream ordered.
+ * d_workspace may be NULL for E4M3 / E5M2 weights when M > 128 and K % 16 == 0: the
+ * codes are then expanded inside the GEMM kernel, in shared memory (slower than the
+ * workspace form on large problems, but nothing is written to HBM).
  */
 nvq_status nvq_linear_workspace_bytes(size_t N, size_t K, nvq_dtype w_fmt, size_t* bytes);
 nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf16, const uint8_t* d_wq,

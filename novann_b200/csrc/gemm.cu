@@ -272,8 +272,11 @@ nvq_status nvq_make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, u
     cuuint32_t estr[2] = {1, 1};
     CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                              : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    // 16-bit operand tiles use the 128-byte swizzle the MMA descriptors name; byte tiles
+    // (raw codes read by converter warps) are stored linearly
     CUresult r = g_encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          elem_bytes == 2 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) NVQ_FAIL(NVQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
     return NVQ_OK;
@@ -294,6 +297,7 @@ nvq_status nvq_linear_launch_single(uint16_t* d_y, const uint16_t* d_x, const ui
     }
     LinearParams p;
     p.y = d_y;
+    p.wq = nullptr;
     p.scales = d_scales;
     p.bias = d_bias;
     p.M = (int)M;
@@ -362,11 +366,26 @@ extern "C" nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf1
     NVQ_REQUIRE(M > 0 && N > 0 && K > 0, "nvq_linear_fwd: empty problem");
     NVQ_REQUIRE(w_fmt == NVQ_E4M3 || w_fmt == NVQ_E5M2 || w_fmt == NVQ_E2M1_B32,
                 "nvq_linear_fwd: unsupported weight format %d", (int)w_fmt);
-    NVQ_REQUIRE(d_workspace && workspace_bytes >= N * K * 2 && nvq_aligned(d_workspace, 32),
-                "nvq_linear_fwd: workspace of %zu bytes (32-byte aligned) required", N * K * 2);
     nvq_status s = nvq_use_device(device);
     if (s != NVQ_OK) return s;
     cudaStream_t st = (cudaStream_t)stream;
+    // FP8 weights, more than one row block: the CTA-pair kernel can expand the codes in shared
+    // memory itself, so no expanded copy of the weight is written to HBM and no workspace is
+    // needed.  Measured on B200 it is slower than expansion pass + plain pair kernel (the
+    // converter warps' shared-memory traffic competes with the tensor core's operand reads),
+    // so it runs when the caller passes no workspace, or on request (NVQ_LINEAR_MODE=fused).
+    const char* mode = getenv("NVQ_LINEAR_MODE");
+    bool can_fuse = w_fmt != NVQ_E2M1_B32 && M > 128 && K % 16 == 0 && nvq_aligned(d_wq, 16);
+    bool fused = can_fuse && ((mode && mode[0] == 'f') || (!mode && d_workspace == nullptr));
+    if (fused) {
+        NVQ_REQUIRE(K % 8 == 0 && N % 8 == 0, "nvq_linear_fwd: K (%zu) and N (%zu) must be multiples of 8", K, N);
+        NVQ_REQUIRE(nvq_aligned(d_y_bf16, 32), "nvq_linear_fwd: Y must be 32-byte aligned");
+        NVQ_REQUIRE(M < (1u << 31) && N < (1u << 31) && K < (1u << 31), "nvq_linear_fwd: dimension too large");
+        return nvq_linear_launch_pair_fused(d_y_bf16, d_x_bf16, d_wq, w_fmt, d_w_scales, d_bias, M, N, K,
+                                            device, st);
+    }
+    NVQ_REQUIRE(d_workspace && workspace_bytes >= N * K * 2 && nvq_aligned(d_workspace, 32),
+                "nvq_linear_fwd: workspace of %zu bytes (32-byte aligned) required", N * K * 2);
     uint16_t* wd = (uint16_t*)d_workspace;
     const float* chan_scales = d_w_scales;
     if (w_fmt == NVQ_E2M1_B32) {

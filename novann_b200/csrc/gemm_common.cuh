@@ -5,6 +5,7 @@
 
 struct LinearParams {
     uint16_t* y;
+    const uint8_t* wq;     // fused kernels: the weight codes (N x K bytes); else unused
     const float* scales;   // N per-output-channel factors or nullptr (= 1)
     const float* bias;     // N or nullptr (= 0)
     int M, N, K;
@@ -24,6 +25,10 @@ nvq_status nvq_linear_launch_single(uint16_t* d_y, const uint16_t* d_x, const ui
 nvq_status nvq_linear_launch_pair(uint16_t* d_y, const uint16_t* d_x, const uint16_t* d_w,
                                   const float* d_scales, const float* d_bias, size_t M, size_t N,
                                   size_t K, int device, cudaStream_t st);
+
+nvq_status nvq_linear_launch_pair_fused(uint16_t* d_y, const uint16_t* d_x, const uint8_t* d_wq,
+                                        nvq_dtype fmt, const float* d_scales, const float* d_bias,
+                                        size_t M, size_t N, size_t K, int device, cudaStream_t st);
 
 #ifdef __CUDACC__
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {

@@ -13,6 +13,9 @@
 //           and commits: slot release and "accumulator ready" are multicast to both CTAs
 //   warps 2-5 epilogue (both CTAs): own 128 rows; "accumulator drained" is signalled to the
 //           leader's barrier, remotely from the peer
+//   warps 6-13 (fused variant only) converters: the weight tile arrives by TMA as raw FP8
+//           codes; these warps expand it to bf16 (exact) straight into the swizzled operand
+//           slot, so no expanded copy of the weight ever exists in HBM.
 // Every wait is bounded; a cluster barrier before teardown keeps a CTA's shared memory alive
 // until its partner has stopped signalling into it.
 #include "gemm_common.cuh"
@@ -23,19 +26,28 @@ constexpr int BM = 256;          // rows per pair tile (128 per CTA)
 constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 6;
 constexpr int A_BYTES = 128 * BK * 2;      // per CTA
 constexpr int B_BYTES = 128 * BK * 2;      // per CTA: half of the tile's weight rows
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int THREADS = 192;
+constexpr int RAW_BYTES = 128 * BK;        // fused variant: the same rows as FP8 codes
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 8192;
+constexpr int MAX_STAGES = 6;
 
-enum { ERR_PRODUCER = 11, ERR_MMA_FULL = 12, ERR_MMA_TMEM = 13, ERR_EPILOGUE = 14 };
+// FUSED = 0: B comes expanded (bf16) from a workspace.  FUSED = NVQ_E4M3 / NVQ_E5M2: B comes as
+// codes and is expanded in shared memory by four extra warps.
+template <int FUSED>
+struct Cfg {
+    static constexpr int STAGES = FUSED ? 5 : 6;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + (FUSED ? RAW_BYTES : 0);
+    static constexpr int THREADS = FUSED ? 448 : 192;   // fused: + 8 converter warps
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 8192;
+};
+
+enum { ERR_PRODUCER = 11, ERR_MMA_FULL = 12, ERR_MMA_TMEM = 13, ERR_EPILOGUE = 14, ERR_CONVERT = 15 };
 
 struct Shared {
-    uint64_t full[STAGES];
-    uint64_t empty[STAGES];
+    uint64_t full[MAX_STAGES];
+    uint64_t empty[MAX_STAGES];
+    uint64_t raw_full[MAX_STAGES];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
@@ -44,9 +56,44 @@ struct Shared {
     float bias[2][BN];
 };
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+// Two FP8 codes (the two bytes selected by `sel` from w) -> two bf16 values, exactly.
+// The code's exponent and mantissa bits are dropped into the low end of the bf16 exponent and
+// the top of its mantissa; one bf16 multiply by 2^(127 - bias) then fixes the exponent bias
+// and, because bf16 arithmetic keeps subnormals, also normalises the codes whose exponent
+// field is zero.
+template <int FMT>
+__device__ __forceinline__ uint32_t expand2(uint32_t w, uint32_t sel) {
+    const uint32_t hi = __byte_perm(w, 0u, sel);                 // code bytes -> bits 15:8 / 31:24
+    constexpr int sh = FMT == NVQ_E4M3 ? 4 : 3;                  // 7 magnitude bits -> bits 10:4 / 11:5
+    constexpr uint32_t mmask = FMT == NVQ_E4M3 ? 0x07F007F0u : 0x0FE00FE0u;
+    constexpr uint32_t rebias = FMT == NVQ_E4M3 ? 0x7B807B80u    // 2^120 as bf16, twice
+                                                : 0x77807780u;   // 2^112
+    const uint32_t t = ((hi >> sh) & mmask) | (hi & 0x80008000u);
+    uint32_t r;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(t), "r"(rebias));
+    return r;
+}
+
+// 16 FP8 codes (four words) -> 16 bf16 values (eight words)
+template <int FMT>
+__device__ __forceinline__ void expand16(const uint4& in, uint4& lo, uint4& hi) {
+    const uint32_t w[4] = {in.x, in.y, in.z, in.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        o[2 * i] = expand2<FMT>(w[i], 0x1404);       // bytes 0, 1
+        o[2 * i + 1] = expand2<FMT>(w[i], 0x3424);   // bytes 2, 3
+    }
+    lo = make_uint4(o[0], o[1], o[2], o[3]);
+    hi = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+template <int FUSED>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg<FUSED>::THREADS, 1)
 linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const LinearParams p) {
+    constexpr int STAGES = Cfg<FUSED>::STAGES;
+    constexpr int STAGE_BYTES = Cfg<FUSED>::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = tc::smem_u32(smem_raw);
     const uint32_t tiles = (raw + 1023u) & ~1023u;
@@ -59,8 +106,11 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
-            tc::mbar_init(tc::smem_u32(&sh->full[s]), 1);
+            // fused: the leader's full barrier also collects one arrival per converter warp of
+            // both CTAs (8 + 8) on top of the producer's
+            tc::mbar_init(tc::smem_u32(&sh->full[s]), FUSED ? 17 : 1);
             tc::mbar_init(tc::smem_u32(&sh->empty[s]), 1);
+            tc::mbar_init(tc::smem_u32(&sh->raw_full[s]), 1);
         }
         for (int a = 0; a < 2; a++) {
             tc::mbar_init(tc::smem_u32(&sh->tmem_full[a]), 1);
@@ -97,13 +147,25 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     if (!ok) break;
                     const uint32_t dst = tiles + stage * STAGE_BYTES;
                     const uint32_t lead_full = tc::mapa(tc::smem_u32(&sh->full[stage]), 0);
-                    if (rank == 0)   // the leader expects the bytes of both CTAs
-                        tc::mbar_arrive_expect_tx(tc::smem_u32(&sh->full[stage]),
-                                                  2 * (A_BYTES + rows_b * BK * 2));
-                    tc::tma_load_2d_pair(dst, &map_a, lead_full, kb * BK, m0);
-                    tc::tma_load_2d_pair(dst + A_BYTES, &map_b, lead_full, kb * BK, n0);
-                    if (rows_b == 128)
-                        tc::tma_load_2d_pair(dst + A_BYTES + B_BYTES / 2, &map_b, lead_full, kb * BK, n0 + 64);
+                    if constexpr (FUSED) {
+                        if (rank == 0)   // the leader expects the X bytes of both CTAs
+                            tc::mbar_arrive_expect_tx(tc::smem_u32(&sh->full[stage]), 2 * A_BYTES);
+                        tc::tma_load_2d_pair(dst, &map_a, lead_full, kb * BK, m0);
+                        // raw codes: own barrier, own CTA; consumed by the converter warps
+                        const uint32_t rbar = tc::smem_u32(&sh->raw_full[stage]);
+                        tc::mbar_arrive_expect_tx(rbar, rows_b * BK);
+                        tc::tma_load_2d(dst + A_BYTES + B_BYTES, &map_b, rbar, kb * BK, n0);
+                        if (rows_b == 128)
+                            tc::tma_load_2d(dst + A_BYTES + B_BYTES + RAW_BYTES / 2, &map_b, rbar, kb * BK, n0 + 64);
+                    } else {
+                        if (rank == 0)   // the leader expects the bytes of both CTAs
+                            tc::mbar_arrive_expect_tx(tc::smem_u32(&sh->full[stage]),
+                                                      2 * (A_BYTES + rows_b * BK * 2));
+                        tc::tma_load_2d_pair(dst, &map_a, lead_full, kb * BK, m0);
+                        tc::tma_load_2d_pair(dst + A_BYTES, &map_b, lead_full, kb * BK, n0);
+                        if (rows_b == 128)
+                            tc::tma_load_2d_pair(dst + A_BYTES + B_BYTES / 2, &map_b, lead_full, kb * BK, n0 + 64);
+                    }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -136,6 +198,61 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
                 if (ok) tc::tc_commit_pair(tc::smem_u32(&sh->tmem_full[acc]), 3);
+            }
+        }
+    } else if (FUSED && warp >= 6) {
+        // ------------------------------------------------------------ converters (both CTAs)
+        if constexpr (FUSED != 0) {
+            const int ct = threadIdx.x - 192;           // 0..255
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int t = pair; t < p.num_items && ok; t += num_pairs) {
+                const TileRef tr = tile_ref(p, t);
+                const int rows_b = (tr.is_half ? BN / 2 : BN) / 2;
+                for (int kb = 0; kb < num_kb; kb++) {
+                    // the B slot is free once the MMAs of its previous use have completed ...
+                    ok = tc::mbar_wait(tc::smem_u32(&sh->empty[stage]), phase ^ 1, abort_flag, ERR_CONVERT);
+                    // ... and the codes of this k-block have landed
+                    ok = ok && tc::mbar_wait(tc::smem_u32(&sh->raw_full[stage]), phase, abort_flag, ERR_CONVERT);
+                    ok = __all_sync(0xFFFFFFFFu, ok);
+                    if (!ok) break;
+                    const uint32_t b_dst = tiles + stage * STAGE_BYTES + A_BYTES;
+                    const uint32_t codes = b_dst + B_BYTES;
+                    // chunk i = 16 codes: row i/4, quarter i%4 of the 64-byte raw row -> 16-byte
+                    // chunks 2q, 2q+1 of the 128-byte operand row, placed by the 128-byte swizzle
+                    // (chunk index XOR row mod 8).  Two chunks per thread, loads first.
+                    uint4 in[2];
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        const int i = ct + 256 * j;
+                        if (i < rows_b * 4)
+                            asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+                                         : "=r"(in[j].x), "=r"(in[j].y), "=r"(in[j].z), "=r"(in[j].w)
+                                         : "r"(codes + i * 16));
+                    }
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        const int i = ct + 256 * j;
+                        if (i < rows_b * 4) {
+                            const int r = i >> 2, q = i & 3;
+                            uint4 lo, hi;
+                            expand16<FUSED>(in[j], lo, hi);
+                            const uint32_t row_base = b_dst + (r >> 3) * 1024 + (r & 7) * 128;
+                            const uint32_t c0 = (uint32_t)((2 * q) ^ (r & 7)), c1 = (uint32_t)((2 * q + 1) ^ (r & 7));
+                            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(row_base + c0 * 16),
+                                         "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
+                            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(row_base + c1 * 16),
+                                         "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
+                        }
+                    }
+                    // make the generic-proxy writes visible to the tensor core's (async proxy)
+                    // reads, then one arrival per warp on the leader's full barrier (CTA-scope
+                    // release: a cluster-scope release here cost 2x in whole-kernel time)
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) tc::mbar_arrive_remote(tc::mapa(tc::smem_u32(&sh->full[stage]), 0));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
             }
         }
     } else {
@@ -189,24 +306,25 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     if (threadIdx.x == 0 && *abort_flag && p.status) atomicCAS(p.status, 0, *abort_flag);
 }
 
-}  // namespace
-
-nvq_status nvq_linear_launch_pair(uint16_t* d_y, const uint16_t* d_x, const uint16_t* d_w,
-                                  const float* d_scales, const float* d_bias, size_t M, size_t N,
-                                  size_t K, int device, cudaStream_t st) {
+template <int FUSED>
+static nvq_status launch_pair(uint16_t* d_y, const uint16_t* d_x, const void* d_w,
+                              const float* d_scales, const float* d_bias, size_t M, size_t N,
+                              size_t K, int device, cudaStream_t st) {
     CUtensorMap map_a, map_b;
     nvq_status s = nvq_make_tmap_2d(&map_a, d_x, M, K, 128, BK, 2);
     if (s != NVQ_OK) return s;
-    s = nvq_make_tmap_2d(&map_b, d_w, N, K, 64, BK, 2);
+    // fused: codes, 64-byte rows, no swizzle (the converters read them linearly)
+    s = FUSED ? nvq_make_tmap_2d(&map_b, d_w, N, K, 64, BK, 1) : nvq_make_tmap_2d(&map_b, d_w, N, K, 64, BK, 2);
     if (s != NVQ_OK) return s;
     static bool attr_set[64];
     if (!attr_set[device]) {
-        NVQ_CUDA(cudaFuncSetAttribute(linear_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      SMEM_BYTES));
+        NVQ_CUDA(cudaFuncSetAttribute(linear_tc_pair_kernel<FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Cfg<FUSED>::SMEM_BYTES));
         attr_set[device] = true;
     }
     LinearParams p;
     p.y = d_y;
+    p.wq = FUSED ? (const uint8_t*)d_w : nullptr;
     p.scales = d_scales;
     p.bias = d_bias;
     p.M = (int)M;
@@ -224,7 +342,24 @@ nvq_status nvq_linear_launch_pair(uint16_t* d_y, const uint16_t* d_x, const uint
     int split = (tiles > pairs && rem > 0 && 2 * rem <= pairs) ? rem : 0;
     p.num_big = tiles - split;
     p.num_items = p.num_big + 2 * split;
-    linear_tc_pair_kernel<<<2 * pairs, THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+    linear_tc_pair_kernel<FUSED><<<2 * pairs, Cfg<FUSED>::THREADS, Cfg<FUSED>::SMEM_BYTES, st>>>(map_a, map_b, p);
     NVQ_LAUNCHED();
     return NVQ_OK;
+}
+
+}  // namespace
+
+nvq_status nvq_linear_launch_pair(uint16_t* d_y, const uint16_t* d_x, const uint16_t* d_w,
+                                  const float* d_scales, const float* d_bias, size_t M, size_t N,
+                                  size_t K, int device, cudaStream_t st) {
+    return launch_pair<0>(d_y, d_x, d_w, d_scales, d_bias, M, N, K, device, st);
+}
+
+nvq_status nvq_linear_launch_pair_fused(uint16_t* d_y, const uint16_t* d_x, const uint8_t* d_wq,
+                                        nvq_dtype fmt, const float* d_scales, const float* d_bias,
+                                        size_t M, size_t N, size_t K, int device, cudaStream_t st) {
+    NVQ_REQUIRE(K % 16 == 0, "nvq_linear_fwd: K (%zu) must be a multiple of 16 for the fused FP8 path", K);
+    if (fmt == NVQ_E4M3)
+        return launch_pair<NVQ_E4M3>(d_y, d_x, d_wq, d_scales, d_bias, M, N, K, device, st);
+    return launch_pair<NVQ_E5M2>(d_y, d_x, d_wq, d_scales, d_bias, M, N, K, device, st);
 }

@@ -31,14 +31,18 @@ def check_device_errors(device: int = 0) -> None:
 
 def linear_q_device(y: DeviceBuffer, x: DeviceBuffer, wq: DeviceBuffer, fmt: str,
                     w_scales: DeviceBuffer, bias: DeviceBuffer | None, m: int, n: int, k: int,
-                    workspace: DeviceBuffer, stream=None) -> None:
+                    workspace: DeviceBuffer | None, stream=None) -> None:
+    """``workspace=None`` selects the in-kernel expansion of FP8 codes (M > 128, K % 16 == 0)."""
     check(lib().nvq_linear_fwd(y.at(0), x.at(0), wq.at(0), _lib.DTYPE_IDS[fmt], w_scales.at(0),
                                bias.at(0) if bias is not None else None, m, n, k,
-                               workspace.at(0), workspace.nbytes, x.device, _sptr(stream)))
+                               workspace.at(0) if workspace is not None else None,
+                               workspace.nbytes if workspace is not None else 0,
+                               x.device, _sptr(stream)))
 
 
 def linear_q_host(x_bf16_bits: np.ndarray, wq: np.ndarray, w_scales: np.ndarray,
-                  bias: np.ndarray | None, fmt: str = "e4m3", device: int = 0) -> np.ndarray:
+                  bias: np.ndarray | None, fmt: str = "e4m3", device: int = 0,
+                  use_workspace: bool = True) -> np.ndarray:
     """Host arrays in, bf16 bits (M, N) out."""
     x = np.ascontiguousarray(x_bf16_bits, np.uint16)
     m, k = x.shape
@@ -48,7 +52,7 @@ def linear_q_host(x_bf16_bits: np.ndarray, wq: np.ndarray, w_scales: np.ndarray,
     ds = DeviceBuffer.from_numpy(np.ascontiguousarray(w_scales, np.float32), device)
     db = DeviceBuffer.from_numpy(np.ascontiguousarray(bias, np.float32), device) if bias is not None else None
     dy = DeviceBuffer(m * n * 2, device)
-    ws = DeviceBuffer(linear_workspace_bytes(n, k, fmt), device)
+    ws = DeviceBuffer(linear_workspace_bytes(n, k, fmt), device) if use_workspace else None
     linear_q_device(dy, dx, dw, fmt, ds, db, m, n, k, ws)
     device_sync(device)
     check_device_errors(device)

@@ -43,6 +43,32 @@ def test_linear_fp8_ragged_shapes(gpu, m, n, k):
     assert err <= 2.0 ** -7, err
 
 
+@pytest.mark.parametrize("fmt", ["e4m3", "e5m2"])
+@pytest.mark.parametrize("m,n,k", [(256, 512, 512), (200, 1000, 336), (1024, 16, 144), (640, 1280, 2048)])
+def test_linear_fp8_expanded_in_kernel(gpu, fmt, m, n, k):
+    """No workspace: the converter warps of the CTA-pair kernel expand the codes in shared
+    memory.  Same oracle, and bit-identical to the workspace form (both feed the tensor
+    cores the exact bf16 value of every code, tile by tile in the same order)."""
+    xb, w, b = workloads.linear_inputs(m, n, k, seed=k)
+    wq, sc = o.quantize_weight_per_channel(w, fmt)
+    wq[0, :8] = np.arange(8)          # E4M3 / E5M2 zero and subnormal codes
+    wq[1, :8] = np.arange(8) | 0x80
+    y_fused = F.linear_q_host(xb, wq, sc, b, fmt, gpu, use_workspace=False)
+    y_ws = F.linear_q_host(xb, wq, sc, b, fmt, gpu, use_workspace=True)
+    want_bits, _ = o.linear_fwd_qweight(xb, wq, sc, b, fmt)
+    err = o.max_abs_rel(o.bf16_bits_to_f32(y_fused), o.bf16_bits_to_f32(want_bits))
+    assert err <= 2.0 ** -7, err
+    assert np.array_equal(y_fused, y_ws)
+
+
+def test_linear_missing_workspace_is_rejected_when_needed(gpu):
+    from novann_b200 import _lib
+    xb, w, b = workloads.linear_inputs(64, 64, 64, seed=0)    # M <= 128: workspace required
+    wq, sc = o.quantize_weight_per_channel(w, "e4m3")
+    with pytest.raises(_lib.NvqError):
+        F.linear_q_host(xb, wq, sc, b, "e4m3", gpu, use_workspace=False)
+
+
 def test_linear_e5m2_and_no_bias(gpu):
     err, _, _ = _run_fp8(gpu, 256, 256, 512, fmt="e5m2", bias=False)
     assert err <= 2.0 ** -7
