@@ -125,6 +125,11 @@ nvq_status nvq_quantize_fp8_tensor(uint8_t* d_dst, float* d_amax_scale_inv, cons
                                    size_t n, nvq_dtype fmt, const float* d_amax_in, int device,
                                    void* stream);
 
+/* Per-row (per output channel) quantisation of a rows x cols fp32 weight matrix:
+ * d_scales[r] = amax_r / FMAX (1 for an all-zero row); codes = cvt_sat_rne(w * (FMAX/amax_r)). */
+nvq_status nvq_quantize_fp8_rows(uint8_t* d_dst, float* d_scales, const float* d_src, size_t rows,
+                                 size_t cols, nvq_dtype fmt, int device, void* stream);
+
 /* ---------------------------------------------------------------- FP4 E2M1, block 32
  * No reference counterpart.  rows x cols bf16, cols % 32 == 0.
  * d_packed: rows x cols/2 bytes; d_scales: rows x cols/32 fp32.
@@ -188,6 +193,84 @@ nvq_status nvq_linear_fwd_static(uint16_t* d_y_bf16, const uint16_t* d_x_bf16, c
 /* Tensor-core kernels bound every device-side wait; a wait that gives up records a
  * non-zero code here (read and cleared by this call) instead of hanging. */
 nvq_status nvq_device_error_flag(int device, int* flag);
+
+/* ---------------------------------------------------------------- fp32 train step
+ * The pieces of the reference's training step (novann/utils/train/train.py:60-75) in fp32
+ * on the CUDA cores (no tensor cores: results differ from NumPy's sgemm only by summation
+ * order; elementwise steps round exactly as NumPy does).
+ */
+/* F.linear (novann/functional.py:147-163): Y = X @ W^T + b; X MxK, W NxK, b N or NULL.
+ * relu != 0 additionally applies F.relu (novann/functional.py:8-22): mask = (Y > 0),
+ * Y = Y * mask; d_mask (MxN, may be NULL) receives the mask. */
+nvq_status nvq_linear_fwd_f32(float* d_y, const float* d_x, const float* d_w, const float* d_bias,
+                              int M, int N, int K, int relu, float* d_mask, int device,
+                              void* stream);
+/* Linear.backward (novann/layers/linear/linear.py:85-108): dW = G^T @ X (assigned, NxK),
+ * db = sum over rows of G (N), dX = G @ W (MxK).  Any of d_dw, d_db, d_dx may be NULL.  If
+ * d_mask (MxK) is not NULL, dX is multiplied by it (ReLU.backward,
+ * novann/layers/activations/relu.py:36-45). */
+nvq_status nvq_linear_bwd_f32(float* d_dw, float* d_db, float* d_dx, const float* d_g,
+                              const float* d_x, const float* d_w, const float* d_mask, int M,
+                              int N, int K, int device, void* stream);
+/* F.relu (novann/functional.py:8-22): mask = (x > 0) as fp32, out = x * mask. */
+nvq_status nvq_relu_fwd_f32(float* d_out, float* d_mask, const float* d_x, size_t n, int device,
+                            void* stream);
+/* CrossEntropyLoss (novann/losses/loss_functions.py:29-75): d_yhat (MxC) = softmax(logits,
+ * axis 1); grad = float32((double(y_hat) - onehot) / M); *d_loss (may be NULL) = the value the
+ * reference reports, i.e. softmax applied a second time along the batch axis inside
+ * F.cross_entropy (novann/functional.py:108-128), eps 1e-8.  labels int32 in [0, C). */
+nvq_status nvq_softmax_ce_f32(float* d_grad, float* d_loss, const float* d_logits,
+                              const int32_t* d_labels, float* d_yhat, int M, int C, int device,
+                              void* stream);
+/* SGD.step, vanilla path (novann/optim/sgd.py:58-82): p = p - lr * (g * grad_scale), each
+ * product and the subtraction rounded separately (grad_scale == 1 skips its multiply). */
+nvq_status nvq_sgd_step_f32(float* d_param, const float* d_grad, size_t n, float lr,
+                            float grad_scale, int device, void* stream);
+
+/* ---------------------------------------------------------------- Conv2d forward
+ * Replaces F.conv2d, novann/functional.py:275-385: pad (zeros / reflect / replicate /
+ * circular = np.pad constant / reflect / edge / wrap) -> im2col with rows ordered (c,kh,kw)
+ * and columns (n,oh,ow) -> w_col @ col + bias -> (N,Cout,OH,OW).
+ */
+/* _calc_out_size (novann/functional.py:319-323) */
+nvq_status nvq_conv2d_out_size(int H, int W, int KH, int KW, int sh, int sw, int ph, int pw,
+                               int* OH, int* OW);
+/* _im2col (novann/functional.py:346-368): d_col is (C*KH*KW) x (N*OH*OW) fp32, row-major. */
+nvq_status nvq_im2col_f32(float* d_col, const float* d_x, int N, int C, int H, int W, int KH,
+                          int KW, int sh, int sw, int ph, int pw, nvq_pad_mode mode, int device,
+                          void* stream);
+/* fp32 convolution forward: x NCHW, w (Cout,C,KH,KW), bias Cout or NULL, out NCHW contiguous.
+ * d_col: scratch of C*KH*KW*N*OH*OW floats (the reference's `col`, kept for backward). */
+nvq_status nvq_conv2d_fwd_f32(float* d_out, const float* d_x, const float* d_w,
+                              const float* d_bias, float* d_col, int N, int C, int H, int W,
+                              int Cout, int KH, int KW, int sh, int sw, int ph, int pw,
+                              nvq_pad_mode mode, int device, void* stream);
+/* Quantised-weight convolution forward on the tensor cores: patches of x are gathered
+ * (padding mode applied) and rounded to bf16 into d_col_bf16, laid out rows x kpad with
+ * rows = N*OH*OW and kpad = C*KH*KW rounded up to 16 (zero filled); the contraction is
+ * nvq_linear_fwd with Wq (Cout x kpad codes, zero padded, E4M3 / E5M2) and Cout per-channel
+ * scales; out is fp32 NCHW holding the bf16-rounded results.  Cout % 8 == 0.
+ * d_y_bf16: scratch rows x Cout; d_workspace as for nvq_linear_fwd with N=Cout, K=kpad. */
+nvq_status nvq_conv2d_q_sizes(int N, int C, int H, int W, int Cout, int KH, int KW, int sh, int sw,
+                              int ph, int pw, size_t* rows, size_t* kpad);
+nvq_status nvq_conv2d_fwd_q(float* d_out, const float* d_x, const uint8_t* d_wq, nvq_dtype w_fmt,
+                            const float* d_w_scales, const float* d_bias, uint16_t* d_col_bf16,
+                            uint16_t* d_y_bf16, void* d_workspace, size_t workspace_bytes, int N,
+                            int C, int H, int W, int Cout, int KH, int KW, int sh, int sw, int ph,
+                            int pw, nvq_pad_mode mode, int device, void* stream);
+
+/* ---------------------------------------------------------------- data-parallel step
+ * NCCL communicator for the gradient all-reduce of the data-parallel training step (no
+ * reference counterpart: NovaNN is single process).  One process per GPU; rank 0 makes the
+ * unique id and hands it to the others over the launcher's side channel.
+ */
+#define NVQ_UNIQUE_ID_BYTES 128
+nvq_status nvq_comm_unique_id(uint8_t id[NVQ_UNIQUE_ID_BYTES]);
+nvq_status nvq_comm_init(const uint8_t id[NVQ_UNIQUE_ID_BYTES], int rank, int world, int device,
+                         void** comm);
+nvq_status nvq_comm_destroy(void* comm);
+/* in-place sum over ranks of an fp32 bucket */
+nvq_status nvq_allreduce_sum_f32(void* comm, float* d_buf, size_t n, int device, void* stream);
 
 #ifdef __cplusplus
 }

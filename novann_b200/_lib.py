@@ -54,11 +54,26 @@ SIGNATURES = {
     "nvq_quantize_fp8": (i32, [vp, vp, sz, i32, f32c, i32, vp]),
     "nvq_dequantize_fp8": (i32, [vp, vp, sz, i32, f32c, i32, vp]),
     "nvq_quantize_fp8_tensor": (i32, [vp, vp, vp, sz, i32, vp, i32, vp]),
+    "nvq_quantize_fp8_rows": (i32, [vp, vp, vp, sz, sz, i32, i32, vp]),
     "nvq_quantize_fp4_b32": (i32, [vp, vp, vp, sz, sz, i32, vp]),
     "nvq_dequantize_fp4_b32": (i32, [vp, vp, vp, sz, sz, i32, vp]),
     "nvq_linear_workspace_bytes": (i32, [sz, sz, i32, C.POINTER(sz)]),
     "nvq_linear_fwd": (i32, [vp, vp, vp, i32, vp, vp, sz, sz, sz, vp, sz, i32, vp]),
     "nvq_device_error_flag": (i32, [i32, C.POINTER(i32)]),
+    "nvq_linear_fwd_f32": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp, i32, vp]),
+    "nvq_linear_bwd_f32": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]),
+    "nvq_relu_fwd_f32": (i32, [vp, vp, vp, sz, i32, vp]),
+    "nvq_softmax_ce_f32": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, vp]),
+    "nvq_sgd_step_f32": (i32, [vp, vp, sz, f32c, f32c, i32, vp]),
+    "nvq_conv2d_out_size": (i32, [i32] * 8 + [C.POINTER(i32), C.POINTER(i32)]),
+    "nvq_im2col_f32": (i32, [vp, vp] + [i32] * 10 + [i32, i32, vp]),
+    "nvq_conv2d_fwd_f32": (i32, [vp, vp, vp, vp, vp] + [i32] * 11 + [i32, i32, vp]),
+    "nvq_conv2d_q_sizes": (i32, [i32] * 11 + [C.POINTER(sz), C.POINTER(sz)]),
+    "nvq_conv2d_fwd_q": (i32, [vp, vp, vp, i32, vp, vp, vp, vp, vp, sz] + [i32] * 11 + [i32, i32, vp]),
+    "nvq_comm_unique_id": (i32, [vp]),
+    "nvq_comm_init": (i32, [vp, i32, i32, i32, pvp]),
+    "nvq_comm_destroy": (i32, [vp]),
+    "nvq_allreduce_sum_f32": (i32, [vp, vp, sz, i32, vp]),
     "nvq_linear_fwd_static": (i32, [vp, vp, vp, i32, vp, vp, sz, sz, sz, vp, i32, vp]),
 }
 

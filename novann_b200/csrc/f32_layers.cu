@@ -1,0 +1,420 @@
+// fp32 pieces of the reference's training step (novann/utils/train/train.py:60-75):
+// Linear forward / backward, ReLU, softmax cross-entropy, SGD, plus the fp32 im2col
+// convolution forward.  These are the small, latency-bound kernels of the
+// "MLP train step" configuration (batch 128, 784-256-128-10): plain fp32 FMA on the
+// CUDA cores, no tensor cores, so results differ from NumPy's sgemm only by summation
+// order.  Elementwise steps reproduce the reference's roundings exactly (separate
+// multiply and add where NumPy performs two operations).
+#include <math.h>
+
+#include "nvq_common.cuh"
+
+namespace {
+
+// ---- generic strided fp32 GEMM ------------------------------------------------------
+//   C(i,j) = sum_l A(i,l) * B(l,j),  A(i,l) = a[i*a_si + l*a_sl],  B(l,j) = b[l*b_sl + j*b_sj]
+// One 32 x 32 output tile per 256-thread block (2 x 2 per thread), 32-deep k chunks staged
+// in shared memory.  Loads walk the unit-stride index fastest, whichever it is.
+constexpr int TS = 32;
+
+struct GemmArgs {
+    const float* a; long long a_si, a_sl;
+    const float* b; long long b_sl, b_sj;
+    float* c;
+    int I, J, L;
+    // epilogue
+    const float* bias;      // added per column j (bias_per_row = 0) or per row i (= 1)
+    int bias_per_row;
+    int relu;               // out = v * (v > 0); mask (same indexing as c) optional
+    float* mask_out;
+    const float* mask_in;   // out = v * mask_in[c index]
+    // output indexing: 0 = row-major I x J; 1 = "NCHW": j = (n, s) with s < inner:
+    //   c[(n * I + i) * inner + s]
+    int out_mode, inner;
+};
+
+__global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
+    __shared__ float As[TS][TS + 1];   // [l][i]
+    __shared__ float Bs[TS][TS + 1];   // [l][j]
+    const int i0 = blockIdx.y * TS, j0 = blockIdx.x * TS;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;   // 16 x 16 threads, 2 x 2 outputs each
+    float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+    for (int l0 = 0; l0 < g.L; l0 += TS) {
+        // each thread loads 4 elements of each tile
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            int e = threadIdx.x + 256 * r;          // 0..1023
+            int fast = e & 31, slow = e >> 5;
+            {   // A tile: fastest index follows the unit stride
+                int ii = g.a_sl == 1 ? slow : fast, ll = g.a_sl == 1 ? fast : slow;
+                int i = i0 + ii, l = l0 + ll;
+                As[ll][ii] = (i < g.I && l < g.L) ? g.a[i * g.a_si + l * g.a_sl] : 0.f;
+            }
+            {
+                int jj = g.b_sl == 1 ? slow : fast, ll = g.b_sl == 1 ? fast : slow;
+                int j = j0 + jj, l = l0 + ll;
+                Bs[ll][jj] = (j < g.J && l < g.L) ? g.b[l * g.b_sl + j * g.b_sj] : 0.f;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int l = 0; l < TS; l++) {
+            float a0 = As[l][ty], a1 = As[l][ty + 16];
+            float b0 = Bs[l][tx], b1 = Bs[l][tx + 16];
+            acc[0][0] = fmaf(a0, b0, acc[0][0]);
+            acc[0][1] = fmaf(a0, b1, acc[0][1]);
+            acc[1][0] = fmaf(a1, b0, acc[1][0]);
+            acc[1][1] = fmaf(a1, b1, acc[1][1]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+#pragma unroll
+        for (int v = 0; v < 2; v++) {
+            int i = i0 + ty + 16 * u, j = j0 + tx + 16 * v;
+            if (i >= g.I || j >= g.J) continue;
+            float val = acc[u][v];
+            if (g.bias) val = __fadd_rn(val, g.bias_per_row ? g.bias[i] : g.bias[j]);
+            size_t idx = g.out_mode == 0 ? (size_t)i * g.J + j
+                                         : ((size_t)(j / g.inner) * g.I + i) * g.inner + (j % g.inner);
+            if (g.relu) {
+                float m = val > 0.f ? 1.f : 0.f;
+                if (g.mask_out) g.mask_out[idx] = m;
+                val = __fmul_rn(val, m);
+            }
+            if (g.mask_in) val = __fmul_rn(val, g.mask_in[idx]);
+            g.c[idx] = val;
+        }
+    }
+}
+
+nvq_status launch_gemm(const GemmArgs& g, cudaStream_t st) {
+    if (g.I <= 0 || g.J <= 0) return NVQ_OK;
+    dim3 grid((g.J + TS - 1) / TS, (g.I + TS - 1) / TS);
+    gemm_f32_kernel<<<grid, 256, 0, st>>>(g);
+    NVQ_LAUNCHED();
+    return NVQ_OK;
+}
+
+// column sums of an M x N matrix: out[n] = sum_m g[m, n], rows added in order (fp32)
+__global__ void colsum_kernel(const float* __restrict__ g, float* __restrict__ out, int M, int N) {
+    int n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= N) return;
+    float s = 0.f;
+    for (int m = 0; m < M; m++) s = __fadd_rn(s, g[(size_t)m * N + n]);
+    out[n] = s;
+}
+
+__global__ void relu_kernel(float* __restrict__ out, float* __restrict__ mask,
+                            const float* __restrict__ x, size_t n) {
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float v = x[i];
+        float m = v > 0.f ? 1.f : 0.f;
+        if (mask) mask[i] = m;
+        out[i] = __fmul_rn(v, m);
+    }
+}
+
+// One block; thread per row for the softmax, then a block reduction for the loss.
+//   y_hat = softmax(logits, axis 1) in fp32; grad = float((double(y_hat) - onehot) / M)
+//   loss  = -sum(onehot * log(p2 + 1e-8)) / M with p2 = softmax(y_hat, axis 0): the value the
+//   reference reports (it applies softmax a second time, along the batch axis).
+__global__ void softmax_ce_kernel(float* __restrict__ grad, float* __restrict__ loss,
+                                  const float* __restrict__ logits, const int* __restrict__ labels,
+                                  float* __restrict__ yhat_scratch, int M, int C) {
+    extern __shared__ double red[];
+    for (int m = threadIdx.x; m < M; m += blockDim.x) {
+        const float* z = logits + (size_t)m * C;
+        float mx = z[0];
+        for (int c = 1; c < C; c++) mx = fmaxf(mx, z[c]);
+        float s = 0.f;
+        for (int c = 0; c < C; c++) s = __fadd_rn(s, expf(__fsub_rn(z[c], mx)));
+        int lab = labels[m];
+        for (int c = 0; c < C; c++) {
+            float y = __fdiv_rn(expf(__fsub_rn(z[c], mx)), s);
+            yhat_scratch[(size_t)m * C + c] = y;
+            double d = ((double)y - (c == lab ? 1.0 : 0.0)) / (double)M;
+            grad[(size_t)m * C + c] = (float)d;
+        }
+    }
+    __syncthreads();
+    if (!loss) return;
+    // second softmax along the batch axis, per class column; only the labelled entries count
+    double part = 0.0;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float mx = yhat_scratch[c];
+        for (int m = 1; m < M; m++) mx = fmaxf(mx, yhat_scratch[(size_t)m * C + c]);
+        float s = 0.f;
+        for (int m = 0; m < M; m++) s = __fadd_rn(s, expf(__fsub_rn(yhat_scratch[(size_t)m * C + c], mx)));
+        for (int m = 0; m < M; m++) {
+            if (labels[m] == c) {
+                float p2 = __fdiv_rn(expf(__fsub_rn(yhat_scratch[(size_t)m * C + c], mx)), s);
+                part += (double)logf(__fadd_rn(p2, 1e-8f));
+            }
+        }
+    }
+    red[threadIdx.x] = part;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double tot = 0.0;
+        for (int i = 0; i < blockDim.x; i++) tot += red[i];
+        *loss = (float)(-tot / (double)M);
+    }
+}
+
+__global__ void sgd_kernel(float* __restrict__ p, const float* __restrict__ g, size_t n, float lr,
+                           float grad_scale) {
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float gr = g[i];
+        if (grad_scale != 1.f) gr = __fmul_rn(gr, grad_scale);
+        p[i] = __fsub_rn(p[i], __fmul_rn(lr, gr));   // two roundings, as p -= lr * g in NumPy
+    }
+}
+
+// ---- im2col ---------------------------------------------------------------------------
+__device__ __forceinline__ int pad_index(int idx, int size, int mode, bool& zero) {
+    zero = false;
+    if (idx >= 0 && idx < size) return idx;
+    if (mode == NVQ_PAD_ZEROS) { zero = true; return 0; }
+    if (mode == NVQ_PAD_REPLICATE) return idx < 0 ? 0 : size - 1;
+    if (mode == NVQ_PAD_CIRCULAR) { int r = idx % size; return r < 0 ? r + size : r; }
+    // reflect without repeating the edge; a length-1 axis repeats its only value
+    if (size == 1) return 0;
+    int period = 2 * (size - 1);
+    int r = idx % period;
+    if (r < 0) r += period;
+    return r < size ? r : period - r;
+}
+
+struct ConvGeom { int N, C, H, W, KH, KW, sh, sw, ph, pw, OH, OW, mode; };
+
+// fp32 col, rows (c,kh,kw), columns (n,oh,ow): the reference's layout
+__global__ void im2col_f32_kernel(float* __restrict__ col, const float* __restrict__ x, ConvGeom g) {
+    const size_t L = (size_t)g.N * g.OH * g.OW, total = (size_t)g.C * g.KH * g.KW * L;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+        size_t row = e / L, colj = e % L;
+        int kw = row % g.KW, kh = (row / g.KW) % g.KH, c = row / (g.KW * g.KH);
+        int ow = colj % g.OW, oh = (colj / g.OW) % g.OH, n = colj / ((size_t)g.OW * g.OH);
+        bool z1, z2;
+        int ih = pad_index(oh * g.sh + kh - g.ph, g.H, g.mode, z1);
+        int iw = pad_index(ow * g.sw + kw - g.pw, g.W, g.mode, z2);
+        col[e] = (z1 || z2) ? 0.f : x[(((size_t)n * g.C + c) * g.H + ih) * g.W + iw];
+    }
+}
+
+// bf16 patches for the tensor-core path: rows (n,oh,ow), columns (c,kh,kw) padded with zeros
+// to Kpad; values rounded to nearest even
+__global__ void im2col_bf16_rows_kernel(uint16_t* __restrict__ col, const float* __restrict__ x,
+                                        ConvGeom g, int Kpad) {
+    const size_t L = (size_t)g.N * g.OH * g.OW, total = L * Kpad;
+    const int CKK = g.C * g.KH * g.KW;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+        size_t rowj = e / Kpad;
+        int kk = e % Kpad;
+        float v = 0.f;
+        if (kk < CKK) {
+            int kw = kk % g.KW, kh = (kk / g.KW) % g.KH, c = kk / (g.KW * g.KH);
+            int ow = rowj % g.OW, oh = (rowj / g.OW) % g.OH, n = rowj / ((size_t)g.OW * g.OH);
+            bool z1, z2;
+            int ih = pad_index(oh * g.sh + kh - g.ph, g.H, g.mode, z1);
+            int iw = pad_index(ow * g.sw + kw - g.pw, g.W, g.mode, z2);
+            if (!(z1 || z2)) v = x[(((size_t)n * g.C + c) * g.H + ih) * g.W + iw];
+        }
+        col[e] = (uint16_t)spec_f32_to_bf16(__float_as_uint(v));
+    }
+}
+
+// Y (L x Cout, bf16, rows (n,oh,ow)) -> out (N, Cout, OH, OW) fp32
+__global__ void rows_bf16_to_nchw_kernel(float* __restrict__ out, const uint16_t* __restrict__ y,
+                                         int N, int Cout, int S) {
+    size_t total = (size_t)N * Cout * S, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+        int s = e % S, c = (e / S) % Cout, n = e / ((size_t)S * Cout);
+        out[e] = __uint_as_float((uint32_t)y[((size_t)n * S + s) * Cout + c] << 16);
+    }
+}
+
+nvq_status geom(ConvGeom& g, int N, int C, int H, int W, int KH, int KW, int sh, int sw, int ph,
+                int pw, nvq_pad_mode mode) {
+    NVQ_REQUIRE(N > 0 && C > 0 && H > 0 && W > 0 && KH > 0 && KW > 0 && sh > 0 && sw > 0 && ph >= 0 && pw >= 0,
+                "conv2d: bad geometry");
+    NVQ_REQUIRE(mode >= NVQ_PAD_ZEROS && mode <= NVQ_PAD_CIRCULAR,
+                "padding_mode Only accept ('zeros', 'reflect', 'replicate', 'circular')");
+    NVQ_REQUIRE(H + 2 * ph >= KH && W + 2 * pw >= KW, "conv2d: kernel larger than the padded input");
+    g = ConvGeom{N, C, H, W, KH, KW, sh, sw, ph, pw, (H + 2 * ph - KH) / sh + 1, (W + 2 * pw - KW) / sw + 1, (int)mode};
+    return NVQ_OK;
+}
+
+unsigned ew_grid(size_t n, int device) {
+    size_t want = (n + 255) / 256, cap = (size_t)nvq_sm_count(device) * 8;
+    return (unsigned)(want < 1 ? 1 : (want < cap ? want : cap));
+}
+
+}  // namespace
+
+extern "C" nvq_status nvq_linear_fwd_f32(float* d_y, const float* d_x, const float* d_w,
+                                         const float* d_bias, int M, int N, int K, int relu,
+                                         float* d_mask, int device, void* stream) {
+    NVQ_REQUIRE(d_y && d_x && d_w && M >= 0 && N > 0 && K > 0, "nvq_linear_fwd_f32: bad argument");
+    nvq_status s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    GemmArgs g{};
+    g.a = d_x; g.a_si = K; g.a_sl = 1;          // X[m,k]
+    g.b = d_w; g.b_sl = 1; g.b_sj = K;          // W^T: B(k,n) = W[n,k]
+    g.c = d_y; g.I = M; g.J = N; g.L = K;
+    g.bias = d_bias; g.bias_per_row = 0;
+    g.relu = relu; g.mask_out = relu ? d_mask : nullptr;
+    return launch_gemm(g, (cudaStream_t)stream);
+}
+
+extern "C" nvq_status nvq_linear_bwd_f32(float* d_dw, float* d_db, float* d_dx, const float* d_g,
+                                         const float* d_x, const float* d_w, const float* d_mask,
+                                         int M, int N, int K, int device, void* stream) {
+    NVQ_REQUIRE(d_g && M > 0 && N > 0 && K > 0, "nvq_linear_bwd_f32: bad argument");
+    nvq_status s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (d_dw) {   // dW[n,k] = sum_m G[m,n] X[m,k]
+        NVQ_REQUIRE(d_x, "nvq_linear_bwd_f32: dW needs x");
+        GemmArgs g{};
+        g.a = d_g; g.a_si = 1; g.a_sl = N;
+        g.b = d_x; g.b_sl = K; g.b_sj = 1;
+        g.c = d_dw; g.I = N; g.J = K; g.L = M;
+        s = launch_gemm(g, st);
+        if (s != NVQ_OK) return s;
+    }
+    if (d_db) {
+        colsum_kernel<<<(N + 127) / 128, 128, 0, st>>>(d_g, d_db, M, N);
+        NVQ_LAUNCHED();
+    }
+    if (d_dx) {   // dX[m,k] = sum_n G[m,n] W[n,k]
+        NVQ_REQUIRE(d_w, "nvq_linear_bwd_f32: dX needs w");
+        GemmArgs g{};
+        g.a = d_g; g.a_si = N; g.a_sl = 1;
+        g.b = d_w; g.b_sl = K; g.b_sj = 1;
+        g.c = d_dx; g.I = M; g.J = K; g.L = N;
+        g.mask_in = d_mask;
+        s = launch_gemm(g, st);
+        if (s != NVQ_OK) return s;
+    }
+    return NVQ_OK;
+}
+
+extern "C" nvq_status nvq_relu_fwd_f32(float* d_out, float* d_mask, const float* d_x, size_t n,
+                                       int device, void* stream) {
+    if (n == 0) return NVQ_OK;
+    NVQ_REQUIRE(d_out && d_x, "nvq_relu_fwd_f32: null buffer");
+    nvq_status s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    relu_kernel<<<ew_grid(n, device), 256, 0, (cudaStream_t)stream>>>(d_out, d_mask, d_x, n);
+    NVQ_LAUNCHED();
+    return NVQ_OK;
+}
+
+extern "C" nvq_status nvq_softmax_ce_f32(float* d_grad, float* d_loss, const float* d_logits,
+                                         const int32_t* d_labels, float* d_yhat, int M, int C,
+                                         int device, void* stream) {
+    NVQ_REQUIRE(d_grad && d_logits && d_labels && d_yhat && M > 0 && C > 0,
+                "nvq_softmax_ce_f32: bad argument");
+    nvq_status s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    softmax_ce_kernel<<<1, 256, 256 * sizeof(double), (cudaStream_t)stream>>>(d_grad, d_loss, d_logits,
+                                                                             d_labels, d_yhat, M, C);
+    NVQ_LAUNCHED();
+    return NVQ_OK;
+}
+
+extern "C" nvq_status nvq_sgd_step_f32(float* d_param, const float* d_grad, size_t n, float lr,
+                                       float grad_scale, int device, void* stream) {
+    if (n == 0) return NVQ_OK;
+    NVQ_REQUIRE(d_param && d_grad, "nvq_sgd_step_f32: null buffer");
+    nvq_status s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    sgd_kernel<<<ew_grid(n, device), 256, 0, (cudaStream_t)stream>>>(d_param, d_grad, n, lr, grad_scale);
+    NVQ_LAUNCHED();
+    return NVQ_OK;
+}
+
+extern "C" nvq_status nvq_conv2d_out_size(int H, int W, int KH, int KW, int sh, int sw, int ph, int pw,
+                                          int* OH, int* OW) {
+    NVQ_REQUIRE(OH && OW && sh > 0 && sw > 0, "nvq_conv2d_out_size: bad argument");
+    *OH = (H + 2 * ph - KH) / sh + 1;
+    *OW = (W + 2 * pw - KW) / sw + 1;
+    return NVQ_OK;
+}
+
+extern "C" nvq_status nvq_im2col_f32(float* d_col, const float* d_x, int N, int C, int H, int W,
+                                     int KH, int KW, int sh, int sw, int ph, int pw,
+                                     nvq_pad_mode mode, int device, void* stream) {
+    ConvGeom g;
+    nvq_status s = geom(g, N, C, H, W, KH, KW, sh, sw, ph, pw, mode);
+    if (s != NVQ_OK) return s;
+    NVQ_REQUIRE(d_col && d_x, "nvq_im2col_f32: null buffer");
+    s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    size_t total = (size_t)C * KH * KW * N * g.OH * g.OW;
+    im2col_f32_kernel<<<ew_grid(total, device), 256, 0, (cudaStream_t)stream>>>(d_col, d_x, g);
+    NVQ_LAUNCHED();
+    return NVQ_OK;
+}
+
+extern "C" nvq_status nvq_conv2d_fwd_f32(float* d_out, const float* d_x, const float* d_w,
+                                         const float* d_bias, float* d_col, int N, int C, int H,
+                                         int W, int Cout, int KH, int KW, int sh, int sw, int ph,
+                                         int pw, nvq_pad_mode mode, int device, void* stream) {
+    NVQ_REQUIRE(d_out && d_w && d_col && Cout > 0, "nvq_conv2d_fwd_f32: bad argument");
+    nvq_status s = nvq_im2col_f32(d_col, d_x, N, C, H, W, KH, KW, sh, sw, ph, pw, mode, device, stream);
+    if (s != NVQ_OK) return s;
+    ConvGeom gm;
+    geom(gm, N, C, H, W, KH, KW, sh, sw, ph, pw, mode);
+    const int CKK = C * KH * KW, L = N * gm.OH * gm.OW;
+    GemmArgs g{};
+    g.a = d_w; g.a_si = CKK; g.a_sl = 1;        // w_col[cout, ckk]
+    g.b = d_col; g.b_sl = L; g.b_sj = 1;        // col[ckk, l]
+    g.c = d_out; g.I = Cout; g.J = L; g.L = CKK;
+    g.bias = d_bias; g.bias_per_row = 1;
+    g.out_mode = 1; g.inner = gm.OH * gm.OW;    // (n, cout, oh, ow) contiguous
+    return launch_gemm(g, (cudaStream_t)stream);
+}
+
+extern "C" nvq_status nvq_conv2d_q_sizes(int N, int C, int H, int W, int Cout, int KH, int KW, int sh,
+                                         int sw, int ph, int pw, size_t* rows, size_t* kpad) {
+    NVQ_REQUIRE(rows && kpad && sh > 0 && sw > 0, "nvq_conv2d_q_sizes: bad argument");
+    int OH = (H + 2 * ph - KH) / sh + 1, OW = (W + 2 * pw - KW) / sw + 1;
+    *rows = (size_t)N * OH * OW;
+    *kpad = ((size_t)C * KH * KW + 15) / 16 * 16;
+    (void)Cout;
+    return NVQ_OK;
+}
+
+extern "C" nvq_status nvq_conv2d_fwd_q(float* d_out, const float* d_x, const uint8_t* d_wq,
+                                       nvq_dtype w_fmt, const float* d_w_scales, const float* d_bias,
+                                       uint16_t* d_col_bf16, uint16_t* d_y_bf16, void* d_workspace,
+                                       size_t workspace_bytes, int N, int C, int H, int W, int Cout,
+                                       int KH, int KW, int sh, int sw, int ph, int pw,
+                                       nvq_pad_mode mode, int device, void* stream) {
+    ConvGeom g;
+    nvq_status s = geom(g, N, C, H, W, KH, KW, sh, sw, ph, pw, mode);
+    if (s != NVQ_OK) return s;
+    NVQ_REQUIRE(d_out && d_x && d_wq && d_w_scales && d_col_bf16 && d_y_bf16, "nvq_conv2d_fwd_q: null buffer");
+    NVQ_REQUIRE(Cout % 8 == 0, "nvq_conv2d_fwd_q: Cout (%d) must be a multiple of 8", Cout);
+    NVQ_REQUIRE(w_fmt == NVQ_E4M3 || w_fmt == NVQ_E5M2, "nvq_conv2d_fwd_q: weight format must be E4M3 or E5M2");
+    s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t L = (size_t)N * g.OH * g.OW;
+    const int Kpad = (C * KH * KW + 15) / 16 * 16;
+    im2col_bf16_rows_kernel<<<ew_grid(L * Kpad, device), 256, 0, st>>>(d_col_bf16, d_x, g, Kpad);
+    NVQ_LAUNCHED();
+    s = nvq_linear_fwd(d_y_bf16, d_col_bf16, d_wq, w_fmt, d_w_scales, d_bias, L, (size_t)Cout,
+                       (size_t)Kpad, d_workspace, workspace_bytes, device, stream);
+    if (s != NVQ_OK) return s;
+    rows_bf16_to_nchw_kernel<<<ew_grid(L * Cout, device), 256, 0, st>>>(d_out, d_y_bf16, N, Cout, g.OH * g.OW);
+    NVQ_LAUNCHED();
+    return NVQ_OK;
+}

@@ -187,6 +187,40 @@ struct DequantOp {
     }
 };
 
+// ---- per-row (per output channel) quantisation of a weight matrix ----------------------
+//   s_r = amax_r / FMAX (1 when the row is all zero);  q = cvt_sat_rne(w * (FMAX / amax_r))
+// One block per row: block-wide amax, then the row is read again (from L1/L2) and converted.
+template <int FMT>
+__global__ void __launch_bounds__(256)
+quantize_rows_kernel(uint8_t* __restrict__ dst, float* __restrict__ scales,
+                     const float* __restrict__ src, size_t cols) {
+    const float* row = src + (size_t)blockIdx.x * cols;
+    uint8_t* out = dst + (size_t)blockIdx.x * cols;
+    float m = 0.f;
+    for (size_t i = threadIdx.x; i < cols; i += blockDim.x) m = fmaxf(m, fabsf(row[i]));
+    unsigned int b = __float_as_uint(m);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) b = max(b, __shfl_xor_sync(0xFFFFFFFFu, b, o));
+    __shared__ unsigned int warp_max[8];
+    __shared__ float s_inv;
+    if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = b;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; w++) b = max(b, warp_max[w]);
+        float amax = __uint_as_float(b), scale = 1.f, inv = 1.f;
+        if (amax != 0.f) {
+            scale = __fdiv_rn(amax, fmt_max<FMT>());
+            inv = __fdiv_rn(fmt_max<FMT>(), amax);
+        }
+        scales[blockIdx.x] = scale;
+        s_inv = inv;
+    }
+    __syncthreads();
+    const uint32_t invu = __float_as_uint(s_inv);
+    for (size_t i = threadIdx.x; i < cols; i += blockDim.x)
+        out[i] = (uint8_t)spec_f32_to_fp8<FMT>(spec_mul_bits(__float_as_uint(row[i]), invu));
+}
+
 nvq_status launch_amax(const float* d_src, size_t n, float* d_amax, int device, cudaStream_t st) {
     NVQ_CUDA(cudaMemsetAsync(d_amax, 0, sizeof(float), st));
     if (n == 0) return NVQ_OK;
@@ -278,4 +312,22 @@ extern "C" nvq_status nvq_quantize_fp8_tensor(uint8_t* d_dst, float* d_amax_scal
         return NVQ_OK;
     }
     return ew_launch(op, d_src, d_dst, n, device, st, 32, 16);
+}
+
+extern "C" nvq_status nvq_quantize_fp8_rows(uint8_t* d_dst, float* d_scales, const float* d_src,
+                                            size_t rows, size_t cols, nvq_dtype fmt, int device,
+                                            void* stream) {
+    NVQ_REQUIRE(fmt == NVQ_E4M3 || fmt == NVQ_E5M2, "nvq_quantize_fp8_rows: fmt must be E4M3 or E5M2");
+    if (rows == 0 || cols == 0) return NVQ_OK;
+    NVQ_REQUIRE(d_dst && d_scales && d_src, "nvq_quantize_fp8_rows: null buffer");
+    NVQ_REQUIRE(rows < (1u << 31), "nvq_quantize_fp8_rows: too many rows");
+    nvq_status s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (fmt == NVQ_E4M3)
+        quantize_rows_kernel<NVQ_E4M3><<<(unsigned)rows, 256, 0, st>>>(d_dst, d_scales, d_src, cols);
+    else
+        quantize_rows_kernel<NVQ_E5M2><<<(unsigned)rows, 256, 0, st>>>(d_dst, d_scales, d_src, cols);
+    NVQ_LAUNCHED();
+    return NVQ_OK;
 }

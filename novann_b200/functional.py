@@ -57,3 +57,127 @@ def linear_q_host(x_bf16_bits: np.ndarray, wq: np.ndarray, w_scales: np.ndarray,
     device_sync(device)
     check_device_errors(device)
     return dy.to_numpy(np.uint16, (m, n))
+
+
+# ------------------------------------------------------------------ fp32 layers (host arrays)
+def _f32(a):
+    return np.ascontiguousarray(a, np.float32)
+
+
+def linear_f32_host(x, w, b=None, device: int = 0, relu: bool = False):
+    """``F.linear`` (novann/functional.py:147-163) in fp32 on the GPU.  With ``relu`` the
+    fused ``F.relu`` is applied and (out, mask) is returned."""
+    x, w = _f32(x), _f32(w)
+    m, k = x.shape
+    n = w.shape[0]
+    dx, dw = DeviceBuffer.from_numpy(x, device), DeviceBuffer.from_numpy(w, device)
+    db = DeviceBuffer.from_numpy(_f32(b).reshape(-1), device) if b is not None else None
+    dy = DeviceBuffer(max(4, m * n * 4), device)
+    dm = DeviceBuffer(max(4, m * n * 4), device) if relu else None
+    check(lib().nvq_linear_fwd_f32(dy.at(0), dx.at(0), dw.at(0), db.at(0) if db else None, m, n, k,
+                                   int(relu), dm.at(0) if dm else None, device, None))
+    y = dy.to_numpy(np.float32, (m, n))
+    return (y, dm.to_numpy(np.float32, (m, n))) if relu else y
+
+
+def linear_bwd_f32_host(grad, x, w, with_bias: bool = True, device: int = 0, mask=None):
+    """``Linear.backward`` (novann/layers/linear/linear.py:85-108): returns (dW (N,K),
+    db (1,N) or None, dX (M,K)); ``mask`` (M,K) multiplies dX (``ReLU.backward``)."""
+    grad, x, w = _f32(grad), _f32(x), _f32(w)
+    m, n = grad.shape
+    k = x.shape[1]
+    dg, dx, dw = (DeviceBuffer.from_numpy(a, device) for a in (grad, x, w))
+    o_dw, o_db, o_dx = DeviceBuffer(n * k * 4, device), DeviceBuffer(n * 4, device), DeviceBuffer(m * k * 4, device)
+    dmask = DeviceBuffer.from_numpy(_f32(mask), device) if mask is not None else None
+    check(lib().nvq_linear_bwd_f32(o_dw.at(0), o_db.at(0) if with_bias else None, o_dx.at(0), dg.at(0),
+                                   dx.at(0), dw.at(0), dmask.at(0) if dmask else None, m, n, k,
+                                   device, None))
+    return (o_dw.to_numpy(np.float32, (n, k)),
+            o_db.to_numpy(np.float32, (1, n)) if with_bias else None,
+            o_dx.to_numpy(np.float32, (m, k)))
+
+
+def relu_host(x, device: int = 0):
+    """``F.relu(x, extras=True)`` (novann/functional.py:8-22): returns (out, mask)."""
+    x = _f32(x)
+    d = DeviceBuffer.from_numpy(x, device)
+    o, mk = DeviceBuffer(max(4, x.nbytes), device), DeviceBuffer(max(4, x.nbytes), device)
+    check(lib().nvq_relu_fwd_f32(o.at(0), mk.at(0), d.at(0), x.size, device, None))
+    return o.to_numpy(np.float32, x.shape), mk.to_numpy(np.float32, x.shape)
+
+
+def softmax_ce_host(logits, labels, device: int = 0):
+    """``CrossEntropyLoss.__call__`` (novann/losses/loss_functions.py:69-75): (loss, grad)."""
+    z = _f32(logits)
+    m, c = z.shape
+    lab = np.ascontiguousarray(labels, np.int32)
+    dz, dl = DeviceBuffer.from_numpy(z, device), DeviceBuffer.from_numpy(lab, device)
+    g, yh, ls = DeviceBuffer(z.nbytes, device), DeviceBuffer(z.nbytes, device), DeviceBuffer(4, device)
+    check(lib().nvq_softmax_ce_f32(g.at(0), ls.at(0), dz.at(0), dl.at(0), yh.at(0), m, c, device, None))
+    return ls.to_numpy(np.float32, (1,))[0], g.to_numpy(np.float32, (m, c))
+
+
+def conv2d_out_size(h, w, kh, kw, sh, sw, ph, pw):
+    oh, ow = C.c_int(), C.c_int()
+    check(lib().nvq_conv2d_out_size(h, w, kh, kw, sh, sw, ph, pw, C.byref(oh), C.byref(ow)))
+    return oh.value, ow.value
+
+
+def _pad_mode(name: str) -> int:
+    if name not in _lib.PAD_MODES:
+        raise ValueError(f"padding_mode Only accept {tuple(_lib.PAD_MODES)} not '{name}'")
+    return _lib.PAD_MODES[name]
+
+
+def conv2d_f32_host(x, w, b=None, stride=(1, 1), padding=(0, 0), padding_mode: str = "zeros",
+                    device: int = 0, return_col: bool = False):
+    """``F.conv2d`` (novann/functional.py:275-385) in fp32 on the GPU: (N,Cout,OH,OW), and with
+    ``return_col`` also the im2col matrix (C*KH*KW, N*OH*OW) the reference caches."""
+    x, w = _f32(x), _f32(w)
+    n, c, h, wd = x.shape
+    cout, _, kh, kw = w.shape
+    mode = _pad_mode(padding_mode)
+    oh, ow = conv2d_out_size(h, wd, kh, kw, stride[0], stride[1], padding[0], padding[1])
+    dx, dw = DeviceBuffer.from_numpy(x, device), DeviceBuffer.from_numpy(w, device)
+    db = DeviceBuffer.from_numpy(_f32(b).reshape(-1), device) if b is not None else None
+    col = DeviceBuffer(max(4, c * kh * kw * n * oh * ow * 4), device)
+    out = DeviceBuffer(max(4, n * cout * oh * ow * 4), device)
+    check(lib().nvq_conv2d_fwd_f32(out.at(0), dx.at(0), dw.at(0), db.at(0) if db else None, col.at(0),
+                                   n, c, h, wd, cout, kh, kw, stride[0], stride[1], padding[0],
+                                   padding[1], mode, device, None))
+    y = out.to_numpy(np.float32, (n, cout, oh, ow))
+    if return_col:
+        return y, col.to_numpy(np.float32, (c * kh * kw, n * oh * ow))
+    return y
+
+
+def conv2d_q_host(x, wq, w_scales, b, kernel, stride=(1, 1), padding=(0, 0),
+                  padding_mode: str = "zeros", fmt: str = "e4m3", device: int = 0):
+    """Quantised-weight ``F.conv2d``: ``wq`` is (Cout, kpad) FP8 codes of the zero-padded
+    ``w.reshape(Cout, C*KH*KW)``, ``w_scales`` (Cout,).  Returns fp32 (N,Cout,OH,OW)."""
+    x = _f32(x)
+    n, c, h, wd = x.shape
+    kh, kw = kernel
+    cout = wq.shape[0]
+    mode = _pad_mode(padding_mode)
+    rows, kpad = C.c_size_t(), C.c_size_t()
+    check(lib().nvq_conv2d_q_sizes(n, c, h, wd, cout, kh, kw, stride[0], stride[1], padding[0], padding[1],
+                                   C.byref(rows), C.byref(kpad)))
+    if wq.shape[1] != kpad.value:
+        raise ValueError(f"weight codes must be (Cout, {kpad.value})")
+    oh, ow = conv2d_out_size(h, wd, kh, kw, stride[0], stride[1], padding[0], padding[1])
+    dx = DeviceBuffer.from_numpy(x, device)
+    dq = DeviceBuffer.from_numpy(np.ascontiguousarray(wq, np.uint8), device)
+    ds = DeviceBuffer.from_numpy(_f32(w_scales), device)
+    db = DeviceBuffer.from_numpy(_f32(b).reshape(-1), device) if b is not None else None
+    col = DeviceBuffer(rows.value * kpad.value * 2, device)
+    yb = DeviceBuffer(rows.value * cout * 2, device)
+    ws = DeviceBuffer(linear_workspace_bytes(cout, kpad.value, fmt), device)
+    out = DeviceBuffer(n * cout * oh * ow * 4, device)
+    check(lib().nvq_conv2d_fwd_q(out.at(0), dx.at(0), dq.at(0), _lib.DTYPE_IDS[fmt], ds.at(0),
+                                 db.at(0) if db else None, col.at(0), yb.at(0), ws.at(0), ws.nbytes,
+                                 n, c, h, wd, cout, kh, kw, stride[0], stride[1], padding[0], padding[1],
+                                 mode, device, None))
+    device_sync(device)
+    check_device_errors(device)
+    return out.to_numpy(np.float32, (n, cout, oh, ow))

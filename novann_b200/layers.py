@@ -1,0 +1,221 @@
+"""GPU-backed layers with the reference's ``Layer`` contract (NumPy in, NumPy out).
+
+* ``Linear`` / ``ReLU`` / ``Conv2d``: fp32, the reference's own arithmetic on the GPU
+  (``novann/layers/linear/linear.py``, ``novann/layers/activations/relu.py``,
+  ``novann/layers/convolutional/conv2d.py`` forward).
+* ``QuantLinear`` / ``QuantConv2d``: the weight is kept as FP8 (per output channel) or FP4
+  (block 32) codes and the forward contraction runs on the tcgen05 tensor cores with bf16
+  activations.  ``parameters()`` still exposes the fp32 master weight; ``requantize()``
+  refreshes the codes after the optimiser changed it.
+
+Every call uploads its inputs and downloads its result (that is the reference's API); the
+device-resident fast path for whole training steps is ``novann_b200.train``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib, functional as F
+from ._lib import check, lib
+from .device import DeviceBuffer, device_sync
+from .module import Layer, Parameters
+
+
+def kaiming_normal(shape) -> np.ndarray:
+    """N(0, 2 / fan_in) from the global legacy NumPy RNG, the law the reference's Sequential
+    gives a Linear followed by ReLU (novann/core/init.py:155-179)."""
+    fan_in = int(np.prod(shape[1:]))
+    return np.random.normal(0.0, np.sqrt(2.0 / fan_in), shape).astype(np.float32)
+
+
+def _pair(x):
+    if isinstance(x, int):
+        return (x, x)
+    if isinstance(x, str):
+        if x == "valid":
+            return (0, 0)
+        if x == "same":
+            raise ValueError("The 'same' value is not currently supported")
+        raise ValueError(f"Unsupported value '{x}'")
+    return tuple(x)
+
+
+def _dev(a: np.ndarray, device: int) -> DeviceBuffer:
+    return DeviceBuffer.from_numpy(np.ascontiguousarray(a), device)
+
+
+class Linear(Layer):
+    """y = x W^T + b in fp32 on the GPU; same attributes and gradient rules as the reference."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, init=None,
+                 device: int = 0) -> None:
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.use_bias = bias
+        self.init_fn = init
+        self.device = device
+        self.weight = None
+        self.bias = None
+        self._cache_input = None
+        self.reset_parameters()
+
+    def reset_parameters(self, initializer=None) -> None:
+        init = initializer or self.init_fn or kaiming_normal
+        w = init((self.out_features, self.in_features))
+        self.weight = Parameters(np.asarray(w, dtype=np.float32))
+        self.weight.name = "linear weight"
+        if self.use_bias:
+            self.bias = Parameters(np.zeros((1, self.out_features), dtype=np.float32))
+            self.bias.name = "linear bias"
+        else:
+            self.bias = None
+
+    def forward(self, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x.astype(np.float32, copy=False))
+        self._cache_input = x
+        return F.linear_f32_host(x, self.weight.data, None if self.bias is None else self.bias.data,
+                                 self.device)
+
+    def backward(self, grad: np.ndarray) -> np.ndarray:
+        grad = np.ascontiguousarray(grad.astype(np.float32, copy=False))
+        dw, db, dx = F.linear_bwd_f32_host(grad, self._cache_input, self.weight.data,
+                                           self.bias is not None, self.device)
+        self.weight.grad = dw
+        if self.bias is not None:
+            self.bias.grad = db
+        return dx
+
+    def parameters(self):
+        return [self.weight] + ([self.bias] if self.bias is not None else [])
+
+    def __repr__(self):
+        return f"Linear(in_features={self.in_features}, out_features={self.out_features}, bias={self.use_bias})"
+
+
+class ReLU(Layer):
+    def __init__(self, device: int = 0) -> None:
+        super().__init__()
+        self._mask = None
+        self.device = device
+
+    def forward(self, x: np.ndarray) -> np.ndarray:
+        out, self._mask = F.relu_host(np.ascontiguousarray(x, np.float32), self.device)
+        return out
+
+    def backward(self, grad: np.ndarray) -> np.ndarray:
+        return grad * self._mask
+
+    def __repr__(self):
+        return "ReLU()"
+
+
+class QuantLinear(Linear):
+    """Linear whose forward contraction uses FP8 / FP4 weight codes on the tensor cores.
+
+    Forward: ``bf16(x) @ dequant(Wq)^T * s + b`` -> bf16 -> returned as float32.  Backward
+    follows the reference's rules on the fp32 master weight (straight-through)."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, init=None,
+                 fmt: str = "e4m3", device: int = 0) -> None:
+        self.fmt = fmt
+        self._codes = self._scales = None
+        super().__init__(in_features, out_features, bias, init, device)
+
+    def reset_parameters(self, initializer=None) -> None:
+        super().reset_parameters(initializer)
+        self.requantize()
+
+    def requantize(self) -> None:
+        """Recompute the weight codes from ``weight.data`` (call after an optimiser step)."""
+        from . import quant
+        self._codes, self._scales = quant.quantize_weight(self.weight.data, self.fmt, self.device)
+
+    def forward(self, x: np.ndarray) -> np.ndarray:
+        from . import quant
+        x = np.ascontiguousarray(x.astype(np.float32, copy=False))
+        self._cache_input = x
+        xb = quant.cast(x, "bf16", device=self.device)
+        b = None if self.bias is None else self.bias.data.reshape(-1)
+        yb = F.linear_q_host(xb, self._codes, self._scales, b, self.fmt, self.device)
+        return quant.cast(yb, "f32", src_dtype="bf16", device=self.device)
+
+
+class Conv2d(Layer):
+    """2-D convolution, fp32 forward on the GPU (im2col + GEMM, the reference's layout)."""
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0,
+                 bias: bool = True, padding_mode: str = "zeros", init=None, device: int = 0):
+        super().__init__()
+        self.in_channels, self.out_channels = in_channels, out_channels
+        self.KH, self.KW = _pair(kernel_size)
+        self.sh, self.sw = _pair(stride if stride is not None else kernel_size)
+        self.ph, self.pw = _pair(padding)
+        self.pm = padding_mode
+        self.init_fn = init
+        self.use_bias = bias
+        self.device = device
+        self.weight = self.bias = None
+        self._cache = {}
+        self.reset_parameters()
+
+    def reset_parameters(self, initializer=None):
+        init = initializer or self.init_fn or kaiming_normal
+        w = init((self.out_channels, self.in_channels, self.KH, self.KW))
+        self.weight = Parameters(np.asarray(w, dtype=np.float32))
+        self.weight.name = "conv2d weight"
+        if self.use_bias:
+            self.bias = Parameters(np.zeros((self.out_channels, 1), dtype=np.float32))
+            self.bias.name = "conv2d bias"
+        else:
+            self.bias = None
+
+    def forward(self, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x.astype(np.float32, copy=False))
+        out, col = F.conv2d_f32_host(x, self.weight.data, None if self.bias is None else self.bias.data,
+                                     (self.sh, self.sw), (self.ph, self.pw), self.pm, self.device,
+                                     return_col=True)
+        self._cache = {"x_shape": x.shape, "col": col,
+                       "w_col": self.weight.data.reshape(self.out_channels, -1)}
+        return out
+
+    def backward(self, grad: np.ndarray) -> np.ndarray:
+        raise NotImplementedError(
+            "Conv2d.backward (col2im) is not part of this build: forward only")
+
+    def parameters(self):
+        return [self.weight] + ([self.bias] if self.bias is not None else [])
+
+    def __repr__(self):
+        return (f"Conv2d(in_channels={self.in_channels}, out_channels={self.out_channels}, "
+                f"kernel_size={(self.KH, self.KW)}, stride={(self.sh, self.sw)}, "
+                f"padding={(self.ph, self.pw)}, bias={self.use_bias})")
+
+
+class QuantConv2d(Conv2d):
+    """Conv2d whose im2col contraction runs on the tensor cores with FP8 weight codes."""
+
+    def __init__(self, *args, fmt: str = "e4m3", **kwargs):
+        self.fmt = fmt
+        self._codes = self._scales = None
+        super().__init__(*args, **kwargs)
+
+    def reset_parameters(self, initializer=None):
+        super().reset_parameters(initializer)
+        self.requantize()
+
+    def requantize(self) -> None:
+        from . import quant
+        w_col = self.weight.data.reshape(self.out_channels, -1)
+        kpad = (w_col.shape[1] + 15) // 16 * 16
+        padded = np.zeros((self.out_channels, kpad), np.float32)
+        padded[:, :w_col.shape[1]] = w_col
+        self._codes, self._scales = quant.quantize_weight(padded, self.fmt, self.device)
+
+    def forward(self, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x.astype(np.float32, copy=False))
+        self._cache = {"x_shape": x.shape}
+        b = None if self.bias is None else self.bias.data.reshape(-1)
+        return F.conv2d_q_host(x, self._codes, self._scales, b, (self.KH, self.KW), (self.sh, self.sw),
+                               (self.ph, self.pw), self.pm, self.fmt, self.device)

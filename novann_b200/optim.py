@@ -1,0 +1,37 @@
+"""Vanilla ``SGD`` with the reference's contract (``novann/optim/sgd.py:6-87``, the path with
+momentum 0, weight decay 0 and no clipping): ``p.data -= lr * p.grad`` on the GPU, written
+back into the same NumPy arrays so the layers' ``Parameters`` stay the source of truth."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from ._lib import check, lib
+from .device import DeviceBuffer
+
+
+class SGD:
+    def __init__(self, parameters, lr: float, momentum: float = 0, weight_decay: float = 0,
+                 max_grad_norm=None, device: int = 0) -> None:
+        if momentum or weight_decay or max_grad_norm:
+            raise NotImplementedError("only the vanilla SGD path (momentum 0, weight decay 0, "
+                                      "no clipping) is built")
+        self.params = list(parameters)
+        self.lr = float(lr)
+        self.device = device
+
+    def step(self) -> None:
+        for p in self.params:
+            if p.grad is None:
+                continue
+            d = DeviceBuffer.from_numpy(np.ascontiguousarray(p.data, np.float32), self.device)
+            g = DeviceBuffer.from_numpy(np.ascontiguousarray(p.grad, np.float32), self.device)
+            check(lib().nvq_sgd_step_f32(d.at(0), g.at(0), p.data.size, C.c_float(self.lr),
+                                         C.c_float(1.0), self.device, None))
+            new = d.to_numpy(np.float32, p.data.shape)
+            p.data[...] = new
+
+    def zero_grad(self, set_to_none: bool = False) -> None:
+        for p in self.params:
+            p.zero_grad(set_to_none=set_to_none)

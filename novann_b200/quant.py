@@ -192,3 +192,20 @@ def dequantize_fp4_b32(packed: np.ndarray, scales: np.ndarray, device: int = 0) 
     o = DeviceBuffer(out.nbytes, device)
     dequantize_fp4_b32_device(o, p, s, rows, half * 2)
     return o.download(out)
+
+
+def quantize_weight(w: np.ndarray, fmt: str = "e4m3", device: int = 0):
+    """Weight preparation for the quantised layers.
+
+    FP8 (``"e4m3"`` / ``"e5m2"``): per-output-channel scales; returns (codes uint8 (N, K),
+    scales float32 (N,)).  FP4 (``"e2m1_b32"``): the weight is rounded to bf16 and quantised
+    in blocks of 32 along K; returns (packed uint8 (N, K/2), scales float32 (N, K/32))."""
+    w = np.ascontiguousarray(w, np.float32)
+    n, k = w.shape
+    if fmt == "e2m1_b32":
+        return quantize_fp4_b32(cast(w, "bf16", device=device), device)
+    d = DeviceBuffer.from_numpy(w, device)
+    q = DeviceBuffer(max(1, w.size), device)
+    s = DeviceBuffer(max(4, n * 4), device)
+    check(lib().nvq_quantize_fp8_rows(q.at(0), s.at(0), d.at(0), n, k, _fmt_id(fmt), device, None))
+    return q.to_numpy(np.uint8, (n, k)), s.to_numpy(np.float32, (n,))

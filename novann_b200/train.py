@@ -1,0 +1,144 @@
+"""Device-resident training step of an MLP: the reference's loop body
+(``novann/utils/train/train.py:60-75``: zero_grad, forward, CrossEntropyLoss, backward,
+SGD.step) for ``Sequential(Linear, ReLU, ..., Linear)`` with every tensor kept in HBM.
+
+Weights, activations, masks and gradients live in one device arena; a step is a fixed
+sequence of kernel launches on one stream (fused Linear+bias+ReLU forward, softmax-CE,
+Linear backward with the ReLU mask folded into dX, SGD over the flat parameter bucket).
+With more than one rank the flat gradient bucket is summed over ranks with one NCCL
+all-reduce and scaled by 1/world inside the SGD kernel, which equals the gradient of the
+global batch because the reference divides its loss gradient by the local batch size.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import check, lib
+from .device import DeviceBuffer, Stream, _sptr
+
+
+def shard_rows(n_rows: int, rank: int, world: int) -> tuple[int, int]:
+    """Contiguous row range [lo, hi) of ``rank`` when ``n_rows`` rows are split evenly."""
+    if n_rows % world:
+        raise ValueError(f"{n_rows} rows do not split evenly over {world} ranks")
+    per = n_rows // world
+    return rank * per, (rank + 1) * per
+
+
+def flatten_params(params) -> np.ndarray:
+    """[W0, b0, W1, b1, ...] -> one flat fp32 bucket (layer order, weight then bias)."""
+    return np.concatenate([np.ascontiguousarray(p, np.float32).ravel() for p in params])
+
+
+def unflatten_params(flat: np.ndarray, dims) -> list[np.ndarray]:
+    out, off = [], 0
+    for fi, fo in zip(dims[:-1], dims[1:]):
+        out.append(flat[off:off + fo * fi].reshape(fo, fi).copy())
+        off += fo * fi
+        out.append(flat[off:off + fo].reshape(1, fo).copy())
+        off += fo
+    return out
+
+
+class Communicator:
+    """NCCL communicator of the library (one process per GPU)."""
+
+    def __init__(self, unique_id: bytes, rank: int, world: int, device: int):
+        self.rank, self.world, self.device = rank, world, device
+        buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
+        h = C.c_void_p()
+        check(lib().nvq_comm_init(buf, rank, world, device, C.byref(h)))
+        self.handle = h.value
+
+    @staticmethod
+    def make_unique_id() -> bytes:
+        buf = (C.c_uint8 * 128)()
+        check(lib().nvq_comm_unique_id(buf))
+        return bytes(buf)
+
+    def allreduce_sum(self, buf: DeviceBuffer, n: int, stream=None, offset: int = 0) -> None:
+        check(lib().nvq_allreduce_sum_f32(C.c_void_p(self.handle), buf.at(offset), n, self.device,
+                                          _sptr(stream)))
+
+    def close(self) -> None:
+        if self.handle:
+            lib().nvq_comm_destroy(C.c_void_p(self.handle))
+            self.handle = None
+
+
+class MLPTrainStep:
+    """``step(x, labels)`` runs one training step on the device and returns nothing; read
+    results with ``logits()``, ``loss()``, ``grads()``, ``params()``."""
+
+    def __init__(self, params, batch: int, lr: float, device: int = 0, comm: Communicator | None = None):
+        self.dims = [params[0].shape[1]] + [params[2 * i].shape[0] for i in range(len(params) // 2)]
+        self.nl = len(self.dims) - 1
+        self.batch, self.lr, self.device, self.comm = batch, float(lr), device, comm
+        self.stream = Stream(device)
+        flat = flatten_params(params)
+        self.n_params = flat.size
+        self.d_params = DeviceBuffer.from_numpy(flat, device)
+        self.d_grads = DeviceBuffer(flat.nbytes, device)
+        self.w_off, self.b_off, off = [], [], 0
+        for fi, fo in zip(self.dims[:-1], self.dims[1:]):
+            self.w_off.append(off * 4)
+            off += fo * fi
+            self.b_off.append(off * 4)
+            off += fo
+        f4 = 4 * batch
+        self.d_x = DeviceBuffer(f4 * self.dims[0], device)
+        self.d_labels = DeviceBuffer(4 * batch, device)
+        self.d_act = [self.d_x] + [DeviceBuffer(f4 * d, device) for d in self.dims[1:]]
+        self.d_mask = [DeviceBuffer(f4 * d, device) for d in self.dims[1:-1]]
+        self.d_g = [DeviceBuffer(f4 * d, device) for d in self.dims]     # gradient w.r.t. each activation
+        self.d_yhat = DeviceBuffer(f4 * self.dims[-1], device)
+        self.d_loss = DeviceBuffer(4, device)
+
+    def upload(self, x: np.ndarray, labels: np.ndarray) -> None:
+        self.d_x.upload(np.ascontiguousarray(x, np.float32), stream=self.stream)
+        self.d_labels.upload(np.ascontiguousarray(labels, np.int32), stream=self.stream)
+
+    def launch(self) -> None:
+        """Enqueue one step on ``self.stream`` (inputs already uploaded)."""
+        L, dev, st, B = lib(), self.device, _sptr(self.stream), self.batch
+        for i in range(self.nl):
+            last = i == self.nl - 1
+            check(L.nvq_linear_fwd_f32(self.d_act[i + 1].at(0), self.d_act[i].at(0),
+                                       self.d_params.at(self.w_off[i]), self.d_params.at(self.b_off[i]),
+                                       B, self.dims[i + 1], self.dims[i], 0 if last else 1,
+                                       None if last else self.d_mask[i].at(0), dev, st))
+        check(L.nvq_softmax_ce_f32(self.d_g[self.nl].at(0), self.d_loss.at(0), self.d_act[self.nl].at(0),
+                                   self.d_labels.at(0), self.d_yhat.at(0), B, self.dims[-1], dev, st))
+        for i in reversed(range(self.nl)):
+            check(L.nvq_linear_bwd_f32(self.d_grads.at(self.w_off[i]), self.d_grads.at(self.b_off[i]),
+                                       self.d_g[i].at(0) if i > 0 else None, self.d_g[i + 1].at(0),
+                                       self.d_act[i].at(0), self.d_params.at(self.w_off[i]),
+                                       self.d_mask[i - 1].at(0) if i > 0 else None,
+                                       B, self.dims[i + 1], self.dims[i], dev, st))
+        scale = 1.0
+        if self.comm is not None and self.comm.world > 1:
+            self.comm.allreduce_sum(self.d_grads, self.n_params, stream=self.stream)
+            scale = 1.0 / self.comm.world
+        check(L.nvq_sgd_step_f32(self.d_params.at(0), self.d_grads.at(0), self.n_params,
+                                 C.c_float(self.lr), C.c_float(scale), dev, st))
+
+    def step(self, x: np.ndarray, labels: np.ndarray) -> None:
+        self.upload(x, labels)
+        self.launch()
+        self.stream.sync()
+
+    # ---- results
+    def logits(self) -> np.ndarray:
+        return self.d_act[self.nl].to_numpy(np.float32, (self.batch, self.dims[-1]))
+
+    def loss(self) -> np.float32:
+        return self.d_loss.to_numpy(np.float32, (1,))[0]
+
+    def grads(self) -> list[np.ndarray]:
+        return unflatten_params(self.d_grads.to_numpy(np.float32, (self.n_params,)), self.dims)
+
+    def params(self) -> list[np.ndarray]:
+        return unflatten_params(self.d_params.to_numpy(np.float32, (self.n_params,)), self.dims)

@@ -1,0 +1,92 @@
+"""Pins the CPU oracle's restatement of the reference's fp32 layers against golden vectors
+produced by the reference itself (``tests/golden/make_golden.py``)."""
+import os
+
+import numpy as np
+import pytest
+
+from novann_b200 import workloads
+from oracle import oracle_np as o
+
+G = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def load(name):
+    return np.load(os.path.join(G, f"{name}.npz"))
+
+
+def close(a, b, rel=1e-5):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return np.max(np.abs(a - b)) <= rel * max(1e-30, np.max(np.abs(b)))
+
+
+def test_astype_edge_block_is_what_numpy_gives():
+    g = load("astype")
+    e = workloads.edge_block_f32()
+    assert np.array_equal(e.view(np.uint32), g["f32_bits"])          # generator is stable
+    assert np.array_equal(o.f32_to_f16_bits(e), g["f16_bits"])
+    assert np.array_equal(o.f16_bits_to_f32(g["f16_bits"]).view(np.uint32), g["back_bits"])
+
+
+def test_linear_forward_backward():
+    g = load("linear")
+    y = o.linear_fwd_f32(g["x"], g["w"], g["b"])
+    assert close(y, g["y"], 1e-6)
+    dw, db, dx = o.linear_bwd_f32(g["x"], g["w"], g["g"])
+    assert close(dw, g["dw"], 1e-6) and close(db, g["db"], 1e-6) and close(dx, g["dx"], 1e-6)
+    assert db.shape == (1, 12)
+
+
+def test_relu_and_cross_entropy():
+    g = load("relu_ce")
+    y, m = o.relu_fwd(g["x"])
+    assert np.array_equal(y.view(np.uint32), g["y"].view(np.uint32))
+    assert np.array_equal(m, g["mask_grad"])
+    loss, grad = o.softmax_ce(g["logits"], g["labels"])
+    assert close(grad, g["grad"], 1e-6)
+    assert abs(float(loss) - float(g["loss"])) <= 1e-6 * abs(float(g["loss"]))
+
+
+def test_sgd_update_bit_exact():
+    g = load("sgd")
+    after = (g["before"] - np.float32(0.01) * g["grad"]).astype(np.float32)
+    assert np.array_equal(after.view(np.uint32), g["after"].view(np.uint32))
+
+
+def test_conv2d_forward_all_padding_modes():
+    g = load("conv2d")
+    modes = ["zeros", "reflect", "replicate", "circular"]
+    for i in range(int(g["n_cases"])):
+        kh, kw, sh, sw, ph, pw, mi = (int(v) for v in g[f"geom{i}"])
+        y = o.conv2d_fwd_f32(g[f"x{i}"], g[f"w{i}"], g[f"b{i}"], (sh, sw), (ph, pw), modes[mi])
+        assert y.shape == g[f"y{i}"].shape
+        assert close(y, g[f"y{i}"], 1e-5), i
+    kh, kw, sh, sw, ph, pw, mi = (int(v) for v in g["geom1"])
+    col, _, _ = o.im2col(g["x1"], kh, kw, sh, sw, ph, pw, modes[mi])
+    assert np.array_equal(col, g["col1"])                              # same (c,kh,kw) x (n,oh,ow) order
+
+
+def test_mlp_step_small_full_vectors():
+    g = load("mlp_small")
+    x, y, params = workloads.mlp_inputs(16, (32, 16, 8, 10), seed=1)
+    r = o.mlp_train_step(params, x, y, 0.01)
+    assert close(r["logits"], g["logits"], 1e-6)
+    assert abs(float(r["loss"]) - float(g["loss"])) <= 1e-6 * abs(float(g["loss"]))
+    for i in range(6):
+        assert close(r["grads"][i], g[f"grad{i}"], 1e-5), i
+        assert close(r["params"][i], g[f"new{i}"], 1e-6), i
+        assert r["grads"][i].shape == g[f"grad{i}"].shape
+
+
+def test_mlp_step_config_sampled_vectors():
+    g = load("mlp_config")
+    x, y, params = workloads.mlp_inputs(128, (784, 256, 128, 10), seed=0)
+    r = o.mlp_train_step(params, x, y, 0.01)
+    assert close(r["logits"], g["logits"], 1e-5)
+    assert abs(float(r["loss"]) - float(g["loss"])) <= 1e-5 * abs(float(g["loss"]))
+    assert 4.5 < float(g["loss"]) < 5.2          # ~ln(128): the double-softmax value, not textbook CE
+    for i in range(6):
+        idx = g[f"idx{i}"]
+        assert close(r["grads"][i].ravel()[idx], g[f"grad{i}"], 1e-4), i
+        assert close(r["params"][i].ravel()[idx], g[f"new{i}"], 1e-6), i
+        assert abs(r["grads"][i].astype(np.float64).sum() - float(g[f"gsum{i}"])) <= 1e-4 * (1 + abs(float(g[f"gsum{i}"])))

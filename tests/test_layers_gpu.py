@@ -1,0 +1,247 @@
+"""The fp32 layers, Conv2d forward, quantised layers and the device-resident MLP step on the
+GPU against the reference's golden vectors and the CPU oracle.
+
+Tolerances: fp32 GEMM results differ from NumPy's sgemm by summation order only -> 1e-5 of
+the largest magnitude (1e-4 for gradients that sum 128 products of small numbers);
+elementwise steps (ReLU, SGD) are bit-exact; quantised layers use the 1e-2 / 5e-2 bounds.
+"""
+import os
+
+import numpy as np
+import pytest
+
+import novann_b200 as nb
+from novann_b200 import functional as F, quant, workloads
+from novann_b200.train import MLPTrainStep
+from oracle import oracle_np as o
+
+pytestmark = pytest.mark.gpu
+G = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def load(name):
+    return np.load(os.path.join(G, f"{name}.npz"))
+
+
+def close(a, b, rel=1e-5):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return np.max(np.abs(a - b)) <= rel * max(1e-30, np.max(np.abs(b)))
+
+
+def test_linear_layer_matches_reference_vectors(gpu):
+    g = load("linear")
+    lin = nb.Linear(24, 12, device=gpu)
+    lin.weight.data, lin.bias.data = g["w"].copy(), g["b"].copy()
+    y = lin(g["x"])
+    assert y.shape == (7, 12) and y.dtype == np.float32          # the reference's own assertions
+    assert close(y, g["y"], 1e-6)
+    dx = lin.backward(g["g"])
+    assert dx.shape == (7, 24) and lin.weight.grad.shape == (12, 24) and lin.bias.grad.shape == (1, 12)
+    assert close(dx, g["dx"], 1e-6) and close(lin.weight.grad, g["dw"], 1e-6)
+    assert close(lin.bias.grad, g["db"], 1e-6)
+    assert [p.name for p in lin.parameters()] == ["linear weight", "linear bias"]
+
+
+def test_linear_accepts_float64_input_like_astype(gpu):
+    lin = nb.Linear(8, 4, device=gpu)
+    x = np.random.default_rng(0).standard_normal((3, 8))          # float64, as BatchNorm would emit
+    y = lin(x)
+    assert y.dtype == np.float32
+    assert close(y, o.linear_fwd_f32(x.astype(np.float32), lin.weight.data, lin.bias.data), 1e-6)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (33, 65, 97), (128, 256, 784), (128, 10, 128), (300, 7, 40)])
+def test_linear_f32_shapes_against_float64(gpu, m, n, k):
+    rng = np.random.default_rng(m * n)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    w = rng.standard_normal((n, k)).astype(np.float32)
+    b = rng.standard_normal((1, n)).astype(np.float32)
+    ref = x.astype(np.float64) @ w.T.astype(np.float64) + b
+    assert close(F.linear_f32_host(x, w, b, gpu), ref, 2e-6)
+    gr = rng.standard_normal((m, n)).astype(np.float32)
+    mask = (rng.random((m, k)) > 0.5).astype(np.float32)
+    dw, db, dx = F.linear_bwd_f32_host(gr, x, w, True, gpu, mask=mask)
+    assert close(dw, gr.T.astype(np.float64) @ x, 2e-6)
+    assert close(db, gr.astype(np.float64).sum(0, keepdims=True), 2e-6)
+    assert close(dx, (gr.astype(np.float64) @ w) * mask, 2e-6)
+
+
+def test_relu_bit_exact_including_negative_zero(gpu):
+    g = load("relu_ce")
+    r = nb.ReLU(device=gpu)
+    y = r.forward(g["x"])
+    assert np.array_equal(y.view(np.uint32), g["y"].view(np.uint32))
+    assert np.array_equal(r.backward(np.ones_like(g["x"])), g["mask_grad"])
+
+
+def test_cross_entropy_loss_and_grad(gpu):
+    g = load("relu_ce")
+    loss, grad = nb.CrossEntropyLoss(device=gpu)(g["logits"], g["labels"])
+    assert grad.dtype == np.float32 and close(grad, g["grad"], 1e-6)
+    assert abs(float(loss) - float(g["loss"])) <= 1e-5 * abs(float(g["loss"]))
+
+
+def test_sgd_step_bit_exact_and_in_place(gpu):
+    g = load("sgd")
+    p = nb.Parameters(g["before"].copy())
+    p.grad = g["grad"].copy()
+    held = p.data
+    opt = nb.SGD([p], lr=0.01, device=gpu)
+    opt.step()
+    assert held is p.data                                          # updated in place, as the reference does
+    assert np.array_equal(p.data.view(np.uint32), g["after"].view(np.uint32))
+    opt.zero_grad()
+    assert not p.grad.any()
+
+
+def test_conv2d_forward_reference_vectors(gpu):
+    g = load("conv2d")
+    modes = ["zeros", "reflect", "replicate", "circular"]
+    for i in range(int(g["n_cases"])):
+        kh, kw, sh, sw, ph, pw, mi = (int(v) for v in g[f"geom{i}"])
+        w = g[f"w{i}"]
+        layer = nb.Conv2d(w.shape[1], w.shape[0], (kh, kw), stride=(sh, sw), padding=(ph, pw),
+                          padding_mode=modes[mi], device=gpu)
+        layer.weight.data, layer.bias.data = w.copy(), g[f"b{i}"].copy()
+        y = layer(g[f"x{i}"])
+        assert y.shape == g[f"y{i}"].shape and y.dtype == np.float32
+        assert close(y, g[f"y{i}"], 1e-5), i
+        if i == 1:
+            assert np.array_equal(layer._cache["col"], g["col1"])   # same im2col ordering, bit for bit
+
+
+def test_conv2d_rejects_bad_padding(gpu):
+    with pytest.raises(ValueError):
+        nb.Conv2d(1, 1, 3, padding="same")
+    layer = nb.Conv2d(1, 1, 3, padding_mode="mirror", device=gpu)
+    with pytest.raises(ValueError):
+        layer(np.zeros((1, 1, 5, 5), np.float32))
+
+
+def test_weight_quantisation_per_channel_bit_exact(gpu):
+    _, w, _ = workloads.linear_inputs(8, 96, 200, seed=4)
+    w[3] = 0
+    for fmt in ("e4m3", "e5m2"):
+        codes, scales = quant.quantize_weight(w, fmt, gpu)
+        wc, ws = o.quantize_weight_per_channel(w, fmt)
+        assert np.array_equal(codes, wc)
+        assert np.array_equal(scales.view(np.uint32), ws.view(np.uint32))
+
+
+@pytest.mark.parametrize("fmt,tol", [("e4m3", 1e-2), ("e5m2", 1e-2), ("e2m1_b32", 5e-2)])
+def test_quant_linear_layer(gpu, fmt, tol):
+    rng = np.random.default_rng(3)
+    layer = nb.QuantLinear(256, 192, fmt=fmt, device=gpu)
+    layer.bias.data = rng.standard_normal((1, 192)).astype(np.float32) * 0.01
+    x = rng.standard_normal((160, 256)).astype(np.float32)
+    y = layer(x)
+    assert y.shape == (160, 192) and y.dtype == np.float32
+    xb = o.f32_to_bf16_bits(x).reshape(x.shape)
+    if fmt == "e2m1_b32":
+        wd = o.dequantize_fp4_weight(*o.quantize_fp4_b32(o.f32_to_bf16_bits(layer.weight.data).reshape(192, 256)))
+        ref = o.bf16_bits_to_f32(xb).astype(np.float64) @ wd.T.astype(np.float64) + layer.bias.data
+    else:
+        wq, sc = o.quantize_weight_per_channel(layer.weight.data, fmt)
+        ref = o.bf16_bits_to_f32(o.linear_fwd_qweight(xb, wq, sc, layer.bias.data.reshape(-1), fmt)[0])
+    assert o.max_abs_rel(y, ref) <= 2.0 ** -6
+    # against the unquantised fp32 layer the error is the quantisation error: inside the bound
+    full = o.linear_fwd_f32(x, layer.weight.data, layer.bias.data)
+    assert o.max_abs_rel(y, full) <= (tol if fmt != "e2m1_b32" else 0.25) * 4
+    dx = layer.backward(np.ones((160, 192), np.float32))
+    assert dx.shape == (160, 256) and layer.weight.grad.shape == (192, 256)
+
+
+@pytest.mark.parametrize("case", [0, 1, 3, 4, 5])
+def test_quant_conv2d_layer(gpu, case):
+    g = load("conv2d")
+    modes = ["zeros", "reflect", "replicate", "circular"]
+    kh, kw, sh, sw, ph, pw, mi = (int(v) for v in g[f"geom{case}"])
+    w, x = g[f"w{case}"], g[f"x{case}"]
+    cout = (w.shape[0] + 7) // 8 * 8                                # tensor-core path wants Cout % 8 == 0
+    rng = np.random.default_rng(case)
+    w8 = rng.standard_normal((cout, *w.shape[1:])).astype(np.float32)
+    w8[:w.shape[0]] = w
+    layer = nb.QuantConv2d(w.shape[1], cout, (kh, kw), stride=(sh, sw), padding=(ph, pw),
+                           padding_mode=modes[mi], fmt="e4m3", device=gpu)
+    layer.weight.data = w8
+    layer.bias.data = rng.standard_normal((cout, 1)).astype(np.float32)
+    layer.requantize()
+    y = layer(x)
+    # oracle: same codes, bf16-rounded patches, float64 contraction, bf16-rounded result
+    wq, sc = o.quantize_weight_per_channel(w8.reshape(cout, -1), "e4m3")
+    wd = (o.E4M3_TABLE[wq] * sc[:, None]).reshape(w8.shape)
+    xr = o.bf16_bits_to_f32(o.f32_to_bf16_bits(x)).reshape(x.shape)
+    ref = o.conv2d_fwd_f32(xr.astype(np.float64), wd.astype(np.float64), None, (sh, sw), (ph, pw), modes[mi])
+    col, oh, ow = o.im2col(xr, kh, kw, sh, sw, ph, pw, modes[mi])
+    ref = (wd.reshape(cout, -1).astype(np.float64) @ col.astype(np.float64)) + layer.bias.data
+    ref = ref.reshape(cout, x.shape[0], oh, ow).transpose(1, 0, 2, 3)
+    assert y.shape == ref.shape
+    assert o.max_abs_rel(y, ref) <= 2.0 ** -6
+    # the first Cout channels approximate the reference's fp32 convolution within the FP8 bound
+    assert o.max_abs_rel(y[:, :w.shape[0]] - layer.bias.data[:w.shape[0]].reshape(1, -1, 1, 1),
+                         g[f"y{case}"] - g[f"b{case}"].reshape(1, -1, 1, 1)) <= 6e-2
+
+
+def _check_step(step_out, g, sampled):
+    logits, loss, grads, params = step_out
+    assert close(logits, g["logits"], 1e-5)
+    assert abs(float(loss) - float(g["loss"])) <= 1e-4 * abs(float(g["loss"]))
+    for i in range(6):
+        if sampled:
+            idx = g[f"idx{i}"]
+            assert close(grads[i].ravel()[idx], g[f"grad{i}"], 1e-4), i
+            assert close(params[i].ravel()[idx], g[f"new{i}"], 1e-6), i
+        else:
+            assert grads[i].shape == g[f"grad{i}"].shape
+            assert close(grads[i], g[f"grad{i}"], 1e-4), i
+            assert close(params[i], g[f"new{i}"], 1e-6), i
+
+
+def test_mlp_train_step_device_resident_small(gpu):
+    x, y, params = workloads.mlp_inputs(16, (32, 16, 8, 10), seed=1)
+    st = MLPTrainStep(params, 16, 0.01, gpu)
+    st.step(x, y)
+    _check_step((st.logits(), st.loss(), st.grads(), st.params()), load("mlp_small"), sampled=False)
+
+
+def test_mlp_train_step_config_and_three_more_steps(gpu):
+    """batch 128, 784-256-128-10, SGD 0.01: the first step against the reference's vectors,
+    then three further steps against the oracle run in lock step."""
+    dims = (784, 256, 128, 10)
+    x, y, params = workloads.mlp_inputs(128, dims, seed=0)
+    st = MLPTrainStep(params, 128, 0.01, gpu)
+    st.step(x, y)
+    _check_step((st.logits(), st.loss(), st.grads(), st.params()), load("mlp_config"), sampled=True)
+    cur = o.mlp_train_step(params, x, y, 0.01)["params"]
+    for s in range(1, 4):
+        xs, ys, _ = workloads.mlp_inputs(128, dims, seed=10 + s)
+        r = o.mlp_train_step(cur, xs, ys, 0.01)
+        st.step(xs, ys)
+        assert close(st.logits(), r["logits"], 1e-4)
+        for a, b in zip(st.params(), r["params"]):
+            assert close(a, b, 1e-5)
+        cur = r["params"]
+
+
+def test_sequential_of_gpu_layers_runs_the_reference_loop(gpu):
+    """zero_grad -> forward -> loss -> backward -> step through the Layer API, as in the
+    reference's train loop, compared with its vectors."""
+    dims = (32, 16, 8, 10)
+    x, y, params = workloads.mlp_inputs(16, dims, seed=1)
+    layers = []
+    for i, (fi, fo) in enumerate(zip(dims[:-1], dims[1:])):
+        lin = nb.Linear(fi, fo, device=gpu)
+        lin.weight.data, lin.bias.data = params[2 * i].copy(), params[2 * i + 1].copy()
+        layers.append(lin)
+        if i < len(dims) - 2:
+            layers.append(nb.ReLU(device=gpu))
+    model = nb.Sequential(*layers)
+    opt = nb.SGD(model.parameters(), lr=0.01, device=gpu)
+    opt.zero_grad()
+    logits = model(x)
+    loss, grad = nb.CrossEntropyLoss(device=gpu)(logits, y)
+    model.backward(grad)
+    grads = [p.grad.copy() for p in model.parameters()]
+    opt.step()
+    _check_step((logits, loss, grads, [p.data for p in model.parameters()]), load("mlp_small"), sampled=False)
+    assert len(model.parameters()) == 6
