@@ -82,6 +82,14 @@ nvq_status nvq_event_record(int device, void* event, void* stream);
 nvq_status nvq_event_sync(int device, void* event);
 nvq_status nvq_event_elapsed_ms(void* start, void* stop, float* ms);
 
+/* CUDA graphs for launch-bound sequences (the fp32 train step is ~13 small kernels): every
+ * compute call of this library may be captured once it has run at least once on the device
+ * (first calls query attributes).  nvq_launch_count() counts launches at capture time only. */
+nvq_status nvq_graph_begin_capture(int device, void* stream);
+nvq_status nvq_graph_end_capture(int device, void* stream, void** graph_exec);
+nvq_status nvq_graph_launch(int device, void* graph_exec, void* stream);
+nvq_status nvq_graph_destroy(int device, void* graph_exec);
+
 /* Number of kernels this library has launched in the calling process so far. */
 uint64_t nvq_launch_count(void);
 

@@ -47,6 +47,10 @@ SIGNATURES = {
     "nvq_event_record": (i32, [i32, vp, vp]),
     "nvq_event_sync": (i32, [i32, vp]),
     "nvq_event_elapsed_ms": (i32, [vp, vp, C.POINTER(f32c)]),
+    "nvq_graph_begin_capture": (i32, [i32, vp]),
+    "nvq_graph_end_capture": (i32, [i32, vp, pvp]),
+    "nvq_graph_launch": (i32, [i32, vp, vp]),
+    "nvq_graph_destroy": (i32, [i32, vp]),
     "nvq_launch_count": (u64, []),
     "nvq_cast": (i32, [vp, i32, vp, i32, sz, i32, vp]),
     "nvq_cast_host": (i32, [vp, i32, vp, i32, sz, i32]),
@@ -87,6 +91,23 @@ class NvqError(RuntimeError):
 _lib = None
 
 
+def _point_at_bundled_nccl() -> None:
+    """Name the NCCL build that ships with PyTorch (when present) as the one the library
+    should dlopen, so that a process which also imports torch holds a single libnccl."""
+    if "NVQ_NCCL_LIB" in os.environ:
+        return
+    try:
+        import importlib.util
+        spec = importlib.util.find_spec("nvidia.nccl")
+        for root in (spec.submodule_search_locations if spec else []):
+            cand = os.path.join(root, "lib", "libnccl.so.2")
+            if os.path.exists(cand):
+                os.environ["NVQ_NCCL_LIB"] = cand
+                return
+    except Exception:
+        pass
+
+
 def lib() -> C.CDLL:
     """The loaded library.  Raises if it has not been built (no CPU fallback)."""
     global _lib
@@ -95,6 +116,7 @@ def lib() -> C.CDLL:
             raise ImportError(
                 f"{LIB_PATH} not found: build it with `python -m novann_b200.build` "
                 "(there is no CPU fallback)")
+        _point_at_bundled_nccl()
         L = C.CDLL(LIB_PATH)
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(L, name)

@@ -38,13 +38,6 @@ def _newest_header() -> float:
     return max(os.path.getmtime(h) for h in hs)
 
 
-def _nccl_flags() -> list[str]:
-    """Link flags for NCCL: the system library when its header is present."""
-    if os.path.exists("/usr/include/nccl.h"):
-        return ["-lnccl"]
-    return []
-
-
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
     nvcc = _nvcc()
@@ -73,7 +66,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         list(ex.map(run, jobs))
     if jobs or not os.path.exists(LIB):
         link = [nvcc, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a",
-                *_nccl_flags()]
+                "-ldl"]
         r = subprocess.run(link, capture_output=True, text=True)
         if r.returncode:
             sys.stderr.write(r.stdout + r.stderr)

@@ -175,4 +175,36 @@ nvq_status nvq_event_elapsed_ms(void* start, void* stop, float* ms) {
     return NVQ_OK;
 }
 
+// ---- CUDA graphs: capture a fixed launch sequence once, replay it with one launch -------
+nvq_status nvq_graph_begin_capture(int device, void* stream) {
+    NVQ_REQUIRE(stream, "graph capture needs an explicit (non-default) stream");
+    NVQ_CUDA(cudaSetDevice(device));
+    NVQ_CUDA(cudaStreamBeginCapture((cudaStream_t)stream, cudaStreamCaptureModeThreadLocal));
+    return NVQ_OK;
+}
+nvq_status nvq_graph_end_capture(int device, void* stream, void** graph_exec) {
+    NVQ_REQUIRE(stream && graph_exec, "null argument");
+    NVQ_CUDA(cudaSetDevice(device));
+    cudaGraph_t g = nullptr;
+    NVQ_CUDA(cudaStreamEndCapture((cudaStream_t)stream, &g));
+    cudaGraphExec_t e = nullptr;
+    cudaError_t err = cudaGraphInstantiate(&e, g, 0);
+    cudaGraphDestroy(g);
+    if (err != cudaSuccess) NVQ_FAIL(NVQ_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(err));
+    *graph_exec = (void*)e;
+    return NVQ_OK;
+}
+nvq_status nvq_graph_launch(int device, void* graph_exec, void* stream) {
+    NVQ_REQUIRE(graph_exec, "null graph");
+    NVQ_CUDA(cudaSetDevice(device));
+    NVQ_CUDA(cudaGraphLaunch((cudaGraphExec_t)graph_exec, (cudaStream_t)stream));
+    return NVQ_OK;
+}
+nvq_status nvq_graph_destroy(int device, void* graph_exec) {
+    if (!graph_exec) return NVQ_OK;
+    NVQ_CUDA(cudaSetDevice(device));
+    NVQ_CUDA(cudaGraphExecDestroy((cudaGraphExec_t)graph_exec));
+    return NVQ_OK;
+}
+
 }  // extern "C"

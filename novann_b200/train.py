@@ -96,6 +96,7 @@ class MLPTrainStep:
         self.d_g = [DeviceBuffer(f4 * d, device) for d in self.dims]     # gradient w.r.t. each activation
         self.d_yhat = DeviceBuffer(f4 * self.dims[-1], device)
         self.d_loss = DeviceBuffer(4, device)
+        self._graph = None
 
     def upload(self, x: np.ndarray, labels: np.ndarray) -> None:
         self.d_x.upload(np.ascontiguousarray(x, np.float32), stream=self.stream)
@@ -125,9 +126,35 @@ class MLPTrainStep:
         check(L.nvq_sgd_step_f32(self.d_params.at(0), self.d_grads.at(0), self.n_params,
                                  C.c_float(self.lr), C.c_float(scale), dev, st))
 
+    def capture(self) -> None:
+        """Record the step's launch sequence into a CUDA graph (after one eager step has run,
+        so that first-call set-up is done).  ``replay()`` then issues the whole step as one
+        graph launch; the buffers it reads and writes are the same ones ``upload`` fills."""
+        if self._graph is not None:
+            return
+        check(lib().nvq_graph_begin_capture(self.device, _sptr(self.stream)))
+        try:
+            self.launch()
+        finally:
+            h = C.c_void_p()
+            check(lib().nvq_graph_end_capture(self.device, _sptr(self.stream), C.byref(h)))
+        self._graph = h.value
+        self.launches_per_step = self.kernels_per_step()
+
+    def replay(self) -> None:
+        check(lib().nvq_graph_launch(self.device, C.c_void_p(self._graph), _sptr(self.stream)))
+
+    def kernels_per_step(self) -> int:
+        """Kernel launches of this library in one step: nl forward, 1 loss, per layer dW + db
+        (+ dX except for the first layer), 1 SGD."""
+        return self.nl + 1 + (3 * self.nl - 1) + 1
+
     def step(self, x: np.ndarray, labels: np.ndarray) -> None:
         self.upload(x, labels)
-        self.launch()
+        if self._graph is not None:
+            self.replay()
+        else:
+            self.launch()
         self.stream.sync()
 
     # ---- results

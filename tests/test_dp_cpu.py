@@ -1,0 +1,66 @@
+"""Host-side logic of the multi-GPU paths on CPU with world_size 2 (gloo): row sharding, the
+flat gradient bucket, and the data-parallel gradient rule (sum over ranks x 1/world equals
+the global-batch gradient because the reference divides by the LOCAL batch size).  The
+arithmetic here is the CPU oracle's; the collective is gloo standing in for NCCL."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, tmpdir):
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+    from novann_b200 import workloads
+    from novann_b200.launch import exchange_bytes
+    from novann_b200.train import flatten_params, shard_rows, unflatten_params
+    from oracle import oracle_np as o
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dims = (32, 16, 8, 10)
+    x, y, params = workloads.mlp_inputs(16, dims, seed=1)
+    lo, hi = shard_rows(16, rank, world)
+    r = o.mlp_train_step(params, x[lo:hi], y[lo:hi], 0.01)
+    bucket = torch.from_numpy(flatten_params(r["grads"]))
+    dist.all_reduce(bucket, op=dist.ReduceOp.SUM)
+    avg = unflatten_params((bucket.numpy() * np.float32(1.0 / world)).astype(np.float32), dims)
+    full = o.mlp_train_step(params, x, y, 0.01)
+    for a, b in zip(avg, full["grads"]):
+        assert a.shape == b.shape
+        assert np.max(np.abs(a - b)) <= 1e-6 * max(1e-30, np.max(np.abs(b))) + 1e-9
+    # per-tensor FP8 over row shards: max of the partial amax values == amax of the whole tensor
+    t = workloads.fp8_input(8, 64, seed=3)
+    part = torch.tensor([float(o.amax_f32(t[rank * 4:(rank + 1) * 4]))])
+    dist.all_reduce(part, op=dist.ReduceOp.MAX)
+    assert np.float32(part.item()) == o.amax_f32(t)
+    # the unique-id side channel
+    got = exchange_bytes(b"x" * 128 if rank == 0 else None, rank, os.path.join(tmpdir, "id"))
+    assert got == b"x" * 128
+    dist.destroy_process_group()
+
+
+def test_world_size_2_gloo(tmp_path):
+    import torch.multiprocessing as mp
+    port = 29500 + os.getpid() % 2000
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+
+
+def test_shard_rows_and_bucket_layout():
+    sys.path.insert(0, ROOT)
+    from novann_b200 import workloads
+    from novann_b200.train import flatten_params, shard_rows, unflatten_params
+    assert [shard_rows(16384, r, 8) for r in (0, 7)] == [(0, 2048), (14336, 16384)]
+    with pytest.raises(ValueError):
+        shard_rows(10, 0, 4)
+    _, _, params = workloads.mlp_inputs(4, (784, 256, 128, 10), seed=0)
+    flat = flatten_params(params)
+    assert flat.size == 235146                       # the bucket the all-reduce moves
+    back = unflatten_params(flat, (784, 256, 128, 10))
+    assert all(np.array_equal(a, b) for a, b in zip(back, params))
+    assert [b.shape for b in back] == [(256, 784), (1, 256), (128, 256), (1, 128), (10, 128), (1, 10)]

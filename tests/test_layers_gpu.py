@@ -144,9 +144,10 @@ def test_quant_linear_layer(gpu, fmt, tol):
         wq, sc = o.quantize_weight_per_channel(layer.weight.data, fmt)
         ref = o.bf16_bits_to_f32(o.linear_fwd_qweight(xb, wq, sc, layer.bias.data.reshape(-1), fmt)[0])
     assert o.max_abs_rel(y, ref) <= 2.0 ** -6
-    # against the unquantised fp32 layer the error is the quantisation error: inside the bound
+    # against the unquantised fp32 layer only the quantisation error of the weight remains
+    # (3, 2 and 1 mantissa bits): a sanity bound on the codes, not a kernel tolerance
     full = o.linear_fwd_f32(x, layer.weight.data, layer.bias.data)
-    assert o.max_abs_rel(y, full) <= (tol if fmt != "e2m1_b32" else 0.25) * 4
+    assert o.max_abs_rel(y, full) <= {"e4m3": 0.04, "e5m2": 0.08, "e2m1_b32": 0.5}[fmt]
     dx = layer.backward(np.ones((160, 192), np.float32))
     assert dx.shape == (160, 256) and layer.weight.grad.shape == (192, 256)
 
@@ -221,6 +222,23 @@ def test_mlp_train_step_config_and_three_more_steps(gpu):
         for a, b in zip(st.params(), r["params"]):
             assert close(a, b, 1e-5)
         cur = r["params"]
+
+
+def test_mlp_train_step_graph_replay_equals_eager(gpu):
+    dims = (784, 256, 128, 10)
+    x, y, params = workloads.mlp_inputs(128, dims, seed=0)
+    eager, graph = MLPTrainStep(params, 128, 0.01, gpu), MLPTrainStep(params, 128, 0.01, gpu)
+    graph.step(x, y)                   # first step eagerly (first-call set-up), then capture
+    eager.step(x, y)
+    graph.capture()
+    for s in range(3):
+        xs, ys, _ = workloads.mlp_inputs(128, dims, seed=30 + s)
+        eager.step(xs, ys)
+        graph.step(xs, ys)
+    for a, b in zip(eager.params(), graph.params()):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    assert eager.loss() == graph.loss()
+    assert graph.kernels_per_step() == 13
 
 
 def test_sequential_of_gpu_layers_runs_the_reference_loop(gpu):
