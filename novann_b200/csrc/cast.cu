@@ -62,9 +62,12 @@ struct NarrowOp {
 
 // ---- 16-bit -> fp32: 8 elements per packet, 128-bit load, 256-bit store ----------
 template <bool BF16>
+#ifndef NVQ_WIDEN_UNROLL
+#define NVQ_WIDEN_UNROLL 4
+#endif
 struct WidenOp {
     static constexpr int VEC = 8;
-    static constexpr int UNROLL = 4;
+    static constexpr int UNROLL = NVQ_WIDEN_UNROLL;
     using In = uint4;
     __device__ __forceinline__ void init() {}
     __device__ __forceinline__ In load(const void* src, size_t p) const {

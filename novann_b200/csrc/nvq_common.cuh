@@ -165,6 +165,14 @@ __device__ __forceinline__ uint32_t spec_mul_bits(uint32_t xu, uint32_t yu) {
 // ---- memory access helpers: streaming 128/256-bit global loads and stores -------
 struct __align__(32) u32x8 { uint32_t v[8]; };
 
+// instruction spellings, overridable for measurements
+#ifndef NVQ_ST256
+#define NVQ_ST256 "st.global.L1::no_allocate.v8.b32"
+#endif
+#ifndef NVQ_LD128
+#define NVQ_LD128 "ld.global.nc.L1::no_allocate.v4.b32"
+#endif
+
 __device__ __forceinline__ u32x8 ldg_stream_256(const void* p) {
     u32x8 r;
     asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
@@ -175,7 +183,7 @@ __device__ __forceinline__ u32x8 ldg_stream_256(const void* p) {
 }
 __device__ __forceinline__ uint4 ldg_stream_128(const void* p) {
     uint4 r;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
+    asm volatile(NVQ_LD128 " {%0,%1,%2,%3}, [%4];"
                  : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
                  : "l"(p));
     return r;
@@ -186,7 +194,7 @@ __device__ __forceinline__ uint2 ldg_stream_64(const void* p) {
     return r;
 }
 __device__ __forceinline__ void stg_stream_256(void* p, const u32x8& r) {
-    asm volatile("st.global.L1::no_allocate.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p),
+    asm volatile(NVQ_ST256 " [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p),
                  "r"(r.v[0]), "r"(r.v[1]), "r"(r.v[2]), "r"(r.v[3]), "r"(r.v[4]), "r"(r.v[5]),
                  "r"(r.v[6]), "r"(r.v[7])
                  : "memory");
