@@ -17,9 +17,12 @@ template <class Op>
 __global__ void __launch_bounds__(kEwThreads)
 ew_vector_kernel(Op op, const void* __restrict__ src, void* __restrict__ dst, size_t n_packets,
                  size_t n) {
-    const size_t stride = (size_t)gridDim.x * kEwThreads;
     const size_t tid = (size_t)blockIdx.x * kEwThreads + threadIdx.x;
     op.init();
+    // grid-stride over packets: at any moment the whole grid works on one contiguous window
+    // of the tensor (a per-block contiguous slice measured the same at 1 Gi elements and 5 %
+    // slower at 64 Mi)
+    const size_t stride = (size_t)gridDim.x * kEwThreads;
     for (size_t base = tid; base < n_packets; base += stride * Op::UNROLL) {
         typename Op::In in[Op::UNROLL];
 #pragma unroll
@@ -33,6 +36,7 @@ ew_vector_kernel(Op op, const void* __restrict__ src, void* __restrict__ dst, si
             if (p < n_packets) op.store(dst, p, in[u]);
         }
     }
+
     // ragged tail: fewer than VEC elements, one per thread
     size_t tail0 = n_packets * Op::VEC;
     if (tail0 + tid < n) op.scalar(src, dst, tail0 + tid);

@@ -13,7 +13,7 @@ namespace {
 
 // ---- generic strided fp32 GEMM ------------------------------------------------------
 //   C(i,j) = sum_l A(i,l) * B(l,j),  A(i,l) = a[i*a_si + l*a_sl],  B(l,j) = b[l*b_sl + j*b_sj]
-// One 32 x 32 output tile per 256-thread block (2 x 2 per thread), 32-deep k chunks staged
+// One 32 x 32 output tile per 256-thread block (2 x 2 per thread), 64-deep k chunks staged
 // in shared memory.  Loads walk the unit-stride index fastest, whichever it is.
 constexpr int TS = 32;
 
@@ -33,40 +33,68 @@ struct GemmArgs {
     int out_mode, inner;
 };
 
+constexpr int TK = 64;   // k depth of one staged chunk
+
+// element e (0..2047) of a TS x TK tile -> (row-in-tile, k-in-chunk); the index that has unit
+// stride in memory runs fastest across threads so global loads coalesce
+__device__ __forceinline__ void tile_coord(int e, bool k_contiguous, int& r, int& l) {
+    if (k_contiguous) { l = e & (TK - 1); r = e >> 6; }
+    else              { r = e & (TS - 1); l = e >> 5; }
+}
+
 __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
-    __shared__ float As[TS][TS + 1];   // [l][i]
-    __shared__ float Bs[TS][TS + 1];   // [l][j]
+    // double-buffered tiles: chunk c+1 is fetched into registers while chunk c is multiplied,
+    // so the global-memory latency of the (few, small) blocks overlaps the FMA loop
+    __shared__ float As[2][TK][TS + 1];   // [buf][l][i]
+    __shared__ float Bs[2][TK][TS + 1];   // [buf][l][j]
     const int i0 = blockIdx.y * TS, j0 = blockIdx.x * TS;
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;   // 16 x 16 threads, 2 x 2 outputs each
+    const bool a_kc = g.a_sl == 1, b_kc = g.b_sl == 1;
     float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-    for (int l0 = 0; l0 < g.L; l0 += TS) {
-        // each thread loads 4 elements of each tile
+    float ra[8], rb[8];
+    auto fetch = [&](int l0) {
 #pragma unroll
-        for (int r = 0; r < 4; r++) {
-            int e = threadIdx.x + 256 * r;          // 0..1023
-            int fast = e & 31, slow = e >> 5;
-            {   // A tile: fastest index follows the unit stride
-                int ii = g.a_sl == 1 ? slow : fast, ll = g.a_sl == 1 ? fast : slow;
-                int i = i0 + ii, l = l0 + ll;
-                As[ll][ii] = (i < g.I && l < g.L) ? g.a[i * g.a_si + l * g.a_sl] : 0.f;
-            }
-            {
-                int jj = g.b_sl == 1 ? slow : fast, ll = g.b_sl == 1 ? fast : slow;
-                int j = j0 + jj, l = l0 + ll;
-                Bs[ll][jj] = (j < g.J && l < g.L) ? g.b[l * g.b_sl + j * g.b_sj] : 0.f;
-            }
+        for (int r = 0; r < 8; r++) {
+            int e = threadIdx.x + 256 * r, ii, ll;
+            tile_coord(e, a_kc, ii, ll);
+            int i = i0 + ii, l = l0 + ll;
+            ra[r] = (i < g.I && l < g.L) ? g.a[i * g.a_si + l * g.a_sl] : 0.f;
+            int jj;
+            tile_coord(e, b_kc, jj, ll);
+            int j = j0 + jj;
+            l = l0 + ll;
+            rb[r] = (j < g.J && l < g.L) ? g.b[l * g.b_sl + j * g.b_sj] : 0.f;
         }
-        __syncthreads();
+    };
+    auto stash = [&](int buf) {
 #pragma unroll
-        for (int l = 0; l < TS; l++) {
-            float a0 = As[l][ty], a1 = As[l][ty + 16];
-            float b0 = Bs[l][tx], b1 = Bs[l][tx + 16];
+        for (int r = 0; r < 8; r++) {
+            int e = threadIdx.x + 256 * r, ii, ll;
+            tile_coord(e, a_kc, ii, ll);
+            As[buf][ll][ii] = ra[r];
+            tile_coord(e, b_kc, ii, ll);
+            Bs[buf][ll][ii] = rb[r];
+        }
+    };
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    int buf = 0;
+    for (int l0 = 0; l0 < g.L; l0 += TK) {
+        const bool more = l0 + TK < g.L;
+        if (more) fetch(l0 + TK);
+#pragma unroll 16
+        for (int l = 0; l < TK; l++) {
+            float a0 = As[buf][l][ty], a1 = As[buf][l][ty + 16];
+            float b0 = Bs[buf][l][tx], b1 = Bs[buf][l][tx + 16];
             acc[0][0] = fmaf(a0, b0, acc[0][0]);
             acc[0][1] = fmaf(a0, b1, acc[0][1]);
             acc[1][0] = fmaf(a1, b0, acc[1][0]);
             acc[1][1] = fmaf(a1, b1, acc[1][1]);
         }
+        if (more) stash(buf ^ 1);
         __syncthreads();
+        buf ^= 1;
     }
 #pragma unroll
     for (int u = 0; u < 2; u++) {
@@ -97,13 +125,20 @@ nvq_status launch_gemm(const GemmArgs& g, cudaStream_t st) {
     return NVQ_OK;
 }
 
-// column sums of an M x N matrix: out[n] = sum_m g[m, n], rows added in order (fp32)
+// column sums of an M x N matrix: out[n] = sum_m g[m, n].  Eight interleaved partial sums keep
+// eight loads in flight; they are combined pairwise at the end.
 __global__ void colsum_kernel(const float* __restrict__ g, float* __restrict__ out, int M, int N) {
     int n = blockIdx.x * blockDim.x + threadIdx.x;
     if (n >= N) return;
-    float s = 0.f;
-    for (int m = 0; m < M; m++) s = __fadd_rn(s, g[(size_t)m * N + n]);
-    out[n] = s;
+    float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    int m = 0;
+    for (; m + 8 <= M; m += 8) {
+#pragma unroll
+        for (int u = 0; u < 8; u++) s[u] = __fadd_rn(s[u], g[(size_t)(m + u) * N + n]);
+    }
+    for (; m < M; m++) s[0] = __fadd_rn(s[0], g[(size_t)m * N + n]);
+    out[n] = __fadd_rn(__fadd_rn(__fadd_rn(s[0], s[1]), __fadd_rn(s[2], s[3])),
+                       __fadd_rn(__fadd_rn(s[4], s[5]), __fadd_rn(s[6], s[7])));
 }
 
 __global__ void relu_kernel(float* __restrict__ out, float* __restrict__ mask,
@@ -141,14 +176,20 @@ __global__ void softmax_ce_kernel(float* __restrict__ grad, float* __restrict__ 
     }
     __syncthreads();
     if (!loss) return;
-    // second softmax along the batch axis, per class column; only the labelled entries count
+    // second softmax along the batch axis: one warp per class column, lanes stride over the
+    // rows; only the labelled entries enter the loss
     double part = 0.0;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        float mx = yhat_scratch[c];
-        for (int m = 1; m < M; m++) mx = fmaxf(mx, yhat_scratch[(size_t)m * C + c]);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int c = warp; c < C; c += nwarps) {
+        float mx = -INFINITY;
+        for (int m = lane; m < M; m += 32) mx = fmaxf(mx, yhat_scratch[(size_t)m * C + c]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
         float s = 0.f;
-        for (int m = 0; m < M; m++) s = __fadd_rn(s, expf(__fsub_rn(yhat_scratch[(size_t)m * C + c], mx)));
-        for (int m = 0; m < M; m++) {
+        for (int m = lane; m < M; m += 32) s += expf(__fsub_rn(yhat_scratch[(size_t)m * C + c], mx));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+        for (int m = lane; m < M; m += 32) {
             if (labels[m] == c) {
                 float p2 = __fdiv_rn(expf(__fsub_rn(yhat_scratch[(size_t)m * C + c], mx)), s);
                 part += (double)logf(__fadd_rn(p2, 1e-8f));

@@ -59,21 +59,32 @@ __device__ __forceinline__ uint32_t quant_word_spec(uint32_t w0, uint32_t w1, ui
 }
 
 __device__ __forceinline__ void quant_block(const Block32& in, uint4& codes, float& scale) {
-    float amax = 0.f, probe = 0.f;
+    // block maximum on the bit patterns: |x| of a bf16 orders like its low 15 bits, two values
+    // per word; inf / NaN patterns (>= 0x7f80) come out on top and send the block down the
+    // integer path, which recomputes the maximum with NaNs ignored
+    uint32_t m2 = 0u;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        float a0 = __uint_as_float(in.a.v[i] << 16), a1 = __uint_as_float(in.a.v[i] & 0xFFFF0000u);
-        float b0 = __uint_as_float(in.b.v[i] << 16), b1 = __uint_as_float(in.b.v[i] & 0xFFFF0000u);
-        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(a0), fabsf(a1)), fmaxf(fabsf(b0), fabsf(b1))));
-        probe = fmaf(a0, 0.f, probe);
-        probe = fmaf(a1, 0.f, probe);
-        probe = fmaf(b0, 0.f, probe);
-        probe = fmaf(b1, 0.f, probe);
+        m2 = __vmaxu2(m2, in.a.v[i] & 0x7FFF7FFFu);
+        m2 = __vmaxu2(m2, in.b.v[i] & 0x7FFF7FFFu);
+    }
+    const uint32_t m16 = max(m2 & 0xFFFFu, m2 >> 16);
+    bool slow = m16 >= 0x7F80u;
+    float amax = __uint_as_float(m16 << 16);
+    if (slow) {
+        amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(in.a.v[i] << 16)),
+                                     fabsf(__uint_as_float(in.a.v[i] & 0xFFFF0000u))));
+            amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(in.b.v[i] << 16)),
+                                     fabsf(__uint_as_float(in.b.v[i] & 0xFFFF0000u))));
+        }
     }
     scale = __fdiv_rn(amax, 6.0f);
     float inv = amax > 0.f ? __fdiv_rn(6.0f, amax) : 0.f;
-    // a block with inf / NaN, or whose reciprocal scale overflowed, takes the integer path
-    bool slow = (probe != probe) || (__float_as_uint(inv) >= 0x7F800000u);
+    // a reciprocal that overflowed (subnormal block maximum) also takes the integer path
+    slow = slow || (__float_as_uint(inv) >= 0x7F800000u);
     if (!slow) {
         codes.x = quant_word_fast(in.a.v[0], in.a.v[1], in.a.v[2], in.a.v[3], inv);
         codes.y = quant_word_fast(in.a.v[4], in.a.v[5], in.a.v[6], in.a.v[7], inv);
