@@ -201,6 +201,10 @@ nvq_status nvq_linear_fwd_static(uint16_t* d_y_bf16, const uint16_t* d_x_bf16, c
 /* Tensor-core kernels bound every device-side wait; a wait that gives up records a
  * non-zero code here (read and cleared by this call) instead of hanging. */
 nvq_status nvq_device_error_flag(int device, int* flag);
+/* Launches a one-warp kernel that waits (limit 1 ms) on a barrier nothing arrives at: the wait
+ * gives up, the kernel returns, and nvq_device_error_flag then reports code 99.  A check of the
+ * give-up path that faults and hangs nothing. */
+nvq_status nvq_selftest_bounded_wait(int device, void* stream);
 
 /* ---------------------------------------------------------------- fp32 train step
  * The pieces of the reference's training step (novann/utils/train/train.py:60-75) in fp32

@@ -64,6 +64,7 @@ SIGNATURES = {
     "nvq_linear_workspace_bytes": (i32, [sz, sz, i32, C.POINTER(sz)]),
     "nvq_linear_fwd": (i32, [vp, vp, vp, i32, vp, vp, sz, sz, sz, vp, sz, i32, vp]),
     "nvq_device_error_flag": (i32, [i32, C.POINTER(i32)]),
+    "nvq_selftest_bounded_wait": (i32, [i32, vp]),
     "nvq_linear_fwd_f32": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp, i32, vp]),
     "nvq_linear_bwd_f32": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "nvq_relu_fwd_f32": (i32, [vp, vp, vp, sz, i32, vp]),

@@ -17,6 +17,7 @@
 // No TMA multicast and no peer memory anywhere: each CTA fetches its own tiles.
 #include <stdlib.h>
 
+#include "elementwise.cuh"
 #include "gemm_common.cuh"
 
 namespace {
@@ -191,38 +192,55 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 }
 
 // ---- exact expansion of weight codes to bf16 (workspace fill) -------------------------
-// 16 codes -> 16 bf16 per thread step; E4M3 / E5M2 values have at most 3 mantissa bits, so the
-// conversion through fp16 -> fp32 -> bf16 is exact.
+// 16 codes -> 16 bf16 per packet through the elementwise driver (several packets in flight per
+// thread; the 32 MB it writes for a 4096 x 4096 weight stay in L2 for the GEMM that follows).
+// E4M3 / E5M2 values have at most 3 mantissa bits, so fp16 -> fp32 -> bf16 is exact.
 template <int FMT>
-__global__ void __launch_bounds__(256)
-expand_fp8_to_bf16_kernel(const uint8_t* __restrict__ src, uint16_t* __restrict__ dst, size_t n) {
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    const size_t packets = n / 16;
-    for (size_t pk = (size_t)blockIdx.x * blockDim.x + threadIdx.x; pk < packets; pk += stride) {
-        uint4 in = ldg_stream_128(src + pk * 16);
-        const uint32_t w[4] = {in.x, in.y, in.z, in.w};
-        u32x8 o;
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            uint32_t h01, h23;
-            if (FMT == NVQ_E4M3) {
-                asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h01) : "h"((uint16_t)(w[i] & 0xFFFFu)));
-                asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h23) : "h"((uint16_t)(w[i] >> 16)));
-            } else {
-                h01 = __byte_perm(w[i], 0u, 0x1404);
-                h23 = __byte_perm(w[i], 0u, 0x3424);
-            }
-            float f0, f1, f2, f3;
-            asm("cvt.f32.f16 %0, %1;" : "=f"(f0) : "h"((uint16_t)(h01 & 0xFFFFu)));
-            asm("cvt.f32.f16 %0, %1;" : "=f"(f1) : "h"((uint16_t)(h01 >> 16)));
-            asm("cvt.f32.f16 %0, %1;" : "=f"(f2) : "h"((uint16_t)(h23 & 0xFFFFu)));
-            asm("cvt.f32.f16 %0, %1;" : "=f"(f3) : "h"((uint16_t)(h23 >> 16)));
-            o.v[2 * i] = pack_bf16(f0, f1);
-            o.v[2 * i + 1] = pack_bf16(f2, f3);
-        }
-        stg_stream_256(dst + pk * 16, o);
+struct ExpandOp {
+    static constexpr int VEC = 16;
+    static constexpr int UNROLL = 4;
+    using In = uint4;
+    // lets the GEMM that follows in the stream start its set-up (barriers, TMEM, descriptors)
+    // while this kernel is still running; the GEMM waits for this grid before its first load
+    __device__ __forceinline__ void init() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+    __device__ __forceinline__ In load(const void* src, size_t p) const {
+        return ldg_stream_128((const char*)src + p * 16);
     }
-}
+    __device__ __forceinline__ void four(uint32_t w, uint32_t& o0, uint32_t& o1) const {
+        uint32_t h01, h23;
+        if (FMT == NVQ_E4M3) {
+            asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h01) : "h"((uint16_t)(w & 0xFFFFu)));
+            asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h23) : "h"((uint16_t)(w >> 16)));
+        } else {
+            h01 = __byte_perm(w, 0u, 0x1404);
+            h23 = __byte_perm(w, 0u, 0x3424);
+        }
+        float f0, f1, f2, f3;
+        asm("cvt.f32.f16 %0, %1;" : "=f"(f0) : "h"((uint16_t)(h01 & 0xFFFFu)));
+        asm("cvt.f32.f16 %0, %1;" : "=f"(f1) : "h"((uint16_t)(h01 >> 16)));
+        asm("cvt.f32.f16 %0, %1;" : "=f"(f2) : "h"((uint16_t)(h23 & 0xFFFFu)));
+        asm("cvt.f32.f16 %0, %1;" : "=f"(f3) : "h"((uint16_t)(h23 >> 16)));
+        o0 = pack_bf16(f0, f1);
+        o1 = pack_bf16(f2, f3);
+    }
+    __device__ __forceinline__ void store(void* dst, size_t p, const In& in) const {
+        u32x8 o;
+        four(in.x, o.v[0], o.v[1]);
+        four(in.y, o.v[2], o.v[3]);
+        four(in.z, o.v[4], o.v[5]);
+        four(in.w, o.v[6], o.v[7]);
+        // plain (L2-allocating) store: the GEMM reads this back at once
+        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"((char*)dst + p * 32),
+                     "r"(o.v[0]), "r"(o.v[1]), "r"(o.v[2]), "r"(o.v[3]), "r"(o.v[4]), "r"(o.v[5]),
+                     "r"(o.v[6]), "r"(o.v[7])
+                     : "memory");
+    }
+    __device__ __forceinline__ void scalar(const void* src, void* dst, size_t i) const {
+        uint32_t c = ((const uint8_t*)src)[i];
+        uint32_t t = FMT == NVQ_E4M3 ? spec_fp8_to_f32<NVQ_E4M3>(c) : spec_fp8_to_f32<NVQ_E5M2>(c);
+        ((uint16_t*)dst)[i] = (uint16_t)(t >> 16);   // exact: the low 16 bits are zero
+    }
+};
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -347,6 +365,35 @@ extern "C" nvq_status nvq_linear_workspace_bytes(size_t N, size_t K, nvq_dtype w
     return NVQ_OK;
 }
 
+// A wait that nothing will ever satisfy, with a 1 ms limit: exercises the give-up path of the
+// bounded waits (record a code, leave, report) without faulting or hanging anything.
+namespace {
+__global__ void wait_selftest_kernel(int* status) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        tc::mbar_init(tc::smem_u32(&bar), 1);
+        abort_flag = 0;
+        tc::mbar_fence_init();
+    }
+    __syncthreads();
+    bool ok = tc::mbar_wait_limit(tc::smem_u32(&bar), 0, &abort_flag, 99, 1000000ull);
+    __syncthreads();
+    if (threadIdx.x == 0 && !ok && status) atomicCAS(status, 0, abort_flag);
+}
+}  // namespace
+
+extern "C" nvq_status nvq_selftest_bounded_wait(int device, void* stream) {
+    nvq_status s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    int* status = nullptr;
+    s = nvq_status_word(device, &status);
+    if (s != NVQ_OK) return s;
+    wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status);
+    NVQ_LAUNCHED();
+    return NVQ_OK;
+}
+
 extern "C" nvq_status nvq_device_error_flag(int device, int* flag) {
     NVQ_REQUIRE(flag && device >= 0 && device < 64, "bad argument");
     *flag = 0;
@@ -398,14 +445,9 @@ extern "C" nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf1
     } else {
         NVQ_REQUIRE((N * K) % 16 == 0 && nvq_aligned(d_wq, 16),
                     "nvq_linear_fwd: weight codes must be 16-byte aligned, N*K a multiple of 16");
-        size_t packets = N * K / 16;
-        size_t want = (packets + 255) / 256, cap = (size_t)nvq_sm_count(device) * 8;
-        unsigned grid = (unsigned)(want < cap ? want : cap);
-        if (w_fmt == NVQ_E4M3)
-            expand_fp8_to_bf16_kernel<NVQ_E4M3><<<grid, 256, 0, st>>>(d_wq, wd, N * K);
-        else
-            expand_fp8_to_bf16_kernel<NVQ_E5M2><<<grid, 256, 0, st>>>(d_wq, wd, N * K);
-        NVQ_LAUNCHED();
+        s = w_fmt == NVQ_E4M3 ? ew_launch(ExpandOp<NVQ_E4M3>{}, d_wq, wd, N * K, device, st, 16, 32)
+                              : ew_launch(ExpandOp<NVQ_E5M2>{}, d_wq, wd, N * K, device, st, 16, 32);
+        if (s != NVQ_OK) return s;
     }
     return nvq_linear_bf16_launch(d_y_bf16, d_x_bf16, wd, chan_scales, d_bias, M, N, K, device, st);
 }

@@ -130,6 +130,9 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     tc::cluster_sync_all();          // the partner's barriers exist before anything targets them
     tc::tc_fence_after();
     const uint32_t tmem_base = sh->tmem_base;
+    // Programmatic dependent launch: everything above ran while the kernel that fills the
+    // weight workspace was still draining; from here on its output is needed.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer (both CTAs)
@@ -342,7 +345,17 @@ static nvq_status launch_pair(uint16_t* d_y, const uint16_t* d_x, const void* d_
     int split = (tiles > pairs && rem > 0 && 2 * rem <= pairs) ? rem : 0;
     p.num_big = tiles - split;
     p.num_items = p.num_big + 2 * split;
-    linear_tc_pair_kernel<FUSED><<<2 * pairs, Cfg<FUSED>::THREADS, Cfg<FUSED>::SMEM_BYTES, st>>>(map_a, map_b, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(Cfg<FUSED>::THREADS);
+    cfg.dynamicSmemBytes = Cfg<FUSED>::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // may start under the tail
+    attr[0].val.programmaticStreamSerializationAllowed = 1;            // of the previous kernel
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    NVQ_CUDA(cudaLaunchKernelEx(&cfg, linear_tc_pair_kernel<FUSED>, map_a, map_b, p));
     NVQ_LAUNCHED();
     return NVQ_OK;
 }

@@ -51,19 +51,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait.  `abort_flag` (shared memory) is raised by whichever role gives up first
 // so that every other role leaves its own waits promptly; returns false on give-up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int code) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity,
+                                                volatile int* abort_flag, int code,
+                                                unsigned long long limit_ns) {
     for (int i = 0; i < 128; i++)
         if (mbar_try_wait(bar, parity)) return true;
     unsigned long long t0 = global_ns();
     while (!mbar_try_wait(bar, parity)) {
         if (*abort_flag) return false;
-        if (global_ns() - t0 > kWaitLimitNs) {
+        if (global_ns() - t0 > limit_ns) {
             *abort_flag = code;
             return false;
         }
     }
     return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int code) {
+    return mbar_wait_limit(bar, parity, abort_flag, code, kWaitLimitNs);
 }
 
 // ---- TMA: 2-D tiled load into this CTA's shared memory, completion on an mbarrier --

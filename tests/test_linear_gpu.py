@@ -119,3 +119,19 @@ def test_linear_argument_validation(gpu):
     wq, sc = o.quantize_weight_per_channel(w, "e4m3")
     with pytest.raises(_lib.NvqError):
         F.linear_q_host(xb, wq, sc, b, "e4m3", gpu)
+
+
+def test_bounded_wait_gives_up_and_reports(gpu):
+    """A device-side wait that can never be satisfied returns after its limit, the host reads
+    the give-up code, and the context stays usable (a Linear right after is still correct)."""
+    from novann_b200 import _lib
+    from novann_b200.device import device_sync
+    F.check_device_errors(gpu)                       # clear
+    _lib.check(_lib.lib().nvq_selftest_bounded_wait(gpu, None))
+    device_sync(gpu)
+    with pytest.raises(_lib.NvqError) as e:
+        F.check_device_errors(gpu)
+    assert e.value.status == _lib.ERR_TIMEOUT and "99" in str(e.value)
+    F.check_device_errors(gpu)                       # flag was cleared by the read
+    err, _, _ = _run_fp8(gpu, 256, 256, 256)
+    assert err <= 2.0 ** -7
