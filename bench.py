@@ -382,7 +382,11 @@ def run_ours(args):
                                 "2^26-element seeded tile repeated 16x"},
             "roofline": {"bound": "hbm", "kernel": f"cast {dom}", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_source": which,
-                         "traffic": None, "per_kernel_ms": per_kernel,
+                         # dram read + write of the dominant kernel per launch: the ncu capture at
+                         # 64 Mi elements (profiles/cast_kernels_64Mi_elements.md) shows reads equal
+                         # to the algorithmic reads and no re-reads; scaled by elements to this size
+                         "traffic": 6.0 * n, "traffic_source": "ncu at 64 Mi elements, scaled x16",
+                         "per_kernel_ms": per_kernel,
                          "frac_of_nominal_8tbs": achieved / 8000.0},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 12 * n,

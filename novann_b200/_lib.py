@@ -73,6 +73,7 @@ SIGNATURES = {
     "nvq_conv2d_out_size": (i32, [i32] * 8 + [C.POINTER(i32), C.POINTER(i32)]),
     "nvq_im2col_f32": (i32, [vp, vp] + [i32] * 10 + [i32, i32, vp]),
     "nvq_conv2d_fwd_f32": (i32, [vp, vp, vp, vp, vp] + [i32] * 11 + [i32, i32, vp]),
+    "nvq_conv2d_bwd_f32": (i32, [vp] * 8 + [i32] * 11 + [i32, vp]),
     "nvq_conv2d_q_sizes": (i32, [i32] * 11 + [C.POINTER(sz), C.POINTER(sz)]),
     "nvq_conv2d_fwd_q": (i32, [vp, vp, vp, i32, vp, vp, vp, vp, vp, sz] + [i32] * 11 + [i32, i32, vp]),
     "nvq_comm_unique_id": (i32, [vp]),

@@ -280,6 +280,56 @@ __global__ void rows_bf16_to_nchw_kernel(float* __restrict__ out, const uint16_t
     }
 }
 
+// grad (N, Cout, S) -> g_r (Cout, N*S): the reference's grad.transpose(1,0,2,3).reshape(Cout,-1)
+__global__ void nchw_to_crows_kernel(float* __restrict__ out, const float* __restrict__ g, int N,
+                                     int Cout, int S) {
+    size_t total = (size_t)N * Cout * S, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+        int s = e % S, n = (e / S) % N, c = e / ((size_t)S * N);
+        out[e] = g[((size_t)n * Cout + c) * S + s];
+    }
+}
+
+// row sums: out[r] = sum_l a[r, l]; one warp per row
+__global__ void rowsum_kernel(const float* __restrict__ a, float* __restrict__ out, int R, size_t L) {
+    int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r >= R) return;
+    float s = 0.f;
+    for (size_t l = lane; l < L; l += 32) s += a[(size_t)r * L + l];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+    if (lane == 0) out[r] = s;
+}
+
+// col2im as a gather (Conv2d._col2im, novann/layers/convolutional/conv2d.py:117-148): every input
+// element sums the dcol entries of the windows that cover it, in (kh, kw) order, which is the
+// order np.add.at applies them in.  As in the reference, gradient that falls on padding is dropped
+// whatever the padding mode.
+__global__ void col2im_kernel(float* __restrict__ dx, const float* __restrict__ dcol, ConvGeom g) {
+    const size_t L = (size_t)g.N * g.OH * g.OW, total = (size_t)g.N * g.C * g.H * g.W;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+        int w = e % g.W, h = (e / g.W) % g.H, c = (e / ((size_t)g.W * g.H)) % g.C;
+        int n = e / ((size_t)g.W * g.H * g.C);
+        float s = 0.f;
+        for (int kh = 0; kh < g.KH; kh++) {
+            int t = h + g.ph - kh;
+            if (t < 0 || t % g.sh) continue;
+            int oh = t / g.sh;
+            if (oh >= g.OH) continue;
+            for (int kw = 0; kw < g.KW; kw++) {
+                int u = w + g.pw - kw;
+                if (u < 0 || u % g.sw) continue;
+                int ow = u / g.sw;
+                if (ow >= g.OW) continue;
+                size_t row = ((size_t)c * g.KH + kh) * g.KW + kw;
+                s = __fadd_rn(s, dcol[row * L + ((size_t)n * g.OH + oh) * g.OW + ow]);
+            }
+        }
+        dx[e] = s;
+    }
+}
+
 nvq_status geom(ConvGeom& g, int N, int C, int H, int W, int KH, int KW, int sh, int sw, int ph,
                 int pw, nvq_pad_mode mode) {
     NVQ_REQUIRE(N > 0 && C > 0 && H > 0 && W > 0 && KH > 0 && KW > 0 && sh > 0 && sw > 0 && ph >= 0 && pw >= 0,
@@ -457,5 +507,49 @@ extern "C" nvq_status nvq_conv2d_fwd_q(float* d_out, const float* d_x, const uin
     if (s != NVQ_OK) return s;
     rows_bf16_to_nchw_kernel<<<ew_grid(L * Cout, device), 256, 0, st>>>(d_out, d_y_bf16, N, Cout, g.OH * g.OW);
     NVQ_LAUNCHED();
+    return NVQ_OK;
+}
+
+extern "C" nvq_status nvq_conv2d_bwd_f32(float* d_dw, float* d_db, float* d_dx, const float* d_grad,
+                                         const float* d_col, const float* d_w, float* d_gr,
+                                         float* d_dcol, int N, int C, int H, int W, int Cout, int KH,
+                                         int KW, int sh, int sw, int ph, int pw, int device,
+                                         void* stream) {
+    ConvGeom gm;
+    nvq_status s = geom(gm, N, C, H, W, KH, KW, sh, sw, ph, pw, NVQ_PAD_ZEROS);
+    if (s != NVQ_OK) return s;
+    NVQ_REQUIRE(d_grad && d_gr && Cout > 0, "nvq_conv2d_bwd_f32: bad argument");
+    s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int S = gm.OH * gm.OW, CKK = C * KH * KW;
+    const size_t L = (size_t)N * S;
+    NVQ_REQUIRE(L < (1u << 31), "nvq_conv2d_bwd_f32: too many output positions");
+    nchw_to_crows_kernel<<<ew_grid(L * Cout, device), 256, 0, st>>>(d_gr, d_grad, N, Cout, S);
+    NVQ_LAUNCHED();
+    if (d_dw) {   // dW = g_r @ col^T
+        NVQ_REQUIRE(d_col, "nvq_conv2d_bwd_f32: dW needs col");
+        GemmArgs g{};
+        g.a = d_gr; g.a_si = (long long)L; g.a_sl = 1;
+        g.b = d_col; g.b_sl = 1; g.b_sj = (long long)L;
+        g.c = d_dw; g.I = Cout; g.J = CKK; g.L = (int)L;
+        s = launch_gemm(g, st);
+        if (s != NVQ_OK) return s;
+    }
+    if (d_db) {
+        rowsum_kernel<<<(Cout + 7) / 8, 256, 0, st>>>(d_gr, d_db, Cout, L);
+        NVQ_LAUNCHED();
+    }
+    if (d_dx) {   // dcol = w_col^T @ g_r, then gather back onto the input
+        NVQ_REQUIRE(d_w && d_dcol, "nvq_conv2d_bwd_f32: dX needs w and the dcol scratch");
+        GemmArgs g{};
+        g.a = d_w; g.a_si = 1; g.a_sl = CKK;
+        g.b = d_gr; g.b_sl = (long long)L; g.b_sj = 1;
+        g.c = d_dcol; g.I = CKK; g.J = (int)L; g.L = Cout;
+        s = launch_gemm(g, st);
+        if (s != NVQ_OK) return s;
+        col2im_kernel<<<ew_grid((size_t)N * C * H * W, device), 256, 0, st>>>(d_dx, d_dcol, gm);
+        NVQ_LAUNCHED();
+    }
     return NVQ_OK;
 }

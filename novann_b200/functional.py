@@ -181,3 +181,35 @@ def conv2d_q_host(x, wq, w_scales, b, kernel, stride=(1, 1), padding=(0, 0),
     device_sync(device)
     check_device_errors(device)
     return out.to_numpy(np.float32, (n, cout, oh, ow))
+
+
+def conv2d_bwd_f32_host(grad, col, w, x_shape, stride, padding, with_bias: bool = True, device: int = 0):
+    """``Conv2d.backward`` (novann/layers/convolutional/conv2d.py:179-207): returns
+    (dW (Cout,C,KH,KW), db (Cout,1) or None, dX (N,C,H,W))."""
+    grad, col, w = _f32(grad), _f32(col), _f32(w)
+    n, c, h, wd = x_shape
+    cout, _, kh, kw = w.shape
+    oh, ow = grad.shape[2], grad.shape[3]
+    L, ckk = n * oh * ow, c * kh * kw
+    dg, dc, dw_ = (DeviceBuffer.from_numpy(a, device) for a in (grad, col, w))
+    o_dw, o_db, o_dx = DeviceBuffer(cout * ckk * 4, device), DeviceBuffer(cout * 4, device), DeviceBuffer(n * c * h * wd * 4, device)
+    gr, dcol = DeviceBuffer(cout * L * 4, device), DeviceBuffer(ckk * L * 4, device)
+    check(lib().nvq_conv2d_bwd_f32(o_dw.at(0), o_db.at(0) if with_bias else None, o_dx.at(0), dg.at(0),
+                                   dc.at(0), dw_.at(0), gr.at(0), dcol.at(0), n, c, h, wd, cout, kh, kw,
+                                   stride[0], stride[1], padding[0], padding[1], device, None))
+    return (o_dw.to_numpy(np.float32, w.shape),
+            o_db.to_numpy(np.float32, (cout, 1)) if with_bias else None,
+            o_dx.to_numpy(np.float32, (n, c, h, wd)))
+
+
+def im2col_f32_host(x, kernel, stride, padding, padding_mode: str = "zeros", device: int = 0):
+    """``_im2col`` (novann/functional.py:346-368): (C*KH*KW, N*OH*OW) fp32."""
+    x = _f32(x)
+    n, c, h, wd = x.shape
+    kh, kw = kernel
+    oh, ow = conv2d_out_size(h, wd, kh, kw, stride[0], stride[1], padding[0], padding[1])
+    dx = DeviceBuffer.from_numpy(x, device)
+    col = DeviceBuffer(max(4, c * kh * kw * n * oh * ow * 4), device)
+    check(lib().nvq_im2col_f32(col.at(0), dx.at(0), n, c, h, wd, kh, kw, stride[0], stride[1],
+                               padding[0], padding[1], _pad_mode(padding_mode), device, None))
+    return col.to_numpy(np.float32, (c * kh * kw, n * oh * ow))

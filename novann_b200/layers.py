@@ -143,7 +143,8 @@ class QuantLinear(Linear):
 
 
 class Conv2d(Layer):
-    """2-D convolution, fp32 forward on the GPU (im2col + GEMM, the reference's layout)."""
+    """2-D convolution in fp32 on the GPU: im2col + GEMM forward, GEMMs + col2im gather backward
+    (the reference's layouts and gradient rules)."""
 
     def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0,
                  bias: bool = True, padding_mode: str = "zeros", init=None, device: int = 0):
@@ -181,8 +182,14 @@ class Conv2d(Layer):
         return out
 
     def backward(self, grad: np.ndarray) -> np.ndarray:
-        raise NotImplementedError(
-            "Conv2d.backward (col2im) is not part of this build: forward only")
+        grad = np.ascontiguousarray(grad.astype(np.float32, copy=False))
+        dw, db, dx = F.conv2d_bwd_f32_host(grad, self._cache["col"], self.weight.data,
+                                           self._cache["x_shape"], (self.sh, self.sw),
+                                           (self.ph, self.pw), self.bias is not None, self.device)
+        self.weight.grad = dw
+        if self.bias is not None:
+            self.bias.grad = db
+        return dx
 
     def parameters(self):
         return [self.weight] + ([self.bias] if self.bias is not None else [])
@@ -215,7 +222,9 @@ class QuantConv2d(Conv2d):
 
     def forward(self, x: np.ndarray) -> np.ndarray:
         x = np.ascontiguousarray(x.astype(np.float32, copy=False))
-        self._cache = {"x_shape": x.shape}
+        # backward uses the fp32 master weight (straight-through), so it needs the fp32 patches
+        self._cache = {"x_shape": x.shape, "col": F.im2col_f32_host(
+            x, (self.KH, self.KW), (self.sh, self.sw), (self.ph, self.pw), self.pm, self.device)}
         b = None if self.bias is None else self.bias.data.reshape(-1)
         return F.conv2d_q_host(x, self._codes, self._scales, b, (self.KH, self.KW), (self.sh, self.sw),
                                (self.ph, self.pw), self.pm, self.fmt, self.device)

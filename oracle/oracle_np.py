@@ -485,3 +485,26 @@ def conv2d_fwd_f32(x, w, b, stride=(1, 1), padding=(0, 0), padding_mode="zeros")
     if b is not None:
         out += np.asarray(b, np.float32).reshape(cout, 1)
     return np.ascontiguousarray(out.reshape(cout, n, oh, ow).transpose(1, 0, 2, 3))
+
+
+def conv2d_bwd_f32(grad, col, w, x_shape, stride=(1, 1), padding=(0, 0)):
+    """``Conv2d.backward`` with ``_col2im`` (novann/layers/convolutional/conv2d.py:117-148,
+    179-207).  Returns (dW, db (Cout,1), dX).  col2im is written as strided slice adds in
+    (kh, kw) order, the order in which np.add.at applies the contributions; gradient that
+    lands on padding is cropped away, as the reference does for every padding mode."""
+    grad = np.asarray(grad, np.float32)
+    w = np.asarray(w, np.float32)
+    n, c, h, wd = x_shape
+    cout, _, kh, kw = w.shape
+    sh, sw = stride
+    ph, pw = padding
+    oh, ow = grad.shape[2], grad.shape[3]
+    g_r = grad.transpose(1, 0, 2, 3).reshape(cout, -1)
+    dw = (g_r @ np.asarray(col, np.float32).T).reshape(w.shape)
+    db = np.sum(g_r, axis=1).reshape(-1, 1)
+    dcol = (w.reshape(cout, -1).T @ g_r).reshape(c, kh, kw, n, oh, ow)
+    dxp = np.zeros((n, c, h + 2 * ph, wd + 2 * pw), np.float32)
+    for i in range(kh):
+        for j in range(kw):
+            dxp[:, :, i:i + sh * oh:sh, j:j + sw * ow:sw] += dcol[:, i, j].transpose(1, 0, 2, 3)
+    return dw, db, np.ascontiguousarray(dxp[:, :, ph:ph + h, pw:pw + wd])

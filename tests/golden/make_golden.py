@@ -116,6 +116,9 @@ def main():
         xc = rs.standard_normal((cs["n"], cs["c"], cs["h"], cs["w"])).astype(np.float32)
         yc = np.ascontiguousarray(layer(xc))
         conv[f"x{i}"], conv[f"w{i}"], conv[f"b{i}"], conv[f"y{i}"] = xc, layer.weight.data, layer.bias.data, yc
+        gc = rs.standard_normal(yc.shape).astype(np.float32)
+        dxc = np.ascontiguousarray(layer.backward(gc))
+        conv[f"g{i}"], conv[f"dx{i}"], conv[f"dw{i}"], conv[f"db{i}"] = gc, dxc, layer.weight.grad, layer.bias.grad
         conv[f"geom{i}"] = np.array([*cs["k"], *cs["s"], *cs["p"],
                                      ["zeros", "reflect", "replicate", "circular"].index(cs["mode"])])
         if i == 1:

@@ -66,6 +66,17 @@ def test_conv2d_forward_all_padding_modes():
     assert np.array_equal(col, g["col1"])                              # same (c,kh,kw) x (n,oh,ow) order
 
 
+def test_conv2d_backward():
+    g = load("conv2d")
+    modes = ["zeros", "reflect", "replicate", "circular"]
+    for i in range(int(g["n_cases"])):
+        kh, kw, sh, sw, ph, pw, mi = (int(v) for v in g[f"geom{i}"])
+        col, _, _ = o.im2col(g[f"x{i}"], kh, kw, sh, sw, ph, pw, modes[mi])
+        dw, db, dx = o.conv2d_bwd_f32(g[f"g{i}"], col, g[f"w{i}"], g[f"x{i}"].shape, (sh, sw), (ph, pw))
+        assert dx.shape == g[f"dx{i}"].shape and db.shape == g[f"db{i}"].shape
+        assert close(dw, g[f"dw{i}"], 1e-5) and close(db, g[f"db{i}"], 1e-5) and close(dx, g[f"dx{i}"], 1e-5), i
+
+
 def test_mlp_step_small_full_vectors():
     g = load("mlp_small")
     x, y, params = workloads.mlp_inputs(16, (32, 16, 8, 10), seed=1)

@@ -110,6 +110,36 @@ def test_conv2d_forward_reference_vectors(gpu):
             assert np.array_equal(layer._cache["col"], g["col1"])   # same im2col ordering, bit for bit
 
 
+def test_conv2d_backward_reference_vectors(gpu):
+    g = load("conv2d")
+    modes = ["zeros", "reflect", "replicate", "circular"]
+    for i in range(int(g["n_cases"])):
+        kh, kw, sh, sw, ph, pw, mi = (int(v) for v in g[f"geom{i}"])
+        w = g[f"w{i}"]
+        layer = nb.Conv2d(w.shape[1], w.shape[0], (kh, kw), stride=(sh, sw), padding=(ph, pw),
+                          padding_mode=modes[mi], device=gpu)
+        layer.weight.data, layer.bias.data = w.copy(), g[f"b{i}"].copy()
+        layer(g[f"x{i}"])
+        dx = layer.backward(g[f"g{i}"])
+        assert dx.shape == g[f"x{i}"].shape and dx.dtype == np.float32
+        assert layer.weight.grad.shape == w.shape and layer.bias.grad.shape == (w.shape[0], 1)
+        assert close(dx, g[f"dx{i}"], 1e-5), i
+        assert close(layer.weight.grad, g[f"dw{i}"], 1e-5), i
+        assert close(layer.bias.grad, g[f"db{i}"], 1e-5), i
+
+
+def test_quant_conv2d_backward_uses_master_weight(gpu):
+    g = load("conv2d")
+    kh, kw, sh, sw, ph, pw, mi = (int(v) for v in g["geom5"])
+    w = g["w5"]
+    layer = nb.QuantConv2d(w.shape[1], w.shape[0], (kh, kw), stride=(sh, sw), padding=(ph, pw), device=gpu)
+    layer.weight.data, layer.bias.data = w.copy(), g["b5"].copy()
+    layer.requantize()
+    layer(g["x5"])
+    dx = layer.backward(g["g5"])
+    assert close(dx, g["dx5"], 1e-5) and close(layer.weight.grad, g["dw5"], 1e-5)
+
+
 def test_conv2d_rejects_bad_padding(gpu):
     with pytest.raises(ValueError):
         nb.Conv2d(1, 1, 3, padding="same")
