@@ -169,6 +169,20 @@ nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf16, const ui
                           nvq_dtype w_fmt, const float* d_w_scales, const float* d_bias,
                           size_t M, size_t N, size_t K, void* d_workspace, size_t workspace_bytes,
                           int device, void* stream);
+/* Backward of the quantised-weight Linear on the tensor cores (Linear.backward,
+ * novann/layers/linear/linear.py:85-108, with the weight held as FP8 codes):
+ *   dX (M x K fp32) = bf16(G) @ bf16(dequant(Wq) * s)      G: M x N fp32 gradient of the output
+ *   dW (N x K fp32) = bf16(G)^T @ bf16(X)                  X: M x K fp32 forward input
+ *   db (N fp32)     = column sums of G, rows added in order
+ * bf16 operands, fp32 accumulation and fp32 results; any of d_dx, d_dw, d_db may be NULL.
+ * M, N, K multiples of 8.  d_workspace: nvq_linear_bwd_q_workspace_bytes bytes, 256-byte
+ * aligned (bf16 copies / transposes of G, X and the scaled weight). */
+nvq_status nvq_linear_bwd_q_workspace_bytes(size_t M, size_t N, size_t K, size_t* bytes);
+nvq_status nvq_linear_bwd_q(float* d_dx, float* d_dw, float* d_db, const float* d_g,
+                            const float* d_x, const uint8_t* d_wq, nvq_dtype w_fmt,
+                            const float* d_w_scales, size_t M, size_t N, size_t K,
+                            void* d_workspace, size_t workspace_bytes, int device, void* stream);
+
 /* Allocation-free form of nvq_linear_fwd.  It has no counterpart in the reference.
  *
  * Some hosts of this library may not allocate device memory at the point where they need a

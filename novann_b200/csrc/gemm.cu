@@ -163,7 +163,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (!ok) break;
             tc::tc_fence_after();
             const int row = m0 + quarter * 32 + lane;
-            uint16_t* yrow = p.y + (size_t)row * p.N + n0;
             const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
             for (int c = 0; c < bn; c += 32) {
@@ -171,7 +170,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 tc::tmem_ld_32x32(taddr + c, r);
                 tc::tmem_ld_wait();
                 if (row < p.M)
-                    store_chunk(r, &sh->scale[acc][c], &sh->bias[acc][c], yrow + c, n0 + c, p.N, vec32);
+                    store_row_chunk(p, r, &sh->scale[acc][c], &sh->bias[acc][c], row, n0 + c, vec32);
             }
             tc::tc_fence_before();
             __syncwarp();
@@ -302,7 +301,7 @@ nvq_status nvq_make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, u
 
 nvq_status nvq_linear_launch_single(uint16_t* d_y, const uint16_t* d_x, const uint16_t* d_w_bf16,
                                     const float* d_scales, const float* d_bias, size_t M, size_t N,
-                                    size_t K, int device, cudaStream_t st) {
+                                    size_t K, int out_f32, int device, cudaStream_t st) {
     CUtensorMap map_a, map_b;
     nvq_status s = nvq_make_tmap_2d(&map_a, d_x, M, K, BM, BK, 2);
     if (s != NVQ_OK) return s;
@@ -315,6 +314,7 @@ nvq_status nvq_linear_launch_single(uint16_t* d_y, const uint16_t* d_x, const ui
     }
     LinearParams p;
     p.y = d_y;
+    p.out_f32 = out_f32;
     p.wq = nullptr;
     p.scales = d_scales;
     p.bias = d_bias;
@@ -344,7 +344,7 @@ nvq_status nvq_linear_launch_single(uint16_t* d_y, const uint16_t* d_x, const ui
 // NVQ_LINEAR_MODE=single|pair overrides the choice (for measurements).
 nvq_status nvq_linear_bf16_launch(uint16_t* d_y, const uint16_t* d_x, const uint16_t* d_w_bf16,
                                   const float* d_scales, const float* d_bias, size_t M, size_t N,
-                                  size_t K, int device, cudaStream_t st) {
+                                  size_t K, int out_f32, int device, cudaStream_t st) {
     NVQ_REQUIRE(K % 8 == 0 && N % 8 == 0, "nvq_linear_fwd: K (%zu) and N (%zu) must be multiples of 8", K, N);
     NVQ_REQUIRE(nvq_aligned(d_y, 32), "nvq_linear_fwd: Y must be 32-byte aligned");
     NVQ_REQUIRE(M < (1u << 31) && N < (1u << 31) && K < (1u << 31), "nvq_linear_fwd: dimension too large");
@@ -353,8 +353,8 @@ nvq_status nvq_linear_bf16_launch(uint16_t* d_y, const uint16_t* d_x, const uint
         if (mode[0] == 's') pair = false;
         if (mode[0] == 'p') pair = true;
     }
-    if (pair) return nvq_linear_launch_pair(d_y, d_x, d_w_bf16, d_scales, d_bias, M, N, K, device, st);
-    return nvq_linear_launch_single(d_y, d_x, d_w_bf16, d_scales, d_bias, M, N, K, device, st);
+    if (pair) return nvq_linear_launch_pair(d_y, d_x, d_w_bf16, d_scales, d_bias, M, N, K, out_f32, device, st);
+    return nvq_linear_launch_single(d_y, d_x, d_w_bf16, d_scales, d_bias, M, N, K, out_f32, device, st);
 }
 
 extern "C" nvq_status nvq_linear_workspace_bytes(size_t N, size_t K, nvq_dtype w_fmt, size_t* bytes) {
@@ -429,7 +429,7 @@ extern "C" nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf1
         NVQ_REQUIRE(nvq_aligned(d_y_bf16, 32), "nvq_linear_fwd: Y must be 32-byte aligned");
         NVQ_REQUIRE(M < (1u << 31) && N < (1u << 31) && K < (1u << 31), "nvq_linear_fwd: dimension too large");
         return nvq_linear_launch_pair_fused(d_y_bf16, d_x_bf16, d_wq, w_fmt, d_w_scales, d_bias, M, N, K,
-                                            device, st);
+                                            0, device, st);
     }
     NVQ_REQUIRE(d_workspace && workspace_bytes >= N * K * 2 && nvq_aligned(d_workspace, 32),
                 "nvq_linear_fwd: workspace of %zu bytes (32-byte aligned) required", N * K * 2);
@@ -449,7 +449,7 @@ extern "C" nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf1
                               : ew_launch(ExpandOp<NVQ_E5M2>{}, d_wq, wd, N * K, device, st, 16, 32);
         if (s != NVQ_OK) return s;
     }
-    return nvq_linear_bf16_launch(d_y_bf16, d_x_bf16, wd, chan_scales, d_bias, M, N, K, device, st);
+    return nvq_linear_bf16_launch(d_y_bf16, d_x_bf16, wd, chan_scales, d_bias, M, N, K, 0, device, st);
 }
 
 // ---------------------------------------------------------------- allocation-free variant

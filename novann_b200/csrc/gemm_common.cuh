@@ -4,7 +4,8 @@
 #include "tc_common.cuh"
 
 struct LinearParams {
-    uint16_t* y;
+    uint16_t* y;           // M x N output: bf16, or fp32 when out_f32 is set
+    int out_f32;
     const uint8_t* wq;     // fused kernels: the weight codes (N x K bytes); else unused
     const float* scales;   // N per-output-channel factors or nullptr (= 1)
     const float* bias;     // N or nullptr (= 0)
@@ -18,17 +19,22 @@ struct LinearParams {
 
 nvq_status nvq_status_word(int device, int** dev_ptr);
 
+// Y = scale_n * X @ Wd^T + bias_n with Wd (N x K) already 16-bit; Y bf16 or fp32 (out_f32)
+nvq_status nvq_linear_bf16_launch(uint16_t* d_y, const uint16_t* d_x, const uint16_t* d_w_bf16,
+                                  const float* d_scales, const float* d_bias, size_t M, size_t N,
+                                  size_t K, int out_f32, int device, cudaStream_t st);
+
 // launchers (gemm.cu: one CTA per 128 x 256 tile; gemm_pair.cu: CTA pair per 256 x 256 tile)
 nvq_status nvq_linear_launch_single(uint16_t* d_y, const uint16_t* d_x, const uint16_t* d_w,
                                     const float* d_scales, const float* d_bias, size_t M, size_t N,
-                                    size_t K, int device, cudaStream_t st);
+                                    size_t K, int out_f32, int device, cudaStream_t st);
 nvq_status nvq_linear_launch_pair(uint16_t* d_y, const uint16_t* d_x, const uint16_t* d_w,
                                   const float* d_scales, const float* d_bias, size_t M, size_t N,
-                                  size_t K, int device, cudaStream_t st);
+                                  size_t K, int out_f32, int device, cudaStream_t st);
 
 nvq_status nvq_linear_launch_pair_fused(uint16_t* d_y, const uint16_t* d_x, const uint8_t* d_wq,
                                         nvq_dtype fmt, const float* d_scales, const float* d_bias,
-                                        size_t M, size_t N, size_t K, int device, cudaStream_t st);
+                                        size_t M, size_t N, size_t K, int out_f32, int device, cudaStream_t st);
 
 #ifdef __CUDACC__
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
@@ -76,6 +82,29 @@ __device__ __forceinline__ TileRef tile_ref(const LinearParams& p, int item) {
     return t;
 }
 
+// fp32 flavour of store_chunk: 32 accumulators -> scale, bias -> 128 bytes of the row
+__device__ __forceinline__ void store_chunk_f32(const uint32_t* r, const float* scale, const float* bias,
+                                                float* yrow, int n_base, int N, bool vec32) {
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+        u32x8 o;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int cc = g * 8 + j;
+            o.v[j] = __float_as_uint(fmaf(__uint_as_float(r[cc]), scale[cc], bias[cc]));
+        }
+        const int n = n_base + g * 8;
+        if (n + 8 <= N) {
+            if (vec32) {
+                stg_stream_256(yrow + g * 8, o);
+            } else {
+                stg_stream_128(yrow + g * 8, make_uint4(o.v[0], o.v[1], o.v[2], o.v[3]));
+                stg_stream_128(yrow + g * 8 + 4, make_uint4(o.v[4], o.v[5], o.v[6], o.v[7]));
+            }
+        }
+    }
+}
+
 // Epilogue of one 32-column chunk: 32 fp32 accumulators of this thread's row -> scale,
 // bias, bf16, global stores.  `vec32` = rows start on 32-byte boundaries.
 __device__ __forceinline__ void store_chunk(const uint32_t* r, const float* scale, const float* bias,
@@ -98,5 +127,14 @@ __device__ __forceinline__ void store_chunk(const uint32_t* r, const float* scal
             if (n + 16 <= N) stg_stream_128(yrow + g * 16 + 8, make_uint4(o.v[4], o.v[5], o.v[6], o.v[7]));
         }
     }
+}
+// one 32-column chunk of output row `row`, columns [n, n + 32), in the output's own type
+__device__ __forceinline__ void store_row_chunk(const LinearParams& p, const uint32_t* r,
+                                                const float* scale, const float* bias, int row, int n,
+                                                bool vec32) {
+    if (p.out_f32)
+        store_chunk_f32(r, scale, bias, (float*)p.y + (size_t)row * p.N + n, n, p.N, (p.N % 8) == 0);
+    else
+        store_chunk(r, scale, bias, p.y + (size_t)row * p.N + n, n, p.N, vec32);
 }
 #endif

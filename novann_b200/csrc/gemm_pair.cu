@@ -281,7 +281,6 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             if (!ok) break;
             tc::tc_fence_after();
             const int row = m0 + quarter * 32 + lane;
-            uint16_t* yrow = p.y + (size_t)row * p.N + n0;
             const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
             for (int c = 0; c < bn; c += 32) {
@@ -289,7 +288,7 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 tc::tmem_ld_32x32(taddr + c, r);
                 tc::tmem_ld_wait();
                 if (row < p.M)
-                    store_chunk(r, &sh->scale[acc][c], &sh->bias[acc][c], yrow + c, n0 + c, p.N, vec32);
+                    store_row_chunk(p, r, &sh->scale[acc][c], &sh->bias[acc][c], row, n0 + c, vec32);
             }
             tc::tc_fence_before();
             __syncwarp();
@@ -312,7 +311,7 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 template <int FUSED>
 static nvq_status launch_pair(uint16_t* d_y, const uint16_t* d_x, const void* d_w,
                               const float* d_scales, const float* d_bias, size_t M, size_t N,
-                              size_t K, int device, cudaStream_t st) {
+                              size_t K, int out_f32, int device, cudaStream_t st) {
     CUtensorMap map_a, map_b;
     nvq_status s = nvq_make_tmap_2d(&map_a, d_x, M, K, 128, BK, 2);
     if (s != NVQ_OK) return s;
@@ -327,6 +326,7 @@ static nvq_status launch_pair(uint16_t* d_y, const uint16_t* d_x, const void* d_
     }
     LinearParams p;
     p.y = d_y;
+    p.out_f32 = out_f32;
     p.wq = FUSED ? (const uint8_t*)d_w : nullptr;
     p.scales = d_scales;
     p.bias = d_bias;
@@ -364,15 +364,15 @@ static nvq_status launch_pair(uint16_t* d_y, const uint16_t* d_x, const void* d_
 
 nvq_status nvq_linear_launch_pair(uint16_t* d_y, const uint16_t* d_x, const uint16_t* d_w,
                                   const float* d_scales, const float* d_bias, size_t M, size_t N,
-                                  size_t K, int device, cudaStream_t st) {
-    return launch_pair<0>(d_y, d_x, d_w, d_scales, d_bias, M, N, K, device, st);
+                                  size_t K, int out_f32, int device, cudaStream_t st) {
+    return launch_pair<0>(d_y, d_x, d_w, d_scales, d_bias, M, N, K, out_f32, device, st);
 }
 
 nvq_status nvq_linear_launch_pair_fused(uint16_t* d_y, const uint16_t* d_x, const uint8_t* d_wq,
                                         nvq_dtype fmt, const float* d_scales, const float* d_bias,
-                                        size_t M, size_t N, size_t K, int device, cudaStream_t st) {
+                                        size_t M, size_t N, size_t K, int out_f32, int device, cudaStream_t st) {
     NVQ_REQUIRE(K % 16 == 0, "nvq_linear_fwd: K (%zu) must be a multiple of 16 for the fused FP8 path", K);
     if (fmt == NVQ_E4M3)
-        return launch_pair<NVQ_E4M3>(d_y, d_x, d_wq, d_scales, d_bias, M, N, K, device, st);
-    return launch_pair<NVQ_E5M2>(d_y, d_x, d_wq, d_scales, d_bias, M, N, K, device, st);
+        return launch_pair<NVQ_E4M3>(d_y, d_x, d_wq, d_scales, d_bias, M, N, K, out_f32, device, st);
+    return launch_pair<NVQ_E5M2>(d_y, d_x, d_wq, d_scales, d_bias, M, N, K, out_f32, device, st);
 }

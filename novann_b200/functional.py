@@ -213,3 +213,26 @@ def im2col_f32_host(x, kernel, stride, padding, padding_mode: str = "zeros", dev
     check(lib().nvq_im2col_f32(col.at(0), dx.at(0), n, c, h, wd, kh, kw, stride[0], stride[1],
                                padding[0], padding[1], _pad_mode(padding_mode), device, None))
     return col.to_numpy(np.float32, (c * kh * kw, n * oh * ow))
+
+
+def linear_q_bwd_host(grad, x, wq, w_scales, fmt: str = "e4m3", with_bias: bool = True, device: int = 0):
+    """Backward of the quantised Linear on the tensor cores: returns (dW (N,K) fp32, db (1,N) or
+    None, dX (M,K) fp32) from the output gradient, the forward input and the weight codes."""
+    grad, x = _f32(grad), _f32(x)
+    m, n = grad.shape
+    k = x.shape[1]
+    need = C.c_size_t()
+    check(lib().nvq_linear_bwd_q_workspace_bytes(m, n, k, C.byref(need)))
+    dg, dx_in = DeviceBuffer.from_numpy(grad, device), DeviceBuffer.from_numpy(x, device)
+    dq = DeviceBuffer.from_numpy(np.ascontiguousarray(wq, np.uint8), device)
+    ds = DeviceBuffer.from_numpy(_f32(w_scales), device)
+    o_dx, o_dw, o_db = DeviceBuffer(m * k * 4, device), DeviceBuffer(n * k * 4, device), DeviceBuffer(n * 4, device)
+    ws = DeviceBuffer(need.value, device)
+    check(lib().nvq_linear_bwd_q(o_dx.at(0), o_dw.at(0), o_db.at(0) if with_bias else None, dg.at(0),
+                                 dx_in.at(0), dq.at(0), _lib.DTYPE_IDS[fmt], ds.at(0), m, n, k,
+                                 ws.at(0), ws.nbytes, device, None))
+    device_sync(device)
+    check_device_errors(device)
+    return (o_dw.to_numpy(np.float32, (n, k)),
+            o_db.to_numpy(np.float32, (1, n)) if with_bias else None,
+            o_dx.to_numpy(np.float32, (m, k)))

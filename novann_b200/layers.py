@@ -115,11 +115,14 @@ class QuantLinear(Linear):
     """Linear whose forward contraction uses FP8 / FP4 weight codes on the tensor cores.
 
     Forward: ``bf16(x) @ dequant(Wq)^T * s + b`` -> bf16 -> returned as float32.  Backward
-    follows the reference's rules on the fp32 master weight (straight-through)."""
+    follows the reference's rules (straight-through to the fp32 master weight): in fp32 on
+    the CUDA cores by default, or with ``tensor_core_backward=True`` (FP8 formats, batch and
+    feature sizes multiples of 8) as bf16 contractions on the tensor cores against the codes."""
 
     def __init__(self, in_features: int, out_features: int, bias: bool = True, init=None,
-                 fmt: str = "e4m3", device: int = 0) -> None:
+                 fmt: str = "e4m3", device: int = 0, tensor_core_backward: bool = False) -> None:
         self.fmt = fmt
+        self.tensor_core_backward = tensor_core_backward
         self._codes = self._scales = None
         super().__init__(in_features, out_features, bias, init, device)
 
@@ -140,6 +143,17 @@ class QuantLinear(Linear):
         b = None if self.bias is None else self.bias.data.reshape(-1)
         yb = F.linear_q_host(xb, self._codes, self._scales, b, self.fmt, self.device)
         return quant.cast(yb, "f32", src_dtype="bf16", device=self.device)
+
+    def backward(self, grad: np.ndarray) -> np.ndarray:
+        if not (self.tensor_core_backward and self.fmt in ("e4m3", "e5m2")):
+            return super().backward(grad)
+        grad = np.ascontiguousarray(grad.astype(np.float32, copy=False))
+        dw, db, dx = F.linear_q_bwd_host(grad, self._cache_input, self._codes, self._scales, self.fmt,
+                                         self.bias is not None, self.device)
+        self.weight.grad = dw
+        if self.bias is not None:
+            self.bias.grad = db
+        return dx
 
 
 class Conv2d(Layer):

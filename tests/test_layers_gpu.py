@@ -182,6 +182,41 @@ def test_quant_linear_layer(gpu, fmt, tol):
     assert dx.shape == (160, 256) and layer.weight.grad.shape == (192, 256)
 
 
+@pytest.mark.parametrize("m,n,k", [(8, 8, 8), (160, 192, 256), (264, 520, 136), (1024, 512, 2048)])
+def test_quant_linear_backward_on_tensor_cores(gpu, m, n, k):
+    """dX, dW, db of the quantised Linear as bf16 tensor-core contractions.  Oracle: the same
+    bf16-rounded operands contracted in float64; bound 1e-2 (max-abs-rel) as for the forward.
+    db is an fp32 sum in row order and matches NumPy's column sum to rounding."""
+    rng = np.random.default_rng(m + n)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    g = (rng.standard_normal((m, n)) / m).astype(np.float32)
+    wq, sc = o.quantize_weight_per_channel(w, "e4m3")
+    dw, db, dx = F.linear_q_bwd_host(g, x, wq, sc, "e4m3", True, gpu)
+    r = lambda a: o.bf16_bits_to_f32(o.f32_to_bf16_bits(a)).reshape(a.shape).astype(np.float64)
+    wd = r(o.E4M3_TABLE[wq] * sc[:, None])
+    assert dx.shape == (m, k) and dw.shape == (n, k) and db.shape == (1, n) and dx.dtype == np.float32
+    assert o.max_abs_rel(dx, r(g) @ wd) <= 2.0 ** -10
+    assert o.max_abs_rel(dw, r(g).T @ r(x)) <= 2.0 ** -10
+    assert close(db, g.astype(np.float64).sum(0, keepdims=True), 1e-5)
+    # and against the reference's fp32 rules on the dequantised weight: inside the FP8 bound
+    rdw, rdb, rdx = o.linear_bwd_f32(x, (o.E4M3_TABLE[wq] * sc[:, None]).astype(np.float32), g)
+    assert o.max_abs_rel(dx, rdx) <= 1e-2 and o.max_abs_rel(dw, rdw) <= 1e-2
+
+
+def test_quant_linear_layer_tensor_core_backward(gpu):
+    rng = np.random.default_rng(1)
+    layer = nb.QuantLinear(128, 64, fmt="e4m3", device=gpu, tensor_core_backward=True)
+    x = rng.standard_normal((96, 128)).astype(np.float32)
+    layer(x)
+    g = rng.standard_normal((96, 64)).astype(np.float32)
+    dx = layer.backward(g)
+    ref_dw, ref_db, ref_dx = o.linear_bwd_f32(x, layer.weight.data, g)
+    assert o.max_abs_rel(dx, ref_dx) <= 4e-2          # FP8 weight error shows in dX
+    assert o.max_abs_rel(layer.weight.grad, ref_dw) <= 1e-2
+    assert close(layer.bias.grad, ref_db, 1e-5)
+
+
 @pytest.mark.parametrize("case", [0, 1, 3, 4, 5])
 def test_quant_conv2d_layer(gpu, case):
     g = load("conv2d")
