@@ -253,6 +253,16 @@ nvq_status nvq_softmax_ce_f32(float* d_grad, float* d_loss, const float* d_logit
 nvq_status nvq_sgd_step_f32(float* d_param, const float* d_grad, size_t n, float lr,
                             float grad_scale, int device, void* stream);
 
+/* AdamW.step (novann/optim/adamw.py:41-65) on one tensor, in place on p, m, v:
+ *   m = b1*m + (1-b1)*g;  v = b2*v + (1-b2)*g*g;  p -= lr*(m/bc1) / (sqrt(v/bc2) + eps);
+ *   if apply_decay: p -= (lr*wd) * p.   bc1 = 1 - b1^t, bc2 = 1 - b2^t.
+ * The caller passes the derived scalars already rounded to fp32 (as NumPy rounds the Python
+ * floats); every operation is a separately rounded fp32 operation, so results are bit-exact. */
+nvq_status nvq_adamw_step_f32(float* d_param, const float* d_grad, float* d_m, float* d_v, size_t n,
+                              float beta1, float one_minus_beta1, float beta2, float one_minus_beta2,
+                              float bias_corr1, float bias_corr2, float lr, float eps,
+                              float lr_times_wd, int apply_decay, int device, void* stream);
+
 /* ---------------------------------------------------------------- Conv2d forward
  * Replaces F.conv2d, novann/functional.py:275-385: pad (zeros / reflect / replicate /
  * circular = np.pad constant / reflect / edge / wrap) -> im2col with rows ordered (c,kh,kw)

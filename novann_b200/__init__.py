@@ -8,7 +8,7 @@ from .layers import Conv2d, Linear, QuantConv2d, QuantLinear, ReLU  # noqa: F401
 from .losses import CrossEntropyLoss  # noqa: F401
 from .model import Sequential  # noqa: F401
 from .module import Layer, Module, Parameters  # noqa: F401
-from .optim import SGD  # noqa: F401
+from .optim import SGD, AdamW  # noqa: F401
 
 __all__ = ["functional", "quant", "Linear", "QuantLinear", "ReLU", "Conv2d", "QuantConv2d",
-           "Sequential", "CrossEntropyLoss", "SGD", "Layer", "Module", "Parameters"]
+           "Sequential", "CrossEntropyLoss", "SGD", "AdamW", "Layer", "Module", "Parameters"]

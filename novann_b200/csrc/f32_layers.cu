@@ -215,6 +215,26 @@ __global__ void sgd_kernel(float* __restrict__ p, const float* __restrict__ g, s
     }
 }
 
+// AdamW.step (novann/optim/adamw.py:41-65), every product, sum, quotient and root rounded
+// separately in fp32 exactly where NumPy rounds them.
+struct AdamWArgs { float b1, c1, b2, c2, bc1, bc2, lr, eps, lr_wd; int decay; };
+__global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+                             float* __restrict__ v, size_t n, AdamWArgs a) {
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float gi = g[i];
+        float mi = __fadd_rn(__fmul_rn(a.b1, m[i]), __fmul_rn(a.c1, gi));
+        float vi = __fadd_rn(__fmul_rn(a.b2, v[i]), __fmul_rn(a.c2, __fmul_rn(gi, gi)));
+        m[i] = mi;
+        v[i] = vi;
+        float mh = __fdiv_rn(mi, a.bc1), vh = __fdiv_rn(vi, a.bc2);
+        float upd = __fdiv_rn(__fmul_rn(a.lr, mh), __fadd_rn(__fsqrt_rn(vh), a.eps));
+        float pi = __fsub_rn(p[i], upd);
+        if (a.decay) pi = __fsub_rn(pi, __fmul_rn(a.lr_wd, pi));
+        p[i] = pi;
+    }
+}
+
 // ---- im2col ---------------------------------------------------------------------------
 __device__ __forceinline__ int pad_index(int idx, int size, int mode, bool& zero) {
     zero = false;
@@ -551,5 +571,21 @@ extern "C" nvq_status nvq_conv2d_bwd_f32(float* d_dw, float* d_db, float* d_dx, 
         col2im_kernel<<<ew_grid((size_t)N * C * H * W, device), 256, 0, st>>>(d_dx, d_dcol, gm);
         NVQ_LAUNCHED();
     }
+    return NVQ_OK;
+}
+
+extern "C" nvq_status nvq_adamw_step_f32(float* d_param, const float* d_grad, float* d_m, float* d_v,
+                                         size_t n, float beta1, float one_minus_beta1, float beta2,
+                                         float one_minus_beta2, float bias_corr1, float bias_corr2,
+                                         float lr, float eps, float lr_times_wd, int apply_decay,
+                                         int device, void* stream) {
+    if (n == 0) return NVQ_OK;
+    NVQ_REQUIRE(d_param && d_grad && d_m && d_v, "nvq_adamw_step_f32: null buffer");
+    nvq_status s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    AdamWArgs a{beta1, one_minus_beta1, beta2, one_minus_beta2, bias_corr1, bias_corr2, lr, eps,
+                lr_times_wd, apply_decay};
+    adamw_kernel<<<ew_grid(n, device), 256, 0, (cudaStream_t)stream>>>(d_param, d_grad, d_m, d_v, n, a);
+    NVQ_LAUNCHED();
     return NVQ_OK;
 }

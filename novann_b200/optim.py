@@ -35,3 +35,40 @@ class SGD:
     def zero_grad(self, set_to_none: bool = False) -> None:
         for p in self.params:
             p.zero_grad(set_to_none=set_to_none)
+
+
+class AdamW:
+    """``AdamW`` with the reference's contract (``novann/optim/adamw.py:6-69``): decoupled weight
+    decay, skipped for parameters named ``gamma`` / ``beta``.  Moments live on the device."""
+
+    def __init__(self, parameters, lr: float, betas=(0.9, 0.999), weight_decay: float = 0,
+                 epsilon: float = 1e-8, device: int = 0) -> None:
+        self.params = list(parameters)
+        self.lr, self.wd = float(lr), float(weight_decay)
+        self.b1, self.b2, self.eps = float(betas[0]), float(betas[1]), float(epsilon)
+        self.device = device
+        self.t = 0
+        self._m = [DeviceBuffer(max(4, p.data.nbytes), device) for p in self.params]
+        self._v = [DeviceBuffer(max(4, p.data.nbytes), device) for p in self.params]
+        for b in self._m + self._v:
+            b.zero()
+
+    def step(self) -> None:
+        self.t += 1
+        f = C.c_float
+        for i, p in enumerate(self.params):
+            if p.grad is None:
+                continue
+            decay = self.wd > 0 and getattr(p, "name", None) not in ("gamma", "beta")
+            d = DeviceBuffer.from_numpy(np.ascontiguousarray(p.data, np.float32), self.device)
+            g = DeviceBuffer.from_numpy(np.ascontiguousarray(p.grad, np.float32), self.device)
+            check(lib().nvq_adamw_step_f32(
+                d.at(0), g.at(0), self._m[i].at(0), self._v[i].at(0), p.data.size,
+                f(self.b1), f(1 - self.b1), f(self.b2), f(1 - self.b2), f(1 - self.b1 ** self.t),
+                f(1 - self.b2 ** self.t), f(self.lr), f(self.eps), f(self.lr * self.wd), int(decay),
+                self.device, None))
+            p.data[...] = d.to_numpy(np.float32, p.data.shape)
+
+    def zero_grad(self, set_to_none: bool = False) -> None:
+        for p in self.params:
+            p.zero_grad(set_to_none=set_to_none)

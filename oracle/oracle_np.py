@@ -508,3 +508,16 @@ def conv2d_bwd_f32(grad, col, w, x_shape, stride=(1, 1), padding=(0, 0)):
         for j in range(kw):
             dxp[:, :, i:i + sh * oh:sh, j:j + sw * ow:sw] += dcol[:, i, j].transpose(1, 0, 2, 3)
     return dw, db, np.ascontiguousarray(dxp[:, :, ph:ph + h, pw:pw + wd])
+
+
+def adamw_step(p, g, m, v, t, lr, b1=0.9, b2=0.999, eps=1e-8, wd=0.0, decay=True):
+    """One ``AdamW.step`` on one tensor (novann/optim/adamw.py:41-65), NumPy fp32 arithmetic
+    with Python-float scalars exactly as the reference writes it.  Returns (p, m, v)."""
+    m = b1 * m + (1 - b1) * g
+    v = b2 * v + (1 - b2) * (g ** 2)
+    m_hat = m / (1 - b1 ** t)
+    v_hat = v / (1 - b2 ** t)
+    p = p - lr * m_hat / (np.sqrt(v_hat) + eps)
+    if wd > 0 and decay:
+        p = p - lr * wd * p
+    return p.astype(np.float32), m.astype(np.float32), v.astype(np.float32)

@@ -131,6 +131,20 @@ def main():
     before = p.data.copy()
     SGD([p], lr=0.01).step()
     out["sgd"] = dict(before=before, grad=p.grad, after=p.data)
+    # ---- AdamW, three steps, one decayed tensor and one named "gamma" (no decay)
+    from novann.optim import AdamW
+    pa = Parameters(rs.standard_normal((6, 9)).astype(np.float32))
+    pg = Parameters(rs.standard_normal((9,)).astype(np.float32))
+    pg.name = "gamma"
+    ad = dict(p0=pa.data.copy(), q0=pg.data.copy())
+    opt = AdamW([pa, pg], lr=1e-3, weight_decay=1e-2)
+    for t in range(3):
+        pa.grad = rs.standard_normal((6, 9)).astype(np.float32)
+        pg.grad = rs.standard_normal((9,)).astype(np.float32)
+        ad[f"gp{t}"], ad[f"gq{t}"] = pa.grad.copy(), pg.grad.copy()
+        opt.step()
+        ad[f"p{t + 1}"], ad[f"q{t + 1}"] = pa.data.copy(), pg.data.copy()
+    out["adamw"] = ad
     # ---- NumPy's own narrowing / widening on the edge block (the reference's cast primitive)
     e = workloads.edge_block_f32()
     with np.errstate(all="ignore"):

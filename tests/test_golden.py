@@ -101,3 +101,15 @@ def test_mlp_step_config_sampled_vectors():
         assert close(r["grads"][i].ravel()[idx], g[f"grad{i}"], 1e-4), i
         assert close(r["params"][i].ravel()[idx], g[f"new{i}"], 1e-6), i
         assert abs(r["grads"][i].astype(np.float64).sum() - float(g[f"gsum{i}"])) <= 1e-4 * (1 + abs(float(g[f"gsum{i}"])))
+
+
+def test_adamw_three_steps_bit_exact():
+    g = load("adamw")
+    p, q = g["p0"], g["q0"]
+    mp = vp = np.zeros_like(p)
+    mq = vq = np.zeros_like(q)
+    for t in range(3):
+        p, mp, vp = o.adamw_step(p, g[f"gp{t}"], mp, vp, t + 1, 1e-3, wd=1e-2)
+        q, mq, vq = o.adamw_step(q, g[f"gq{t}"], mq, vq, t + 1, 1e-3, wd=1e-2, decay=False)
+        assert np.array_equal(p.view(np.uint32), g[f"p{t + 1}"].view(np.uint32))
+        assert np.array_equal(q.view(np.uint32), g[f"q{t + 1}"].view(np.uint32))

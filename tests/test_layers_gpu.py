@@ -328,3 +328,15 @@ def test_sequential_of_gpu_layers_runs_the_reference_loop(gpu):
     opt.step()
     _check_step((logits, loss, grads, [p.data for p in model.parameters()]), load("mlp_small"), sampled=False)
     assert len(model.parameters()) == 6
+
+
+def test_adamw_bit_exact_against_reference_vectors(gpu):
+    g = load("adamw")
+    p, q = nb.Parameters(g["p0"].copy()), nb.Parameters(g["q0"].copy())
+    q.name = "gamma"
+    opt = nb.AdamW([p, q], lr=1e-3, weight_decay=1e-2, device=gpu)
+    for t in range(3):
+        p.grad, q.grad = g[f"gp{t}"].copy(), g[f"gq{t}"].copy()
+        opt.step()
+        assert np.array_equal(p.data.view(np.uint32), g[f"p{t + 1}"].view(np.uint32)), t
+        assert np.array_equal(q.data.view(np.uint32), g[f"q{t + 1}"].view(np.uint32)), t
