@@ -169,6 +169,17 @@ nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf16, const ui
                           nvq_dtype w_fmt, const float* d_w_scales, const float* d_bias,
                           size_t M, size_t N, size_t K, void* d_workspace, size_t workspace_bytes,
                           int device, void* stream);
+/* W8A8 VARIANT (outside the 1e-2 parity bound; offered for throughput, labelled as such):
+ * the bf16 activations are quantised to E4M3 per row (scale_m = amax_m / 448) inside the call and
+ * the contraction runs as FP8 x FP8 (tcgen05 kind::f8f6f4), Y = bf16(sx_m * sw_n * sum + b_n).
+ * E4M3 weights only.  K % 16 == 0, N % 8 == 0.  Workspace: nvq_linear_w8a8_workspace_bytes(M, K)
+ * bytes, 256-byte aligned (activation codes and row scales). */
+nvq_status nvq_linear_w8a8_workspace_bytes(size_t M, size_t K, size_t* bytes);
+nvq_status nvq_linear_fwd_w8a8(uint16_t* d_y_bf16, const uint16_t* d_x_bf16, const uint8_t* d_wq,
+                               const float* d_w_scales, const float* d_bias, size_t M, size_t N,
+                               size_t K, void* d_workspace, size_t workspace_bytes, int device,
+                               void* stream);
+
 /* Backward of the quantised-weight Linear on the tensor cores (Linear.backward,
  * novann/layers/linear/linear.py:85-108, with the weight held as FP8 codes):
  *   dX (M x K fp32) = bf16(G) @ bf16(dequant(Wq) * s)      G: M x N fp32 gradient of the output

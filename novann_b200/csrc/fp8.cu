@@ -190,14 +190,19 @@ struct DequantOp {
 // ---- per-row (per output channel) quantisation of a weight matrix ----------------------
 //   s_r = amax_r / FMAX (1 when the row is all zero);  q = cvt_sat_rne(w * (FMAX / amax_r))
 // One block per row: block-wide amax, then the row is read again (from L1/L2) and converted.
-template <int FMT>
+__device__ __forceinline__ float load_as_f32(const float* p, size_t i) { return p[i]; }
+__device__ __forceinline__ float load_as_f32(const uint16_t* p, size_t i) {   // bf16 bits
+    return __uint_as_float((uint32_t)p[i] << 16);
+}
+
+template <int FMT, class T>
 __global__ void __launch_bounds__(256)
 quantize_rows_kernel(uint8_t* __restrict__ dst, float* __restrict__ scales,
-                     const float* __restrict__ src, size_t cols) {
-    const float* row = src + (size_t)blockIdx.x * cols;
+                     const T* __restrict__ src, size_t cols) {
+    const T* row = src + (size_t)blockIdx.x * cols;
     uint8_t* out = dst + (size_t)blockIdx.x * cols;
     float m = 0.f;
-    for (size_t i = threadIdx.x; i < cols; i += blockDim.x) m = fmaxf(m, fabsf(row[i]));
+    for (size_t i = threadIdx.x; i < cols; i += blockDim.x) m = fmaxf(m, fabsf(load_as_f32(row, i)));
     unsigned int b = __float_as_uint(m);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) b = max(b, __shfl_xor_sync(0xFFFFFFFFu, b, o));
@@ -218,7 +223,84 @@ quantize_rows_kernel(uint8_t* __restrict__ dst, float* __restrict__ scales,
     __syncthreads();
     const uint32_t invu = __float_as_uint(s_inv);
     for (size_t i = threadIdx.x; i < cols; i += blockDim.x)
-        out[i] = (uint8_t)spec_f32_to_fp8<FMT>(spec_mul_bits(__float_as_uint(row[i]), invu));
+        out[i] = (uint8_t)spec_f32_to_fp8<FMT>(spec_mul_bits(__float_as_uint(load_as_f32(row, i)), invu));
+}
+
+// Fast per-row E4M3 quantisation of bf16 rows (the activations of the W8A8 Linear): one block
+// per row, 8 values per 16-byte load, hardware converters.  The row maximum is taken on the bit
+// patterns; a row that holds inf / NaN (pattern >= 0x7f80), or whose reciprocal scale overflows,
+// is redone lane by lane with the written rules (NaN ignored by the maximum, integer conversion).
+__global__ void __launch_bounds__(256)
+quantize_rows_bf16_fast_kernel(uint8_t* __restrict__ dst, float* __restrict__ scales,
+                               const uint16_t* __restrict__ src, size_t cols) {
+    const uint16_t* row = src + (size_t)blockIdx.x * cols;
+    uint8_t* out = dst + (size_t)blockIdx.x * cols;
+    const size_t chunks = cols / 8;
+    __shared__ unsigned int warp_max[8];
+    __shared__ float s_inv;
+    __shared__ int s_slow;
+    uint32_t m2 = 0u;
+    for (size_t c = threadIdx.x; c < chunks; c += blockDim.x) {
+        uint4 v = *(const uint4*)(row + c * 8);
+        m2 = __vmaxu2(m2, v.x & 0x7FFF7FFFu);
+        m2 = __vmaxu2(m2, v.y & 0x7FFF7FFFu);
+        m2 = __vmaxu2(m2, v.z & 0x7FFF7FFFu);
+        m2 = __vmaxu2(m2, v.w & 0x7FFF7FFFu);
+    }
+    unsigned int b = max(m2 & 0xFFFFu, m2 >> 16);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) b = max(b, __shfl_xor_sync(0xFFFFFFFFu, b, o));
+    if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = b;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; w++) b = max(b, warp_max[w]);
+        float amax = __uint_as_float(b << 16), scale = 1.f, inv = 1.f;
+        if (amax != 0.f) {
+            scale = __fdiv_rn(amax, 448.0f);
+            inv = __fdiv_rn(448.0f, amax);
+        }
+        s_slow = (b >= 0x7F80u) || (__float_as_uint(inv) >= 0x7F800000u);
+        scales[blockIdx.x] = scale;
+        s_inv = inv;
+    }
+    __syncthreads();
+    if (!s_slow) {
+        const float inv = s_inv;
+        for (size_t c = threadIdx.x; c < chunks; c += blockDim.x) {
+            uint4 v = *(const uint4*)(row + c * 8);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            uint32_t q[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                q[i] = cvt_fp8x2<NVQ_E4M3>(__fmul_rn(__uint_as_float(w[i] << 16), inv),
+                                           __fmul_rn(__uint_as_float(w[i] & 0xFFFF0000u), inv));
+            *(uint2*)(out + c * 8) = make_uint2(q[0] | (q[1] << 16), q[2] | (q[3] << 16));
+        }
+        return;
+    }
+    // slow path: the written rules
+    float m = 0.f;
+    for (size_t i = threadIdx.x; i < cols; i += blockDim.x) m = fmaxf(m, fabsf(load_as_f32(row, i)));
+    b = __float_as_uint(m);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) b = max(b, __shfl_xor_sync(0xFFFFFFFFu, b, o));
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = b;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; w++) b = max(b, warp_max[w]);
+        float amax = __uint_as_float(b), scale = 1.f, inv = 1.f;
+        if (amax != 0.f) {
+            scale = __fdiv_rn(amax, 448.0f);
+            inv = __fdiv_rn(448.0f, amax);
+        }
+        scales[blockIdx.x] = scale;
+        s_inv = inv;
+    }
+    __syncthreads();
+    const uint32_t invu = __float_as_uint(s_inv);
+    for (size_t i = threadIdx.x; i < cols; i += blockDim.x)
+        out[i] = (uint8_t)spec_f32_to_fp8<NVQ_E4M3>(spec_mul_bits(__float_as_uint(load_as_f32(row, i)), invu));
 }
 
 nvq_status launch_amax(const float* d_src, size_t n, float* d_amax, int device, cudaStream_t st) {
@@ -325,9 +407,20 @@ extern "C" nvq_status nvq_quantize_fp8_rows(uint8_t* d_dst, float* d_scales, con
     if (s != NVQ_OK) return s;
     cudaStream_t st = (cudaStream_t)stream;
     if (fmt == NVQ_E4M3)
-        quantize_rows_kernel<NVQ_E4M3><<<(unsigned)rows, 256, 0, st>>>(d_dst, d_scales, d_src, cols);
+        quantize_rows_kernel<NVQ_E4M3, float><<<(unsigned)rows, 256, 0, st>>>(d_dst, d_scales, d_src, cols);
     else
-        quantize_rows_kernel<NVQ_E5M2><<<(unsigned)rows, 256, 0, st>>>(d_dst, d_scales, d_src, cols);
+        quantize_rows_kernel<NVQ_E5M2, float><<<(unsigned)rows, 256, 0, st>>>(d_dst, d_scales, d_src, cols);
+    NVQ_LAUNCHED();
+    return NVQ_OK;
+}
+
+// the same rule for bf16 input rows (activations of the quantised Linear)
+nvq_status nvq_quantize_e4m3_rows_bf16(uint8_t* d_dst, float* d_scales, const uint16_t* d_src,
+                                       size_t rows, size_t cols, cudaStream_t st) {
+    if (cols % 8 == 0 && nvq_aligned(d_src, 16) && nvq_aligned(d_dst, 8))
+        quantize_rows_bf16_fast_kernel<<<(unsigned)rows, 256, 0, st>>>(d_dst, d_scales, d_src, cols);
+    else
+        quantize_rows_kernel<NVQ_E4M3, uint16_t><<<(unsigned)rows, 256, 0, st>>>(d_dst, d_scales, d_src, cols);
     NVQ_LAUNCHED();
     return NVQ_OK;
 }

@@ -271,7 +271,7 @@ nvq_status nvq_status_word(int device, int** dev_ptr) {
 }
 
 nvq_status nvq_make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
-                            uint32_t box_rows, uint32_t box_cols, int elem_bytes) {
+                            uint32_t box_rows, uint32_t box_cols, int elem_bytes, int swizzle128) {
     if (!g_encode) {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult q;
@@ -293,7 +293,7 @@ nvq_status nvq_make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, u
     // (raw codes read by converter warps) are stored linearly
     CUresult r = g_encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          elem_bytes == 2 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                          swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) NVQ_FAIL(NVQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
     return NVQ_OK;
@@ -303,9 +303,9 @@ nvq_status nvq_linear_launch_single(uint16_t* d_y, const uint16_t* d_x, const ui
                                     const float* d_scales, const float* d_bias, size_t M, size_t N,
                                     size_t K, int out_f32, int device, cudaStream_t st) {
     CUtensorMap map_a, map_b;
-    nvq_status s = nvq_make_tmap_2d(&map_a, d_x, M, K, BM, BK, 2);
+    nvq_status s = nvq_make_tmap_2d(&map_a, d_x, M, K, BM, BK, 2, 1);
     if (s != NVQ_OK) return s;
-    s = nvq_make_tmap_2d(&map_b, d_w_bf16, N, K, BN / 2, BK, 2);
+    s = nvq_make_tmap_2d(&map_b, d_w_bf16, N, K, BN / 2, BK, 2, 1);
     if (s != NVQ_OK) return s;
     static bool attr_set[64];
     if (!attr_set[device]) {
@@ -316,6 +316,7 @@ nvq_status nvq_linear_launch_single(uint16_t* d_y, const uint16_t* d_x, const ui
     p.y = d_y;
     p.out_f32 = out_f32;
     p.wq = nullptr;
+    p.row_scales = nullptr;
     p.scales = d_scales;
     p.bias = d_bias;
     p.M = (int)M;
@@ -485,4 +486,38 @@ extern "C" nvq_status nvq_linear_fwd_static(uint16_t* d_y_bf16, const uint16_t* 
     t_status_override = false;
     t_status_override_ptr = nullptr;
     return s;
+}
+
+// ---------------------------------------------------------------- W8A8 variant
+nvq_status nvq_quantize_e4m3_rows_bf16(uint8_t* d_dst, float* d_scales, const uint16_t* d_src,
+                                       size_t rows, size_t cols, cudaStream_t st);
+
+extern "C" nvq_status nvq_linear_w8a8_workspace_bytes(size_t M, size_t K, size_t* bytes) {
+    NVQ_REQUIRE(bytes, "null out pointer");
+    *bytes = (M * K + 255) / 256 * 256 + M * sizeof(float);
+    return NVQ_OK;
+}
+
+extern "C" nvq_status nvq_linear_fwd_w8a8(uint16_t* d_y_bf16, const uint16_t* d_x_bf16,
+                                          const uint8_t* d_wq, const float* d_w_scales,
+                                          const float* d_bias, size_t M, size_t N, size_t K,
+                                          void* d_workspace, size_t workspace_bytes, int device,
+                                          void* stream) {
+    NVQ_REQUIRE(d_y_bf16 && d_x_bf16 && d_wq && d_w_scales && M > 0 && N > 0 && K > 0,
+                "nvq_linear_fwd_w8a8: bad argument");
+    NVQ_REQUIRE(K % 16 == 0 && N % 8 == 0, "nvq_linear_fwd_w8a8: K (%zu) must be a multiple of 16, N (%zu) of 8", K, N);
+    NVQ_REQUIRE(nvq_aligned(d_y_bf16, 32) && nvq_aligned(d_wq, 16), "nvq_linear_fwd_w8a8: Y 32-byte, Wq 16-byte aligned");
+    size_t need = 0;
+    nvq_linear_w8a8_workspace_bytes(M, K, &need);
+    NVQ_REQUIRE(d_workspace && workspace_bytes >= need && nvq_aligned(d_workspace, 256),
+                "nvq_linear_fwd_w8a8: workspace of %zu bytes (256-byte aligned) required", need);
+    NVQ_REQUIRE(M < (1u << 31) && N < (1u << 31) && K < (1u << 31), "nvq_linear_fwd_w8a8: dimension too large");
+    nvq_status s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    cudaStream_t st = (cudaStream_t)stream;
+    uint8_t* xq = (uint8_t*)d_workspace;
+    float* xs = (float*)((char*)d_workspace + (M * K + 255) / 256 * 256);
+    s = nvq_quantize_e4m3_rows_bf16(xq, xs, d_x_bf16, M, K, st);
+    if (s != NVQ_OK) return s;
+    return nvq_linear_launch_pair_w8a8(d_y_bf16, xq, xs, d_wq, d_w_scales, d_bias, M, N, K, device, st);
 }

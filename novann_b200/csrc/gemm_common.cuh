@@ -8,6 +8,7 @@ struct LinearParams {
     int out_f32;
     const uint8_t* wq;     // fused kernels: the weight codes (N x K bytes); else unused
     const float* scales;   // N per-output-channel factors or nullptr (= 1)
+    const float* row_scales;  // M per-row factors (quantised activations) or nullptr
     const float* bias;     // N or nullptr (= 0)
     int M, N, K;
     int m_blocks, n_blocks;   // in units of the kernel's own tile
@@ -35,6 +36,11 @@ nvq_status nvq_linear_launch_pair(uint16_t* d_y, const uint16_t* d_x, const uint
 nvq_status nvq_linear_launch_pair_fused(uint16_t* d_y, const uint16_t* d_x, const uint8_t* d_wq,
                                         nvq_dtype fmt, const float* d_scales, const float* d_bias,
                                         size_t M, size_t N, size_t K, int out_f32, int device, cudaStream_t st);
+
+nvq_status nvq_linear_launch_pair_w8a8(uint16_t* d_y, const uint8_t* d_xq, const float* d_x_scales,
+                                       const uint8_t* d_wq, const float* d_w_scales,
+                                       const float* d_bias, size_t M, size_t N, size_t K, int device,
+                                       cudaStream_t st);
 
 #ifdef __CUDACC__
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {

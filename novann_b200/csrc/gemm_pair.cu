@@ -34,11 +34,17 @@ constexpr int MAX_STAGES = 6;
 
 // FUSED = 0: B comes expanded (bf16) from a workspace.  FUSED = NVQ_E4M3 / NVQ_E5M2: B comes as
 // codes and is expanded in shared memory by four extra warps.
+// FUSED = kW8A8: both operands arrive as E4M3 codes (activations quantised per row beforehand)
+// and the MMAs are kind::f8f6f4: 128 codes per 128-byte row, so a k-block spans 128 elements.
+constexpr int kW8A8 = -8;
 template <int FUSED>
 struct Cfg {
-    static constexpr int STAGES = FUSED ? 5 : 6;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + (FUSED ? RAW_BYTES : 0);
-    static constexpr int THREADS = FUSED ? 448 : 192;   // fused: + 8 converter warps
+    static constexpr bool CONV = FUSED > 0;
+    static constexpr bool F8 = FUSED == kW8A8;
+    static constexpr int BKE = F8 ? 128 : BK;           // elements of K per k-block
+    static constexpr int STAGES = CONV ? 5 : 6;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + (CONV ? RAW_BYTES : 0);
+    static constexpr int THREADS = CONV ? 448 : 192;    // fused: + 8 converter warps
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 8192;
 };
 
@@ -94,6 +100,9 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                       const LinearParams p) {
     constexpr int STAGES = Cfg<FUSED>::STAGES;
     constexpr int STAGE_BYTES = Cfg<FUSED>::STAGE_BYTES;
+    constexpr bool CONV = Cfg<FUSED>::CONV;
+    constexpr bool F8 = Cfg<FUSED>::F8;
+    constexpr int BKE = Cfg<FUSED>::BKE;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = tc::smem_u32(smem_raw);
     const uint32_t tiles = (raw + 1023u) & ~1023u;
@@ -101,14 +110,14 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = tc::cluster_ctarank();
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-    const int num_kb = (p.K + BK - 1) / BK;
+    const int num_kb = (p.K + BKE - 1) / BKE;
     volatile int* abort_flag = &sh->abort_flag;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             // fused: the leader's full barrier also collects one arrival per converter warp of
             // both CTAs (8 + 8) on top of the producer's
-            tc::mbar_init(tc::smem_u32(&sh->full[s]), FUSED ? 17 : 1);
+            tc::mbar_init(tc::smem_u32(&sh->full[s]), CONV ? 17 : 1);
             tc::mbar_init(tc::smem_u32(&sh->empty[s]), 1);
             tc::mbar_init(tc::smem_u32(&sh->raw_full[s]), 1);
         }
@@ -150,7 +159,7 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     if (!ok) break;
                     const uint32_t dst = tiles + stage * STAGE_BYTES;
                     const uint32_t lead_full = tc::mapa(tc::smem_u32(&sh->full[stage]), 0);
-                    if constexpr (FUSED) {
+                    if constexpr (CONV) {
                         if (rank == 0)   // the leader expects the X bytes of both CTAs
                             tc::mbar_arrive_expect_tx(tc::smem_u32(&sh->full[stage]), 2 * A_BYTES);
                         tc::tma_load_2d_pair(dst, &map_a, lead_full, kb * BK, m0);
@@ -164,10 +173,10 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                         if (rank == 0)   // the leader expects the bytes of both CTAs
                             tc::mbar_arrive_expect_tx(tc::smem_u32(&sh->full[stage]),
                                                       2 * (A_BYTES + rows_b * BK * 2));
-                        tc::tma_load_2d_pair(dst, &map_a, lead_full, kb * BK, m0);
-                        tc::tma_load_2d_pair(dst + A_BYTES, &map_b, lead_full, kb * BK, n0);
+                        tc::tma_load_2d_pair(dst, &map_a, lead_full, kb * BKE, m0);
+                        tc::tma_load_2d_pair(dst + A_BYTES, &map_b, lead_full, kb * BKE, n0);
                         if (rows_b == 128)
-                            tc::tma_load_2d_pair(dst + A_BYTES + B_BYTES / 2, &map_b, lead_full, kb * BK, n0 + 64);
+                            tc::tma_load_2d_pair(dst + A_BYTES + B_BYTES / 2, &map_b, lead_full, kb * BKE, n0 + 64);
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -182,7 +191,8 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             for (int t = pair; t < p.num_items && ok; t += num_pairs, it++) {
                 const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
                 const TileRef tr = tile_ref(p, t);
-                const uint32_t idesc = tc::idesc_f16(BM, tr.is_half ? BN / 2 : BN, 1, 1);
+                const uint32_t idesc = F8 ? tc::idesc_f16(BM, tr.is_half ? BN / 2 : BN, 0, 0)   // E4M3 x E4M3
+                                          : tc::idesc_f16(BM, tr.is_half ? BN / 2 : BN, 1, 1);  // bf16 x bf16
                 ok = tc::mbar_wait(tc::smem_u32(&sh->tmem_empty[acc]), acc_phase ^ 1, abort_flag, ERR_MMA_TMEM);
                 if (!ok) break;
                 tc::tc_fence_after();
@@ -195,17 +205,21 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     const uint64_t a_desc = tc::smem_desc_k_sw128(a_addr);
                     const uint64_t b_desc = tc::smem_desc_k_sw128(a_addr + A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; k++)
-                        tc::tc_mma_f16_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+                    for (int k = 0; k < BK / UMMA_K; k++) {   // four 32-byte k-steps either way
+                        if constexpr (F8)
+                            tc::tc_mma_f8_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+                        else
+                            tc::tc_mma_f16_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+                    }
                     tc::tc_commit_pair(tc::smem_u32(&sh->empty[stage]), 3);   // both CTAs' slots
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
                 if (ok) tc::tc_commit_pair(tc::smem_u32(&sh->tmem_full[acc]), 3);
             }
         }
-    } else if (FUSED && warp >= 6) {
+    } else if (CONV && warp >= 6) {
         // ------------------------------------------------------------ converters (both CTAs)
-        if constexpr (FUSED != 0) {
+        if constexpr (CONV) {
             const int ct = threadIdx.x - 192;           // 0..255
             uint32_t stage = 0, phase = 0;
             bool ok = true;
@@ -287,8 +301,14 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 uint32_t r[32];
                 tc::tmem_ld_32x32(taddr + c, r);
                 tc::tmem_ld_wait();
-                if (row < p.M)
+                if (row < p.M) {
+                    if (p.row_scales) {   // per-row activation scale (quantised activations)
+                        const float rs = p.row_scales[row];
+#pragma unroll
+                        for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__fmul_rn(__uint_as_float(r[j]), rs));
+                    }
                     store_row_chunk(p, r, &sh->scale[acc][c], &sh->bias[acc][c], row, n0 + c, vec32);
+                }
             }
             tc::tc_fence_before();
             __syncwarp();
@@ -309,14 +329,20 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 }
 
 template <int FUSED>
-static nvq_status launch_pair(uint16_t* d_y, const uint16_t* d_x, const void* d_w,
+static nvq_status launch_pair(uint16_t* d_y, const void* d_x, const void* d_w,
                               const float* d_scales, const float* d_bias, size_t M, size_t N,
-                              size_t K, int out_f32, int device, cudaStream_t st) {
+                              size_t K, int out_f32, int device, cudaStream_t st,
+                              const float* row_scales = nullptr) {
     CUtensorMap map_a, map_b;
-    nvq_status s = nvq_make_tmap_2d(&map_a, d_x, M, K, 128, BK, 2);
+    constexpr bool F8 = Cfg<FUSED>::F8;
+    // operand tiles: 128-byte rows with the 128-byte swizzle (64 bf16 or 128 FP8 codes)
+    nvq_status s = F8 ? nvq_make_tmap_2d(&map_a, d_x, M, K, 128, 128, 1, 1)
+                      : nvq_make_tmap_2d(&map_a, d_x, M, K, 128, BK, 2, 1);
     if (s != NVQ_OK) return s;
     // fused: codes, 64-byte rows, no swizzle (the converters read them linearly)
-    s = FUSED ? nvq_make_tmap_2d(&map_b, d_w, N, K, 64, BK, 1) : nvq_make_tmap_2d(&map_b, d_w, N, K, 64, BK, 2);
+    s = F8 ? nvq_make_tmap_2d(&map_b, d_w, N, K, 64, 128, 1, 1)
+           : (FUSED ? nvq_make_tmap_2d(&map_b, d_w, N, K, 64, BK, 1, 0)
+                    : nvq_make_tmap_2d(&map_b, d_w, N, K, 64, BK, 2, 1));
     if (s != NVQ_OK) return s;
     static bool attr_set[64];
     if (!attr_set[device]) {
@@ -327,7 +353,8 @@ static nvq_status launch_pair(uint16_t* d_y, const uint16_t* d_x, const void* d_
     LinearParams p;
     p.y = d_y;
     p.out_f32 = out_f32;
-    p.wq = FUSED ? (const uint8_t*)d_w : nullptr;
+    p.wq = nullptr;
+    p.row_scales = row_scales;
     p.scales = d_scales;
     p.bias = d_bias;
     p.M = (int)M;
@@ -375,4 +402,12 @@ nvq_status nvq_linear_launch_pair_fused(uint16_t* d_y, const uint16_t* d_x, cons
     if (fmt == NVQ_E4M3)
         return launch_pair<NVQ_E4M3>(d_y, d_x, d_wq, d_scales, d_bias, M, N, K, out_f32, device, st);
     return launch_pair<NVQ_E5M2>(d_y, d_x, d_wq, d_scales, d_bias, M, N, K, out_f32, device, st);
+}
+
+// W8A8: X and W both E4M3 codes, per-row and per-channel scales applied in the epilogue
+nvq_status nvq_linear_launch_pair_w8a8(uint16_t* d_y, const uint8_t* d_xq, const float* d_x_scales,
+                                       const uint8_t* d_wq, const float* d_w_scales,
+                                       const float* d_bias, size_t M, size_t N, size_t K, int device,
+                                       cudaStream_t st) {
+    return launch_pair<kW8A8>(d_y, d_xq, d_wq, d_w_scales, d_bias, M, N, K, 0, device, st, d_x_scales);
 }

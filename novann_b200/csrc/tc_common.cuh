@@ -118,6 +118,16 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uin
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
 }
+// the same for 8-bit float operands (kind::f8f6f4; 32 codes per k-step)
+__device__ __forceinline__ void tc_mma_f8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                               uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
 // 32 lanes x 32 consecutive fp32 columns: thread t of the warp gets lane (base + t)
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t* r) {
     asm volatile(
@@ -230,7 +240,8 @@ __host__ __device__ constexpr uint32_t idesc_f16(uint32_t m, uint32_t n, uint32_
 #endif  // __CUDACC__
 
 // ---- host: tensor-map encoding through the driver entry point (no libcuda link) ----
-// 2-D row-major tensor of `rows` x `cols` elements of `elem_bytes`; box = box_rows x
-// box_cols with the 128-byte swizzle (box_cols * elem_bytes must be 128).
+// 2-D row-major tensor of `rows` x `cols` elements of `elem_bytes` (2 = bf16, 1 = bytes);
+// box = box_rows x box_cols, stored with the 128-byte swizzle (box_cols * elem_bytes must then
+// be 128) or linearly.
 nvq_status nvq_make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
-                            uint32_t box_rows, uint32_t box_cols, int elem_bytes);
+                            uint32_t box_rows, uint32_t box_cols, int elem_bytes, int swizzle128);

@@ -236,3 +236,34 @@ def linear_q_bwd_host(grad, x, wq, w_scales, fmt: str = "e4m3", with_bias: bool 
     return (o_dw.to_numpy(np.float32, (n, k)),
             o_db.to_numpy(np.float32, (1, n)) if with_bias else None,
             o_dx.to_numpy(np.float32, (m, k)))
+
+
+def linear_w8a8_device(y: DeviceBuffer, x: DeviceBuffer, wq: DeviceBuffer, w_scales: DeviceBuffer,
+                       bias: DeviceBuffer | None, m: int, n: int, k: int, workspace: DeviceBuffer,
+                       stream=None) -> None:
+    """W8A8 variant: activations quantised to E4M3 per row inside the call, FP8 x FP8 MMAs."""
+    check(lib().nvq_linear_fwd_w8a8(y.at(0), x.at(0), wq.at(0), w_scales.at(0),
+                                    bias.at(0) if bias is not None else None, m, n, k,
+                                    workspace.at(0), workspace.nbytes, x.device, _sptr(stream)))
+
+
+def linear_w8a8_workspace_bytes(m: int, k: int) -> int:
+    out = C.c_size_t()
+    check(lib().nvq_linear_w8a8_workspace_bytes(m, k, C.byref(out)))
+    return out.value
+
+
+def linear_w8a8_host(x_bf16_bits, wq, w_scales, bias, device: int = 0) -> np.ndarray:
+    x = np.ascontiguousarray(x_bf16_bits, np.uint16)
+    m, k = x.shape
+    n = wq.shape[0]
+    dx = DeviceBuffer.from_numpy(x, device)
+    dw = DeviceBuffer.from_numpy(np.ascontiguousarray(wq, np.uint8), device)
+    ds = DeviceBuffer.from_numpy(_f32(w_scales), device)
+    db = DeviceBuffer.from_numpy(_f32(bias), device) if bias is not None else None
+    dy = DeviceBuffer(m * n * 2, device)
+    ws = DeviceBuffer(linear_w8a8_workspace_bytes(m, k), device)
+    linear_w8a8_device(dy, dx, dw, ds, db, m, n, k, ws)
+    device_sync(device)
+    check_device_errors(device)
+    return dy.to_numpy(np.uint16, (m, n))

@@ -135,3 +135,24 @@ def test_bounded_wait_gives_up_and_reports(gpu):
     F.check_device_errors(gpu)                       # flag was cleared by the read
     err, _, _ = _run_fp8(gpu, 256, 256, 256)
     assert err <= 2.0 ** -7
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 128), (512, 768, 1024), (200, 264, 400), (4096, 4096, 4096)])
+def test_linear_w8a8_variant(gpu, m, n, k):
+    """The labelled W8A8 variant (activations quantised to E4M3 per row): exact against an oracle
+    that quantises the same way (the contraction of two FP8 code matrices is exact in fp32 up to
+    accumulation order), and its distance from the bf16-activation result is reported - it is the
+    reason this variant sits outside the 1e-2 parity bound."""
+    xb, w, b = workloads.linear_inputs(m, n, k, seed=m)
+    wq, sc = o.quantize_weight_per_channel(w, "e4m3")
+    y = o.bf16_bits_to_f32(F.linear_w8a8_host(xb, wq, sc, b, gpu))
+    x = o.bf16_bits_to_f32(xb)
+    xq, xs = o.quantize_weight_per_channel(x, "e4m3")          # same per-row rule
+    rows = slice(None) if m <= 512 else np.arange(0, m, 97)
+    acc = o.E4M3_TABLE[xq[rows]].astype(np.float64) @ o.E4M3_TABLE[wq].astype(np.float64).T
+    ref = (acc * xs[rows, None]).astype(np.float32) * sc[None, :] + b
+    assert o.max_abs_rel(y[rows], ref) <= 2.0 ** -7
+    full = o.bf16_bits_to_f32(o.linear_fwd_qweight(xb[rows], wq, sc, b, "e4m3")[0])
+    dist = o.max_abs_rel(y[rows], full)
+    assert dist <= 8e-2                                        # sanity: E4M3 activation error
+    print(f"W8A8 vs bf16-activation result, {m}x{n}x{k}: max-abs-rel {dist:.4f}")
