@@ -35,32 +35,42 @@ struct GemmArgs {
 
 constexpr int TK = 64;   // k depth of one staged chunk
 
-// element e (0..2047) of a TS x TK tile -> (row-in-tile, k-in-chunk); the index that has unit
-// stride in memory runs fastest across threads so global loads coalesce
+// element e of a T x TK tile -> (row-in-tile, k-in-chunk); the index that has unit stride in
+// memory runs fastest across threads so global loads coalesce
+template <int T>
 __device__ __forceinline__ void tile_coord(int e, bool k_contiguous, int& r, int& l) {
     if (k_contiguous) { l = e & (TK - 1); r = e >> 6; }
-    else              { r = e & (TS - 1); l = e >> 5; }
+    else              { r = e & (T - 1); l = e / T; }
 }
 
+// T x T output tile per 256-thread block: T = 32 (2 x 2 outputs per thread) for large outputs,
+// T = 16 (one output per thread) when the output is so small that 32 x 32 tiles would leave
+// most SMs idle - these GEMMs are latency-bound, so more blocks means more loads in flight.
+template <int T>
 __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
-    // double-buffered tiles: chunk c+1 is fetched into registers while chunk c is multiplied,
-    // so the global-memory latency of the (few, small) blocks overlaps the FMA loop
-    __shared__ float As[2][TK][TS + 1];   // [buf][l][i]
-    __shared__ float Bs[2][TK][TS + 1];   // [buf][l][j]
-    const int i0 = blockIdx.y * TS, j0 = blockIdx.x * TS;
-    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;   // 16 x 16 threads, 2 x 2 outputs each
+    constexpr int R = T / 16;                 // outputs per thread per dimension
+    constexpr int LD = T * TK / 256;          // tile elements each thread stages per chunk
+    // double-buffered tiles: chunk c+1 is fetched into registers while chunk c is multiplied
+    __shared__ float As[2][TK][T + 1];   // [buf][l][i]
+    __shared__ float Bs[2][TK][T + 1];   // [buf][l][j]
+    const int i0 = blockIdx.y * T, j0 = blockIdx.x * T;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     const bool a_kc = g.a_sl == 1, b_kc = g.b_sl == 1;
-    float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-    float ra[8], rb[8];
+    float acc[R][R];
+#pragma unroll
+    for (int u = 0; u < R; u++)
+#pragma unroll
+        for (int v = 0; v < R; v++) acc[u][v] = 0.f;
+    float ra[LD], rb[LD];
     auto fetch = [&](int l0) {
 #pragma unroll
-        for (int r = 0; r < 8; r++) {
+        for (int r = 0; r < LD; r++) {
             int e = threadIdx.x + 256 * r, ii, ll;
-            tile_coord(e, a_kc, ii, ll);
+            tile_coord<T>(e, a_kc, ii, ll);
             int i = i0 + ii, l = l0 + ll;
             ra[r] = (i < g.I && l < g.L) ? g.a[i * g.a_si + l * g.a_sl] : 0.f;
             int jj;
-            tile_coord(e, b_kc, jj, ll);
+            tile_coord<T>(e, b_kc, jj, ll);
             int j = j0 + jj;
             l = l0 + ll;
             rb[r] = (j < g.J && l < g.L) ? g.b[l * g.b_sl + j * g.b_sj] : 0.f;
@@ -68,11 +78,11 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
     };
     auto stash = [&](int buf) {
 #pragma unroll
-        for (int r = 0; r < 8; r++) {
+        for (int r = 0; r < LD; r++) {
             int e = threadIdx.x + 256 * r, ii, ll;
-            tile_coord(e, a_kc, ii, ll);
+            tile_coord<T>(e, a_kc, ii, ll);
             As[buf][ll][ii] = ra[r];
-            tile_coord(e, b_kc, ii, ll);
+            tile_coord<T>(e, b_kc, ii, ll);
             Bs[buf][ll][ii] = rb[r];
         }
     };
@@ -85,21 +95,22 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
         if (more) fetch(l0 + TK);
 #pragma unroll 16
         for (int l = 0; l < TK; l++) {
-            float a0 = As[buf][l][ty], a1 = As[buf][l][ty + 16];
-            float b0 = Bs[buf][l][tx], b1 = Bs[buf][l][tx + 16];
-            acc[0][0] = fmaf(a0, b0, acc[0][0]);
-            acc[0][1] = fmaf(a0, b1, acc[0][1]);
-            acc[1][0] = fmaf(a1, b0, acc[1][0]);
-            acc[1][1] = fmaf(a1, b1, acc[1][1]);
+            float a[R], b[R];
+#pragma unroll
+            for (int u = 0; u < R; u++) { a[u] = As[buf][l][ty + 16 * u]; b[u] = Bs[buf][l][tx + 16 * u]; }
+#pragma unroll
+            for (int u = 0; u < R; u++)
+#pragma unroll
+                for (int v = 0; v < R; v++) acc[u][v] = fmaf(a[u], b[v], acc[u][v]);
         }
         if (more) stash(buf ^ 1);
         __syncthreads();
         buf ^= 1;
     }
 #pragma unroll
-    for (int u = 0; u < 2; u++) {
+    for (int u = 0; u < R; u++) {
 #pragma unroll
-        for (int v = 0; v < 2; v++) {
+        for (int v = 0; v < R; v++) {
             int i = i0 + ty + 16 * u, j = j0 + tx + 16 * v;
             if (i >= g.I || j >= g.J) continue;
             float val = acc[u][v];
@@ -119,26 +130,36 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
 
 nvq_status launch_gemm(const GemmArgs& g, cudaStream_t st) {
     if (g.I <= 0 || g.J <= 0) return NVQ_OK;
-    dim3 grid((g.J + TS - 1) / TS, (g.I + TS - 1) / TS);
-    gemm_f32_kernel<<<grid, 256, 0, st>>>(g);
+    const long long big_blocks = (long long)((g.J + 31) / 32) * ((g.I + 31) / 32);
+    if (big_blocks >= 148) {
+        dim3 grid((g.J + 31) / 32, (g.I + 31) / 32);
+        gemm_f32_kernel<32><<<grid, 256, 0, st>>>(g);
+    } else {
+        dim3 grid((g.J + 15) / 16, (g.I + 15) / 16);
+        gemm_f32_kernel<16><<<grid, 256, 0, st>>>(g);
+    }
     NVQ_LAUNCHED();
     return NVQ_OK;
 }
 
-// column sums of an M x N matrix: out[n] = sum_m g[m, n].  Eight interleaved partial sums keep
-// eight loads in flight; they are combined pairwise at the end.
-__global__ void colsum_kernel(const float* __restrict__ g, float* __restrict__ out, int M, int N) {
-    int n = blockIdx.x * blockDim.x + threadIdx.x;
-    if (n >= N) return;
-    float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    int m = 0;
-    for (; m + 8 <= M; m += 8) {
+// column sums of an M x N matrix: out[n] = sum_m g[m, n].  A block covers 32 columns with 8
+// row groups; each thread adds its rows in order, the 8 partial sums are combined in order.
+__global__ void __launch_bounds__(256)
+colsum_kernel(const float* __restrict__ g, float* __restrict__ out, int M, int N) {
+    __shared__ float part[8][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int n = blockIdx.x * 32 + tx;
+    float s = 0.f;
+    if (n < N)
+        for (int m = ty; m < M; m += 8) s = __fadd_rn(s, g[(size_t)m * N + n]);
+    part[ty][tx] = s;
+    __syncthreads();
+    if (ty == 0 && n < N) {
+        float t = part[0][tx];
 #pragma unroll
-        for (int u = 0; u < 8; u++) s[u] = __fadd_rn(s[u], g[(size_t)(m + u) * N + n]);
+        for (int r = 1; r < 8; r++) t = __fadd_rn(t, part[r][tx]);
+        out[n] = t;
     }
-    for (; m < M; m++) s[0] = __fadd_rn(s[0], g[(size_t)m * N + n]);
-    out[n] = __fadd_rn(__fadd_rn(__fadd_rn(s[0], s[1]), __fadd_rn(s[2], s[3])),
-                       __fadd_rn(__fadd_rn(s[4], s[5]), __fadd_rn(s[6], s[7])));
 }
 
 __global__ void relu_kernel(float* __restrict__ out, float* __restrict__ mask,
@@ -400,7 +421,7 @@ extern "C" nvq_status nvq_linear_bwd_f32(float* d_dw, float* d_db, float* d_dx, 
         if (s != NVQ_OK) return s;
     }
     if (d_db) {
-        colsum_kernel<<<(N + 127) / 128, 128, 0, st>>>(d_g, d_db, M, N);
+        colsum_kernel<<<(N + 31) / 32, 256, 0, st>>>(d_g, d_db, M, N);
         NVQ_LAUNCHED();
     }
     if (d_dx) {   // dX[m,k] = sum_n G[m,n] W[n,k]

@@ -29,16 +29,17 @@ __device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {
 
 __device__ __forceinline__ uint32_t quant_word_fast(uint32_t w0, uint32_t w1, uint32_t w2,
                                                     uint32_t w3, float inv) {
-    // 8 bf16 values (four words) -> 8 codes (one word)
+    // 8 bf16 values (four words) -> 8 codes (one word): four converter results (one byte each)
+    // gathered with three byte permutes
     const uint32_t w[4] = {w0, w1, w2, w3};
-    uint32_t out = 0;
+    uint32_t q[4];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         float lo = __fmul_rn(__uint_as_float(w[i] << 16), inv);
         float hi = __fmul_rn(__uint_as_float(w[i] & 0xFFFF0000u), inv);
-        out |= cvt_e2m1x2(lo, hi) << (8 * i);
+        q[i] = cvt_e2m1x2(lo, hi);
     }
-    return out;
+    return __byte_perm(__byte_perm(q[0], q[1], 0x0040), __byte_perm(q[2], q[3], 0x0040), 0x5410);
 }
 
 __device__ __forceinline__ uint32_t quant_one_spec(uint32_t xu, uint32_t invu) {
