@@ -239,6 +239,16 @@ def measure_extras(dev, st, rank, world, dist, local):
                          "note": "bf16 activations x FP8 weight codes; weight expansion pass "
                                  "included; tcgen05 kind::f16 (a bf16-activation GEMM cannot "
                                  "exceed half of FP8 peak)"}
+    F.linear_expand_weight_device(ws, dw, "e4m3", None, nn, kk, stream=st)
+    t = timed(lambda: F.linear_expanded_device(dy, dxx, ws, dss, dbb, m, nn, kk, stream=st),
+              iters=20, do_flush=True)
+    F.check_device_errors(dev)
+    tfe = 2.0 * m * nn * kk / t / 1e9
+    out["linear_fp8_weight_expanded_once"] = {
+        "ms": t, "tflops_per_gpu": tfe,
+        "frac_of_measured_bf16_peak": tfe / peak_bf16 if peak_bf16 else None,
+        "note": "contraction alone: the codes were expanded to bf16 once, outside the call "
+                "(nvq_linear_expand_weight + nvq_linear_fwd_expanded; 2 bytes per weight kept)"}
     ws8 = DeviceBuffer(F.linear_w8a8_workspace_bytes(m, kk), dev)
     t = timed(lambda: F.linear_w8a8_device(dy, dxx, dw, dss, dbb, m, nn, kk, ws8, stream=st),
               iters=20, do_flush=True)

@@ -405,6 +405,39 @@ extern "C" nvq_status nvq_device_error_flag(int device, int* flag) {
     return NVQ_OK;
 }
 
+extern "C" nvq_status nvq_linear_expand_weight(uint16_t* d_wd_bf16, const uint8_t* d_wq,
+                                               nvq_dtype w_fmt, const float* d_w_scales, size_t N,
+                                               size_t K, int device, void* stream) {
+    NVQ_REQUIRE(d_wd_bf16 && d_wq && N > 0 && K > 0, "nvq_linear_expand_weight: bad argument");
+    NVQ_REQUIRE(nvq_aligned(d_wd_bf16, 32), "nvq_linear_expand_weight: destination must be 32-byte aligned");
+    nvq_status s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (w_fmt == NVQ_E2M1_B32) {
+        // block scales vary along K, so they are folded into the expanded weight:
+        // Wd = bf16(e2m1_value * scale_block); no per-channel factor is left
+        NVQ_REQUIRE(K % 32 == 0 && d_w_scales, "nvq_linear_fwd: K (%zu) must be a multiple of 32 for E2M1_B32", K);
+        return nvq_dequantize_fp4_b32(d_wd_bf16, d_wq, d_w_scales, N, K, device, stream);
+    }
+    NVQ_REQUIRE(w_fmt == NVQ_E4M3 || w_fmt == NVQ_E5M2, "nvq_linear_expand_weight: unsupported weight format %d", (int)w_fmt);
+    NVQ_REQUIRE((N * K) % 16 == 0 && nvq_aligned(d_wq, 16),
+                "nvq_linear_fwd: weight codes must be 16-byte aligned, N*K a multiple of 16");
+    return w_fmt == NVQ_E4M3 ? ew_launch(ExpandOp<NVQ_E4M3>{}, d_wq, d_wd_bf16, N * K, device, st, 16, 32)
+                             : ew_launch(ExpandOp<NVQ_E5M2>{}, d_wq, d_wd_bf16, N * K, device, st, 16, 32);
+}
+
+extern "C" nvq_status nvq_linear_fwd_expanded(uint16_t* d_y_bf16, const uint16_t* d_x_bf16,
+                                              const uint16_t* d_wd_bf16, const float* d_chan_scales,
+                                              const float* d_bias, size_t M, size_t N, size_t K,
+                                              int device, void* stream) {
+    NVQ_REQUIRE(d_y_bf16 && d_x_bf16 && d_wd_bf16 && M > 0 && N > 0 && K > 0,
+                "nvq_linear_fwd_expanded: bad argument");
+    nvq_status s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    return nvq_linear_bf16_launch(d_y_bf16, d_x_bf16, d_wd_bf16, d_chan_scales, d_bias, M, N, K, 0, device,
+                                  (cudaStream_t)stream);
+}
+
 extern "C" nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf16,
                                      const uint8_t* d_wq, nvq_dtype w_fmt, const float* d_w_scales,
                                      const float* d_bias, size_t M, size_t N, size_t K,
@@ -434,22 +467,10 @@ extern "C" nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf1
     }
     NVQ_REQUIRE(d_workspace && workspace_bytes >= N * K * 2 && nvq_aligned(d_workspace, 32),
                 "nvq_linear_fwd: workspace of %zu bytes (32-byte aligned) required", N * K * 2);
+    s = nvq_linear_expand_weight((uint16_t*)d_workspace, d_wq, w_fmt, d_w_scales, N, K, device, stream);
+    if (s != NVQ_OK) return s;
     uint16_t* wd = (uint16_t*)d_workspace;
-    const float* chan_scales = d_w_scales;
-    if (w_fmt == NVQ_E2M1_B32) {
-        // block scales vary along K, so they are folded into the expanded weight:
-        // Wd = bf16(e2m1_value * scale_block); no per-channel factor is left
-        NVQ_REQUIRE(K % 32 == 0, "nvq_linear_fwd: K (%zu) must be a multiple of 32 for E2M1_B32", K);
-        s = nvq_dequantize_fp4_b32(wd, d_wq, d_w_scales, N, K, device, stream);
-        if (s != NVQ_OK) return s;
-        chan_scales = nullptr;
-    } else {
-        NVQ_REQUIRE((N * K) % 16 == 0 && nvq_aligned(d_wq, 16),
-                    "nvq_linear_fwd: weight codes must be 16-byte aligned, N*K a multiple of 16");
-        s = w_fmt == NVQ_E4M3 ? ew_launch(ExpandOp<NVQ_E4M3>{}, d_wq, wd, N * K, device, st, 16, 32)
-                              : ew_launch(ExpandOp<NVQ_E5M2>{}, d_wq, wd, N * K, device, st, 16, 32);
-        if (s != NVQ_OK) return s;
-    }
+    const float* chan_scales = w_fmt == NVQ_E2M1_B32 ? nullptr : d_w_scales;
     return nvq_linear_bf16_launch(d_y_bf16, d_x_bf16, wd, chan_scales, d_bias, M, N, K, 0, device, st);
 }
 

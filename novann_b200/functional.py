@@ -267,3 +267,19 @@ def linear_w8a8_host(x_bf16_bits, wq, w_scales, bias, device: int = 0) -> np.nda
     device_sync(device)
     check_device_errors(device)
     return dy.to_numpy(np.uint16, (m, n))
+
+
+def linear_expand_weight_device(wd: DeviceBuffer, wq: DeviceBuffer, fmt: str, w_scales: DeviceBuffer | None,
+                                n: int, k: int, stream=None) -> None:
+    check(lib().nvq_linear_expand_weight(wd.at(0), wq.at(0), _lib.DTYPE_IDS[fmt],
+                                         w_scales.at(0) if w_scales is not None else None, n, k,
+                                         wq.device, _sptr(stream)))
+
+
+def linear_expanded_device(y: DeviceBuffer, x: DeviceBuffer, wd: DeviceBuffer,
+                           chan_scales: DeviceBuffer | None, bias: DeviceBuffer | None, m: int, n: int,
+                           k: int, stream=None) -> None:
+    check(lib().nvq_linear_fwd_expanded(y.at(0), x.at(0), wd.at(0),
+                                        chan_scales.at(0) if chan_scales is not None else None,
+                                        bias.at(0) if bias is not None else None, m, n, k, x.device,
+                                        _sptr(stream)))

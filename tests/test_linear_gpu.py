@@ -156,3 +156,21 @@ def test_linear_w8a8_variant(gpu, m, n, k):
     dist = o.max_abs_rel(y[rows], full)
     assert dist <= 8e-2                                        # sanity: E4M3 activation error
     print(f"W8A8 vs bf16-activation result, {m}x{n}x{k}: max-abs-rel {dist:.4f}")
+
+
+def test_expand_once_then_contract_equals_one_call(gpu):
+    """nvq_linear_expand_weight + nvq_linear_fwd_expanded give the bytes of nvq_linear_fwd."""
+    from novann_b200.device import DeviceBuffer, device_sync
+    m, n, k = 320, 512, 768
+    xb, w, b = workloads.linear_inputs(m, n, k, seed=11)
+    wq, sc = o.quantize_weight_per_channel(w, "e4m3")
+    want = F.linear_q_host(xb, wq, sc, b, "e4m3", gpu)
+    dx, dq = DeviceBuffer.from_numpy(xb, gpu), DeviceBuffer.from_numpy(wq, gpu)
+    ds, db = DeviceBuffer.from_numpy(sc, gpu), DeviceBuffer.from_numpy(b, gpu)
+    wd, dy = DeviceBuffer(n * k * 2, gpu), DeviceBuffer(m * n * 2, gpu)
+    F.linear_expand_weight_device(wd, dq, "e4m3", None, n, k)
+    for _ in range(2):                                   # the expanded weight is reusable
+        F.linear_expanded_device(dy, dx, wd, ds, db, m, n, k)
+    device_sync(gpu)
+    F.check_device_errors(gpu)
+    assert np.array_equal(dy.to_numpy(np.uint16, (m, n)), want)
