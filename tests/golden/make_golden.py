@@ -17,7 +17,9 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-sys.path.insert(0, os.environ.get("NOVANN_REF", "/root/reference"))
+if "NOVANN_REF" not in os.environ:
+    raise SystemExit("set NOVANN_REF to a checkout of the reference (NovaNN)")
+sys.path.insert(0, os.environ["NOVANN_REF"])
 logging.disable(logging.CRITICAL)
 
 import novann  # noqa: E402  (the reference)
