@@ -31,6 +31,7 @@ template <bool BF16>
 struct NarrowOp {
     static constexpr int VEC = 8;
     static constexpr int UNROLL = 4;
+    static constexpr int RESIDENT = 3;
     using In = u32x8;
     __device__ __forceinline__ void init() {}
     __device__ __forceinline__ In load(const void* src, size_t p) const {
@@ -68,6 +69,7 @@ template <bool BF16>
 struct WidenOp {
     static constexpr int VEC = 8;
     static constexpr int UNROLL = NVQ_WIDEN_UNROLL;
+    static constexpr int RESIDENT = 2;
     using In = uint4;
     __device__ __forceinline__ void init() {}
     __device__ __forceinline__ In load(const void* src, size_t p) const {

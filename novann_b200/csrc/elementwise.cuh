@@ -5,9 +5,12 @@
 //   void    store(void* dst, size_t packet, const In&)   convert + 128/256-bit stores
 //   void    scalar(const void* src, void* dst, size_t i) one element by the written rules
 //   void    init()                                        once per thread, before the loop
+//   Op::RESIDENT                                          cap on resident blocks per SM (0 = none)
 // Every thread keeps Op::UNROLL packets in flight; consecutive threads own
 // consecutive packets so each warp-wide access covers whole 32-byte sectors once.
 #pragma once
+
+#include <stdlib.h>
 
 #include "nvq_common.cuh"
 
@@ -66,6 +69,14 @@ nvq_status ew_launch(Op op, const void* src, void* dst, size_t n, int device, cu
             NVQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, ew_vector_kernel<Op>,
                                                                    kEwThreads, 0));
             per_sm = b > 0 ? b : 1;
+            // Mixed read/write streams lose DRAM efficiency when too much traffic is in flight
+            // (measured on B200: ~80-100 KB of loads + stores per SM is the sweet spot; full
+            // occupancy costs the write-heavy kernels 5-7 %), so an op may cap its resident blocks.
+            if (Op::RESIDENT > 0 && Op::RESIDENT < per_sm) per_sm = Op::RESIDENT;
+            if (const char* e = getenv("NVQ_EW_BLOCKS_PER_SM")) {   // measurement override
+                int v = atoi(e);
+                if (v > 0 && v < per_sm) per_sm = v;
+            }
         }
         size_t n_packets = n / Op::VEC;
         size_t want = (n_packets + (size_t)kEwThreads * Op::UNROLL - 1) /

@@ -8,6 +8,7 @@
 // One thread owns one block: 64 bytes of bf16 in, 16 bytes of codes + one scale out
 // (2.625 bytes per element either way), no shuffles, every access full-sector.
 #include <math.h>
+#include <stdlib.h>
 
 #include "nvq_common.cuh"
 
@@ -214,11 +215,17 @@ fp4_dequant_kernel(const uint8_t* __restrict__ packed, const float* __restrict__
 }
 
 template <class K>
-unsigned pick_grid(K kernel, size_t n_blocks, int device, int* per_sm_cache) {
+unsigned pick_grid(K kernel, size_t n_blocks, int device, int* per_sm_cache, int resident_cap) {
     if (*per_sm_cache == 0) {
         int b = 0;
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, kernel, kThreads, 0);
         *per_sm_cache = b > 0 ? b : 1;
+        // fewer resident blocks = less mixed traffic in flight = better DRAM efficiency
+        if (resident_cap > 0 && resident_cap < *per_sm_cache) *per_sm_cache = resident_cap;
+        if (const char* e = getenv("NVQ_EW_BLOCKS_PER_SM")) {   // measurement override
+            int v = atoi(e);
+            if (v > 0 && v < *per_sm_cache) *per_sm_cache = v;
+        }
     }
     size_t want = (n_blocks + (size_t)kThreads * kUnroll - 1) / ((size_t)kThreads * kUnroll);
     size_t cap = (size_t)nvq_sm_count(device) * *per_sm_cache;
@@ -239,7 +246,7 @@ extern "C" nvq_status nvq_quantize_fp4_b32(uint8_t* d_packed, float* d_scales,
     nvq_status s = nvq_use_device(device);
     if (s != NVQ_OK) return s;
     static int per_sm = 0;
-    unsigned grid = pick_grid(fp4_quant_kernel, n_blocks, device, &per_sm);
+    unsigned grid = pick_grid(fp4_quant_kernel, n_blocks, device, &per_sm, 3);
     fp4_quant_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>(d_src_bf16, d_packed, d_scales,
                                                                   n_blocks);
     NVQ_LAUNCHED();
@@ -258,7 +265,7 @@ extern "C" nvq_status nvq_dequantize_fp4_b32(uint16_t* d_dst_bf16, const uint8_t
     nvq_status s = nvq_use_device(device);
     if (s != NVQ_OK) return s;
     static int per_sm = 0;
-    unsigned grid = pick_grid(fp4_dequant_kernel, n_blocks, device, &per_sm);
+    unsigned grid = pick_grid(fp4_dequant_kernel, n_blocks, device, &per_sm, 2);
     fp4_dequant_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>(d_packed, d_scales, d_dst_bf16,
                                                                     n_blocks);
     NVQ_LAUNCHED();

@@ -71,9 +71,13 @@ amax_kernel(const float* __restrict__ src, size_t n, unsigned int* __restrict__ 
 struct In16 { u32x8 a, b; };
 
 template <int FMT, bool DEVICE_SCALE>
+#ifndef NVQ_FP8_UNROLL
+#define NVQ_FP8_UNROLL 2
+#endif
 struct QuantOp {
     static constexpr int VEC = 16;
-    static constexpr int UNROLL = 2;
+    static constexpr int UNROLL = NVQ_FP8_UNROLL;
+    static constexpr int RESIDENT = 2;
     using In = In16;
     float inv;                 // host-provided (DEVICE_SCALE == false)
     const float* d_amax;       // device amax (DEVICE_SCALE == true)
@@ -131,7 +135,8 @@ struct QuantOp {
 template <int FMT>
 struct DequantOp {
     static constexpr int VEC = 16;
-    static constexpr int UNROLL = 2;
+    static constexpr int UNROLL = NVQ_FP8_UNROLL;
+    static constexpr int RESIDENT = 2;
     using In = uint4;
     float scale;
     __device__ __forceinline__ void init() {}

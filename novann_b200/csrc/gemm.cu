@@ -198,6 +198,7 @@ template <int FMT>
 struct ExpandOp {
     static constexpr int VEC = 16;
     static constexpr int UNROLL = 4;
+    static constexpr int RESIDENT = 0;
     using In = uint4;
     // lets the GEMM that follows in the stream start its set-up (barriers, TMEM, descriptors)
     // while this kernel is still running; the GEMM waits for this grid before its first load
