@@ -27,3 +27,60 @@ def exchange_bytes(payload: bytes | None, rank: int, path: str, timeout_s: float
         time.sleep(0.01)
     with open(path, "rb") as f:
         return f.read()
+
+
+class PeerLost(RuntimeError):
+    """A rank did not announce the step in time, or announced that it left."""
+
+
+class StepGate:
+    """Host-side gate in front of a collective step (failure detection without touching the GPU).
+
+    Before a rank enqueues step ``k`` (whose kernels wait on the other ranks inside NCCL), it
+    announces ``k`` in a file and waits until every rank has announced ``k``.  A rank that
+    crashed, hung on the host or left on purpose never announces, the others give up after
+    ``timeout_s`` and raise ``PeerLost`` BEFORE launching anything, so no kernel is ever left
+    spinning on a partner that will not come.  Files live in a directory all ranks can see.
+    """
+
+    def __init__(self, directory: str, rank: int, world: int, timeout_s: float = 10.0):
+        self.dir, self.rank, self.world, self.timeout_s = directory, rank, world, timeout_s
+        os.makedirs(directory, exist_ok=True)
+
+    def _path(self, rank: int) -> str:
+        return os.path.join(self.dir, f"step_gate.{rank}")
+
+    def _write(self, text: str) -> None:
+        tmp = self._path(self.rank) + f".tmp.{os.getpid()}"
+        with open(tmp, "w") as f:
+            f.write(text)
+        os.replace(tmp, self._path(self.rank))
+
+    def _read(self, rank: int):
+        try:
+            with open(self._path(rank)) as f:
+                return f.read().strip()
+        except OSError:
+            return None
+
+    def leave(self) -> None:
+        """Announce a clean exit (call between steps, with nothing in flight)."""
+        self._write("left")
+
+    def enter(self, step: int) -> None:
+        """Announce ``step`` and wait for every rank to do the same; raises ``PeerLost``."""
+        self._write(str(step))
+        t0 = time.time()
+        pending = set(range(self.world)) - {self.rank}
+        while pending:
+            for r in list(pending):
+                v = self._read(r)
+                if v == "left":
+                    raise PeerLost(f"rank {r} left before step {step}")
+                if v is not None and v.isdigit() and int(v) >= step:
+                    pending.discard(r)
+            if pending and time.time() - t0 > self.timeout_s:
+                raise PeerLost(f"ranks {sorted(pending)} did not reach step {step} within "
+                               f"{self.timeout_s} s")
+            if pending:
+                time.sleep(0.002)

@@ -73,10 +73,13 @@ class MLPTrainStep:
     """``step(x, labels)`` runs one training step on the device and returns nothing; read
     results with ``logits()``, ``loss()``, ``grads()``, ``params()``."""
 
-    def __init__(self, params, batch: int, lr: float, device: int = 0, comm: Communicator | None = None):
+    def __init__(self, params, batch: int, lr: float, device: int = 0, comm: Communicator | None = None,
+                 gate=None):
         self.dims = [params[0].shape[1]] + [params[2 * i].shape[0] for i in range(len(params) // 2)]
         self.nl = len(self.dims) - 1
         self.batch, self.lr, self.device, self.comm = batch, float(lr), device, comm
+        self.gate = gate            # launch.StepGate: host rendezvous before each collective step
+        self._step_no = 0
         self.stream = Stream(device)
         flat = flatten_params(params)
         self.n_params = flat.size
@@ -150,6 +153,9 @@ class MLPTrainStep:
         return self.nl + 1 + (3 * self.nl - 1) + 1
 
     def step(self, x: np.ndarray, labels: np.ndarray) -> None:
+        self._step_no += 1
+        if self.gate is not None:
+            self.gate.enter(self._step_no)      # raises PeerLost before anything is launched
         self.upload(x, labels)
         if self._graph is not None:
             self.replay()

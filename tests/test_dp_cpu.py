@@ -64,3 +64,52 @@ def test_shard_rows_and_bucket_layout():
     back = unflatten_params(flat, (784, 256, 128, 10))
     assert all(np.array_equal(a, b) for a, b in zip(back, params))
     assert [b.shape for b in back] == [(256, 784), (1, 256), (128, 256), (1, 128), (10, 128), (1, 10)]
+
+
+def _gate_worker(rank, tmpdir, q):
+    sys.path.insert(0, ROOT)
+    from novann_b200.launch import PeerLost, StepGate
+    gate = StepGate(tmpdir, rank, 2, timeout_s=2.0)
+    gate.enter(1)                      # both ranks make step 1
+    if rank == 1:
+        gate.leave()                   # rank 1 leaves between steps, nothing in flight
+        q.put((rank, "left"))
+        return
+    try:
+        gate.enter(2)
+        q.put((rank, "no error"))
+    except PeerLost as e:
+        q.put((rank, f"PeerLost: {e}"))
+
+
+def _silent_worker(rank, tmpdir, q):
+    sys.path.insert(0, ROOT)
+    from novann_b200.launch import PeerLost, StepGate
+    gate = StepGate(tmpdir, rank, 2, timeout_s=1.0)
+    if rank == 1:
+        return                         # never joins (a rank that died before the first step)
+    import time
+    t0 = time.time()
+    try:
+        gate.enter(1)
+        q.put((rank, "no error"))
+    except PeerLost as e:
+        q.put((rank, f"PeerLost after {time.time() - t0:.1f}s: {e}"))
+
+
+def test_step_gate_detects_a_rank_that_left_or_never_joined(tmp_path):
+    """Failure detection happens on the host, before a collective step is enqueued: no kernel
+    is ever left waiting for a partner that will not come."""
+    import multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    for worker, sub in ((_gate_worker, "a"), (_silent_worker, "b")):
+        q = ctx.Queue()
+        d = str(tmp_path / sub)
+        ps = [ctx.Process(target=worker, args=(r, d, q)) for r in range(2)]
+        for p in ps:
+            p.start()
+        for p in ps:
+            p.join(30)
+            assert p.exitcode == 0
+        msgs = dict(q.get(timeout=5) for _ in range(1 if worker is _silent_worker else 2))
+        assert msgs[0].startswith("PeerLost"), msgs
