@@ -4,6 +4,7 @@
     python -m novann_b200.profile_cases fp8    [rows=8192]
     python -m novann_b200.profile_cases fp4    [rows=8192]
     python -m novann_b200.profile_cases linear [M=4096 N=4096 K=4096]
+    python -m novann_b200.profile_cases w8a8   [M=4096 N=4096 K=4096]
 
 Each case uploads seeded inputs, launches the kernels a few times and exits; sizes are
 larger than the 126 MB L2 (so DRAM counters mean something) but hold at most a few GB.
@@ -79,6 +80,21 @@ def case_linear(m: int = 4096, n: int = 4096, k: int = 4096, reps: int = 3) -> N
     F.check_device_errors(0)
 
 
+def case_w8a8(m: int = 4096, n: int = 4096, k: int = 4096, reps: int = 3) -> None:
+    st = Stream(0)
+    xb, _, b = workloads.linear_inputs(m, 8, k, seed=0)
+    rng = np.random.default_rng(1)
+    wq = rng.integers(0, 0x7F, (n, k), dtype=np.uint64).astype(np.uint8)
+    dx, dw = DeviceBuffer.from_numpy(xb, 0), DeviceBuffer.from_numpy(wq, 0)
+    ds = DeviceBuffer.from_numpy(np.full(n, 1e-3, np.float32), 0)
+    dy = DeviceBuffer(m * n * 2, 0)
+    ws = DeviceBuffer(F.linear_w8a8_workspace_bytes(m, k), 0)
+    for _ in range(reps):
+        F.linear_w8a8_device(dy, dx, dw, ds, None, m, n, k, ws, stream=st)
+    st.sync()
+    F.check_device_errors(0)
+
+
 def main(argv) -> None:
     what = argv[1] if len(argv) > 1 else "cast"
     args = [int(a) for a in argv[2:]]
@@ -90,6 +106,8 @@ def main(argv) -> None:
         case_fp4(*args)
     elif what == "linear":
         case_linear(*args)
+    elif what == "w8a8":
+        case_w8a8(*args)
     else:
         raise SystemExit(f"unknown case {what}")
     device_sync(0)
