@@ -244,13 +244,32 @@ quantize_rows_bf16_fast_kernel(uint8_t* __restrict__ dst, float* __restrict__ sc
     __shared__ unsigned int warp_max[8];
     __shared__ float s_inv;
     __shared__ int s_slow;
+    // rows of up to 8192 values stay in registers between the two passes (4 chunks a thread)
+    constexpr int KEEP = 4;
+    const bool in_regs = chunks <= (size_t)KEEP * 256;
+    uint4 keep[KEEP];
     uint32_t m2 = 0u;
-    for (size_t c = threadIdx.x; c < chunks; c += blockDim.x) {
-        uint4 v = *(const uint4*)(row + c * 8);
-        m2 = __vmaxu2(m2, v.x & 0x7FFF7FFFu);
-        m2 = __vmaxu2(m2, v.y & 0x7FFF7FFFu);
-        m2 = __vmaxu2(m2, v.z & 0x7FFF7FFFu);
-        m2 = __vmaxu2(m2, v.w & 0x7FFF7FFFu);
+    if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < KEEP; j++) {
+            size_t c = threadIdx.x + (size_t)j * 256;
+            keep[j] = c < chunks ? ldg_stream_128(row + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int j = 0; j < KEEP; j++) {
+            m2 = __vmaxu2(m2, keep[j].x & 0x7FFF7FFFu);
+            m2 = __vmaxu2(m2, keep[j].y & 0x7FFF7FFFu);
+            m2 = __vmaxu2(m2, keep[j].z & 0x7FFF7FFFu);
+            m2 = __vmaxu2(m2, keep[j].w & 0x7FFF7FFFu);
+        }
+    } else {
+        for (size_t c = threadIdx.x; c < chunks; c += blockDim.x) {
+            uint4 v = *(const uint4*)(row + c * 8);
+            m2 = __vmaxu2(m2, v.x & 0x7FFF7FFFu);
+            m2 = __vmaxu2(m2, v.y & 0x7FFF7FFFu);
+            m2 = __vmaxu2(m2, v.z & 0x7FFF7FFFu);
+            m2 = __vmaxu2(m2, v.w & 0x7FFF7FFFu);
+        }
     }
     unsigned int b = max(m2 & 0xFFFFu, m2 >> 16);
 #pragma unroll
@@ -271,6 +290,21 @@ quantize_rows_bf16_fast_kernel(uint8_t* __restrict__ dst, float* __restrict__ sc
     __syncthreads();
     if (!s_slow) {
         const float inv = s_inv;
+        if (in_regs) {
+#pragma unroll
+            for (int j = 0; j < KEEP; j++) {
+                size_t c = threadIdx.x + (size_t)j * 256;
+                if (c >= chunks) continue;
+                const uint32_t w[4] = {keep[j].x, keep[j].y, keep[j].z, keep[j].w};
+                uint32_t q[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                    q[i] = cvt_fp8x2<NVQ_E4M3>(__fmul_rn(__uint_as_float(w[i] << 16), inv),
+                                               __fmul_rn(__uint_as_float(w[i] & 0xFFFF0000u), inv));
+                *(uint2*)(out + c * 8) = make_uint2(q[0] | (q[1] << 16), q[2] | (q[3] << 16));
+            }
+            return;
+        }
         for (size_t c = threadIdx.x; c < chunks; c += blockDim.x) {
             uint4 v = *(const uint4*)(row + c * 8);
             const uint32_t w[4] = {v.x, v.y, v.z, v.w};
