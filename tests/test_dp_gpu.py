@@ -44,3 +44,46 @@ def test_two_rank_step_equals_global_batch_step(gpu, tmp_path):
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     mp.spawn(_worker, args=(2, str(tmp_path)), nprocs=2, join=True)
+
+
+def _fp8_shard_worker(rank, world, tmpdir):
+    sys.path.insert(0, ROOT)
+    from novann_b200 import quant, workloads
+    from novann_b200.device import DeviceBuffer
+    from novann_b200.launch import exchange_bytes
+    from novann_b200.train import shard_rows
+    from oracle import oracle_np as o
+
+    x = workloads.fp8_input(1024, 2048, seed=9)               # every rank can rebuild the tensor
+    lo, hi = shard_rows(1024, rank, world)
+    shard = np.ascontiguousarray(x[lo:hi])
+    part = quant.amax(shard, device=rank)                     # this rank's partial amax (one float)
+    # the one scalar exchange of the path: max-combine on the host, no collective
+    open(os.path.join(tmpdir, f"amax.{rank}"), "wb").write(np.float32(part).tobytes())
+    vals = []
+    for r in range(world):
+        vals.append(np.frombuffer(exchange_bytes(None, 1, os.path.join(tmpdir, f"amax.{r}")), np.float32)[0])
+    amax = np.float32(max(vals))
+    for fmt in ("e4m3", "e5m2"):
+        d = DeviceBuffer.from_numpy(shard, rank)
+        q = DeviceBuffer(shard.size, rank)
+        asi = DeviceBuffer(12, rank)
+        a_in = DeviceBuffer.from_numpy(np.array([amax], np.float32), rank)
+        quant.quantize_fp8_tensor_device(q, asi, d, shard.size, fmt, amax_in=a_in)
+        codes = q.to_numpy(np.uint8, shard.shape)
+        want, scale, inv = o.quantize_fp8_tensor(x, fmt)      # the one-GPU (whole tensor) result
+        assert np.array_equal(codes, want[lo:hi]), (rank, fmt)
+        assert asi.to_numpy(np.float32, (3,))[1] == scale
+        back = quant.dequantize_fp8(codes, scale, fmt, device=rank)
+        assert np.array_equal(back.view(np.uint32), o.dequantize_fp8(want[lo:hi], scale, fmt).view(np.uint32))
+
+
+def test_two_rank_fp8_row_shards_equal_whole_tensor(gpu, tmp_path):
+    """FP8 per-tensor quantisation over row shards on two GPUs: each rank reduces its own amax,
+    the two floats are max-combined on the host, and the codes equal the one-GPU result bit for
+    bit (no collective on the data path)."""
+    from novann_b200.device import device_count
+    if device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_fp8_shard_worker, args=(2, str(tmp_path)), nprocs=2, join=True)
