@@ -228,15 +228,16 @@ nvq_status nvq_linear_fwd_static(uint16_t* d_y_bf16, const uint16_t* d_x_bf16, c
  * weight: expand once, then run the contraction alone.
  *   nvq_linear_expand_weight: Wd (N x K bf16, 32-byte aligned) = exact value of every E4M3 / E5M2
  *     code (d_w_scales unused), or bf16(value * block scale) for E2M1_B32.
- *   nvq_linear_fwd_expanded: Y = bf16(s_n * X @ Wd^T + b_n); d_chan_scales = the N per-channel
- *     scales for FP8 weights, NULL for an E2M1_B32 weight (scales already folded in). */
+ *   nvq_linear_fwd_expanded: Y = bf16(act(s_n * X @ Wd^T + b_n)); d_chan_scales = the N per-channel
+ *     scales for FP8 weights, NULL for an E2M1_B32 weight (scales already folded in); relu != 0
+ *     fuses F.relu (novann/functional.py:8-22: v * (v > 0)) into the epilogue before rounding. */
 nvq_status nvq_linear_expand_weight(uint16_t* d_wd_bf16, const uint8_t* d_wq, nvq_dtype w_fmt,
                                     const float* d_w_scales, size_t N, size_t K, int device,
                                     void* stream);
 nvq_status nvq_linear_fwd_expanded(uint16_t* d_y_bf16, const uint16_t* d_x_bf16,
                                    const uint16_t* d_wd_bf16, const float* d_chan_scales,
-                                   const float* d_bias, size_t M, size_t N, size_t K, int device,
-                                   void* stream);
+                                   const float* d_bias, size_t M, size_t N, size_t K, int relu,
+                                   int device, void* stream);
 
 /* Tensor-core kernels bound every device-side wait; a wait that gives up records a
  * non-zero code here (read and cleared by this call) instead of hanging. */

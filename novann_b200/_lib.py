@@ -64,7 +64,7 @@ SIGNATURES = {
     "nvq_linear_workspace_bytes": (i32, [sz, sz, i32, C.POINTER(sz)]),
     "nvq_linear_fwd": (i32, [vp, vp, vp, i32, vp, vp, sz, sz, sz, vp, sz, i32, vp]),
     "nvq_linear_expand_weight": (i32, [vp, vp, i32, vp, sz, sz, i32, vp]),
-    "nvq_linear_fwd_expanded": (i32, [vp, vp, vp, vp, vp, sz, sz, sz, i32, vp]),
+    "nvq_linear_fwd_expanded": (i32, [vp, vp, vp, vp, vp, sz, sz, sz, i32, i32, vp]),
     "nvq_linear_w8a8_workspace_bytes": (i32, [sz, sz, C.POINTER(sz)]),
     "nvq_linear_fwd_w8a8": (i32, [vp, vp, vp, vp, vp, sz, sz, sz, vp, sz, i32, vp]),
     "nvq_linear_bwd_q_workspace_bytes": (i32, [sz, sz, sz, C.POINTER(sz)]),

@@ -430,13 +430,13 @@ extern "C" nvq_status nvq_linear_expand_weight(uint16_t* d_wd_bf16, const uint8_
 extern "C" nvq_status nvq_linear_fwd_expanded(uint16_t* d_y_bf16, const uint16_t* d_x_bf16,
                                               const uint16_t* d_wd_bf16, const float* d_chan_scales,
                                               const float* d_bias, size_t M, size_t N, size_t K,
-                                              int device, void* stream) {
+                                              int relu, int device, void* stream) {
     NVQ_REQUIRE(d_y_bf16 && d_x_bf16 && d_wd_bf16 && M > 0 && N > 0 && K > 0,
                 "nvq_linear_fwd_expanded: bad argument");
     nvq_status s = nvq_use_device(device);
     if (s != NVQ_OK) return s;
-    return nvq_linear_bf16_launch(d_y_bf16, d_x_bf16, d_wd_bf16, d_chan_scales, d_bias, M, N, K, 0, device,
-                                  (cudaStream_t)stream);
+    return nvq_linear_bf16_launch(d_y_bf16, d_x_bf16, d_wd_bf16, d_chan_scales, d_bias, M, N, K,
+                                  relu ? 2 : 0, device, (cudaStream_t)stream);
 }
 
 extern "C" nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf16,

@@ -5,7 +5,7 @@
 
 struct LinearParams {
     uint16_t* y;           // M x N output: bf16, or fp32 when out_f32 is set
-    int out_f32;
+    int out_f32;           // bit 0: fp32 output; bit 1: fused ReLU (v * (v > 0), the reference's formula)
     const uint8_t* wq;     // fused kernels: the weight codes (N x K bytes); else unused
     const float* scales;   // N per-output-channel factors or nullptr (= 1)
     const float* row_scales;  // M per-row factors (quantised activations) or nullptr
@@ -90,14 +90,16 @@ __device__ __forceinline__ TileRef tile_ref(const LinearParams& p, int item) {
 
 // fp32 flavour of store_chunk: 32 accumulators -> scale, bias -> 128 bytes of the row
 __device__ __forceinline__ void store_chunk_f32(const uint32_t* r, const float* scale, const float* bias,
-                                                float* yrow, int n_base, int N, bool vec32) {
+                                                float* yrow, int n_base, int N, bool vec32, bool relu) {
 #pragma unroll
     for (int g = 0; g < 4; g++) {
         u32x8 o;
 #pragma unroll
         for (int j = 0; j < 8; j++) {
             const int cc = g * 8 + j;
-            o.v[j] = __float_as_uint(fmaf(__uint_as_float(r[cc]), scale[cc], bias[cc]));
+            float v = fmaf(__uint_as_float(r[cc]), scale[cc], bias[cc]);
+            if (relu) v = __fmul_rn(v, v > 0.f ? 1.f : 0.f);
+            o.v[j] = __float_as_uint(v);
         }
         const int n = n_base + g * 8;
         if (n + 8 <= N) {
@@ -114,7 +116,7 @@ __device__ __forceinline__ void store_chunk_f32(const uint32_t* r, const float* 
 // Epilogue of one 32-column chunk: 32 fp32 accumulators of this thread's row -> scale,
 // bias, bf16, global stores.  `vec32` = rows start on 32-byte boundaries.
 __device__ __forceinline__ void store_chunk(const uint32_t* r, const float* scale, const float* bias,
-                                            uint16_t* yrow, int n_base, int N, bool vec32) {
+                                            uint16_t* yrow, int n_base, int N, bool vec32, bool relu) {
 #pragma unroll
     for (int g = 0; g < 2; g++) {
         u32x8 o;
@@ -123,6 +125,10 @@ __device__ __forceinline__ void store_chunk(const uint32_t* r, const float* scal
             const int cc = g * 16 + 2 * j;
             float v0 = fmaf(__uint_as_float(r[cc]), scale[cc], bias[cc]);
             float v1 = fmaf(__uint_as_float(r[cc + 1]), scale[cc + 1], bias[cc + 1]);
+            if (relu) {
+                v0 = __fmul_rn(v0, v0 > 0.f ? 1.f : 0.f);
+                v1 = __fmul_rn(v1, v1 > 0.f ? 1.f : 0.f);
+            }
             o.v[j] = pack_bf16(v0, v1);
         }
         const int n = n_base + g * 16;
@@ -138,9 +144,10 @@ __device__ __forceinline__ void store_chunk(const uint32_t* r, const float* scal
 __device__ __forceinline__ void store_row_chunk(const LinearParams& p, const uint32_t* r,
                                                 const float* scale, const float* bias, int row, int n,
                                                 bool vec32) {
-    if (p.out_f32)
-        store_chunk_f32(r, scale, bias, (float*)p.y + (size_t)row * p.N + n, n, p.N, (p.N % 8) == 0);
+    const bool relu = (p.out_f32 & 2) != 0;
+    if (p.out_f32 & 1)
+        store_chunk_f32(r, scale, bias, (float*)p.y + (size_t)row * p.N + n, n, p.N, (p.N % 8) == 0, relu);
     else
-        store_chunk(r, scale, bias, p.y + (size_t)row * p.N + n, n, p.N, vec32);
+        store_chunk(r, scale, bias, p.y + (size_t)row * p.N + n, n, p.N, vec32, relu);
 }
 #endif

@@ -278,8 +278,8 @@ def linear_expand_weight_device(wd: DeviceBuffer, wq: DeviceBuffer, fmt: str, w_
 
 def linear_expanded_device(y: DeviceBuffer, x: DeviceBuffer, wd: DeviceBuffer,
                            chan_scales: DeviceBuffer | None, bias: DeviceBuffer | None, m: int, n: int,
-                           k: int, stream=None) -> None:
+                           k: int, stream=None, relu: bool = False) -> None:
     check(lib().nvq_linear_fwd_expanded(y.at(0), x.at(0), wd.at(0),
                                         chan_scales.at(0) if chan_scales is not None else None,
-                                        bias.at(0) if bias is not None else None, m, n, k, x.device,
-                                        _sptr(stream)))
+                                        bias.at(0) if bias is not None else None, m, n, k, int(relu),
+                                        x.device, _sptr(stream)))

@@ -175,3 +175,52 @@ class MLPTrainStep:
 
     def params(self) -> list[np.ndarray]:
         return unflatten_params(self.d_params.to_numpy(np.float32, (self.n_params,)), self.dims)
+
+
+class QuantMLPInference:
+    """Forward pass of ``Sequential(Linear, ReLU, ..., Linear)`` with FP8 weights, resident on the
+    device: weights are quantised per output channel and expanded once at construction; a call
+    uploads the fp32 batch, casts it to bf16, runs one tensor-core kernel per layer with bias and
+    ReLU fused into the epilogue (activations stay bf16 in HBM between layers), casts the logits
+    back to fp32 and downloads them."""
+
+    def __init__(self, params, max_batch: int, fmt: str = "e4m3", device: int = 0):
+        from . import functional as F, quant
+        self.F, self.quant = F, quant
+        self.device, self.fmt, self.max_batch = device, fmt, max_batch
+        self.dims = [params[0].shape[1]] + [params[2 * i].shape[0] for i in range(len(params) // 2)]
+        self.stream = Stream(device)
+        self.wd, self.scales, self.bias = [], [], []
+        for i in range(len(params) // 2):
+            w = np.ascontiguousarray(params[2 * i], np.float32)
+            n, k = w.shape
+            codes, sc = quant.quantize_weight(w, fmt, device)
+            dq = DeviceBuffer.from_numpy(codes, device)
+            wd = DeviceBuffer(n * k * 2, device)
+            F.linear_expand_weight_device(wd, dq, fmt, None, n, k)
+            self.wd.append(wd)
+            self.scales.append(DeviceBuffer.from_numpy(sc, device))
+            self.bias.append(DeviceBuffer.from_numpy(np.ascontiguousarray(params[2 * i + 1], np.float32).ravel(), device))
+        self.d_x32 = DeviceBuffer(max_batch * self.dims[0] * 4, device)
+        self.d_act = [DeviceBuffer(max_batch * d * 2, device) for d in self.dims]
+        self.d_out32 = DeviceBuffer(max_batch * self.dims[-1] * 4, device)
+
+    def forward(self, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x, np.float32)
+        m = x.shape[0]
+        if m > self.max_batch:
+            raise ValueError("batch larger than max_batch")
+        st = self.stream
+        self.d_x32.upload(x, stream=st)
+        self.quant.cast_device(self.d_act[0], "bf16", self.d_x32, "f32", m * self.dims[0], stream=st)
+        nl = len(self.wd)
+        for i in range(nl):
+            self.F.linear_expanded_device(self.d_act[i + 1], self.d_act[i], self.wd[i], self.scales[i],
+                                          self.bias[i], m, self.dims[i + 1], self.dims[i], stream=st,
+                                          relu=i < nl - 1)
+        self.quant.cast_device(self.d_out32, "f32", self.d_act[nl], "bf16", m * self.dims[-1], stream=st)
+        out = np.empty((m, self.dims[-1]), np.float32)
+        self.d_out32.download(out, stream=st)
+        st.sync()
+        self.F.check_device_errors(self.device)
+        return out

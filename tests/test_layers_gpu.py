@@ -340,3 +340,26 @@ def test_adamw_bit_exact_against_reference_vectors(gpu):
         opt.step()
         assert np.array_equal(p.data.view(np.uint32), g[f"p{t + 1}"].view(np.uint32)), t
         assert np.array_equal(q.data.view(np.uint32), g[f"q{t + 1}"].view(np.uint32)), t
+
+
+def test_quant_mlp_inference_fused_relu(gpu):
+    """Device-resident FP8-weight MLP forward with bias + ReLU fused into the GEMM epilogue,
+    against the oracle chain (bf16 activations between layers, same codes)."""
+    from novann_b200.train import QuantMLPInference
+    dims = (512, 384, 256, 16)
+    x, _, params = workloads.mlp_inputs(300, dims, seed=3)
+    for i in range(len(dims) - 1):
+        params[2 * i + 1] = (np.random.default_rng(i).standard_normal((1, dims[i + 1])) * 0.1).astype(np.float32)
+    net = QuantMLPInference(params, max_batch=512, device=gpu)
+    y = net.forward(x)
+    h = o.f32_to_bf16_bits(x).reshape(x.shape)
+    for i in range(len(dims) - 1):
+        wq, sc = o.quantize_weight_per_channel(params[2 * i], "e4m3")
+        _, pre = o.linear_fwd_qweight(h, wq, sc, params[2 * i + 1].ravel(), "e4m3")
+        if i < len(dims) - 2:
+            pre = pre * (pre > 0)
+        h = o.f32_to_bf16_bits(pre).reshape(pre.shape)
+    want = o.bf16_bits_to_f32(h)
+    assert y.shape == (300, 16)
+    assert o.max_abs_rel(y, want) <= 1e-2
+    assert np.mean(y == want) > 0.9          # most outputs agree to the last bf16 bit
