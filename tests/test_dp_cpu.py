@@ -69,8 +69,9 @@ def test_shard_rows_and_bucket_layout():
 def _gate_worker(rank, tmpdir, q):
     sys.path.insert(0, ROOT)
     from novann_b200.launch import PeerLost, StepGate
-    gate = StepGate(tmpdir, rank, 2, timeout_s=2.0)
+    gate = StepGate(tmpdir, rank, 2, timeout_s=60.0)   # generous: process start-up times differ
     gate.enter(1)                      # both ranks make step 1
+    gate.timeout_s = 2.0
     if rank == 1:
         gate.leave()                   # rank 1 leaves between steps, nothing in flight
         q.put((rank, "left"))
