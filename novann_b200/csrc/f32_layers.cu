@@ -13,9 +13,8 @@ namespace {
 
 // ---- generic strided fp32 GEMM ------------------------------------------------------
 //   C(i,j) = sum_l A(i,l) * B(l,j),  A(i,l) = a[i*a_si + l*a_sl],  B(l,j) = b[l*b_sl + j*b_sj]
-// One 32 x 32 output tile per 256-thread block (2 x 2 per thread), 64-deep k chunks staged
-// in shared memory.  Loads walk the unit-stride index fastest, whichever it is.
-constexpr int TS = 32;
+// One T x T output tile per 256-thread block (T = 32 or 16), 64-deep k chunks staged in shared
+// memory.  Loads walk the unit-stride index fastest, whichever it is.
 
 struct GemmArgs {
     const float* a; long long a_si, a_sl;

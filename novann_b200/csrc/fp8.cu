@@ -238,6 +238,9 @@ quantize_rows_kernel(uint8_t* __restrict__ dst, float* __restrict__ scales,
 __global__ void __launch_bounds__(256)
 quantize_rows_bf16_fast_kernel(uint8_t* __restrict__ dst, float* __restrict__ scales,
                                const uint16_t* __restrict__ src, size_t cols) {
+    // the GEMM that consumes these codes may start its set-up now; it waits for this grid to
+    // finish before its first load
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint16_t* row = src + (size_t)blockIdx.x * cols;
     uint8_t* out = dst + (size_t)blockIdx.x * cols;
     const size_t chunks = cols / 8;
