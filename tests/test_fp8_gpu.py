@@ -164,3 +164,24 @@ def test_full_size_roundtrip_idempotence(gpu):
         a = q.download(np.empty(1 << 24, np.uint8), offset=off)
         b = q2.download(np.empty(1 << 24, np.uint8), offset=off)
         assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("inv", [0.37, 37.5])
+def test_every_pattern_of_two_chunks_with_scaling(gpu, oracle_c, fmt, inv):
+    """All fp32 patterns in [0x38000000, 0x48000000) (2^-15 .. 2^17, where the products land on
+    both formats' subnormal, normal and saturating ranges) times a non-trivial scale, positive
+    and negative."""
+    chunk = 1 << 28
+    d_in = DeviceBuffer(chunk * 4, gpu)
+    d_out = DeviceBuffer(chunk, gpu)
+    got = np.empty(chunk, np.uint8)
+    want = np.empty(chunk, np.uint8)
+    for start in (0x38000000, 0xB8000000):
+        u = np.arange(start, start + chunk, dtype=np.uint32)
+        d_in.upload(u)
+        quant.quantize_fp8_device(d_out, d_in, chunk, fmt, inv)
+        d_out.download(got)
+        oracle_c.quantize_fp8(u.view(np.float32), inv, fmt, out=want)
+        bad = np.flatnonzero(got != want)
+        assert bad.size == 0, (hex(int(u[bad[0]])), hex(int(got[bad[0]])), hex(int(want[bad[0]])))

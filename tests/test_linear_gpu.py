@@ -174,3 +174,42 @@ def test_expand_once_then_contract_equals_one_call(gpu):
     device_sync(gpu)
     F.check_device_errors(gpu)
     assert np.array_equal(dy.to_numpy(np.uint16, (m, n)), want)
+
+
+def test_linear_random_shapes_all_formats(gpu):
+    """Shape fuzz: ragged M, N, K (multiples of 8 / 32 as each format requires) through both
+    kernels (M <= 128: one CTA per tile; M > 128: CTA pairs), with and without workspace."""
+    rng = np.random.default_rng(2024)
+    for t in range(14):
+        m = int(rng.integers(1, 700))
+        n = 8 * int(rng.integers(1, 80))
+        fmt = ["e4m3", "e5m2", "e2m1_b32"][t % 3]
+        k = (32 if fmt == "e2m1_b32" else 8) * int(rng.integers(1, 60 if fmt == "e2m1_b32" else 200))
+        xb, w, b = workloads.linear_inputs(m, n, k, seed=t)
+        if fmt == "e2m1_b32":
+            wq, sc = o.quantize_fp4_b32(o.f32_to_bf16_bits(w).reshape(n, k))
+            wd = o.dequantize_fp4_weight(wq, sc)
+            ref = o.bf16_bits_to_f32(xb).astype(np.float64) @ wd.astype(np.float64).T + b
+            tol = 2.0 ** -6
+        else:
+            wq, sc = o.quantize_weight_per_channel(w, fmt)
+            ref = o.bf16_bits_to_f32(o.linear_fwd_qweight(xb, wq, sc, b, fmt)[0])
+            tol = 2.0 ** -7
+        y = o.bf16_bits_to_f32(F.linear_q_host(xb, wq, sc, b, fmt, gpu))
+        assert y.shape == (m, n)
+        assert o.max_abs_rel(y, ref) <= tol, (m, n, k, fmt)
+        if fmt != "e2m1_b32" and m > 128 and k % 16 == 0:
+            y2 = o.bf16_bits_to_f32(F.linear_q_host(xb, wq, sc, b, fmt, gpu, use_workspace=False))
+            assert np.array_equal(y, y2), (m, n, k, fmt)
+
+
+@pytest.mark.parametrize("m,n,k", [(2304, 2200, 512), (4800, 2048, 256), (300, 512, 8192)])
+def test_linear_split_last_wave_and_deep_k(gpu, m, n, k):
+    """Tile counts that leave a partial last wave (cut into half-width tiles, here together
+    with an N tail), and a deep contraction (128 k-blocks)."""
+    xb, w, b = workloads.linear_inputs(m, n, k, seed=7)
+    wq, sc = o.quantize_weight_per_channel(w, "e4m3")
+    y = F.linear_q_host(xb, wq, sc, b, "e4m3", gpu)
+    rows = np.unique(np.concatenate([np.arange(0, m, 37), [m - 1, 255, 256, 257]]))
+    want, _ = o.linear_fwd_qweight(xb[rows], wq, sc, b, "e4m3")
+    assert o.max_abs_rel(o.bf16_bits_to_f32(y[rows]), o.bf16_bits_to_f32(want)) <= 2.0 ** -7
