@@ -268,6 +268,9 @@ nvq_status nvq_linear_bwd_f32(float* d_dw, float* d_db, float* d_dx, const float
 /* F.relu (novann/functional.py:8-22): mask = (x > 0) as fp32, out = x * mask. */
 nvq_status nvq_relu_fwd_f32(float* d_out, float* d_mask, const float* d_x, size_t n, int device,
                             void* stream);
+/* ReLU.backward (novann/layers/activations/relu.py:36-45): out = grad * mask, elementwise. */
+nvq_status nvq_mul_f32(float* d_out, const float* d_a, const float* d_b, size_t n, int device,
+                       void* stream);
 /* CrossEntropyLoss (novann/losses/loss_functions.py:29-75): d_yhat (MxC) = softmax(logits,
  * axis 1); grad = float32((double(y_hat) - onehot) / M); *d_loss (may be NULL) = the value the
  * reference reports, i.e. softmax applied a second time along the batch axis inside

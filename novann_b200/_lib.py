@@ -74,6 +74,7 @@ SIGNATURES = {
     "nvq_linear_fwd_f32": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp, i32, vp]),
     "nvq_linear_bwd_f32": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "nvq_relu_fwd_f32": (i32, [vp, vp, vp, sz, i32, vp]),
+    "nvq_mul_f32": (i32, [vp, vp, vp, sz, i32, vp]),
     "nvq_softmax_ce_f32": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, vp]),
     "nvq_sgd_step_f32": (i32, [vp, vp, sz, f32c, f32c, i32, vp]),
     "nvq_adamw_step_f32": (i32, [vp, vp, vp, vp, sz] + [f32c] * 9 + [i32, i32, vp]),

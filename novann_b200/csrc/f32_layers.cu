@@ -172,6 +172,13 @@ __global__ void relu_kernel(float* __restrict__ out, float* __restrict__ mask,
     }
 }
 
+__global__ void mul_kernel(float* __restrict__ out, const float* __restrict__ a,
+                           const float* __restrict__ b, size_t n) {
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        out[i] = __fmul_rn(a[i], b[i]);
+}
+
 // One block; thread per row for the softmax, then a block reduction for the loss.
 //   y_hat = softmax(logits, axis 1) in fp32; grad = float((double(y_hat) - onehot) / M)
 //   loss  = -sum(onehot * log(p2 + 1e-8)) / M with p2 = softmax(y_hat, axis 0): the value the
@@ -443,6 +450,17 @@ extern "C" nvq_status nvq_relu_fwd_f32(float* d_out, float* d_mask, const float*
     nvq_status s = nvq_use_device(device);
     if (s != NVQ_OK) return s;
     relu_kernel<<<ew_grid(n, device), 256, 0, (cudaStream_t)stream>>>(d_out, d_mask, d_x, n);
+    NVQ_LAUNCHED();
+    return NVQ_OK;
+}
+
+extern "C" nvq_status nvq_mul_f32(float* d_out, const float* d_a, const float* d_b, size_t n,
+                                  int device, void* stream) {
+    if (n == 0) return NVQ_OK;
+    NVQ_REQUIRE(d_out && d_a && d_b, "nvq_mul_f32: null buffer");
+    nvq_status s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    mul_kernel<<<ew_grid(n, device), 256, 0, (cudaStream_t)stream>>>(d_out, d_a, d_b, n);
     NVQ_LAUNCHED();
     return NVQ_OK;
 }

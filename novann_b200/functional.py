@@ -283,3 +283,14 @@ def linear_expanded_device(y: DeviceBuffer, x: DeviceBuffer, wd: DeviceBuffer,
                                         chan_scales.at(0) if chan_scales is not None else None,
                                         bias.at(0) if bias is not None else None, m, n, k, int(relu),
                                         x.device, _sptr(stream)))
+
+
+def mul_host(a, b, device: int = 0) -> np.ndarray:
+    """Elementwise fp32 product on the GPU (``ReLU.backward``: grad * mask)."""
+    a, b = _f32(a), _f32(b)
+    if a.shape != b.shape:
+        raise ValueError("shapes differ")
+    da, db = DeviceBuffer.from_numpy(a, device), DeviceBuffer.from_numpy(b, device)
+    o = DeviceBuffer(max(4, a.nbytes), device)
+    check(lib().nvq_mul_f32(o.at(0), da.at(0), db.at(0), a.size, device, None))
+    return o.to_numpy(np.float32, a.shape)

@@ -105,7 +105,7 @@ class ReLU(Layer):
         return out
 
     def backward(self, grad: np.ndarray) -> np.ndarray:
-        return grad * self._mask
+        return F.mul_host(grad, self._mask, self.device)
 
     def __repr__(self):
         return "ReLU()"
