@@ -223,30 +223,42 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             const int ct = threadIdx.x - 192;           // 0..255
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            // The raw codes of a k-block are read into registers one k-block ahead, so the
+            // shared-memory load latency is off the wait -> expand -> store -> arrive chain.
+            // Chunk i = 16 codes: row i/4, quarter i%4 of the 64-byte raw row; two chunks per
+            // thread.  Rows past a half-width tile's extent are read (inside the slot) and dropped.
+            uint4 nxt[2] = {};
+            auto load_codes = [&](uint32_t st) {
+                const uint32_t codes = tiles + st * STAGE_BYTES + A_BYTES + B_BYTES;
+#pragma unroll
+                for (int j = 0; j < 2; j++)
+                    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(nxt[j].x), "=r"(nxt[j].y), "=r"(nxt[j].z), "=r"(nxt[j].w)
+                                 : "r"(codes + (ct + 256 * j) * 16));
+            };
+            if (pair < p.num_items && num_kb > 0) {
+                ok = tc::mbar_wait(tc::smem_u32(&sh->raw_full[0]), 0, abort_flag, ERR_CONVERT);
+                if (ok) load_codes(0);
+            }
             for (int t = pair; t < p.num_items && ok; t += num_pairs) {
                 const TileRef tr = tile_ref(p, t);
                 const int rows_b = (tr.is_half ? BN / 2 : BN) / 2;
                 for (int kb = 0; kb < num_kb; kb++) {
-                    // the B slot is free once the MMAs of its previous use have completed ...
-                    ok = tc::mbar_wait(tc::smem_u32(&sh->empty[stage]), phase ^ 1, abort_flag, ERR_CONVERT);
-                    // ... and the codes of this k-block have landed
-                    ok = ok && tc::mbar_wait(tc::smem_u32(&sh->raw_full[stage]), phase, abort_flag, ERR_CONVERT);
+                    const uint4 in[2] = {nxt[0], nxt[1]};
+                    uint32_t nstage = stage + 1, nphase = phase;
+                    if (nstage == STAGES) { nstage = 0; nphase ^= 1; }
+                    if (kb + 1 < num_kb || t + num_pairs < p.num_items) {
+                        // the codes of the next k-block have landed (the producer runs ahead)
+                        ok = ok && tc::mbar_wait(tc::smem_u32(&sh->raw_full[nstage]), nphase, abort_flag, ERR_CONVERT);
+                        if (ok) load_codes(nstage);
+                    }
+                    // the B slot is free once the MMAs of its previous use have completed
+                    ok = ok && tc::mbar_wait(tc::smem_u32(&sh->empty[stage]), phase ^ 1, abort_flag, ERR_CONVERT);
                     ok = __all_sync(0xFFFFFFFFu, ok);
                     if (!ok) break;
                     const uint32_t b_dst = tiles + stage * STAGE_BYTES + A_BYTES;
-                    const uint32_t codes = b_dst + B_BYTES;
-                    // chunk i = 16 codes: row i/4, quarter i%4 of the 64-byte raw row -> 16-byte
-                    // chunks 2q, 2q+1 of the 128-byte operand row, placed by the 128-byte swizzle
-                    // (chunk index XOR row mod 8).  Two chunks per thread, loads first.
-                    uint4 in[2];
-#pragma unroll
-                    for (int j = 0; j < 2; j++) {
-                        const int i = ct + 256 * j;
-                        if (i < rows_b * 4)
-                            asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
-                                         : "=r"(in[j].x), "=r"(in[j].y), "=r"(in[j].z), "=r"(in[j].w)
-                                         : "r"(codes + i * 16));
-                    }
+                    // 16 codes -> 16-byte chunks 2q, 2q+1 of the 128-byte operand row, placed by
+                    // the 128-byte swizzle (chunk index XOR row mod 8)
 #pragma unroll
                     for (int j = 0; j < 2; j++) {
                         const int i = ct + 256 * j;
@@ -268,7 +280,8 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) tc::mbar_arrive_remote(tc::mapa(tc::smem_u32(&sh->full[stage]), 0));
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    stage = nstage;
+                    phase = nphase;
                 }
             }
         }
