@@ -334,6 +334,63 @@ nvq_status nvq_conv2d_fwd_q(float* d_out, const float* d_x, const uint8_t* d_wq,
                             int C, int H, int W, int Cout, int KH, int KW, int sh, int sw, int ph,
                             int pw, nvq_pad_mode mode, int device, void* stream);
 
+/* ---------------------------------------------------------------- BatchNorm, pooling, Dropout
+ * The layers either side of the GEMMs in NovaNN's CNN.  Activations are fp32 (N, C, S)
+ * row-major with S = H*W (BatchNorm2d), the sequence length (BatchNorm1d, 3-D input) or 1
+ * (BatchNorm1d, 2-D input).  NovaNN keeps gamma, beta and the running statistics as float64
+ * arrays, so they are float64 here; the fp32 output is the value every consumer in NovaNN
+ * obtains with astype(np.float32) from the float64 result.  Batch statistics are summed in
+ * float64, so they match NumPy's fp32 pairwise sums to rounding, not bit for bit.
+ */
+/* Bytes of float64 scratch the two BatchNorm calls need for C channels. */
+size_t nvq_batchnorm_scratch_bytes(int C);
+/* BatchNorm2d.forward (novann/layers/batchnorm/batchnorm2d.py:57-102) and BatchNorm1d.forward
+ * (batchnorm1d.py:96-141).  training != 0: batch mean and Bessel-corrected variance, running
+ * statistics updated in place, d_save_stats (2*C floats: mean, variance) kept for backward.
+ * training == 0: running statistics, float64 arithmetic; d_save_stats / d_scratch unused. */
+nvq_status nvq_batchnorm_fwd_f32(float* d_y, const float* d_x, const double* d_gamma,
+                                 const double* d_beta, double* d_running_mean,
+                                 double* d_running_var, float* d_save_stats, double* d_scratch,
+                                 int N, int C, int S, double momentum, double eps, int training,
+                                 int device, void* stream);
+/* BatchNorm2d.backward (batchnorm2d.py:104-146) / BatchNorm1d.backward: d_dgamma, d_dbeta
+ * (C float64 each; either may be NULL) and d_dx (may be NULL) from the forward input d_x and the
+ * statistics saved by the training forward. */
+nvq_status nvq_batchnorm_bwd_f32(float* d_dx, double* d_dgamma, double* d_dbeta, const float* d_grad,
+                                 const float* d_x, const float* d_save_stats, const double* d_gamma,
+                                 double* d_scratch, int N, int C, int S, double eps, int device,
+                                 void* stream);
+/* F.max_pool2d (novann/functional.py:450-536): pad (np.pad modes; zero padding takes part in the
+ * maximum), windows KHxKW at stride (sh, sw), np.max per window.  out is (N, C, OH, OW). */
+nvq_status nvq_maxpool2d_fwd_f32(float* d_out, const float* d_x, int N, int C, int H, int W, int KH,
+                                 int KW, int sh, int sw, int ph, int pw, nvq_pad_mode mode,
+                                 int device, void* stream);
+/* MaxPool2d.backward (novann/layers/pooling/maxpool/maxpool2d.py backward): the gradient of a
+ * window is split evenly over the entries equal to its maximum, windows are added in (oh, ow)
+ * order, gradient on padding is dropped.  Bit-exact with the reference. */
+nvq_status nvq_maxpool2d_bwd_f32(float* d_dx, const float* d_grad, const float* d_x, int N, int C,
+                                 int H, int W, int KH, int KW, int sh, int sw, int ph, int pw,
+                                 nvq_pad_mode mode, int device, void* stream);
+/* F.avg_pool2d (novann/functional.py:550-559): mean over each of `planes` = N*C planes of S
+ * elements; GlobalAvgPool2d.backward (novann/layers/pooling/gap/gap2d.py backward):
+ * dx = ones * (grad * float32(1/S)). */
+nvq_status nvq_gap2d_fwd_f32(float* d_out, const float* d_x, size_t planes, int S, int device,
+                             void* stream);
+nvq_status nvq_gap2d_bwd_f32(float* d_dx, const float* d_grad, size_t planes, int S, int device,
+                             void* stream);
+/* Dropout.forward / backward (novann/layers/regularization/dropout.py:40-70):
+ * out = (x * mask) / keep_prob with the 0/1 mask drawn by the caller (the reference draws it
+ * from NumPy's global generator, which only the host can reproduce). */
+nvq_status nvq_dropout_f32(float* d_out, const float* d_x, const float* d_mask, size_t n,
+                           float keep_prob, int device, void* stream);
+/* AdamW.step (novann/optim/adamw.py:41-65) on a float64 tensor (BatchNorm's gamma / beta);
+ * same operation order as nvq_adamw_step_f32, in float64. */
+nvq_status nvq_adamw_step_f64(double* d_param, const double* d_grad, double* d_m, double* d_v,
+                              size_t n, double beta1, double one_minus_beta1, double beta2,
+                              double one_minus_beta2, double bias_corr1, double bias_corr2, double lr,
+                              double eps, double lr_times_wd, int apply_decay, int device,
+                              void* stream);
+
 /* ---------------------------------------------------------------- data-parallel step
  * NCCL communicator for the gradient all-reduce of the data-parallel training step (no
  * reference counterpart: NovaNN is single process).  One process per GPU; rank 0 makes the

@@ -21,6 +21,7 @@ PAD_MODES = {"zeros": 0, "reflect": 1, "replicate": 2, "circular": 3}
 OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_NCCL = 0, -1, -2, -3, -4, -5
 
 vp, sz, i32, f32c, u64 = C.c_void_p, C.c_size_t, C.c_int, C.c_float, C.c_uint64
+f64c = C.c_double
 pvp = C.POINTER(C.c_void_p)
 
 # name -> (restype, argtypes).  Every symbol declared in include/nvq.h is listed here;
@@ -83,6 +84,15 @@ SIGNATURES = {
     "nvq_conv2d_fwd_f32": (i32, [vp, vp, vp, vp, vp] + [i32] * 11 + [i32, i32, vp]),
     "nvq_conv2d_bwd_f32": (i32, [vp] * 8 + [i32] * 11 + [i32, vp]),
     "nvq_conv2d_q_sizes": (i32, [i32] * 11 + [C.POINTER(sz), C.POINTER(sz)]),
+    "nvq_batchnorm_scratch_bytes": (sz, [i32]),
+    "nvq_batchnorm_fwd_f32": (i32, [vp] * 8 + [i32, i32, i32, f64c, f64c, i32, i32, vp]),
+    "nvq_batchnorm_bwd_f32": (i32, [vp] * 8 + [i32, i32, i32, f64c, i32, vp]),
+    "nvq_maxpool2d_fwd_f32": (i32, [vp, vp] + [i32] * 10 + [i32, i32, vp]),
+    "nvq_maxpool2d_bwd_f32": (i32, [vp, vp, vp] + [i32] * 10 + [i32, i32, vp]),
+    "nvq_gap2d_fwd_f32": (i32, [vp, vp, sz, i32, i32, vp]),
+    "nvq_gap2d_bwd_f32": (i32, [vp, vp, sz, i32, i32, vp]),
+    "nvq_dropout_f32": (i32, [vp, vp, vp, sz, f32c, i32, vp]),
+    "nvq_adamw_step_f64": (i32, [vp, vp, vp, vp, sz] + [f64c] * 9 + [i32, i32, vp]),
     "nvq_conv2d_fwd_q": (i32, [vp, vp, vp, i32, vp, vp, vp, vp, vp, sz] + [i32] * 11 + [i32, i32, vp]),
     "nvq_comm_unique_id": (i32, [vp]),
     "nvq_comm_init": (i32, [vp, i32, i32, i32, pvp]),

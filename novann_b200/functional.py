@@ -294,3 +294,109 @@ def mul_host(a, b, device: int = 0) -> np.ndarray:
     o = DeviceBuffer(max(4, a.nbytes), device)
     check(lib().nvq_mul_f32(o.at(0), da.at(0), db.at(0), a.size, device, None))
     return o.to_numpy(np.float32, a.shape)
+
+
+# ------------------------------------------------------------------ BatchNorm, pooling, Dropout
+def _f64(a):
+    return np.ascontiguousarray(a, np.float64)
+
+
+def _ncs(shape):
+    """(N, C, S) view of a BatchNorm input shape: (N,C), (N,C,L) or (N,C,H,W)."""
+    if len(shape) not in (2, 3, 4):
+        raise ValueError(f"BatchNorm expects 2D, 3D or 4D input, got {len(shape)}D")
+    return shape[0], shape[1], int(np.prod(shape[2:], dtype=np.int64))
+
+
+def batchnorm_fwd_host(x, gamma, beta, running_mean, running_var, momentum: float = 0.1,
+                       eps: float = 1e-5, training: bool = True, device: int = 0):
+    """``BatchNorm2d.forward`` / ``BatchNorm1d.forward`` (novann/layers/batchnorm/batchnorm2d.py:57-102,
+    batchnorm1d.py:96-141).  gamma / beta / running statistics: float64, C entries.  Returns
+    (y fp32, new_running_mean, new_running_var, save_stats): y is the float32 narrowing of the
+    reference's float64 result; save_stats (2, C) fp32 holds the batch mean and the
+    Bessel-corrected variance for ``batchnorm_bwd_host`` (None in evaluation mode)."""
+    x = _f32(x)
+    n, c, s = _ncs(x.shape)
+    dx = DeviceBuffer.from_numpy(x, device)
+    dg, db = DeviceBuffer.from_numpy(_f64(gamma).ravel(), device), DeviceBuffer.from_numpy(_f64(beta).ravel(), device)
+    drm = DeviceBuffer.from_numpy(_f64(running_mean).ravel(), device)
+    drv = DeviceBuffer.from_numpy(_f64(running_var).ravel(), device)
+    dy = DeviceBuffer(max(4, x.nbytes), device)
+    dst = DeviceBuffer(2 * c * 4, device)
+    dsc = DeviceBuffer(lib().nvq_batchnorm_scratch_bytes(c), device)
+    check(lib().nvq_batchnorm_fwd_f32(dy.at(0), dx.at(0), dg.at(0), db.at(0), drm.at(0), drv.at(0),
+                                      dst.at(0), dsc.at(0), n, c, s, float(momentum), float(eps),
+                                      int(bool(training)), device, None))
+    y = dy.to_numpy(np.float32, x.shape) if x.size else np.empty(x.shape, np.float32)
+    return (y, drm.to_numpy(np.float64, (c,)), drv.to_numpy(np.float64, (c,)),
+            dst.to_numpy(np.float32, (2, c)) if training and x.size else None)
+
+
+def batchnorm_bwd_host(grad, x, save_stats, gamma, eps: float = 1e-5, device: int = 0):
+    """``BatchNorm2d.backward`` (batchnorm2d.py:104-146): returns (dx fp32, dgamma, dbeta float64 (C,))."""
+    grad, x = _f32(grad), _f32(x)
+    n, c, s = _ncs(x.shape)
+    dgr, dx = DeviceBuffer.from_numpy(grad, device), DeviceBuffer.from_numpy(x, device)
+    dst = DeviceBuffer.from_numpy(_f32(save_stats), device)
+    dg = DeviceBuffer.from_numpy(_f64(gamma).ravel(), device)
+    o_dx = DeviceBuffer(max(4, x.nbytes), device)
+    o_dg, o_db = DeviceBuffer(c * 8, device), DeviceBuffer(c * 8, device)
+    dsc = DeviceBuffer(lib().nvq_batchnorm_scratch_bytes(c), device)
+    check(lib().nvq_batchnorm_bwd_f32(o_dx.at(0), o_dg.at(0), o_db.at(0), dgr.at(0), dx.at(0), dst.at(0),
+                                      dg.at(0), dsc.at(0), n, c, s, float(eps), device, None))
+    return (o_dx.to_numpy(np.float32, x.shape), o_dg.to_numpy(np.float64, (c,)),
+            o_db.to_numpy(np.float64, (c,)))
+
+
+def max_pool2d_host(x, kernel, stride, padding=(0, 0), padding_mode: str = "zeros", device: int = 0):
+    """``F.max_pool2d`` (novann/functional.py:450-536): (N, C, OH, OW) fp32."""
+    x = _f32(x)
+    n, c, h, w = x.shape
+    mode = _pad_mode(padding_mode)
+    oh = (h + 2 * padding[0] - kernel[0]) // stride[0] + 1
+    ow = (w + 2 * padding[1] - kernel[1]) // stride[1] + 1
+    dx = DeviceBuffer.from_numpy(x, device)
+    dy = DeviceBuffer(max(4, n * c * max(oh, 0) * max(ow, 0) * 4), device)
+    check(lib().nvq_maxpool2d_fwd_f32(dy.at(0), dx.at(0), n, c, h, w, kernel[0], kernel[1], stride[0],
+                                      stride[1], padding[0], padding[1], mode, device, None))
+    return dy.to_numpy(np.float32, (n, c, oh, ow))
+
+
+def max_pool2d_bwd_host(grad, x, kernel, stride, padding=(0, 0), padding_mode: str = "zeros",
+                        device: int = 0):
+    """``MaxPool2d.backward`` (novann/layers/pooling/maxpool/maxpool2d.py): dX (N, C, H, W)."""
+    grad, x = _f32(grad), _f32(x)
+    n, c, h, w = x.shape
+    dg, dx = DeviceBuffer.from_numpy(grad, device), DeviceBuffer.from_numpy(x, device)
+    o = DeviceBuffer(max(4, x.nbytes), device)
+    check(lib().nvq_maxpool2d_bwd_f32(o.at(0), dg.at(0), dx.at(0), n, c, h, w, kernel[0], kernel[1],
+                                      stride[0], stride[1], padding[0], padding[1],
+                                      _pad_mode(padding_mode), device, None))
+    return o.to_numpy(np.float32, x.shape)
+
+
+def avg_pool2d_host(x, device: int = 0):
+    """``F.avg_pool2d`` (novann/functional.py:550-559): (N, C, 1, 1) fp32."""
+    x = _f32(x)
+    n, c, h, w = x.shape
+    dx, o = DeviceBuffer.from_numpy(x, device), DeviceBuffer(max(4, n * c * 4), device)
+    check(lib().nvq_gap2d_fwd_f32(o.at(0), dx.at(0), n * c, h * w, device, None))
+    return o.to_numpy(np.float32, (n, c, 1, 1))
+
+
+def avg_pool2d_bwd_host(grad, x_shape, device: int = 0):
+    """``GlobalAvgPool2d.backward``: (N, C, H, W) fp32."""
+    grad = _f32(grad)
+    n, c, h, w = x_shape
+    dg, o = DeviceBuffer.from_numpy(grad, device), DeviceBuffer(max(4, n * c * h * w * 4), device)
+    check(lib().nvq_gap2d_bwd_f32(o.at(0), dg.at(0), n * c, h * w, device, None))
+    return o.to_numpy(np.float32, (n, c, h, w))
+
+
+def dropout_host(x, mask, keep_prob: float, device: int = 0):
+    """``(x * mask) / keep_prob`` (novann/layers/regularization/dropout.py:52-54, :66)."""
+    x, mask = _f32(x), _f32(mask)
+    dx, dm = DeviceBuffer.from_numpy(x, device), DeviceBuffer.from_numpy(mask, device)
+    o = DeviceBuffer(max(4, x.nbytes), device)
+    check(lib().nvq_dropout_f32(o.at(0), dx.at(0), dm.at(0), x.size, C.c_float(keep_prob), device, None))
+    return o.to_numpy(np.float32, x.shape)

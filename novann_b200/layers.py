@@ -242,3 +242,191 @@ class QuantConv2d(Conv2d):
         b = None if self.bias is None else self.bias.data.reshape(-1)
         return F.conv2d_q_host(x, self._codes, self._scales, b, (self.KH, self.KW), (self.sh, self.sw),
                                (self.ph, self.pw), self.pm, self.fmt, self.device)
+
+
+class _BatchNorm(Layer):
+    """Shared body of ``BatchNorm1d`` / ``BatchNorm2d``.  As in the reference, gamma, beta and the
+    running statistics are float64 arrays.  The reference's forward therefore returns float64,
+    which every consumer narrows with ``astype(np.float32)``; here the narrowed fp32 value is
+    returned directly (and likewise for the input gradient)."""
+
+    _param_shape = None     # set by subclasses: shape of gamma / beta for a given C
+
+    def __init__(self, num_features: int, momentum: float = 0.1, eps: float = 1e-5, device: int = 0):
+        super().__init__()
+        self.num_features = int(num_features)
+        self.momentum, self.eps = float(momentum), float(eps)
+        self.device = device
+        shp = self._shape()
+        self.gamma = Parameters(np.ones(shp))
+        self.beta = Parameters(np.zeros(shp))
+        self.gamma.name, self.beta.name = "gamma", "beta"
+        self.running_mean = np.zeros(shp)
+        self.running_var = np.ones(shp)
+        self._x = self._stats = None
+
+    def _check(self, x):
+        raise NotImplementedError
+
+    def forward(self, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x.astype(np.float32, copy=False))
+        self._check(x)
+        y, rm, rv, stats = F.batchnorm_fwd_host(x, self.gamma.data, self.beta.data, self.running_mean,
+                                                self.running_var, self.momentum, self.eps,
+                                                self._training, self.device)
+        if self._training:
+            self._x, self._stats = x, stats
+            self.running_mean = rm.reshape(self.running_mean.shape)
+            self.running_var = rv.reshape(self.running_var.shape)
+        return y
+
+    def backward(self, grad: np.ndarray) -> np.ndarray:
+        if self._x is None or self._stats is None:
+            raise ValueError("Backward called before forward pass or cache cleared")
+        dx, dg, db = F.batchnorm_bwd_host(grad, self._x, self._stats, self.gamma.data, self.eps, self.device)
+        self.gamma.grad = dg.reshape(self.gamma.data.shape)
+        self.beta.grad = db.reshape(self.beta.data.shape)
+        return dx
+
+    def parameters(self):
+        return [self.gamma, self.beta]
+
+    def __repr__(self):
+        return f"{type(self).__name__}(num_features={self.num_features}, momentum={self.momentum}, eps={self.eps})"
+
+
+class BatchNorm2d(_BatchNorm):
+    """``novann/layers/batchnorm/batchnorm2d.py``: per-channel statistics over (N, H, W);
+    parameters shaped (1, C, 1, 1)."""
+
+    def _shape(self):
+        return (1, self.num_features, 1, 1)
+
+    def _check(self, x):
+        if x.ndim != 4 or x.shape[1] != self.num_features:
+            raise ValueError(f"BatchNorm2d expects (N, {self.num_features}, H, W) input, got {x.shape}")
+
+
+class BatchNorm1d(_BatchNorm):
+    """``novann/layers/batchnorm/batchnorm1d.py``: statistics over the batch for (N, C) input, over
+    batch and length for (N, C, L) input (gamma / beta are then reshaped to (1, C, 1), as the
+    reference does)."""
+
+    def _shape(self):
+        return (1, self.num_features)
+
+    def _check(self, x):
+        if x.ndim not in (2, 3):
+            raise ValueError(f"BatchNorm1d expects 2D or 3D input, got {x.ndim}D")
+        if x.shape[1] != self.num_features:
+            raise ValueError(f"BatchNorm1d expects {self.num_features} features, got {x.shape[1]}")
+        if x.ndim == 3:
+            self.gamma.data = self.gamma.data.reshape(1, self.num_features, 1)
+            self.beta.data = self.beta.data.reshape(1, self.num_features, 1)
+
+
+class MaxPool2d(Layer):
+    """``novann/layers/pooling/maxpool/maxpool2d.py``: windows over the padded input; ties share
+    the gradient evenly."""
+
+    def __init__(self, kernel_size, stride=None, padding=0, padding_mode: str = "zeros", device: int = 0):
+        super().__init__()
+        self.KH, self.KW = _pair(kernel_size)
+        self.sh, self.sw = _pair(stride if stride is not None else kernel_size)
+        self.ph, self.pw = _pair(padding)
+        self.pm = padding_mode
+        self.device = device
+        self._x = None
+
+    def forward(self, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x.astype(np.float32, copy=False))
+        self._x = x
+        return F.max_pool2d_host(x, (self.KH, self.KW), (self.sh, self.sw), (self.ph, self.pw), self.pm,
+                                 self.device)
+
+    def backward(self, grad_output: np.ndarray) -> np.ndarray:
+        grad_output = np.ascontiguousarray(grad_output.astype(np.float32, copy=False))
+        dx = F.max_pool2d_bwd_host(grad_output, self._x, (self.KH, self.KW), (self.sh, self.sw),
+                                   (self.ph, self.pw), self.pm, self.device)
+        self._x = None
+        return dx
+
+    def __repr__(self):
+        return f"MaxPool2d(kernel_size={(self.KH, self.KW)}, stride={(self.sh, self.sw)}, padding={(self.ph, self.pw)})"
+
+
+class GlobalAvgPool2d(Layer):
+    """``novann/layers/pooling/gap/gap2d.py``: (N, C, H, W) -> (N, C, 1, 1)."""
+
+    def __init__(self, device: int = 0):
+        super().__init__()
+        self.device = device
+        self._x_shape = None
+
+    def forward(self, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x.astype(np.float32, copy=False))
+        self._x_shape = x.shape
+        return F.avg_pool2d_host(x, self.device)
+
+    def backward(self, grad_output: np.ndarray) -> np.ndarray:
+        return F.avg_pool2d_bwd_host(grad_output.astype(np.float32, copy=False), self._x_shape, self.device)
+
+    def __repr__(self):
+        return "GlobalAvgPool2d()"
+
+
+class Flatten(Layer):
+    """``novann/layers/flatten/flatten.py``: a reshape; nothing to compute."""
+
+    def __init__(self):
+        super().__init__()
+        self._origin_shape = None
+
+    def forward(self, x: np.ndarray) -> np.ndarray:
+        self._origin_shape = x.shape
+        return x.reshape(x.shape[0], -1)
+
+    def backward(self, grad: np.ndarray) -> np.ndarray:
+        return grad.reshape(*self._origin_shape)
+
+    def __repr__(self):
+        return "Flatten()"
+
+
+class Dropout(Layer):
+    """``novann/layers/regularization/dropout.py``: the keep mask is drawn on the host from
+    NumPy's global generator with the reference's own call (so a seeded run drops the same
+    units); the masking and scaling run on the GPU."""
+
+    def __init__(self, p: float, device: int = 0) -> None:
+        super().__init__()
+        if not (0.0 < p < 1.0):
+            raise ValueError("Dropout probability must be in the interval [0.0, 1.0).")
+        self.p = p
+        self.device = device
+        self._mask = None
+
+    def train(self) -> None:
+        super().train()
+        self._mask = None
+
+    def eval(self) -> None:
+        super().eval()
+        self._mask = None
+
+    def forward(self, x: np.ndarray) -> np.ndarray:
+        if not self._training or self.p == 0.0:
+            return x
+        keep = 1.0 - self.p
+        self._mask = (np.random.rand(*x.shape) < keep).astype(np.float32)
+        return F.dropout_host(x, self._mask, keep, self.device)
+
+    def backward(self, grad: np.ndarray) -> np.ndarray:
+        if not self._training:
+            return grad
+        out = F.dropout_host(grad, self._mask, 1.0 - self.p, self.device)
+        self._mask = None
+        return out
+
+    def __repr__(self):
+        return f"Dropout(p={self.p})"

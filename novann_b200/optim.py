@@ -48,26 +48,28 @@ class AdamW:
         self.b1, self.b2, self.eps = float(betas[0]), float(betas[1]), float(epsilon)
         self.device = device
         self.t = 0
-        self._m = [DeviceBuffer(max(4, p.data.nbytes), device) for p in self.params]
-        self._v = [DeviceBuffer(max(4, p.data.nbytes), device) for p in self.params]
+        self._m = [DeviceBuffer(max(8, p.data.nbytes), device) for p in self.params]
+        self._v = [DeviceBuffer(max(8, p.data.nbytes), device) for p in self.params]
         for b in self._m + self._v:
             b.zero()
 
     def step(self) -> None:
         self.t += 1
-        f = C.c_float
         for i, p in enumerate(self.params):
             if p.grad is None:
                 continue
             decay = self.wd > 0 and getattr(p, "name", None) not in ("gamma", "beta")
-            d = DeviceBuffer.from_numpy(np.ascontiguousarray(p.data, np.float32), self.device)
-            g = DeviceBuffer.from_numpy(np.ascontiguousarray(p.grad, np.float32), self.device)
-            check(lib().nvq_adamw_step_f32(
-                d.at(0), g.at(0), self._m[i].at(0), self._v[i].at(0), p.data.size,
-                f(self.b1), f(1 - self.b1), f(self.b2), f(1 - self.b2), f(1 - self.b1 ** self.t),
-                f(1 - self.b2 ** self.t), f(self.lr), f(self.eps), f(self.lr * self.wd), int(decay),
-                self.device, None))
-            p.data[...] = d.to_numpy(np.float32, p.data.shape)
+            # float64 tensors (BatchNorm's gamma / beta) are stepped in float64, as NumPy would
+            wide = p.data.dtype == np.float64
+            dt, f = (np.float64, C.c_double) if wide else (np.float32, C.c_float)
+            fn = lib().nvq_adamw_step_f64 if wide else lib().nvq_adamw_step_f32
+            d = DeviceBuffer.from_numpy(np.ascontiguousarray(p.data, dt), self.device)
+            g = DeviceBuffer.from_numpy(np.ascontiguousarray(p.grad, dt), self.device)
+            check(fn(d.at(0), g.at(0), self._m[i].at(0), self._v[i].at(0), p.data.size,
+                     f(self.b1), f(1 - self.b1), f(self.b2), f(1 - self.b2), f(1 - self.b1 ** self.t),
+                     f(1 - self.b2 ** self.t), f(self.lr), f(self.eps), f(self.lr * self.wd), int(decay),
+                     self.device, None))
+            p.data[...] = d.to_numpy(dt, p.data.shape)
 
     def zero_grad(self, set_to_none: bool = False) -> None:
         for p in self.params:

@@ -97,3 +97,26 @@ def mlp_inputs(batch: int = 128, dims=(784, 256, 128, 10), seed: int = 0):
                        * np.float32(np.sqrt(2.0 / fi))).astype(np.float32))
         params.append(np.zeros((1, fo), np.float32))
     return x, y, params
+
+
+def cnn_inputs(batch: int = 128, steps: int = 1, seed: int = 0):
+    """Seeded stand-in for the reference's MNIST CNN job (main.py:14-46): ``steps`` batches of
+    normalised-pixel-like images U[0,1] fp32 (batch, 1, 28, 28) with labels in [0, 10), and the
+    parameter list of that CNN in ``Sequential.parameters()`` order -- conv weights N(0, 2/fan_in)
+    fp32, BatchNorm gamma ~ 1 and beta ~ 0 as float64 (the reference's dtype for them) with the
+    reference's shapes, Linear weights fp32, final bias (1, 10)."""
+    rng = np.random.default_rng(seed)
+    x = rng.random((steps, batch, 1, 28, 28), dtype=np.float32)
+    y = rng.integers(0, 10, (steps, batch)).astype(np.int64)
+
+    def w(*shape):
+        fan_in = int(np.prod(shape[1:]))
+        return (rng.standard_normal(shape) * np.sqrt(2.0 / fan_in)).astype(np.float32)
+
+    def bn(c, nd):
+        shp = (1, c, 1, 1) if nd == 4 else (1, c)
+        return [1.0 + 0.1 * rng.standard_normal(shp), 0.1 * rng.standard_normal(shp)]
+
+    params = [w(16, 1, 3, 3), *bn(16, 4), w(32, 16, 3, 3), *bn(32, 4), w(64, 32, 3, 3), *bn(64, 4),
+              w(32, 64), *bn(32, 2), w(10, 32), (0.01 * rng.standard_normal((1, 10))).astype(np.float32)]
+    return x, y, params

@@ -521,3 +521,243 @@ def adamw_step(p, g, m, v, t, lr, b1=0.9, b2=0.999, eps=1e-8, wd=0.0, decay=True
     if wd > 0 and decay:
         p = p - lr * wd * p
     return p.astype(np.float32), m.astype(np.float32), v.astype(np.float32)
+
+
+# ----------------------------------------------------------------------------
+# BatchNorm, pooling, Dropout and the CNN step of the reference's main.py
+# ----------------------------------------------------------------------------
+def _bn_axes(x):
+    if x.ndim == 4:
+        return (0, 2, 3), (1, -1, 1, 1)
+    if x.ndim == 3:
+        return (0, 2), (1, -1, 1)
+    if x.ndim == 2:
+        return (0,), (1, -1)
+    raise ValueError(f"BatchNorm expects 2D, 3D or 4D input, got {x.ndim}D")
+
+
+def batchnorm_fwd(x, gamma, beta, running_mean, running_var, momentum=0.1, eps=1e-5, training=True):
+    """``BatchNorm2d.forward`` (novann/layers/batchnorm/batchnorm2d.py:57-102) and
+    ``BatchNorm1d.forward`` (batchnorm1d.py:96-141).  gamma / beta / running statistics are
+    float64 vectors of length C (the reference creates them with np.ones / np.zeros), x is
+    fp32.  Returns (out float64, new_running_mean, new_running_var, cache); the cache holds
+    what backward needs.  The float64 output is what the reference returns; its consumers
+    narrow it with astype(float32)."""
+    x = np.asarray(x, np.float32)
+    axes, shp = _bn_axes(x)
+    ga, be = np.asarray(gamma, np.float64).reshape(shp), np.asarray(beta, np.float64).reshape(shp)
+    rm, rv = np.asarray(running_mean, np.float64).reshape(shp), np.asarray(running_var, np.float64).reshape(shp)
+    m = x.size // x.shape[1]
+    if not training:
+        x_hat = (x - rm) / np.sqrt(rv + eps)
+        return ga * x_hat + be, rm.ravel(), rv.ravel(), None
+    mu = np.mean(x, axis=axes, keepdims=True)
+    var = np.var(x, axis=axes, keepdims=True)
+    if m > 1:
+        var = var * (m / (m - 1))
+    x_mu = x - mu
+    x_hat = x_mu / np.sqrt(var + eps)
+    out = ga * x_hat + be
+    new_rm = (1 - momentum) * rm + momentum * mu
+    new_rv = (1 - momentum) * rv + momentum * var
+    cache = dict(x_hat=x_hat, x_mu=x_mu, var=var, mu=mu, m=m, axes=axes, gamma=ga, eps=eps)
+    return out, new_rm.ravel(), new_rv.ravel(), cache
+
+
+def batchnorm_bwd(grad, cache):
+    """``BatchNorm2d.backward`` (batchnorm2d.py:104-146).  Returns (dx, dgamma, dbeta), the
+    parameter gradients as flat length-C vectors."""
+    x_hat, x_mu, var, m, axes, ga, eps = (cache[k] for k in ("x_hat", "x_mu", "var", "m", "axes", "gamma", "eps"))
+    dgamma = np.sum(grad * x_hat, axis=axes, keepdims=True)
+    dbeta = np.sum(grad, axis=axes, keepdims=True)
+    dx_hat = grad * ga
+    inv_std = (var + eps) ** (-0.5)
+    inv_std3 = (var + eps) ** (-1.5)
+    dvar = np.sum(dx_hat * x_mu * (-0.5) * inv_std3, axis=axes, keepdims=True)
+    dmu = np.sum(dx_hat * (-inv_std), axis=axes, keepdims=True) + \
+        dvar * np.sum(-2.0 * x_mu, axis=axes, keepdims=True) / m
+    dx = dx_hat * inv_std + dvar * (2.0 * x_mu) / m + dmu / m
+    return dx, dgamma.ravel(), dbeta.ravel()
+
+
+def _pool_windows(x, kh, kw, sh, sw, ph, pw, padding_mode):
+    """(N, C, OH, OW, KH, KW) windows of the padded input, gathered explicitly."""
+    if padding_mode not in _PAD_MODES:
+        raise ValueError(f"padding_mode Only accept {tuple(_PAD_MODES)} not '{padding_mode}'")
+    n, c, h, w = x.shape
+    xp = np.pad(x, ((0, 0), (0, 0), (ph, ph), (pw, pw)), mode=_PAD_MODES[padding_mode])
+    oh, ow = conv2d_out_size(h, w, kh, kw, sh, sw, ph, pw)
+    win = np.empty((n, c, oh, ow, kh, kw), x.dtype)
+    for i in range(kh):
+        for j in range(kw):
+            win[..., i, j] = xp[:, :, i:i + sh * oh:sh, j:j + sw * ow:sw]
+    return win, xp.shape
+
+
+def maxpool2d_fwd(x, kernel, stride=None, padding=(0, 0), padding_mode="zeros"):
+    """``F.max_pool2d`` (novann/functional.py:450-536).  Returns (out, windows, padded_shape)."""
+    x = np.asarray(x, np.float32)
+    stride = kernel if stride is None else stride
+    win, pshape = _pool_windows(x, kernel[0], kernel[1], stride[0], stride[1], padding[0], padding[1],
+                                padding_mode)
+    return win.max(axis=(4, 5)), win, pshape
+
+
+def maxpool2d_bwd(grad, windows, padded_shape, x_shape, kernel, stride, padding):
+    """``MaxPool2d.backward`` (novann/layers/pooling/maxpool/maxpool2d.py): ties share the
+    gradient evenly; windows are added back in (oh, ow) order; padding is cropped."""
+    grad = np.asarray(grad, np.float32)
+    kh, kw = kernel
+    sh, sw = stride
+    ph, pw = padding
+    mx = windows.max(axis=(4, 5), keepdims=True)
+    mask = (windows == mx).astype(np.float32)
+    counts = mask.sum(axis=(4, 5), keepdims=True)
+    counts[counts == 0] = 1.0
+    gw = mask * (grad[..., None, None] / counts)
+    dxp = np.zeros(padded_shape, np.float32)
+    for i in range(grad.shape[2]):
+        for j in range(grad.shape[3]):
+            dxp[:, :, i * sh:i * sh + kh, j * sw:j * sw + kw] += gw[:, :, i, j]
+    h, w = x_shape[2], x_shape[3]
+    return np.ascontiguousarray(dxp[:, :, ph:ph + h, pw:pw + w])
+
+
+def gap2d_fwd(x):
+    """``F.avg_pool2d`` (novann/functional.py:550-559) on fp32 input."""
+    return np.mean(np.asarray(x, np.float32), axis=(2, 3), keepdims=True)
+
+
+def gap2d_bwd(grad, x_shape):
+    """``GlobalAvgPool2d.backward``: ones * (grad * (1 / (H*W)))."""
+    grad = np.asarray(grad, np.float32)
+    factor = 1.0 / (x_shape[2] * x_shape[3])
+    return np.ones(x_shape, np.float32) * (grad * factor)
+
+
+def dropout(x, mask, p):
+    """``Dropout.forward`` / ``backward`` (novann/layers/regularization/dropout.py:40-70) with
+    the mask given: (x * mask) / (1 - p)."""
+    return (x * mask) / (1.0 - p)
+
+
+def cnn_main_spec():
+    """The layer list of the reference's main.py (main.py:24-46) as (kind, args) tuples."""
+    return [
+        ("conv", dict(cin=1, cout=16, k=3, s=1, p=1)), ("bn2d", dict(c=16)), ("relu", {}),
+        ("conv", dict(cin=16, cout=32, k=3, s=2, p=1)), ("bn2d", dict(c=32)), ("relu", {}),
+        ("maxpool", dict(k=2, s=2)),
+        ("conv", dict(cin=32, cout=64, k=3, s=1, p=1)), ("bn2d", dict(c=64)), ("relu", {}),
+        ("gap", {}), ("flatten", {}),
+        ("linear", dict(fin=64, fout=32, bias=False)), ("bn1d", dict(c=32)), ("relu", {}),
+        ("dropout", dict(p=0.5)),
+        ("linear", dict(fin=32, fout=10, bias=True)),
+    ]
+
+
+def cnn_train_step(spec, params, state, x, labels, drop_masks, opt, t):
+    """One training step of a Sequential CNN given as ``spec`` (see ``cnn_main_spec``):
+    zero_grad -> forward -> CrossEntropyLoss -> backward -> AdamW.step, written layer by layer
+    with the functions above (novann/model/nn.py:185-223 drives the same loop).
+
+    params: list in ``Sequential.parameters()`` order (conv weight; bn gamma, beta (float64);
+    linear weight [, bias (1, N)]).  state: {"running": [(mean, var) per BatchNorm], "m": [...],
+    "v": [...]} AdamW moments per parameter.  drop_masks: one 0/1 array per Dropout layer.
+    opt: dict(lr, b1, b2, eps, wd).  Returns dict(logits, loss, grads, params, state)."""
+    pi = bi = di = 0
+    tape = []
+    h = np.asarray(x, np.float32)
+    for kind, a in spec:
+        if kind == "conv":
+            w = params[pi]
+            h32 = h.astype(np.float32, copy=False)
+            col, _, _ = im2col(h32, a["k"], a["k"], a["s"], a["s"], a["p"], a["p"])
+            out = conv2d_fwd_f32(h32, w, None, (a["s"], a["s"]), (a["p"], a["p"]))
+            tape.append((kind, a, pi, dict(col=col, x_shape=h32.shape)))
+            pi += 1
+            h = out
+        elif kind in ("bn2d", "bn1d"):
+            ga, be = params[pi], params[pi + 1]
+            rm, rv = state["running"][bi]
+            out, nrm, nrv, cache = batchnorm_fwd(h.astype(np.float32, copy=False), ga.ravel(), be.ravel(),
+                                                 rm, rv, training=True)
+            state["running"][bi] = (nrm, nrv)
+            tape.append((kind, a, pi, cache))
+            pi += 2
+            bi += 1
+            h = out
+        elif kind == "relu":
+            mask = (h > 0).astype(h.dtype)
+            tape.append((kind, a, None, mask))
+            h = h * mask
+        elif kind == "maxpool":
+            h32 = h.astype(np.float32, copy=False)
+            out, win, pshape = maxpool2d_fwd(h32, (a["k"], a["k"]), (a["s"], a["s"]))
+            tape.append((kind, a, None, dict(win=win, pshape=pshape, x_shape=h32.shape)))
+            h = out
+        elif kind == "gap":
+            h32 = h.astype(np.float32, copy=False)
+            tape.append((kind, a, None, h32.shape))
+            h = gap2d_fwd(h32)
+        elif kind == "flatten":
+            tape.append((kind, a, None, h.shape))
+            h = h.reshape(h.shape[0], -1)
+        elif kind == "linear":
+            w = params[pi]
+            b = params[pi + 1] if a["bias"] else None
+            h32 = h.astype(np.float32, copy=False)
+            tape.append((kind, a, pi, h32))
+            h = h32 @ w.T
+            if b is not None:
+                h = h + b
+            pi += 2 if a["bias"] else 1
+        elif kind == "dropout":
+            mask = drop_masks[di].astype(h.dtype)
+            di += 1
+            tape.append((kind, a, None, mask))
+            h = dropout(h, mask, a["p"])
+        else:
+            raise ValueError(kind)
+    logits = h
+    loss, g = softmax_ce(logits, labels)
+    grads = [None] * len(params)
+    for kind, a, p0, c in reversed(tape):
+        if kind == "conv":
+            dw, _, dx = conv2d_bwd_f32(g.astype(np.float32, copy=False), c["col"], params[p0], c["x_shape"],
+                                       (a["s"], a["s"]), (a["p"], a["p"]))
+            grads[p0] = dw
+            g = dx
+        elif kind in ("bn2d", "bn1d"):
+            dx, dga, dbe = batchnorm_bwd(g, c)
+            grads[p0], grads[p0 + 1] = dga.reshape(params[p0].shape), dbe.reshape(params[p0 + 1].shape)
+            g = dx
+        elif kind == "relu":
+            g = g * c
+        elif kind == "maxpool":
+            g = maxpool2d_bwd(g.astype(np.float32, copy=False), c["win"], c["pshape"], c["x_shape"],
+                              (a["k"], a["k"]), (a["s"], a["s"]), (0, 0))
+        elif kind == "gap":
+            g = gap2d_bwd(g, c)
+        elif kind == "flatten":
+            g = g.reshape(c)
+        elif kind == "linear":
+            g32 = g.astype(np.float32, copy=False)
+            grads[p0] = g32.T @ c
+            if a["bias"]:
+                grads[p0 + 1] = np.sum(g32, axis=0, keepdims=True)
+            g = g32 @ params[p0]
+        elif kind == "dropout":
+            g = dropout(g, c, a["p"])
+    new = []
+    for i, (p, gr) in enumerate(zip(params, grads)):
+        is_bn = p.dtype == np.float64
+        m = opt["b1"] * state["m"][i] + (1 - opt["b1"]) * gr
+        v = opt["b2"] * state["v"][i] + (1 - opt["b2"]) * (gr ** 2)
+        m_hat = m / (1 - opt["b1"] ** t)
+        v_hat = v / (1 - opt["b2"] ** t)
+        q = p - opt["lr"] * m_hat / (np.sqrt(v_hat) + opt["eps"])
+        if opt["wd"] > 0 and not is_bn:
+            q = q - opt["lr"] * opt["wd"] * q
+        state["m"][i], state["v"][i] = m.astype(p.dtype), v.astype(p.dtype)
+        new.append(q.astype(p.dtype))
+    return dict(logits=logits, loss=loss, grads=grads, params=new, state=state)

@@ -147,6 +147,117 @@ def main():
         opt.step()
         ad[f"p{t + 1}"], ad[f"q{t + 1}"] = pa.data.copy(), pg.data.copy()
     out["adamw"] = ad
+    # ---- BatchNorm2d / BatchNorm1d: training forward + backward + running statistics, then an
+    # evaluation forward with the updated statistics
+    from novann.layers import BatchNorm1d, BatchNorm2d, Dropout, Flatten, GlobalAvgPool2d, MaxPool2d
+    bn = {}
+    bn_cases = [("2d", (6, 5, 7, 4)), ("2d", (24, 8, 6, 5)), ("1d", (9, 12)), ("1d", (4, 6, 10)),
+                ("2d", (1, 3, 1, 1))]
+    for i, (kind, shape) in enumerate(bn_cases):
+        layer = (BatchNorm2d if kind == "2d" else BatchNorm1d)(shape[1])
+        layer.train()
+        layer.gamma.data = rs.standard_normal(layer.gamma.data.shape) * 0.5 + 1.0
+        layer.beta.data = rs.standard_normal(layer.beta.data.shape) * 0.3
+        layer.running_mean = rs.standard_normal(layer.running_mean.shape) * 0.1
+        layer.running_var = rs.random(layer.running_var.shape) + 0.5
+        xb = (rs.standard_normal(shape) * 2.0 + 0.7).astype(np.float32)
+        gb = rs.standard_normal(shape).astype(np.float32)
+        bn[f"x{i}"], bn[f"g{i}"] = xb, gb
+        bn[f"gamma{i}"], bn[f"beta{i}"] = layer.gamma.data.ravel().copy(), layer.beta.data.ravel().copy()
+        bn[f"rm{i}"], bn[f"rv{i}"] = layer.running_mean.ravel().copy(), layer.running_var.ravel().copy()
+        yb = layer.forward(xb)
+        dxb = layer.backward(gb)
+        bn[f"y{i}"], bn[f"dx{i}"] = yb, dxb
+        bn[f"dgamma{i}"], bn[f"dbeta{i}"] = layer.gamma.grad.ravel().copy(), layer.beta.grad.ravel().copy()
+        bn[f"rm_new{i}"], bn[f"rv_new{i}"] = layer.running_mean.ravel().copy(), layer.running_var.ravel().copy()
+        layer.eval()
+        bn[f"y_eval{i}"] = layer.forward(xb)
+    bn["n_cases"] = np.array(len(bn_cases))
+    out["batchnorm"] = bn
+    # ---- MaxPool2d (ties, zero padding taking part in the maximum, every padding mode),
+    # GlobalAvgPool2d, Dropout
+    pool = {}
+    pool_cases = [
+        dict(shape=(2, 3, 8, 8), k=(2, 2), s=None, p=(0, 0), mode="zeros"),
+        dict(shape=(2, 2, 9, 7), k=(3, 3), s=(2, 2), p=(1, 1), mode="zeros"),
+        dict(shape=(1, 2, 7, 9), k=(3, 2), s=(1, 2), p=(1, 1), mode="reflect"),
+        dict(shape=(2, 1, 6, 6), k=(3, 3), s=(1, 1), p=(2, 2), mode="replicate"),
+        dict(shape=(1, 3, 5, 8), k=(2, 3), s=(2, 1), p=(1, 2), mode="circular"),
+        dict(shape=(3, 4, 14, 14), k=(2, 2), s=(2, 2), p=(0, 0), mode="zeros"),
+    ]
+    for i, cs in enumerate(pool_cases):
+        layer = MaxPool2d(cs["k"], cs["s"], cs["p"], cs["mode"])
+        xp_ = rs.standard_normal(cs["shape"]).astype(np.float32)
+        if i in (0, 1):
+            xp_ = np.round(xp_ * 2) / 2          # coarse grid: many ties, many negative windows
+        if i == 1:
+            xp_ -= 1.0                            # mostly negative: the zero padding wins at the border
+        yp = layer.forward(xp_)
+        gp_ = rs.standard_normal(yp.shape).astype(np.float32)
+        dxp = layer.backward(gp_)
+        st = cs["s"] if cs["s"] is not None else cs["k"]
+        pool[f"x{i}"], pool[f"y{i}"], pool[f"g{i}"], pool[f"dx{i}"] = xp_, yp, gp_, np.ascontiguousarray(dxp)
+        pool[f"geom{i}"] = np.array([*cs["k"], *st, *cs["p"],
+                                     ["zeros", "reflect", "replicate", "circular"].index(cs["mode"])])
+    pool["n_cases"] = np.array(len(pool_cases))
+    gap = GlobalAvgPool2d()
+    xg = rs.standard_normal((5, 6, 7, 7)).astype(np.float32)
+    pool["gap_x"], pool["gap_y"] = xg, gap.forward(xg)
+    gg = rs.standard_normal((5, 6, 1, 1)).astype(np.float32)
+    pool["gap_g"], pool["gap_dx"] = gg, gap.backward(gg)
+    for i, pdrop in enumerate((0.5, 0.3)):
+        dr = Dropout(pdrop)
+        dr.train()
+        xd = rs.standard_normal((8, 16)).astype(np.float32)
+        np.random.seed(77 + i)
+        yd = dr.forward(xd)
+        pool[f"drop_x{i}"], pool[f"drop_y{i}"], pool[f"drop_mask{i}"] = xd, yd, dr._mask.copy()
+        gd = rs.standard_normal((8, 16)).astype(np.float32)
+        pool[f"drop_g{i}"], pool[f"drop_dx{i}"] = gd, dr.backward(gd)
+        pool[f"drop_p{i}"] = np.float64(pdrop)
+    out["pool_dropout"] = pool
+    # ---- the CNN of main.py, two AdamW training steps at batch 16 on seeded inputs.  Weights are
+    # assigned (the reference's own initialisers play no part); the Dropout masks the reference
+    # drew are stored.
+    from novann_b200 import workloads as wl
+    cnn = {}
+    x_all, y_all, cparams = wl.cnn_inputs(16, steps=2, seed=3)
+    model = Sequential(
+        Conv2d(1, 16, 3, padding=1, bias=False), BatchNorm2d(16), ReLU(),
+        Conv2d(16, 32, 3, padding=1, stride=2, bias=False), BatchNorm2d(32), ReLU(),
+        MaxPool2d(2, 2),
+        Conv2d(32, 64, 3, padding=1, bias=False), BatchNorm2d(64), ReLU(),
+        GlobalAvgPool2d(), Flatten(),
+        Linear(64, 32, bias=False), BatchNorm1d(32), ReLU(), Dropout(0.5), Linear(32, 10))
+    model.train()
+    plist = model.parameters()
+    assert len(plist) == len(cparams), (len(plist), len(cparams))
+    for pr, val in zip(plist, cparams):
+        assert pr.data.shape == val.shape, (pr.data.shape, val.shape)
+        pr.data = val.copy()
+    opt = AdamW(model.parameters(), lr=1e-3, betas=(0.9, 0.999), weight_decay=1e-2, epsilon=1e-8)
+    loss_fn = CrossEntropyLoss()
+    drop_layer = [l for l in model._layers if isinstance(l, Dropout)][0]
+    bns = [l for l in model._layers if isinstance(l, (BatchNorm1d, BatchNorm2d))]
+    for t in range(2):
+        np.random.seed(500 + t)
+        opt.zero_grad()
+        logits = model(x_all[t])
+        cnn[f"mask{t}"] = drop_layer._mask.astype(np.float32)
+        loss, grad = loss_fn(logits, y_all[t])
+        model.backward(grad)
+        cnn[f"logits{t}"], cnn[f"loss{t}"] = logits, np.float32(loss)
+        for i, pr in enumerate(model.parameters()):
+            cnn[f"grad{t}_{i}"] = pr.grad.copy()
+        opt.step()
+        for i, pr in enumerate(model.parameters()):
+            cnn[f"param{t}_{i}"] = pr.data.copy()
+        for i, b_ in enumerate(bns):
+            cnn[f"rm{t}_{i}"], cnn[f"rv{t}_{i}"] = b_.running_mean.ravel().copy(), b_.running_var.ravel().copy()
+    model.eval()
+    cnn["eval_logits"] = model(x_all[0])
+    cnn["n_params"] = np.array(len(plist))
+    out["cnn_main"] = cnn
     # ---- NumPy's own narrowing / widening on the edge block (the reference's cast primitive)
     e = workloads.edge_block_f32()
     with np.errstate(all="ignore"):

@@ -1,0 +1,192 @@
+"""BatchNorm, MaxPool2d, GlobalAvgPool2d, Dropout, float64 AdamW and the whole CNN of the
+reference's main.py on the GPU, against the reference's golden vectors and the CPU oracle.
+
+Tolerances: the batch statistics are summed in float64 on the device and pairwise in fp32 by
+NumPy, so BatchNorm results agree to fp32 rounding of the statistics (1e-5 of the largest
+magnitude is asserted; observed ~1e-7).  MaxPool2d backward, the average pool's backward and
+Dropout are bit-exact."""
+import os
+
+import numpy as np
+import pytest
+
+import novann_b200 as nb
+from novann_b200 import functional as F, workloads
+from oracle import oracle_np as o
+
+pytestmark = pytest.mark.gpu
+G = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+MODES = ["zeros", "reflect", "replicate", "circular"]
+
+
+def load(name):
+    return np.load(os.path.join(G, f"{name}.npz"))
+
+
+def close(a, b, rel=1e-5):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    assert a.shape == b.shape, (a.shape, b.shape)
+    return np.max(np.abs(a - b)) <= rel * max(1e-30, np.max(np.abs(b)))
+
+
+def bits(a):
+    return np.ascontiguousarray(a, np.float32).view(np.uint32)
+
+
+def test_batchnorm_against_reference_vectors():
+    g = load("batchnorm")
+    for i in range(int(g["n_cases"])):
+        x = g[f"x{i}"]
+        y, rm, rv, stats = F.batchnorm_fwd_host(x, g[f"gamma{i}"], g[f"beta{i}"], g[f"rm{i}"], g[f"rv{i}"])
+        assert y.dtype == np.float32
+        assert close(y, g[f"y{i}"].astype(np.float32), 1e-5), i
+        assert close(rm, g[f"rm_new{i}"], 1e-6) and close(rv, g[f"rv_new{i}"], 1e-6), i
+        dx, dga, dbe = F.batchnorm_bwd_host(g[f"g{i}"], x, stats, g[f"gamma{i}"])
+        assert close(dx, g[f"dx{i}"].astype(np.float32), 2e-5), i
+        assert close(dga, g[f"dgamma{i}"], 1e-5) and close(dbe, g[f"dbeta{i}"], 1e-6), i
+        ye, rm2, rv2, st2 = F.batchnorm_fwd_host(x, g[f"gamma{i}"], g[f"beta{i}"], g[f"rm_new{i}"],
+                                                 g[f"rv_new{i}"], training=False)
+        # evaluation mode is float64 arithmetic on given statistics: bit-exact after narrowing
+        assert np.array_equal(bits(ye), bits(g[f"y_eval{i}"].astype(np.float32))), i
+        assert st2 is None and np.array_equal(rm2, g[f"rm_new{i}"]) and np.array_equal(rv2, g[f"rv_new{i}"])
+
+
+@pytest.mark.parametrize("shape", [(128, 16, 28, 28), (128, 32), (3, 5, 7), (2, 1, 1, 1), (64, 64, 7, 7),
+                                   (1, 4, 300, 301)])
+def test_batchnorm_against_oracle_shapes(shape):
+    rng = np.random.default_rng(sum(shape))
+    c = shape[1]
+    x = (rng.standard_normal(shape) * 3 + 1.5).astype(np.float32)
+    grad = rng.standard_normal(shape).astype(np.float32)
+    ga, be = 1 + 0.2 * rng.standard_normal(c), 0.2 * rng.standard_normal(c)
+    rm, rv = 0.1 * rng.standard_normal(c), 0.5 + rng.random(c)
+    yo, rmo, rvo, cache = o.batchnorm_fwd(x, ga, be, rm, rv, momentum=0.2, eps=1e-4)
+    y, rm1, rv1, stats = F.batchnorm_fwd_host(x, ga, be, rm, rv, momentum=0.2, eps=1e-4)
+    assert close(y, yo.astype(np.float32), 1e-5)
+    assert close(rm1, rmo, 1e-6) and close(rv1, rvo, 1e-5)
+    dxo, dgo, dbo = o.batchnorm_bwd(grad, cache)
+    dx, dg, db = F.batchnorm_bwd_host(grad, x, stats, ga, eps=1e-4)
+    assert close(dx, dxo.astype(np.float32), 5e-5)
+    assert close(dg, dgo, 1e-5) and close(db, dbo, 1e-6)
+
+
+def test_maxpool_gap_dropout_against_reference_vectors():
+    g = load("pool_dropout")
+    for i in range(int(g["n_cases"])):
+        kh, kw, sh, sw, ph, pw, mi = (int(v) for v in g[f"geom{i}"])
+        y = F.max_pool2d_host(g[f"x{i}"], (kh, kw), (sh, sw), (ph, pw), MODES[mi])
+        assert np.array_equal(y, g[f"y{i}"]), i           # values; the sign of a zero maximum is free
+        dx = F.max_pool2d_bwd_host(g[f"g{i}"], g[f"x{i}"], (kh, kw), (sh, sw), (ph, pw), MODES[mi])
+        assert np.array_equal(bits(dx), bits(g[f"dx{i}"])), i
+    assert close(F.avg_pool2d_host(g["gap_x"]), g["gap_y"], 1e-6)
+    assert np.array_equal(bits(F.avg_pool2d_bwd_host(g["gap_g"], g["gap_x"].shape)), bits(g["gap_dx"]))
+    for i in range(2):
+        keep = 1.0 - float(g[f"drop_p{i}"])
+        assert np.array_equal(bits(F.dropout_host(g[f"drop_x{i}"], g[f"drop_mask{i}"], keep)), bits(g[f"drop_y{i}"]))
+        assert np.array_equal(bits(F.dropout_host(g[f"drop_g{i}"], g[f"drop_mask{i}"], keep)), bits(g[f"drop_dx{i}"]))
+
+
+@pytest.mark.parametrize("case", [
+    dict(shape=(128, 32, 14, 14), k=(2, 2), s=(2, 2), p=(0, 0), mode="zeros"),
+    dict(shape=(3, 5, 13, 17), k=(3, 3), s=(2, 2), p=(1, 1), mode="zeros"),
+    dict(shape=(2, 3, 9, 9), k=(4, 2), s=(1, 3), p=(2, 1), mode="reflect"),
+    dict(shape=(2, 2, 8, 11), k=(3, 5), s=(2, 2), p=(2, 3), mode="replicate"),
+    dict(shape=(1, 2, 6, 7), k=(3, 3), s=(1, 1), p=(3, 3), mode="circular"),
+    dict(shape=(2, 2, 5, 5), k=(5, 5), s=(1, 1), p=(0, 0), mode="zeros"),
+])
+def test_maxpool_against_oracle_with_ties_and_nan(case):
+    rng = np.random.default_rng(case["shape"][2])
+    x = np.round(rng.standard_normal(case["shape"]) * 1.5).astype(np.float32) / 2 - 0.5   # many ties
+    if case["mode"] == "zeros" and case["shape"][0] == 3:
+        x[0, 0, 2, 3] = np.nan                     # a NaN poisons its windows, as np.max does
+    yo, win, pshape = o.maxpool2d_fwd(x, case["k"], case["s"], case["p"], case["mode"])
+    y = F.max_pool2d_host(x, case["k"], case["s"], case["p"], case["mode"])
+    assert np.array_equal(np.isnan(y), np.isnan(yo))
+    assert np.array_equal(np.nan_to_num(y), np.nan_to_num(yo))
+    grad = rng.standard_normal(yo.shape).astype(np.float32)
+    dxo = o.maxpool2d_bwd(grad, win, pshape, x.shape, case["k"], case["s"], case["p"])
+    dx = F.max_pool2d_bwd_host(grad, x, case["k"], case["s"], case["p"], case["mode"])
+    assert np.array_equal(bits(dx), bits(dxo))
+
+
+def test_pool_rejects_bad_arguments():
+    x = np.zeros((1, 1, 4, 4), np.float32)
+    with pytest.raises(ValueError):
+        F.max_pool2d_host(x, (2, 2), (2, 2), (0, 0), "same")
+    with pytest.raises(nb._lib.NvqError):
+        F.max_pool2d_host(x, (9, 9), (1, 1), (0, 0), "zeros")
+    with pytest.raises(ValueError):
+        nb.BatchNorm2d(3).forward(np.zeros((2, 4, 2, 2), np.float32))
+    with pytest.raises(ValueError):
+        nb.BatchNorm1d(3).forward(np.zeros((2, 3, 2, 2), np.float32))
+    with pytest.raises(ValueError):
+        nb.BatchNorm2d(3).backward(np.zeros((2, 3, 2, 2), np.float32))
+    with pytest.raises(ValueError):
+        nb.Dropout(1.0)
+
+
+def test_adamw_float64_three_steps_bit_exact():
+    rng = np.random.default_rng(8)
+    p = nb.Parameters(rng.standard_normal((1, 7, 1, 1)))
+    p.name = "gamma"
+    q = nb.Parameters(rng.standard_normal((3, 5)))            # float64 but decayed
+    opt = nb.AdamW([p, q], lr=1e-3, weight_decay=1e-2)
+    rp, rq = p.data.copy(), q.data.copy()
+    mp = vp = np.zeros_like(rp)
+    mq = vq = np.zeros_like(rq)
+    for t in range(3):
+        p.grad, q.grad = rng.standard_normal(p.data.shape), rng.standard_normal(q.data.shape)
+        opt.step()
+        mp = 0.9 * mp + (1 - 0.9) * p.grad
+        vp = 0.999 * vp + (1 - 0.999) * (p.grad ** 2)
+        rp = rp - 1e-3 * (mp / (1 - 0.9 ** (t + 1))) / (np.sqrt(vp / (1 - 0.999 ** (t + 1))) + 1e-8)
+        mq = 0.9 * mq + (1 - 0.9) * q.grad
+        vq = 0.999 * vq + (1 - 0.999) * (q.grad ** 2)
+        rq = rq - 1e-3 * (mq / (1 - 0.9 ** (t + 1))) / (np.sqrt(vq / (1 - 0.999 ** (t + 1))) + 1e-8)
+        rq = rq - 1e-3 * 1e-2 * rq
+        assert np.array_equal(p.data.view(np.uint64), rp.view(np.uint64)), t
+        assert np.array_equal(q.data.view(np.uint64), rq.view(np.uint64)), t
+
+
+def build_main_cnn(params):
+    model = nb.Sequential(
+        nb.Conv2d(1, 16, 3, padding=1, bias=False), nb.BatchNorm2d(16), nb.ReLU(),
+        nb.Conv2d(16, 32, 3, padding=1, stride=2, bias=False), nb.BatchNorm2d(32), nb.ReLU(),
+        nb.MaxPool2d(2, 2),
+        nb.Conv2d(32, 64, 3, padding=1, bias=False), nb.BatchNorm2d(64), nb.ReLU(),
+        nb.GlobalAvgPool2d(), nb.Flatten(),
+        nb.Linear(64, 32, bias=False), nb.BatchNorm1d(32), nb.ReLU(), nb.Dropout(0.5), nb.Linear(32, 10))
+    plist = model.parameters()
+    assert len(plist) == len(params)
+    for pr, val in zip(plist, params):
+        assert pr.data.shape == val.shape
+        pr.data = val.copy()
+    return model
+
+
+def test_main_cnn_layer_api_two_adamw_steps_match_reference():
+    """The reference's main.py model and training loop, written with this package's layers."""
+    g = load("cnn_main")
+    xs, ys, params = workloads.cnn_inputs(16, steps=2, seed=3)
+    model = build_main_cnn(params)
+    model.train()
+    opt = nb.AdamW(model.parameters(), lr=1e-3, betas=(0.9, 0.999), weight_decay=1e-2, epsilon=1e-8)
+    loss_fn = nb.CrossEntropyLoss()
+    drop = [l for l in model._layers if isinstance(l, nb.Dropout)][0]
+    for t in range(2):
+        np.random.seed(500 + t)                    # the seed the reference run drew its mask under
+        opt.zero_grad()
+        logits = model(xs[t])
+        assert np.array_equal(drop._mask, g[f"mask{t}"])
+        loss, grad = loss_fn(logits, ys[t])
+        model.backward(grad)
+        assert close(logits, g[f"logits{t}"], 1e-5), t
+        assert abs(float(loss) - float(g[f"loss{t}"])) <= 1e-5 * abs(float(g[f"loss{t}"]))
+        for i, pr in enumerate(model.parameters()):
+            assert pr.grad.dtype == g[f"grad{t}_{i}"].dtype, (t, i)
+            assert close(pr.grad, g[f"grad{t}_{i}"], 5e-4), (t, i)
+        opt.step()
+        for i, pr in enumerate(model.parameters()):
+            assert close(pr.data, g[f"param{t}_{i}"], 1e-5), (t, i)
+    model.eval()
+    assert close(model(xs[0]), g["eval_logits"], 1e-4)

@@ -113,3 +113,62 @@ def test_adamw_three_steps_bit_exact():
         q, mq, vq = o.adamw_step(q, g[f"gq{t}"], mq, vq, t + 1, 1e-3, wd=1e-2, decay=False)
         assert np.array_equal(p.view(np.uint32), g[f"p{t + 1}"].view(np.uint32))
         assert np.array_equal(q.view(np.uint32), g[f"q{t + 1}"].view(np.uint32))
+
+
+MODES = ["zeros", "reflect", "replicate", "circular"]
+
+
+def test_batchnorm_forward_backward_running_stats_and_eval():
+    g = load("batchnorm")
+    for i in range(int(g["n_cases"])):
+        x = g[f"x{i}"]
+        y, rm, rv, cache = o.batchnorm_fwd(x, g[f"gamma{i}"], g[f"beta{i}"], g[f"rm{i}"], g[f"rv{i}"])
+        assert y.dtype == np.float64 and y.shape == x.shape
+        assert np.array_equal(y, g[f"y{i}"]), i                    # same NumPy expression: exact
+        assert np.array_equal(rm, g[f"rm_new{i}"]) and np.array_equal(rv, g[f"rv_new{i}"])
+        dx, dga, dbe = o.batchnorm_bwd(g[f"g{i}"], cache)
+        assert np.array_equal(dx, g[f"dx{i}"]), i
+        assert np.array_equal(dga, g[f"dgamma{i}"]) and np.array_equal(dbe, g[f"dbeta{i}"])
+        ye, _, _, _ = o.batchnorm_fwd(x, g[f"gamma{i}"], g[f"beta{i}"], rm, rv, training=False)
+        assert np.array_equal(ye, g[f"y_eval{i}"]), i
+
+
+def test_maxpool_gap_dropout():
+    g = load("pool_dropout")
+    for i in range(int(g["n_cases"])):
+        kh, kw, sh, sw, ph, pw, mi = (int(v) for v in g[f"geom{i}"])
+        y, win, pshape = o.maxpool2d_fwd(g[f"x{i}"], (kh, kw), (sh, sw), (ph, pw), MODES[mi])
+        assert np.array_equal(y, g[f"y{i}"]), i
+        dx = o.maxpool2d_bwd(g[f"g{i}"], win, pshape, g[f"x{i}"].shape, (kh, kw), (sh, sw), (ph, pw))
+        assert np.array_equal(dx.view(np.uint32), g[f"dx{i}"].view(np.uint32)), i
+    assert np.array_equal(o.gap2d_fwd(g["gap_x"]), g["gap_y"])
+    assert np.array_equal(o.gap2d_bwd(g["gap_g"], g["gap_x"].shape), g["gap_dx"])
+    for i in range(2):
+        p = float(g[f"drop_p{i}"])
+        assert np.array_equal(o.dropout(g[f"drop_x{i}"], g[f"drop_mask{i}"], p), g[f"drop_y{i}"])
+        assert np.array_equal(o.dropout(g[f"drop_g{i}"], g[f"drop_mask{i}"], p), g[f"drop_dx{i}"])
+
+
+def _cnn_state(params):
+    bn_c = [p.size for p in params if p.dtype == np.float64][::2]
+    return dict(running=[(np.zeros(c), np.ones(c)) for c in bn_c],
+                m=[np.zeros_like(p) for p in params], v=[np.zeros_like(p) for p in params])
+
+
+def test_cnn_main_two_adamw_steps():
+    g = load("cnn_main")
+    xs, ys, params = workloads.cnn_inputs(16, steps=2, seed=3)
+    assert len(params) == int(g["n_params"])
+    state = _cnn_state(params)
+    opt = dict(lr=1e-3, b1=0.9, b2=0.999, eps=1e-8, wd=1e-2)
+    for t in range(2):
+        r = o.cnn_train_step(o.cnn_main_spec(), params, state, xs[t], ys[t], [g[f"mask{t}"]], opt, t + 1)
+        assert close(r["logits"], g[f"logits{t}"], 1e-5), t
+        assert abs(float(r["loss"]) - float(g[f"loss{t}"])) <= 1e-5 * abs(float(g[f"loss{t}"]))
+        for i in range(len(params)):
+            assert r["grads"][i].shape == g[f"grad{t}_{i}"].shape and r["grads"][i].dtype == g[f"grad{t}_{i}"].dtype
+            assert close(r["grads"][i], g[f"grad{t}_{i}"], 2e-4), (t, i)
+            assert close(r["params"][i], g[f"param{t}_{i}"], 1e-5), (t, i)
+        params, state = r["params"], r["state"]
+        for i, (rm, rv) in enumerate(state["running"]):
+            assert close(rm, g[f"rm{t}_{i}"], 1e-6) and close(rv, g[f"rv{t}_{i}"], 1e-6)
