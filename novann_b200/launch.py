@@ -45,6 +45,7 @@ class StepGate:
 
     def __init__(self, directory: str, rank: int, world: int, timeout_s: float = 10.0):
         self.dir, self.rank, self.world, self.timeout_s = directory, rank, world, timeout_s
+        self._last = 0
         os.makedirs(directory, exist_ok=True)
 
     def _path(self, rank: int) -> str:
@@ -64,18 +65,25 @@ class StepGate:
             return None
 
     def leave(self) -> None:
-        """Announce a clean exit (call between steps, with nothing in flight)."""
-        self._write("left")
+        """Announce a clean exit (call between steps, with nothing in flight).  The marker
+        carries the last step this rank entered, so a slower peer still inside that step's
+        rendezvous sees that this rank did reach it."""
+        self._write(f"left {self._last}")
 
     def enter(self, step: int) -> None:
         """Announce ``step`` and wait for every rank to do the same; raises ``PeerLost``."""
         self._write(str(step))
+        self._last = step
         t0 = time.time()
         pending = set(range(self.world)) - {self.rank}
         while pending:
             for r in list(pending):
                 v = self._read(r)
-                if v == "left":
+                if v is not None and v.startswith("left"):
+                    parts = v.split()
+                    if len(parts) == 2 and parts[1].isdigit() and int(parts[1]) >= step:
+                        pending.discard(r)          # it made this step and left afterwards
+                        continue
                     raise PeerLost(f"rank {r} left before step {step}")
                 if v is not None and v.isdigit() and int(v) >= step:
                     pending.discard(r)

@@ -114,3 +114,17 @@ def test_step_gate_detects_a_rank_that_left_or_never_joined(tmp_path):
             assert p.exitcode == 0
         msgs = dict(q.get(timeout=5) for _ in range(1 if worker is _silent_worker else 2))
         assert msgs[0].startswith("PeerLost"), msgs
+
+
+def test_step_gate_peer_that_left_right_after_a_step_still_counts_for_that_step(tmp_path):
+    """A fast rank may finish step k and leave before a slow rank has looked: the slow rank must
+    still pass step k's rendezvous and only fail at step k + 1."""
+    from novann_b200.launch import PeerLost, StepGate
+    fast = StepGate(str(tmp_path), 1, 2, timeout_s=0.5)
+    slow = StepGate(str(tmp_path), 0, 2, timeout_s=0.5)
+    fast._write("1")
+    fast._last = 1
+    fast.leave()
+    slow.enter(1)
+    with pytest.raises(PeerLost, match="left before step 2"):
+        slow.enter(2)
