@@ -190,3 +190,76 @@ def test_main_cnn_layer_api_two_adamw_steps_match_reference():
             assert close(pr.data, g[f"param{t}_{i}"], 1e-5), (t, i)
     model.eval()
     assert close(model(xs[0]), g["eval_logits"], 1e-4)
+
+
+def _bn_index(params):
+    return [i for i, p in enumerate(params) if p.dtype == np.float64]
+
+
+def test_main_cnn_device_resident_step_matches_reference_and_layer_api():
+    """CNNTrainStep keeps every tensor of main.py's step in HBM; two AdamW steps against the
+    reference's vectors, then the evaluation forward with the running statistics."""
+    from novann_b200.train_cnn import CNNTrainStep, main_cnn_spec
+    g = load("cnn_main")
+    xs, ys, params = workloads.cnn_inputs(16, steps=2, seed=3)
+    step = CNNTrainStep(main_cnn_spec(), params, 16, (1, 28, 28), lr=1e-3, weight_decay=1e-2)
+    for t in range(2):
+        step.step(xs[t], ys[t], drop_masks=[g[f"mask{t}"]])
+        assert close(step.logits(), g[f"logits{t}"], 1e-5), t
+        assert abs(float(step.loss()) - float(g[f"loss{t}"])) <= 1e-5 * abs(float(g[f"loss{t}"]))
+        for i, (gr, pa) in enumerate(zip(step.grads(), step.params())):
+            assert gr.dtype == g[f"grad{t}_{i}"].dtype and pa.dtype == g[f"param{t}_{i}"].dtype
+            assert close(gr, g[f"grad{t}_{i}"], 5e-4), (t, i)
+            assert close(pa, g[f"param{t}_{i}"], 1e-5), (t, i)
+        for i, (rm, rv) in enumerate(step.running_stats()):
+            assert close(rm, g[f"rm{t}_{i}"], 1e-6) and close(rv, g[f"rv{t}_{i}"], 1e-6)
+    assert step.launches_per_step > 30
+    step.eval()
+    assert close(step.forward(xs[0]), g["eval_logits"], 1e-4)
+
+
+def test_main_cnn_graph_replay_equals_eager_and_draws_the_reference_masks():
+    from novann_b200.train_cnn import CNNTrainStep, main_cnn_spec
+    xs, ys, params = workloads.cnn_inputs(32, steps=4, seed=11)
+    eager = CNNTrainStep(main_cnn_spec(), params, 32, (1, 28, 28))
+    graph = CNNTrainStep(main_cnn_spec(), params, 32, (1, 28, 28))
+    for t in range(4):
+        np.random.seed(40 + t)
+        eager.step(xs[t], ys[t])
+        np.random.seed(40 + t)                      # same seed -> same host-drawn Dropout mask
+        graph.step(xs[t], ys[t])
+        if t == 0:
+            graph.capture()
+        assert np.array_equal(eager.logits(), graph.logits()), t
+        for a, b in zip(eager.params(), graph.params()):
+            assert np.array_equal(a, b), t
+    assert float(eager.loss()) == float(graph.loss())
+
+
+def test_main_cnn_full_batch_against_oracle():
+    """Batch 128 (the reference's batch size): one step against the CPU oracle.
+
+    With 2.7 million ReLU inputs per step, one or two BatchNorm outputs land within an ulp of
+    zero, where the float64-summed statistics of the device and NumPy's fp32 pairwise sums put
+    them on different sides: that unit's gradient is then masked on one side only (observed: one
+    flip out of 802 816 at the second ReLU), which moves the gradients upstream of it by ~1e-3
+    of their maximum.  So gradients are compared in relative L2 norm, with a loose bound on the
+    largest entry; each layer on its own agrees to ~3e-7 (tests above)."""
+    from novann_b200.train_cnn import CNNTrainStep, main_cnn_spec
+    xs, ys, params = workloads.cnn_inputs(128, steps=1, seed=0)
+    mask = (np.random.default_rng(5).random((128, 32)) < 0.5).astype(np.float32)
+    state = dict(running=[(np.zeros(c), np.ones(c)) for c in (16, 32, 64, 32)],
+                 m=[np.zeros_like(p) for p in params], v=[np.zeros_like(p) for p in params])
+    opt = dict(lr=1e-3, b1=0.9, b2=0.999, eps=1e-8, wd=1e-2)
+    r = o.cnn_train_step(o.cnn_main_spec(), params, state, xs[0], ys[0], [mask], opt, 1)
+    step = CNNTrainStep(main_cnn_spec(), params, 128, (1, 28, 28))
+    step.step(xs[0], ys[0], drop_masks=[mask])
+    assert close(step.logits(), r["logits"], 1e-5)
+    assert abs(float(step.loss()) - float(r["loss"])) <= 1e-5 * abs(float(r["loss"]))
+    for i, (gr, pa) in enumerate(zip(step.grads(), step.params())):
+        ref = np.asarray(r["grads"][i], np.float64)
+        assert np.linalg.norm(gr.astype(np.float64) - ref) <= 1e-3 * np.linalg.norm(ref), i
+        assert close(gr, ref, 1e-2), i
+        # first AdamW step moves every entry by ~lr * sign(g): entries whose tiny gradient changed
+        # sign differ by up to 2 lr
+        assert np.max(np.abs(pa.astype(np.float64) - r["params"][i])) <= 2.5e-3, i
