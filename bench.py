@@ -297,6 +297,26 @@ def measure_extras(dev, st, rank, world, dist, local):
     e1.record(step.stream)
     e1.sync()
     out["mlp_step_us"] = e0.elapsed_ms(e1) / 50 * 1e3
+    # ---- the CNN of the reference's main.py, batch 128 / world per GPU: forward + CE + backward
+    # replayed as one CUDA graph, then the two AdamW launches
+    from novann_b200.train_cnn import CNNTrainStep, main_cnn_spec
+    cb = 128 // world
+    xc, yc, cparams = workloads.cnn_inputs(cb, steps=1, seed=0)
+    cnn = CNNTrainStep(main_cnn_spec(), cparams, cb, (1, 28, 28), device=dev)
+    cnn.step(xc[0], yc[0])
+    cnn.capture()
+    for _ in range(3):
+        cnn.step(xc[0], yc[0])
+    e0, e1 = Event(dev), Event(dev)
+    e0.record(cnn.stream)
+    for _ in range(20):
+        cnn.replay()
+    e1.record(cnn.stream)
+    e1.sync()
+    out["cnn_step_us"] = e0.elapsed_ms(e1) / 20 * 1e3
+    out["cnn_step_note"] = ("main.py CNN (3 conv + 4 BatchNorm + pool + 2 Linear + Dropout), batch %d per GPU, "
+                            "forward + CE + backward + AdamW, %d kernels per step, inputs resident" %
+                            (cb, cnn.launches_per_step))
     out["mlp_step_note"] = ("fp32 784-256-128-10, batch %d per GPU, forward + CE + backward + SGD, "
                             "13 kernels replayed as one CUDA graph, no all-reduce in this figure" % bsz)
     return out

@@ -314,8 +314,9 @@ nvq_status nvq_conv2d_fwd_f32(float* d_out, const float* d_x, const float* d_w,
 /* Conv2d.backward (novann/layers/convolutional/conv2d.py:179-207, _col2im :117-148):
  * dW (Cout,C,KH,KW) = g_r @ col^T, db (Cout) = row sums of g_r, dX (N,C,H,W) = col2im(w_col^T @ g_r)
  * with g_r = grad.transpose(1,0,2,3).reshape(Cout,-1).  d_col is the im2col matrix of the forward
- * pass.  Scratch: d_gr Cout*N*OH*OW floats, d_dcol C*KH*KW*N*OH*OW floats.  Any of d_dw, d_db, d_dx
- * may be NULL.  As in the reference, gradient falling on padding is dropped for every padding mode. */
+ * pass.  Scratch: d_gr Cout*N*OH*OW floats, d_dcol C*KH*KW*N*OH*OW floats (it also holds the
+ * partial sums of the split-k weight-gradient GEMM; it may be NULL when d_dx is NULL, at the
+ * price of an unsplit dW contraction).  Any of d_dw, d_db, d_dx may be NULL.  As in the reference, gradient falling on padding is dropped for every padding mode. */
 nvq_status nvq_conv2d_bwd_f32(float* d_dw, float* d_db, float* d_dx, const float* d_grad,
                               const float* d_col, const float* d_w, float* d_gr, float* d_dcol,
                               int N, int C, int H, int W, int Cout, int KH, int KW, int sh, int sw,

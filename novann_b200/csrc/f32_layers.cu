@@ -7,6 +7,8 @@
 // multiply and add where NumPy performs two operations).
 #include <math.h>
 
+#include <algorithm>
+
 #include "nvq_common.cuh"
 
 namespace {
@@ -30,6 +32,10 @@ struct GemmArgs {
     // output indexing: 0 = row-major I x J; 1 = "NCHW": j = (n, s) with s < inner:
     //   c[(n * I + i) * inner + s]
     int out_mode, inner;
+    // split-K (epilogue-free calls only): block z covers k in [z * l_per_split, (z+1) * l_per_split)
+    // and stores its raw sums to partial[z][I][J]; splitk_reduce_kernel adds them in z order
+    int splits, l_per_split;
+    float* partial;
 };
 
 constexpr int TK = 64;   // k depth of one staged chunk
@@ -61,18 +67,20 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
 #pragma unroll
         for (int v = 0; v < R; v++) acc[u][v] = 0.f;
     float ra[LD], rb[LD];
+    const int l_lo = g.splits > 1 ? blockIdx.z * g.l_per_split : 0;
+    const int l_hi = g.splits > 1 ? min(g.L, l_lo + g.l_per_split) : g.L;
     auto fetch = [&](int l0) {
 #pragma unroll
         for (int r = 0; r < LD; r++) {
             int e = threadIdx.x + 256 * r, ii, ll;
             tile_coord<T>(e, a_kc, ii, ll);
             int i = i0 + ii, l = l0 + ll;
-            ra[r] = (i < g.I && l < g.L) ? g.a[i * g.a_si + l * g.a_sl] : 0.f;
+            ra[r] = (i < g.I && l < l_hi) ? g.a[i * g.a_si + l * g.a_sl] : 0.f;
             int jj;
             tile_coord<T>(e, b_kc, jj, ll);
             int j = j0 + jj;
             l = l0 + ll;
-            rb[r] = (j < g.J && l < g.L) ? g.b[l * g.b_sl + j * g.b_sj] : 0.f;
+            rb[r] = (j < g.J && l < l_hi) ? g.b[l * g.b_sl + j * g.b_sj] : 0.f;
         }
     };
     auto stash = [&](int buf) {
@@ -85,12 +93,12 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
             Bs[buf][ll][ii] = rb[r];
         }
     };
-    fetch(0);
+    fetch(l_lo);
     stash(0);
     __syncthreads();
     int buf = 0;
-    for (int l0 = 0; l0 < g.L; l0 += TK) {
-        const bool more = l0 + TK < g.L;
+    for (int l0 = l_lo; l0 < l_hi; l0 += TK) {
+        const bool more = l0 + TK < l_hi;
         if (more) fetch(l0 + TK);
 #pragma unroll 16
         for (int l = 0; l < TK; l++) {
@@ -113,6 +121,10 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
             int i = i0 + ty + 16 * u, j = j0 + tx + 16 * v;
             if (i >= g.I || j >= g.J) continue;
             float val = acc[u][v];
+            if (g.splits > 1) {
+                g.partial[((size_t)blockIdx.z * g.I + i) * g.J + j] = val;
+                continue;
+            }
             if (g.bias) val = __fadd_rn(val, g.bias_per_row ? g.bias[i] : g.bias[j]);
             size_t idx = g.out_mode == 0 ? (size_t)i * g.J + j
                                          : ((size_t)(j / g.inner) * g.I + i) * g.inner + (j % g.inner);
@@ -125,6 +137,50 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
             g.c[idx] = val;
         }
     }
+}
+
+// c[e] = sum over z of partial[z][e]: one warp per output, lane t adds z = t, t+32, ... in
+// order and the 32 lane sums are combined by a fixed butterfly (same result on every run)
+__global__ void splitk_reduce_kernel(float* __restrict__ c, const float* __restrict__ partial,
+                                     int n, int splits) {
+    const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (e >= n) return;
+    float s = 0.f;
+    for (int z = lane; z < splits; z += 32) s = __fadd_rn(s, partial[(size_t)z * n + e]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s = __fadd_rn(s, __shfl_xor_sync(0xFFFFFFFFu, s, o));
+    if (lane == 0) c[e] = s;
+}
+
+// A small output with a very deep contraction (the convolution weight gradient: Cout x CKK
+// outputs, k = every output position of the batch) is split along k over enough blocks to fill
+// the GPU; `scratch` must hold scratch_elems floats.
+nvq_status launch_gemm_splitk(GemmArgs g, float* scratch, size_t scratch_elems, int device,
+                              cudaStream_t st) {
+    if (g.I <= 0 || g.J <= 0) return NVQ_OK;
+    const long long tiles = (long long)((g.J + 15) / 16) * ((g.I + 15) / 16);
+    const long long out = (long long)g.I * g.J;
+    long long want = (4LL * nvq_sm_count(device) + tiles - 1) / tiles;
+    want = std::min<long long>(want, g.L / 128);
+    if (scratch) want = std::min<long long>(want, (long long)(scratch_elems / (size_t)out));
+    if (!scratch || want < 2 || g.bias || g.relu || g.mask_in || g.out_mode != 0) {
+        g.splits = 1;
+        dim3 grid((g.J + 15) / 16, (g.I + 15) / 16);
+        gemm_f32_kernel<16><<<grid, 256, 0, st>>>(g);
+        NVQ_LAUNCHED();
+        return NVQ_OK;
+    }
+    int lps = (int)((g.L + want - 1) / want);
+    lps = (lps + TK - 1) / TK * TK;
+    g.l_per_split = lps;
+    g.splits = (g.L + lps - 1) / lps;
+    g.partial = scratch;
+    dim3 grid((g.J + 15) / 16, (g.I + 15) / 16, g.splits);
+    gemm_f32_kernel<16><<<grid, 256, 0, st>>>(g);
+    NVQ_LAUNCHED();
+    splitk_reduce_kernel<<<(unsigned)((out + 7) / 8), 256, 0, st>>>(g.c, scratch, (int)out, g.splits);
+    NVQ_LAUNCHED();
+    return NVQ_OK;
 }
 
 nvq_status launch_gemm(const GemmArgs& g, cudaStream_t st) {
@@ -280,17 +336,20 @@ __device__ __forceinline__ int pad_index(int idx, int size, int mode, bool& zero
 struct ConvGeom { int N, C, H, W, KH, KW, sh, sw, ph, pw, OH, OW, mode; };
 
 // fp32 col, rows (c,kh,kw), columns (n,oh,ow): the reference's layout
+// Idx = uint32_t whenever every element count fits 31 bits (64-bit divisions are several times
+// dearer and these kernels are bound by their index arithmetic), size_t otherwise.
+template <class Idx>
 __global__ void im2col_f32_kernel(float* __restrict__ col, const float* __restrict__ x, ConvGeom g) {
-    const size_t L = (size_t)g.N * g.OH * g.OW, total = (size_t)g.C * g.KH * g.KW * L;
-    size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
-        size_t row = e / L, colj = e % L;
+    const Idx L = (Idx)g.N * g.OH * g.OW, total = (Idx)g.C * g.KH * g.KW * L;
+    Idx stride = (Idx)gridDim.x * blockDim.x;
+    for (Idx e = (Idx)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+        Idx row = e / L, colj = e - row * L;
         int kw = row % g.KW, kh = (row / g.KW) % g.KH, c = row / (g.KW * g.KH);
-        int ow = colj % g.OW, oh = (colj / g.OW) % g.OH, n = colj / ((size_t)g.OW * g.OH);
+        int ow = colj % g.OW, oh = (colj / g.OW) % g.OH, n = colj / ((Idx)g.OW * g.OH);
         bool z1, z2;
         int ih = pad_index(oh * g.sh + kh - g.ph, g.H, g.mode, z1);
         int iw = pad_index(ow * g.sw + kw - g.pw, g.W, g.mode, z2);
-        col[e] = (z1 || z2) ? 0.f : x[(((size_t)n * g.C + c) * g.H + ih) * g.W + iw];
+        col[e] = (z1 || z2) ? 0.f : x[(((Idx)n * g.C + c) * g.H + ih) * g.W + iw];
     }
 }
 
@@ -328,11 +387,12 @@ __global__ void rows_bf16_to_nchw_kernel(float* __restrict__ out, const uint16_t
 }
 
 // grad (N, Cout, S) -> g_r (Cout, N*S): the reference's grad.transpose(1,0,2,3).reshape(Cout,-1)
+template <class Idx>
 __global__ void nchw_to_crows_kernel(float* __restrict__ out, const float* __restrict__ g, int N,
                                      int Cout, int S) {
-    size_t total = (size_t)N * Cout * S, stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
-        int s = e % S, n = (e / S) % N, c = e / ((size_t)S * N);
+    Idx total = (Idx)N * Cout * S, stride = (Idx)gridDim.x * blockDim.x;
+    for (Idx e = (Idx)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+        int s = e % S, n = (e / S) % N, c = e / ((Idx)S * N);
         out[e] = g[((size_t)n * Cout + c) * S + s];
     }
 }
@@ -352,12 +412,13 @@ __global__ void rowsum_kernel(const float* __restrict__ a, float* __restrict__ o
 // element sums the dcol entries of the windows that cover it, in (kh, kw) order, which is the
 // order np.add.at applies them in.  As in the reference, gradient that falls on padding is dropped
 // whatever the padding mode.
+template <class Idx>
 __global__ void col2im_kernel(float* __restrict__ dx, const float* __restrict__ dcol, ConvGeom g) {
-    const size_t L = (size_t)g.N * g.OH * g.OW, total = (size_t)g.N * g.C * g.H * g.W;
-    size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
-        int w = e % g.W, h = (e / g.W) % g.H, c = (e / ((size_t)g.W * g.H)) % g.C;
-        int n = e / ((size_t)g.W * g.H * g.C);
+    const Idx L = (Idx)g.N * g.OH * g.OW, total = (Idx)g.N * g.C * g.H * g.W;
+    Idx stride = (Idx)gridDim.x * blockDim.x;
+    for (Idx e = (Idx)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+        int w = e % g.W, h = (e / g.W) % g.H, c = (e / ((Idx)g.W * g.H)) % g.C;
+        int n = e / ((Idx)g.W * g.H * g.C);
         float s = 0.f;
         for (int kh = 0; kh < g.KH; kh++) {
             int t = h + g.ph - kh;
@@ -369,8 +430,8 @@ __global__ void col2im_kernel(float* __restrict__ dx, const float* __restrict__ 
                 if (u < 0 || u % g.sw) continue;
                 int ow = u / g.sw;
                 if (ow >= g.OW) continue;
-                size_t row = ((size_t)c * g.KH + kh) * g.KW + kw;
-                s = __fadd_rn(s, dcol[row * L + ((size_t)n * g.OH + oh) * g.OW + ow]);
+                Idx row = ((Idx)c * g.KH + kh) * g.KW + kw;
+                s = __fadd_rn(s, dcol[row * L + ((Idx)n * g.OH + oh) * g.OW + ow]);
             }
         }
         dx[e] = s;
@@ -507,7 +568,10 @@ extern "C" nvq_status nvq_im2col_f32(float* d_col, const float* d_x, int N, int 
     s = nvq_use_device(device);
     if (s != NVQ_OK) return s;
     size_t total = (size_t)C * KH * KW * N * g.OH * g.OW;
-    im2col_f32_kernel<<<ew_grid(total, device), 256, 0, (cudaStream_t)stream>>>(d_col, d_x, g);
+    if (total < (1u << 31) && (size_t)N * C * H * W < (1u << 31))
+        im2col_f32_kernel<uint32_t><<<ew_grid(total, device), 256, 0, (cudaStream_t)stream>>>(d_col, d_x, g);
+    else
+        im2col_f32_kernel<size_t><<<ew_grid(total, device), 256, 0, (cudaStream_t)stream>>>(d_col, d_x, g);
     NVQ_LAUNCHED();
     return NVQ_OK;
 }
@@ -583,7 +647,10 @@ extern "C" nvq_status nvq_conv2d_bwd_f32(float* d_dw, float* d_db, float* d_dx, 
     const int S = gm.OH * gm.OW, CKK = C * KH * KW;
     const size_t L = (size_t)N * S;
     NVQ_REQUIRE(L < (1u << 31), "nvq_conv2d_bwd_f32: too many output positions");
-    nchw_to_crows_kernel<<<ew_grid(L * Cout, device), 256, 0, st>>>(d_gr, d_grad, N, Cout, S);
+    const bool small = (size_t)CKK * L < (1u << 31) && L * Cout < (1u << 31) &&
+                       (size_t)N * C * H * W < (1u << 31);
+    if (small) nchw_to_crows_kernel<uint32_t><<<ew_grid(L * Cout, device), 256, 0, st>>>(d_gr, d_grad, N, Cout, S);
+    else nchw_to_crows_kernel<size_t><<<ew_grid(L * Cout, device), 256, 0, st>>>(d_gr, d_grad, N, Cout, S);
     NVQ_LAUNCHED();
     if (d_dw) {   // dW = g_r @ col^T
         NVQ_REQUIRE(d_col, "nvq_conv2d_bwd_f32: dW needs col");
@@ -591,7 +658,8 @@ extern "C" nvq_status nvq_conv2d_bwd_f32(float* d_dw, float* d_db, float* d_dx, 
         g.a = d_gr; g.a_si = (long long)L; g.a_sl = 1;
         g.b = d_col; g.b_sl = 1; g.b_sj = (long long)L;
         g.c = d_dw; g.I = Cout; g.J = CKK; g.L = (int)L;
-        s = launch_gemm(g, st);
+        // d_dcol (free until the dX pass below) holds the split-k partial sums
+        s = launch_gemm_splitk(g, d_dcol, d_dcol ? (size_t)CKK * L : 0, device, st);
         if (s != NVQ_OK) return s;
     }
     if (d_db) {
@@ -606,7 +674,8 @@ extern "C" nvq_status nvq_conv2d_bwd_f32(float* d_dw, float* d_db, float* d_dx, 
         g.c = d_dcol; g.I = CKK; g.J = (int)L; g.L = Cout;
         s = launch_gemm(g, st);
         if (s != NVQ_OK) return s;
-        col2im_kernel<<<ew_grid((size_t)N * C * H * W, device), 256, 0, st>>>(d_dx, d_dcol, gm);
+        if (small) col2im_kernel<uint32_t><<<ew_grid((size_t)N * C * H * W, device), 256, 0, st>>>(d_dx, d_dcol, gm);
+        else col2im_kernel<size_t><<<ew_grid((size_t)N * C * H * W, device), 256, 0, st>>>(d_dx, d_dcol, gm);
         NVQ_LAUNCHED();
     }
     return NVQ_OK;

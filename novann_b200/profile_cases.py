@@ -5,6 +5,7 @@
     python -m novann_b200.profile_cases fp4    [rows=8192]
     python -m novann_b200.profile_cases linear [M=4096 N=4096 K=4096]
     python -m novann_b200.profile_cases w8a8   [M=4096 N=4096 K=4096]
+    python -m novann_b200.profile_cases cnn    [batch=128 steps=3]
 
 Each case uploads seeded inputs, launches the kernels a few times and exits; sizes are
 larger than the 126 MB L2 (so DRAM counters mean something) but hold at most a few GB.
@@ -95,6 +96,16 @@ def case_w8a8(m: int = 4096, n: int = 4096, k: int = 4096, reps: int = 3) -> Non
     F.check_device_errors(0)
 
 
+def case_cnn(batch: int = 128, steps: int = 3) -> None:
+    """Training steps of the reference's main.py CNN, eager launches (one kernel per line in a
+    profiler's launch list)."""
+    from .train_cnn import CNNTrainStep, main_cnn_spec
+    xs, ys, params = workloads.cnn_inputs(batch, steps=1, seed=0)
+    step = CNNTrainStep(main_cnn_spec(), params, batch, (1, 28, 28))
+    for _ in range(steps):
+        step.step(xs[0], ys[0])
+
+
 def main(argv) -> None:
     what = argv[1] if len(argv) > 1 else "cast"
     args = [int(a) for a in argv[2:]]
@@ -108,6 +119,8 @@ def main(argv) -> None:
         case_linear(*args)
     elif what == "w8a8":
         case_w8a8(*args)
+    elif what == "cnn":
+        case_cnn(*args)
     else:
         raise SystemExit(f"unknown case {what}")
     device_sync(0)

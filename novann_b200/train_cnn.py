@@ -330,6 +330,17 @@ class CNNTrainStep:
             check(lib().nvq_graph_end_capture(self.device, _sptr(self.stream), C.byref(h)))
         self._graph = h.value
 
+    def replay(self) -> None:
+        """Enqueue one more training step on the batch already in HBM (no upload, no sync):
+        the captured graph if there is one, else the eager sequence; then AdamW."""
+        self.t += 1
+        if self._graph is not None:
+            check(lib().nvq_graph_launch(self.device, C.c_void_p(self._graph), _sptr(self.stream)))
+        else:
+            self.launch_forward()
+            self.launch_backward()
+        self.launch_update()
+
     def forward(self, x: np.ndarray) -> np.ndarray:
         """Forward pass only (uses running statistics and no Dropout after ``eval()``)."""
         self.upload(x, np.zeros(self.batch, np.int32))
