@@ -38,20 +38,22 @@ struct GemmArgs {
     float* partial;
 };
 
-constexpr int TK = 64;   // k depth of one staged chunk
+constexpr int kSplitChunk = 64;   // split-k ranges are multiples of the deepest chunk
 
 // element e of a T x TK tile -> (row-in-tile, k-in-chunk); the index that has unit stride in
 // memory runs fastest across threads so global loads coalesce
-template <int T>
+template <int T, int TK>
 __device__ __forceinline__ void tile_coord(int e, bool k_contiguous, int& r, int& l) {
-    if (k_contiguous) { l = e & (TK - 1); r = e >> 6; }
+    if (k_contiguous) { l = e & (TK - 1); r = e / TK; }
     else              { r = e & (T - 1); l = e / T; }
 }
 
 // T x T output tile per 256-thread block: T = 32 (2 x 2 outputs per thread) for large outputs,
 // T = 16 (one output per thread) when the output is so small that 32 x 32 tiles would leave
 // most SMs idle - these GEMMs are latency-bound, so more blocks means more loads in flight.
-template <int T>
+// TK = k depth of one staged chunk: 64, or 16 for shallow contractions (the first convolution
+// has k = 9; a 64-deep chunk would multiply 55 rows of zeros).
+template <int T, int TK = 64>
 __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
     constexpr int R = T / 16;                 // outputs per thread per dimension
     constexpr int LD = T * TK / 256;          // tile elements each thread stages per chunk
@@ -73,11 +75,11 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
 #pragma unroll
         for (int r = 0; r < LD; r++) {
             int e = threadIdx.x + 256 * r, ii, ll;
-            tile_coord<T>(e, a_kc, ii, ll);
+            tile_coord<T, TK>(e, a_kc, ii, ll);
             int i = i0 + ii, l = l0 + ll;
             ra[r] = (i < g.I && l < l_hi) ? g.a[i * g.a_si + l * g.a_sl] : 0.f;
             int jj;
-            tile_coord<T>(e, b_kc, jj, ll);
+            tile_coord<T, TK>(e, b_kc, jj, ll);
             int j = j0 + jj;
             l = l0 + ll;
             rb[r] = (j < g.J && l < l_hi) ? g.b[l * g.b_sl + j * g.b_sj] : 0.f;
@@ -87,9 +89,9 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
 #pragma unroll
         for (int r = 0; r < LD; r++) {
             int e = threadIdx.x + 256 * r, ii, ll;
-            tile_coord<T>(e, a_kc, ii, ll);
+            tile_coord<T, TK>(e, a_kc, ii, ll);
             As[buf][ll][ii] = ra[r];
-            tile_coord<T>(e, b_kc, ii, ll);
+            tile_coord<T, TK>(e, b_kc, ii, ll);
             Bs[buf][ll][ii] = rb[r];
         }
     };
@@ -171,7 +173,7 @@ nvq_status launch_gemm_splitk(GemmArgs g, float* scratch, size_t scratch_elems, 
         return NVQ_OK;
     }
     int lps = (int)((g.L + want - 1) / want);
-    lps = (lps + TK - 1) / TK * TK;
+    lps = (lps + kSplitChunk - 1) / kSplitChunk * kSplitChunk;
     g.l_per_split = lps;
     g.splits = (g.L + lps - 1) / lps;
     g.partial = scratch;
@@ -186,7 +188,16 @@ nvq_status launch_gemm_splitk(GemmArgs g, float* scratch, size_t scratch_elems, 
 nvq_status launch_gemm(const GemmArgs& g, cudaStream_t st) {
     if (g.I <= 0 || g.J <= 0) return NVQ_OK;
     const long long big_blocks = (long long)((g.J + 31) / 32) * ((g.I + 31) / 32);
-    if (big_blocks >= 148) {
+    if (big_blocks >= 148 && g.L <= 16) {
+        // shallow contraction: 16-deep chunks; 16-row tiles when the output has few rows
+        if (g.I <= 16) {
+            dim3 grid((g.J + 15) / 16, (g.I + 15) / 16);
+            gemm_f32_kernel<16, 16><<<grid, 256, 0, st>>>(g);
+        } else {
+            dim3 grid((g.J + 31) / 32, (g.I + 31) / 32);
+            gemm_f32_kernel<32, 16><<<grid, 256, 0, st>>>(g);
+        }
+    } else if (big_blocks >= 148) {
         dim3 grid((g.J + 31) / 32, (g.I + 31) / 32);
         gemm_f32_kernel<32><<<grid, 256, 0, st>>>(g);
     } else {
@@ -412,8 +423,10 @@ __global__ void rowsum_kernel(const float* __restrict__ a, float* __restrict__ o
 // element sums the dcol entries of the windows that cover it, in (kh, kw) order, which is the
 // order np.add.at applies them in.  As in the reference, gradient that falls on padding is dropped
 // whatever the padding mode.
-template <class Idx>
+// ST = the stride when it is 1 or 2 in both directions (divisions fold away), 0 = read it from g.
+template <class Idx, int ST>
 __global__ void col2im_kernel(float* __restrict__ dx, const float* __restrict__ dcol, ConvGeom g) {
+    const int sh = ST ? ST : g.sh, sw = ST ? ST : g.sw;
     const Idx L = (Idx)g.N * g.OH * g.OW, total = (Idx)g.N * g.C * g.H * g.W;
     Idx stride = (Idx)gridDim.x * blockDim.x;
     for (Idx e = (Idx)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
@@ -422,13 +435,13 @@ __global__ void col2im_kernel(float* __restrict__ dx, const float* __restrict__ 
         float s = 0.f;
         for (int kh = 0; kh < g.KH; kh++) {
             int t = h + g.ph - kh;
-            if (t < 0 || t % g.sh) continue;
-            int oh = t / g.sh;
+            if (t < 0 || t % sh) continue;
+            int oh = t / sh;
             if (oh >= g.OH) continue;
             for (int kw = 0; kw < g.KW; kw++) {
                 int u = w + g.pw - kw;
-                if (u < 0 || u % g.sw) continue;
-                int ow = u / g.sw;
+                if (u < 0 || u % sw) continue;
+                int ow = u / sw;
                 if (ow >= g.OW) continue;
                 Idx row = ((Idx)c * g.KH + kh) * g.KW + kw;
                 s = __fadd_rn(s, dcol[row * L + ((Idx)n * g.OH + oh) * g.OW + ow]);
@@ -674,8 +687,11 @@ extern "C" nvq_status nvq_conv2d_bwd_f32(float* d_dw, float* d_db, float* d_dx, 
         g.c = d_dcol; g.I = CKK; g.J = (int)L; g.L = Cout;
         s = launch_gemm(g, st);
         if (s != NVQ_OK) return s;
-        if (small) col2im_kernel<uint32_t><<<ew_grid((size_t)N * C * H * W, device), 256, 0, st>>>(d_dx, d_dcol, gm);
-        else col2im_kernel<size_t><<<ew_grid((size_t)N * C * H * W, device), 256, 0, st>>>(d_dx, d_dcol, gm);
+        const unsigned grid = ew_grid((size_t)N * C * H * W, device);
+        if (small && sh == 1 && sw == 1) col2im_kernel<uint32_t, 1><<<grid, 256, 0, st>>>(d_dx, d_dcol, gm);
+        else if (small && sh == 2 && sw == 2) col2im_kernel<uint32_t, 2><<<grid, 256, 0, st>>>(d_dx, d_dcol, gm);
+        else if (small) col2im_kernel<uint32_t, 0><<<grid, 256, 0, st>>>(d_dx, d_dcol, gm);
+        else col2im_kernel<size_t, 0><<<grid, 256, 0, st>>>(d_dx, d_dcol, gm);
         NVQ_LAUNCHED();
     }
     return NVQ_OK;

@@ -351,12 +351,12 @@ unsigned flat_grid(size_t n, int device) {
     return (unsigned)(want < 1 ? 1 : (want < cap ? want : cap));
 }
 
-// blocks per channel: enough to cover the SMs about twice, at most kMaxSplits, and no more
+// blocks per channel: enough for about eight blocks per SM (the loops are latency-bound), at most kMaxSplits, and no more
 // than the channel has 256-element slices
 int bn_splits(int N, int C, int S, int device) {
     long m = (long)N * S;
     long by_size = (m + kThreads - 1) / kThreads;
-    long by_sm = (2L * nvq_sm_count(device) + C - 1) / C;
+    long by_sm = (8L * nvq_sm_count(device) + C - 1) / C;
     long p = by_size < by_sm ? by_size : by_sm;
     if (p > kMaxSplits) p = kMaxSplits;
     return (int)(p < 1 ? 1 : p);
