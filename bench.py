@@ -192,46 +192,54 @@ def measure_extras(dev, st, rank, world, dist, local):
     pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(pk):
         peak_bf16 = float(json.load(open(pk))["bf16_tflops"])
+    def timed_rotating(fn, sets, rounds=4):
+        """Back-to-back launches that rotate over buffer sets, so that a set is touched again
+        only after >= 512 MB of other traffic: every launch reads DRAM, and no flush write-back
+        lands inside the timed region."""
+        k = len(sets)
+        for i in range(k):
+            fn(*sets[i])
+        st.sync()
+        e0, e1 = Event(dev), Event(dev)
+        e0.record(st)
+        for i in range(rounds * k):
+            fn(*sets[i % k])
+        e1.record(st)
+        e1.sync()
+        return e0.elapsed_ms(e1) / (rounds * k)
+
+    def n_sets_for(set_bytes):
+        return max(2, int(np.ceil((512 << 20) / set_bytes)) + 1)
+
     # ---- FP8 per tensor: fp32 [16384, 16384 / world] row shard (1 GiB per GPU at world = 1)
     rows = 16384 // world
     n = rows * 16384
     x = workloads.fp8_input(min(rows, 1024), 16384, seed=rank)
-    d32 = DeviceBuffer(n * 4, dev)
-    for off in range(0, n, x.size):
-        d32.upload(x, offset=off * 4)
-    d8 = DeviceBuffer(n, dev)
     asi = DeviceBuffer(12, dev)
-    big = n * 4 > (200 << 20)
-    t = timed(lambda: quant.quantize_fp8_tensor_device(d8, asi, d32, n, "e4m3", stream=st), do_flush=not big)
+    sets = []
+    for _ in range(n_sets_for(5 * n)):
+        d32 = DeviceBuffer(n * 4, dev)
+        for off in range(0, n, x.size):
+            d32.upload(x, offset=off * 4)
+        sets.append((d32, DeviceBuffer(n, dev)))
+    t = timed_rotating(lambda d32, d8: quant.quantize_fp8_tensor_device(d8, asi, d32, n, "e4m3", stream=st), sets)
     out["fp8_e4m3_amax_quantize_gbs"] = 9 * n / t / 1e6
-    t = timed(lambda: quant.dequantize_fp8_device(d32, d8, n, "e4m3", 0.02, stream=st), do_flush=not big)
+    t = timed_rotating(lambda d32, d8: quant.dequantize_fp8_device(d32, d8, n, "e4m3", 0.02, stream=st), sets)
     out["fp8_e4m3_dequantize_gbs"] = 5 * n / t / 1e6
-    d32.free(); d8.free()
-    # ---- FP4 block 32: bf16 [8192, 8192] (128 MiB in, about the L2 size).  Launches rotate over
-    # enough buffer sets that a set is touched again only after >= 512 MB of other traffic, so
-    # every launch reads from DRAM and no flush write-back lands inside the timed region.
+    out["fp8_note"] = "%d rotating buffer sets of %.0f MB" % (len(sets), 5 * n / 1e6)
+    for bufs in sets:
+        for b_ in bufs:
+            b_.free()
+    # ---- FP4 block 32: bf16 [8192, 8192] (128 MiB in, about the L2 size), rotating sets as above
     r4 = 8192 // world
     xb = workloads.fp4_input_bits(r4, 8192, seed=rank)
     set_bytes = r4 * 8192 * 2.625
-    n_sets = max(3, int(np.ceil((512 << 20) / set_bytes)) + 1)
     sets = [(DeviceBuffer.from_numpy(xb, dev), DeviceBuffer(r4 * 4096, dev),
-             DeviceBuffer(r4 * 256 * 4, dev)) for _ in range(n_sets)]
-
-    def timed_rotating(fn, iters=4 * n_sets, warm=n_sets):
-        for i in range(warm):
-            fn(*sets[i % n_sets])
-        st.sync()
-        e0, e1 = Event(dev), Event(dev)
-        e0.record(st)
-        for i in range(iters):
-            fn(*sets[i % n_sets])
-        e1.record(st)
-        e1.sync()
-        return e0.elapsed_ms(e1) / iters
-
-    t = timed_rotating(lambda dx, dp, dsc: quant.quantize_fp4_b32_device(dp, dsc, dx, r4, 8192, stream=st))
+             DeviceBuffer(r4 * 256 * 4, dev)) for _ in range(n_sets_for(set_bytes))]
+    n_sets = len(sets)
+    t = timed_rotating(lambda dx, dp, dsc: quant.quantize_fp4_b32_device(dp, dsc, dx, r4, 8192, stream=st), sets)
     out["fp4_quantize_gbs"] = 2.625 * r4 * 8192 / t / 1e6
-    t = timed_rotating(lambda dx, dp, dsc: quant.dequantize_fp4_b32_device(dx, dp, dsc, r4, 8192, stream=st))
+    t = timed_rotating(lambda dx, dp, dsc: quant.dequantize_fp4_b32_device(dx, dp, dsc, r4, 8192, stream=st), sets)
     out["fp4_dequantize_gbs"] = 2.625 * r4 * 8192 / t / 1e6
     out["fp4_note"] = "%d rotating buffer sets of %.0f MB, %d launches back to back" % (
         n_sets, set_bytes / 1e6, 4 * n_sets)

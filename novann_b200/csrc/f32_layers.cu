@@ -6,10 +6,12 @@
 // order.  Elementwise steps reproduce the reference's roundings exactly (separate
 // multiply and add where NumPy performs two operations).
 #include <math.h>
+#include <stdlib.h>
 
 #include <algorithm>
 
 #include "nvq_common.cuh"
+#include "gemm_common.cuh"
 
 namespace {
 
@@ -397,6 +399,135 @@ __global__ void rows_bf16_to_nchw_kernel(float* __restrict__ out, const uint16_t
     }
 }
 
+// Tiled forms of the two kernels above, used whenever the geometry fits their tables.
+// Patches: a block takes 32 consecutive rows (n,oh,ow) and walks the columns (c,kh,kw) in
+// chunks of 64.  Reads: one warp per column, lanes = rows, so a warp reads 32 consecutive
+// pixels of one input plane; writes: 128 contiguous bytes per row through shared memory.
+constexpr int kImRows = 32, kImK = 64, kImLut = 4096;
+
+__global__ void __launch_bounds__(256)
+im2col_bf16_tiled_kernel(uint16_t* __restrict__ col, const float* __restrict__ x, ConvGeom g,
+                         int Kpad, int L) {
+    __shared__ uint16_t tile[kImRows][kImK + 2];     // 33-word rows: conflict-free column writes
+    __shared__ uint32_t lut[kImLut];                 // column -> c << 16 | kh << 8 | kw
+    const int CKK = g.C * g.KH * g.KW;
+    for (int kk = threadIdx.x; kk < CKK; kk += 256) {
+        int kw = kk % g.KW, kh = (kk / g.KW) % g.KH, c = kk / (g.KW * g.KH);
+        lut[kk] = ((uint32_t)c << 16) | ((uint32_t)kh << 8) | (uint32_t)kw;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int wr = threadIdx.x >> 3, wseg = threadIdx.x & 7;      // write role: row, 8-column group
+    for (int row0 = blockIdx.x * kImRows; row0 < L; row0 += gridDim.x * kImRows) {
+        const int row = row0 + lane;
+        const bool valid = row < L;
+        int ow = row % g.OW, oh = (row / g.OW) % g.OH, n = row / (g.OW * g.OH);
+        const int base_h = oh * g.sh - g.ph, base_w = ow * g.sw - g.pw;
+        const float* xn = x + (size_t)n * g.C * g.H * g.W;
+        for (int k0 = 0; k0 < Kpad; k0 += kImK) {
+#pragma unroll
+            for (int i = 0; i < kImK / 8; i++) {
+                const int kc = warp + 8 * i, kk = k0 + kc;
+                float v = 0.f;
+                if (valid && kk < CKK) {
+                    const uint32_t e = lut[kk];
+                    bool z1, z2;
+                    int ih = pad_index(base_h + (int)((e >> 8) & 0xFFu), g.H, g.mode, z1);
+                    int iw = pad_index(base_w + (int)(e & 0xFFu), g.W, g.mode, z2);
+                    if (!(z1 || z2)) v = xn[((size_t)(e >> 16) * g.H + ih) * g.W + iw];
+                }
+                tile[lane][kc] = (uint16_t)spec_f32_to_bf16(__float_as_uint(v));
+            }
+            __syncthreads();
+            const int kk = k0 + wseg * 8;
+            if (row0 + wr < L && kk < Kpad) {
+                const uint32_t* src = reinterpret_cast<const uint32_t*>(&tile[wr][wseg * 8]);
+                uint4 o = make_uint4(src[0], src[1], src[2], src[3]);
+                *reinterpret_cast<uint4*>(col + (size_t)(row0 + wr) * Kpad + kk) = o;
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// Y (N*S x Cout, bf16) -> out (N, Cout, S) fp32 through a 32 x 64 shared tile: 128-byte reads
+// along Cout, 128-byte writes along S.
+__global__ void __launch_bounds__(256)
+rows_bf16_to_nchw_tiled_kernel(float* __restrict__ out, const uint16_t* __restrict__ y, int N,
+                               int Cout, int S) {
+    __shared__ float tile[64][33];
+    const int s_tiles = (S + 31) / 32, c_tiles = (Cout + 63) / 64;
+    const long long total = (long long)N * s_tiles * c_tiles;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rr = threadIdx.x >> 3, seg = threadIdx.x & 7;
+    for (long long t = blockIdx.x; t < total; t += gridDim.x) {
+        const int ct = (int)(t % c_tiles), stl = (int)((t / c_tiles) % s_tiles), n = (int)(t / ((long long)c_tiles * s_tiles));
+        const int s0 = stl * 32, c0 = ct * 64;
+        if (s0 + rr < S && c0 + seg * 8 < Cout) {
+            const uint4 v = *reinterpret_cast<const uint4*>(y + ((size_t)n * S + s0 + rr) * Cout + c0 + seg * 8);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                tile[seg * 8 + 2 * q][rr] = __uint_as_float(w[q] << 16);
+                tile[seg * 8 + 2 * q + 1][rr] = __uint_as_float(w[q] & 0xFFFF0000u);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int c = c0 + warp + 8 * i;
+            if (c < Cout && s0 + lane < S)
+                out[((size_t)n * Cout + c) * S + s0 + lane] = tile[warp + 8 * i][lane];
+        }
+        __syncthreads();
+    }
+}
+
+// ---- pre-passes of the implicit-GEMM convolution ---------------------------------------
+// x (N, C, S) fp32 -> (N, S, C) bf16 (round to nearest even): 32 pixels x 64 channels per tile,
+// 128-byte reads along S, 128-byte writes along C.
+__global__ void __launch_bounds__(256)
+nchw_f32_to_nhwc_bf16_kernel(uint16_t* __restrict__ out, const float* __restrict__ x, int N, int C,
+                             int S) {
+    __shared__ uint16_t tile[32][64 + 2];
+    const int s_tiles = (S + 31) / 32, c_tiles = C / 64;
+    const long long total = (long long)N * s_tiles * c_tiles;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int wr = threadIdx.x >> 3, wseg = threadIdx.x & 7;
+    for (long long t = blockIdx.x; t < total; t += gridDim.x) {
+        const int ct = (int)(t % c_tiles), stl = (int)((t / c_tiles) % s_tiles);
+        const int n = (int)(t / ((long long)c_tiles * s_tiles));
+        const int s0 = stl * 32, c0 = ct * 64;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int c = warp + 8 * i;
+            float v = s0 + lane < S ? x[((size_t)n * C + c0 + c) * S + s0 + lane] : 0.f;
+            tile[lane][c] = (uint16_t)spec_f32_to_bf16(__float_as_uint(v));
+        }
+        __syncthreads();
+        if (s0 + wr < S) {
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(&tile[wr][wseg * 8]);
+            *reinterpret_cast<uint4*>(out + ((size_t)n * S + s0 + wr) * C + c0 + wseg * 8) =
+                make_uint4(src[0], src[1], src[2], src[3]);
+        }
+        __syncthreads();
+    }
+}
+
+// FP8 weight codes (Cout x Kpad, columns (c, kh, kw)) -> bf16 (Cout x KH*KW*C, columns
+// (kh, kw, c)), exact
+template <int FMT>
+__global__ void expand_permute_weight_kernel(uint16_t* __restrict__ out, const uint8_t* __restrict__ wq,
+                                             int Cout, int C, int KH, int KW, int Kpad) {
+    const int K = C * KH * KW, total = Cout * K;
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
+        const int co = e / K, k = e - co * K;
+        const int c = k % C, tap = k / C, kh = tap / KW, kw = tap - kh * KW;
+        const uint32_t code = wq[(size_t)co * Kpad + (c * KH + kh) * KW + kw];
+        out[e] = (uint16_t)(spec_fp8_to_f32<FMT>(code) >> 16);   // the low 16 bits are zero
+    }
+}
+
 // grad (N, Cout, S) -> g_r (Cout, N*S): the reference's grad.transpose(1,0,2,3).reshape(Cout,-1)
 template <class Idx>
 __global__ void nchw_to_crows_kernel(float* __restrict__ out, const float* __restrict__ g, int N,
@@ -635,12 +766,49 @@ extern "C" nvq_status nvq_conv2d_fwd_q(float* d_out, const float* d_x, const uin
     cudaStream_t st = (cudaStream_t)stream;
     const size_t L = (size_t)N * g.OH * g.OW;
     const int Kpad = (C * KH * KW + 15) / 16 * 16;
-    im2col_bf16_rows_kernel<<<ew_grid(L * Kpad, device), 256, 0, st>>>(d_col_bf16, d_x, g, Kpad);
+    // Implicit GEMM (no patch matrix): stride 1, zero padding, channels in blocks of 64, output
+    // rows of at most 128 positions.  d_col_bf16 holds x as bf16 NHWC, d_workspace the weight with
+    // its columns reordered to (kh, kw, c).  NVQ_CONV_MODE=explicit forces the patch-matrix path.
+    const char* cmode = getenv("NVQ_CONV_MODE");
+    const bool implicit_ok = sh == 1 && sw == 1 && mode == NVQ_PAD_ZEROS && C % 64 == 0 && g.OW <= 128 &&
+                             L < (1u << 31) && (size_t)Cout * C * KH * KW < (1u << 31) &&
+                             workspace_bytes >= (size_t)Cout * C * KH * KW * 2 && d_workspace &&
+                             (size_t)H * W <= (size_t)g.OH * g.OW * KH * KW &&
+                             !(cmode && cmode[0] == 'e');
+    if (implicit_ok) {
+        const int S_in = H * W;
+        const size_t want = (size_t)N * ((S_in + 31) / 32) * (C / 64), cap = (size_t)nvq_sm_count(device) * 16;
+        nchw_f32_to_nhwc_bf16_kernel<<<(unsigned)std::min(want, cap), 256, 0, st>>>(d_col_bf16, d_x, N, C, S_in);
+        NVQ_LAUNCHED();
+        const int wtotal = Cout * C * KH * KW;
+        if (w_fmt == NVQ_E4M3)
+            expand_permute_weight_kernel<NVQ_E4M3><<<ew_grid(wtotal, device), 256, 0, st>>>(
+                (uint16_t*)d_workspace, d_wq, Cout, C, KH, KW, Kpad);
+        else
+            expand_permute_weight_kernel<NVQ_E5M2><<<ew_grid(wtotal, device), 256, 0, st>>>(
+                (uint16_t*)d_workspace, d_wq, Cout, C, KH, KW, Kpad);
+        NVQ_LAUNCHED();
+        return nvq_conv_launch_pair_implicit(d_out, d_col_bf16, (const uint16_t*)d_workspace, d_w_scales,
+                                             d_bias, N, C, H, W, Cout, KH, KW, ph, pw, device, st);
+    }
+    const bool tiled = C * KH * KW <= kImLut && KH < 256 && KW < 256 && C < 65536 && L < (1u << 31);
+    if (tiled) {
+        const size_t want = (L + kImRows - 1) / kImRows, cap = (size_t)nvq_sm_count(device) * 8;
+        im2col_bf16_tiled_kernel<<<(unsigned)std::min(want, cap), 256, 0, st>>>(d_col_bf16, d_x, g, Kpad, (int)L);
+    } else {
+        im2col_bf16_rows_kernel<<<ew_grid(L * Kpad, device), 256, 0, st>>>(d_col_bf16, d_x, g, Kpad);
+    }
     NVQ_LAUNCHED();
     s = nvq_linear_fwd(d_y_bf16, d_col_bf16, d_wq, w_fmt, d_w_scales, d_bias, L, (size_t)Cout,
                        (size_t)Kpad, d_workspace, workspace_bytes, device, stream);
     if (s != NVQ_OK) return s;
-    rows_bf16_to_nchw_kernel<<<ew_grid(L * Cout, device), 256, 0, st>>>(d_out, d_y_bf16, N, Cout, g.OH * g.OW);
+    if (tiled) {
+        const int S = g.OH * g.OW;
+        const size_t want = (size_t)N * ((S + 31) / 32) * ((Cout + 63) / 64), cap = (size_t)nvq_sm_count(device) * 16;
+        rows_bf16_to_nchw_tiled_kernel<<<(unsigned)std::min(want, cap), 256, 0, st>>>(d_out, d_y_bf16, N, Cout, S);
+    } else {
+        rows_bf16_to_nchw_kernel<<<ew_grid(L * Cout, device), 256, 0, st>>>(d_out, d_y_bf16, N, Cout, g.OH * g.OW);
+    }
     NVQ_LAUNCHED();
     return NVQ_OK;
 }

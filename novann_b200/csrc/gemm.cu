@@ -271,8 +271,7 @@ nvq_status nvq_status_word(int device, int** dev_ptr) {
     return NVQ_OK;
 }
 
-nvq_status nvq_make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
-                            uint32_t box_rows, uint32_t box_cols, int elem_bytes, int swizzle128) {
+static nvq_status ensure_encode() {
     if (!g_encode) {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult q;
@@ -281,6 +280,13 @@ nvq_status nvq_make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, u
             NVQ_FAIL(NVQ_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
         g_encode = (EncodeTiledFn)fn;
     }
+    return NVQ_OK;
+}
+
+nvq_status nvq_make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                            uint32_t box_rows, uint32_t box_cols, int elem_bytes, int swizzle128) {
+    nvq_status s0 = ensure_encode();
+    if (s0 != NVQ_OK) return s0;
     NVQ_REQUIRE(nvq_aligned(base, 16), "tensor base must be 16-byte aligned");
     NVQ_REQUIRE((cols * elem_bytes) % 16 == 0, "row pitch (%llu bytes) must be a multiple of 16",
                 (unsigned long long)(cols * elem_bytes));
@@ -297,6 +303,25 @@ nvq_status nvq_make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, u
                           swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) NVQ_FAIL(NVQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    return NVQ_OK;
+}
+
+nvq_status nvq_make_tmap_nhwc(CUtensorMap* map, const void* base, uint64_t N, uint64_t H, uint64_t W,
+                              uint64_t C, uint32_t box_w, uint32_t box_h) {
+    nvq_status s0 = ensure_encode();
+    if (s0 != NVQ_OK) return s0;
+    NVQ_REQUIRE(nvq_aligned(base, 16), "tensor base must be 16-byte aligned");
+    NVQ_REQUIRE(C % 64 == 0, "NHWC map: channels (%llu) must be a multiple of 64", (unsigned long long)C);
+    NVQ_REQUIRE(box_w >= 1 && box_h >= 1 && box_w <= 256 && box_h <= 256 && box_w * box_h <= 128,
+                "NHWC map: box %u x %u does not fit a 128-row operand tile", box_w, box_h);
+    cuuint64_t dims[4] = {C, W, H, N};
+    cuuint64_t strides[3] = {C * 2, W * C * 2, H * W * C * 2};
+    cuuint32_t box[4] = {64, box_w, box_h, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides,
+                          box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) NVQ_FAIL(NVQ_ERR_CUDA, "cuTensorMapEncodeTiled (NHWC) failed with %d", (int)r);
     return NVQ_OK;
 }
 

@@ -16,6 +16,13 @@ struct LinearParams {
     int num_items;            // items [num_big, num_items) are half-width tiles
     int group_m;              // rasterisation: m-blocks per group
     int* status;              // mapped host word: first non-zero give-up code
+    // implicit-GEMM convolution (stride 1, zero padding): a CTA's 128-row operand tile is a box
+    // of conv_bw x conv_bh output positions of one image; M tiles are numbered image-major
+    int conv_bw, conv_bh;     // box (conv_bw = OW)
+    int conv_th;              // boxes per image = ceil(OH / conv_bh)
+    int conv_images, conv_OH, conv_OW;
+    int conv_KW, conv_ph, conv_pw;
+    int conv_cpb;             // 64-channel blocks per filter tap = C / 64
 };
 
 nvq_status nvq_status_word(int device, int** dev_ptr);
@@ -41,6 +48,13 @@ nvq_status nvq_linear_launch_pair_w8a8(uint16_t* d_y, const uint8_t* d_xq, const
                                        const uint8_t* d_wq, const float* d_w_scales,
                                        const float* d_bias, size_t M, size_t N, size_t K, int device,
                                        cudaStream_t st);
+
+// Convolution as an implicit GEMM on the CTA-pair kernel: x bf16 NHWC, weight bf16 (Cout x
+// KH*KW*C, columns ordered (kh, kw, c)), out fp32 NCHW holding bf16-rounded values.
+nvq_status nvq_conv_launch_pair_implicit(float* d_out, const uint16_t* d_x_nhwc, const uint16_t* d_w,
+                                         const float* d_scales, const float* d_bias, int N, int C,
+                                         int H, int W, int Cout, int KH, int KW, int ph, int pw,
+                                         int device, cudaStream_t st);
 
 #ifdef __CUDACC__
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {

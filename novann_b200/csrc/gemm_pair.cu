@@ -36,11 +36,16 @@ constexpr int MAX_STAGES = 6;
 // codes and is expanded in shared memory by four extra warps.
 // FUSED = kW8A8: both operands arrive as E4M3 codes (activations quantised per row beforehand)
 // and the MMAs are kind::f8f6f4: 128 codes per 128-byte row, so a k-block spans 128 elements.
+// FUSED = kImplicitConv: A is gathered by 4-D TMA boxes from an NHWC activation tensor (one box
+// per filter tap and 64-channel block), B is the expanded weight with columns ordered
+// (kh, kw, c), and the epilogue writes fp32 NCHW.
 constexpr int kW8A8 = -8;
+constexpr int kImplicitConv = -16;
 template <int FUSED>
 struct Cfg {
     static constexpr bool CONV = FUSED > 0;
     static constexpr bool F8 = FUSED == kW8A8;
+    static constexpr bool IMPL = FUSED == kImplicitConv;
     static constexpr int BKE = F8 ? 128 : BK;           // elements of K per k-block
     static constexpr int STAGES = CONV ? 5 : 6;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + (CONV ? RAW_BYTES : 0);
@@ -102,6 +107,7 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     constexpr int STAGE_BYTES = Cfg<FUSED>::STAGE_BYTES;
     constexpr bool CONV = Cfg<FUSED>::CONV;
     constexpr bool F8 = Cfg<FUSED>::F8;
+    constexpr bool IMPL = Cfg<FUSED>::IMPL;
     constexpr int BKE = Cfg<FUSED>::BKE;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = tc::smem_u32(smem_raw);
@@ -169,6 +175,22 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                         tc::tma_load_2d(dst + A_BYTES + B_BYTES, &map_b, rbar, kb * BK, n0);
                         if (rows_b == 128)
                             tc::tma_load_2d(dst + A_BYTES + B_BYTES + RAW_BYTES / 2, &map_b, rbar, kb * BK, n0 + 64);
+                    } else if constexpr (IMPL) {
+                        // this CTA's box: image and first output row of operand tile 2 * m_blk + rank
+                        const int cta_tile = tr.m_blk * 2 + (int)rank;
+                        const int img = cta_tile / p.conv_th, oh0 = (cta_tile % p.conv_th) * p.conv_bh;
+                        const int tap = kb / p.conv_cpb, c0 = (kb % p.conv_cpb) * BK;
+                        const int kh = tap / p.conv_KW, kw = tap % p.conv_KW;
+                        const int a_bytes = p.conv_bw * p.conv_bh * BK * 2;   // the box, padding included
+                        if (rank == 0)
+                            tc::mbar_arrive_expect_tx(tc::smem_u32(&sh->full[stage]),
+                                                      2 * (a_bytes + rows_b * BK * 2));
+                        // input pixel of output (oh, ow) under tap (kh, kw): (oh + kh - ph, ow + kw - pw);
+                        // pixels outside the image (and images past the last) read as zeros
+                        tc::tma_load_4d_pair(dst, &map_a, lead_full, c0, kw - p.conv_pw, oh0 + kh - p.conv_ph, img);
+                        tc::tma_load_2d_pair(dst + A_BYTES, &map_b, lead_full, kb * BKE, n0);
+                        if (rows_b == 128)
+                            tc::tma_load_2d_pair(dst + A_BYTES + B_BYTES / 2, &map_b, lead_full, kb * BKE, n0 + 64);
                     } else {
                         if (rank == 0)   // the leader expects the bytes of both CTAs
                             tc::mbar_arrive_expect_tx(tc::smem_u32(&sh->full[stage]),
@@ -309,6 +331,35 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             tc::tc_fence_after();
             const int row = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+            if constexpr (IMPL) {
+                // row r of this CTA's tile is output position oh0 * OW + r of image img (the box
+                // spans whole output rows); each thread owns one position, so for a fixed channel
+                // a warp writes 32 consecutive floats of the NCHW plane
+                const int cta_tile = tr.m_blk * 2 + (int)rank;
+                const int img = cta_tile / p.conv_th, oh0 = (cta_tile % p.conv_th) * p.conv_bh;
+                const int r_in = quarter * 32 + lane, S = p.conv_OH * p.conv_OW;
+                const int pos = oh0 * p.conv_OW + r_in;
+                const bool valid = img < p.conv_images && r_in < p.conv_bw * p.conv_bh && pos < S;
+                float* obase = (float*)p.y + ((size_t)img * p.N + n0) * S + pos;
+#pragma unroll 1
+                for (int c = 0; c < bn; c += 32) {
+                    uint32_t r[32];
+                    tc::tmem_ld_32x32(taddr + c, r);
+                    tc::tmem_ld_wait();
+                    if (valid) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            if (n0 + c + j < p.N) {      // N % 8 == 0: pairs are in or out together
+                                const float v0 = fmaf(__uint_as_float(r[j]), sh->scale[acc][c + j], sh->bias[acc][c + j]);
+                                const float v1 = fmaf(__uint_as_float(r[j + 1]), sh->scale[acc][c + j + 1], sh->bias[acc][c + j + 1]);
+                                const uint32_t pk = pack_bf16(v0, v1);     // the bf16 result, widened again
+                                obase[(size_t)(c + j) * S] = __uint_as_float(pk << 16);
+                                obase[(size_t)(c + j + 1) * S] = __uint_as_float(pk & 0xFFFF0000u);
+                            }
+                        }
+                    }
+                }
+            } else
 #pragma unroll 1
             for (int c = 0; c < bn; c += 32) {
                 uint32_t r[32];
@@ -400,7 +451,76 @@ static nvq_status launch_pair(uint16_t* d_y, const void* d_x, const void* d_w,
     return NVQ_OK;
 }
 
+static nvq_status launch_implicit_conv(float* d_out, const uint16_t* d_x_nhwc, const uint16_t* d_w,
+                                       const float* d_scales, const float* d_bias, int N, int C, int H,
+                                       int W, int Cout, int KH, int KW, int ph, int pw, int device,
+                                       cudaStream_t st) {
+    const int OH = H + 2 * ph - KH + 1, OW = W + 2 * pw - KW + 1;
+    NVQ_REQUIRE(OH > 0 && OW > 0 && OW <= 128 && C % 64 == 0 && Cout % 8 == 0,
+                "implicit convolution: needs OW <= 128, C %% 64 == 0, Cout %% 8 == 0");
+    // box height: whole output rows, at most 128 positions, least padding over the image
+    int bh = 1;
+    long best = -1;
+    for (int h = 1; h <= OH && h * OW <= 128; h++) {
+        long tiles = (OH + h - 1) / h;
+        if (best < 0 || tiles < best) { best = tiles; bh = h; }
+    }
+    const int th = (OH + bh - 1) / bh;
+    const size_t K = (size_t)KH * KW * C;
+    CUtensorMap map_a, map_b;
+    nvq_status s = nvq_make_tmap_nhwc(&map_a, d_x_nhwc, N, H, W, C, OW, bh);
+    if (s != NVQ_OK) return s;
+    s = nvq_make_tmap_2d(&map_b, d_w, Cout, K, 64, BK, 2, 1);
+    if (s != NVQ_OK) return s;
+    static bool attr_set[64];
+    if (!attr_set[device]) {
+        NVQ_CUDA(cudaFuncSetAttribute(linear_tc_pair_kernel<kImplicitConv>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Cfg<kImplicitConv>::SMEM_BYTES));
+        attr_set[device] = true;
+    }
+    LinearParams p = {};
+    p.y = (uint16_t*)d_out;
+    p.out_f32 = 1;
+    p.scales = d_scales;
+    p.bias = d_bias;
+    p.M = N * th * 128;
+    p.N = Cout;
+    p.K = (int)K;
+    p.m_blocks = (N * th + 1) / 2;
+    p.n_blocks = (Cout + BN - 1) / BN;
+    p.group_m = 8;
+    p.conv_bw = OW; p.conv_bh = bh; p.conv_th = th;
+    p.conv_images = N; p.conv_OH = OH; p.conv_OW = OW;
+    p.conv_KW = KW; p.conv_ph = ph; p.conv_pw = pw; p.conv_cpb = C / 64;
+    s = nvq_status_word(device, &p.status);
+    if (s != NVQ_OK) return s;
+    int tiles = p.m_blocks * p.n_blocks;
+    int pairs = nvq_sm_count(device) / 2;
+    if (tiles < pairs) pairs = tiles;
+    int rem = tiles % pairs;
+    int split = (tiles > pairs && rem > 0 && 2 * rem <= pairs) ? rem : 0;
+    p.num_big = tiles - split;
+    p.num_items = p.num_big + 2 * split;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(Cfg<kImplicitConv>::THREADS);
+    cfg.dynamicSmemBytes = Cfg<kImplicitConv>::SMEM_BYTES;
+    cfg.stream = st;
+    NVQ_CUDA(cudaLaunchKernelEx(&cfg, linear_tc_pair_kernel<kImplicitConv>, map_a, map_b, p));
+    NVQ_LAUNCHED();
+    return NVQ_OK;
+}
+
 }  // namespace
+
+nvq_status nvq_conv_launch_pair_implicit(float* d_out, const uint16_t* d_x_nhwc, const uint16_t* d_w,
+                                         const float* d_scales, const float* d_bias, int N, int C,
+                                         int H, int W, int Cout, int KH, int KW, int ph, int pw,
+                                         int device, cudaStream_t st) {
+    return launch_implicit_conv(d_out, d_x_nhwc, d_w, d_scales, d_bias, N, C, H, W, Cout, KH, KW, ph, pw,
+                                device, st);
+}
 
 nvq_status nvq_linear_launch_pair(uint16_t* d_y, const uint16_t* d_x, const uint16_t* d_w,
                                   const float* d_scales, const float* d_bias, size_t M, size_t N,

@@ -184,6 +184,16 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtens
         "l"(map), "r"(bar), "r"(x), "r"(y)
         : "memory");
 }
+// Same, for a 4-D box (c, w, h, n) of an NHWC tensor: the box's pixels land as consecutive
+// 128-byte rows, i.e. as a K-major operand tile whose rows are the box's (h, w) positions.
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t smem_dst, const CUtensorMap* map,
+                                                 uint32_t bar, int c, int w, int h, int n) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_dst),
+        "l"(map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_slot, uint32_t cols) {  // one warp per CTA
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot),
                  "r"(cols)
@@ -243,5 +253,9 @@ __host__ __device__ constexpr uint32_t idesc_f16(uint32_t m, uint32_t n, uint32_
 // 2-D row-major tensor of `rows` x `cols` elements of `elem_bytes` (2 = bf16, 1 = bytes);
 // box = box_rows x box_cols, stored with the 128-byte swizzle (box_cols * elem_bytes must then
 // be 128) or linearly.
+// bf16 NHWC activation tensor (N, H, W, C), box = 64 channels x box_w x box_h pixels of one
+// image, 128-byte swizzle; out-of-range pixels (the zero padding of a convolution) read as 0
+nvq_status nvq_make_tmap_nhwc(CUtensorMap* map, const void* base, uint64_t N, uint64_t H, uint64_t W,
+                              uint64_t C, uint32_t box_w, uint32_t box_h);
 nvq_status nvq_make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
                             uint32_t box_rows, uint32_t box_cols, int elem_bytes, int swizzle128);

@@ -363,3 +363,43 @@ def test_quant_mlp_inference_fused_relu(gpu):
     assert y.shape == (300, 16)
     assert o.max_abs_rel(y, want) <= 1e-2
     assert np.mean(y == want) > 0.9          # most outputs agree to the last bf16 bit
+
+
+@pytest.mark.parametrize("case", [
+    # n, c, h, w, cout, k, p: stride 1, channels in blocks of 64 -> the implicit-GEMM kernel
+    (2, 64, 8, 8, 64, 3, 1),          # one box per image, boxes of 8 x 8
+    (3, 64, 14, 14, 72, 3, 1),        # two boxes of 7 rows per image; odd image count: last CTA tile empty
+    (2, 128, 12, 10, 264, 3, 1),      # Cout over one 256-column tile; two channel blocks per tap
+    (1, 64, 30, 30, 16, 5, 2),        # 5 x 5 taps, boxes of 4 rows, last box of an image partly outside
+    (5, 64, 9, 9, 40, 1, 0),          # 1 x 1 convolution, no padding
+    (2, 64, 6, 20, 24, 3, 0),         # no padding: output 4 x 18
+    (4, 192, 7, 7, 128, 3, 1),        # three channel blocks
+])
+def test_implicit_gemm_conv_equals_patch_matrix_conv_and_oracle(gpu, case, monkeypatch):
+    """The tcgen05 implicit-GEMM convolution (4-D TMA boxes, no patch matrix) against the
+    patch-matrix path of the same entry point (bit-identical inputs to the MMAs, so only the fp32
+    accumulation order differs) and against the oracle within the FP8 bound."""
+    n, c, h, w, cout, k, p = case
+    rng = np.random.default_rng(n * 1000 + c + h)
+    x = rng.standard_normal((n, c, h, w)).astype(np.float32)
+    wt = (rng.standard_normal((cout, c, k, k)) * 0.05).astype(np.float32)
+    b = (rng.standard_normal(cout) * 0.1).astype(np.float32)
+    w_col = wt.reshape(cout, -1)
+    assert w_col.shape[1] % 16 == 0
+    codes, scales = quant.quantize_weight(w_col, "e4m3", gpu)
+    monkeypatch.delenv("NVQ_CONV_MODE", raising=False)
+    y_imp = F.conv2d_q_host(x, codes, scales, b, (k, k), (1, 1), (p, p), "zeros", "e4m3", gpu)
+    monkeypatch.setenv("NVQ_CONV_MODE", "explicit")
+    y_exp = F.conv2d_q_host(x, codes, scales, b, (k, k), (1, 1), (p, p), "zeros", "e4m3", gpu)
+    assert y_imp.shape == y_exp.shape == (n, cout, h + 2 * p - k + 1, w + 2 * p - k + 1)
+    # both are bf16-rounded: equal up to one bf16 ulp where the fp32 sums differ in their last bits
+    assert o.max_abs_rel(y_imp, y_exp) <= 2.0 ** -8
+    assert np.mean(y_imp == y_exp) > 0.9
+    # oracle: bf16 activations x dequantised weight, float64 accumulation
+    wd = o.dequantize_fp8(codes, 1.0, "e4m3").reshape(cout, c, k, k) * scales.reshape(-1, 1, 1, 1)
+    xb = o.bf16_bits_to_f32(o.f32_to_bf16_bits(x))
+    col, oh, ow = o.im2col(xb, k, k, 1, 1, p, p)
+    ref = (wd.reshape(cout, -1).astype(np.float64) @ col.astype(np.float64) + b.reshape(-1, 1))
+    ref = ref.reshape(cout, n, oh, ow).transpose(1, 0, 2, 3)
+    assert o.max_abs_rel(y_imp, ref) <= 1e-2
+    F.check_device_errors(gpu)
