@@ -289,6 +289,34 @@ def measure_extras(dev, st, rank, world, dist, local):
                                           "inside the call (included in the time), FP8 x FP8 MMAs "
                                           "(kind::f8f6f4); max-abs-rel vs the bf16-activation result "
                                           "is 2.4-3.2e-2, outside the 1e-2 bound"}
+    # ---- FP8-weight Conv2d forward as an implicit GEMM: x fp32 [128 / world, 64, 56, 56], 3x3, pad 1,
+    # 128 output channels (a ResNet-style block); NCHW fp32 in and out, everything on the device
+    from novann_b200 import _lib as _l
+    cn, cc, chw, cco = max(1, 128 // world), 64, 56, 128
+    xcv = rng.standard_normal((cn, cc, chw, chw), dtype=np.float32)
+    wcv = rng.integers(0, 0x7F, (cco, cc * 9), dtype=np.uint64).astype(np.uint8)
+    d_xc, d_wc = DeviceBuffer.from_numpy(xcv, dev), DeviceBuffer.from_numpy(wcv, dev)
+    d_sc = DeviceBuffer.from_numpy(np.full(cco, 1e-3, np.float32), dev)
+    crows, ckp = cn * chw * chw, cc * 9
+    d_col, d_yb = DeviceBuffer(crows * ckp * 2, dev), DeviceBuffer(crows * cco * 2, dev)
+    d_wsc = DeviceBuffer(F.linear_workspace_bytes(cco, ckp, "e4m3"), dev)
+    d_oc = DeviceBuffer(crows * cco * 4, dev)
+    from novann_b200._lib import check as _check, lib as _lib_fn
+    from novann_b200.device import _sptr
+
+    def conv_call():
+        _check(_lib_fn().nvq_conv2d_fwd_q(d_oc.at(0), d_xc.at(0), d_wc.at(0), _l.DTYPE_IDS["e4m3"], d_sc.at(0),
+                                          None, d_col.at(0), d_yb.at(0), d_wsc.at(0), d_wsc.nbytes, cn, cc,
+                                          chw, chw, cco, 3, 3, 1, 1, 1, 1, 0, dev, _sptr(st)))
+    t = timed(conv_call, iters=10)
+    F.check_device_errors(dev)
+    out["conv2d_fp8"] = {"N_per_gpu": cn, "C": cc, "HW": chw, "Cout": cco, "kernel": 3, "ms": t,
+                         "tflops_per_gpu": 2.0 * crows * cco * ckp / t / 1e9,
+                         "note": "nvq_conv2d_fwd_q: fp32 NCHW -> bf16 NHWC pass, weight expansion, tcgen05 "
+                                 "implicit GEMM with 4-D TMA boxes (no patch matrix), fp32 NCHW written by "
+                                 "the epilogue; all three kernels in the time"}
+    for b_ in (d_xc, d_wc, d_col, d_yb, d_wsc, d_oc):
+        b_.free()
     # ---- fp32 MLP train step, batch 128 / world rows per GPU, CUDA-graph replay
     bsz = 128 // world
     xm, ym, params = workloads.mlp_inputs(128, (784, 256, 128, 10), seed=0)

@@ -321,12 +321,19 @@ nvq_status nvq_conv2d_bwd_f32(float* d_dw, float* d_db, float* d_dx, const float
                               const float* d_col, const float* d_w, float* d_gr, float* d_dcol,
                               int N, int C, int H, int W, int Cout, int KH, int KW, int sh, int sw,
                               int ph, int pw, int device, void* stream);
-/* Quantised-weight convolution forward on the tensor cores: patches of x are gathered
- * (padding mode applied) and rounded to bf16 into d_col_bf16, laid out rows x kpad with
- * rows = N*OH*OW and kpad = C*KH*KW rounded up to 16 (zero filled); the contraction is
- * nvq_linear_fwd with Wq (Cout x kpad codes, zero padded, E4M3 / E5M2) and Cout per-channel
- * scales; out is fp32 NCHW holding the bf16-rounded results.  Cout % 8 == 0.
- * d_y_bf16: scratch rows x Cout; d_workspace as for nvq_linear_fwd with N=Cout, K=kpad. */
+/* Quantised-weight convolution forward on the tensor cores; Wq is Cout x kpad codes (E4M3 /
+ * E5M2) of w.reshape(Cout, C*KH*KW) zero padded to kpad = C*KH*KW rounded up to 16, with Cout
+ * per-channel scales; out is fp32 NCHW holding the bf16-rounded results.  Cout % 8 == 0.
+ *   Stride 1, zero padding, C % 64 == 0, OW <= 128: implicit GEMM.  x is rewritten as bf16 NHWC
+ *   (into d_col_bf16), the codes are expanded with their columns reordered to (kh, kw, c) (into
+ *   d_workspace), and the CTA-pair tcgen05 kernel gathers its A operand with one 4-D TMA box per
+ *   filter tap and 64-channel block (padding = out-of-range box = zeros) and writes NCHW fp32
+ *   from its epilogue.  No patch matrix exists.
+ *   Otherwise: patches of x are gathered (padding mode applied) and rounded to bf16 into
+ *   d_col_bf16 (rows x kpad, rows = N*OH*OW), the contraction is nvq_linear_fwd, and d_y_bf16
+ *   (rows x Cout) is transposed to NCHW.
+ * Scratch for either path: d_col_bf16 rows*kpad uint16, d_y_bf16 rows*Cout uint16, d_workspace
+ * as for nvq_linear_fwd with N=Cout, K=kpad. */
 nvq_status nvq_conv2d_q_sizes(int N, int C, int H, int W, int Cout, int KH, int KW, int sh, int sw,
                               int ph, int pw, size_t* rows, size_t* kpad);
 nvq_status nvq_conv2d_fwd_q(float* d_out, const float* d_x, const uint8_t* d_wq, nvq_dtype w_fmt,

@@ -99,6 +99,8 @@ __device__ __forceinline__ TileRef tile_ref(const LinearParams& p, int item) {
     const int gsize = min(p.group_m, p.m_blocks - first);
     t.m_blk = first + r % gsize;
     t.n_blk = r / gsize;
+    // a last column block with at most 128 valid columns runs as a half-width tile
+    if (!t.is_half && p.N - t.n_blk * 256 <= 128) t.is_half = 1;
     return t;
 }
 

@@ -376,7 +376,10 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             }
             tc::tc_fence_before();
             __syncwarp();
-            if (lane == 0) tc::mbar_arrive_cluster(tc::mapa(tc::smem_u32(&sh->tmem_empty[acc]), 0));
+            // CTA-scope arrival: what it publishes is "the TMEM reads of this warp are complete"
+            // (tcgen05.wait::ld above); a cluster-scope release would also wait for this warp's
+            // global stores to be acknowledged, which costs microseconds per tile
+            if (lane == 0) tc::mbar_arrive_remote(tc::mapa(tc::smem_u32(&sh->tmem_empty[acc]), 0));
         }
     }
 

@@ -56,15 +56,20 @@ __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity,
                                                 unsigned long long limit_ns) {
     for (int i = 0; i < 128; i++)
         if (mbar_try_wait(bar, parity)) return true;
+    // The clock and the abort flag are looked at once per 32 polls: reading the global timer
+    // between any two polls delayed every hand-off by the read's latency, which short tiles
+    // (a few k-blocks between hand-offs) cannot hide.
     unsigned long long t0 = global_ns();
-    while (!mbar_try_wait(bar, parity)) {
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; i++)
+            if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
         if (global_ns() - t0 > limit_ns) {
             *abort_flag = code;
             return false;
         }
     }
-    return true;
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int code) {
