@@ -6,6 +6,7 @@
     python -m novann_b200.profile_cases linear [M=4096 N=4096 K=4096]
     python -m novann_b200.profile_cases w8a8   [M=4096 N=4096 K=4096]
     python -m novann_b200.profile_cases cnn    [batch=128 steps=3]
+    python -m novann_b200.profile_cases conv   [N=128 C=64 HW=56 Cout=128 reps=2]
 
 Each case uploads seeded inputs, launches the kernels a few times and exits; sizes are
 larger than the 126 MB L2 (so DRAM counters mean something) but hold at most a few GB.
@@ -106,6 +107,30 @@ def case_cnn(batch: int = 128, steps: int = 3) -> None:
         step.step(xs[0], ys[0])
 
 
+def case_conv(n: int = 128, c: int = 64, hw: int = 56, cout: int = 128, reps: int = 2) -> None:
+    """FP8-weight 3x3 convolution (stride 1, pad 1) through nvq_conv2d_fwd_q, device resident."""
+    import ctypes as C
+    from . import _lib
+    from ._lib import check, lib
+    from .device import _sptr
+    st = Stream(0)
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((n, c, hw, hw), dtype=np.float32)
+    wq = rng.integers(0, 0x7F, (cout, c * 9), dtype=np.uint64).astype(np.uint8)
+    dx, dq = DeviceBuffer.from_numpy(x, 0), DeviceBuffer.from_numpy(wq, 0)
+    ds = DeviceBuffer.from_numpy(np.full(cout, 1e-3, np.float32), 0)
+    rows, kpad = n * hw * hw, c * 9
+    col, yb = DeviceBuffer(rows * kpad * 2, 0), DeviceBuffer(rows * cout * 2, 0)
+    ws = DeviceBuffer(F.linear_workspace_bytes(cout, kpad, "e4m3"), 0)
+    out = DeviceBuffer(rows * cout * 4, 0)
+    for _ in range(reps):
+        check(lib().nvq_conv2d_fwd_q(out.at(0), dx.at(0), dq.at(0), _lib.DTYPE_IDS["e4m3"], ds.at(0), None,
+                                     col.at(0), yb.at(0), ws.at(0), ws.nbytes, n, c, hw, hw, cout, 3, 3,
+                                     1, 1, 1, 1, 0, 0, _sptr(st)))
+    st.sync()
+    F.check_device_errors(0)
+
+
 def main(argv) -> None:
     what = argv[1] if len(argv) > 1 else "cast"
     args = [int(a) for a in argv[2:]]
@@ -121,6 +146,8 @@ def main(argv) -> None:
         case_w8a8(*args)
     elif what == "cnn":
         case_cnn(*args)
+    elif what == "conv":
+        case_conv(*args)
     else:
         raise SystemExit(f"unknown case {what}")
     device_sync(0)
