@@ -63,16 +63,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return r;
 }
 
-// AND-reduction + barrier over the 128 epilogue threads (named barrier 1)
+// AND-reduction + barrier over the THREADS epilogue threads (named barrier 1)
+template <int THREADS = 128>
 __device__ __forceinline__ bool epilogue_all(bool ok) {
     uint32_t r;
     asm volatile(
         "{\n\t.reg .pred p, q;\n\t"
         "setp.ne.b32 q, %1, 0;\n\t"
-        "bar.red.and.pred p, 1, 128, q;\n\t"
+        "bar.red.and.pred p, 1, %2, q;\n\t"
         "selp.b32 %0, 1, 0, p;\n\t}"
         : "=r"(r)
-        : "r"((uint32_t)ok)
+        : "r"((uint32_t)ok), "n"(THREADS)
         : "memory");
     return r != 0;
 }

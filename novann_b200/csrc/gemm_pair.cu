@@ -11,9 +11,11 @@
 //           CTAs are counted on the LEADER's full barrier (no multicast anywhere)
 //   warp 1  TMEM allocation (both CTAs, cta_group::2); in the leader one lane issues the MMAs
 //           and commits: slot release and "accumulator ready" are multicast to both CTAs
-//   warps 2-5 epilogue (both CTAs): own 128 rows; "accumulator drained" is signalled to the
-//           leader's barrier, remotely from the peer
-//   warps 6-13 (fused variant only) converters: the weight tile arrives by TMA as raw FP8
+//   warps 2-9 epilogue (both CTAs): own 128 rows, two warps per 32-row TMEM quarter taking
+//           alternate 32-column chunks, the TMEM load of a warp's next chunk in flight while it
+//           stores the current one; "accumulator drained" is signalled to the leader's barrier,
+//           remotely from the peer
+//   warps 10-17 (fused variant only) converters: the weight tile arrives by TMA as raw FP8
 //           codes; these warps expand it to bf16 (exact) straight into the swizzled operand
 //           slot, so no expanded copy of the weight ever exists in HBM.
 // Every wait is bounded; a cluster barrier before teardown keeps a CTA's shared memory alive
@@ -31,6 +33,8 @@ constexpr int B_BYTES = 128 * BK * 2;      // per CTA: half of the tile's weight
 constexpr int RAW_BYTES = 128 * BK;        // fused variant: the same rows as FP8 codes
 constexpr int TMEM_COLS = 512;
 constexpr int MAX_STAGES = 6;
+constexpr int EPI_WARPS = 8;               // warps 2 .. 9
+constexpr int FIRST_CONV_WARP = 2 + EPI_WARPS;
 
 // FUSED = 0: B comes expanded (bf16) from a workspace.  FUSED = NVQ_E4M3 / NVQ_E5M2: B comes as
 // codes and is expanded in shared memory by four extra warps.
@@ -49,7 +53,7 @@ struct Cfg {
     static constexpr int BKE = F8 ? 128 : BK;           // elements of K per k-block
     static constexpr int STAGES = CONV ? 5 : 6;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + (CONV ? RAW_BYTES : 0);
-    static constexpr int THREADS = CONV ? 448 : 192;    // fused: + 8 converter warps
+    static constexpr int THREADS = CONV ? 576 : 320;    // 2 + 8 epilogue warps; fused: + 8 converter warps
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 8192;
 };
 
@@ -129,7 +133,7 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         }
         for (int a = 0; a < 2; a++) {
             tc::mbar_init(tc::smem_u32(&sh->tmem_full[a]), 1);
-            tc::mbar_init(tc::smem_u32(&sh->tmem_empty[a]), 8);   // 4 epilogue warps x 2 CTAs
+            tc::mbar_init(tc::smem_u32(&sh->tmem_empty[a]), 2 * EPI_WARPS);   // epilogue warps x 2 CTAs
         }
         sh->abort_flag = 0;
         tc::mbar_fence_init();
@@ -239,10 +243,10 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 if (ok) tc::tc_commit_pair(tc::smem_u32(&sh->tmem_full[acc]), 3);
             }
         }
-    } else if (CONV && warp >= 6) {
+    } else if (CONV && warp >= FIRST_CONV_WARP) {
         // ------------------------------------------------------------ converters (both CTAs)
         if constexpr (CONV) {
-            const int ct = threadIdx.x - 192;           // 0..255
+            const int ct = threadIdx.x - 32 * FIRST_CONV_WARP;           // 0..255
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             // The raw codes of a k-block are read into registers one k-block ahead, so the
@@ -309,8 +313,9 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         }
     } else {
         // ------------------------------------------------------------ epilogue (both CTAs)
-        const int quarter = warp & 3;
-        const int et = threadIdx.x - 64;
+        const int quarter = warp & 3;                 // the TMEM lanes this warp may read
+        const int colgrp = (warp - 2) >> 2;           // 0 / 1: even / odd 32-column chunks
+        const int et = threadIdx.x - 64;              // 0 .. 255
         const bool vec32 = (p.N % 16) == 0;
         bool ok = true;
         int it = 0;
@@ -320,58 +325,72 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             const int bn = tr.is_half ? BN / 2 : BN;
             const int m0 = tr.m_blk * BM + (int)rank * 128;
             const int n0 = tr.n_blk * BN + tr.half * (BN / 2);
-            for (int c = et; c < bn; c += 128) {
+            for (int c = et; c < bn; c += 32 * EPI_WARPS) {
                 int n = n0 + c;
                 sh->scale[acc][c] = (p.scales && n < p.N) ? p.scales[n] : 1.f;
                 sh->bias[acc][c] = (p.bias && n < p.N) ? p.bias[n] : 0.f;
             }
             ok = tc::mbar_wait(tc::smem_u32(&sh->tmem_full[acc]), acc_phase, abort_flag, ERR_EPILOGUE);
-            ok = epilogue_all(ok);
+            ok = epilogue_all<32 * EPI_WARPS>(ok);
             if (!ok) break;
             tc::tc_fence_after();
             const int row = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+            // implicit convolution: row r of this CTA's tile is output position oh0 * OW + r of
+            // image img (the box spans whole output rows); each thread owns one position, so for a
+            // fixed channel a warp writes 32 consecutive floats of the NCHW plane
+            bool valid = row < p.M;
+            float* obase = nullptr;
+            int S = 0;
             if constexpr (IMPL) {
-                // row r of this CTA's tile is output position oh0 * OW + r of image img (the box
-                // spans whole output rows); each thread owns one position, so for a fixed channel
-                // a warp writes 32 consecutive floats of the NCHW plane
                 const int cta_tile = tr.m_blk * 2 + (int)rank;
                 const int img = cta_tile / p.conv_th, oh0 = (cta_tile % p.conv_th) * p.conv_bh;
-                const int r_in = quarter * 32 + lane, S = p.conv_OH * p.conv_OW;
+                const int r_in = quarter * 32 + lane;
+                S = p.conv_OH * p.conv_OW;
                 const int pos = oh0 * p.conv_OW + r_in;
-                const bool valid = img < p.conv_images && r_in < p.conv_bw * p.conv_bh && pos < S;
-                float* obase = (float*)p.y + ((size_t)img * p.N + n0) * S + pos;
-#pragma unroll 1
-                for (int c = 0; c < bn; c += 32) {
-                    uint32_t r[32];
-                    tc::tmem_ld_32x32(taddr + c, r);
-                    tc::tmem_ld_wait();
-                    if (valid) {
+                valid = img < p.conv_images && r_in < p.conv_bw * p.conv_bh && pos < S;
+                obase = (float*)p.y + ((size_t)img * p.N + n0) * S + pos;
+            }
+            auto emit = [&](uint32_t* r, int c) {      // one 32-column chunk of this thread's row
+                if (!valid) return;
+                if constexpr (IMPL) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 2) {
-                            if (n0 + c + j < p.N) {      // N % 8 == 0: pairs are in or out together
-                                const float v0 = fmaf(__uint_as_float(r[j]), sh->scale[acc][c + j], sh->bias[acc][c + j]);
-                                const float v1 = fmaf(__uint_as_float(r[j + 1]), sh->scale[acc][c + j + 1], sh->bias[acc][c + j + 1]);
-                                const uint32_t pk = pack_bf16(v0, v1);     // the bf16 result, widened again
-                                obase[(size_t)(c + j) * S] = __uint_as_float(pk << 16);
-                                obase[(size_t)(c + j + 1) * S] = __uint_as_float(pk & 0xFFFF0000u);
-                            }
+                    for (int j = 0; j < 32; j += 2) {
+                        if (n0 + c + j < p.N) {      // N % 8 == 0: pairs are in or out together
+                            const float v0 = fmaf(__uint_as_float(r[j]), sh->scale[acc][c + j], sh->bias[acc][c + j]);
+                            const float v1 = fmaf(__uint_as_float(r[j + 1]), sh->scale[acc][c + j + 1], sh->bias[acc][c + j + 1]);
+                            const uint32_t pk = pack_bf16(v0, v1);     // the bf16 result, widened again
+                            obase[(size_t)(c + j) * S] = __uint_as_float(pk << 16);
+                            obase[(size_t)(c + j + 1) * S] = __uint_as_float(pk & 0xFFFF0000u);
                         }
                     }
-                }
-            } else
-#pragma unroll 1
-            for (int c = 0; c < bn; c += 32) {
-                uint32_t r[32];
-                tc::tmem_ld_32x32(taddr + c, r);
-                tc::tmem_ld_wait();
-                if (row < p.M) {
+                } else {
                     if (p.row_scales) {   // per-row activation scale (quantised activations)
                         const float rs = p.row_scales[row];
 #pragma unroll
                         for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__fmul_rn(__uint_as_float(r[j]), rs));
                     }
                     store_row_chunk(p, r, &sh->scale[acc][c], &sh->bias[acc][c], row, n0 + c, vec32);
+                }
+            };
+            // this warp's chunks: columns colgrp*32 + 64*i; chunk i+1 is loaded from TMEM while
+            // chunk i is scaled and stored (tcgen05.wait::ld waits for every load issued so far,
+            // so the next load is issued right after the wait)
+            uint32_t ra[32], rb[32];
+            const int c_first = colgrp * 32;
+            tc::tmem_ld_32x32(taddr + c_first, ra);
+#pragma unroll
+            for (int i = 0; i < BN / 64; i += 2) {
+                const int c0 = c_first + 64 * i, c1 = c0 + 64, c2 = c1 + 64;
+                if (c0 < bn) {
+                    tc::tmem_ld_wait();
+                    if (c1 < bn) tc::tmem_ld_32x32(taddr + c1, rb);
+                    emit(ra, c0);
+                }
+                if (c1 < bn) {
+                    tc::tmem_ld_wait();
+                    if (c2 < bn) tc::tmem_ld_32x32(taddr + c2, ra);
+                    emit(rb, c1);
                 }
             }
             tc::tc_fence_before();
