@@ -514,6 +514,49 @@ nchw_f32_to_nhwc_bf16_kernel(uint16_t* __restrict__ out, const float* __restrict
     }
 }
 
+// Same for S % 4 == 0: 64 pixels x 64 channels per tile, four 16-byte loads in flight per thread
+// (one channel, four consecutive pixels each), two 16-byte stores (one pixel, eight channels each).
+__global__ void __launch_bounds__(256)
+nchw_f32_to_nhwc_bf16_v4_kernel(uint16_t* __restrict__ out, const float* __restrict__ x, int N, int C,
+                                int S) {
+    __shared__ uint16_t tile[64][64 + 2];
+    const int s_tiles = (S + 63) / 64, c_tiles = C / 64;
+    const long long total = (long long)N * s_tiles * c_tiles;
+    const int lc = threadIdx.x >> 4, lp = threadIdx.x & 15;       // load role: channel row, pixel quad
+    const int wr = threadIdx.x >> 3, wseg = threadIdx.x & 7;      // store role: pixel, 8-channel group
+    for (long long t = blockIdx.x; t < total; t += gridDim.x) {
+        const int ct = (int)(t % c_tiles), stl = (int)((t / c_tiles) % s_tiles);
+        const int n = (int)(t / ((long long)c_tiles * s_tiles));
+        const int s0 = stl * 64, c0 = ct * 64;
+        float4 v[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int c = lc + 16 * i, s = s0 + 4 * lp;
+            v[i] = s < S ? *reinterpret_cast<const float4*>(x + ((size_t)n * C + c0 + c) * S + s)
+                         : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int c = lc + 16 * i;
+            tile[4 * lp + 0][c] = (uint16_t)spec_f32_to_bf16(__float_as_uint(v[i].x));
+            tile[4 * lp + 1][c] = (uint16_t)spec_f32_to_bf16(__float_as_uint(v[i].y));
+            tile[4 * lp + 2][c] = (uint16_t)spec_f32_to_bf16(__float_as_uint(v[i].z));
+            tile[4 * lp + 3][c] = (uint16_t)spec_f32_to_bf16(__float_as_uint(v[i].w));
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int px = wr + 32 * i;
+            if (s0 + px < S) {
+                const uint32_t* src = reinterpret_cast<const uint32_t*>(&tile[px][wseg * 8]);
+                *reinterpret_cast<uint4*>(out + ((size_t)n * S + s0 + px) * C + c0 + wseg * 8) =
+                    make_uint4(src[0], src[1], src[2], src[3]);
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // FP8 weight codes (Cout x Kpad, columns (c, kh, kw)) -> bf16 (Cout x KH*KW*C, columns
 // (kh, kw, c)), exact
 template <int FMT>
@@ -777,8 +820,14 @@ extern "C" nvq_status nvq_conv2d_fwd_q(float* d_out, const float* d_x, const uin
                              !(cmode && cmode[0] == 'e');
     if (implicit_ok) {
         const int S_in = H * W;
-        const size_t want = (size_t)N * ((S_in + 31) / 32) * (C / 64), cap = (size_t)nvq_sm_count(device) * 16;
-        nchw_f32_to_nhwc_bf16_kernel<<<(unsigned)std::min(want, cap), 256, 0, st>>>(d_col_bf16, d_x, N, C, S_in);
+        const size_t cap = (size_t)nvq_sm_count(device) * 16;
+        if (S_in % 4 == 0 && nvq_aligned(d_x, 16)) {
+            const size_t want = (size_t)N * ((S_in + 63) / 64) * (C / 64);
+            nchw_f32_to_nhwc_bf16_v4_kernel<<<(unsigned)std::min(want, cap), 256, 0, st>>>(d_col_bf16, d_x, N, C, S_in);
+        } else {
+            const size_t want = (size_t)N * ((S_in + 31) / 32) * (C / 64);
+            nchw_f32_to_nhwc_bf16_kernel<<<(unsigned)std::min(want, cap), 256, 0, st>>>(d_col_bf16, d_x, N, C, S_in);
+        }
         NVQ_LAUNCHED();
         const int wtotal = Cout * C * KH * KW;
         if (w_fmt == NVQ_E4M3)
