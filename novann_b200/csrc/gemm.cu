@@ -491,6 +491,13 @@ extern "C" nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf1
         return nvq_linear_launch_pair_fused(d_y_bf16, d_x_bf16, d_wq, w_fmt, d_w_scales, d_bias, M, N, K,
                                             0, device, st);
     }
+    // Few rows: the time is the time to read the weight, so read it once, as codes.  The
+    // workspace then holds fp32 partial sums instead of an expanded weight.
+    if (w_fmt != NVQ_E2M1_B32 && M <= 128 && K % 16 == 0 && nvq_aligned(d_wq, 16) && nvq_aligned(d_x_bf16, 16) &&
+        d_workspace && nvq_aligned(d_workspace, 16) && !mode && M * N < (1u << 31) && N < (1u << 24) &&
+        K < (1u << 24) && workspace_bytes >= nvq_linear_small_m_workspace(M, N, K, device))
+        return nvq_linear_launch_small_m(d_y_bf16, d_x_bf16, d_wq, w_fmt, d_w_scales, d_bias, M, N, K,
+                                         (float*)d_workspace, device, st);
     NVQ_REQUIRE(d_workspace && workspace_bytes >= N * K * 2 && nvq_aligned(d_workspace, 32),
                 "nvq_linear_fwd: workspace of %zu bytes (32-byte aligned) required", N * K * 2);
     s = nvq_linear_expand_weight((uint16_t*)d_workspace, d_wq, w_fmt, d_w_scales, N, K, device, stream);

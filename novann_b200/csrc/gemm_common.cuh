@@ -49,6 +49,14 @@ nvq_status nvq_linear_launch_pair_w8a8(uint16_t* d_y, const uint8_t* d_xq, const
                                        const float* d_bias, size_t M, size_t N, size_t K, int device,
                                        cudaStream_t st);
 
+// Few rows (M <= 128), FP8 codes: weight-streaming kernel with the dequantisation fused (the codes
+// are read once, nothing expanded is written); d_partial holds nvq_linear_small_m_workspace bytes.
+size_t nvq_linear_small_m_workspace(size_t M, size_t N, size_t K, int device);
+nvq_status nvq_linear_launch_small_m(uint16_t* d_y, const uint16_t* d_x, const uint8_t* d_wq,
+                                     nvq_dtype fmt, const float* d_scales, const float* d_bias,
+                                     size_t M, size_t N, size_t K, float* d_partial, int device,
+                                     cudaStream_t st);
+
 // Convolution as an implicit GEMM on the CTA-pair kernel: x bf16 NHWC, weight bf16 (Cout x
 // KH*KW*C, columns ordered (kh, kw, c)), out fp32 NCHW holding bf16-rounded values.
 nvq_status nvq_conv_launch_pair_implicit(float* d_out, const uint16_t* d_x_nhwc, const uint16_t* d_w,
@@ -61,6 +69,67 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
+}
+
+// ---- exact FP8 -> bf16 expansion in registers (the converter warps of the fused kernels) ----
+// Two FP8 codes (the bytes of w selected by sel) -> two bf16 values.  The code's exponent and
+// mantissa bits are dropped into the low end of the bf16 exponent and the top of its mantissa;
+// one bf16 multiply by 2^(127 - bias) then fixes the exponent bias and, because bf16 arithmetic
+// keeps subnormals, also normalises the codes whose exponent field is zero.  Exact for every
+// finite code; the non-finite codes are patched by expand16.
+template <int FMT>
+__device__ __forceinline__ uint32_t expand2(uint32_t w, uint32_t sel) {
+    const uint32_t hi = __byte_perm(w, 0u, sel);                 // code bytes -> bits 15:8 / 31:24
+    constexpr int sh = FMT == NVQ_E4M3 ? 4 : 3;                  // 7 magnitude bits -> bits 10:4 / 11:5
+    constexpr uint32_t mmask = FMT == NVQ_E4M3 ? 0x07F007F0u : 0x0FE00FE0u;
+    constexpr uint32_t rebias = FMT == NVQ_E4M3 ? 0x7B807B80u    // 2^120 as bf16, twice
+                                                : 0x77807780u;   // 2^112
+    const uint32_t t = ((hi >> sh) & mmask) | (hi & 0x80008000u);
+    uint32_t r;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(t), "r"(rebias));
+    return r;
+}
+
+// Lanes of an expand2 result whose code is non-finite (E4M3: 0x7f / 0xff = NaN; E5M2: 0x7c = inf,
+// 0x7d.. = NaN) get all exponent bits (and for E4M3 the top mantissa bit) set on top of what the
+// bit placement produced: 0x7f -> NaN; 0x7c -> inf exactly (its mantissa is zero), 0x7d.. -> NaN.
+// `flags` has bit 7 of a byte set where that code is non-finite.
+template <int FMT>
+__device__ __forceinline__ uint32_t patch_non_finite(uint32_t r, uint32_t flags, uint32_t sel) {
+    const uint32_t f = __byte_perm(flags, 0u, sel);              // flag -> bit 15 / 31 of its lane
+    return r | (f - (f >> (FMT == NVQ_E4M3 ? 9 : 8)));           // 0x7fc0 / 0x7f80 per flagged lane
+}
+
+// 16 FP8 codes (four words) -> 16 bf16 values (eight words), so that the fused kernels give what
+// the expansion pass gives for every code.  The test for non-finite codes is two operations per
+// word; the patch itself runs only for chunks that hold one.
+template <int FMT>
+__device__ __forceinline__ uint32_t non_finite_flags(uint32_t w) {
+    const uint32_t x = w | 0x80808080u;      // sign out of the way: 0xff / >= 0xfc marks a non-finite code
+    return FMT == NVQ_E4M3 ? __vcmpeq4(x, 0xFFFFFFFFu) : __vcmpgeu4(x, 0xFCFCFCFCu);
+}
+
+template <int FMT>
+__device__ __forceinline__ void expand16(const uint4& in, uint4& lo, uint4& hi) {
+    const uint32_t w[4] = {in.x, in.y, in.z, in.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        o[2 * i] = expand2<FMT>(w[i], 0x1404);       // bytes 0, 1
+        o[2 * i + 1] = expand2<FMT>(w[i], 0x3424);   // bytes 2, 3
+    }
+    const uint32_t any = non_finite_flags<FMT>(w[0]) | non_finite_flags<FMT>(w[1]) |
+                         non_finite_flags<FMT>(w[2]) | non_finite_flags<FMT>(w[3]);
+    if (__builtin_expect(any != 0, 0)) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t fl = non_finite_flags<FMT>(w[i]) & 0x80808080u;
+            o[2 * i] = patch_non_finite<FMT>(o[2 * i], fl, 0x1404);
+            o[2 * i + 1] = patch_non_finite<FMT>(o[2 * i + 1], fl, 0x3424);
+        }
+    }
+    lo = make_uint4(o[0], o[1], o[2], o[3]);
+    hi = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
 // AND-reduction + barrier over the THREADS epilogue threads (named barrier 1)

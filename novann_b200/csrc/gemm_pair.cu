@@ -71,38 +71,6 @@ struct Shared {
     float bias[2][BN];
 };
 
-// Two FP8 codes (the two bytes selected by `sel` from w) -> two bf16 values, exactly.
-// The code's exponent and mantissa bits are dropped into the low end of the bf16 exponent and
-// the top of its mantissa; one bf16 multiply by 2^(127 - bias) then fixes the exponent bias
-// and, because bf16 arithmetic keeps subnormals, also normalises the codes whose exponent
-// field is zero.
-template <int FMT>
-__device__ __forceinline__ uint32_t expand2(uint32_t w, uint32_t sel) {
-    const uint32_t hi = __byte_perm(w, 0u, sel);                 // code bytes -> bits 15:8 / 31:24
-    constexpr int sh = FMT == NVQ_E4M3 ? 4 : 3;                  // 7 magnitude bits -> bits 10:4 / 11:5
-    constexpr uint32_t mmask = FMT == NVQ_E4M3 ? 0x07F007F0u : 0x0FE00FE0u;
-    constexpr uint32_t rebias = FMT == NVQ_E4M3 ? 0x7B807B80u    // 2^120 as bf16, twice
-                                                : 0x77807780u;   // 2^112
-    const uint32_t t = ((hi >> sh) & mmask) | (hi & 0x80008000u);
-    uint32_t r;
-    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(t), "r"(rebias));
-    return r;
-}
-
-// 16 FP8 codes (four words) -> 16 bf16 values (eight words)
-template <int FMT>
-__device__ __forceinline__ void expand16(const uint4& in, uint4& lo, uint4& hi) {
-    const uint32_t w[4] = {in.x, in.y, in.z, in.w};
-    uint32_t o[8];
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        o[2 * i] = expand2<FMT>(w[i], 0x1404);       // bytes 0, 1
-        o[2 * i + 1] = expand2<FMT>(w[i], 0x3424);   // bytes 2, 3
-    }
-    lo = make_uint4(o[0], o[1], o[2], o[3]);
-    hi = make_uint4(o[4], o[5], o[6], o[7]);
-}
-
 template <int FUSED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg<FUSED>::THREADS, 1)
 linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,

@@ -213,3 +213,49 @@ def test_linear_split_last_wave_and_deep_k(gpu, m, n, k):
     rows = np.unique(np.concatenate([np.arange(0, m, 37), [m - 1, 255, 256, 257]]))
     want, _ = o.linear_fwd_qweight(xb[rows], wq, sc, b, "e4m3")
     assert o.max_abs_rel(o.bf16_bits_to_f32(y[rows]), o.bf16_bits_to_f32(want)) <= 2.0 ** -7
+
+
+@pytest.mark.parametrize("fmt", ["e4m3", "e5m2"])
+@pytest.mark.parametrize("m,n,k", [
+    (1, 128, 64), (3, 8, 16), (16, 4096, 4096), (17, 1000, 336), (64, 264, 8192), (100, 2048, 48),
+    (128, 4096, 1024), (128, 136, 4160), (31, 20000, 64),
+])
+def test_linear_few_rows_weight_streaming_kernel(gpu, fmt, m, n, k, monkeypatch):
+    """M <= 128 runs the weight-streaming kernel (codes read once, expanded in shared memory,
+    operands swapped, split along K with a deterministic reduction): against the oracle, against
+    the expansion-pass path of the same call, and twice in a row (same bits)."""
+    xb, w, b = workloads.linear_inputs(m, n, k, seed=m + n)
+    wq, sc = o.quantize_weight_per_channel(w, fmt)
+    monkeypatch.delenv("NVQ_LINEAR_MODE", raising=False)
+    y = F.linear_q_host(xb, wq, sc, b, fmt, gpu)
+    y2 = F.linear_q_host(xb, wq, sc, b, fmt, gpu)
+    assert np.array_equal(y, y2)
+    want_bits, _ = o.linear_fwd_qweight(xb, wq, sc, b, fmt)
+    err = o.max_abs_rel(o.bf16_bits_to_f32(y), o.bf16_bits_to_f32(want_bits))
+    assert err <= 2.0 ** -7, err
+    monkeypatch.setenv("NVQ_LINEAR_MODE", "single")          # expansion pass + single-CTA kernel
+    y_old = F.linear_q_host(xb, wq, sc, b, fmt, gpu)
+    assert o.max_abs_rel(o.bf16_bits_to_f32(y), o.bf16_bits_to_f32(y_old)) <= 2.0 ** -7
+    assert np.mean(y == y_old) > 0.9
+    F.check_device_errors(gpu)
+
+
+@pytest.mark.parametrize("m,fmt", [(8, "e4m3"), (8, "e5m2"), (256, "e4m3"), (256, "e5m2")])
+def test_linear_in_kernel_expansion_of_every_code(gpu, m, fmt):
+    """Every FP8 code (subnormals, NaN / inf codes, both zeros) through the in-kernel expansion:
+    the few-rows kernel (m = 8) and the fused CTA-pair kernel (m = 256, no workspace).  Row n of
+    the weight holds code n repeated, x is all ones."""
+    n, k = 256, 64
+    wq = np.repeat(np.arange(256, dtype=np.uint8)[:, None], k, axis=1)
+    xb = o.f32_to_bf16_bits(np.ones((m, k), np.float32))
+    sc = np.ones(n, np.float32)
+    y = o.bf16_bits_to_f32(F.linear_q_host(xb, wq, sc, None, fmt, gpu, use_workspace=m <= 128))
+    table = o.E4M3_TABLE if fmt == "e4m3" else o.E5M2_TABLE
+    with np.errstate(all="ignore"):
+        vals = table[np.arange(256)].astype(np.float64) * k
+        want = o.bf16_bits_to_f32(o.f32_to_bf16_bits(vals.astype(np.float32)))
+    nan = np.isnan(want)
+    assert nan.sum() == (2 if fmt == "e4m3" else 6)
+    assert np.array_equal(np.isnan(y[0]), nan)
+    assert np.array_equal(y[0][~nan], want[~nan])
+    assert np.array_equal(np.nan_to_num(y), np.nan_to_num(np.broadcast_to(y[0], y.shape)))
