@@ -196,20 +196,27 @@ linear_small_m_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                              : "=r"(nxt[j].x), "=r"(nxt[j].y), "=r"(nxt[j].z), "=r"(nxt[j].w)
                              : "r"(codes + (ct + GT * j) * 16));
         };
+        // ring position of this group's current unit and of its next one, advanced by
+        // CONV_GROUPS slots per step (no divisions in the loop)
+        uint32_t stage = (uint32_t)grp % STAGES, phase = ((uint32_t)grp / STAGES) & 1u;
+        auto advance = [&](uint32_t& st, uint32_t& ph) {
+            st += CONV_GROUPS;
+            if (st >= STAGES) { st -= STAGES; ph ^= 1u; }
+        };
+        uint32_t nstage = stage, nphase = phase;
+        advance(nstage, nphase);
         bool ok = grp < my_units;
         if (ok) {   // the codes of a unit are read into registers one unit of this group ahead
-            ok = tc::mbar_wait(tc::smem_u32(&sh->raw_full[grp % STAGES]), (grp / STAGES) & 1, abort_flag, ERR_CONVERT);
-            if (ok) load_codes(grp % STAGES);
+            ok = tc::mbar_wait(tc::smem_u32(&sh->raw_full[stage]), phase, abort_flag, ERR_CONVERT);
+            if (ok) load_codes(stage);
         }
         for (int u = grp; u < my_units && ok; u += CONV_GROUPS) {
             uint4 in[CH];
 #pragma unroll
             for (int j = 0; j < CH; j++) in[j] = nxt[j];
-            const uint32_t stage = u % STAGES, phase = (u / STAGES) & 1;
-            const int un = u + CONV_GROUPS;
-            if (un < my_units) {
-                ok = tc::mbar_wait(tc::smem_u32(&sh->raw_full[un % STAGES]), (un / STAGES) & 1, abort_flag, ERR_CONVERT);
-                if (ok) load_codes(un % STAGES);
+            if (u + CONV_GROUPS < my_units) {
+                ok = tc::mbar_wait(tc::smem_u32(&sh->raw_full[nstage]), nphase, abort_flag, ERR_CONVERT);
+                if (ok) load_codes(nstage);
             }
             // the operand slot is free once the MMAs of its previous use have completed
             ok = ok && tc::mbar_wait(tc::smem_u32(&sh->empty[stage]), phase ^ 1, abort_flag, ERR_CONVERT);
@@ -235,6 +242,9 @@ linear_small_m_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(tc::smem_u32(&sh->full[stage]));
+            stage = nstage;
+            phase = nphase;
+            advance(nstage, nphase);
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 2-5)
