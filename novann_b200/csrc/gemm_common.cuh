@@ -72,20 +72,29 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // ---- exact FP8 -> bf16 expansion in registers (the converter warps of the fused kernels) ----
-// Two FP8 codes (the bytes of w selected by sel) -> two bf16 values.  The code's exponent and
-// mantissa bits are dropped into the low end of the bf16 exponent and the top of its mantissa;
-// one bf16 multiply by 2^(127 - bias) then fixes the exponent bias and, because bf16 arithmetic
-// keeps subnormals, also normalises the codes whose exponent field is zero.  Exact for every
-// finite code; the non-finite codes are patched by expand16.
-template <int FMT>
-__device__ __forceinline__ uint32_t expand2(uint32_t w, uint32_t sel) {
-    const uint32_t hi = __byte_perm(w, 0u, sel);                 // code bytes -> bits 15:8 / 31:24
-    constexpr int sh = FMT == NVQ_E4M3 ? 4 : 3;                  // 7 magnitude bits -> bits 10:4 / 11:5
-    constexpr uint32_t mmask = FMT == NVQ_E4M3 ? 0x07F007F0u : 0x0FE00FE0u;
-    constexpr uint32_t rebias = FMT == NVQ_E4M3 ? 0x7B807B80u    // 2^120 as bf16, twice
-                                                : 0x77807780u;   // 2^112
-    const uint32_t t = ((hi >> sh) & mmask) | (hi & 0x80008000u);
-    uint32_t r;
+// Two FP8 codes (bytes 2*PAIR and 2*PAIR+1 of w) -> two bf16 values.  The code's exponent and
+// mantissa bits are dropped into the low end of the bf16 exponent and the top of its mantissa,
+// the sign into bit 15; one bf16 multiply by 2^(127 - bias) then fixes the exponent bias and,
+// because bf16 arithmetic keeps subnormals, also normalises the codes whose exponent field is
+// zero.  Exact for every finite code; the non-finite codes are patched by expand16.
+// With b = s << 7 | mag the placed pattern s << 15 | mag << SH equals b << SH + (b & 0x80) *
+// (2^8 - 2^SH), per 16-bit lane and without carries between lanes.  It is written as two
+// integer multiply-adds on purpose: they issue on the FMA pipe, and the converter warps are
+// bound by the half-rate integer / logic pipe that shifts and logic operations use.
+template <int FMT, int PAIR>
+__device__ __forceinline__ uint32_t expand2(uint32_t w) {
+    const uint32_t L = __byte_perm(w, 0u, PAIR == 0 ? 0x4140 : 0x4342);   // codes -> low byte of each lane
+    constexpr uint32_t up = FMT == NVQ_E4M3 ? 16u : 8u;                     // 2^SH
+    constexpr uint32_t lift = 256u - up;
+    constexpr uint32_t rebias = FMT == NVQ_E4M3 ? 0x7B807B80u               // 2^120 as bf16, twice
+                                                : 0x77807780u;              // 2^112
+    uint32_t t, r;
+    asm("{\n\t.reg .b32 s, u;\n\t"
+        "and.b32 s, %1, 0x00800080;\n\t"
+        "mul.lo.u32 u, s, %2;\n\t"
+        "mad.lo.u32 %0, %1, %3, u;\n\t}"
+        : "=r"(t)
+        : "r"(L), "r"(lift), "r"(up));
     asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(t), "r"(rebias));
     return r;
 }
@@ -115,8 +124,8 @@ __device__ __forceinline__ void expand16(const uint4& in, uint4& lo, uint4& hi) 
     uint32_t o[8];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        o[2 * i] = expand2<FMT>(w[i], 0x1404);       // bytes 0, 1
-        o[2 * i + 1] = expand2<FMT>(w[i], 0x3424);   // bytes 2, 3
+        o[2 * i] = expand2<FMT, 0>(w[i]);       // bytes 0, 1
+        o[2 * i + 1] = expand2<FMT, 1>(w[i]);   // bytes 2, 3
     }
     const uint32_t any = non_finite_flags<FMT>(w[0]) | non_finite_flags<FMT>(w[1]) |
                          non_finite_flags<FMT>(w[2]) | non_finite_flags<FMT>(w[3]);

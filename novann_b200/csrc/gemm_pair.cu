@@ -35,6 +35,11 @@ constexpr int TMEM_COLS = 512;
 constexpr int MAX_STAGES = 6;
 constexpr int EPI_WARPS = 8;               // warps 2 .. 9
 constexpr int FIRST_CONV_WARP = 2 + EPI_WARPS;
+#ifndef NVQ_PAIR_CONV_GROUPS
+#define NVQ_PAIR_CONV_GROUPS 2
+#endif
+constexpr int PAIR_CONV_GROUPS = NVQ_PAIR_CONV_GROUPS;   // fused variant: k-blocks expanded concurrently
+static_assert(PAIR_CONV_GROUPS == 1 || PAIR_CONV_GROUPS == 2, "the five-slot ring feeds at most two groups");
 
 // FUSED = 0: B comes expanded (bf16) from a workspace.  FUSED = NVQ_E4M3 / NVQ_E5M2: B comes as
 // codes and is expanded in shared memory by four extra warps.
@@ -95,7 +100,7 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         for (int s = 0; s < STAGES; s++) {
             // fused: the leader's full barrier also collects one arrival per converter warp of
             // both CTAs (8 + 8) on top of the producer's
-            tc::mbar_init(tc::smem_u32(&sh->full[s]), CONV ? 17 : 1);
+            tc::mbar_init(tc::smem_u32(&sh->full[s]), CONV ? 1 + 16 / PAIR_CONV_GROUPS : 1);
             tc::mbar_init(tc::smem_u32(&sh->empty[s]), 1);
             tc::mbar_init(tc::smem_u32(&sh->raw_full[s]), 1);
         }
@@ -214,35 +219,50 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     } else if (CONV && warp >= FIRST_CONV_WARP) {
         // ------------------------------------------------------------ converters (both CTAs)
         if constexpr (CONV) {
-            const int ct = threadIdx.x - 32 * FIRST_CONV_WARP;           // 0..255
-            uint32_t stage = 0, phase = 0;
+            // The eight warps form PAIR_CONV_GROUPS groups that take alternate k-blocks, so that
+            // many k-blocks are being expanded at any time (a group's wait -> load -> expand -> store
+            // -> fence -> arrive chain is latency-bound).  A group reads the codes of its next
+            // k-block into registers before it expands the current one.  Chunk i = 16 codes:
+            // row i/4, quarter i%4 of the 64-byte raw row; rows past a half-width tile's extent are
+            // read (inside the slot) and dropped.
+            constexpr int G = PAIR_CONV_GROUPS, GT = 256 / G, CH = 512 / GT;
+            const int cidx = threadIdx.x - 32 * FIRST_CONV_WARP;          // 0..255
+            const int grp = cidx / GT, ct = cidx % GT;
             bool ok = true;
-            // The raw codes of a k-block are read into registers one k-block ahead, so the
-            // shared-memory load latency is off the wait -> expand -> store -> arrive chain.
-            // Chunk i = 16 codes: row i/4, quarter i%4 of the 64-byte raw row; two chunks per
-            // thread.  Rows past a half-width tile's extent are read (inside the slot) and dropped.
-            uint4 nxt[2] = {};
+            uint4 nxt[CH];
             auto load_codes = [&](uint32_t st) {
                 const uint32_t codes = tiles + st * STAGE_BYTES + A_BYTES + B_BYTES;
 #pragma unroll
-                for (int j = 0; j < 2; j++)
+                for (int j = 0; j < CH; j++)
                     asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
                                  : "=r"(nxt[j].x), "=r"(nxt[j].y), "=r"(nxt[j].z), "=r"(nxt[j].w)
-                                 : "r"(codes + (ct + 256 * j) * 16));
+                                 : "r"(codes + (ct + GT * j) * 16));
             };
-            if (pair < p.num_items && num_kb > 0) {
-                ok = tc::mbar_wait(tc::smem_u32(&sh->raw_full[0]), 0, abort_flag, ERR_CONVERT);
-                if (ok) load_codes(0);
+            const int my_tiles = pair < p.num_items ? (p.num_items - pair + num_pairs - 1) / num_pairs : 0;
+            const int total_units = my_tiles * num_kb;
+            // ring position of unit `unit` (all k-blocks of this CTA, in order)
+            uint32_t stage = 0, phase = 0;
+            auto step = [&](uint32_t& st, uint32_t& ph, int n) {
+                st += n;
+                if (st >= (uint32_t)STAGES) { st -= STAGES; ph ^= 1u; }
+            };
+            if (grp < total_units) {
+                ok = tc::mbar_wait(tc::smem_u32(&sh->raw_full[grp]), 0, abort_flag, ERR_CONVERT);   // grp < STAGES
+                if (ok) load_codes(grp);
             }
+            int unit = 0;
             for (int t = pair; t < p.num_items && ok; t += num_pairs) {
                 const TileRef tr = tile_ref(p, t);
                 const int rows_b = (tr.is_half ? BN / 2 : BN) / 2;
-                for (int kb = 0; kb < num_kb; kb++) {
-                    const uint4 in[2] = {nxt[0], nxt[1]};
-                    uint32_t nstage = stage + 1, nphase = phase;
-                    if (nstage == STAGES) { nstage = 0; nphase ^= 1; }
-                    if (kb + 1 < num_kb || t + num_pairs < p.num_items) {
-                        // the codes of the next k-block have landed (the producer runs ahead)
+                for (int kb = 0; kb < num_kb; kb++, unit++, step(stage, phase, 1)) {
+                    if ((unit % G) != grp) continue;
+                    uint4 in[CH];
+#pragma unroll
+                    for (int j = 0; j < CH; j++) in[j] = nxt[j];
+                    if (unit + G < total_units) {
+                        // the codes of this group's next k-block have landed (the producer runs ahead)
+                        uint32_t nstage = stage, nphase = phase;
+                        step(nstage, nphase, G);
                         ok = ok && tc::mbar_wait(tc::smem_u32(&sh->raw_full[nstage]), nphase, abort_flag, ERR_CONVERT);
                         if (ok) load_codes(nstage);
                     }
@@ -254,8 +274,8 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     // 16 codes -> 16-byte chunks 2q, 2q+1 of the 128-byte operand row, placed by
                     // the 128-byte swizzle (chunk index XOR row mod 8)
 #pragma unroll
-                    for (int j = 0; j < 2; j++) {
-                        const int i = ct + 256 * j;
+                    for (int j = 0; j < CH; j++) {
+                        const int i = ct + GT * j;
                         if (i < rows_b * 4) {
                             const int r = i >> 2, q = i & 3;
                             uint4 lo, hi;
@@ -274,8 +294,6 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) tc::mbar_arrive_remote(tc::mapa(tc::smem_u32(&sh->full[stage]), 0));
-                    stage = nstage;
-                    phase = nphase;
                 }
             }
         }
@@ -341,24 +359,36 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     store_row_chunk(p, r, &sh->scale[acc][c], &sh->bias[acc][c], row, n0 + c, vec32);
                 }
             };
-            // this warp's chunks: columns colgrp*32 + 64*i; chunk i+1 is loaded from TMEM while
-            // chunk i is scaled and stored (tcgen05.wait::ld waits for every load issued so far,
-            // so the next load is issued right after the wait)
-            uint32_t ra[32], rb[32];
+            // this warp's chunks: columns colgrp*32 + 64*i
             const int c_first = colgrp * 32;
-            tc::tmem_ld_32x32(taddr + c_first, ra);
-#pragma unroll
-            for (int i = 0; i < BN / 64; i += 2) {
-                const int c0 = c_first + 64 * i, c1 = c0 + 64, c2 = c1 + 64;
-                if (c0 < bn) {
+            if constexpr (CONV) {
+                // the fused variant runs 18 warps, which leaves 96 registers per thread: one chunk
+                // buffer (a second one spilled, and the spill reloads stalled the converter warps)
+#pragma unroll 1
+                for (int c = c_first; c < bn; c += 64) {
+                    uint32_t r[32];
+                    tc::tmem_ld_32x32(taddr + c, r);
                     tc::tmem_ld_wait();
-                    if (c1 < bn) tc::tmem_ld_32x32(taddr + c1, rb);
-                    emit(ra, c0);
+                    emit(r, c);
                 }
-                if (c1 < bn) {
-                    tc::tmem_ld_wait();
-                    if (c2 < bn) tc::tmem_ld_32x32(taddr + c2, ra);
-                    emit(rb, c1);
+            } else {
+                // chunk i+1 is loaded from TMEM while chunk i is scaled and stored (tcgen05.wait::ld
+                // waits for every load issued so far, so the next load is issued right after the wait)
+                uint32_t ra[32], rb[32];
+                tc::tmem_ld_32x32(taddr + c_first, ra);
+#pragma unroll
+                for (int i = 0; i < BN / 64; i += 2) {
+                    const int c0 = c_first + 64 * i, c1 = c0 + 64, c2 = c1 + 64;
+                    if (c0 < bn) {
+                        tc::tmem_ld_wait();
+                        if (c1 < bn) tc::tmem_ld_32x32(taddr + c1, rb);
+                        emit(ra, c0);
+                    }
+                    if (c1 < bn) {
+                        tc::tmem_ld_wait();
+                        if (c2 < bn) tc::tmem_ld_32x32(taddr + c2, ra);
+                        emit(rb, c1);
+                    }
                 }
             }
             tc::tc_fence_before();
