@@ -84,7 +84,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int FMT, int PAIR>
 __device__ __forceinline__ uint32_t expand2(uint32_t w) {
     const uint32_t L = __byte_perm(w, 0u, PAIR == 0 ? 0x4140 : 0x4342);   // codes -> low byte of each lane
-    constexpr uint32_t up = FMT == NVQ_E4M3 ? 16u : 8u;                     // 2^SH
+    constexpr uint32_t up = FMT == NVQ_E4M3 ? 16u : 32u;                    // 2^SH: mantissa top at bit 6
     constexpr uint32_t lift = 256u - up;
     constexpr uint32_t rebias = FMT == NVQ_E4M3 ? 0x7B807B80u               // 2^120 as bf16, twice
                                                 : 0x77807780u;              // 2^112
