@@ -302,6 +302,19 @@ def measure_extras(dev, st, rank, world, dist, local):
                                           "inside the call (included in the time), FP8 x FP8 MMAs "
                                           "(kind::f8f6f4); max-abs-rel vs the bf16-activation result "
                                           "is 2.4-3.2e-2, outside the 1e-2 bound"}
+    # few rows (serving shape): the weight-streaming kernel; same rotating sets, so the 16 MB of
+    # codes come from DRAM on every call
+    ms_ = 16
+    t = timed_rotating(lambda dxx, dw, ws, dy: F.linear_q_device(dy, dxx, dw, "e4m3", dss, dbb, ms_, nn, kk, ws,
+                                                                 stream=st), lsets)
+    t_warm = timed_rotating(lambda dxx, dw, ws, dy: F.linear_q_device(dy, dxx, dw, "e4m3", dss, dbb, ms_, nn, kk,
+                                                                      ws, stream=st), lsets[:1], rounds=20)
+    F.check_device_errors(dev)
+    out["linear_fp8_few_rows"] = {"M": ms_, "N": nn, "K": kk, "us": t * 1e3, "us_l2_warm": t_warm * 1e3,
+                                  "weight_gbs": nn * kk / t / 1e6,
+                                  "note": "M <= 128: codes read once (1 byte per weight), expanded in shared "
+                                          "memory, operands swapped, split along K with a deterministic "
+                                          "reduction kernel; weight_gbs = code bytes / time"}
     for bufs in lsets:
         for b_ in bufs:
             b_.free()
