@@ -263,3 +263,32 @@ def test_main_cnn_full_batch_against_oracle():
         # first AdamW step moves every entry by ~lr * sign(g): entries whose tiny gradient changed
         # sign differ by up to 2 lr
         assert np.max(np.abs(pa.astype(np.float64) - r["params"][i])) <= 2.5e-3, i
+
+
+def test_empty_batches_pass_through_every_new_layer():
+    """N = 0 (an empty last batch): shapes are kept, nothing is launched, nothing faults."""
+    x = np.zeros((0, 4, 6, 6), np.float32)
+    y, rm, rv, st = F.batchnorm_fwd_host(x, np.ones(4), np.zeros(4), np.zeros(4), np.ones(4))
+    assert y.shape == x.shape and st is None
+    assert np.array_equal(rm, np.zeros(4)) and np.array_equal(rv, np.ones(4))   # statistics untouched
+    assert F.max_pool2d_host(x, (2, 2), (2, 2)).shape == (0, 4, 3, 3)
+    assert F.max_pool2d_bwd_host(np.zeros((0, 4, 3, 3), np.float32), x, (2, 2), (2, 2)).shape == x.shape
+    assert F.avg_pool2d_host(x).shape == (0, 4, 1, 1)
+    assert F.avg_pool2d_bwd_host(np.zeros((0, 4, 1, 1), np.float32), x.shape).shape == x.shape
+    assert F.dropout_host(np.zeros((0, 8), np.float32), np.zeros((0, 8), np.float32), 0.5).shape == (0, 8)
+
+
+def test_batchnorm_single_element_per_channel_and_large_offsets():
+    """m = 1 (no Bessel correction, variance 0) and data with a mean far from zero (the sum of
+    squares is accumulated in float64, so the variance keeps its digits)."""
+    x = np.array([[[[3.0]], [[-2.0]]]], np.float32)                      # (1, 2, 1, 1)
+    yo, rmo, rvo, _ = o.batchnorm_fwd(x, np.ones(2), np.zeros(2), np.zeros(2), np.ones(2))
+    y, rm, rv, _ = F.batchnorm_fwd_host(x, np.ones(2), np.zeros(2), np.zeros(2), np.ones(2))
+    assert np.array_equal(y, yo.astype(np.float32)) and close(rm, rmo, 1e-7) and close(rv, rvo, 1e-7)
+    rng = np.random.default_rng(3)
+    xb = (1000.0 + rng.standard_normal((64, 3, 9, 9))).astype(np.float32)
+    yo, _, _, cache = o.batchnorm_fwd(xb.astype(np.float64).astype(np.float32), np.ones(3), np.zeros(3), np.zeros(3), np.ones(3))
+    y, _, _, st = F.batchnorm_fwd_host(xb, np.ones(3), np.zeros(3), np.zeros(3), np.ones(3))
+    ref_var = xb.astype(np.float64).var(axis=(0, 2, 3)) * (xb.size / 3) / (xb.size / 3 - 1)
+    assert np.max(np.abs(st[1] - ref_var) / ref_var) < 1e-6               # device variance vs float64 truth
+    assert close(y, yo.astype(np.float32), 2e-3)                          # NumPy's own fp32 variance is the loose side here
