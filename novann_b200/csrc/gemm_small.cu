@@ -326,7 +326,8 @@ nvq_status nvq_linear_launch_small_m(uint16_t* d_y, const uint16_t* d_x, const u
                                      cudaStream_t st) {
     NVQ_REQUIRE(M >= 1 && M <= 128 && K % 16 == 0, "small-M Linear: needs 1 <= M <= 128 and K %% 16 == 0");
     NVQ_REQUIRE(fmt == NVQ_E4M3 || fmt == NVQ_E5M2, "small-M Linear: FP8 weight formats only");
-    NVQ_REQUIRE(M * N < (1u << 31) && N < (1u << 24) && K < (1u << 24), "small-M Linear: dimension too large");
+    NVQ_REQUIRE(M * N < (1u << 31) && N < (1u << 24) && K < (1u << 24) && N * K < (1ull << 40),
+                "small-M Linear: dimension too large");
     SmallParams p;
     p.partial = d_partial;
     p.M = (int)M;
