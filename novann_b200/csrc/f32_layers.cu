@@ -143,6 +143,109 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
     }
 }
 
+// Register-tiled form for large outputs: a 16 x 16 thread grid, each thread RI x RJ outputs
+// (RJ consecutive columns, read from shared memory as float4), 16-deep chunks, double
+// buffered.  Per k step a thread issues RI + RJ/4 shared loads for RI * RJ multiply-adds,
+// against 4 loads for 4 multiply-adds in the 32 x 32 kernel above.  The additions of one output
+// run in the same k order as there, so both kernels return the same bits.
+template <int RI, int RJ>
+__global__ void __launch_bounds__(256) gemm_f32_big_kernel(const GemmArgs g) {
+    constexpr int TI = 16 * RI, TJ = 16 * RJ, TKB = 16;
+    constexpr int LDA = TI * TKB / 256, LDB = TJ * TKB / 256;
+    __shared__ __align__(16) float As[2][TKB][TI + 4];
+    __shared__ __align__(16) float Bs[2][TKB][TJ + 4];
+    const int i0 = blockIdx.y * TI, j0 = blockIdx.x * TJ;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const bool a_kc = g.a_sl == 1, b_kc = g.b_sl == 1;
+    float acc[RI][RJ];
+#pragma unroll
+    for (int u = 0; u < RI; u++)
+#pragma unroll
+        for (int v = 0; v < RJ; v++) acc[u][v] = 0.f;
+    float ra[LDA], rb[LDB];
+    const int l_lo = g.splits > 1 ? blockIdx.z * g.l_per_split : 0;
+    const int l_hi = g.splits > 1 ? min(g.L, l_lo + g.l_per_split) : g.L;
+    auto fetch = [&](int l0) {
+#pragma unroll
+        for (int r = 0; r < LDA; r++) {
+            int ii, ll;
+            tile_coord<TI, TKB>(threadIdx.x + 256 * r, a_kc, ii, ll);
+            const int i = i0 + ii, l = l0 + ll;
+            ra[r] = (i < g.I && l < l_hi) ? g.a[i * g.a_si + l * g.a_sl] : 0.f;
+        }
+#pragma unroll
+        for (int r = 0; r < LDB; r++) {
+            int jj, ll;
+            tile_coord<TJ, TKB>(threadIdx.x + 256 * r, b_kc, jj, ll);
+            const int j = j0 + jj, l = l0 + ll;
+            rb[r] = (j < g.J && l < l_hi) ? g.b[l * g.b_sl + j * g.b_sj] : 0.f;
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int r = 0; r < LDA; r++) {
+            int ii, ll;
+            tile_coord<TI, TKB>(threadIdx.x + 256 * r, a_kc, ii, ll);
+            As[buf][ll][ii] = ra[r];
+        }
+#pragma unroll
+        for (int r = 0; r < LDB; r++) {
+            int jj, ll;
+            tile_coord<TJ, TKB>(threadIdx.x + 256 * r, b_kc, jj, ll);
+            Bs[buf][ll][jj] = rb[r];
+        }
+    };
+    fetch(l_lo);
+    stash(0);
+    __syncthreads();
+    int buf = 0;
+    for (int l0 = l_lo; l0 < l_hi; l0 += TKB) {
+        const bool more = l0 + TKB < l_hi;
+        if (more) fetch(l0 + TKB);
+#pragma unroll
+        for (int l = 0; l < TKB; l++) {
+            float a[RI], b[RJ];
+#pragma unroll
+            for (int u = 0; u < RI; u++) a[u] = As[buf][l][ty * RI + u];
+#pragma unroll
+            for (int v = 0; v < RJ; v += 4) {
+                const float4 t = *reinterpret_cast<const float4*>(&Bs[buf][l][tx * RJ + v]);
+                b[v] = t.x; b[v + 1] = t.y; b[v + 2] = t.z; b[v + 3] = t.w;
+            }
+#pragma unroll
+            for (int u = 0; u < RI; u++)
+#pragma unroll
+                for (int v = 0; v < RJ; v++) acc[u][v] = fmaf(a[u], b[v], acc[u][v]);
+        }
+        if (more) stash(buf ^ 1);
+        __syncthreads();
+        buf ^= 1;
+    }
+#pragma unroll
+    for (int u = 0; u < RI; u++) {
+#pragma unroll
+        for (int v = 0; v < RJ; v++) {
+            const int i = i0 + ty * RI + u, j = j0 + tx * RJ + v;
+            if (i >= g.I || j >= g.J) continue;
+            float val = acc[u][v];
+            if (g.splits > 1) {
+                g.partial[((size_t)blockIdx.z * g.I + i) * g.J + j] = val;
+                continue;
+            }
+            if (g.bias) val = __fadd_rn(val, g.bias_per_row ? g.bias[i] : g.bias[j]);
+            size_t idx = g.out_mode == 0 ? (size_t)i * g.J + j
+                                         : ((size_t)(j / g.inner) * g.I + i) * g.inner + (j % g.inner);
+            if (g.relu) {
+                float m = val > 0.f ? 1.f : 0.f;
+                if (g.mask_out) g.mask_out[idx] = m;
+                val = __fmul_rn(val, m);
+            }
+            if (g.mask_in) val = __fmul_rn(val, g.mask_in[idx]);
+            g.c[idx] = val;
+        }
+    }
+}
+
 // c[e] = sum over z of partial[z][e]: one warp per output, lane t adds z = t, t+32, ... in
 // order and the 32 lane sums are combined by a fixed butterfly (same result on every run)
 __global__ void splitk_reduce_kernel(float* __restrict__ c, const float* __restrict__ partial,
@@ -189,6 +292,28 @@ nvq_status launch_gemm_splitk(GemmArgs g, float* scratch, size_t scratch_elems, 
 
 nvq_status launch_gemm(const GemmArgs& g, cudaStream_t st) {
     if (g.I <= 0 || g.J <= 0) return NVQ_OK;
+    // large outputs with a contraction worth tiling in registers: 64 x 64, 32 x 128 or 16 x 128
+    // tiles by the number of rows, as long as there are blocks for about half of the SMs
+    if (g.L > 16) {
+        const long long b44 = (long long)((g.J + 63) / 64) * ((g.I + 63) / 64);
+        const long long b28 = (long long)((g.J + 127) / 128) * ((g.I + 31) / 32);
+        const long long b18 = (long long)((g.J + 127) / 128) * ((g.I + 15) / 16);
+        if (g.I > 32 && b44 >= 64) {
+            gemm_f32_big_kernel<4, 4><<<dim3((g.J + 63) / 64, (g.I + 63) / 64), 256, 0, st>>>(g);
+            NVQ_LAUNCHED();
+            return NVQ_OK;
+        }
+        if (g.I > 16 && g.I <= 32 && b28 >= 64) {
+            gemm_f32_big_kernel<2, 8><<<dim3((g.J + 127) / 128, (g.I + 31) / 32), 256, 0, st>>>(g);
+            NVQ_LAUNCHED();
+            return NVQ_OK;
+        }
+        if (g.I <= 16 && b18 >= 64) {
+            gemm_f32_big_kernel<1, 8><<<dim3((g.J + 127) / 128, (g.I + 15) / 16), 256, 0, st>>>(g);
+            NVQ_LAUNCHED();
+            return NVQ_OK;
+        }
+    }
     const long long big_blocks = (long long)((g.J + 31) / 32) * ((g.I + 31) / 32);
     if (big_blocks >= 148 && g.L <= 16) {
         // shallow contraction: 16-deep chunks; 16-row tiles when the output has few rows
