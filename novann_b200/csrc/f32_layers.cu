@@ -148,9 +148,12 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
 // buffered.  Per k step a thread issues RI + RJ/4 shared loads for RI * RJ multiply-adds,
 // against 4 loads for 4 multiply-adds in the 32 x 32 kernel above.  The additions of one output
 // run in the same k order as there, so both kernels return the same bits.
+#ifndef NVQ_GEMM_BIG_TK
+#define NVQ_GEMM_BIG_TK 16
+#endif
 template <int RI, int RJ>
 __global__ void __launch_bounds__(256) gemm_f32_big_kernel(const GemmArgs g) {
-    constexpr int TI = 16 * RI, TJ = 16 * RJ, TKB = 16;
+    constexpr int TI = 16 * RI, TJ = 16 * RJ, TKB = NVQ_GEMM_BIG_TK;
     constexpr int LDA = TI * TKB / 256, LDB = TJ * TKB / 256;
     __shared__ __align__(16) float As[2][TKB][TI + 4];
     __shared__ __align__(16) float Bs[2][TKB][TJ + 4];
@@ -265,15 +268,28 @@ __global__ void splitk_reduce_kernel(float* __restrict__ c, const float* __restr
 nvq_status launch_gemm_splitk(GemmArgs g, float* scratch, size_t scratch_elems, int device,
                               cudaStream_t st) {
     if (g.I <= 0 || g.J <= 0) return NVQ_OK;
-    const long long tiles = (long long)((g.J + 15) / 16) * ((g.I + 15) / 16);
+    // tile shape by the number of rows, as in launch_gemm; 16 x 16 tiles for tiny outputs
+    int ti, tj, kind;
+    if (g.I > 32)                  { ti = 64; tj = 64; kind = 44; }
+    else if (g.I > 16)             { ti = 32; tj = 128; kind = 28; }
+    else if (g.J >= 64)            { ti = 16; tj = 128; kind = 18; }
+    else                           { ti = 16; tj = 16; kind = 0; }
+    const dim3 tiles2((g.J + tj - 1) / tj, (g.I + ti - 1) / ti);
+    auto launch = [&](unsigned z) {
+        const dim3 grid(tiles2.x, tiles2.y, z);
+        if (kind == 44) gemm_f32_big_kernel<4, 4><<<grid, 256, 0, st>>>(g);
+        else if (kind == 28) gemm_f32_big_kernel<2, 8><<<grid, 256, 0, st>>>(g);
+        else if (kind == 18) gemm_f32_big_kernel<1, 8><<<grid, 256, 0, st>>>(g);
+        else gemm_f32_kernel<16><<<grid, 256, 0, st>>>(g);
+    };
+    const long long tiles = (long long)tiles2.x * tiles2.y;
     const long long out = (long long)g.I * g.J;
     long long want = (4LL * nvq_sm_count(device) + tiles - 1) / tiles;
-    want = std::min<long long>(want, g.L / 128);
+    want = std::min<long long>(want, g.L / 64);
     if (scratch) want = std::min<long long>(want, (long long)(scratch_elems / (size_t)out));
     if (!scratch || want < 2 || g.bias || g.relu || g.mask_in || g.out_mode != 0) {
         g.splits = 1;
-        dim3 grid((g.J + 15) / 16, (g.I + 15) / 16);
-        gemm_f32_kernel<16><<<grid, 256, 0, st>>>(g);
+        launch(1);
         NVQ_LAUNCHED();
         return NVQ_OK;
     }
@@ -282,8 +298,7 @@ nvq_status launch_gemm_splitk(GemmArgs g, float* scratch, size_t scratch_elems, 
     g.l_per_split = lps;
     g.splits = (g.L + lps - 1) / lps;
     g.partial = scratch;
-    dim3 grid((g.J + 15) / 16, (g.I + 15) / 16, g.splits);
-    gemm_f32_kernel<16><<<grid, 256, 0, st>>>(g);
+    launch((unsigned)g.splits);
     NVQ_LAUNCHED();
     splitk_reduce_kernel<<<(unsigned)((out + 7) / 8), 256, 0, st>>>(g.c, scratch, (int)out, g.splits);
     NVQ_LAUNCHED();
