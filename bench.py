@@ -384,7 +384,7 @@ def measure_extras(dev, st, rank, world, dist, local):
                             "forward + CE + backward + AdamW, %d kernels per step, inputs resident" %
                             (cb, cnn.launches_per_step))
     out["mlp_step_note"] = ("fp32 784-256-128-10, batch %d per GPU, forward + CE + backward + SGD, "
-                            "13 kernels replayed as one CUDA graph, no all-reduce in this figure" % bsz)
+                            "%d kernels replayed as one CUDA graph, no all-reduce in this figure" % (bsz, step.kernels_per_step()))
     return out
 
 

@@ -38,6 +38,9 @@ struct GemmArgs {
     // and stores its raw sums to partial[z][I][J]; splitk_reduce_kernel adds them in z order
     int splits, l_per_split;
     float* partial;
+    // optional by-product: rowsum[i] = sum_l A(i, l), added in l order by the blocks of the first
+    // tile column (Linear.backward's bias gradient = column sums of grad = row sums of grad^T)
+    float* rowsum;
 };
 
 constexpr int kSplitChunk = 64;   // split-k ranges are multiples of the deepest chunk
@@ -66,10 +69,14 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     const bool a_kc = g.a_sl == 1, b_kc = g.b_sl == 1;
     float acc[R][R];
+    float rs[R];
 #pragma unroll
-    for (int u = 0; u < R; u++)
+    for (int u = 0; u < R; u++) {
+        rs[u] = 0.f;
 #pragma unroll
         for (int v = 0; v < R; v++) acc[u][v] = 0.f;
+    }
+    const bool do_rowsum = g.rowsum != nullptr && blockIdx.x == 0 && tx == 0;
     float ra[LD], rb[LD];
     const int l_lo = g.splits > 1 ? blockIdx.z * g.l_per_split : 0;
     const int l_hi = g.splits > 1 ? min(g.L, l_lo + g.l_per_split) : g.L;
@@ -113,10 +120,19 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
             for (int u = 0; u < R; u++)
 #pragma unroll
                 for (int v = 0; v < R; v++) acc[u][v] = fmaf(a[u], b[v], acc[u][v]);
+            if (do_rowsum) {
+#pragma unroll
+                for (int u = 0; u < R; u++) rs[u] = __fadd_rn(rs[u], a[u]);
+            }
         }
         if (more) stash(buf ^ 1);
         __syncthreads();
         buf ^= 1;
+    }
+    if (do_rowsum) {
+#pragma unroll
+        for (int u = 0; u < R; u++)
+            if (i0 + ty + 16 * u < g.I) g.rowsum[i0 + ty + 16 * u] = rs[u];
     }
 #pragma unroll
     for (int u = 0; u < R; u++) {
@@ -161,10 +177,14 @@ __global__ void __launch_bounds__(256) gemm_f32_big_kernel(const GemmArgs g) {
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     const bool a_kc = g.a_sl == 1, b_kc = g.b_sl == 1;
     float acc[RI][RJ];
+    float rs[RI];
 #pragma unroll
-    for (int u = 0; u < RI; u++)
+    for (int u = 0; u < RI; u++) {
+        rs[u] = 0.f;
 #pragma unroll
         for (int v = 0; v < RJ; v++) acc[u][v] = 0.f;
+    }
+    const bool do_rowsum = g.rowsum != nullptr && blockIdx.x == 0 && tx == 0;
     float ra[LDA], rb[LDB];
     const int l_lo = g.splits > 1 ? blockIdx.z * g.l_per_split : 0;
     const int l_hi = g.splits > 1 ? min(g.L, l_lo + g.l_per_split) : g.L;
@@ -219,10 +239,19 @@ __global__ void __launch_bounds__(256) gemm_f32_big_kernel(const GemmArgs g) {
             for (int u = 0; u < RI; u++)
 #pragma unroll
                 for (int v = 0; v < RJ; v++) acc[u][v] = fmaf(a[u], b[v], acc[u][v]);
+            if (do_rowsum) {
+#pragma unroll
+                for (int u = 0; u < RI; u++) rs[u] = __fadd_rn(rs[u], a[u]);
+            }
         }
         if (more) stash(buf ^ 1);
         __syncthreads();
         buf ^= 1;
+    }
+    if (do_rowsum) {
+#pragma unroll
+        for (int u = 0; u < RI; u++)
+            if (i0 + ty * RI + u < g.I) g.rowsum[i0 + ty * RI + u] = rs[u];
     }
 #pragma unroll
     for (int u = 0; u < RI; u++) {
@@ -811,10 +840,10 @@ extern "C" nvq_status nvq_linear_bwd_f32(float* d_dw, float* d_db, float* d_dx, 
         g.a = d_g; g.a_si = 1; g.a_sl = N;
         g.b = d_x; g.b_sl = K; g.b_sj = 1;
         g.c = d_dw; g.I = N; g.J = K; g.L = M;
+        g.rowsum = d_db;          // db[n] = sum_m G[m,n]: the row sums of the A operand, for free
         s = launch_gemm(g, st);
         if (s != NVQ_OK) return s;
-    }
-    if (d_db) {
+    } else if (d_db) {
         colsum_kernel<<<(N + 31) / 32, 256, 0, st>>>(d_g, d_db, M, N);
         NVQ_LAUNCHED();
     }

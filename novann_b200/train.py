@@ -4,7 +4,8 @@ SGD.step) for ``Sequential(Linear, ReLU, ..., Linear)`` with every tensor kept i
 
 Weights, activations, masks and gradients live in one device arena; a step is a fixed
 sequence of kernel launches on one stream (fused Linear+bias+ReLU forward, softmax-CE,
-Linear backward with the ReLU mask folded into dX, SGD over the flat parameter bucket).
+Linear backward with the bias gradient as a by-product of the weight-gradient GEMM and the ReLU
+mask folded into dX, SGD over the flat parameter bucket).
 With more than one rank the flat gradient bucket is summed over ranks with one NCCL
 all-reduce and scaled by 1/world inside the SGD kernel, which equals the gradient of the
 global batch because the reference divides its loss gradient by the local batch size.
@@ -148,9 +149,9 @@ class MLPTrainStep:
         check(lib().nvq_graph_launch(self.device, C.c_void_p(self._graph), _sptr(self.stream)))
 
     def kernels_per_step(self) -> int:
-        """Kernel launches of this library in one step: nl forward, 1 loss, per layer dW + db
-        (+ dX except for the first layer), 1 SGD."""
-        return self.nl + 1 + (3 * self.nl - 1) + 1
+        """Kernel launches of this library in one step: nl forward, 1 loss, per layer one GEMM for
+        dW with db as its by-product (+ one for dX except for the first layer), 1 SGD."""
+        return self.nl + 1 + (2 * self.nl - 1) + 1
 
     def step(self, x: np.ndarray, labels: np.ndarray) -> None:
         self._step_no += 1

@@ -303,7 +303,7 @@ def test_mlp_train_step_graph_replay_equals_eager(gpu):
     for a, b in zip(eager.params(), graph.params()):
         assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
     assert eager.loss() == graph.loss()
-    assert graph.kernels_per_step() == 13
+    assert graph.kernels_per_step() == 10
 
 
 def test_sequential_of_gpu_layers_runs_the_reference_loop(gpu):
