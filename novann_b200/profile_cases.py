@@ -7,6 +7,7 @@
     python -m novann_b200.profile_cases w8a8   [M=4096 N=4096 K=4096]
     python -m novann_b200.profile_cases cnn    [batch=128 steps=3]
     python -m novann_b200.profile_cases conv   [N=128 C=64 HW=56 Cout=128 reps=2]
+    python -m novann_b200.profile_cases fewrows [M=16 N=8192 K=8192 reps=3]
 
 Each case uploads seeded inputs, launches the kernels a few times and exits; sizes are
 larger than the 126 MB L2 (so DRAM counters mean something) but hold at most a few GB.
@@ -131,6 +132,26 @@ def case_conv(n: int = 128, c: int = 64, hw: int = 56, cout: int = 128, reps: in
     F.check_device_errors(0)
 
 
+def case_fewrows(m: int = 16, n: int = 8192, k: int = 8192, reps: int = 3) -> None:
+    """FP8-weight Linear with few rows (the weight-streaming kernel), rotating over four weight
+    copies so that every call reads its codes from DRAM."""
+    st = Stream(0)
+    rng = np.random.default_rng(1)
+    xb, _, b = workloads.linear_inputs(m, 8, k, seed=0)
+    sets = []
+    for i in range(4):
+        wq = rng.integers(0, 0x7F, (n, k), dtype=np.uint64).astype(np.uint8)
+        sets.append((DeviceBuffer.from_numpy(wq, 0), DeviceBuffer(F.linear_workspace_bytes(n, k, "e4m3"), 0)))
+    dx = DeviceBuffer.from_numpy(xb, 0)
+    ds = DeviceBuffer.from_numpy(np.full(n, 1e-3, np.float32), 0)
+    dy = DeviceBuffer(m * n * 2, 0)
+    for r in range(reps * 4):
+        dw, ws = sets[r % 4]
+        F.linear_q_device(dy, dx, dw, "e4m3", ds, None, m, n, k, ws, stream=st)
+    st.sync()
+    F.check_device_errors(0)
+
+
 def main(argv) -> None:
     what = argv[1] if len(argv) > 1 else "cast"
     args = [int(a) for a in argv[2:]]
@@ -148,6 +169,8 @@ def main(argv) -> None:
         case_cnn(*args)
     elif what == "conv":
         case_conv(*args)
+    elif what == "fewrows":
+        case_fewrows(*args)
     else:
         raise SystemExit(f"unknown case {what}")
     device_sync(0)
