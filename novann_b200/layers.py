@@ -13,13 +13,10 @@ device-resident fast path for whole training steps is ``novann_b200.train``.
 """
 from __future__ import annotations
 
-import ctypes as C
-
 import numpy as np
 
-from . import _lib, functional as F
-from ._lib import check, lib
-from .device import DeviceBuffer, device_sync
+from . import functional as F
+from .device import DeviceBuffer
 from .module import Layer, Parameters
 
 

@@ -110,7 +110,6 @@ def case_cnn(batch: int = 128, steps: int = 3) -> None:
 
 def case_conv(n: int = 128, c: int = 64, hw: int = 56, cout: int = 128, reps: int = 2) -> None:
     """FP8-weight 3x3 convolution (stride 1, pad 1) through nvq_conv2d_fwd_q, device resident."""
-    import ctypes as C
     from . import _lib
     from ._lib import check, lib
     from .device import _sptr

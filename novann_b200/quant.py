@@ -16,7 +16,7 @@ import numpy as np
 
 from . import _lib
 from ._lib import check, lib
-from .device import DeviceBuffer, _sptr, device_sync
+from .device import DeviceBuffer, _sptr
 
 _NP_OF = {"f32": np.float32, "f16": np.float16, "bf16": np.uint16}
 

@@ -16,7 +16,6 @@ import ctypes as C
 
 import numpy as np
 
-from . import _lib
 from ._lib import check, lib
 from .device import DeviceBuffer, Stream, _sptr
 
