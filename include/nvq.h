@@ -321,9 +321,11 @@ nvq_status nvq_conv2d_bwd_f32(float* d_dw, float* d_db, float* d_dx, const float
                               const float* d_col, const float* d_w, float* d_gr, float* d_dcol,
                               int N, int C, int H, int W, int Cout, int KH, int KW, int sh, int sw,
                               int ph, int pw, int device, void* stream);
-/* Quantised-weight convolution forward on the tensor cores; Wq is Cout x kpad codes (E4M3 /
- * E5M2) of w.reshape(Cout, C*KH*KW) zero padded to kpad = C*KH*KW rounded up to 16, with Cout
- * per-channel scales; out is fp32 NCHW holding the bf16-rounded results.  Cout % 8 == 0.
+/* Quantised-weight convolution forward on the tensor cores; Wq holds the codes of
+ * w.reshape(Cout, C*KH*KW) zero padded to kpad columns: E4M3 / E5M2 - Cout x kpad bytes, kpad =
+ * C*KH*KW rounded up to 16 (nvq_conv2d_q_sizes), Cout per-channel scales; E2M1_B32 - Cout x kpad/2
+ * packed bytes, kpad rounded up to 32, scales Cout x kpad/32 (the layout of nvq_quantize_fp4_b32).
+ * out is fp32 NCHW holding the bf16-rounded results.  Cout % 8 == 0.
  *   Stride 1, zero padding, C % 64 == 0, OW <= 128: implicit GEMM.  x is rewritten as bf16 NHWC
  *   (into d_col_bf16), the codes are expanded with their columns reordered to (kh, kw, c) (into
  *   d_workspace), and the CTA-pair tcgen05 kernel gathers its A operand with one 4-D TMA box per

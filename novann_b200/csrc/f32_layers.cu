@@ -740,6 +740,26 @@ __global__ void expand_permute_weight_kernel(uint16_t* __restrict__ out, const u
     }
 }
 
+// FP4 E2M1 block-32 weight (Cout x Kpad/2 packed bytes, Kpad/32 fp32 scales per row, columns
+// (c, kh, kw)) -> bf16(value * scale) (Cout x KH*KW*C, columns (kh, kw, c)): the block scale
+// varies along k, so it is folded into the expanded weight (same rule as the FP4 dequantiser)
+__global__ void expand_permute_weight_fp4_kernel(uint16_t* __restrict__ out, const uint8_t* __restrict__ wq,
+                                                 const float* __restrict__ scales, int Cout, int C,
+                                                 int KH, int KW, int Kpad) {
+    const int K = C * KH * KW, total = Cout * K;
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
+        const int co = e / K, k = e - co * K;
+        const int c = k % C, tap = k / C, kh = tap / KW, kw = tap - kh * KW;
+        const int ko = (c * KH + kh) * KW + kw;
+        const uint32_t code = (wq[(size_t)co * (Kpad / 2) + (ko >> 1)] >> (4 * (ko & 1))) & 0xFu;
+        const uint32_t m = code & 7u;   // {0, .5, 1, 1.5, 2, 3, 4, 6} as fp32 patterns
+        const uint32_t vb = (m == 0 ? 0u : m == 1 ? 0x3F000000u : (((m >> 1) + 126u) << 23) | ((m & 1u) << 22)) |
+                            ((code & 8u) << 28);
+        const uint32_t su = __float_as_uint(scales[(size_t)co * (Kpad / 32) + (ko >> 5)]);
+        out[e] = (uint16_t)spec_f32_to_bf16(spec_mul_bits(vb, su));
+    }
+}
+
 // grad (N, Cout, S) -> g_r (Cout, N*S): the reference's grad.transpose(1,0,2,3).reshape(Cout,-1)
 template <class Idx>
 __global__ void nchw_to_crows_kernel(float* __restrict__ out, const float* __restrict__ g, int N,
@@ -972,12 +992,14 @@ extern "C" nvq_status nvq_conv2d_fwd_q(float* d_out, const float* d_x, const uin
     if (s != NVQ_OK) return s;
     NVQ_REQUIRE(d_out && d_x && d_wq && d_w_scales && d_col_bf16 && d_y_bf16, "nvq_conv2d_fwd_q: null buffer");
     NVQ_REQUIRE(Cout % 8 == 0, "nvq_conv2d_fwd_q: Cout (%d) must be a multiple of 8", Cout);
-    NVQ_REQUIRE(w_fmt == NVQ_E4M3 || w_fmt == NVQ_E5M2, "nvq_conv2d_fwd_q: weight format must be E4M3 or E5M2");
+    NVQ_REQUIRE(w_fmt == NVQ_E4M3 || w_fmt == NVQ_E5M2 || w_fmt == NVQ_E2M1_B32,
+                "nvq_conv2d_fwd_q: weight format must be E4M3, E5M2 or E2M1_B32");
     s = nvq_use_device(device);
     if (s != NVQ_OK) return s;
     cudaStream_t st = (cudaStream_t)stream;
     const size_t L = (size_t)N * g.OH * g.OW;
-    const int Kpad = (C * KH * KW + 15) / 16 * 16;
+    const int kq = w_fmt == NVQ_E2M1_B32 ? 32 : 16;          // FP4 blocks are 32 columns
+    const int Kpad = (C * KH * KW + kq - 1) / kq * kq;
     // Implicit GEMM (no patch matrix): stride 1, zero padding, channels in blocks of 64, output
     // rows of at most 128 positions.  d_col_bf16 holds x as bf16 NHWC, d_workspace the weight with
     // its columns reordered to (kh, kw, c).  NVQ_CONV_MODE=explicit forces the patch-matrix path.
@@ -1002,12 +1024,17 @@ extern "C" nvq_status nvq_conv2d_fwd_q(float* d_out, const float* d_x, const uin
         if (w_fmt == NVQ_E4M3)
             expand_permute_weight_kernel<NVQ_E4M3><<<ew_grid(wtotal, device), 256, 0, st>>>(
                 (uint16_t*)d_workspace, d_wq, Cout, C, KH, KW, Kpad);
-        else
+        else if (w_fmt == NVQ_E5M2)
             expand_permute_weight_kernel<NVQ_E5M2><<<ew_grid(wtotal, device), 256, 0, st>>>(
                 (uint16_t*)d_workspace, d_wq, Cout, C, KH, KW, Kpad);
+        else
+            expand_permute_weight_fp4_kernel<<<ew_grid(wtotal, device), 256, 0, st>>>(
+                (uint16_t*)d_workspace, d_wq, d_w_scales, Cout, C, KH, KW, Kpad);
         NVQ_LAUNCHED();
-        return nvq_conv_launch_pair_implicit(d_out, d_col_bf16, (const uint16_t*)d_workspace, d_w_scales,
-                                             d_bias, N, C, H, W, Cout, KH, KW, ph, pw, device, st);
+        // FP4 block scales are already in the expanded weight; FP8 channel scales go to the epilogue
+        return nvq_conv_launch_pair_implicit(d_out, d_col_bf16, (const uint16_t*)d_workspace,
+                                             w_fmt == NVQ_E2M1_B32 ? nullptr : d_w_scales, d_bias, N, C, H, W,
+                                             Cout, KH, KW, ph, pw, device, st);
     }
     const bool tiled = C * KH * KW <= kImLut && KH < 256 && KW < 256 && C < 65536 && L < (1u << 31);
     if (tiled) {

@@ -154,7 +154,9 @@ def conv2d_f32_host(x, w, b=None, stride=(1, 1), padding=(0, 0), padding_mode: s
 def conv2d_q_host(x, wq, w_scales, b, kernel, stride=(1, 1), padding=(0, 0),
                   padding_mode: str = "zeros", fmt: str = "e4m3", device: int = 0):
     """Quantised-weight ``F.conv2d``: ``wq`` is (Cout, kpad) FP8 codes of the zero-padded
-    ``w.reshape(Cout, C*KH*KW)``, ``w_scales`` (Cout,).  Returns fp32 (N,Cout,OH,OW)."""
+    ``w.reshape(Cout, C*KH*KW)`` with ``w_scales`` (Cout,), or for ``fmt="e2m1_b32"`` the packed
+    (Cout, kpad/2) FP4 codes with block scales (Cout, kpad/32), kpad a multiple of 32.  Returns
+    fp32 (N,Cout,OH,OW)."""
     x = _f32(x)
     n, c, h, wd = x.shape
     kh, kw = kernel
@@ -163,7 +165,11 @@ def conv2d_q_host(x, wq, w_scales, b, kernel, stride=(1, 1), padding=(0, 0),
     rows, kpad = C.c_size_t(), C.c_size_t()
     check(lib().nvq_conv2d_q_sizes(n, c, h, wd, cout, kh, kw, stride[0], stride[1], padding[0], padding[1],
                                    C.byref(rows), C.byref(kpad)))
-    if wq.shape[1] != kpad.value:
+    if fmt == "e2m1_b32":
+        kpad = C.c_size_t((c * kh * kw + 31) // 32 * 32)       # FP4 blocks are 32 columns
+        if wq.shape[1] * 2 != kpad.value:
+            raise ValueError(f"packed FP4 weight must be (Cout, {kpad.value // 2})")
+    elif wq.shape[1] != kpad.value:
         raise ValueError(f"weight codes must be (Cout, {kpad.value})")
     oh, ow = conv2d_out_size(h, wd, kh, kw, stride[0], stride[1], padding[0], padding[1])
     dx = DeviceBuffer.from_numpy(x, device)

@@ -226,7 +226,8 @@ class QuantConv2d(Conv2d):
     def requantize(self) -> None:
         from . import quant
         w_col = self.weight.data.reshape(self.out_channels, -1)
-        kpad = (w_col.shape[1] + 15) // 16 * 16
+        q = 32 if self.fmt == "e2m1_b32" else 16
+        kpad = (w_col.shape[1] + q - 1) // q * q
         padded = np.zeros((self.out_channels, kpad), np.float32)
         padded[:, :w_col.shape[1]] = w_col
         self._codes, self._scales = quant.quantize_weight(padded, self.fmt, self.device)
