@@ -493,7 +493,7 @@ extern "C" nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf1
     }
     // Few rows: the time is the time to read the weight, so read it once, as codes.  The
     // workspace then holds fp32 partial sums instead of an expanded weight.
-    if (w_fmt != NVQ_E2M1_B32 && M <= 128 && K % 16 == 0 && nvq_aligned(d_wq, 16) && nvq_aligned(d_x_bf16, 16) &&
+    if (M <= 128 && K % (w_fmt == NVQ_E2M1_B32 ? 32 : 16) == 0 && nvq_aligned(d_wq, 16) && nvq_aligned(d_x_bf16, 16) &&
         d_workspace && nvq_aligned(d_workspace, 16) && !mode && M * N < (1u << 31) && N < (1u << 24) &&
         K < (1u << 24) && N * K < (1ull << 40) &&
         workspace_bytes >= nvq_linear_small_m_workspace(M, N, K, device))

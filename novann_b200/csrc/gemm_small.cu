@@ -56,6 +56,7 @@ struct SmallParams {
     int total;            // n_blocks * num_kb units
     int quota;            // units per CTA
     int pieces;           // partial slots per weight block
+    const float* wscales; // FP4 only: block scales, N x K/32 (folded into the expanded weight)
     int* status;
 };
 
@@ -71,6 +72,25 @@ struct Shared {
 
 // first CTA whose run reaches into weight block nb
 __host__ __device__ inline int first_cta_of(int nb, int num_kb, int quota) { return (nb * num_kb) / quota; }
+
+// 16 FP4 E2M1 codes (eight bytes, low nibble first) times their block scale -> 16 bf16 values:
+// bf16_rne(fp32(value) * scale), the rule of the FP4 dequantiser.
+__device__ __forceinline__ void expand16_fp4(uint32_t w0, uint32_t w1, float scale, uint4& lo, uint4& hi) {
+    const uint32_t w[2] = {w0, w1};
+    uint32_t o[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const uint32_t byte = (w[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+        uint32_t f01;
+        asm("{ .reg .b8 t, z; mov.b16 {t, z}, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(f01) : "h"((uint16_t)byte));
+        float v0, v1;
+        asm("cvt.f32.f16 %0, %1;" : "=f"(v0) : "h"((uint16_t)(f01 & 0xFFFFu)));
+        asm("cvt.f32.f16 %0, %1;" : "=f"(v1) : "h"((uint16_t)(f01 >> 16)));
+        o[i] = pack_bf16(__fmul_rn(v0, scale), __fmul_rn(v1, scale));
+    }
+    lo = make_uint4(o[0], o[1], o[2], o[3]);
+    hi = make_uint4(o[4], o[5], o[6], o[7]);
+}
 
 // Calls f(nb, kb0, kb1, piece) for every weight block this CTA's run touches, in order.
 template <class F>
@@ -98,6 +118,8 @@ linear_small_m_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     volatile int* abort_flag = &sh->abort_flag;
     const uint32_t STAGES = (uint32_t)num_stages(p.MP), STAGE_BYTES = (uint32_t)stage_bytes(p.MP);
     const uint32_t X_OFF = A_BYTES, RAW_OFF = A_BYTES + (uint32_t)p.MP * BK * 2;
+    constexpr bool FP4 = FMT == NVQ_E2M1_B32;
+    constexpr int CODE_ROW_BYTES = FP4 ? BK / 2 : BK;     // bytes of codes per weight row and k-block
     // the finalising kernel may be scheduled now; it waits for this grid before it reads
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
@@ -138,8 +160,8 @@ linear_small_m_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                     tc::mbar_arrive_expect_tx(fbar, p.MP * BK * 2);
                     tc::tma_load_2d(dst + X_OFF, &map_x, fbar, kb * BK, 0);
                     const uint32_t rbar = tc::smem_u32(&sh->raw_full[stage]);
-                    tc::mbar_arrive_expect_tx(rbar, RAW_BYTES);
-                    tc::tma_load_2d(dst + RAW_OFF, &map_w, rbar, kb * BK, nb * WROWS);
+                    tc::mbar_arrive_expect_tx(rbar, WROWS * CODE_ROW_BYTES);
+                    tc::tma_load_2d(dst + RAW_OFF, &map_w, rbar, kb * CODE_ROW_BYTES, nb * WROWS);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
                 return true;
@@ -186,15 +208,35 @@ linear_small_m_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         constexpr int CH = 512 / GT;                          // 16-code chunks per thread and unit
         const int grp = (threadIdx.x - 192) / GT, ct = (threadIdx.x - 192) % GT;
         const int my_units = min(p.total, ((int)blockIdx.x + 1) * p.quota) - (int)blockIdx.x * p.quota;
-        // chunk i = 16 codes: row i / 4, quarter i % 4 of the 64-byte code row
+        // chunk i = 16 codes: row i / 4, quarter i % 4 of the code row (16 bytes of FP8 codes,
+        // 8 bytes of packed FP4 codes); FP4 also fetches the chunk's block scale
         uint4 nxt[CH];
-        auto load_codes = [&](uint32_t st) {
+        float nsc[CH];
+        auto load_codes = [&](uint32_t st, int unit) {
             const uint32_t codes = tiles + st * STAGE_BYTES + RAW_OFF;
 #pragma unroll
-            for (int j = 0; j < CH; j++)
-                asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(nxt[j].x), "=r"(nxt[j].y), "=r"(nxt[j].z), "=r"(nxt[j].w)
-                             : "r"(codes + (ct + GT * j) * 16));
+            for (int j = 0; j < CH; j++) {
+                if constexpr (FP4) {
+                    asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];"
+                                 : "=r"(nxt[j].x), "=r"(nxt[j].y)
+                                 : "r"(codes + (ct + GT * j) * 8));
+                } else {
+                    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(nxt[j].x), "=r"(nxt[j].y), "=r"(nxt[j].z), "=r"(nxt[j].w)
+                                 : "r"(codes + (ct + GT * j) * 16));
+                }
+            }
+            if constexpr (FP4) {
+                const int ug = (int)blockIdx.x * p.quota + unit;
+                const int nb = ug / p.num_kb, kb = ug - nb * p.num_kb;
+                const int kblocks = p.K / 32;
+#pragma unroll
+                for (int j = 0; j < CH; j++) {
+                    const int i = ct + GT * j;
+                    const int row = nb * WROWS + (i >> 2), blk = kb * 2 + ((i & 3) >> 1);
+                    nsc[j] = (row < p.N && blk < kblocks) ? __ldg(p.wscales + (size_t)row * kblocks + blk) : 0.f;
+                }
+            }
         };
         // ring position of this group's current unit and of its next one, advanced by
         // CONV_GROUPS slots per step (no divisions in the loop)
@@ -208,15 +250,16 @@ linear_small_m_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         bool ok = grp < my_units;
         if (ok) {   // the codes of a unit are read into registers one unit of this group ahead
             ok = tc::mbar_wait(tc::smem_u32(&sh->raw_full[stage]), phase, abort_flag, ERR_CONVERT);
-            if (ok) load_codes(stage);
+            if (ok) load_codes(stage, grp);
         }
         for (int u = grp; u < my_units && ok; u += CONV_GROUPS) {
             uint4 in[CH];
+            float sc[CH];
 #pragma unroll
-            for (int j = 0; j < CH; j++) in[j] = nxt[j];
+            for (int j = 0; j < CH; j++) { in[j] = nxt[j]; sc[j] = FP4 ? nsc[j] : 0.f; }
             if (u + CONV_GROUPS < my_units) {
                 ok = tc::mbar_wait(tc::smem_u32(&sh->raw_full[nstage]), nphase, abort_flag, ERR_CONVERT);
-                if (ok) load_codes(nstage);
+                if (ok) load_codes(nstage, u + CONV_GROUPS);
             }
             // the operand slot is free once the MMAs of its previous use have completed
             ok = ok && tc::mbar_wait(tc::smem_u32(&sh->empty[stage]), phase ^ 1, abort_flag, ERR_CONVERT);
@@ -230,7 +273,8 @@ linear_small_m_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 const int i = ct + GT * j;
                 const int r = i >> 2, q = i & 3;
                 uint4 lo, hi;
-                expand16<FMT>(in[j], lo, hi);
+                if constexpr (FP4) expand16_fp4(in[j].x, in[j].y, sc[j], lo, hi);
+                else expand16<FMT>(in[j], lo, hi);
                 const uint32_t row_base = a_dst + (r >> 3) * 1024 + (r & 7) * 128;
                 const uint32_t c0 = (uint32_t)((2 * q) ^ (r & 7)), c1 = (uint32_t)((2 * q + 1) ^ (r & 7));
                 asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(row_base + c0 * 16),
@@ -325,7 +369,9 @@ nvq_status nvq_linear_launch_small_m(uint16_t* d_y, const uint16_t* d_x, const u
                                      size_t M, size_t N, size_t K, float* d_partial, int device,
                                      cudaStream_t st) {
     NVQ_REQUIRE(M >= 1 && M <= 128 && K % 16 == 0, "small-M Linear: needs 1 <= M <= 128 and K %% 16 == 0");
-    NVQ_REQUIRE(fmt == NVQ_E4M3 || fmt == NVQ_E5M2, "small-M Linear: FP8 weight formats only");
+    NVQ_REQUIRE(fmt == NVQ_E4M3 || fmt == NVQ_E5M2 || (fmt == NVQ_E2M1_B32 && K % 32 == 0),
+                "small-M Linear: FP8 codes, or FP4 block-32 codes with K %% 32 == 0");
+    const bool fp4 = fmt == NVQ_E2M1_B32;
     NVQ_REQUIRE(M * N < (1u << 31) && N < (1u << 24) && K < (1u << 24) && N * K < (1ull << 40),
                 "small-M Linear: dimension too large");
     SmallParams p;
@@ -342,27 +388,35 @@ nvq_status nvq_linear_launch_small_m(uint16_t* d_y, const uint16_t* d_x, const u
     p.quota = (p.total + grid - 1) / grid;
     grid = (p.total + p.quota - 1) / p.quota;
     p.pieces = (p.num_kb + p.quota - 1) / p.quota + 1;
+    p.wscales = fp4 ? d_scales : nullptr;
     nvq_status s = nvq_status_word(device, &p.status);
     if (s != NVQ_OK) return s;
     CUtensorMap map_w, map_x;
-    s = nvq_make_tmap_2d(&map_w, d_wq, N, K, WROWS, BK, 1, 0);          // codes, linear rows of 64 bytes
+    // codes: linear rows of 64 bytes (FP8) or 32 bytes (64 packed FP4 codes) per k-block
+    s = fp4 ? nvq_make_tmap_2d(&map_w, d_wq, N, K / 2, WROWS, BK / 2, 1, 0)
+            : nvq_make_tmap_2d(&map_w, d_wq, N, K, WROWS, BK, 1, 0);
     if (s != NVQ_OK) return s;
     s = nvq_make_tmap_2d(&map_x, d_x, M, K, (uint32_t)p.MP, BK, 2, 1);  // bf16, 128-byte swizzle
     if (s != NVQ_OK) return s;
-    static bool attr_set[64][2];
-    const int fi = fmt == NVQ_E4M3 ? 0 : 1;
+    static bool attr_set[64][3];
+    const int fi = fmt == NVQ_E4M3 ? 0 : (fmt == NVQ_E5M2 ? 1 : 2);
     if (!attr_set[device][fi]) {
         if (fi == 0)
             NVQ_CUDA(cudaFuncSetAttribute(linear_small_m_kernel<NVQ_E4M3>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        else
+        else if (fi == 1)
             NVQ_CUDA(cudaFuncSetAttribute(linear_small_m_kernel<NVQ_E5M2>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        else
+            NVQ_CUDA(cudaFuncSetAttribute(linear_small_m_kernel<NVQ_E2M1_B32>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         attr_set[device][fi] = true;
     }
     if (fi == 0) linear_small_m_kernel<NVQ_E4M3><<<grid, THREADS, SMEM_BYTES, st>>>(map_w, map_x, p);
-    else linear_small_m_kernel<NVQ_E5M2><<<grid, THREADS, SMEM_BYTES, st>>>(map_w, map_x, p);
+    else if (fi == 1) linear_small_m_kernel<NVQ_E5M2><<<grid, THREADS, SMEM_BYTES, st>>>(map_w, map_x, p);
+    else linear_small_m_kernel<NVQ_E2M1_B32><<<grid, THREADS, SMEM_BYTES, st>>>(map_w, map_x, p);
     NVQ_LAUNCHED();
+    if (fp4) d_scales = nullptr;          // block scales are already in the expanded weight
     const int total = p.M * p.N;
     int fgrid = (total + 255) / 256;
     const int cap = nvq_sm_count(device) * 8;

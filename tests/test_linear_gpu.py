@@ -259,3 +259,22 @@ def test_linear_in_kernel_expansion_of_every_code(gpu, m, fmt):
     assert np.array_equal(np.isnan(y[0]), nan)
     assert np.array_equal(y[0][~nan], want[~nan])
     assert np.array_equal(np.nan_to_num(y), np.nan_to_num(np.broadcast_to(y[0], y.shape)))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 128, 64), (16, 4096, 4096), (33, 1000, 352), (128, 264, 2048), (7, 136, 96)])
+def test_linear_few_rows_fp4_weights(gpu, m, n, k, monkeypatch):
+    """FP4 block-32 weights through the few-rows kernel (codes and block scales read once, the
+    scale folded in while the tile is expanded in shared memory): against the oracle and against
+    the expansion-pass path of the same call."""
+    xb, w, b = workloads.linear_inputs(m, n, k, seed=m * n)
+    packed, scales = o.quantize_fp4_b32(o.f32_to_bf16_bits(w).reshape(w.shape))
+    monkeypatch.delenv("NVQ_LINEAR_MODE", raising=False)
+    y = o.bf16_bits_to_f32(F.linear_q_host(xb, packed, scales, b, "e2m1_b32", gpu))
+    wd = o.bf16_bits_to_f32(o.f32_to_bf16_bits(o.dequantize_fp4_weight(packed, scales))).reshape(n, k)
+    ref = o.bf16_bits_to_f32(xb).astype(np.float64) @ wd.astype(np.float64).T + b
+    assert o.max_abs_rel(y, ref) <= FP4_TOL
+    assert o.max_abs_rel(y, ref) <= 2.0 ** -7
+    monkeypatch.setenv("NVQ_LINEAR_MODE", "single")
+    y_old = o.bf16_bits_to_f32(F.linear_q_host(xb, packed, scales, b, "e2m1_b32", gpu))
+    assert o.max_abs_rel(y, y_old) <= 2.0 ** -7
+    F.check_device_errors(gpu)
