@@ -188,20 +188,40 @@ __global__ void __launch_bounds__(256) gemm_f32_big_kernel(const GemmArgs g) {
     float ra[LDA], rb[LDB];
     const int l_lo = g.splits > 1 ? blockIdx.z * g.l_per_split : 0;
     const int l_hi = g.splits > 1 ? min(g.L, l_lo + g.l_per_split) : g.L;
+    // Each thread stages the same tile positions in every chunk: their addresses at l_lo, their
+    // k offsets and their row / column validity are worked out once; a chunk then costs one
+    // compare, one load and one pointer bump per element.
+    const float* pa[LDA];
+    const float* pb[LDB];
+    int ka[LDA], kb[LDB];          // k offset inside a chunk, or a huge value for rows outside
+#pragma unroll
+    for (int r = 0; r < LDA; r++) {
+        int ii, ll;
+        tile_coord<TI, TKB>(threadIdx.x + 256 * r, a_kc, ii, ll);
+        const int i = i0 + ii;
+        ka[r] = i < g.I ? ll : (1 << 30);
+        pa[r] = g.a + (long long)min(i, g.I - 1) * g.a_si + (long long)(l_lo + ll) * g.a_sl;
+    }
+#pragma unroll
+    for (int r = 0; r < LDB; r++) {
+        int jj, ll;
+        tile_coord<TJ, TKB>(threadIdx.x + 256 * r, b_kc, jj, ll);
+        const int j = j0 + jj;
+        kb[r] = j < g.J ? ll : (1 << 30);
+        pb[r] = g.b + (long long)(l_lo + ll) * g.b_sl + (long long)min(j, g.J - 1) * g.b_sj;
+    }
+    const long long a_step = (long long)TKB * g.a_sl, b_step = (long long)TKB * g.b_sl;
     auto fetch = [&](int l0) {
+        const int room = l_hi - l0;           // elements with k offset < room exist
 #pragma unroll
         for (int r = 0; r < LDA; r++) {
-            int ii, ll;
-            tile_coord<TI, TKB>(threadIdx.x + 256 * r, a_kc, ii, ll);
-            const int i = i0 + ii, l = l0 + ll;
-            ra[r] = (i < g.I && l < l_hi) ? g.a[i * g.a_si + l * g.a_sl] : 0.f;
+            ra[r] = ka[r] < room ? *pa[r] : 0.f;
+            pa[r] += a_step;
         }
 #pragma unroll
         for (int r = 0; r < LDB; r++) {
-            int jj, ll;
-            tile_coord<TJ, TKB>(threadIdx.x + 256 * r, b_kc, jj, ll);
-            const int j = j0 + jj, l = l0 + ll;
-            rb[r] = (j < g.J && l < l_hi) ? g.b[l * g.b_sl + j * g.b_sj] : 0.f;
+            rb[r] = kb[r] < room ? *pb[r] : 0.f;
+            pb[r] += b_step;
         }
     };
     auto stash = [&](int buf) {
