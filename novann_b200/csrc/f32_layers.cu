@@ -481,11 +481,14 @@ __global__ void softmax_ce_kernel(float* __restrict__ grad, float* __restrict__ 
             }
         }
     }
-    red[threadIdx.x] = part;
+    // fixed butterfly inside each warp, then the warp sums in order: the same value on every run
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xFFFFFFFFu, part, o);
+    if (lane == 0) red[warp] = part;
     __syncthreads();
     if (threadIdx.x == 0) {
         double tot = 0.0;
-        for (int i = 0; i < blockDim.x; i++) tot += red[i];
+        for (int i = 0; i < nwarps; i++) tot += red[i];
         *loss = (float)(-tot / (double)M);
     }
 }

@@ -172,12 +172,19 @@ __device__ __forceinline__ TileRef tile_ref(const LinearParams& p, int item) {
         t.half = (item - p.num_big) & 1;
         t.is_half = 1;
     }
-    const int per_group = p.group_m * p.n_blocks;
-    const int g = big / per_group, r = big % per_group;
-    const int first = g * p.group_m;
-    const int gsize = min(p.group_m, p.m_blocks - first);
-    t.m_blk = first + r % gsize;
-    t.n_blk = r / gsize;
+    if (p.n_blocks == 1) {
+        // one column block: tiles are the row blocks in order (and the single-thread roles that
+        // call this once per tile are spared four integer divisions)
+        t.m_blk = big;
+        t.n_blk = 0;
+    } else {
+        const int per_group = p.group_m * p.n_blocks;
+        const int g = big / per_group, r = big % per_group;
+        const int first = g * p.group_m;
+        const int gsize = min(p.group_m, p.m_blocks - first);
+        t.m_blk = first + r % gsize;
+        t.n_blk = r / gsize;
+    }
     // a last column block with at most 128 valid columns runs as a half-width tile
     if (!t.is_half && p.N - t.n_blk * 256 <= 128) t.is_half = 1;
     return t;

@@ -68,8 +68,8 @@ struct Shared {
     uint64_t full[MAX_STAGES];
     uint64_t empty[MAX_STAGES];
     uint64_t raw_full[MAX_STAGES];
-    uint64_t tmem_full[2];
-    uint64_t tmem_empty[2];
+    uint64_t tmem_full[4];
+    uint64_t tmem_empty[4];
     uint32_t tmem_base;
     int abort_flag;
     float scale[2][BN];
@@ -95,6 +95,15 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
     const int num_kb = (p.K + BKE - 1) / BKE;
     volatile int* abort_flag = &sh->abort_flag;
+    // Accumulator buffers in TMEM: two of 256 columns, or four of 128 columns when the output has
+    // at most 128 columns (every tile is then half-width).  Short tiles (few k-blocks) need the
+    // deeper queue to hide the hand-off between the MMA warp and the epilogue warps.
+    const bool narrow = p.N <= BN / 2;
+    const uint32_t acc_cols = narrow ? BN / 2 : BN;
+    auto acc_of = [&](int it, uint32_t& acc, uint32_t& acc_phase) {
+        if (narrow) { acc = it & 3; acc_phase = (it >> 2) & 1; }
+        else        { acc = it & 1; acc_phase = (it >> 1) & 1; }
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -104,7 +113,7 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             tc::mbar_init(tc::smem_u32(&sh->empty[s]), 1);
             tc::mbar_init(tc::smem_u32(&sh->raw_full[s]), 1);
         }
-        for (int a = 0; a < 2; a++) {
+        for (int a = 0; a < 4; a++) {
             tc::mbar_init(tc::smem_u32(&sh->tmem_full[a]), 1);
             tc::mbar_init(tc::smem_u32(&sh->tmem_empty[a]), 2 * EPI_WARPS);   // epilogue warps x 2 CTAs
         }
@@ -131,6 +140,8 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            [[maybe_unused]] int img = 0, oh0 = 0, kh = 0, kw = 0, cb = 0;
+            [[maybe_unused]] const int a_bytes = IMPL ? p.conv_bw * p.conv_bh * BK * 2 : 0;   // the box, padding included
             for (int t = pair; t < p.num_items && ok; t += num_pairs) {
                 const TileRef tr = tile_ref(p, t);
                 const int bn = tr.is_half ? BN / 2 : BN;
@@ -153,12 +164,16 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                         if (rows_b == 128)
                             tc::tma_load_2d(dst + A_BYTES + B_BYTES + RAW_BYTES / 2, &map_b, rbar, kb * BK, n0 + 64);
                     } else if constexpr (IMPL) {
-                        // this CTA's box: image and first output row of operand tile 2 * m_blk + rank
-                        const int cta_tile = tr.m_blk * 2 + (int)rank;
-                        const int img = cta_tile / p.conv_th, oh0 = (cta_tile % p.conv_th) * p.conv_bh;
-                        const int tap = kb / p.conv_cpb, c0 = (kb % p.conv_cpb) * BK;
-                        const int kh = tap / p.conv_KW, kw = tap % p.conv_KW;
-                        const int a_bytes = p.conv_bw * p.conv_bh * BK * 2;   // the box, padding included
+                        // this CTA's box: image and first output row of operand tile 2 * m_blk + rank;
+                        // k-block kb = (tap (kh, kw), channel block), walked with counters (no
+                        // divisions on the producer's per-k-block path)
+                        if (kb == 0) {
+                            const int cta_tile = tr.m_blk * 2 + (int)rank;
+                            img = cta_tile / p.conv_th;
+                            oh0 = (cta_tile % p.conv_th) * p.conv_bh;
+                            kh = kw = cb = 0;
+                        }
+                        const int c0 = cb * BK;
                         if (rank == 0)
                             tc::mbar_arrive_expect_tx(tc::smem_u32(&sh->full[stage]),
                                                       2 * (a_bytes + rows_b * BK * 2));
@@ -168,6 +183,7 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                         tc::tma_load_2d_pair(dst + A_BYTES, &map_b, lead_full, kb * BKE, n0);
                         if (rows_b == 128)
                             tc::tma_load_2d_pair(dst + A_BYTES + B_BYTES / 2, &map_b, lead_full, kb * BKE, n0 + 64);
+                        if (++cb == p.conv_cpb) { cb = 0; if (++kw == p.conv_KW) { kw = 0; kh++; } }
                     } else {
                         if (rank == 0)   // the leader expects the bytes of both CTAs
                             tc::mbar_arrive_expect_tx(tc::smem_u32(&sh->full[stage]),
@@ -185,21 +201,26 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         // ------------------------------------------------------------ MMA issuer (leader only)
         if (lane == 0 && rank == 0) {
             uint32_t stage = 0, phase = 0;
-            bool ok = true;
+            bool ok = true, ready = false;
             int it = 0;
             for (int t = pair; t < p.num_items && ok; t += num_pairs, it++) {
-                const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+                uint32_t acc, acc_phase;
+                acc_of(it, acc, acc_phase);
                 const TileRef tr = tile_ref(p, t);
                 const uint32_t idesc = F8 ? tc::idesc_f16(BM, tr.is_half ? BN / 2 : BN, 0, 0)   // E4M3 x E4M3
                                           : tc::idesc_f16(BM, tr.is_half ? BN / 2 : BN, 1, 1);  // bf16 x bf16
                 ok = tc::mbar_wait(tc::smem_u32(&sh->tmem_empty[acc]), acc_phase ^ 1, abort_flag, ERR_MMA_TMEM);
                 if (!ok) break;
                 tc::tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * BN;
+                const uint32_t d_tmem = tmem_base + acc * acc_cols;
                 for (int kb = 0; kb < num_kb; kb++) {
-                    ok = tc::mbar_wait(tc::smem_u32(&sh->full[stage]), phase, abort_flag, ERR_MMA_FULL);
-                    if (!ok) break;
+                    if (!ready) {
+                        ok = tc::mbar_wait(tc::smem_u32(&sh->full[stage]), phase, abort_flag, ERR_MMA_FULL);
+                        if (!ok) break;
+                    }
                     tc::tc_fence_after();
+                    const uint32_t nstage = stage + 1 == (uint32_t)STAGES ? 0u : stage + 1;
+                    const uint32_t nphase = nstage == 0 ? phase ^ 1u : phase;
                     const uint32_t a_addr = tiles + stage * STAGE_BYTES;
                     const uint64_t a_desc = tc::smem_desc_k_sw128(a_addr);
                     const uint64_t b_desc = tc::smem_desc_k_sw128(a_addr + A_BYTES);
@@ -209,9 +230,13 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                             tc::tc_mma_f8_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
                         else
                             tc::tc_mma_f16_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+                        // look at the next slot's barrier while the MMAs are being taken up: the
+                        // answer is there when this k-block's commit has been issued
+                        if (k == 0) ready = tc::mbar_test_wait(tc::smem_u32(&sh->full[nstage]), nphase);
                     }
                     tc::tc_commit_pair(tc::smem_u32(&sh->empty[stage]), 3);   // both CTAs' slots
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    stage = nstage;
+                    phase = nphase;
                 }
                 if (ok) tc::tc_commit_pair(tc::smem_u32(&sh->tmem_full[acc]), 3);
             }
@@ -306,22 +331,26 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         bool ok = true;
         int it = 0;
         for (int t = pair; t < p.num_items && ok; t += num_pairs, it++) {
-            const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+            uint32_t acc, acc_phase;
+            acc_of(it, acc, acc_phase);
             const TileRef tr = tile_ref(p, t);
             const int bn = tr.is_half ? BN / 2 : BN;
             const int m0 = tr.m_blk * BM + (int)rank * 128;
             const int n0 = tr.n_blk * BN + tr.half * (BN / 2);
+            // this buffer's scale and bias rows (2 x 256 or 4 x 128 floats)
+            float* sc = &sh->scale[0][0] + acc * acc_cols;
+            float* bi = &sh->bias[0][0] + acc * acc_cols;
             for (int c = et; c < bn; c += 32 * EPI_WARPS) {
                 int n = n0 + c;
-                sh->scale[acc][c] = (p.scales && n < p.N) ? p.scales[n] : 1.f;
-                sh->bias[acc][c] = (p.bias && n < p.N) ? p.bias[n] : 0.f;
+                sc[c] = (p.scales && n < p.N) ? p.scales[n] : 1.f;
+                bi[c] = (p.bias && n < p.N) ? p.bias[n] : 0.f;
             }
             ok = tc::mbar_wait(tc::smem_u32(&sh->tmem_full[acc]), acc_phase, abort_flag, ERR_EPILOGUE);
             ok = epilogue_all<32 * EPI_WARPS>(ok);
             if (!ok) break;
             tc::tc_fence_after();
             const int row = m0 + quarter * 32 + lane;
-            const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+            const uint32_t taddr = tmem_base + acc * acc_cols + ((uint32_t)(quarter * 32) << 16);
             // implicit convolution: row r of this CTA's tile is output position oh0 * OW + r of
             // image img (the box spans whole output rows); each thread owns one position, so for a
             // fixed channel a warp writes 32 consecutive floats of the NCHW plane
@@ -343,8 +372,8 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #pragma unroll
                     for (int j = 0; j < 32; j += 2) {
                         if (n0 + c + j < p.N) {      // N % 8 == 0: pairs are in or out together
-                            const float v0 = fmaf(__uint_as_float(r[j]), sh->scale[acc][c + j], sh->bias[acc][c + j]);
-                            const float v1 = fmaf(__uint_as_float(r[j + 1]), sh->scale[acc][c + j + 1], sh->bias[acc][c + j + 1]);
+                            const float v0 = fmaf(__uint_as_float(r[j]), sc[c + j], bi[c + j]);
+                            const float v1 = fmaf(__uint_as_float(r[j + 1]), sc[c + j + 1], bi[c + j + 1]);
                             const uint32_t pk = pack_bf16(v0, v1);     // the bf16 result, widened again
                             obase[(size_t)(c + j) * S] = __uint_as_float(pk << 16);
                             obase[(size_t)(c + j + 1) * S] = __uint_as_float(pk & 0xFFFF0000u);
@@ -356,7 +385,7 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #pragma unroll
                         for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__fmul_rn(__uint_as_float(r[j]), rs));
                     }
-                    store_row_chunk(p, r, &sh->scale[acc][c], &sh->bias[acc][c], row, n0 + c, vec32);
+                    store_row_chunk(p, r, &sc[c], &bi[c], row, n0 + c, vec32);
                 }
             };
             // this warp's chunks: columns colgrp*32 + 64*i
@@ -454,6 +483,7 @@ static nvq_status launch_pair(uint16_t* d_y, const void* d_x, const void* d_w,
     if (tiles < pairs) pairs = tiles;
     int rem = tiles % pairs;
     int split = (tiles > pairs && rem > 0 && 2 * rem <= pairs) ? rem : 0;
+    if (p.N <= BN / 2) split = 0;   // every tile is half-width already
     p.num_big = tiles - split;
     p.num_items = p.num_big + 2 * split;
     cudaLaunchConfig_t cfg = {};
@@ -520,6 +550,7 @@ static nvq_status launch_implicit_conv(float* d_out, const uint16_t* d_x_nhwc, c
     if (tiles < pairs) pairs = tiles;
     int rem = tiles % pairs;
     int split = (tiles > pairs && rem > 0 && 2 * rem <= pairs) ? rem : 0;
+    if (p.N <= BN / 2) split = 0;   // every tile is half-width already
     p.num_big = tiles - split;
     p.num_items = p.num_big + 2 * split;
     cudaLaunchConfig_t cfg = {};

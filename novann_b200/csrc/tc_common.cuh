@@ -49,6 +49,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Non-blocking look at a barrier phase (try_wait may suspend the thread for a while).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait.  `abort_flag` (shared memory) is raised by whichever role gives up first
 // so that every other role leaves its own waits promptly; returns false on give-up.
 __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity,

@@ -6,6 +6,7 @@
     python -m novann_b200.profile_cases linear [M=4096 N=4096 K=4096]
     python -m novann_b200.profile_cases w8a8   [M=4096 N=4096 K=4096]
     python -m novann_b200.profile_cases cnn    [batch=128 steps=3]
+    python -m novann_b200.profile_cases mlp    [batch=128 steps=3]
     python -m novann_b200.profile_cases conv   [N=128 C=64 HW=56 Cout=128 reps=2]
     python -m novann_b200.profile_cases fewrows [M=16 N=8192 K=8192 reps=3]
 
@@ -108,6 +109,15 @@ def case_cnn(batch: int = 128, steps: int = 3) -> None:
         step.step(xs[0], ys[0])
 
 
+def case_mlp(batch: int = 128, steps: int = 3) -> None:
+    """Training steps of the 784-256-128-10 MLP, eager launches."""
+    from .train import MLPTrainStep
+    x, y, params = workloads.mlp_inputs(batch, seed=0)
+    step = MLPTrainStep(params, batch, lr=0.01)
+    for _ in range(steps):
+        step.step(x, y)
+
+
 def case_conv(n: int = 128, c: int = 64, hw: int = 56, cout: int = 128, reps: int = 2) -> None:
     """FP8-weight 3x3 convolution (stride 1, pad 1) through nvq_conv2d_fwd_q, device resident."""
     from . import _lib
@@ -166,6 +176,8 @@ def main(argv) -> None:
         case_w8a8(*args)
     elif what == "cnn":
         case_cnn(*args)
+    elif what == "mlp":
+        case_mlp(*args)
     elif what == "conv":
         case_conv(*args)
     elif what == "fewrows":

@@ -43,6 +43,19 @@ def test_linear_fp8_ragged_shapes(gpu, m, n, k):
     assert err <= 2.0 ** -7, err
 
 
+@pytest.mark.parametrize("use_workspace", [True, False])
+@pytest.mark.parametrize("m,n,k", [(100000, 128, 192), (60000, 72, 80)])
+def test_linear_narrow_output_many_tiles_per_cta(gpu, m, n, k, use_workspace):
+    """At most 128 output columns: the CTA-pair kernel cycles through four accumulator buffers
+    in tensor memory; with five and more tiles per CTA pair every buffer is reused."""
+    xb, w, b = workloads.linear_inputs(m, n, k, seed=n)
+    wq, sc = o.quantize_weight_per_channel(w, "e4m3")
+    y = F.linear_q_host(xb, wq, sc, b, "e4m3", gpu, use_workspace=use_workspace)
+    want_bits, _ = o.linear_fwd_qweight(xb, wq, sc, b, "e4m3")
+    err = o.max_abs_rel(o.bf16_bits_to_f32(y), o.bf16_bits_to_f32(want_bits))
+    assert err <= 2.0 ** -7, err
+
+
 @pytest.mark.parametrize("fmt", ["e4m3", "e5m2"])
 @pytest.mark.parametrize("m,n,k", [(256, 512, 512), (200, 1000, 336), (1024, 16, 144), (640, 1280, 2048)])
 def test_linear_fp8_expanded_in_kernel(gpu, fmt, m, n, k):
