@@ -374,6 +374,8 @@ def test_quant_mlp_inference_fused_relu(gpu):
     (5, 64, 9, 9, 40, 1, 0),          # 1 x 1 convolution, no padding
     (2, 64, 6, 20, 24, 3, 0),         # no padding: output 4 x 18
     (4, 192, 7, 7, 128, 3, 1),        # three channel blocks
+    (372, 64, 14, 14, 128, 3, 1),     # five tiles per CTA pair: all four accumulator buffers reused
+    (3, 128, 10, 10, 96, 3, 1),       # at most 128 channels out, an even number of k-blocks
 ])
 def test_implicit_gemm_conv_equals_patch_matrix_conv_and_oracle(gpu, case, monkeypatch):
     """The tcgen05 implicit-GEMM convolution (4-D TMA boxes, no patch matrix) against the
