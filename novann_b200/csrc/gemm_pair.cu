@@ -10,7 +10,8 @@
 //   warp 0  producer (both CTAs): TMA loads into the CTA's own ring slot; the bytes of both
 //           CTAs are counted on the LEADER's full barrier (no multicast anywhere)
 //   warp 1  TMEM allocation (both CTAs, cta_group::2); in the leader one lane issues the MMAs
-//           and commits: slot release and "accumulator ready" are multicast to both CTAs
+//           and commits: slot release and "accumulator ready" are multicast to both CTAs;
+//           accumulators: two of 256 TMEM columns, or four of 128 for outputs of <= 128 columns
 //   warps 2-9 epilogue (both CTAs): own 128 rows, two warps per 32-row TMEM quarter taking
 //           alternate 32-column chunks, the TMEM load of a warp's next chunk in flight while it
 //           stores the current one; "accumulator drained" is signalled to the leader's barrier,
