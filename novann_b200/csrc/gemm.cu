@@ -43,8 +43,8 @@ struct Shared {            // lives after the tile ring
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
     int abort_flag;
-    float scale[2][BN];
-    float bias[2][BN];
+    alignas(16) float scale[2][BN];   // read as float4 by the epilogue
+    alignas(16) float bias[2][BN];
 };
 
 __global__ void __launch_bounds__(THREADS, 1)

@@ -190,16 +190,28 @@ __device__ __forceinline__ TileRef tile_ref(const LinearParams& p, int item) {
     return t;
 }
 
+// eight consecutive floats of a 16-byte aligned (shared-memory) array as two 128-bit loads: the
+// epilogue's scale / bias reads are broadcasts, and four times fewer of them leave the
+// shared-memory pipe to the MMAs' operand reads
+__device__ __forceinline__ void load8_f32(float* dst, const float* src) {
+    const float4 a = *reinterpret_cast<const float4*>(src);
+    const float4 b = *reinterpret_cast<const float4*>(src + 4);
+    dst[0] = a.x; dst[1] = a.y; dst[2] = a.z; dst[3] = a.w;
+    dst[4] = b.x; dst[5] = b.y; dst[6] = b.z; dst[7] = b.w;
+}
+
 // fp32 flavour of store_chunk: 32 accumulators -> scale, bias -> 128 bytes of the row
 __device__ __forceinline__ void store_chunk_f32(const uint32_t* r, const float* scale, const float* bias,
                                                 float* yrow, int n_base, int N, bool vec32, bool relu) {
 #pragma unroll
     for (int g = 0; g < 4; g++) {
         u32x8 o;
+        float sc[8], bi[8];
+        load8_f32(sc, scale + g * 8);
+        load8_f32(bi, bias + g * 8);
 #pragma unroll
         for (int j = 0; j < 8; j++) {
-            const int cc = g * 8 + j;
-            float v = fmaf(__uint_as_float(r[cc]), scale[cc], bias[cc]);
+            float v = fmaf(__uint_as_float(r[g * 8 + j]), sc[j], bi[j]);
             if (relu) v = __fmul_rn(v, v > 0.f ? 1.f : 0.f);
             o.v[j] = __float_as_uint(v);
         }
@@ -222,11 +234,16 @@ __device__ __forceinline__ void store_chunk(const uint32_t* r, const float* scal
 #pragma unroll
     for (int g = 0; g < 2; g++) {
         u32x8 o;
+        float sc[16], bi[16];
+        load8_f32(sc, scale + g * 16);
+        load8_f32(sc + 8, scale + g * 16 + 8);
+        load8_f32(bi, bias + g * 16);
+        load8_f32(bi + 8, bias + g * 16 + 8);
 #pragma unroll
         for (int j = 0; j < 8; j++) {
             const int cc = g * 16 + 2 * j;
-            float v0 = fmaf(__uint_as_float(r[cc]), scale[cc], bias[cc]);
-            float v1 = fmaf(__uint_as_float(r[cc + 1]), scale[cc + 1], bias[cc + 1]);
+            float v0 = fmaf(__uint_as_float(r[cc]), sc[2 * j], bi[2 * j]);
+            float v1 = fmaf(__uint_as_float(r[cc + 1]), sc[2 * j + 1], bi[2 * j + 1]);
             if (relu) {
                 v0 = __fmul_rn(v0, v0 > 0.f ? 1.f : 0.f);
                 v1 = __fmul_rn(v1, v1 > 0.f ? 1.f : 0.f);

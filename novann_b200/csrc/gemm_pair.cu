@@ -73,8 +73,8 @@ struct Shared {
     uint64_t tmem_empty[4];
     uint32_t tmem_base;
     int abort_flag;
-    float scale[2][BN];
-    float bias[2][BN];
+    alignas(16) float scale[2][BN];   // read as float4 by the epilogue
+    alignas(16) float bias[2][BN];
 };
 
 template <int FUSED>
@@ -371,13 +371,18 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 if (!valid) return;
                 if constexpr (IMPL) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        if (n0 + c + j < p.N) {      // N % 8 == 0: pairs are in or out together
-                            const float v0 = fmaf(__uint_as_float(r[j]), sc[c + j], bi[c + j]);
-                            const float v1 = fmaf(__uint_as_float(r[j + 1]), sc[c + j + 1], bi[c + j + 1]);
+                    for (int j8 = 0; j8 < 32; j8 += 8) {
+                        if (n0 + c + j8 >= p.N) break;      // N % 8 == 0: groups of 8 are in or out together
+                        float s8[8], b8[8];
+                        load8_f32(s8, sc + c + j8);
+                        load8_f32(b8, bi + c + j8);
+#pragma unroll
+                        for (int j = 0; j < 8; j += 2) {
+                            const float v0 = fmaf(__uint_as_float(r[j8 + j]), s8[j], b8[j]);
+                            const float v1 = fmaf(__uint_as_float(r[j8 + j + 1]), s8[j + 1], b8[j + 1]);
                             const uint32_t pk = pack_bf16(v0, v1);     // the bf16 result, widened again
-                            obase[(size_t)(c + j) * S] = __uint_as_float(pk << 16);
-                            obase[(size_t)(c + j + 1) * S] = __uint_as_float(pk & 0xFFFF0000u);
+                            obase[(size_t)(c + j8 + j) * S] = __uint_as_float(pk << 16);
+                            obase[(size_t)(c + j8 + j + 1) * S] = __uint_as_float(pk & 0xFFFF0000u);
                         }
                     }
                 } else {
