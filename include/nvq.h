@@ -163,6 +163,15 @@ nvq_status nvq_dequantize_fp4_b32(uint16_t* d_dst_bf16, const uint8_t* d_packed,
  * d_workspace may be NULL for E4M3 / E5M2 weights when M > 128 and K % 16 == 0: the
  * codes are then expanded inside the GEMM kernel, in shared memory (slower than the
  * workspace form on large problems, but nothing is written to HBM).
+ * M <= 128 (few rows): the weight is read once, as codes, and the workspace holds
+ * partial sums instead.  FP8 codes are then the tensor cores' operand as they are
+ * (kind::f8f6f4) and each activation row is carried as two rows of E4M3 codes,
+ * x = a_m * (p1 + p2 / 16) with a_m a power of two: exact for every element down to
+ * 2^-13 of its row's largest, an absolute error <= 2^-21 of the row's largest below
+ * that; a non-finite activation makes its output row NaN, and an E5M2 infinity code
+ * in the weight gives NaN (the quantiser never emits one).  NVQ_FEW_ROWS_MODE=convert
+ * selects the kernel that expands the codes to bf16 in shared memory instead (bf16
+ * activations as they are; also the FP4 path).
  */
 nvq_status nvq_linear_workspace_bytes(size_t N, size_t K, nvq_dtype w_fmt, size_t* bytes);
 nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf16, const uint8_t* d_wq,

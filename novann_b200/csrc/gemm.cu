@@ -496,9 +496,17 @@ extern "C" nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf1
     if (M <= 128 && K % (w_fmt == NVQ_E2M1_B32 ? 32 : 16) == 0 && nvq_aligned(d_wq, 16) && nvq_aligned(d_x_bf16, 16) &&
         d_workspace && nvq_aligned(d_workspace, 16) && !mode && M * N < (1u << 31) && N < (1u << 24) &&
         K < (1u << 24) && N * K < (1ull << 40) &&
-        workspace_bytes >= nvq_linear_small_m_workspace(M, N, K, device))
+        workspace_bytes >= nvq_linear_small_m_workspace(M, N, K, device)) {
+        // FP8 codes feed the tensor cores directly (activations split into two E4M3 rows);
+        // NVQ_FEW_ROWS_MODE=convert keeps the kernel that expands the codes to bf16
+        const char* few = getenv("NVQ_FEW_ROWS_MODE");
+        if (w_fmt != NVQ_E2M1_B32 && !(few && few[0] == 'c') &&
+            workspace_bytes >= nvq_linear_small_m_direct_workspace(M, N, K, device))
+            return nvq_linear_launch_small_m_direct(d_y_bf16, d_x_bf16, d_wq, w_fmt, d_w_scales, d_bias, M, N,
+                                                    K, d_workspace, device, st);
         return nvq_linear_launch_small_m(d_y_bf16, d_x_bf16, d_wq, w_fmt, d_w_scales, d_bias, M, N, K,
                                          (float*)d_workspace, device, st);
+    }
     NVQ_REQUIRE(d_workspace && workspace_bytes >= N * K * 2 && nvq_aligned(d_workspace, 32),
                 "nvq_linear_fwd: workspace of %zu bytes (32-byte aligned) required", N * K * 2);
     s = nvq_linear_expand_weight((uint16_t*)d_workspace, d_wq, w_fmt, d_w_scales, N, K, device, stream);

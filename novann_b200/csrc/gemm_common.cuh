@@ -52,6 +52,13 @@ nvq_status nvq_linear_launch_pair_w8a8(uint16_t* d_y, const uint8_t* d_xq, const
 // Few rows (M <= 128), FP8 codes: weight-streaming kernel with the dequantisation fused (the codes
 // are read once, nothing expanded is written); d_partial holds nvq_linear_small_m_workspace bytes.
 size_t nvq_linear_small_m_workspace(size_t M, size_t N, size_t K, int device);
+// FP8 codes only: the weight codes are the MMA operand as they are (kind::f8f6f4) and each
+// activation row is split into two rows of E4M3 codes; workspace = partial sums + those codes.
+size_t nvq_linear_small_m_direct_workspace(size_t M, size_t N, size_t K, int device);
+nvq_status nvq_linear_launch_small_m_direct(uint16_t* d_y, const uint16_t* d_x, const uint8_t* d_wq,
+                                            nvq_dtype fmt, const float* d_scales, const float* d_bias,
+                                            size_t M, size_t N, size_t K, void* d_workspace, int device,
+                                            cudaStream_t st);
 nvq_status nvq_linear_launch_small_m(uint16_t* d_y, const uint16_t* d_x, const uint8_t* d_wq,
                                      nvq_dtype fmt, const float* d_scales, const float* d_bias,
                                      size_t M, size_t N, size_t K, float* d_partial, int device,

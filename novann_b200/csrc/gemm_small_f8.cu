@@ -1,0 +1,399 @@
+// FP8-weight Linear forward for few rows (M <= 128), direct form: the weight codes go from HBM
+// into the tensor cores' operand slots by TMA and are never touched by a thread.
+//
+// tcgen05.mma.kind::f8f6f4 multiplies 8-bit float codes by 8-bit float codes.  The activations are
+// bf16 (8 significant bits), so each row of X is first written as TWO rows of E4M3 codes:
+//
+//   a_m  = 2^(floor(log2 max_k |x[m,k]|) - 7)              a power of two: x / a_m is exact, < 256
+//   p1   = e4m3_rn(x / a_m)                                 the leading 4 significant bits
+//   p2   = e4m3_rn(16 * (x / a_m - p1))                     the remaining 4 bits (exact: the
+//                                                           residual of an 8-bit value has <= 4)
+//   x    = a_m * (p1 + p2 / 16)                             exactly, for |x| >= a_m / 64; smaller
+//                                                           elements (below 2^-13 of the row's
+//                                                           maximum) keep an absolute error
+//                                                           <= a_m * 2^-14 (E4M3 subnormal spacing)
+//
+//   Y[m, n] = bf16( a_m * s_n * (sum_k w[n,k] p1[m,k] + sum_k w[n,k] p2[m,k] / 16) + b_n )
+//
+// Operands are swapped as in the converter kernel of gemm_small.cu: MMA M = 128 weight rows,
+// MMA N = 2 * MP (MP = M rounded up to 16; columns [0, MP) hold the p1 sums, [MP, 2 MP) the p2
+// sums), K = 32 codes per instruction.  A unit is (128-row weight block, 128-code k-block); each
+// CTA takes a contiguous run of units, writes fp32 partial sums per weight block it touched, and
+// a second kernel adds them in CTA order, applies a_m, s_n, b_n and rounds to bf16.
+//
+//   warp 0      TMA producer: 128 x 128 weight codes (16 KB) + 2 MP x 128 activation codes per unit,
+//               both with the 128-byte swizzle, into a ring of 4 (MP = 128) to 10 (MP = 16) slots
+//   warp 1      TMEM allocation; one lane issues the MMAs (128 x 2MP x 32) and commits
+//   warps 2-5   epilogue: TMEM -> p1 sum + p2 sum / 16 -> fp32 partial slot
+// Every wait is bounded.  A non-finite activation makes its whole output row NaN.
+#include "gemm_common.cuh"
+
+namespace {
+
+constexpr int BKC = 128;                    // codes per k-block = one 128-byte operand row
+constexpr int WROWS = 128;                  // weight rows per block = MMA M
+constexpr int A_BYTES = WROWS * BKC;        // 16 KB
+constexpr int MAX_STAGES = 10;
+constexpr int RING_BYTES = 212992;          // 208 KB of operand ring
+__host__ __device__ constexpr int stage_bytes(int MP) { return A_BYTES + 2 * MP * BKC; }
+__host__ __device__ constexpr int num_stages(int MP) {
+    return RING_BYTES / stage_bytes(MP) < MAX_STAGES ? RING_BYTES / stage_bytes(MP) : MAX_STAGES;
+}
+constexpr int THREADS = 192;                // producer, MMA, four epilogue warps
+constexpr int ACC_COLS = 256;               // TMEM columns per accumulator (2 MP <= 256)
+constexpr int TMEM_COLS = 2 * ACC_COLS;
+constexpr int SMEM_BYTES = RING_BYTES + 1024 + 1024;
+
+enum { ERR_PRODUCER = 31, ERR_MMA_FULL = 32, ERR_MMA_TMEM = 33, ERR_EPILOGUE = 34 };
+
+struct DirectParams {
+    float* partial;       // [n_blocks][pieces][MP][128] fp32
+    const float* xscale;  // a_m, MP floats
+    int M, MP, N, K;
+    int n_blocks, num_kb;
+    int total;            // n_blocks * num_kb units
+    int quota;            // units per CTA
+    int pieces;           // partial slots per weight block
+    int* status;
+};
+
+struct Shared {
+    uint64_t full[MAX_STAGES];
+    uint64_t empty[MAX_STAGES];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__host__ __device__ inline int first_cta_of(int nb, int num_kb, int quota) { return (nb * num_kb) / quota; }
+
+__device__ __forceinline__ uint32_t e4m3x2(float lo, float hi) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ void e4m3x2_to_f32(uint32_t codes, float& lo, float& hi) {
+    uint32_t h;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h) : "h"((uint16_t)codes));
+    asm("cvt.f32.f16 %0, %1;" : "=f"(lo) : "h"((uint16_t)(h & 0xFFFFu)));
+    asm("cvt.f32.f16 %0, %1;" : "=f"(hi) : "h"((uint16_t)(h >> 16)));
+}
+
+// One block per activation row (rows M .. MP-1 are written as zeros): row maximum, then the two
+// code rows.  x8 is [2 MP][K] bytes: row m = p1 of activation row m, row MP + m = p2.
+__global__ void __launch_bounds__(256)
+split_activations_kernel(uint8_t* __restrict__ x8, float* __restrict__ xscale,
+                         const uint16_t* __restrict__ x, int M, int MP, int K) {
+    __shared__ float red[8];
+    __shared__ int bad_s;
+    const int m = blockIdx.x;
+    const int pairs = K / 2;                       // K % 16 == 0
+    uint16_t* row1 = (uint16_t*)(x8 + (size_t)m * K);
+    uint16_t* row2 = (uint16_t*)(x8 + (size_t)(MP + m) * K);
+    if (m >= M) {
+        for (int i = threadIdx.x; i < pairs; i += blockDim.x) { row1[i] = 0; row2[i] = 0; }
+        if (threadIdx.x == 0) xscale[m] = 0.f;
+        return;
+    }
+    const uint32_t* xr = (const uint32_t*)(x + (size_t)m * K);
+    float amax = 0.f;
+    int bad = 0;
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const uint32_t w = xr[i];
+        const float a = fabsf(__uint_as_float(w << 16)), b = fabsf(__uint_as_float(w & 0xFFFF0000u));
+        bad |= !(a <= 3.4e38f) | !(b <= 3.4e38f);   // inf or NaN
+        amax = fmaxf(amax, fmaxf(a, b));
+    }
+    if (threadIdx.x == 0) bad_s = 0;
+    __syncthreads();
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    if (bad) bad_s = 1;
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) amax = fmaxf(amax, red[i]);
+    const bool non_finite = bad_s != 0;
+    // a = 2^(e - 7) with e the exponent of the row maximum; an all-zero row keeps a = 1.
+    // Exponents are clamped so that a and 1 / a stay normal fp32 numbers.
+    int e = amax > 0.f ? (int)((__float_as_uint(amax) >> 23) & 0xFF) - 127 : 7;
+    e = max(-119, min(127, e));
+    const float a = __uint_as_float((uint32_t)(e - 7 + 127) << 23);
+    const float inv = __uint_as_float((uint32_t)(7 - e + 127) << 23);
+    if (threadIdx.x == 0) xscale[m] = non_finite ? __uint_as_float(0x7FC00000u) : a;
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const uint32_t w = xr[i];
+        const float v0 = __uint_as_float(w << 16) * inv, v1 = __uint_as_float(w & 0xFFFF0000u) * inv;
+        const uint32_t c1 = e4m3x2(v0, v1);
+        float f0, f1;
+        e4m3x2_to_f32(c1, f0, f1);
+        const uint32_t c2 = e4m3x2((v0 - f0) * 16.f, (v1 - f1) * 16.f);
+        row1[i] = non_finite ? 0 : (uint16_t)c1;
+        row2[i] = non_finite ? 0 : (uint16_t)c2;
+    }
+}
+
+// Calls f(nb, kb0, kb1, piece) for every weight block this CTA's run touches, in order.
+template <class F>
+__device__ __forceinline__ bool for_each_segment(const DirectParams& p, F f) {
+    const int u_begin = blockIdx.x * p.quota;
+    const int u_end = min(p.total, u_begin + p.quota);
+    for (int u = u_begin; u < u_end;) {
+        const int nb = u / p.num_kb, kb0 = u - nb * p.num_kb;
+        const int kb1 = min(p.num_kb, kb0 + (u_end - u));
+        if (!f(nb, kb0, kb1, (int)blockIdx.x - first_cta_of(nb, p.num_kb, p.quota))) return false;
+        u += kb1 - kb0;
+    }
+    return true;
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(THREADS, 1)
+linear_small_m_direct_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                             const DirectParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = tc::smem_u32(smem_raw);
+    const uint32_t tiles = (raw + 1023u) & ~1023u;
+    Shared* sh = (Shared*)(smem_raw + (tiles - raw) + RING_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int* abort_flag = &sh->abort_flag;
+    const uint32_t STAGES = (uint32_t)num_stages(p.MP), STAGE_BYTES = (uint32_t)stage_bytes(p.MP);
+    const uint32_t NP = 2u * (uint32_t)p.MP;           // MMA N: p1 columns, then p2 columns
+    // the finalising kernel may be scheduled now; it waits for this grid before it reads
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < STAGES; s++) {
+            tc::mbar_init(tc::smem_u32(&sh->full[s]), 1);
+            tc::mbar_init(tc::smem_u32(&sh->empty[s]), 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            tc::mbar_init(tc::smem_u32(&sh->tmem_full[a]), 1);
+            tc::mbar_init(tc::smem_u32(&sh->tmem_empty[a]), 4);
+        }
+        sh->abort_flag = 0;
+        tc::mbar_fence_init();
+        tc::tma_prefetch_desc(&map_w);
+        tc::tma_prefetch_desc(&map_x);
+    }
+    if (warp == 1) {
+        tc::tmem_alloc(tc::smem_u32(&sh->tmem_base), TMEM_COLS);
+        tc::tmem_relinquish();
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::tc_fence_after();
+    const uint32_t tmem_base = sh->tmem_base;
+    // the activation codes come from the splitting kernel launched just before this one
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            for_each_segment(p, [&](int nb, int kb0, int kb1, int) {
+                for (int kb = kb0; kb < kb1; kb++) {
+                    if (!tc::mbar_wait(tc::smem_u32(&sh->empty[stage]), phase ^ 1, abort_flag, ERR_PRODUCER))
+                        return false;
+                    const uint32_t dst = tiles + stage * STAGE_BYTES;
+                    const uint32_t fbar = tc::smem_u32(&sh->full[stage]);
+                    tc::mbar_arrive_expect_tx(fbar, A_BYTES + NP * BKC);
+                    tc::tma_load_2d(dst, &map_w, fbar, kb * BKC, nb * WROWS);
+                    tc::tma_load_2d(dst + A_BYTES, &map_x, fbar, kb * BKC, 0);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                return true;
+            });
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            int it = 0;
+            // A = weight codes (E4M3 = 0, E5M2 = 1), B = activation codes (E4M3)
+            const uint32_t idesc = tc::idesc_f16(WROWS, NP, FMT == NVQ_E5M2 ? 1u : 0u, 0u);
+            for_each_segment(p, [&](int, int kb0, int kb1, int) {
+                const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+                it++;
+                if (!tc::mbar_wait(tc::smem_u32(&sh->tmem_empty[acc]), acc_phase ^ 1, abort_flag, ERR_MMA_TMEM))
+                    return false;
+                tc::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
+                for (int kb = kb0; kb < kb1; kb++) {
+                    if (!tc::mbar_wait(tc::smem_u32(&sh->full[stage]), phase, abort_flag, ERR_MMA_FULL))
+                        return false;
+                    tc::tc_fence_after();
+                    const uint32_t a_addr = tiles + stage * STAGE_BYTES;
+                    const uint64_t a_desc = tc::smem_desc_k_sw128(a_addr);
+                    const uint64_t b_desc = tc::smem_desc_k_sw128(a_addr + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < 4; k++)      // four 32-byte k-steps of 32 codes
+                        tc::tc_mma_f8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    tc::tc_commit(tc::smem_u32(&sh->empty[stage]));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                tc::tc_commit(tc::smem_u32(&sh->tmem_full[acc]));
+                return true;
+            });
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2-5)
+        const int quarter = warp & 3;
+        int it = 0;
+        for_each_segment(p, [&](int nb, int, int, int piece) {
+            const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+            it++;
+            bool ok = tc::mbar_wait(tc::smem_u32(&sh->tmem_full[acc]), acc_phase, abort_flag, ERR_EPILOGUE);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) return false;
+            tc::tc_fence_after();
+            const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+            // thread = weight row quarter*32 + lane of the block; column m is activation row m:
+            // for a fixed m a warp writes 32 consecutive floats
+            float* out = p.partial + ((size_t)(nb * p.pieces + piece) * p.MP) * WROWS + quarter * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < p.MP; c += 16) {
+                uint32_t r1[16], r2[16];
+                tc::tmem_ld_32x16(taddr + c, r1);
+                tc::tmem_ld_32x16(taddr + p.MP + c, r2);
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; j++)
+                    if (c + j < p.M)
+                        out[(size_t)(c + j) * WROWS] = fmaf(__uint_as_float(r2[j]), 0.0625f, __uint_as_float(r1[j]));
+            }
+            tc::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(tc::smem_u32(&sh->tmem_empty[acc]));
+            return true;
+        });
+    }
+
+    // ---------------------------------------------------------------- teardown
+    if (*abort_flag) {
+        for (int i = 0; i < 64; i++) __nanosleep(20000);   // let copies in flight land
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::tc_fence_after();
+    if (warp == 1) tc::tmem_dealloc(tmem_base, TMEM_COLS);
+    if (threadIdx.x == 0 && *abort_flag && p.status) atomicCAS(p.status, 0, *abort_flag);
+}
+
+// y[m, n] = bf16(a_m * scale_n * sum over the slots of n's weight block + bias_n)
+__global__ void direct_finalize_kernel(uint16_t* __restrict__ y, const float* __restrict__ partial,
+                                       const float* __restrict__ scales, const float* __restrict__ bias,
+                                       DirectParams p) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the partial sums are complete
+    const int total = p.M * p.N;
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
+        const int m = e / p.N, n = e - m * p.N;
+        const int nb = n / WROWS, nl = n - nb * WROWS;
+        const int first = first_cta_of(nb, p.num_kb, p.quota);
+        const int last = ((nb + 1) * p.num_kb - 1) / p.quota;
+        const float* src = partial + ((size_t)(nb * p.pieces) * p.MP + m) * WROWS + nl;
+        float s = src[0];
+        for (int pc = 1; pc <= last - first; pc++) s = __fadd_rn(s, src[(size_t)pc * p.MP * WROWS]);
+        const float v = fmaf(__fmul_rn(s, p.xscale[m]), scales ? scales[n] : 1.f, bias ? bias[n] : 0.f);
+        y[e] = (uint16_t)(pack_bf16(v, 0.f) & 0xFFFFu);
+    }
+}
+
+struct Geometry { int MP, n_blocks, num_kb, total, grid, quota, pieces; size_t partial_bytes, x8_bytes; };
+Geometry geometry(size_t M, size_t N, size_t K, int device) {
+    Geometry g;
+    g.MP = (int)((M + 15) / 16 * 16);
+    g.n_blocks = (int)((N + WROWS - 1) / WROWS);
+    g.num_kb = (int)((K + BKC - 1) / BKC);
+    g.total = g.n_blocks * g.num_kb;
+    g.grid = nvq_sm_count(device);
+    if (g.grid > g.total) g.grid = g.total;
+    g.quota = (g.total + g.grid - 1) / g.grid;
+    g.grid = (g.total + g.quota - 1) / g.quota;
+    g.pieces = (g.num_kb + g.quota - 1) / g.quota + 1;
+    g.partial_bytes = ((size_t)g.n_blocks * g.pieces * g.MP * WROWS * sizeof(float) + 255) / 256 * 256;
+    g.x8_bytes = ((size_t)2 * g.MP * K + 255) / 256 * 256;
+    return g;
+}
+
+}  // namespace
+
+// workspace: [fp32 partial sums][activation codes, 2 MP x K bytes][a_m, MP floats]
+size_t nvq_linear_small_m_direct_workspace(size_t M, size_t N, size_t K, int device) {
+    const Geometry g = geometry(M, N, K, device);
+    return g.partial_bytes + g.x8_bytes + (size_t)g.MP * sizeof(float);
+}
+
+nvq_status nvq_linear_launch_small_m_direct(uint16_t* d_y, const uint16_t* d_x, const uint8_t* d_wq,
+                                            nvq_dtype fmt, const float* d_scales, const float* d_bias,
+                                            size_t M, size_t N, size_t K, void* d_workspace, int device,
+                                            cudaStream_t st) {
+    NVQ_REQUIRE(M >= 1 && M <= 128 && K % 16 == 0, "small-M Linear: needs 1 <= M <= 128 and K %% 16 == 0");
+    NVQ_REQUIRE(fmt == NVQ_E4M3 || fmt == NVQ_E5M2, "small-M direct Linear: FP8 weight codes only");
+    NVQ_REQUIRE(M * N < (1u << 31) && N < (1u << 24) && K < (1u << 24) && N * K < (1ull << 40),
+                "small-M Linear: dimension too large");
+    const Geometry g = geometry(M, N, K, device);
+    uint8_t* ws = (uint8_t*)d_workspace;
+    uint8_t* d_x8 = ws + g.partial_bytes;
+    float* d_xscale = (float*)(ws + g.partial_bytes + g.x8_bytes);
+    DirectParams p;
+    p.partial = (float*)ws;
+    p.xscale = d_xscale;
+    p.M = (int)M;
+    p.MP = g.MP;
+    p.N = (int)N;
+    p.K = (int)K;
+    p.n_blocks = g.n_blocks;
+    p.num_kb = g.num_kb;
+    p.total = g.total;
+    p.quota = g.quota;
+    p.pieces = g.pieces;
+    nvq_status s = nvq_status_word(device, &p.status);
+    if (s != NVQ_OK) return s;
+    CUtensorMap map_w, map_x;
+    // both operands: rows of 128 codes, 128-byte swizzle; columns past K read as zero codes
+    s = nvq_make_tmap_2d(&map_w, d_wq, N, K, WROWS, BKC, 1, 1);
+    if (s != NVQ_OK) return s;
+    s = nvq_make_tmap_2d(&map_x, d_x8, (uint64_t)2 * g.MP, K, (uint32_t)(2 * g.MP), BKC, 1, 1);
+    if (s != NVQ_OK) return s;
+    static bool attr_set[64];
+    if (!attr_set[device]) {
+        NVQ_CUDA(cudaFuncSetAttribute(linear_small_m_direct_kernel<NVQ_E4M3>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        NVQ_CUDA(cudaFuncSetAttribute(linear_small_m_direct_kernel<NVQ_E5M2>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        attr_set[device] = true;
+    }
+    split_activations_kernel<<<g.MP, 256, 0, st>>>(d_x8, d_xscale, d_x, (int)M, g.MP, (int)K);
+    NVQ_LAUNCHED();
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // set up under the previous kernel's tail
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(g.grid);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (fmt == NVQ_E4M3)
+        NVQ_CUDA(cudaLaunchKernelEx(&cfg, linear_small_m_direct_kernel<NVQ_E4M3>, map_w, map_x, p));
+    else
+        NVQ_CUDA(cudaLaunchKernelEx(&cfg, linear_small_m_direct_kernel<NVQ_E5M2>, map_w, map_x, p));
+    NVQ_LAUNCHED();
+    const int total = p.M * p.N;
+    int fgrid = (total + 255) / 256;
+    const int cap = nvq_sm_count(device) * 8;
+    if (fgrid > cap) fgrid = cap;
+    cudaLaunchConfig_t fcfg = {};
+    fcfg.gridDim = dim3(fgrid);
+    fcfg.blockDim = dim3(256);
+    fcfg.stream = st;
+    fcfg.attrs = attr;
+    fcfg.numAttrs = 1;
+    NVQ_CUDA(cudaLaunchKernelEx(&fcfg, direct_finalize_kernel, d_y, (const float*)p.partial, d_scales, d_bias, p));
+    NVQ_LAUNCHED();
+    return NVQ_OK;
+}

@@ -233,13 +233,17 @@ def test_linear_split_last_wave_and_deep_k(gpu, m, n, k):
     (1, 128, 64), (3, 8, 16), (16, 4096, 4096), (17, 1000, 336), (64, 264, 8192), (100, 2048, 48),
     (128, 4096, 1024), (128, 136, 4160), (31, 20000, 64),
 ])
-def test_linear_few_rows_weight_streaming_kernel(gpu, fmt, m, n, k, monkeypatch):
-    """M <= 128 runs the weight-streaming kernel (codes read once, expanded in shared memory,
-    operands swapped, split along K with a deterministic reduction): against the oracle, against
-    the expansion-pass path of the same call, and twice in a row (same bits)."""
+@pytest.mark.parametrize("few_rows_mode", ["direct", "convert"])
+def test_linear_few_rows_weight_streaming_kernel(gpu, fmt, m, n, k, few_rows_mode, monkeypatch):
+    """M <= 128 runs a weight-streaming kernel (codes read once, operands swapped, split along K
+    with a deterministic reduction) - "direct": the codes are the tensor cores' operand and each
+    activation row is two rows of E4M3 codes; "convert": the codes are expanded to bf16 in shared
+    memory.  Against the oracle, against the expansion-pass path of the same call, and twice in a
+    row (same bits)."""
     xb, w, b = workloads.linear_inputs(m, n, k, seed=m + n)
     wq, sc = o.quantize_weight_per_channel(w, fmt)
     monkeypatch.delenv("NVQ_LINEAR_MODE", raising=False)
+    monkeypatch.setenv("NVQ_FEW_ROWS_MODE", few_rows_mode)
     y = F.linear_q_host(xb, wq, sc, b, fmt, gpu)
     y2 = F.linear_q_host(xb, wq, sc, b, fmt, gpu)
     assert np.array_equal(y, y2)
@@ -254,10 +258,11 @@ def test_linear_few_rows_weight_streaming_kernel(gpu, fmt, m, n, k, monkeypatch)
 
 
 @pytest.mark.parametrize("m,fmt", [(8, "e4m3"), (8, "e5m2"), (256, "e4m3"), (256, "e5m2")])
-def test_linear_in_kernel_expansion_of_every_code(gpu, m, fmt):
+def test_linear_in_kernel_expansion_of_every_code(gpu, m, fmt, monkeypatch):
     """Every FP8 code (subnormals, NaN / inf codes, both zeros) through the in-kernel expansion:
-    the few-rows kernel (m = 8) and the fused CTA-pair kernel (m = 256, no workspace).  Row n of
-    the weight holds code n repeated, x is all ones."""
+    the converting few-rows kernel (m = 8) and the fused CTA-pair kernel (m = 256, no workspace).
+    Row n of the weight holds code n repeated, x is all ones."""
+    monkeypatch.setenv("NVQ_FEW_ROWS_MODE", "convert")
     n, k = 256, 64
     wq = np.repeat(np.arange(256, dtype=np.uint8)[:, None], k, axis=1)
     xb = o.f32_to_bf16_bits(np.ones((m, k), np.float32))
@@ -272,6 +277,45 @@ def test_linear_in_kernel_expansion_of_every_code(gpu, m, fmt):
     assert np.array_equal(np.isnan(y[0]), nan)
     assert np.array_equal(y[0][~nan], want[~nan])
     assert np.array_equal(np.nan_to_num(y), np.nan_to_num(np.broadcast_to(y[0], y.shape)))
+
+
+@pytest.mark.parametrize("fmt", ["e4m3", "e5m2"])
+def test_linear_few_rows_direct_every_code_and_activation_split(gpu, fmt, monkeypatch):
+    """The direct few-rows kernel (FP8 codes straight into kind::f8f6f4 MMAs).  (1) Every weight
+    code against x = 1: finite codes bit-exact, NaN codes NaN; an E5M2 infinity code meets the
+    zero low-order piece of the activation and gives NaN where the bf16 paths give infinity (the
+    quantiser never emits those codes).  (2) Activations that use all eight significant bits and
+    span 2^-20 .. 2^6 within a row against a float64 product: the two-piece split is exact down
+    to 2^-13 of the row maximum."""
+    monkeypatch.delenv("NVQ_LINEAR_MODE", raising=False)
+    monkeypatch.setenv("NVQ_FEW_ROWS_MODE", "direct")
+    n, k = 256, 64
+    wq = np.repeat(np.arange(256, dtype=np.uint8)[:, None], k, axis=1)
+    xb = o.f32_to_bf16_bits(np.ones((8, k), np.float32))
+    y = o.bf16_bits_to_f32(F.linear_q_host(xb, wq, np.ones(n, np.float32), None, fmt, gpu))
+    table = o.E4M3_TABLE if fmt == "e4m3" else o.E5M2_TABLE
+    with np.errstate(all="ignore"):
+        want = o.bf16_bits_to_f32(o.f32_to_bf16_bits((table[np.arange(256)].astype(np.float64) * k).astype(np.float32)))
+    finite = np.isfinite(want)
+    assert np.array_equal(y[0][finite], want[finite])
+    assert np.all(np.isnan(y[0][~finite]) | (y[0][~finite] == want[~finite]))
+    assert np.array_equal(np.nan_to_num(y), np.nan_to_num(np.broadcast_to(y[0], y.shape)))
+    # (2)
+    rng = np.random.default_rng(5)
+    m, n, k = 24, 384, 512
+    mant = rng.integers(128, 256, (m, k)).astype(np.float64) / 128.0          # 8 significant bits
+    x = mant * 2.0 ** rng.integers(-20, 7, (m, k)) * rng.choice([-1.0, 1.0], (m, k))
+    x[3] = 0.0                                                                  # an all-zero row
+    xb = o.f32_to_bf16_bits(x.astype(np.float32))
+    assert np.array_equal(o.bf16_bits_to_f32(xb).astype(np.float64), x)
+    w = rng.standard_normal((n, k)).astype(np.float32)
+    wq, sc = o.quantize_weight_per_channel(w, fmt)
+    y = o.bf16_bits_to_f32(F.linear_q_host(xb, wq, sc, None, fmt, gpu)).astype(np.float64)
+    wd = o.dequantize_fp8(wq, 1.0, fmt).astype(np.float64) * sc.astype(np.float64)[:, None]
+    ref = x @ wd.T
+    assert np.all(y[3] == 0.0)
+    assert np.max(np.abs(y - ref)) <= 2.0 ** -8 * np.max(np.abs(ref)) + 1e-30   # bf16 rounding of y only
+    F.check_device_errors(gpu)
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 128, 64), (16, 4096, 4096), (33, 1000, 352), (128, 264, 2048), (7, 136, 96)])

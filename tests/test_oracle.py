@@ -164,3 +164,21 @@ def test_weight_quant_and_linear_oracle():
     yb, y = o.linear_fwd_qweight(xb, wq, s, b)
     ref = o.bf16_bits_to_f32(xb).astype(np.float64) @ w.T.astype(np.float64) + b
     assert o.max_abs_rel(o.bf16_bits_to_f32(yb), ref) < 5e-2  # FP8 weight error only
+
+
+def test_two_piece_e4m3_split_of_bf16_activations():
+    """The few-rows FP8 kernel carries a bf16 activation v (already divided by its row's power of
+    two, so v < 256) as p1 = e4m3(v), p2 = e4m3(16 (v - p1)).  v = p1 + p2 / 16 must hold exactly
+    for every bf16 value in [2^-6, 256), and within 2^-14 below that."""
+    ml_dtypes = pytest.importorskip("ml_dtypes")
+    bits = np.arange(0, 0x8000, dtype=np.uint16)
+    v = (bits.astype(np.uint32) << 16).view(np.float32)
+    for sign in (1.0, -1.0):
+        exact = v[(v >= 2.0 ** -6) & (v < 256)] * np.float32(sign)
+        p1 = exact.astype(ml_dtypes.float8_e4m3fn).astype(np.float32)
+        p2 = ((exact - p1) * 16).astype(ml_dtypes.float8_e4m3fn).astype(np.float32)
+        assert exact.size == 1792 and np.array_equal(p1 + p2 / 16, exact)
+        small = v[(v > 0) & (v < 2.0 ** -6)] * np.float32(sign)
+        p1 = small.astype(ml_dtypes.float8_e4m3fn).astype(np.float32)
+        p2 = ((small - p1) * 16).astype(ml_dtypes.float8_e4m3fn).astype(np.float32)
+        assert np.max(np.abs(p1 + p2 / 16 - small)) <= 2.0 ** -14
