@@ -81,29 +81,62 @@ __device__ __forceinline__ void e4m3x2_to_f32(uint32_t codes, float& lo, float& 
 }
 
 // One block per activation row (rows M .. MP-1 are written as zeros): row maximum, then the two
-// code rows.  x8 is [2 MP][K] bytes: row m = p1 of activation row m, row MP + m = p2.
+// code rows.  x8 is [2 MP][K] bytes: row m = p1 of activation row m, row MP + m = p2.  A row of
+// up to 16384 values is read once (eight 128-bit loads per thread, all issued before the first
+// use) and kept in registers between the two passes; longer rows are read again.
+constexpr int SPLIT_KEEP = 8;
+__device__ __forceinline__ void split8(const uint4& w, float inv, bool non_finite, uint2& c1, uint2& c2) {
+    const uint32_t in[4] = {w.x, w.y, w.z, w.w};
+    uint32_t o1[4], o2[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float v0 = __uint_as_float(in[i] << 16) * inv, v1 = __uint_as_float(in[i] & 0xFFFF0000u) * inv;
+        o1[i] = e4m3x2(v0, v1);
+        float f0, f1;
+        e4m3x2_to_f32(o1[i], f0, f1);
+        o2[i] = e4m3x2((v0 - f0) * 16.f, (v1 - f1) * 16.f);
+    }
+    c1 = non_finite ? make_uint2(0u, 0u) : make_uint2(o1[0] | (o1[1] << 16), o1[2] | (o1[3] << 16));
+    c2 = non_finite ? make_uint2(0u, 0u) : make_uint2(o2[0] | (o2[1] << 16), o2[2] | (o2[3] << 16));
+}
 __global__ void __launch_bounds__(256)
 split_activations_kernel(uint8_t* __restrict__ x8, float* __restrict__ xscale,
                          const uint16_t* __restrict__ x, int M, int MP, int K) {
     __shared__ float red[8];
     __shared__ int bad_s;
     const int m = blockIdx.x;
-    const int pairs = K / 2;                       // K % 16 == 0
-    uint16_t* row1 = (uint16_t*)(x8 + (size_t)m * K);
-    uint16_t* row2 = (uint16_t*)(x8 + (size_t)(MP + m) * K);
+    const int nvec = K / 8;                        // K % 16 == 0
+    uint2* row1 = (uint2*)(x8 + (size_t)m * K);
+    uint2* row2 = (uint2*)(x8 + (size_t)(MP + m) * K);
     if (m >= M) {
-        for (int i = threadIdx.x; i < pairs; i += blockDim.x) { row1[i] = 0; row2[i] = 0; }
+        for (int i = threadIdx.x; i < nvec; i += blockDim.x) { row1[i] = make_uint2(0u, 0u); row2[i] = make_uint2(0u, 0u); }
         if (threadIdx.x == 0) xscale[m] = 0.f;
         return;
     }
-    const uint32_t* xr = (const uint32_t*)(x + (size_t)m * K);
+    const uint4* xr = (const uint4*)(x + (size_t)m * K);
+    const bool in_regs = nvec <= SPLIT_KEEP * 256;
+    uint4 keep[SPLIT_KEEP];
     float amax = 0.f;
     int bad = 0;
-    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
-        const uint32_t w = xr[i];
-        const float a = fabsf(__uint_as_float(w << 16)), b = fabsf(__uint_as_float(w & 0xFFFF0000u));
-        bad |= !(a <= 3.4e38f) | !(b <= 3.4e38f);   // inf or NaN
-        amax = fmaxf(amax, fmaxf(a, b));
+    auto look = [&](const uint4& w) {
+        const uint32_t in[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float a = fabsf(__uint_as_float(in[i] << 16)), b = fabsf(__uint_as_float(in[i] & 0xFFFF0000u));
+            bad |= !(a <= 3.4e38f) | !(b <= 3.4e38f);   // inf or NaN
+            amax = fmaxf(amax, fmaxf(a, b));
+        }
+    };
+    if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < SPLIT_KEEP; j++) {
+            const int i = threadIdx.x + 256 * j;
+            keep[j] = i < nvec ? xr[i] : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int j = 0; j < SPLIT_KEEP; j++) look(keep[j]);
+    } else {
+        for (int i = threadIdx.x; i < nvec; i += blockDim.x) look(xr[i]);
     }
     if (threadIdx.x == 0) bad_s = 0;
     __syncthreads();
@@ -123,15 +156,14 @@ split_activations_kernel(uint8_t* __restrict__ x8, float* __restrict__ xscale,
     const float a = __uint_as_float((uint32_t)(e - 7 + 127) << 23);
     const float inv = __uint_as_float((uint32_t)(7 - e + 127) << 23);
     if (threadIdx.x == 0) xscale[m] = non_finite ? __uint_as_float(0x7FC00000u) : a;
-    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
-        const uint32_t w = xr[i];
-        const float v0 = __uint_as_float(w << 16) * inv, v1 = __uint_as_float(w & 0xFFFF0000u) * inv;
-        const uint32_t c1 = e4m3x2(v0, v1);
-        float f0, f1;
-        e4m3x2_to_f32(c1, f0, f1);
-        const uint32_t c2 = e4m3x2((v0 - f0) * 16.f, (v1 - f1) * 16.f);
-        row1[i] = non_finite ? 0 : (uint16_t)c1;
-        row2[i] = non_finite ? 0 : (uint16_t)c2;
+    if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < SPLIT_KEEP; j++) {
+            const int i = threadIdx.x + 256 * j;
+            if (i < nvec) split8(keep[j], inv, non_finite, row1[i], row2[i]);
+        }
+    } else {
+        for (int i = threadIdx.x; i < nvec; i += blockDim.x) split8(xr[i], inv, non_finite, row1[i], row2[i]);
     }
 }
 
@@ -294,9 +326,21 @@ __global__ void direct_finalize_kernel(uint16_t* __restrict__ y, const float* __
         const int first = first_cta_of(nb, p.num_kb, p.quota);
         const int last = ((nb + 1) * p.num_kb - 1) / p.quota;
         const float* src = partial + ((size_t)(nb * p.pieces) * p.MP + m) * WROWS + nl;
-        float s = src[0];
-        for (int pc = 1; pc <= last - first; pc++) s = __fadd_rn(s, src[(size_t)pc * p.MP * WROWS]);
-        const float v = fmaf(__fmul_rn(s, p.xscale[m]), scales ? scales[n] : 1.f, bias ? bias[n] : 0.f);
+        // the loads of up to four slots, the scales and the bias are independent and go out
+        // together; the sum keeps the slot order
+        const int np = last - first + 1;
+        const size_t pitch = (size_t)p.MP * WROWS;
+        const float p0 = src[0];
+        const float p1 = np > 1 ? src[pitch] : 0.f;
+        const float p2 = np > 2 ? src[2 * pitch] : 0.f;
+        const float p3 = np > 3 ? src[3 * pitch] : 0.f;
+        const float xs = p.xscale[m], sn = scales ? scales[n] : 1.f, bn = bias ? bias[n] : 0.f;
+        float s = p0;
+        if (np > 1) s = __fadd_rn(s, p1);
+        if (np > 2) s = __fadd_rn(s, p2);
+        if (np > 3) s = __fadd_rn(s, p3);
+        for (int pc = 4; pc < np; pc++) s = __fadd_rn(s, src[(size_t)pc * pitch]);
+        const float v = fmaf(__fmul_rn(s, xs), sn, bn);
         y[e] = (uint16_t)(pack_bf16(v, 0.f) & 0xFFFFu);
     }
 }
