@@ -17,12 +17,13 @@
 //
 // Operands are swapped as in the converter kernel of gemm_small.cu: MMA M = 128 weight rows,
 // MMA N = 2 * MP (MP = M rounded up to 16; columns [0, MP) hold the p1 sums, [MP, 2 MP) the p2
-// sums), K = 32 codes per instruction.  A unit is (128-row weight block, 128-code k-block); each
+// sums), K = 32 codes per instruction.  A unit is (128-row weight block, one or two 128-code k-blocks); each
 // CTA takes a contiguous run of units, writes fp32 partial sums per weight block it touched, and
 // a second kernel adds them in CTA order, applies a_m, s_n, b_n and rounds to bf16.
 //
-//   warp 0      TMA producer: 128 x 128 weight codes (16 KB) + 2 MP x 128 activation codes per unit,
-//               both with the 128-byte swizzle, into a ring of 4 (MP = 128) to 10 (MP = 16) slots
+//   warp 0      TMA producer: 128 x 128 weight codes (16 KB) + 2 MP x 128 activation codes per
+//               k-block, both with the 128-byte swizzle; a ring slot holds one k-block, or two
+//               when MP <= 32 (ring of 4 to 7 slots)
 //   warp 1      TMEM allocation; one lane issues the MMAs (128 x 2MP x 32) and commits
 //   warps 2-5   epilogue: TMEM -> p1 sum + p2 sum / 16 -> fp32 partial slot
 // Every wait is bounded.  A non-finite activation makes its whole output row NaN.
@@ -35,10 +36,14 @@ constexpr int WROWS = 128;                  // weight rows per block = MMA M
 constexpr int A_BYTES = WROWS * BKC;        // 16 KB
 constexpr int MAX_STAGES = 10;
 constexpr int RING_BYTES = 212992;          // 208 KB of operand ring
-__host__ __device__ constexpr int stage_bytes(int MP) { return A_BYTES + 2 * MP * BKC; }
-__host__ __device__ constexpr int num_stages(int MP) {
-    return RING_BYTES / stage_bytes(MP) < MAX_STAGES ? RING_BYTES / stage_bytes(MP) : MAX_STAGES;
+// A ring slot holds `ukb` k-blocks (weight tiles first, then the activation tiles): with few
+// activation rows a k-block is only 16-20 KB and four tiny MMAs, less than the MMA warp's wait /
+// issue / commit round, so two k-blocks share a round.
+__host__ __device__ constexpr int stage_bytes(int MP, int ukb) { return ukb * (A_BYTES + 2 * MP * BKC); }
+__host__ __device__ constexpr int num_stages(int MP, int ukb) {
+    return RING_BYTES / stage_bytes(MP, ukb) < MAX_STAGES ? RING_BYTES / stage_bytes(MP, ukb) : MAX_STAGES;
 }
+__host__ __device__ constexpr int unit_kblocks(int MP) { return MP <= 32 ? 2 : 1; }
 constexpr int THREADS = 192;                // producer, MMA, four epilogue warps
 constexpr int ACC_COLS = 256;               // TMEM columns per accumulator (2 MP <= 256)
 constexpr int TMEM_COLS = 2 * ACC_COLS;
@@ -50,7 +55,8 @@ struct DirectParams {
     float* partial;       // [n_blocks][pieces][MP][128] fp32
     const float* xscale;  // a_m, MP floats
     int M, MP, N, K;
-    int n_blocks, num_kb;
+    int n_blocks, num_kb; // num_kb: units along K (each `ukb` k-blocks of 128 codes)
+    int ukb, k_blocks;    // k-blocks per unit; k-blocks in all (the last unit may hold fewer)
     int total;            // n_blocks * num_kb units
     int quota;            // units per CTA
     int pieces;           // partial slots per weight block
@@ -191,8 +197,9 @@ linear_small_m_direct_kernel(const __grid_constant__ CUtensorMap map_w, const __
     Shared* sh = (Shared*)(smem_raw + (tiles - raw) + RING_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* abort_flag = &sh->abort_flag;
-    const uint32_t STAGES = (uint32_t)num_stages(p.MP), STAGE_BYTES = (uint32_t)stage_bytes(p.MP);
+    const uint32_t STAGES = (uint32_t)num_stages(p.MP, p.ukb), STAGE_BYTES = (uint32_t)stage_bytes(p.MP, p.ukb);
     const uint32_t NP = 2u * (uint32_t)p.MP;           // MMA N: p1 columns, then p2 columns
+    const uint32_t X_OFF = (uint32_t)p.ukb * A_BYTES, X_BYTES = NP * BKC;
     // the finalising kernel may be scheduled now; it waits for this grid before it reads
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
@@ -231,9 +238,12 @@ linear_small_m_direct_kernel(const __grid_constant__ CUtensorMap map_w, const __
                         return false;
                     const uint32_t dst = tiles + stage * STAGE_BYTES;
                     const uint32_t fbar = tc::smem_u32(&sh->full[stage]);
-                    tc::mbar_arrive_expect_tx(fbar, A_BYTES + NP * BKC);
-                    tc::tma_load_2d(dst, &map_w, fbar, kb * BKC, nb * WROWS);
-                    tc::tma_load_2d(dst + A_BYTES, &map_x, fbar, kb * BKC, 0);
+                    const int k0 = kb * p.ukb, nk = min(p.ukb, p.k_blocks - k0);
+                    tc::mbar_arrive_expect_tx(fbar, nk * (A_BYTES + X_BYTES));
+                    for (int j = 0; j < nk; j++) {
+                        tc::tma_load_2d(dst + j * A_BYTES, &map_w, fbar, (k0 + j) * BKC, nb * WROWS);
+                        tc::tma_load_2d(dst + X_OFF + j * X_BYTES, &map_x, fbar, (k0 + j) * BKC, 0);
+                    }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
                 return true;
@@ -258,11 +268,15 @@ linear_small_m_direct_kernel(const __grid_constant__ CUtensorMap map_w, const __
                         return false;
                     tc::tc_fence_after();
                     const uint32_t a_addr = tiles + stage * STAGE_BYTES;
-                    const uint64_t a_desc = tc::smem_desc_k_sw128(a_addr);
-                    const uint64_t b_desc = tc::smem_desc_k_sw128(a_addr + A_BYTES);
+                    const int nk = min(p.ukb, p.k_blocks - kb * p.ukb);
+                    for (int j = 0; j < nk; j++) {
+                        const uint64_t a_desc = tc::smem_desc_k_sw128(a_addr + j * A_BYTES);
+                        const uint64_t b_desc = tc::smem_desc_k_sw128(a_addr + X_OFF + j * X_BYTES);
 #pragma unroll
-                    for (int k = 0; k < 4; k++)      // four 32-byte k-steps of 32 codes
-                        tc::tc_mma_f8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        for (int k = 0; k < 4; k++)      // four 32-byte k-steps of 32 codes
+                            tc::tc_mma_f8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc,
+                                          (kb > kb0 || j > 0 || k > 0) ? 1u : 0u);
+                    }
                     tc::tc_commit(tc::smem_u32(&sh->empty[stage]));
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -345,12 +359,14 @@ __global__ void direct_finalize_kernel(uint16_t* __restrict__ y, const float* __
     }
 }
 
-struct Geometry { int MP, n_blocks, num_kb, total, grid, quota, pieces; size_t partial_bytes, x8_bytes; };
+struct Geometry { int MP, n_blocks, num_kb, ukb, k_blocks, total, grid, quota, pieces; size_t partial_bytes, x8_bytes; };
 Geometry geometry(size_t M, size_t N, size_t K, int device) {
     Geometry g;
     g.MP = (int)((M + 15) / 16 * 16);
     g.n_blocks = (int)((N + WROWS - 1) / WROWS);
-    g.num_kb = (int)((K + BKC - 1) / BKC);
+    g.ukb = unit_kblocks(g.MP);
+    g.k_blocks = (int)((K + BKC - 1) / BKC);
+    g.num_kb = (g.k_blocks + g.ukb - 1) / g.ukb;
     g.total = g.n_blocks * g.num_kb;
     g.grid = nvq_sm_count(device);
     if (g.grid > g.total) g.grid = g.total;
@@ -391,6 +407,8 @@ nvq_status nvq_linear_launch_small_m_direct(uint16_t* d_y, const uint16_t* d_x, 
     p.K = (int)K;
     p.n_blocks = g.n_blocks;
     p.num_kb = g.num_kb;
+    p.ukb = g.ukb;
+    p.k_blocks = g.k_blocks;
     p.total = g.total;
     p.quota = g.quota;
     p.pieces = g.pieces;
