@@ -210,6 +210,34 @@ def measure_extras(dev, st, rank, world, dist, local):
         e1.sync()
         return e0.elapsed_ms(e1) / (rounds * k)
 
+    def timed_graph(fn, sets, rounds=4):
+        """The same rotation recorded once into a CUDA graph (one call per buffer set) and replayed:
+        the device time of a call without the host's launch cost, as a serving loop would issue it."""
+        import ctypes as C
+        from novann_b200._lib import check, lib
+        from novann_b200.device import _sptr
+        for args_ in sets:
+            fn(*args_)
+        st.sync()
+        check(lib().nvq_graph_begin_capture(dev, _sptr(st)))
+        try:
+            for args_ in sets:
+                fn(*args_)
+        finally:
+            h = C.c_void_p()
+            check(lib().nvq_graph_end_capture(dev, _sptr(st), C.byref(h)))
+        graph = C.c_void_p(h.value)
+        check(lib().nvq_graph_launch(dev, graph, _sptr(st)))
+        st.sync()
+        e0, e1 = Event(dev), Event(dev)
+        e0.record(st)
+        for _ in range(rounds):
+            check(lib().nvq_graph_launch(dev, graph, _sptr(st)))
+        e1.record(st)
+        e1.sync()
+        check(lib().nvq_graph_destroy(dev, graph))
+        return e0.elapsed_ms(e1) / (rounds * len(sets))
+
     def n_sets_for(set_bytes):
         return max(2, int(np.ceil((512 << 20) / set_bytes)) + 1)
 
@@ -309,16 +337,44 @@ def measure_extras(dev, st, rank, world, dist, local):
                                                                  stream=st), lsets)
     t_warm = timed_rotating(lambda dxx, dw, ws, dy: F.linear_q_device(dy, dxx, dw, "e4m3", dss, dbb, ms_, nn, kk,
                                                                       ws, stream=st), lsets[:1], rounds=20)
+    t_graph = timed_graph(lambda dxx, dw, ws, dy: F.linear_q_device(dy, dxx, dw, "e4m3", dss, dbb, ms_, nn, kk, ws,
+                                                                    stream=st), lsets)
     F.check_device_errors(dev)
     out["linear_fp8_few_rows"] = {"M": ms_, "N": nn, "K": kk, "us": t * 1e3, "us_l2_warm": t_warm * 1e3,
+                                  "us_cuda_graph": t_graph * 1e3,
                                   "weight_gbs": nn * kk / t / 1e6,
-                                  "note": "M <= 128: codes read once (1 byte per weight), expanded in shared "
-                                          "memory, operands swapped, split along K with a deterministic "
-                                          "reduction kernel; weight_gbs = code bytes / time"}
+                                  "note": "M <= 128: codes read once (1 byte per weight) and fed to "
+                                          "kind::f8f6f4 MMAs as they are, activations carried as two rows "
+                                          "of E4M3 codes, operands swapped, split along K with a "
+                                          "deterministic reduction kernel; weight_gbs = code bytes / time; us = eager "
+                                          "calls from Python (three launches, host-bound), us_cuda_graph = the "
+                                          "same rotation replayed from one CUDA graph"}
     for bufs in lsets:
         for b_ in bufs:
             b_.free()
     ws8.free()
+    # the same kernel on a weight far larger than L2 (an 8192 x 28672 projection, 235 MB of codes):
+    # the streaming rate without the fixed cost of a 16 MB call; two rotating weights
+    nl, kl = 28672, 8192
+    wl = rng.integers(0, 0x7F, (nl, kl), dtype=np.uint64).astype(np.uint8)
+    xl, _, _ = workloads.linear_inputs(ms_, 8, kl, seed=rank)
+    dsl = DeviceBuffer.from_numpy(np.full(nl, 1e-3, np.float32), dev)
+    big = [(DeviceBuffer.from_numpy(xl, dev), DeviceBuffer.from_numpy(wl, dev),
+            DeviceBuffer(64 << 20, dev), DeviceBuffer(ms_ * nl * 2, dev))   # partial sums need < 8 MB
+           for _ in range(2)]
+    t = timed_rotating(lambda dxx, dw, ws, dy: F.linear_q_device(dy, dxx, dw, "e4m3", dsl, None, ms_, nl, kl, ws,
+                                                                 stream=st), big, rounds=5)
+    F.check_device_errors(dev)
+    peak_hbm, _ = _peaks()
+    out["linear_fp8_few_rows_large"] = {"M": ms_, "N": nl, "K": kl, "us": t * 1e3,
+                                        "weight_gbs": nl * kl / t / 1e6,
+                                        "frac_of_measured_hbm_peak": nl * kl / t / 1e6 / peak_hbm,
+                                        "note": "three kernels per call (activation split, stream, reduction) "
+                                                "in the time; 235 MB of codes per call from DRAM"}
+    for bufs in big:
+        for b_ in bufs:
+            b_.free()
+    dsl.free()
     # ---- FP8-weight Conv2d forward as an implicit GEMM: x fp32 [128 / world, 64, 56, 56], 3x3, pad 1,
     # 128 output channels (a ResNet-style block); NCHW fp32 in and out, everything on the device
     from novann_b200 import _lib as _l
