@@ -110,6 +110,9 @@ split_activations_kernel(uint8_t* __restrict__ x8, float* __restrict__ xscale,
                          const uint16_t* __restrict__ x, int M, int MP, int K) {
     __shared__ float red[8];
     __shared__ int bad_s;
+    // the streaming kernel may be scheduled now: it sets itself up and starts fetching weight
+    // codes on the SMs this kernel leaves free, and waits for this grid before it reads x8
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int m = blockIdx.x;
     const int nvec = K / 8;                        // K % 16 == 0
     uint2* row1 = (uint2*)(x8 + (size_t)m * K);
@@ -225,25 +228,43 @@ linear_small_m_direct_kernel(const __grid_constant__ CUtensorMap map_w, const __
     __syncthreads();
     tc::tc_fence_after();
     const uint32_t tmem_base = sh->tmem_base;
-    // the activation codes come from the splitting kernel launched just before this one
-    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
+            // The weight does not depend on the kernel that splits the activations, which may
+            // still be running: the first ring of weight tiles is requested before the wait for
+            // that kernel, the activation tiles of those slots after it.
+            uint32_t early = 0;
             for_each_segment(p, [&](int nb, int kb0, int kb1, int) {
                 for (int kb = kb0; kb < kb1; kb++) {
-                    if (!tc::mbar_wait(tc::smem_u32(&sh->empty[stage]), phase ^ 1, abort_flag, ERR_PRODUCER))
-                        return false;
+                    if (early == STAGES) return false;
+                    const uint32_t dst = tiles + early * STAGE_BYTES;
+                    const uint32_t fbar = tc::smem_u32(&sh->full[early]);
+                    const int k0 = kb * p.ukb, nk = min(p.ukb, p.k_blocks - k0);
+                    tc::mbar_arrive_expect_tx(fbar, nk * (A_BYTES + X_BYTES));
+                    for (int j = 0; j < nk; j++)
+                        tc::tma_load_2d(dst + j * A_BYTES, &map_w, fbar, (k0 + j) * BKC, nb * WROWS);
+                    early++;
+                }
+                return true;
+            });
+            asm volatile("griddepcontrol.wait;" ::: "memory");   // x8 is complete and visible
+            uint32_t stage = 0, phase = 0, unit = 0;
+            for_each_segment(p, [&](int nb, int kb0, int kb1, int) {
+                for (int kb = kb0; kb < kb1; kb++, unit++) {
                     const uint32_t dst = tiles + stage * STAGE_BYTES;
                     const uint32_t fbar = tc::smem_u32(&sh->full[stage]);
                     const int k0 = kb * p.ukb, nk = min(p.ukb, p.k_blocks - k0);
-                    tc::mbar_arrive_expect_tx(fbar, nk * (A_BYTES + X_BYTES));
-                    for (int j = 0; j < nk; j++) {
-                        tc::tma_load_2d(dst + j * A_BYTES, &map_w, fbar, (k0 + j) * BKC, nb * WROWS);
-                        tc::tma_load_2d(dst + X_OFF + j * X_BYTES, &map_x, fbar, (k0 + j) * BKC, 0);
+                    if (unit >= early) {
+                        if (!tc::mbar_wait(tc::smem_u32(&sh->empty[stage]), phase ^ 1, abort_flag, ERR_PRODUCER))
+                            return false;
+                        tc::mbar_arrive_expect_tx(fbar, nk * (A_BYTES + X_BYTES));
+                        for (int j = 0; j < nk; j++)
+                            tc::tma_load_2d(dst + j * A_BYTES, &map_w, fbar, (k0 + j) * BKC, nb * WROWS);
                     }
+                    for (int j = 0; j < nk; j++)
+                        tc::tma_load_2d(dst + X_OFF + j * X_BYTES, &map_x, fbar, (k0 + j) * BKC, 0);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
                 return true;
