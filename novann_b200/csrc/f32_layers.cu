@@ -1023,11 +1023,12 @@ extern "C" nvq_status nvq_conv2d_fwd_q(float* d_out, const float* d_x, const uin
     const size_t L = (size_t)N * g.OH * g.OW;
     const int kq = w_fmt == NVQ_E2M1_B32 ? 32 : 16;          // FP4 blocks are 32 columns
     const int Kpad = (C * KH * KW + kq - 1) / kq * kq;
-    // Implicit GEMM (no patch matrix): stride 1, zero padding, channels in blocks of 64, output
+    // Implicit GEMM (no patch matrix): strides 1 or 2, zero padding, channels in blocks of 64, output
     // rows of at most 128 positions.  d_col_bf16 holds x as bf16 NHWC, d_workspace the weight with
     // its columns reordered to (kh, kw, c).  NVQ_CONV_MODE=explicit forces the patch-matrix path.
     const char* cmode = getenv("NVQ_CONV_MODE");
-    const bool implicit_ok = sh == 1 && sw == 1 && mode == NVQ_PAD_ZEROS && C % 64 == 0 && g.OW <= 128 &&
+    const bool implicit_ok = sh >= 1 && sh <= 2 && sw >= 1 && sw <= 2 && mode == NVQ_PAD_ZEROS && C % 64 == 0 &&
+                             g.OW <= 128 &&
                              L < (1u << 31) && (size_t)Cout * C * KH * KW < (1u << 31) &&
                              workspace_bytes >= (size_t)Cout * C * KH * KW * 2 && d_workspace &&
                              (size_t)H * W <= (size_t)g.OH * g.OW * KH * KW &&
@@ -1057,7 +1058,7 @@ extern "C" nvq_status nvq_conv2d_fwd_q(float* d_out, const float* d_x, const uin
         // FP4 block scales are already in the expanded weight; FP8 channel scales go to the epilogue
         return nvq_conv_launch_pair_implicit(d_out, d_col_bf16, (const uint16_t*)d_workspace,
                                              w_fmt == NVQ_E2M1_B32 ? nullptr : d_w_scales, d_bias, N, C, H, W,
-                                             Cout, KH, KW, ph, pw, device, st);
+                                             Cout, KH, KW, ph, pw, sh, sw, device, st);
     }
     const bool tiled = C * KH * KW <= kImLut && KH < 256 && KW < 256 && C < 65536 && L < (1u << 31);
     if (tiled) {

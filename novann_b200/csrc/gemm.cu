@@ -307,7 +307,8 @@ nvq_status nvq_make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, u
 }
 
 nvq_status nvq_make_tmap_nhwc(CUtensorMap* map, const void* base, uint64_t N, uint64_t H, uint64_t W,
-                              uint64_t C, uint32_t box_w, uint32_t box_h) {
+                              uint64_t C, uint32_t box_w, uint32_t box_h, uint32_t stride_w,
+                              uint32_t stride_h) {
     nvq_status s0 = ensure_encode();
     if (s0 != NVQ_OK) return s0;
     NVQ_REQUIRE(nvq_aligned(base, 16), "tensor base must be 16-byte aligned");
@@ -316,8 +317,12 @@ nvq_status nvq_make_tmap_nhwc(CUtensorMap* map, const void* base, uint64_t N, ui
                 "NHWC map: box %u x %u does not fit a 128-row operand tile", box_w, box_h);
     cuuint64_t dims[4] = {C, W, H, N};
     cuuint64_t strides[3] = {C * 2, W * C * 2, H * W * C * 2};
-    cuuint32_t box[4] = {64, box_w, box_h, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
+    NVQ_REQUIRE(stride_w >= 1 && stride_w <= 8 && stride_h >= 1 && stride_h <= 8 &&
+                    box_w * stride_w <= 256 && box_h * stride_h <= 256,
+                "NHWC map: strides %u x %u out of range for a box of %u x %u", stride_w, stride_h, box_w, box_h);
+    // with a traversal stride s the box extent is given in pixels walked: n loaded pixels = n * s
+    cuuint32_t box[4] = {64, box_w * stride_w, box_h * stride_h, 1};
+    cuuint32_t estr[4] = {1, stride_w, stride_h, 1};
     CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides,
                           box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

@@ -21,7 +21,7 @@ struct LinearParams {
     int conv_bw, conv_bh;     // box (conv_bw = OW)
     int conv_th;              // boxes per image = ceil(OH / conv_bh)
     int conv_images, conv_OH, conv_OW;
-    int conv_KW, conv_ph, conv_pw;
+    int conv_KW, conv_ph, conv_pw, conv_sh;
     int conv_cpb;             // 64-channel blocks per filter tap = C / 64
 };
 
@@ -68,7 +68,7 @@ nvq_status nvq_linear_launch_small_m(uint16_t* d_y, const uint16_t* d_x, const u
 // KH*KW*C, columns ordered (kh, kw, c)), out fp32 NCHW holding bf16-rounded values.
 nvq_status nvq_conv_launch_pair_implicit(float* d_out, const uint16_t* d_x_nhwc, const uint16_t* d_w,
                                          const float* d_scales, const float* d_bias, int N, int C,
-                                         int H, int W, int Cout, int KH, int KW, int ph, int pw,
+                                         int H, int W, int Cout, int KH, int KW, int ph, int pw, int sh, int sw,
                                          int device, cudaStream_t st);
 
 #ifdef __CUDACC__

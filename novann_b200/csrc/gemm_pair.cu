@@ -178,9 +178,10 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                         if (rank == 0)
                             tc::mbar_arrive_expect_tx(tc::smem_u32(&sh->full[stage]),
                                                       2 * (a_bytes + rows_b * BK * 2));
-                        // input pixel of output (oh, ow) under tap (kh, kw): (oh + kh - ph, ow + kw - pw);
+                        // input pixel of output (oh, ow) under tap (kh, kw): (oh * sh + kh - ph, ow * sw + kw - pw),
+                        // the strides being the tensor map's traversal strides;
                         // pixels outside the image (and images past the last) read as zeros
-                        tc::tma_load_4d_pair(dst, &map_a, lead_full, c0, kw - p.conv_pw, oh0 + kh - p.conv_ph, img);
+                        tc::tma_load_4d_pair(dst, &map_a, lead_full, c0, kw - p.conv_pw, oh0 * p.conv_sh + kh - p.conv_ph, img);
                         tc::tma_load_2d_pair(dst + A_BYTES, &map_b, lead_full, kb * BKE, n0);
                         if (rows_b == 128)
                             tc::tma_load_2d_pair(dst + A_BYTES + B_BYTES / 2, &map_b, lead_full, kb * BKE, n0 + 64);
@@ -509,9 +510,9 @@ static nvq_status launch_pair(uint16_t* d_y, const void* d_x, const void* d_w,
 
 static nvq_status launch_implicit_conv(float* d_out, const uint16_t* d_x_nhwc, const uint16_t* d_w,
                                        const float* d_scales, const float* d_bias, int N, int C, int H,
-                                       int W, int Cout, int KH, int KW, int ph, int pw, int device,
-                                       cudaStream_t st) {
-    const int OH = H + 2 * ph - KH + 1, OW = W + 2 * pw - KW + 1;
+                                       int W, int Cout, int KH, int KW, int ph, int pw, int sh, int sw,
+                                       int device, cudaStream_t st) {
+    const int OH = (H + 2 * ph - KH) / sh + 1, OW = (W + 2 * pw - KW) / sw + 1;
     NVQ_REQUIRE(OH > 0 && OW > 0 && OW <= 128 && C % 64 == 0 && Cout % 8 == 0,
                 "implicit convolution: needs OW <= 128, C %% 64 == 0, Cout %% 8 == 0");
     // box height: whole output rows, at most 128 positions, least padding over the image
@@ -524,7 +525,7 @@ static nvq_status launch_implicit_conv(float* d_out, const uint16_t* d_x_nhwc, c
     const int th = (OH + bh - 1) / bh;
     const size_t K = (size_t)KH * KW * C;
     CUtensorMap map_a, map_b;
-    nvq_status s = nvq_make_tmap_nhwc(&map_a, d_x_nhwc, N, H, W, C, OW, bh);
+    nvq_status s = nvq_make_tmap_nhwc(&map_a, d_x_nhwc, N, H, W, C, OW, bh, sw, sh);
     if (s != NVQ_OK) return s;
     s = nvq_make_tmap_2d(&map_b, d_w, Cout, K, 64, BK, 2, 1);
     if (s != NVQ_OK) return s;
@@ -548,7 +549,7 @@ static nvq_status launch_implicit_conv(float* d_out, const uint16_t* d_x_nhwc, c
     p.group_m = 8;
     p.conv_bw = OW; p.conv_bh = bh; p.conv_th = th;
     p.conv_images = N; p.conv_OH = OH; p.conv_OW = OW;
-    p.conv_KW = KW; p.conv_ph = ph; p.conv_pw = pw; p.conv_cpb = C / 64;
+    p.conv_KW = KW; p.conv_ph = ph; p.conv_pw = pw; p.conv_sh = sh; p.conv_cpb = C / 64;
     s = nvq_status_word(device, &p.status);
     if (s != NVQ_OK) return s;
     int tiles = p.m_blocks * p.n_blocks;
@@ -574,9 +575,9 @@ static nvq_status launch_implicit_conv(float* d_out, const uint16_t* d_x_nhwc, c
 nvq_status nvq_conv_launch_pair_implicit(float* d_out, const uint16_t* d_x_nhwc, const uint16_t* d_w,
                                          const float* d_scales, const float* d_bias, int N, int C,
                                          int H, int W, int Cout, int KH, int KW, int ph, int pw,
-                                         int device, cudaStream_t st) {
+                                         int sh, int sw, int device, cudaStream_t st) {
     return launch_implicit_conv(d_out, d_x_nhwc, d_w, d_scales, d_bias, N, C, H, W, Cout, KH, KW, ph, pw,
-                                device, st);
+                                sh, sw, device, st);
 }
 
 nvq_status nvq_linear_launch_pair(uint16_t* d_y, const uint16_t* d_x, const uint16_t* d_w,

@@ -294,7 +294,9 @@ __host__ __device__ constexpr uint32_t idesc_f16(uint32_t m, uint32_t n, uint32_
 // be 128) or linearly.
 // bf16 NHWC activation tensor (N, H, W, C), box = 64 channels x box_w x box_h pixels of one
 // image, 128-byte swizzle; out-of-range pixels (the zero padding of a convolution) read as 0
+// stride_w / stride_h: the box takes every stride-th pixel (a strided convolution's taps)
 nvq_status nvq_make_tmap_nhwc(CUtensorMap* map, const void* base, uint64_t N, uint64_t H, uint64_t W,
-                              uint64_t C, uint32_t box_w, uint32_t box_h);
+                              uint64_t C, uint32_t box_w, uint32_t box_h, uint32_t stride_w = 1,
+                              uint32_t stride_h = 1);
 nvq_status nvq_make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
                             uint32_t box_rows, uint32_t box_cols, int elem_bytes, int swizzle128);

@@ -408,6 +408,41 @@ def test_implicit_gemm_conv_equals_patch_matrix_conv_and_oracle(gpu, case, monke
 
 
 @pytest.mark.parametrize("case", [
+    (2, 64, 16, 16, 64, 3, 1, 2, 2),      # ResNet-style 3 x 3 stride 2: boxes of every second pixel
+    (3, 128, 15, 13, 72, 3, 1, 2, 2),     # odd sizes: the last strided pixel sits on the padding
+    (2, 64, 12, 20, 40, 3, 0, 2, 2),      # no padding
+    (2, 64, 9, 17, 24, 3, 1, 1, 2),       # stride 2 across only
+    (2, 64, 17, 9, 24, 5, 2, 2, 1),       # stride 2 down only, 5 x 5 taps
+    (37, 64, 28, 28, 128, 3, 1, 2, 2),    # several tiles per CTA pair
+])
+def test_strided_implicit_gemm_conv(gpu, case, monkeypatch):
+    """Strides of 2: the 4-D TMA box walks the NHWC tensor with a traversal stride, so the box of
+    a filter tap still lands as consecutive operand rows.  Against the patch-matrix path of the
+    same call and against the oracle."""
+    n, c, h, w, cout, k, p, sh, sw = case
+    rng = np.random.default_rng(sum(case))
+    x = rng.standard_normal((n, c, h, w)).astype(np.float32)
+    wt = (rng.standard_normal((cout, c, k, k)) * 0.05).astype(np.float32)
+    b = (rng.standard_normal(cout) * 0.1).astype(np.float32)
+    codes, scales = quant.quantize_weight(wt.reshape(cout, -1), "e4m3", gpu)
+    monkeypatch.delenv("NVQ_CONV_MODE", raising=False)
+    y_imp = F.conv2d_q_host(x, codes, scales, b, (k, k), (sh, sw), (p, p), "zeros", "e4m3", gpu)
+    monkeypatch.setenv("NVQ_CONV_MODE", "explicit")
+    y_exp = F.conv2d_q_host(x, codes, scales, b, (k, k), (sh, sw), (p, p), "zeros", "e4m3", gpu)
+    oh, ow = (h + 2 * p - k) // sh + 1, (w + 2 * p - k) // sw + 1
+    assert y_imp.shape == y_exp.shape == (n, cout, oh, ow)
+    assert o.max_abs_rel(y_imp, y_exp) <= 2.0 ** -8
+    assert np.mean(y_imp == y_exp) > 0.9
+    wd = o.dequantize_fp8(codes, 1.0, "e4m3").reshape(cout, c, k, k) * scales.reshape(-1, 1, 1, 1)
+    xb = o.bf16_bits_to_f32(o.f32_to_bf16_bits(x))
+    col, oh2, ow2 = o.im2col(xb, k, k, sh, sw, p, p)
+    ref = (wd.reshape(cout, -1).astype(np.float64) @ col.astype(np.float64) + b.reshape(-1, 1))
+    ref = ref.reshape(cout, n, oh2, ow2).transpose(1, 0, 2, 3)
+    assert o.max_abs_rel(y_imp, ref) <= 1e-2
+    F.check_device_errors(gpu)
+
+
+@pytest.mark.parametrize("case", [
     (2, 64, 10, 10, 32, 3, 1, 1),      # implicit GEMM (stride 1, C % 64 == 0)
     (3, 128, 7, 9, 72, 3, 1, 1),       # implicit, two channel blocks, odd CTA-tile count
     (2, 16, 9, 9, 24, 3, 2, 1),        # patch-matrix path (stride 2, C = 16): kpad = 160
