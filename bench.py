@@ -356,7 +356,7 @@ def measure_extras(dev, st, rank, world, dist, local):
     # the same kernel on a weight far larger than L2 (an 8192 x 28672 projection, 235 MB of codes):
     # the streaming rate without the fixed cost of a 16 MB call; two rotating weights
     nl, kl = 28672, 8192
-    wl = rng.integers(0, 0x7F, (nl, kl), dtype=np.uint64).astype(np.uint8)
+    wl = np.tile(rng.integers(0, 0x7F, (nl // 8, kl), dtype=np.uint8), (8, 1))   # values do not matter here
     xl, _, _ = workloads.linear_inputs(ms_, 8, kl, seed=rank)
     dsl = DeviceBuffer.from_numpy(np.full(nl, 1e-3, np.float32), dev)
     big = [(DeviceBuffer.from_numpy(xl, dev), DeviceBuffer.from_numpy(wl, dev),
