@@ -313,8 +313,8 @@ nvq_status nvq_make_tmap_nhwc(CUtensorMap* map, const void* base, uint64_t N, ui
     if (s0 != NVQ_OK) return s0;
     NVQ_REQUIRE(nvq_aligned(base, 16), "tensor base must be 16-byte aligned");
     NVQ_REQUIRE(C % 64 == 0, "NHWC map: channels (%llu) must be a multiple of 64", (unsigned long long)C);
-    NVQ_REQUIRE(box_w >= 1 && box_h >= 1 && box_w <= 256 && box_h <= 256 && box_w * box_h <= 128,
-                "NHWC map: box %u x %u does not fit a 128-row operand tile", box_w, box_h);
+    NVQ_REQUIRE(box_w >= 1 && box_h >= 1 && box_w <= 256 && box_h <= 256 && box_w * box_h <= 256,
+                "NHWC map: box %u x %u does not fit a 256-row operand tile", box_w, box_h);
     cuuint64_t dims[4] = {C, W, H, N};
     cuuint64_t strides[3] = {C * 2, W * C * 2, H * W * C * 2};
     NVQ_REQUIRE(stride_w >= 1 && stride_w <= 8 && stride_h >= 1 && stride_h <= 8 &&

@@ -98,6 +98,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
         "l"(map), "r"(bar), "r"(x), "r"(y)
         : "memory");
 }
+// 4-D tiled load (channels, x, y, image) into this CTA's shared memory
+__device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar,
+                                            int c, int w, int h, int n) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_dst),
+        "l"(map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n)
+        : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }

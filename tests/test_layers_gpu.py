@@ -397,6 +397,13 @@ def test_implicit_gemm_conv_equals_patch_matrix_conv_and_oracle(gpu, case, monke
     # both are bf16-rounded: equal up to one bf16 ulp where the fp32 sums differ in their last bits
     assert o.max_abs_rel(y_imp, y_exp) <= 2.0 ** -8
     assert np.mean(y_imp == y_exp) > 0.9
+    # both implicit kernels, whichever the dispatch picks: the CTA-pair kernel and (for at most
+    # 128 output channels) the operand-swapped kernel
+    for forced in ("pair", "swapped"):
+        monkeypatch.setenv("NVQ_CONV_MODE", forced)
+        y_f = F.conv2d_q_host(x, codes, scales, b, (k, k), (1, 1), (p, p), "zeros", "e4m3", gpu)
+        assert o.max_abs_rel(y_f, y_exp) <= 2.0 ** -8, forced
+        assert np.mean(y_f == y_exp) > 0.9, forced
     # oracle: bf16 activations x dequantised weight, float64 accumulation
     wd = o.dequantize_fp8(codes, 1.0, "e4m3").reshape(cout, c, k, k) * scales.reshape(-1, 1, 1, 1)
     xb = o.bf16_bits_to_f32(o.f32_to_bf16_bits(x))
@@ -433,6 +440,11 @@ def test_strided_implicit_gemm_conv(gpu, case, monkeypatch):
     assert y_imp.shape == y_exp.shape == (n, cout, oh, ow)
     assert o.max_abs_rel(y_imp, y_exp) <= 2.0 ** -8
     assert np.mean(y_imp == y_exp) > 0.9
+    for forced in ("pair", "swapped"):
+        monkeypatch.setenv("NVQ_CONV_MODE", forced)
+        y_f = F.conv2d_q_host(x, codes, scales, b, (k, k), (sh, sw), (p, p), "zeros", "e4m3", gpu)
+        assert o.max_abs_rel(y_f, y_exp) <= 2.0 ** -8, forced
+        assert np.mean(y_f == y_exp) > 0.9, forced
     wd = o.dequantize_fp8(codes, 1.0, "e4m3").reshape(cout, c, k, k) * scales.reshape(-1, 1, 1, 1)
     xb = o.bf16_bits_to_f32(o.f32_to_bf16_bits(x))
     col, oh2, ow2 = o.im2col(xb, k, k, sh, sw, p, p)
