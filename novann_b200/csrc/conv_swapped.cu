@@ -14,7 +14,9 @@
 //              (64 channels x OW x bh pixels, traversal strides = the convolution's strides;
 //              pixels outside the image read as zeros) per k-block, ring of four 48 KB slots
 //   warp 1     TMEM allocation; one lane issues tcgen05.mma kind::f16 (128 x NP x 16) and commits
-//   warps 2-5  epilogue: TMEM -> scale, bias, bf16 rounding -> fp32 NCHW
+//   warps 2-5  epilogue: TMEM -> scale, bias, bf16 rounding -> swizzled staging buffer -> TMA store
+//              of 32-channel x 32-position boxes into the fp32 NCHW output (register stores for
+//              ragged tails and unaligned shapes)
 // One CTA per SM, cta_group::1, persistent over (image, row block, channel block) tiles.
 // Every wait is bounded.
 #include "gemm_common.cuh"
@@ -32,7 +34,8 @@ constexpr int STAGES = 4;
 constexpr int THREADS = 192;
 constexpr int ACC_COLS = 256;
 constexpr int TMEM_COLS = 2 * ACC_COLS;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 1024;
+constexpr int STG_BYTES = 32 * 128;          // one 32-channel x 32-position fp32 box of the output
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 1024 + 4 * 2 * STG_BYTES;
 
 enum { ERR_PRODUCER = 41, ERR_MMA_FULL = 42, ERR_MMA_TMEM = 43, ERR_EPILOGUE = 44 };
 
@@ -46,6 +49,7 @@ struct ConvParams {
     int cpb, KW, num_kb;   // channel blocks per tap, filter width, k-blocks per tile
     int ph, pw, sh;
     int num_tiles;
+    int tma_out;           // the epilogue stores whole 32 x 32 boxes by TMA (alignment permitting)
     int* status;
 };
 
@@ -71,7 +75,7 @@ __device__ __forceinline__ Tile tile_of(const ConvParams& p, int t) {
 
 __global__ void __launch_bounds__(THREADS, 1)
 conv_swapped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                    const ConvParams p) {
+                    const __grid_constant__ CUtensorMap map_out, const ConvParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = tc::smem_u32(smem_raw);
     const uint32_t tiles = (raw + 1023u) & ~1023u;
@@ -94,6 +98,7 @@ conv_swapped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         tc::mbar_fence_init();
         tc::tma_prefetch_desc(&map_w);
         tc::tma_prefetch_desc(&map_x);
+        if (p.tma_out) tc::tma_prefetch_desc(&map_out);
     }
     if (warp == 1) {
         tc::tmem_alloc(tc::smem_u32(&sh->tmem_base), TMEM_COLS);
@@ -163,6 +168,8 @@ conv_swapped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const int S = p.OH * p.OW;
         bool ok = true;
         int it = 0;
+        uint32_t chunk_no = 0;
+        const uint32_t stg_base = tiles + STAGES * STAGE_BYTES + 1024 + (uint32_t)(warp - 2) * 2 * STG_BYTES;
         for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x, it++) {
             const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
             const Tile tl = tile_of(p, t);
@@ -186,23 +193,45 @@ conv_swapped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 uint32_t r[32];
                 tc::tmem_ld_32x32(taddr + c, r);
                 tc::tmem_ld_wait();
-                if (!ch_ok) continue;
+                float v[32];
 #pragma unroll
-                for (int j = 0; j < 32; j += 4) {
-                    float v[4];
+                for (int j = 0; j < 32; j += 2) {
+                    const uint32_t pk = pack_bf16(fmaf(__uint_as_float(r[j]), sc, bi),
+                                                  fmaf(__uint_as_float(r[j + 1]), sc, bi));
+                    v[j] = __uint_as_float(pk << 16);                   // the bf16 result, widened again
+                    v[j + 1] = __uint_as_float(pk & 0xFFFF0000u);
+                }
+                if (p.tma_out && c + 32 <= valid) {
+                    // A thread's 32 positions are one 128-byte row of a 32-channel box.  Stored from
+                    // registers, every warp instruction would touch 32 different lines; the box goes
+                    // through a swizzled staging buffer and one TMA store instead (two buffers per
+                    // warp: the store of chunk i reads while chunk i + 1 is written).
+                    const uint32_t stg = stg_base + (uint32_t)(chunk_no & 1) * STG_BYTES;
+                    chunk_no++;
+                    if (lane == 0) tc::bulk_wait_read<1>();
+                    __syncwarp();
 #pragma unroll
-                    for (int q = 0; q < 4; q += 2) {
-                        const uint32_t pk = pack_bf16(fmaf(__uint_as_float(r[j + q]), sc, bi),
-                                                      fmaf(__uint_as_float(r[j + q + 1]), sc, bi));
-                        v[q] = __uint_as_float(pk << 16);               // the bf16 result, widened again
-                        v[q + 1] = __uint_as_float(pk & 0xFFFF0000u);
+                    for (int j8 = 0; j8 < 8; j8++)
+                        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(
+                                         stg + (uint32_t)lane * 128u + (uint32_t)((j8 ^ (lane & 7)) << 4)),
+                                     "f"(v[4 * j8]), "f"(v[4 * j8 + 1]), "f"(v[4 * j8 + 2]), "f"(v[4 * j8 + 3])
+                                     : "memory");
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        tc::tma_store_3d(&map_out, stg, tl.oh0 * p.OW + c, tl.cb * CH_ROWS + quarter * 32, tl.img);
+                        tc::bulk_commit();
                     }
-                    if (vec && c + j + 4 <= valid) {
-                        *reinterpret_cast<float4*>(plane + c + j) = make_float4(v[0], v[1], v[2], v[3]);
-                    } else {
+                } else if (ch_ok) {
 #pragma unroll
-                        for (int q = 0; q < 4; q++)
-                            if (c + j + q < valid) plane[c + j + q] = v[q];
+                    for (int j = 0; j < 32; j += 4) {
+                        if (vec && c + j + 4 <= valid) {
+                            *reinterpret_cast<float4*>(plane + c + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < 4; q++)
+                                if (c + j + q < valid) plane[c + j + q] = v[j + q];
+                        }
                     }
                 }
             }
@@ -210,6 +239,7 @@ conv_swapped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(tc::smem_u32(&sh->tmem_empty[acc]));
         }
+        if (lane == 0) tc::bulk_wait_all();     // the staging buffers are read, the boxes written
     }
 
     // ---------------------------------------------------------------- teardown
@@ -241,11 +271,21 @@ nvq_status nvq_conv_launch_swapped(float* d_out, const uint16_t* d_x_nhwc, const
         if (best < 0 || tiles < best) { best = tiles; bh = h; }
     }
     const size_t K = (size_t)KH * KW * C;
-    CUtensorMap map_w, map_x;
+    CUtensorMap map_w, map_x, map_out;
     nvq_status s = nvq_make_tmap_2d(&map_w, d_w, Cout, K, CH_ROWS, BK, 2, 1);
     if (s != NVQ_OK) return s;
     s = nvq_make_tmap_nhwc(&map_x, d_x_nhwc, N, H, W, C, OW, bh, sw, sh);
     if (s != NVQ_OK) return s;
+    // TMA stores need every box to start on a 16-byte boundary: planes and tiles of a multiple of
+    // four positions; otherwise the epilogue stores from registers
+    const size_t S = (size_t)OH * OW;
+    const bool tma_out = S % 4 == 0 && (bh * OW) % 4 == 0 && nvq_aligned(d_out, 16);
+    if (tma_out) {
+        s = nvq_make_tmap_nchw_out(&map_out, d_out, N, Cout, S);
+        if (s != NVQ_OK) return s;
+    } else {
+        map_out = map_w;   // never used
+    }
     static bool attr_set[64];
     if (!attr_set[device]) {
         NVQ_CUDA(cudaFuncSetAttribute(conv_swapped_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
@@ -261,6 +301,7 @@ nvq_status nvq_conv_launch_swapped(float* d_out, const uint16_t* d_x_nhwc, const
     p.cpb = C / 64; p.KW = KW; p.num_kb = KH * KW * (C / 64);
     p.ph = ph; p.pw = pw; p.sh = sh;
     p.num_tiles = N * p.th * p.c_blocks;
+    p.tma_out = tma_out ? 1 : 0;
     s = nvq_status_word(device, &p.status);
     if (s != NVQ_OK) return s;
     int grid = nvq_sm_count(device);
@@ -275,7 +316,7 @@ nvq_status nvq_conv_launch_swapped(float* d_out, const uint16_t* d_x_nhwc, const
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    NVQ_CUDA(cudaLaunchKernelEx(&cfg, conv_swapped_kernel, map_w, map_x, p));
+    NVQ_CUDA(cudaLaunchKernelEx(&cfg, conv_swapped_kernel, map_w, map_x, map_out, p));
     NVQ_LAUNCHED();
     return NVQ_OK;
 }

@@ -1056,10 +1056,9 @@ extern "C" nvq_status nvq_conv2d_fwd_q(float* d_out, const float* d_x, const uin
                 (uint16_t*)d_workspace, d_wq, d_w_scales, Cout, C, KH, KW, Kpad);
         NVQ_LAUNCHED();
         // FP4 block scales are already in the expanded weight; FP8 channel scales go to the epilogue.
-        // Few output channels and at least two channel blocks per tap (18+ k-blocks per tile): the
-        // operand-swapped kernel, measured 25 % faster there ([64, 128, 28, 28] -> 128: 0.039 against
-        // 0.049 ms) and no faster with nine k-blocks per tile.  NVQ_CONV_MODE=pair / swapped force one.
-        const bool want_swapped = cmode && cmode[0] == 's' ? true : (cmode && cmode[0] == 'p' ? false : C >= 128);
+        // At most 128 output channels: the operand-swapped kernel ([128, 64, 56, 56] -> 128: 0.106 ms
+        // against 0.139 ms on the pair kernel).  NVQ_CONV_MODE=pair / swapped force one.
+        const bool want_swapped = !(cmode && cmode[0] == 'p');
         if (Cout <= 128 && g.OW * sw <= 256 && want_swapped)
             return nvq_conv_launch_swapped(d_out, d_col_bf16, (const uint16_t*)d_workspace,
                                            w_fmt == NVQ_E2M1_B32 ? nullptr : d_w_scales, d_bias, N, C, H, W,

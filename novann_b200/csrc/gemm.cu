@@ -306,6 +306,23 @@ nvq_status nvq_make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, u
     return NVQ_OK;
 }
 
+// fp32 NCHW output seen as (image, channel, position): box = 32 channels x 32 positions of one
+// image, 128-byte rows with the 128-byte swizzle (the layout the storing warps write)
+nvq_status nvq_make_tmap_nchw_out(CUtensorMap* map, const void* base, uint64_t N, uint64_t C, uint64_t S) {
+    nvq_status s0 = ensure_encode();
+    if (s0 != NVQ_OK) return s0;
+    NVQ_REQUIRE(nvq_aligned(base, 16) && S % 4 == 0, "NCHW output map: base and plane size must be 16-byte multiples");
+    cuuint64_t dims[3] = {S, C, N};
+    cuuint64_t strides[2] = {S * 4, C * S * 4};
+    cuuint32_t box[3] = {32, 32, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box,
+                          estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) NVQ_FAIL(NVQ_ERR_CUDA, "cuTensorMapEncodeTiled (NCHW output) failed with %d", (int)r);
+    return NVQ_OK;
+}
+
 nvq_status nvq_make_tmap_nhwc(CUtensorMap* map, const void* base, uint64_t N, uint64_t H, uint64_t W,
                               uint64_t C, uint32_t box_w, uint32_t box_h, uint32_t stride_w,
                               uint32_t stride_h) {

@@ -107,6 +107,20 @@ __device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap
         "l"(map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n)
         : "memory");
 }
+// 3-D tiled store from this CTA's shared memory (bulk async group of the issuing thread)
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t smem_src, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map),
+        "r"(smem_src), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// until at most N of this thread's bulk groups still read their shared-memory source
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -307,5 +321,6 @@ __host__ __device__ constexpr uint32_t idesc_f16(uint32_t m, uint32_t n, uint32_
 nvq_status nvq_make_tmap_nhwc(CUtensorMap* map, const void* base, uint64_t N, uint64_t H, uint64_t W,
                               uint64_t C, uint32_t box_w, uint32_t box_h, uint32_t stride_w = 1,
                               uint32_t stride_h = 1);
+nvq_status nvq_make_tmap_nchw_out(CUtensorMap* map, const void* base, uint64_t N, uint64_t C, uint64_t S);
 nvq_status nvq_make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
                             uint32_t box_rows, uint32_t box_cols, int elem_bytes, int swizzle128);
