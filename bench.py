@@ -399,8 +399,9 @@ def measure_extras(dev, st, rank, world, dist, local):
     out["conv2d_fp8"] = {"N_per_gpu": cn, "C": cc, "HW": chw, "Cout": cco, "kernel": 3, "ms": t,
                          "tflops_per_gpu": 2.0 * crows * cco * ckp / t / 1e9,
                          "note": "nvq_conv2d_fwd_q: fp32 NCHW -> bf16 NHWC pass, weight expansion, tcgen05 "
-                                 "implicit GEMM with 4-D TMA boxes (no patch matrix), fp32 NCHW written by "
-                                 "the epilogue; all three kernels in the time"}
+                                 "implicit GEMM with 4-D TMA boxes (no patch matrix; output channels on the "
+                                 "MMA's M side), fp32 NCHW written by TMA stores from the epilogue; all "
+                                 "three kernels in the time"}
     for b_ in (d_xc, d_wc, d_col, d_yb, d_wsc, d_oc):
         b_.free()
     # ---- fp32 MLP train step, batch 128 / world rows per GPU, CUDA-graph replay
