@@ -335,7 +335,7 @@ nvq_status nvq_conv2d_bwd_f32(float* d_dw, float* d_db, float* d_dx, const float
  * C*KH*KW rounded up to 16 (nvq_conv2d_q_sizes), Cout per-channel scales; E2M1_B32 - Cout x kpad/2
  * packed bytes, kpad rounded up to 32, scales Cout x kpad/32 (the layout of nvq_quantize_fp4_b32).
  * out is fp32 NCHW holding the bf16-rounded results.  Cout % 8 == 0.
- *   Strides 1 or 2, zero padding, C % 64 == 0, OW <= 128: implicit GEMM.  x is rewritten as bf16 NHWC
+ *   Strides 1 or 2, zero padding, C % 64 == 0, OW * stride <= 256: implicit GEMM.  x is rewritten as bf16 NHWC
  *   (into d_col_bf16), the codes are expanded with their columns reordered to (kh, kw, c) (into
  *   d_workspace), and the CTA-pair tcgen05 kernel gathers its A operand with one 4-D TMA box per
  *   filter tap and 64-channel block (padding = out-of-range box = zeros) and writes NCHW fp32

@@ -1024,11 +1024,12 @@ extern "C" nvq_status nvq_conv2d_fwd_q(float* d_out, const float* d_x, const uin
     const int kq = w_fmt == NVQ_E2M1_B32 ? 32 : 16;          // FP4 blocks are 32 columns
     const int Kpad = (C * KH * KW + kq - 1) / kq * kq;
     // Implicit GEMM (no patch matrix): strides 1 or 2, zero padding, channels in blocks of 64, output
-    // rows of at most 128 positions.  d_col_bf16 holds x as bf16 NHWC, d_workspace the weight with
+    // rows of at most 256 positions (and at most 256 input pixels walked per row).  d_col_bf16 holds x as bf16 NHWC, d_workspace the weight with
     // its columns reordered to (kh, kw, c).  NVQ_CONV_MODE=explicit forces the patch-matrix path.
     const char* cmode = getenv("NVQ_CONV_MODE");
+    const bool pair_only = cmode && cmode[0] == 'p';      // the pair kernel's tiles hold 128 positions per CTA
     const bool implicit_ok = sh >= 1 && sh <= 2 && sw >= 1 && sw <= 2 && mode == NVQ_PAD_ZEROS && C % 64 == 0 &&
-                             g.OW <= 128 &&
+                             (g.OW <= 128 || (!pair_only && g.OW * sw <= 256)) &&
                              L < (1u << 31) && (size_t)Cout * C * KH * KW < (1u << 31) &&
                              workspace_bytes >= (size_t)Cout * C * KH * KW * 2 && d_workspace &&
                              (size_t)H * W <= (size_t)g.OH * g.OW * KH * KW &&

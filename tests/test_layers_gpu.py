@@ -376,6 +376,7 @@ def test_quant_mlp_inference_fused_relu(gpu):
     (4, 192, 7, 7, 128, 3, 1),        # three channel blocks
     (372, 64, 14, 14, 128, 3, 1),     # five tiles per CTA pair: all four accumulator buffers reused
     (3, 128, 10, 10, 96, 3, 1),       # at most 128 channels out, an even number of k-blocks
+    (2, 64, 6, 200, 16, 3, 1),        # output rows of 200 positions: one row per tile (swapped kernel only)
 ])
 def test_implicit_gemm_conv_equals_patch_matrix_conv_and_oracle(gpu, case, monkeypatch):
     """The tcgen05 implicit-GEMM convolution (4-D TMA boxes, no patch matrix) against the
