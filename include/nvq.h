@@ -337,9 +337,10 @@ nvq_status nvq_conv2d_bwd_f32(float* d_dw, float* d_db, float* d_dx, const float
  * out is fp32 NCHW holding the bf16-rounded results.  Cout % 8 == 0.
  *   Strides 1 or 2, zero padding, C % 64 == 0, OW * stride <= 256: implicit GEMM.  x is rewritten as bf16 NHWC
  *   (into d_col_bf16), the codes are expanded with their columns reordered to (kh, kw, c) (into
- *   d_workspace), and the CTA-pair tcgen05 kernel gathers its A operand with one 4-D TMA box per
- *   filter tap and 64-channel block (padding = out-of-range box = zeros) and writes NCHW fp32
- *   from its epilogue.  No patch matrix exists.
+ *   d_workspace), and a tcgen05 kernel gathers the input operand with one 4-D TMA box per
+ *   filter tap and 64-channel block (padding = out-of-range box = zeros, stride = the tensor
+ *   map's traversal stride) and writes NCHW fp32 from its epilogue (TMA stores where planes
+ *   and tiles are multiples of four positions).  No patch matrix exists.
  *   Otherwise: patches of x are gathered (padding mode applied) and rounded to bf16 into
  *   d_col_bf16 (rows x kpad, rows = N*OH*OW), the contraction is nvq_linear_fwd, and d_y_bf16
  *   (rows x Cout) is transposed to NCHW.
