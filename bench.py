@@ -1,7 +1,8 @@
 #!/usr/bin/env python
-"""Benchmark of the cast hot path (and, as extra fields, the FP8-weight Linear).
+"""Benchmark of the cast / quantised-Linear hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --case NAME [ints ...]          one small case of one kernel (profiler captures)
 
 One "step" is one pass of the cast sweep over one 1 Gi-element tensor resident in HBM:
 fp32->bf16, bf16->fp32, fp32->fp16, fp16->fp32 (6 algorithmic bytes per element each,
@@ -10,11 +11,17 @@ ranks (weak scaling: every rank owns its own 1 Gi-element shard, no collective).
 
 `e2e` repeats the same sweep through the host-array call that replaces
 ``ndarray.astype`` (NumPy array in pinned memory in, NumPy array out), so every byte
-crosses PCIe inside the timed region.
+crosses PCIe inside the timed region; next to it the same bytes are moved by plain copies
+with no kernel (the ceiling of that path) and the sweep is repeated on pageable arrays.
 
-`--impl reference` times the reference's CPU path for the same sweep on the host:
-``ndarray.astype`` for fp16 (NovaNN's own primitive, single-threaded by nature) and
-the CPU oracle's C restatement on all cores for bf16 (the reference has no bf16).
+The FP8-weight Linear (the other half of the headline metric), the smaller cast sizes, the
+float64 cast, the quantisers, the convolution and the training steps are measured in the
+same run and reported as flat keys; with more than one rank the data-parallel MLP step runs
+with its NCCL all-reduce over all ranks.
+
+`--impl reference` times the reference's CPU path for the same sweep on the host, at the
+same size: ``ndarray.astype`` for fp16 (NovaNN's own primitive, single-threaded by nature)
+and the CPU oracle's C restatement on all cores for bf16 (the reference has no bf16).
 """
 from __future__ import annotations
 
@@ -36,14 +43,25 @@ N_ELEMS = 1 << 30          # per rank
 TILE = 1 << 26             # seeded block the big tensor is tiled from
 BYTES_PER_ELEM_STEP = 24   # 4 directions x 6 B
 DIRECTIONS = [("f32", "bf16"), ("bf16", "f32"), ("f32", "f16"), ("f16", "f32")]
+MLP_PARAMS = 235146        # floats in the 784-256-128-10 gradient bucket
+
+
+def workload_config(n: int = N_ELEMS) -> dict:
+    """The workload both arms run; identical in the GPU line and the reference line."""
+    return {"workload": "cast sweep fp32->bf16->fp32->fp16->fp32, 1 Gi elements per GPU "
+                        "(BASELINE configs[1], largest size)",
+            "elements_per_gpu": n, "bytes_per_element_step": BYTES_PER_ELEM_STEP,
+            "l2": "inputs (4 GiB + 2 GiB) far exceed the 126 MB L2; no flush needed",
+            "input": "N(0,1) with 1% N(0,sigma=100) + 4096-element edge block; "
+                     "2^26-element seeded tile repeated 16x"}
 
 
 def _peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         d = json.load(open(p))
-        return float(d["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
 
 
 class ClockSampler:
@@ -104,132 +122,137 @@ def _dist_env():
     return rank, world, local
 
 
-def cpu_cast_sweep(n: int, reps: int = 1):
-    """The CPU path for the sweep on n elements; returns (seconds per sweep, detail)."""
-    from novann_b200 import workloads
-    from oracle import oracle_c
-    oc = oracle_c.load()
-    x = workloads.cast_input(n, seed=0)
-    b16 = np.empty(n, np.uint16)
-    f32 = np.empty(n, np.float32)
-    t = {}
-    best = None
-    for _ in range(reps):
+def _host_threads() -> int:
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+# ------------------------------------------------------------------ CPU arm
+class CpuSweep:
+    """The CPU path of the sweep on n elements: fp16 legs = ``ndarray.astype`` (the reference's
+    own primitive, one thread), bf16 legs = the C oracle with OpenMP on every host thread this
+    process may use (set explicitly: a launcher that exports OMP_NUM_THREADS=1 does not shrink it)."""
+
+    def __init__(self, n: int):
+        from novann_b200 import workloads
+        from oracle import oracle_c
+        self.oc = oracle_c.load()
+        self.threads = _host_threads()
+        self.oc.set_threads(self.threads)
+        self.n = n
+        self.x = np.empty(n, np.float32)
+        tile = workloads.cast_input(min(n, TILE), seed=0)
+        for off in range(0, n, tile.size):
+            self.x[off:off + tile.size] = tile[:n - off]
+        self.b16 = np.empty(n, np.uint16)
+        self.f32 = np.empty(n, np.float32)
+
+    def run(self):
+        """One sweep; returns (seconds, GB/s per direction)."""
+        n, oc, x = self.n, self.oc, self.x
         t0 = time.perf_counter()
-        oc.f32_to_bf16_bits(x, out=b16)
+        oc.f32_to_bf16_bits(x, out=self.b16)
         t1 = time.perf_counter()
-        oc.bf16_bits_to_f32(b16, out=f32)
+        oc.bf16_bits_to_f32(self.b16, out=self.f32)
         t2 = time.perf_counter()
         with np.errstate(all="ignore"):
             h = x.astype(np.float16)       # the reference's own primitive
         t3 = time.perf_counter()
         h.astype(np.float32)
         t4 = time.perf_counter()
-        tot = t4 - t0
-        if best is None or tot < best:
-            best = tot
-            t = {"f32->bf16_c_omp": 6 * n / (t1 - t0) / 1e9, "bf16->f32_c_omp": 6 * n / (t2 - t1) / 1e9,
-                 "f32->f16_numpy_astype": 6 * n / (t3 - t2) / 1e9,
-                 "f16->f32_numpy_astype": 6 * n / (t4 - t3) / 1e9}
-    return best, t, oc.max_threads()
+        g = 6 * n / 1e9
+        return t4 - t0, {"f32->bf16_c_omp": g / (t1 - t0), "bf16->f32_c_omp": g / (t2 - t1),
+                         "f32->f16_numpy_astype": g / (t3 - t2), "f16->f32_numpy_astype": g / (t4 - t3)}
 
 
 def run_reference(args):
+    """The reference arm: the full 1 Gi-element sweep per step on the host.  A step takes about
+    ten seconds, so the number of steps is cut to what fits ~200 s; `steps` reports what ran."""
     rank, world, _ = _dist_env()
     if rank != 0:
         return
-    n = 1 << 27  # bounded sample of the 1 Gi-element sweep
-    sec, detail, threads = None, None, None
-    times = []
-    for i in range(args.warmup + args.steps):
-        s, detail, threads = cpu_cast_sweep(n)
-        if i >= args.warmup:
-            times.append(s)
+    n = N_ELEMS
+    cpu = CpuSweep(n)
+    budget_s = 200.0
+    t_begin = time.perf_counter()
+    warm = min(args.warmup, 1)
+    for _ in range(warm):
+        cpu.run()
+    times, detail = [], None
+    for i in range(max(1, args.steps)):
+        s, detail = cpu.run()
+        times.append(s)
+        elapsed = time.perf_counter() - t_begin
+        if elapsed + s > budget_s:
+            break
     tot = sum(times)
     value = BYTES_PER_ELEM_STEP * n * len(times) / tot / 1e9
-    sample = (f"{n} of {N_ELEMS} elements per step, 4 directions: fp16 legs = ndarray.astype "
-              f"(1 thread), bf16 legs = C oracle with OpenMP ({threads} threads)")
+    sample = (f"full size: {n} elements per step, {len(times)} timed steps (+{warm} warm-up); fp16 legs "
+              f"ndarray.astype (1 thread), bf16 legs C oracle OpenMP ({cpu.threads} threads)")
     line = {
         "impl": "reference", "metric": "cast_hbm_gbs", "value": value, "unit": "GB/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "n_gpus": args.gpus, "steps": len(times), "warmup": warm, "steps_requested": args.steps,
         "ms_per_step": tot / len(times) * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32<->bf16/f16", "data": "synthetic",
-        "config": {"workload": "cast sweep fp32<->bf16, fp32<->fp16 (CPU sample)", "elements": n},
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "reference",
-                         "sample": sample, "per_direction_gbs": detail},
+        "config": workload_config(n),
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cpu.threads, "kind": "reference",
+                         "sample": sample,
+                         **{"gbs_" + k.replace("->", "_to_"): v for k, v in detail.items()}},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
 
 
-def measure_extras(dev, st, rank, world, dist, local):
-    """The other kernels of the path, timed with CUDA events on the library's stream.  Where a
-    call's working set is below the 126 MB L2, launches rotate over enough operand sets that
-    every launch finds its inputs in DRAM (a flushing write between launches would leave dirty
-    lines whose write-back lands inside the next timed kernel).  Reported under "extra"; the
-    headline metric above is the cast sweep."""
-    from novann_b200 import functional as F, quant, workloads
-    from novann_b200.device import DeviceBuffer, Event
-    from novann_b200.train import MLPTrainStep
+# ------------------------------------------------------------------ GPU arm: helpers
+class Timing:
+    """CUDA-event timing on the library's stream.  Where a call's working set is below the 126 MB
+    L2, launches rotate over enough operand sets that every launch finds its inputs in DRAM (a
+    flushing write between launches would leave dirty lines whose write-back lands inside the
+    next timed kernel)."""
 
-    flush = DeviceBuffer(256 << 20, dev)
+    def __init__(self, dev, st):
+        self.dev, self.st = dev, st
 
-    def timed(fn, iters=10, warm=3, do_flush=False):
-        for _ in range(warm):
-            fn()
-        tot = 0.0
-        for _ in range(iters):
-            if do_flush:
-                flush.zero(stream=st)
-            e0, e1 = Event(dev), Event(dev)
-            e0.record(st)
-            fn()
-            e1.record(st)
-            e1.sync()
-            tot += e0.elapsed_ms(e1)
-        return tot / iters
+    def events(self):
+        from novann_b200.device import Event
+        return Event(self.dev), Event(self.dev)
 
-    out = {}
-    peak_bf16 = None
-    pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(pk):
-        peak_bf16 = float(json.load(open(pk))["bf16_tflops"])
-    def timed_rotating(fn, sets, rounds=4):
-        """Back-to-back launches that rotate over buffer sets, so that a set is touched again
-        only after >= 512 MB of other traffic: every launch reads DRAM, and no flush write-back
-        lands inside the timed region."""
+    def rotating(self, fn, sets, rounds=4):
         k = len(sets)
         for i in range(k):
             fn(*sets[i])
-        st.sync()
-        e0, e1 = Event(dev), Event(dev)
-        e0.record(st)
+        self.st.sync()
+        e0, e1 = self.events()
+        e0.record(self.st)
         for i in range(rounds * k):
             fn(*sets[i % k])
-        e1.record(st)
+        e1.record(self.st)
         e1.sync()
         return e0.elapsed_ms(e1) / (rounds * k)
 
-    def timed_graph(fn, sets, rounds=4):
-        """The same rotation recorded once into a CUDA graph (one call per buffer set) and replayed:
-        the device time of a call without the host's launch cost, as a serving loop would issue it."""
+    def graph(self, fn, sets, rounds=4):
+        """The same rotation recorded once into a CUDA graph (one call per buffer set) and
+        replayed: the device time of a call without the host's launch cost."""
         import ctypes as C
         from novann_b200._lib import check, lib
         from novann_b200.device import _sptr
-        for args_ in sets:
-            fn(*args_)
+        dev, st = self.dev, self.st
+        for a in sets:
+            fn(*a)
         st.sync()
         check(lib().nvq_graph_begin_capture(dev, _sptr(st)))
         try:
-            for args_ in sets:
-                fn(*args_)
+            for a in sets:
+                fn(*a)
         finally:
             h = C.c_void_p()
             check(lib().nvq_graph_end_capture(dev, _sptr(st), C.byref(h)))
         graph = C.c_void_p(h.value)
         check(lib().nvq_graph_launch(dev, graph, _sptr(st)))
         st.sync()
-        e0, e1 = Event(dev), Event(dev)
+        e0, e1 = self.events()
         e0.record(st)
         for _ in range(rounds):
             check(lib().nvq_graph_launch(dev, graph, _sptr(st)))
@@ -238,146 +261,182 @@ def measure_extras(dev, st, rank, world, dist, local):
         check(lib().nvq_graph_destroy(dev, graph))
         return e0.elapsed_ms(e1) / (rounds * len(sets))
 
+    @staticmethod
     def n_sets_for(set_bytes):
         return max(2, int(np.ceil((512 << 20) / set_bytes)) + 1)
 
-    # ---- FP8 per tensor: fp32 [16384, 16384 / world] row shard (1 GiB per GPU at world = 1)
+
+def _free(sets):
+    for bufs in sets:
+        for b in bufs:
+            if b is not None:
+                b.free()
+
+
+def _random_codes(rng, n, k):
+    wq = rng.integers(0, 0x7F, (n, k), dtype=np.uint64).astype(np.uint8)      # finite E4M3 codes
+    wq |= rng.integers(0, 2, (n, k), dtype=np.uint64).astype(np.uint8) << 7
+    return wq
+
+
+# ------------------------------------------------------------------ GPU arm: the other kernels
+def measure_cast_sizes(T, rank):
+    """The other sizes of the cast-sweep config (1 Mi and 64 Mi elements) and the float64 pair:
+    the four-direction sweep over rotating buffer pairs; GB/s over 24 B (12 B for float64) per
+    element."""
+    from novann_b200 import quant, workloads
+    from novann_b200.device import DeviceBuffer
+    out = {}
+    for name, n in (("cast_1Mi_gbs", 1 << 20), ("cast_64Mi_gbs", 1 << 26)):
+        x = workloads.cast_input(n, seed=rank)
+        sets = [(DeviceBuffer.from_numpy(x, T.dev), DeviceBuffer(n * 2, T.dev))
+                for _ in range(Timing.n_sets_for(6 * n))]
+
+        def sweep(d32, d16):
+            for src, dst in DIRECTIONS:
+                a, b = (d32, d16) if src == "f32" else (d16, d32)
+                quant.cast_device(b, dst, a, src, n, stream=T.st)
+        t = T.rotating(sweep, sets, rounds=4 if n > (1 << 22) else 8)
+        out[name] = BYTES_PER_ELEM_STEP * n / t / 1e6
+        if n == 1 << 20:
+            out["cast_1Mi_us_per_sweep"] = t * 1e3
+            out["cast_1Mi_us_per_sweep_graph"] = T.graph(sweep, sets, rounds=8) * 1e3
+        _free(sets)
+    # float64 -> float32 (what the reference's layers do to BatchNorm's output) and back: 2^28
+    # elements (2 GiB of float64), 12 algorithmic bytes per element and direction
+    n = 1 << 28
+    rng = np.random.default_rng(rank)
+    tile = rng.standard_normal(1 << 24)
+    d64, d32 = DeviceBuffer(n * 8, T.dev), DeviceBuffer(n * 4, T.dev)
+    for off in range(0, n, tile.size):
+        d64.upload(tile, offset=off * 8)
+    sets = [(d64, d32)]
+    t = T.rotating(lambda a, b: quant.cast_device(b, "f32", a, "f64", n, stream=T.st), sets, rounds=10)
+    out["cast_f64_to_f32_gbs"] = 12 * n / t / 1e6
+    t = T.rotating(lambda a, b: quant.cast_device(a, "f64", b, "f32", n, stream=T.st), sets, rounds=10)
+    out["cast_f32_to_f64_gbs"] = 12 * n / t / 1e6
+    _free(sets)
+    return out
+
+
+def measure_quantisers(T, rank, world):
+    from novann_b200 import quant, workloads
+    from novann_b200.device import DeviceBuffer
+    out = {}
+    # FP8 per tensor: fp32 [16384, 16384 / world] row shard (1 GiB per GPU at world = 1)
     rows = 16384 // world
     n = rows * 16384
     x = workloads.fp8_input(min(rows, 1024), 16384, seed=rank)
-    asi = DeviceBuffer(12, dev)
+    asi = DeviceBuffer(12, T.dev)
     sets = []
-    for _ in range(n_sets_for(5 * n)):
-        d32 = DeviceBuffer(n * 4, dev)
+    for _ in range(Timing.n_sets_for(5 * n)):
+        d32 = DeviceBuffer(n * 4, T.dev)
         for off in range(0, n, x.size):
             d32.upload(x, offset=off * 4)
-        sets.append((d32, DeviceBuffer(n, dev)))
-    t = timed_rotating(lambda d32, d8: quant.quantize_fp8_tensor_device(d8, asi, d32, n, "e4m3", stream=st), sets)
+        sets.append((d32, DeviceBuffer(n, T.dev)))
+    t = T.rotating(lambda d32, d8: quant.quantize_fp8_tensor_device(d8, asi, d32, n, "e4m3", stream=T.st), sets)
     out["fp8_e4m3_amax_quantize_gbs"] = 9 * n / t / 1e6
-    t = timed_rotating(lambda d32, d8: quant.dequantize_fp8_device(d32, d8, n, "e4m3", 0.02, stream=st), sets)
+    t = T.rotating(lambda d32, d8: quant.dequantize_fp8_device(d32, d8, n, "e4m3", 0.02, stream=T.st), sets)
     out["fp8_e4m3_dequantize_gbs"] = 5 * n / t / 1e6
-    out["fp8_note"] = "%d rotating buffer sets of %.0f MB" % (len(sets), 5 * n / 1e6)
-    for bufs in sets:
-        for b_ in bufs:
-            b_.free()
-    # ---- FP4 block 32: bf16 [8192, 8192] (128 MiB in, about the L2 size), rotating sets as above
+    _free(sets)
+    # FP4 block 32: bf16 [8192 / world, 8192]
     r4 = 8192 // world
     xb = workloads.fp4_input_bits(r4, 8192, seed=rank)
     set_bytes = r4 * 8192 * 2.625
-    sets = [(DeviceBuffer.from_numpy(xb, dev), DeviceBuffer(r4 * 4096, dev),
-             DeviceBuffer(r4 * 256 * 4, dev)) for _ in range(n_sets_for(set_bytes))]
-    n_sets = len(sets)
-    t = timed_rotating(lambda dx, dp, dsc: quant.quantize_fp4_b32_device(dp, dsc, dx, r4, 8192, stream=st), sets)
-    out["fp4_quantize_gbs"] = 2.625 * r4 * 8192 / t / 1e6
-    t = timed_rotating(lambda dx, dp, dsc: quant.dequantize_fp4_b32_device(dx, dp, dsc, r4, 8192, stream=st), sets)
-    out["fp4_dequantize_gbs"] = 2.625 * r4 * 8192 / t / 1e6
-    out["fp4_note"] = "%d rotating buffer sets of %.0f MB, %d launches back to back" % (
-        n_sets, set_bytes / 1e6, 4 * n_sets)
-    for bufs in sets:
-        for b_ in bufs:
-            b_.free()
-    # ---- FP8-weight Linear forward: M = 4096 (world 1) or 8192 / world rows per GPU; N = K = 4096
+    sets = [(DeviceBuffer.from_numpy(xb, T.dev), DeviceBuffer(r4 * 4096, T.dev),
+             DeviceBuffer(r4 * 256 * 4, T.dev)) for _ in range(Timing.n_sets_for(set_bytes))]
+    t = T.rotating(lambda dx, dp, dsc: quant.quantize_fp4_b32_device(dp, dsc, dx, r4, 8192, stream=T.st), sets)
+    out["fp4_quantize_gbs"] = set_bytes / t / 1e6
+    t = T.rotating(lambda dx, dp, dsc: quant.dequantize_fp4_b32_device(dx, dp, dsc, r4, 8192, stream=T.st), sets)
+    out["fp4_dequantize_gbs"] = set_bytes / t / 1e6
+    _free(sets)
+    return out
+
+
+def measure_linear(T, rank, world):
+    """FP8-weight Linear forward: M = 4096 (one GPU) or 8192 / world rows per GPU; N = K = 4096.
+    Rotating operand sets (x, codes, workspace, y): a set comes round again only after the other
+    sets' >= 512 MB went through L2, so every call finds its operands in DRAM."""
+    from novann_b200 import functional as F, workloads
+    from novann_b200.device import DeviceBuffer
+    dev, st = T.dev, T.st
+    _, peak_bf16, _ = _peaks()
     m = 4096 if world == 1 else 8192 // world
     nn = kk = 4096
     rng = np.random.default_rng(rank)
-    xb, _, b = workloads.linear_inputs(m, 8, kk, seed=rank)
-    wq = rng.integers(0, 0x7F, (nn, kk), dtype=np.uint64).astype(np.uint8)
-    wq |= rng.integers(0, 2, (nn, kk), dtype=np.uint64).astype(np.uint8) << 7
+    xb, _, _ = workloads.linear_inputs(m, 8, kk, seed=rank)
+    wq = _random_codes(rng, nn, kk)
     dss = DeviceBuffer.from_numpy(np.full(nn, 1e-3, np.float32), dev)
     dbb = DeviceBuffer.from_numpy(np.zeros(nn, np.float32), dev)
-    # rotating operand sets (x, codes, workspace, y): a set comes round again only after the other
-    # sets' >= 512 MB went through L2, so every call finds its operands in DRAM
     per_set = m * kk * 2 + nn * kk + nn * kk * 2 + m * nn * 2
     lsets = [(DeviceBuffer.from_numpy(xb, dev), DeviceBuffer.from_numpy(wq, dev),
               DeviceBuffer(F.linear_workspace_bytes(nn, kk, "e4m3"), dev), DeviceBuffer(m * nn * 2, dev))
-             for _ in range(n_sets_for(per_set))]
-    t = timed_rotating(lambda dxx, dw, ws, dy: F.linear_q_device(dy, dxx, dw, "e4m3", dss, dbb, m, nn, kk, ws,
-                                                                 stream=st), lsets)
+             for _ in range(Timing.n_sets_for(per_set))]
+    flops = 2.0 * m * nn * kk
+    out = {"linear_fp8_M_per_gpu": m}
+
+    def call(path=None, use_ws=True):
+        return lambda dxx, dw, ws, dy: F.linear_q_device(dy, dxx, dw, "e4m3", dss, dbb, m, nn, kk,
+                                                         ws if use_ws else None, stream=st, path=path)
+    t = T.rotating(call(), lsets)
     F.check_device_errors(dev)
-    tf = 2.0 * m * nn * kk / t / 1e9
-    t_warm = timed_rotating(lambda dxx, dw, ws, dy: F.linear_q_device(dy, dxx, dw, "e4m3", dss, dbb, m, nn, kk,
-                                                                      ws, stream=st), lsets[:1], rounds=20)
-    out["linear_fp8"] = {"M_per_gpu": m, "N": nn, "K": kk, "ms": t, "tflops_per_gpu": tf,
-                         "tflops_per_gpu_l2_warm": 2.0 * m * nn * kk / t_warm / 1e9,
-                         "frac_of_measured_bf16_peak": tf / peak_bf16 if peak_bf16 else None,
-                         "frac_of_nominal_fp8_peak_4500": tf / 4500.0,
-                         "note": "bf16 activations x FP8 weight codes; weight expansion pass "
-                                 "included; tcgen05 kind::f16 (a bf16-activation GEMM cannot "
-                                 "exceed half of FP8 peak); tflops_per_gpu: %d rotating operand sets, every call reads "
-                                 "its 112 MB of operands from DRAM; _l2_warm: the same buffers back to back "
-                                 "(operands stay in the 126 MB L2)" % len(lsets)}
+    out["linear_fp8_ms"] = t
+    out["linear_fp8_tflops_per_gpu"] = flops / t / 1e9
+    out["linear_fp8_frac_bf16_peak"] = flops / t / 1e9 / peak_bf16
+    out["linear_fp8_frac_nominal_fp8_4500"] = flops / t / 1e9 / 4500.0
+    t = T.rotating(call(use_ws=False), lsets)
+    F.check_device_errors(dev)
+    out["linear_fp8_in_kernel_expansion_tflops_per_gpu"] = flops / t / 1e9
     for dxx, dw, ws, dy in lsets:
         F.linear_expand_weight_device(ws, dw, "e4m3", None, nn, kk, stream=st)
-    t = timed_rotating(lambda dxx, dw, ws, dy: F.linear_expanded_device(dy, dxx, ws, dss, dbb, m, nn, kk,
-                                                                        stream=st), lsets)
+    t = T.rotating(lambda dxx, dw, ws, dy: F.linear_expanded_device(dy, dxx, ws, dss, dbb, m, nn, kk, stream=st), lsets)
     F.check_device_errors(dev)
-    tfe = 2.0 * m * nn * kk / t / 1e9
-    t_warm = timed_rotating(lambda dxx, dw, ws, dy: F.linear_expanded_device(dy, dxx, ws, dss, dbb, m, nn, kk,
-                                                                             stream=st), lsets[:1], rounds=20)
-    out["linear_fp8_weight_expanded_once"] = {
-        "ms": t, "tflops_per_gpu": tfe, "tflops_per_gpu_l2_warm": 2.0 * m * nn * kk / t_warm / 1e9,
-        "frac_of_measured_bf16_peak": tfe / peak_bf16 if peak_bf16 else None,
-        "note": "contraction alone: the codes were expanded to bf16 once, outside the call "
-                "(nvq_linear_expand_weight + nvq_linear_fwd_expanded; 2 bytes per weight kept)"}
+    out["linear_fp8_weight_expanded_once_tflops_per_gpu"] = flops / t / 1e9
     ws8 = DeviceBuffer(F.linear_w8a8_workspace_bytes(m, kk), dev)
-    t = timed_rotating(lambda dxx, dw, ws, dy: F.linear_w8a8_device(dy, dxx, dw, dss, dbb, m, nn, kk, ws8,
-                                                                    stream=st), lsets)
+    t = T.rotating(lambda dxx, dw, ws, dy: F.linear_w8a8_device(dy, dxx, dw, dss, dbb, m, nn, kk, ws8, stream=st), lsets)
     F.check_device_errors(dev)
-    tf8 = 2.0 * m * nn * kk / t / 1e9
-    out["linear_w8a8_variant"] = {"M_per_gpu": m, "N": nn, "K": kk, "ms": t, "tflops_per_gpu": tf8,
-                                  "frac_of_nominal_fp8_peak_4500": tf8 / 4500.0,
-                                  "note": "NOT the parity path: activations quantised to E4M3 per row "
-                                          "inside the call (included in the time), FP8 x FP8 MMAs "
-                                          "(kind::f8f6f4); max-abs-rel vs the bf16-activation result "
-                                          "is 2.4-3.2e-2, outside the 1e-2 bound"}
+    out["linear_w8a8_variant_tflops_per_gpu"] = flops / t / 1e9     # NOT the parity path (2.4-3.2e-2 off)
     # few rows (serving shape): the weight-streaming kernel; same rotating sets, so the 16 MB of
     # codes come from DRAM on every call
     ms_ = 16
-    t = timed_rotating(lambda dxx, dw, ws, dy: F.linear_q_device(dy, dxx, dw, "e4m3", dss, dbb, ms_, nn, kk, ws,
-                                                                 stream=st), lsets)
-    t_warm = timed_rotating(lambda dxx, dw, ws, dy: F.linear_q_device(dy, dxx, dw, "e4m3", dss, dbb, ms_, nn, kk,
-                                                                      ws, stream=st), lsets[:1], rounds=20)
-    t_graph = timed_graph(lambda dxx, dw, ws, dy: F.linear_q_device(dy, dxx, dw, "e4m3", dss, dbb, ms_, nn, kk, ws,
-                                                                    stream=st), lsets)
+
+    def few(dxx, dw, ws, dy):
+        F.linear_q_device(dy, dxx, dw, "e4m3", dss, dbb, ms_, nn, kk, ws, stream=st)
+    t = T.rotating(few, lsets)
+    tg = T.graph(few, lsets)
     F.check_device_errors(dev)
-    out["linear_fp8_few_rows"] = {"M": ms_, "N": nn, "K": kk, "us": t * 1e3, "us_l2_warm": t_warm * 1e3,
-                                  "us_cuda_graph": t_graph * 1e3,
-                                  "weight_gbs": nn * kk / t / 1e6,
-                                  "note": "M <= 128: codes read once (1 byte per weight) and fed to "
-                                          "kind::f8f6f4 MMAs as they are, activations carried as two rows "
-                                          "of E4M3 codes, operands swapped, split along K with a "
-                                          "deterministic reduction kernel; weight_gbs = code bytes / time; us = eager "
-                                          "calls from Python (three launches, host-bound), us_cuda_graph = the "
-                                          "same rotation replayed from one CUDA graph"}
-    for bufs in lsets:
-        for b_ in bufs:
-            b_.free()
+    hbm, _, _ = _peaks()
+    out["linear_fp8_few_rows_us"] = t * 1e3
+    out["linear_fp8_few_rows_us_graph"] = tg * 1e3
+    out["linear_fp8_few_rows_frac_hbm_graph"] = nn * kk / tg / 1e6 / hbm
+    _free(lsets)
     ws8.free()
-    # the same kernel on a weight far larger than L2 (an 8192 x 28672 projection, 235 MB of codes):
-    # the streaming rate without the fixed cost of a 16 MB call; two rotating weights
+    # the same kernel on a weight far larger than L2 (an 8192 x 28672 projection, 235 MB of codes)
     nl, kl = 28672, 8192
-    wl = np.tile(rng.integers(0, 0x7F, (nl // 8, kl), dtype=np.uint8), (8, 1))   # values do not matter here
+    wl = np.tile(rng.integers(0, 0x7F, (nl // 8, kl), dtype=np.uint8), (8, 1))
     xl, _, _ = workloads.linear_inputs(ms_, 8, kl, seed=rank)
     dsl = DeviceBuffer.from_numpy(np.full(nl, 1e-3, np.float32), dev)
     big = [(DeviceBuffer.from_numpy(xl, dev), DeviceBuffer.from_numpy(wl, dev),
-            DeviceBuffer(64 << 20, dev), DeviceBuffer(ms_ * nl * 2, dev))   # partial sums need < 8 MB
-           for _ in range(2)]
-    t = timed_rotating(lambda dxx, dw, ws, dy: F.linear_q_device(dy, dxx, dw, "e4m3", dsl, None, ms_, nl, kl, ws,
-                                                                 stream=st), big, rounds=5)
+            DeviceBuffer(64 << 20, dev), DeviceBuffer(ms_ * nl * 2, dev)) for _ in range(2)]
+    t = T.rotating(lambda dxx, dw, ws, dy: F.linear_q_device(dy, dxx, dw, "e4m3", dsl, None, ms_, nl, kl, ws,
+                                                             stream=st), big, rounds=5)
     F.check_device_errors(dev)
-    peak_hbm, _ = _peaks()
-    out["linear_fp8_few_rows_large"] = {"M": ms_, "N": nl, "K": kl, "us": t * 1e3,
-                                        "weight_gbs": nl * kl / t / 1e6,
-                                        "frac_of_measured_hbm_peak": nl * kl / t / 1e6 / peak_hbm,
-                                        "note": "three kernels per call (activation split, stream, reduction) "
-                                                "in the time; 235 MB of codes per call from DRAM"}
-    for bufs in big:
-        for b_ in bufs:
-            b_.free()
-    dsl.free()
-    # ---- FP8-weight Conv2d forward as an implicit GEMM: x fp32 [128 / world, 64, 56, 56], 3x3, pad 1,
-    # 128 output channels (a ResNet-style block); NCHW fp32 in and out, everything on the device
-    from novann_b200 import _lib as _l
+    out["linear_fp8_few_rows_large_us"] = t * 1e3
+    out["linear_fp8_few_rows_large_frac_hbm"] = nl * kl / t / 1e6 / hbm
+    _free(big)
+    for b in (dsl, dss, dbb):
+        b.free()
+    return out
+
+
+def measure_conv(T, rank, world):
+    """FP8-weight Conv2d forward as an implicit GEMM: x fp32 [128 / world, 64, 56, 56], 3x3, pad 1,
+    128 output channels; NCHW fp32 in and out, all kernels of the call in the time."""
+    from novann_b200 import _lib, functional as F
+    from novann_b200._lib import check, lib
+    from novann_b200.device import DeviceBuffer, _sptr
+    dev, st = T.dev, T.st
+    rng = np.random.default_rng(rank)
     cn, cc, chw, cco = max(1, 128 // world), 64, 56, 128
     xcv = rng.standard_normal((cn, cc, chw, chw), dtype=np.float32)
     wcv = rng.integers(0, 0x7F, (cco, cc * 9), dtype=np.uint64).astype(np.uint8)
@@ -387,68 +446,201 @@ def measure_extras(dev, st, rank, world, dist, local):
     d_col, d_yb = DeviceBuffer(crows * ckp * 2, dev), DeviceBuffer(crows * cco * 2, dev)
     d_wsc = DeviceBuffer(F.linear_workspace_bytes(cco, ckp, "e4m3"), dev)
     d_oc = DeviceBuffer(crows * cco * 4, dev)
-    from novann_b200._lib import check as _check, lib as _lib_fn
-    from novann_b200.device import _sptr
 
-    def conv_call():
-        _check(_lib_fn().nvq_conv2d_fwd_q(d_oc.at(0), d_xc.at(0), d_wc.at(0), _l.DTYPE_IDS["e4m3"], d_sc.at(0),
-                                          None, d_col.at(0), d_yb.at(0), d_wsc.at(0), d_wsc.nbytes, cn, cc,
-                                          chw, chw, cco, 3, 3, 1, 1, 1, 1, 0, dev, _sptr(st)))
-    t = timed(conv_call, iters=10)
+    def conv_call(*_):
+        check(lib().nvq_conv2d_fwd_q(d_oc.at(0), d_xc.at(0), d_wc.at(0), _lib.DTYPE_IDS["e4m3"], d_sc.at(0),
+                                     None, d_col.at(0), d_yb.at(0), d_wsc.at(0), d_wsc.nbytes, cn, cc,
+                                     chw, chw, cco, 3, 3, 1, 1, 1, 1, 0, dev, _sptr(st)))
+    t = T.rotating(conv_call, [()], rounds=10)
     F.check_device_errors(dev)
-    out["conv2d_fp8"] = {"N_per_gpu": cn, "C": cc, "HW": chw, "Cout": cco, "kernel": 3, "ms": t,
-                         "tflops_per_gpu": 2.0 * crows * cco * ckp / t / 1e9,
-                         "note": "nvq_conv2d_fwd_q: fp32 NCHW -> bf16 NHWC pass, weight expansion, tcgen05 "
-                                 "implicit GEMM with 4-D TMA boxes (no patch matrix; output channels on the "
-                                 "MMA's M side), fp32 NCHW written by TMA stores from the epilogue; all "
-                                 "three kernels in the time"}
-    for b_ in (d_xc, d_wc, d_col, d_yb, d_wsc, d_oc):
-        b_.free()
-    # ---- fp32 MLP train step, batch 128 / world rows per GPU, CUDA-graph replay
-    bsz = 128 // world
+    for b in (d_xc, d_wc, d_col, d_yb, d_wsc, d_oc, d_sc):
+        b.free()
+    return {"conv2d_fp8_ms": t, "conv2d_fp8_tflops_per_gpu": 2.0 * crows * cco * ckp / t / 1e9,
+            "conv2d_fp8_N_per_gpu": cn}
+
+
+def measure_train_steps(T, rank, world):
+    """The fp32 MLP step (784-256-128-10) and the CNN of the reference's main.py, batch 128 / world
+    per GPU, replayed as CUDA graphs; no collective in these two figures."""
+    from novann_b200 import workloads
+    from novann_b200.train import MLPTrainStep
+    from novann_b200.train_cnn import CNNTrainStep, main_cnn_spec
+    dev = T.dev
+    out = {}
+    bsz = max(1, 128 // world)
     xm, ym, params = workloads.mlp_inputs(128, (784, 256, 128, 10), seed=0)
     step = MLPTrainStep(params, bsz, 0.01, dev)
     step.step(xm[:bsz], ym[:bsz])
     step.capture()
-    e0, e1 = Event(dev), Event(dev)
     for _ in range(5):
         step.replay()
     step.stream.sync()
+    T2 = Timing(dev, step.stream)
+    e0, e1 = T2.events()
     e0.record(step.stream)
     for _ in range(50):
         step.replay()
     e1.record(step.stream)
     e1.sync()
     out["mlp_step_us"] = e0.elapsed_ms(e1) / 50 * 1e3
-    # ---- the CNN of the reference's main.py, batch 128 / world per GPU: forward + CE + backward
-    # replayed as one CUDA graph, then the two AdamW launches
-    from novann_b200.train_cnn import CNNTrainStep, main_cnn_spec
-    cb = 128 // world
-    xc, yc, cparams = workloads.cnn_inputs(cb, steps=1, seed=0)
-    cnn = CNNTrainStep(main_cnn_spec(), cparams, cb, (1, 28, 28), device=dev)
+    xc, yc, cparams = workloads.cnn_inputs(bsz, steps=1, seed=0)
+    cnn = CNNTrainStep(main_cnn_spec(), cparams, bsz, (1, 28, 28), device=dev)
     cnn.step(xc[0], yc[0])
     cnn.capture()
     for _ in range(3):
         cnn.step(xc[0], yc[0])
-    e0, e1 = Event(dev), Event(dev)
+    T3 = Timing(dev, cnn.stream)
+    e0, e1 = T3.events()
     e0.record(cnn.stream)
     for _ in range(20):
         cnn.replay()
     e1.record(cnn.stream)
     e1.sync()
     out["cnn_step_us"] = e0.elapsed_ms(e1) / 20 * 1e3
-    out["cnn_step_note"] = ("main.py CNN (3 conv + 4 BatchNorm + pool + 2 Linear + Dropout), batch %d per GPU, "
-                            "forward + CE + backward + AdamW, %d kernels per step, inputs resident" %
-                            (cb, cnn.launches_per_step))
-    out["mlp_step_note"] = ("fp32 784-256-128-10, batch %d per GPU, forward + CE + backward + SGD, "
-                            "%d kernels replayed as one CUDA graph, no all-reduce in this figure" % (bsz, step.kernels_per_step()))
     return out
 
 
+def measure_dp_step(dev, rank, world, dist, local):
+    """The one collective of the project: the data-parallel MLP step, batch 128 split over the
+    ranks, its flat 235 146-float gradient bucket summed by nvq_allreduce_sum_f32 (NCCL over
+    NVLink), 1 / world folded into the SGD kernel.  Times are the max over ranks.
+    dp_step_us: eager steps (11 launches) with the all-reduce, device time per step;
+    dp_step_us_graph: the same step replayed from a CUDA graph; allreduce_us: the all-reduce alone."""
+    import torch
+    from novann_b200 import workloads
+    from novann_b200.device import DeviceBuffer
+    from novann_b200.train import Communicator, MLPTrainStep, shard_rows
+
+    def max_over_ranks(v):
+        t = torch.tensor([v], device=f"cuda:{local}", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    uid = torch.zeros(128, dtype=torch.uint8, device=f"cuda:{local}")
+    if rank == 0:
+        uid = torch.tensor(list(Communicator.make_unique_id()), dtype=torch.uint8, device=f"cuda:{local}")
+    dist.broadcast(uid, src=0)
+    comm = Communicator(bytes(uid.cpu().tolist()), rank, world, device=dev)
+    out = {}
+    x, y, params = workloads.mlp_inputs(128, (784, 256, 128, 10), seed=0)
+    lo, hi = shard_rows(128, rank, world)
+    step = MLPTrainStep(params, hi - lo, 0.01, dev, comm=comm)
+    T = Timing(dev, step.stream)
+    for _ in range(3):
+        step.step(x[lo:hi], y[lo:hi])
+    dist.barrier()
+    e0, e1 = T.events()
+    e0.record(step.stream)
+    for _ in range(50):
+        step.launch()
+    e1.record(step.stream)
+    step.sync()
+    out["dp_step_us"] = max_over_ranks(e0.elapsed_ms(e1) / 50 * 1e3)
+    # the all-reduce alone, on the gradient bucket
+    buf = DeviceBuffer(MLP_PARAMS * 4, dev)
+    buf.zero(stream=step.stream)
+    for _ in range(5):
+        comm.allreduce_sum(buf, MLP_PARAMS, stream=step.stream)
+    step.sync()
+    dist.barrier()
+    e0, e1 = T.events()
+    e0.record(step.stream)
+    for _ in range(50):
+        comm.allreduce_sum(buf, MLP_PARAMS, stream=step.stream)
+    e1.record(step.stream)
+    step.sync()
+    out["allreduce_us"] = max_over_ranks(e0.elapsed_ms(e1) / 50 * 1e3)
+    out["allreduce_floats"] = MLP_PARAMS
+    try:
+        step.capture()
+        for _ in range(3):
+            step.replay()
+        step.sync()
+        dist.barrier()
+        e0, e1 = T.events()
+        e0.record(step.stream)
+        for _ in range(50):
+            step.replay()
+        e1.record(step.stream)
+        step.sync()
+        out["dp_step_us_graph"] = max_over_ranks(e0.elapsed_ms(e1) / 50 * 1e3)
+    except Exception as e:          # a capture NCCL refuses is reported, not fatal
+        out["dp_step_us_graph"] = None
+        out["dp_graph_error"] = str(e)[:120]
+    dist.barrier()
+    buf.free()
+    comm.close()
+    return out
+
+
+def measure_e2e(dev, tile, n, steps, barrier, max_over_ranks):
+    """The sweep through the host-array call on pinned arrays (the headline e2e figure), the same
+    bytes moved by plain pinned copies with no kernel (H2D and D2H of each cast issued together,
+    one synchronisation per cast: what a synchronous astype replacement can reach at best), and
+    the sweep on pageable arrays at a quarter of the size."""
+    from novann_b200 import quant
+    from novann_b200._lib import check, lib
+    from novann_b200.device import DeviceBuffer, Stream, _sptr, device_sync, pinned_empty
+    import ctypes as C
+    h32 = pinned_empty(n, np.float32)
+    h16 = pinned_empty(n, np.uint16)
+    for off in range(0, n, tile.size):
+        h32[off:off + tile.size] = tile
+    h16f = h16.view(np.float16)
+
+    def sweep_host(a32, a16, a16f):
+        quant.cast(a32, "bf16", out=a16, device=dev)
+        quant.cast(a16, "f32", src_dtype="bf16", out=a32, device=dev)
+        quant.cast(a32, np.float16, out=a16f, device=dev)
+        quant.cast(a16f, np.float32, out=a32, device=dev)
+
+    sweep_host(h32, h16, h16f)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        sweep_host(h32, h16, h16f)
+    device_sync(dev)
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    out = {"e2e_s": e2e_s}
+    # ---- ceiling: the same bytes, copies only
+    d_in, d_out = DeviceBuffer(n * 4, dev), DeviceBuffer(n * 4, dev)
+    s_in, s_out = Stream(dev), Stream(dev)
+    vp = C.c_void_p
+
+    def copies_only():
+        for src_b, dst_b, hs, hd in ((4, 2, h32, h16), (2, 4, h16, h32), (4, 2, h32, h16), (2, 4, h16, h32)):
+            check(lib().nvq_memcpy_h2d(d_in.at(0), vp(hs.ctypes.data), n * src_b, dev, _sptr(s_in)))
+            check(lib().nvq_memcpy_d2h(vp(hd.ctypes.data), d_out.at(0), n * dst_b, dev, _sptr(s_out)))
+            s_in.sync()
+            s_out.sync()
+    d_out.zero()
+    copies_only()
+    barrier()
+    t0 = time.perf_counter()
+    copies_only()
+    out["copy_s"] = max_over_ranks(time.perf_counter() - t0)
+    d_in.free()
+    d_out.free()
+    # ---- pageable arrays (what a plain ndarray is): a quarter of the size
+    npg = n // 4
+    p32 = np.empty(npg, np.float32)
+    p16 = np.empty(npg, np.uint16)
+    p32[:] = h32[:npg]
+    sweep_host(p32, p16, p16.view(np.float16))
+    barrier()
+    t0 = time.perf_counter()
+    sweep_host(p32, p16, p16.view(np.float16))
+    device_sync(dev)
+    out["pageable_s"] = max_over_ranks(time.perf_counter() - t0)
+    out["pageable_elems"] = npg
+    return out
+
+
+# ------------------------------------------------------------------ GPU arm
 def run_ours(args):
     rank, world, local = _dist_env()
     from novann_b200 import _lib, quant, workloads
-    from novann_b200.device import DeviceBuffer, Event, Stream, device_sync, pinned_empty
+    from novann_b200.device import DeviceBuffer, Event, Stream, device_sync
 
     dist = None
     if world > 1:
@@ -460,6 +652,14 @@ def run_ours(args):
     L = _lib.lib()
     st = Stream(dev)
     n = N_ELEMS
+
+    def max_over_ranks(v):
+        if dist is None:
+            return v
+        import torch
+        t = torch.tensor([v], device=f"cuda:{local}", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
     # ---- inputs resident in HBM before the timed region
     tile = workloads.cast_input(TILE, seed=rank)
@@ -481,7 +681,8 @@ def run_ours(args):
             if events is not None:
                 events[i + 1].record(st)
 
-    for _ in range(max(3, args.warmup)):
+    warm = max(3, args.warmup)
+    for _ in range(warm):
         sweep()
     barrier()
     sampler = ClockSampler(dev)
@@ -496,94 +697,209 @@ def run_ours(args):
     t_stop.record(st)
     barrier()
     launches = L.nvq_launch_count() - launches0
-    ms_total = t_start.elapsed_ms(t_stop)
+    ms_total = max_over_ranks(t_start.elapsed_ms(t_stop))
     per_kernel = {}
     for i, (src, dst) in enumerate(DIRECTIONS):
         per_kernel[f"{src}->{dst}"] = statistics.mean(ev[k][i].elapsed_ms(ev[k][i + 1])
                                                       for k in range(args.steps))
-    if dist is not None:
-        import torch
-        t = torch.tensor([ms_total], device=f"cuda:{local}", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
     value = BYTES_PER_ELEM_STEP * n * args.steps * world / (ms_total * 1e-3) / 1e9
-
     d32.free()
     d16.free()
-    extra = measure_extras(dev, st, rank, world, dist, local)
-    clocks = sampler.stop()   # sampled over the timed region and the extra kernels
+
+    T = Timing(dev, st)
+    flat = {}
+    flat.update(measure_cast_sizes(T, rank))
+    flat.update(measure_quantisers(T, rank, world))
+    flat.update(measure_linear(T, rank, world))
+    flat.update(measure_conv(T, rank, world))
+    flat.update(measure_train_steps(T, rank, world))
+    clocks = sampler.stop()   # sampled over the timed region and the other kernels
+    if dist is not None:
+        flat.update(measure_dp_step(dev, rank, world, dist, local))
+        # aggregate Linear throughput of the job: every rank multiplies its own row shard
+        import torch
+        t = torch.tensor([flat["linear_fp8_tflops_per_gpu"]], device=f"cuda:{local}", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        flat["linear_fp8_tflops"] = float(t.item())
+        t = torch.tensor([flat["linear_fp8_tflops_per_gpu"]], device=f"cuda:{local}", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        flat["linear_fp8_tflops_per_gpu"] = float(t.item())      # the slowest rank's
+    else:
+        flat["linear_fp8_tflops"] = flat["linear_fp8_tflops_per_gpu"]
 
     # ---- e2e: host arrays through the astype-replacement call
-    h32 = pinned_empty(n, np.float32)
-    h16 = pinned_empty(n, np.uint16)
-    for off in range(0, n, TILE):
-        h32[off:off + TILE] = tile
-    h16f = h16.view(np.float16)
-
-    def sweep_host():
-        quant.cast(h32, "bf16", out=h16, device=dev)
-        quant.cast(h16, "f32", src_dtype="bf16", out=h32, device=dev)
-        quant.cast(h32, np.float16, out=h16f, device=dev)
-        quant.cast(h16f, np.float32, out=h32, device=dev)
-
     e2e_steps = max(1, min(args.steps, 5))
-    sweep_host()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        sweep_host()
-    device_sync(dev)
-    e2e_s = time.perf_counter() - t0
-    if dist is not None:
-        import torch
-        t = torch.tensor([e2e_s], device=f"cuda:{local}", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    e2e_value = BYTES_PER_ELEM_STEP * n * e2e_steps * world / e2e_s / 1e9
+    e = measure_e2e(dev, tile, n, e2e_steps, barrier, max_over_ranks)
+    e2e_value = BYTES_PER_ELEM_STEP * n * e2e_steps * world / e["e2e_s"] / 1e9
+    copy_ceiling = BYTES_PER_ELEM_STEP * n * world / e["copy_s"] / 1e9
+    pageable = BYTES_PER_ELEM_STEP * e["pageable_elems"] * world / e["pageable_s"] / 1e9
 
     if rank == 0:
-        peak, which = _peaks()
+        peak, peak_bf16, which = _peaks()
         dom = max(per_kernel, key=per_kernel.get)
         achieved = 6 * n / (per_kernel[dom] * 1e-3) / 1e9
         cpu = None
         if world == 1:
             cpu_n = 1 << 27
-            sec, detail, threads = cpu_cast_sweep(cpu_n, reps=3)
-            cpu = {"value": BYTES_PER_ELEM_STEP * cpu_n / sec / 1e9, "unit": "GB/s", "cores": threads,
+            sweep_cpu = CpuSweep(cpu_n)
+            best, detail = None, None
+            for _ in range(3):
+                s, dt = sweep_cpu.run()
+                if best is None or s < best:
+                    best, detail = s, dt
+            cpu = {"value": BYTES_PER_ELEM_STEP * cpu_n / best / 1e9, "unit": "GB/s", "cores": sweep_cpu.threads,
                    "kind": "port",
-                   "sample": f"{cpu_n} of {n} elements, best of 3 sweeps; bf16 legs: C oracle "
-                             f"OpenMP {threads} threads; fp16 legs: ndarray.astype (1 thread)",
-                   "per_direction_gbs": detail}
+                   "sample": f"{cpu_n} of {n} elements, best of 3; bf16 legs C oracle OpenMP "
+                             f"{sweep_cpu.threads} threads, fp16 legs ndarray.astype (1 thread)",
+                   **{"gbs_" + k.replace("->", "_to_"): v for k, v in detail.items()}}
+        # DRAM bytes of the dominant kernel per launch: one ncu capture at 64 Mi elements
+        # (profiles/cast_kernels_64Mi_elements.md) counted dram reads equal to the algorithmic
+        # reads (no re-reads) and writes short of the algorithmic writes by what was still in L2
+        # when the single profiled launch ended; scaled by elements (x16) to this size.
+        narrow = dom.startswith("f32")
+        ncu_64mi = (268.4e6 + 88.8e6) if narrow else (134.2e6 + 210.7e6)
         line = {
             "metric": "cast_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(3, args.warmup),
+            "steps": args.steps, "warmup": warm,
             "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32<->bf16/f16", "data": "synthetic",
-            "config": {"workload": "cast sweep fp32->bf16->fp32->fp16->fp32, 1 Gi elements per GPU "
-                                   "(BASELINE configs[1], largest size)",
-                       "elements_per_gpu": n, "bytes_per_element_step": BYTES_PER_ELEM_STEP,
-                       "l2": "inputs (4 GiB + 2 GiB) far exceed the 126 MB L2; no flush needed",
-                       "input": "N(0,1) with 1% N(0,sigma=100) + 4096-element edge block; "
-                                "2^26-element seeded tile repeated 16x"},
+            "config": workload_config(n),
             "roofline": {"bound": "hbm", "kernel": f"cast {dom}", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_source": which,
-                         # dram read + write of the dominant kernel per launch: the ncu capture at
-                         # 64 Mi elements (profiles/cast_kernels_64Mi_elements.md) shows reads equal
-                         # to the algorithmic reads and no re-reads; scaled by elements to this size
-                         "traffic": 6.0 * n, "traffic_source": "ncu at 64 Mi elements, scaled x16",
-                         "per_kernel_ms": per_kernel,
-                         "frac_of_nominal_8tbs": achieved / 8000.0},
+                         "traffic": ncu_64mi * 16,
+                         "traffic_source": "ncu dram read+write at 64 Mi elements x16 (reads = algorithmic; "
+                                           "writes short by the L2-resident tail of the one profiled launch)",
+                         "algorithmic_bytes": 6.0 * n, "frac_uses": "algorithmic_bytes",
+                         "frac_of_nominal_8tbs": achieved / 8000.0,
+                         **{"ms_" + k.replace("->", "_to_"): v for k, v in per_kernel.items()},
+                         "cast_64Mi_gbs": flat["cast_64Mi_gbs"], "cast_1Mi_gbs": flat["cast_1Mi_gbs"],
+                         "cast_f64_to_f32_gbs": flat["cast_f64_to_f32_gbs"],
+                         "linear_fp8_tflops_per_gpu": flat["linear_fp8_tflops_per_gpu"],
+                         "linear_fp8_frac_bf16_peak": flat["linear_fp8_frac_bf16_peak"],
+                         "linear_fp8_M_per_gpu": flat["linear_fp8_M_per_gpu"],
+                         "dp_step_us": flat.get("dp_step_us"), "allreduce_us": flat.get("allreduce_us")},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 12 * n,
                     "d2h_bytes_per_step": 12 * n, "steps": e2e_steps,
-                    "api": "novann_b200.quant.cast(host array) -> nvq_cast_host"},
+                    "api": "novann_b200.quant.cast(host array) -> nvq_cast_host, pinned arrays",
+                    "copy_ceiling_gbs": copy_ceiling, "frac_of_copy_ceiling": e2e_value / copy_ceiling,
+                    "pageable_gbs": pageable, "pageable_elements": e["pageable_elems"]},
             "gpu_launches": int(launches),
             "clocks": clocks,
-            "extra": extra,
         }
+        line.update(flat)       # flat scalar keys: the Linear, the other cast sizes, the DP step ...
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------ single small cases
+def run_case(name: str, a: list[int]) -> None:
+    """One small, self-ending case of one kernel on device 0, for profiler captures: seeded
+    inputs, a few launches, exit.  Sizes are larger than the 126 MB L2 (so DRAM counters mean
+    something) but hold at most a few GB.
+
+        cast [log2_elems=26 reps=3]      cast64 [log2_elems=26 reps=3]    fp8 [rows=8192 reps=3]
+        fp4 [rows=8192 reps=3]           linear [M=4096 N=4096 K=4096 reps=3 in_kernel=0]
+        w8a8 [M N K reps]                fewrows [M=16 N=8192 K=8192 reps=3]
+        conv [N=128 C=64 HW=56 Cout=128 reps=2]     mlp [batch=128 steps=3]     cnn [batch=128 steps=3]
+    """
+    from novann_b200 import _lib, functional as F, quant, workloads
+    from novann_b200._lib import check, lib
+    from novann_b200.device import DeviceBuffer, Stream, _sptr, device_sync
+
+    def arg(i, default):
+        return a[i] if len(a) > i else default
+    st = Stream(0)
+    rng = np.random.default_rng(1)
+    if name == "cast":
+        n, reps = 1 << arg(0, 26), arg(1, 3)
+        d32 = DeviceBuffer.from_numpy(workloads.cast_input(n, seed=0), 0)
+        d16 = DeviceBuffer(n * 2, 0)
+        for _ in range(reps):
+            for src, dst in DIRECTIONS:
+                s_, d_ = (d32, d16) if src == "f32" else (d16, d32)
+                quant.cast_device(d_, dst, s_, src, n, stream=st)
+    elif name == "cast64":
+        n, reps = 1 << arg(0, 26), arg(1, 3)
+        d64 = DeviceBuffer.from_numpy(np.random.default_rng(0).standard_normal(n), 0)
+        d32 = DeviceBuffer(n * 4, 0)
+        for _ in range(reps):
+            quant.cast_device(d32, "f32", d64, "f64", n, stream=st)
+            quant.cast_device(d64, "f64", d32, "f32", n, stream=st)
+    elif name == "fp8":
+        rows, reps, cols = arg(0, 8192), arg(1, 3), 8192
+        n = rows * cols
+        d = DeviceBuffer.from_numpy(workloads.fp8_input(rows, cols, seed=0), 0)
+        q, asi = DeviceBuffer(n, 0), DeviceBuffer(12, 0)
+        for _ in range(reps):
+            quant.quantize_fp8_tensor_device(q, asi, d, n, "e4m3", stream=st)
+            quant.dequantize_fp8_device(d, q, n, "e4m3", 0.01, stream=st)
+    elif name == "fp4":
+        rows, reps, cols = arg(0, 8192), arg(1, 3), 8192
+        d = DeviceBuffer.from_numpy(workloads.fp4_input_bits(rows, cols, seed=0), 0)
+        p, s = DeviceBuffer(rows * cols // 2, 0), DeviceBuffer(rows * cols // 32 * 4, 0)
+        for _ in range(reps):
+            quant.quantize_fp4_b32_device(p, s, d, rows, cols, stream=st)
+            quant.dequantize_fp4_b32_device(d, p, s, rows, cols, stream=st)
+    elif name in ("linear", "w8a8"):
+        m, n, k, reps, in_kernel = arg(0, 4096), arg(1, 4096), arg(2, 4096), arg(3, 3), arg(4, 0)
+        xb, _, b = workloads.linear_inputs(m, 8, k, seed=0)
+        dx, dw = DeviceBuffer.from_numpy(xb, 0), DeviceBuffer.from_numpy(_random_codes(rng, n, k), 0)
+        ds = DeviceBuffer.from_numpy(np.full(n, 1e-3, np.float32), 0)
+        dy = DeviceBuffer(m * n * 2, 0)
+        if name == "w8a8":
+            ws = DeviceBuffer(F.linear_w8a8_workspace_bytes(m, k), 0)
+            for _ in range(reps):
+                F.linear_w8a8_device(dy, dx, dw, ds, None, m, n, k, ws, stream=st)
+        else:
+            ws = None if in_kernel else DeviceBuffer(F.linear_workspace_bytes(n, k, "e4m3"), 0)
+            for _ in range(reps):
+                F.linear_q_device(dy, dx, dw, "e4m3", ds, None, m, n, k, ws, stream=st)
+    elif name == "fewrows":
+        m, n, k, reps = arg(0, 16), arg(1, 8192), arg(2, 8192), arg(3, 3)
+        xb, _, _ = workloads.linear_inputs(m, 8, k, seed=0)
+        sets = [(DeviceBuffer.from_numpy(rng.integers(0, 0x7F, (n, k), dtype=np.uint64).astype(np.uint8), 0),
+                 DeviceBuffer(F.linear_workspace_bytes(n, k, "e4m3"), 0)) for _ in range(4)]
+        dx = DeviceBuffer.from_numpy(xb, 0)
+        ds = DeviceBuffer.from_numpy(np.full(n, 1e-3, np.float32), 0)
+        dy = DeviceBuffer(m * n * 2, 0)
+        for r in range(reps * 4):       # four weight copies in rotation: every call reads DRAM
+            dw, ws = sets[r % 4]
+            F.linear_q_device(dy, dx, dw, "e4m3", ds, None, m, n, k, ws, stream=st)
+    elif name == "conv":
+        n, c, hw, cout, reps = arg(0, 128), arg(1, 64), arg(2, 56), arg(3, 128), arg(4, 2)
+        x = np.random.default_rng(0).standard_normal((n, c, hw, hw), dtype=np.float32)
+        wq = rng.integers(0, 0x7F, (cout, c * 9), dtype=np.uint64).astype(np.uint8)
+        dx, dq = DeviceBuffer.from_numpy(x, 0), DeviceBuffer.from_numpy(wq, 0)
+        ds = DeviceBuffer.from_numpy(np.full(cout, 1e-3, np.float32), 0)
+        rows, kpad = n * hw * hw, c * 9
+        col, yb = DeviceBuffer(rows * kpad * 2, 0), DeviceBuffer(rows * cout * 2, 0)
+        ws = DeviceBuffer(F.linear_workspace_bytes(cout, kpad, "e4m3"), 0)
+        out = DeviceBuffer(rows * cout * 4, 0)
+        for _ in range(reps):
+            check(lib().nvq_conv2d_fwd_q(out.at(0), dx.at(0), dq.at(0), _lib.DTYPE_IDS["e4m3"], ds.at(0), None,
+                                         col.at(0), yb.at(0), ws.at(0), ws.nbytes, n, c, hw, hw, cout, 3, 3,
+                                         1, 1, 1, 1, 0, 0, _sptr(st)))
+    elif name == "mlp":
+        from novann_b200.train import MLPTrainStep
+        batch, steps = arg(0, 128), arg(1, 3)
+        x, y, params = workloads.mlp_inputs(batch, seed=0)
+        step = MLPTrainStep(params, batch, lr=0.01)
+        for _ in range(steps):
+            step.step(x, y)
+    elif name == "cnn":
+        from novann_b200.train_cnn import CNNTrainStep, main_cnn_spec
+        batch, steps = arg(0, 128), arg(1, 3)
+        xs, ys, params = workloads.cnn_inputs(batch, steps=1, seed=0)
+        step = CNNTrainStep(main_cnn_spec(), params, batch, (1, 28, 28))
+        for _ in range(steps):
+            step.step(xs[0], ys[0])
+    else:
+        raise SystemExit(f"unknown case {name}")
+    st.sync()
+    device_sync(0)
+    F.check_device_errors(0)
 
 
 def main():
@@ -592,8 +908,12 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--case", default=None, help="run one small case of one kernel and exit")
+    ap.add_argument("case_args", nargs="*", type=int)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case:
+        run_case(args.case, args.case_args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -43,8 +43,9 @@ typedef enum {
     NVQ_BF16 = 2,
     NVQ_E4M3 = 3,     /* FP8 E4M3 "fn": bias 7, no inf, NaN 0x7f/0xff, max 448 */
     NVQ_E5M2 = 4,     /* FP8 E5M2: bias 15, max finite 57344 */
-    NVQ_E2M1_B32 = 5  /* FP4 E2M1, two codes per byte (low nibble first), one fp32
+    NVQ_E2M1_B32 = 5, /* FP4 E2M1, two codes per byte (low nibble first), one fp32
                          scale per 32 consecutive elements of a row */
+    NVQ_F64 = 6       /* float64: what NovaNN's BatchNorm emits (float64 gamma / beta) */
 } nvq_dtype;
 
 typedef enum {
@@ -62,6 +63,11 @@ nvq_status nvq_device_count(int* count);
 /* SM count and total memory of a device (grid sizing / shard sizing). */
 nvq_status nvq_device_info(int device, int* sm_count, size_t* total_bytes, int* cc_major,
                            int* cc_minor);
+/* Frees what the library allocated lazily on every device: the staging buffers and streams of
+ * the host-array calls (nvq_cast_host), and the words behind nvq_device_error_flag.  Buffers,
+ * streams, events, graphs and communicators handed to the caller stay the caller's to free.
+ * No other call of the library may be in flight; later calls allocate again on demand. */
+nvq_status nvq_shutdown(void);
 
 nvq_status nvq_malloc(int device, size_t bytes, void** d_ptr);
 nvq_status nvq_free(int device, void* d_ptr);
@@ -99,8 +105,12 @@ uint64_t nvq_launch_count(void);
  * narrowing, overflow to +-inf, exact widening), extended to bf16.
  *   f32->f16: bit-identical to NumPy astype(float16), NaN payload rule included.
  *   f32->bf16: RNE, any NaN -> sign|0x7fc0.   f16/bf16->f32: exact.
- * Supported pairs: {f32}<->{f16,bf16}.  n elements, any alignment (16-byte
- * aligned pointers take the vectorised path).
+ *   f64->f32 (the narrowing NovaNN really performs, on BatchNorm's float64 output):
+ *   bit-identical to NumPy astype(float32): RNE, overflow to +-inf, subnormal results kept,
+ *   NaN -> sign | 0x7fc00000 | (payload >> 29).   f32->f64: exact, NaN quiet with its
+ *   payload shifted left 29.
+ * Supported pairs: {f32}<->{f16,bf16,f64}.  n elements, any alignment (pointers aligned to
+ * 16 bytes on the narrow side and 32 on the wide side take the vectorised path).
  */
 nvq_status nvq_cast(void* d_dst, nvq_dtype dst_dtype, const void* d_src, nvq_dtype src_dtype,
                     size_t n, int device, void* stream);
@@ -108,7 +118,10 @@ nvq_status nvq_cast(void* d_dst, nvq_dtype dst_dtype, const void* d_src, nvq_dty
 /* Host-buffer variant of nvq_cast: h_src/h_dst are host arrays (pinned memory
  * gives full PCIe rate); the data is streamed through device staging buffers in
  * chunks with H2D, kernel and D2H overlapped.  Synchronous.  This is the call that
- * sits exactly where ndarray.astype sat (host array in, host array out). */
+ * sits exactly where ndarray.astype sat (host array in, host array out).  The staging
+ * buffers (6 x 64 MiB per device) are allocated by the first call on a device and kept
+ * until nvq_shutdown; calls on one device are serialised, calls on different devices
+ * run concurrently. */
 nvq_status nvq_cast_host(void* h_dst, nvq_dtype dst_dtype, const void* h_src,
                          nvq_dtype src_dtype, size_t n, int device);
 
@@ -169,15 +182,31 @@ nvq_status nvq_dequantize_fp4_b32(uint16_t* d_dst_bf16, const uint8_t* d_packed,
  * x = a_m * (p1 + p2 / 16) with a_m a power of two: exact for every element down to
  * 2^-13 of its row's largest, an absolute error <= 2^-21 of the row's largest below
  * that; a non-finite activation makes its output row NaN, and an E5M2 infinity code
- * in the weight gives NaN (the quantiser never emits one).  NVQ_FEW_ROWS_MODE=convert
- * selects the kernel that expands the codes to bf16 in shared memory instead (bf16
- * activations as they are; also the FP4 path).
+ * in the weight gives NaN (the quantiser never emits one).  A caller that needs the bf16
+ * activations taken as they are passes NVQ_LINEAR_BF16_ACTIVATIONS to nvq_linear_fwd_opts:
+ * the kernel that expands the codes to bf16 in shared memory then runs (also the FP4 path).
  */
 nvq_status nvq_linear_workspace_bytes(size_t N, size_t K, nvq_dtype w_fmt, size_t* bytes);
 nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf16, const uint8_t* d_wq,
                           nvq_dtype w_fmt, const float* d_w_scales, const float* d_bias,
                           size_t M, size_t N, size_t K, void* d_workspace, size_t workspace_bytes,
                           int device, void* stream);
+/* nvq_linear_fwd with the kernel path chosen by the caller instead of by the shape rules above.
+ * `path` is NVQ_LINEAR_AUTO (= nvq_linear_fwd) or NVQ_LINEAR_BF16_ACTIVATIONS, optionally
+ * or-ed with at most one of the three kernel selectors.  A kernel selector switches the
+ * few-rows kernels off; NVQ_LINEAR_EXPAND_IN_KERNEL falls back to the expansion pass where the
+ * in-kernel form does not apply (FP4 weights, M <= 128, K % 16 != 0). */
+enum {
+    NVQ_LINEAR_AUTO = 0,
+    NVQ_LINEAR_BF16_ACTIVATIONS = 1 << 0, /* M <= 128: no two-piece E4M3 carrier for the activations */
+    NVQ_LINEAR_EXPAND_IN_KERNEL = 1 << 1, /* FP8 codes expanded in shared memory, nothing written to HBM */
+    NVQ_LINEAR_SINGLE_CTA = 1 << 2,       /* expansion pass + one CTA per 128 x 256 tile */
+    NVQ_LINEAR_CTA_PAIR = 1 << 3          /* expansion pass + CTA pair per 256 x 256 tile */
+};
+nvq_status nvq_linear_fwd_opts(uint16_t* d_y_bf16, const uint16_t* d_x_bf16, const uint8_t* d_wq,
+                               nvq_dtype w_fmt, const float* d_w_scales, const float* d_bias,
+                               size_t M, size_t N, size_t K, void* d_workspace,
+                               size_t workspace_bytes, uint32_t path, int device, void* stream);
 /* W8A8 VARIANT (outside the 1e-2 parity bound; offered for throughput, labelled as such):
  * the bf16 activations are quantised to E4M3 per row (scale_m = amax_m / 448) inside the call and
  * the contraction runs as FP8 x FP8 (tcgen05 kind::f8f6f4), Y = bf16(sx_m * sw_n * sum + b_n).
@@ -218,6 +247,9 @@ nvq_status nvq_linear_bwd_q(float* d_dx, float* d_dw, float* d_db, const float* 
  *    larger weights are rejected with NVQ_ERR_INVALID and a message naming the limit.
  *  - The first call on each device looks up the array's address on that device (a host-side
  *    query, no allocation).  Make that first call before any stream capture begins.
+ *  - For M <= 128 the array holds what the few-rows kernels keep in a workspace instead of an
+ *    expanded weight: fp32 partial sums, the activations' E4M3 codes and their row scales;
+ *    a problem whose partial sums do not fit takes the expanded-weight path.
  *  - Every call on a device shares the one array, and it keeps the previous call's contents.
  *    Each call rewrites every byte it later reads, so nothing needs clearing, but two calls
  *    that overlap on the GPU (different streams, or threads racing on one device) corrupt each
@@ -354,6 +386,17 @@ nvq_status nvq_conv2d_fwd_q(float* d_out, const float* d_x, const uint8_t* d_wq,
                             int C, int H, int W, int Cout, int KH, int KW, int sh, int sw, int ph,
                             int pw, nvq_pad_mode mode, int device, void* stream);
 
+/* nvq_conv2d_fwd_q with the path chosen by the caller: NVQ_CONV_AUTO (= nvq_conv2d_fwd_q),
+ * NVQ_CONV_PATCH_MATRIX (always gather patches and run nvq_linear_fwd) or NVQ_CONV_CTA_PAIR
+ * (implicit GEMM on the CTA-pair kernel where the shape allows an implicit GEMM at all). */
+enum { NVQ_CONV_AUTO = 0, NVQ_CONV_PATCH_MATRIX = 1, NVQ_CONV_CTA_PAIR = 2 };
+nvq_status nvq_conv2d_fwd_q_opts(float* d_out, const float* d_x, const uint8_t* d_wq,
+                                 nvq_dtype w_fmt, const float* d_w_scales, const float* d_bias,
+                                 uint16_t* d_col_bf16, uint16_t* d_y_bf16, void* d_workspace,
+                                 size_t workspace_bytes, int N, int C, int H, int W, int Cout,
+                                 int KH, int KW, int sh, int sw, int ph, int pw, nvq_pad_mode mode,
+                                 uint32_t path, int device, void* stream);
+
 /* ---------------------------------------------------------------- BatchNorm, pooling, Dropout
  * The layers either side of the GEMMs in NovaNN's CNN.  Activations are fp32 (N, C, S)
  * row-major with S = H*W (BatchNorm2d), the sequence length (BatchNorm1d, 3-D input) or 1
@@ -423,6 +466,15 @@ nvq_status nvq_comm_init(const uint8_t id[NVQ_UNIQUE_ID_BYTES], int rank, int wo
 nvq_status nvq_comm_destroy(void* comm);
 /* in-place sum over ranks of an fp32 bucket */
 nvq_status nvq_allreduce_sum_f32(void* comm, float* d_buf, size_t n, int device, void* stream);
+/* Watchdog for the collective: waits on the host until everything enqueued on `stream` has
+ * finished, polling the communicator's asynchronous error state (ncclCommGetAsyncError) every
+ * few hundred microseconds.  Returns NVQ_OK when the stream drained, NVQ_ERR_NCCL when NCCL
+ * reported an error, NVQ_ERR_TIMEOUT when timeout_ms passed first (a peer that never joined
+ * the collective).  After a failure the communicator is unusable: call nvq_comm_abort. */
+nvq_status nvq_comm_wait(void* comm, int device, void* stream, uint32_t timeout_ms);
+/* ncclCommAbort: tears the communicator down without waiting for outstanding collectives
+ * (nvq_comm_destroy waits for them).  The handle is invalid afterwards. */
+nvq_status nvq_comm_abort(void* comm);
 
 #ifdef __cplusplus
 }

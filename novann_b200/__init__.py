@@ -13,7 +13,11 @@ from .losses import CrossEntropyLoss  # noqa: F401
 from .model import Sequential  # noqa: F401
 from .module import Layer, Module, Parameters  # noqa: F401
 from .optim import SGD, AdamW  # noqa: F401
+from .compat import register_if_imported, register_with_novann  # noqa: F401
+
+register_if_imported()
 
 __all__ = ["functional", "quant", "Linear", "QuantLinear", "ReLU", "Conv2d", "QuantConv2d",
            "BatchNorm1d", "BatchNorm2d", "MaxPool2d", "GlobalAvgPool2d", "Flatten", "Dropout",
-           "Sequential", "CrossEntropyLoss", "SGD", "AdamW", "Layer", "Module", "Parameters"]
+           "Sequential", "CrossEntropyLoss", "SGD", "AdamW", "Layer", "Module", "Parameters",
+           "register_with_novann"]

@@ -13,9 +13,13 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("NVQ_LIB", os.path.join(_HERE, "libnvq.so"))
 
 # dtype ids of nvq_dtype
-F32, F16, BF16, E4M3, E5M2, E2M1_B32 = 0, 1, 2, 3, 4, 5
-DTYPE_IDS = {"f32": F32, "f16": F16, "bf16": BF16, "e4m3": E4M3, "e5m2": E5M2, "e2m1_b32": E2M1_B32}
-DTYPE_SIZE = {F32: 4, F16: 2, BF16: 2, E4M3: 1, E5M2: 1}
+F32, F16, BF16, E4M3, E5M2, E2M1_B32, F64 = 0, 1, 2, 3, 4, 5, 6
+DTYPE_IDS = {"f32": F32, "f16": F16, "bf16": BF16, "e4m3": E4M3, "e5m2": E5M2, "e2m1_b32": E2M1_B32,
+             "f64": F64}
+DTYPE_SIZE = {F32: 4, F16: 2, BF16: 2, E4M3: 1, E5M2: 1, F64: 8}
+# path selectors of nvq_linear_fwd_opts / nvq_conv2d_fwd_q_opts
+LINEAR_AUTO, LINEAR_BF16_ACTIVATIONS, LINEAR_EXPAND_IN_KERNEL, LINEAR_SINGLE_CTA, LINEAR_CTA_PAIR = 0, 1, 2, 4, 8
+CONV_AUTO, CONV_PATCH_MATRIX, CONV_CTA_PAIR = 0, 1, 2
 PAD_MODES = {"zeros": 0, "reflect": 1, "replicate": 2, "circular": 3}
 
 OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_NCCL = 0, -1, -2, -3, -4, -5
@@ -31,6 +35,7 @@ SIGNATURES = {
     "nvq_version": (C.c_char_p, []),
     "nvq_device_count": (i32, [C.POINTER(i32)]),
     "nvq_device_info": (i32, [i32, C.POINTER(i32), C.POINTER(sz), C.POINTER(i32), C.POINTER(i32)]),
+    "nvq_shutdown": (i32, []),
     "nvq_malloc": (i32, [i32, sz, pvp]),
     "nvq_free": (i32, [i32, vp]),
     "nvq_host_alloc": (i32, [sz, pvp]),
@@ -64,6 +69,7 @@ SIGNATURES = {
     "nvq_dequantize_fp4_b32": (i32, [vp, vp, vp, sz, sz, i32, vp]),
     "nvq_linear_workspace_bytes": (i32, [sz, sz, i32, C.POINTER(sz)]),
     "nvq_linear_fwd": (i32, [vp, vp, vp, i32, vp, vp, sz, sz, sz, vp, sz, i32, vp]),
+    "nvq_linear_fwd_opts": (i32, [vp, vp, vp, i32, vp, vp, sz, sz, sz, vp, sz, C.c_uint32, i32, vp]),
     "nvq_linear_expand_weight": (i32, [vp, vp, i32, vp, sz, sz, i32, vp]),
     "nvq_linear_fwd_expanded": (i32, [vp, vp, vp, vp, vp, sz, sz, sz, i32, i32, vp]),
     "nvq_linear_w8a8_workspace_bytes": (i32, [sz, sz, C.POINTER(sz)]),
@@ -94,10 +100,14 @@ SIGNATURES = {
     "nvq_dropout_f32": (i32, [vp, vp, vp, sz, f32c, i32, vp]),
     "nvq_adamw_step_f64": (i32, [vp, vp, vp, vp, sz] + [f64c] * 9 + [i32, i32, vp]),
     "nvq_conv2d_fwd_q": (i32, [vp, vp, vp, i32, vp, vp, vp, vp, vp, sz] + [i32] * 11 + [i32, i32, vp]),
+    "nvq_conv2d_fwd_q_opts": (i32, [vp, vp, vp, i32, vp, vp, vp, vp, vp, sz] + [i32] * 11 +
+                              [i32, C.c_uint32, i32, vp]),
     "nvq_comm_unique_id": (i32, [vp]),
     "nvq_comm_init": (i32, [vp, i32, i32, i32, pvp]),
     "nvq_comm_destroy": (i32, [vp]),
     "nvq_allreduce_sum_f32": (i32, [vp, vp, sz, i32, vp]),
+    "nvq_comm_wait": (i32, [vp, i32, vp, C.c_uint32]),
+    "nvq_comm_abort": (i32, [vp]),
     "nvq_linear_fwd_static": (i32, [vp, vp, vp, i32, vp, vp, sz, sz, sz, vp, i32, vp]),
 }
 

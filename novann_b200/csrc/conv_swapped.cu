@@ -286,7 +286,7 @@ nvq_status nvq_conv_launch_swapped(float* d_out, const uint16_t* d_x_nhwc, const
     } else {
         map_out = map_w;   // never used
     }
-    static bool attr_set[64];
+    static std::atomic<bool> attr_set[64];   // per device; setting the attribute twice is harmless
     if (!attr_set[device]) {
         NVQ_CUDA(cudaFuncSetAttribute(conv_swapped_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         attr_set[device] = true;

@@ -63,7 +63,8 @@ nvq_status ew_launch(Op op, const void* src, void* dst, size_t n, int device, cu
     if (n == 0) return NVQ_OK;
     int sms = nvq_sm_count(device);
     if (nvq_aligned(src, src_align) && nvq_aligned(dst, dst_align)) {
-        static int per_sm = 0;
+        static std::atomic<int> per_sm_of[64];   // resident blocks per SM, per device (0 = not asked yet)
+        int per_sm = per_sm_of[device].load(std::memory_order_relaxed);
         if (per_sm == 0) {
             int b = 0;
             NVQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, ew_vector_kernel<Op>,
@@ -73,10 +74,7 @@ nvq_status ew_launch(Op op, const void* src, void* dst, size_t n, int device, cu
             // (measured on B200: ~80-100 KB of loads + stores per SM is the sweet spot; full
             // occupancy costs the write-heavy kernels 5-7 %), so an op may cap its resident blocks.
             if (Op::RESIDENT > 0 && Op::RESIDENT < per_sm) per_sm = Op::RESIDENT;
-            if (const char* e = getenv("NVQ_EW_BLOCKS_PER_SM")) {   // measurement override
-                int v = atoi(e);
-                if (v > 0 && v < per_sm) per_sm = v;
-            }
+            per_sm_of[device].store(per_sm, std::memory_order_relaxed);
         }
         size_t n_packets = n / Op::VEC;
         size_t want = (n_packets + (size_t)kEwThreads * Op::UNROLL - 1) /

@@ -1010,6 +1010,21 @@ extern "C" nvq_status nvq_conv2d_fwd_q(float* d_out, const float* d_x, const uin
                                        size_t workspace_bytes, int N, int C, int H, int W, int Cout,
                                        int KH, int KW, int sh, int sw, int ph, int pw,
                                        nvq_pad_mode mode, int device, void* stream) {
+    return nvq_conv2d_fwd_q_opts(d_out, d_x, d_wq, w_fmt, d_w_scales, d_bias, d_col_bf16, d_y_bf16,
+                                 d_workspace, workspace_bytes, N, C, H, W, Cout, KH, KW, sh, sw, ph, pw,
+                                 mode, NVQ_CONV_AUTO, device, stream);
+}
+
+extern "C" nvq_status nvq_conv2d_fwd_q_opts(float* d_out, const float* d_x, const uint8_t* d_wq,
+                                            nvq_dtype w_fmt, const float* d_w_scales,
+                                            const float* d_bias, uint16_t* d_col_bf16,
+                                            uint16_t* d_y_bf16, void* d_workspace,
+                                            size_t workspace_bytes, int N, int C, int H, int W,
+                                            int Cout, int KH, int KW, int sh, int sw, int ph, int pw,
+                                            nvq_pad_mode mode, uint32_t path, int device,
+                                            void* stream) {
+    NVQ_REQUIRE(path == NVQ_CONV_AUTO || path == NVQ_CONV_PATCH_MATRIX || path == NVQ_CONV_CTA_PAIR,
+                "nvq_conv2d_fwd_q_opts: unknown path selector 0x%x", path);
     ConvGeom g;
     nvq_status s = geom(g, N, C, H, W, KH, KW, sh, sw, ph, pw, mode);
     if (s != NVQ_OK) return s;
@@ -1025,15 +1040,14 @@ extern "C" nvq_status nvq_conv2d_fwd_q(float* d_out, const float* d_x, const uin
     const int Kpad = (C * KH * KW + kq - 1) / kq * kq;
     // Implicit GEMM (no patch matrix): strides 1 or 2, zero padding, channels in blocks of 64, output
     // rows of at most 256 positions (and at most 256 input pixels walked per row).  d_col_bf16 holds x as bf16 NHWC, d_workspace the weight with
-    // its columns reordered to (kh, kw, c).  NVQ_CONV_MODE=explicit forces the patch-matrix path.
-    const char* cmode = getenv("NVQ_CONV_MODE");
-    const bool pair_only = cmode && cmode[0] == 'p';      // the pair kernel's tiles hold 128 positions per CTA
+    // its columns reordered to (kh, kw, c).  NVQ_CONV_PATCH_MATRIX forces the patch-matrix path.
+    const bool pair_only = path == NVQ_CONV_CTA_PAIR;     // the pair kernel's tiles hold 128 positions per CTA
     const bool implicit_ok = sh >= 1 && sh <= 2 && sw >= 1 && sw <= 2 && mode == NVQ_PAD_ZEROS && C % 64 == 0 &&
                              (g.OW <= 128 || (!pair_only && g.OW * sw <= 256)) &&
                              L < (1u << 31) && (size_t)Cout * C * KH * KW < (1u << 31) &&
                              workspace_bytes >= (size_t)Cout * C * KH * KW * 2 && d_workspace &&
                              (size_t)H * W <= (size_t)g.OH * g.OW * KH * KW &&
-                             !(cmode && cmode[0] == 'e');
+                             path != NVQ_CONV_PATCH_MATRIX;
     if (implicit_ok) {
         const int S_in = H * W;
         const size_t cap = (size_t)nvq_sm_count(device) * 16;
@@ -1059,8 +1073,8 @@ extern "C" nvq_status nvq_conv2d_fwd_q(float* d_out, const float* d_x, const uin
         // FP4 block scales are already in the expanded weight; FP8 channel scales go to the epilogue.
         // The operand-swapped kernel is the default: measured 4-13 % faster than the CTA-pair kernel
         // at 256 and 512 output channels and 25 % faster at 128 ([128, 64, 56, 56] -> 128: 0.106 ms
-        // against 0.139 ms).  NVQ_CONV_MODE=pair selects the pair kernel.
-        if (g.OW * sw <= 256 && !(cmode && cmode[0] == 'p'))
+        // against 0.139 ms).  NVQ_CONV_CTA_PAIR selects the pair kernel.
+        if (g.OW * sw <= 256 && !pair_only)
             return nvq_conv_launch_swapped(d_out, d_col_bf16, (const uint16_t*)d_workspace,
                                            w_fmt == NVQ_E2M1_B32 ? nullptr : d_w_scales, d_bias, N, C, H, W,
                                            Cout, KH, KW, ph, pw, sh, sw, device, st);

@@ -215,20 +215,18 @@ fp4_dequant_kernel(const uint8_t* __restrict__ packed, const float* __restrict__
 }
 
 template <class K>
-unsigned pick_grid(K kernel, size_t n_blocks, int device, int* per_sm_cache, int resident_cap) {
-    if (*per_sm_cache == 0) {
+unsigned pick_grid(K kernel, size_t n_blocks, int device, std::atomic<int>* per_sm_of, int resident_cap) {
+    int per_sm = per_sm_of[device].load(std::memory_order_relaxed);
+    if (per_sm == 0) {
         int b = 0;
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, kernel, kThreads, 0);
-        *per_sm_cache = b > 0 ? b : 1;
+        per_sm = b > 0 ? b : 1;
         // fewer resident blocks = less mixed traffic in flight = better DRAM efficiency
-        if (resident_cap > 0 && resident_cap < *per_sm_cache) *per_sm_cache = resident_cap;
-        if (const char* e = getenv("NVQ_EW_BLOCKS_PER_SM")) {   // measurement override
-            int v = atoi(e);
-            if (v > 0 && v < *per_sm_cache) *per_sm_cache = v;
-        }
+        if (resident_cap > 0 && resident_cap < per_sm) per_sm = resident_cap;
+        per_sm_of[device].store(per_sm, std::memory_order_relaxed);
     }
     size_t want = (n_blocks + (size_t)kThreads * kUnroll - 1) / ((size_t)kThreads * kUnroll);
-    size_t cap = (size_t)nvq_sm_count(device) * *per_sm_cache;
+    size_t cap = (size_t)nvq_sm_count(device) * per_sm;
     return (unsigned)(want < 1 ? 1 : (want < cap ? want : cap));
 }
 
@@ -245,8 +243,8 @@ extern "C" nvq_status nvq_quantize_fp4_b32(uint8_t* d_packed, float* d_scales,
                 "nvq_quantize_fp4_b32: src must be 32-byte, packed 16-byte, scales 4-byte aligned");
     nvq_status s = nvq_use_device(device);
     if (s != NVQ_OK) return s;
-    static int per_sm = 0;
-    unsigned grid = pick_grid(fp4_quant_kernel, n_blocks, device, &per_sm, 3);
+    static std::atomic<int> per_sm_of[64];
+    unsigned grid = pick_grid(fp4_quant_kernel, n_blocks, device, per_sm_of, 3);
     fp4_quant_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>(d_src_bf16, d_packed, d_scales,
                                                                   n_blocks);
     NVQ_LAUNCHED();
@@ -264,8 +262,8 @@ extern "C" nvq_status nvq_dequantize_fp4_b32(uint16_t* d_dst_bf16, const uint8_t
                 "nvq_dequantize_fp4_b32: dst must be 32-byte, packed 16-byte, scales 4-byte aligned");
     nvq_status s = nvq_use_device(device);
     if (s != NVQ_OK) return s;
-    static int per_sm = 0;
-    unsigned grid = pick_grid(fp4_dequant_kernel, n_blocks, device, &per_sm, 2);
+    static std::atomic<int> per_sm_of[64];
+    unsigned grid = pick_grid(fp4_dequant_kernel, n_blocks, device, per_sm_of, 2);
     fp4_dequant_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>(d_packed, d_scales, d_dst_bf16,
                                                                     n_blocks);
     NVQ_LAUNCHED();

@@ -348,11 +348,13 @@ quantize_rows_bf16_fast_kernel(uint8_t* __restrict__ dst, float* __restrict__ sc
 nvq_status launch_amax(const float* d_src, size_t n, float* d_amax, int device, cudaStream_t st) {
     NVQ_CUDA(cudaMemsetAsync(d_amax, 0, sizeof(float), st));
     if (n == 0) return NVQ_OK;
-    static int per_sm = 0;
+    static std::atomic<int> per_sm_of[64];   // per device
+    int per_sm = per_sm_of[device].load(std::memory_order_relaxed);
     if (per_sm == 0) {
         int b = 0;
         NVQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, amax_kernel, 256, 0));
         per_sm = b > 0 ? b : 1;
+        per_sm_of[device].store(per_sm, std::memory_order_relaxed);
     }
     size_t want = (n / 8 + 256 * 4 - 1) / (256 * 4);
     size_t cap = (size_t)nvq_sm_count(device) * per_sm;

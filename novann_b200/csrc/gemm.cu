@@ -17,6 +17,8 @@
 // No TMA multicast and no peer memory anywhere: each CTA fetches its own tiles.
 #include <stdlib.h>
 
+#include <mutex>
+
 #include "elementwise.cuh"
 #include "gemm_common.cuh"
 
@@ -254,6 +256,7 @@ int* g_status_dev[64];
 }  // namespace
 
 // set by the allocation-free entry point for the duration of its launches (per thread)
+static std::mutex g_status_mu;
 static thread_local bool t_status_override = false;
 static thread_local int* t_status_override_ptr = nullptr;
 
@@ -262,10 +265,13 @@ nvq_status nvq_status_word(int device, int** dev_ptr) {
         *dev_ptr = t_status_override_ptr;
         return NVQ_OK;
     }
+    std::lock_guard<std::mutex> lock(g_status_mu);
     if (!g_status_host[device]) {
-        NVQ_CUDA(cudaHostAlloc((void**)&g_status_host[device], sizeof(int), cudaHostAllocMapped));
-        *g_status_host[device] = 0;
-        NVQ_CUDA(cudaHostGetDevicePointer((void**)&g_status_dev[device], g_status_host[device], 0));
+        int* h = nullptr;
+        NVQ_CUDA(cudaHostAlloc((void**)&h, sizeof(int), cudaHostAllocMapped));
+        *h = 0;
+        NVQ_CUDA(cudaHostGetDevicePointer((void**)&g_status_dev[device], h, 0));
+        g_status_host[device] = h;
     }
     *dev_ptr = g_status_dev[device];
     return NVQ_OK;
@@ -355,7 +361,7 @@ nvq_status nvq_linear_launch_single(uint16_t* d_y, const uint16_t* d_x, const ui
     if (s != NVQ_OK) return s;
     s = nvq_make_tmap_2d(&map_b, d_w_bf16, N, K, BN / 2, BK, 2, 1);
     if (s != NVQ_OK) return s;
-    static bool attr_set[64];
+    static std::atomic<bool> attr_set[64];   // per device; setting the attribute twice is harmless
     if (!attr_set[device]) {
         NVQ_CUDA(cudaFuncSetAttribute(linear_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         attr_set[device] = true;
@@ -390,18 +396,14 @@ nvq_status nvq_linear_launch_single(uint16_t* d_y, const uint16_t* d_x, const ui
 
 // Y = bf16(scale_n * X @ Wd^T + bias_n) with Wd already expanded to bf16 (N x K).
 // More than 128 rows: CTA pairs on 256 x 256 tiles; otherwise one CTA per 128 x 256 tile.
-// NVQ_LINEAR_MODE=single|pair overrides the choice (for measurements).
+// `kernel` (0 = by M, 1 = single CTA, 2 = CTA pair) carries the caller's path selector.
 nvq_status nvq_linear_bf16_launch(uint16_t* d_y, const uint16_t* d_x, const uint16_t* d_w_bf16,
                                   const float* d_scales, const float* d_bias, size_t M, size_t N,
-                                  size_t K, int out_f32, int device, cudaStream_t st) {
+                                  size_t K, int out_f32, int device, cudaStream_t st, int kernel) {
     NVQ_REQUIRE(K % 8 == 0 && N % 8 == 0, "nvq_linear_fwd: K (%zu) and N (%zu) must be multiples of 8", K, N);
     NVQ_REQUIRE(nvq_aligned(d_y, 32), "nvq_linear_fwd: Y must be 32-byte aligned");
     NVQ_REQUIRE(M < (1u << 31) && N < (1u << 31) && K < (1u << 31), "nvq_linear_fwd: dimension too large");
-    bool pair = M > 128;
-    if (const char* mode = getenv("NVQ_LINEAR_MODE")) {
-        if (mode[0] == 's') pair = false;
-        if (mode[0] == 'p') pair = true;
-    }
+    const bool pair = kernel == 2 || (kernel == 0 && M > 128);
     if (pair) return nvq_linear_launch_pair(d_y, d_x, d_w_bf16, d_scales, d_bias, M, N, K, out_f32, device, st);
     return nvq_linear_launch_single(d_y, d_x, d_w_bf16, d_scales, d_bias, M, N, K, out_f32, device, st);
 }
@@ -443,9 +445,22 @@ extern "C" nvq_status nvq_selftest_bounded_wait(int device, void* stream) {
     return NVQ_OK;
 }
 
+// Frees the status words of every device (nvq_shutdown).
+nvq_status nvq_gemm_release_status_words() {
+    std::lock_guard<std::mutex> lock(g_status_mu);
+    for (int d = 0; d < 64; d++) {
+        if (!g_status_host[d]) continue;
+        NVQ_CUDA(cudaFreeHost(g_status_host[d]));
+        g_status_host[d] = nullptr;
+        g_status_dev[d] = nullptr;
+    }
+    return NVQ_OK;
+}
+
 extern "C" nvq_status nvq_device_error_flag(int device, int* flag) {
     NVQ_REQUIRE(flag && device >= 0 && device < 64, "bad argument");
     *flag = 0;
+    std::lock_guard<std::mutex> lock(g_status_mu);
     if (g_status_host[device]) {
         *flag = *(volatile int*)g_status_host[device];
         *(volatile int*)g_status_host[device] = 0;
@@ -491,7 +506,22 @@ extern "C" nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf1
                                      const float* d_bias, size_t M, size_t N, size_t K,
                                      void* d_workspace, size_t workspace_bytes, int device,
                                      void* stream) {
+    return nvq_linear_fwd_opts(d_y_bf16, d_x_bf16, d_wq, w_fmt, d_w_scales, d_bias, M, N, K, d_workspace,
+                               workspace_bytes, NVQ_LINEAR_AUTO, device, stream);
+}
+
+extern "C" nvq_status nvq_linear_fwd_opts(uint16_t* d_y_bf16, const uint16_t* d_x_bf16,
+                                          const uint8_t* d_wq, nvq_dtype w_fmt,
+                                          const float* d_w_scales, const float* d_bias, size_t M,
+                                          size_t N, size_t K, void* d_workspace,
+                                          size_t workspace_bytes, uint32_t path, int device,
+                                          void* stream) {
     NVQ_REQUIRE(d_y_bf16 && d_x_bf16 && d_wq && d_w_scales, "nvq_linear_fwd: null buffer");
+    const uint32_t kernel_bits = path & (NVQ_LINEAR_EXPAND_IN_KERNEL | NVQ_LINEAR_SINGLE_CTA | NVQ_LINEAR_CTA_PAIR);
+    NVQ_REQUIRE((path & ~(uint32_t)(NVQ_LINEAR_BF16_ACTIVATIONS | NVQ_LINEAR_EXPAND_IN_KERNEL |
+                                    NVQ_LINEAR_SINGLE_CTA | NVQ_LINEAR_CTA_PAIR)) == 0 &&
+                    (kernel_bits & (kernel_bits - 1)) == 0,
+                "nvq_linear_fwd_opts: unknown or contradictory path selector 0x%x", path);
     NVQ_REQUIRE(M > 0 && N > 0 && K > 0, "nvq_linear_fwd: empty problem");
     NVQ_REQUIRE(w_fmt == NVQ_E4M3 || w_fmt == NVQ_E5M2 || w_fmt == NVQ_E2M1_B32,
                 "nvq_linear_fwd: unsupported weight format %d", (int)w_fmt);
@@ -502,10 +532,9 @@ extern "C" nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf1
     // memory itself, so no expanded copy of the weight is written to HBM and no workspace is
     // needed.  Measured on B200 it is slower than expansion pass + plain pair kernel (the
     // converter warps' shared-memory traffic competes with the tensor core's operand reads),
-    // so it runs when the caller passes no workspace, or on request (NVQ_LINEAR_MODE=fused).
-    const char* mode = getenv("NVQ_LINEAR_MODE");
+    // so it runs when the caller passes no workspace, or asks for it (NVQ_LINEAR_EXPAND_IN_KERNEL).
     bool can_fuse = w_fmt != NVQ_E2M1_B32 && M > 128 && K % 16 == 0 && nvq_aligned(d_wq, 16);
-    bool fused = can_fuse && ((mode && mode[0] == 'f') || (!mode && d_workspace == nullptr));
+    bool fused = can_fuse && ((path & NVQ_LINEAR_EXPAND_IN_KERNEL) || (!kernel_bits && d_workspace == nullptr));
     if (fused) {
         NVQ_REQUIRE(K % 8 == 0 && N % 8 == 0, "nvq_linear_fwd: K (%zu) and N (%zu) must be multiples of 8", K, N);
         NVQ_REQUIRE(nvq_aligned(d_y_bf16, 32), "nvq_linear_fwd: Y must be 32-byte aligned");
@@ -516,13 +545,12 @@ extern "C" nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf1
     // Few rows: the time is the time to read the weight, so read it once, as codes.  The
     // workspace then holds fp32 partial sums instead of an expanded weight.
     if (M <= 128 && K % (w_fmt == NVQ_E2M1_B32 ? 32 : 16) == 0 && nvq_aligned(d_wq, 16) && nvq_aligned(d_x_bf16, 16) &&
-        d_workspace && nvq_aligned(d_workspace, 16) && !mode && M * N < (1u << 31) && N < (1u << 24) &&
+        d_workspace && nvq_aligned(d_workspace, 16) && !kernel_bits && M * N < (1u << 31) && N < (1u << 24) &&
         K < (1u << 24) && N * K < (1ull << 40) &&
         workspace_bytes >= nvq_linear_small_m_workspace(M, N, K, device)) {
         // FP8 codes feed the tensor cores directly (activations split into two E4M3 rows);
-        // NVQ_FEW_ROWS_MODE=convert keeps the kernel that expands the codes to bf16
-        const char* few = getenv("NVQ_FEW_ROWS_MODE");
-        if (w_fmt != NVQ_E2M1_B32 && !(few && few[0] == 'c') &&
+        // NVQ_LINEAR_BF16_ACTIVATIONS keeps the kernel that expands the codes to bf16
+        if (w_fmt != NVQ_E2M1_B32 && !(path & NVQ_LINEAR_BF16_ACTIVATIONS) &&
             workspace_bytes >= nvq_linear_small_m_direct_workspace(M, N, K, device))
             return nvq_linear_launch_small_m_direct(d_y_bf16, d_x_bf16, d_wq, w_fmt, d_w_scales, d_bias, M, N,
                                                     K, d_workspace, device, st);
@@ -535,7 +563,8 @@ extern "C" nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf1
     if (s != NVQ_OK) return s;
     uint16_t* wd = (uint16_t*)d_workspace;
     const float* chan_scales = w_fmt == NVQ_E2M1_B32 ? nullptr : d_w_scales;
-    return nvq_linear_bf16_launch(d_y_bf16, d_x_bf16, wd, chan_scales, d_bias, M, N, K, 0, device, st);
+    return nvq_linear_bf16_launch(d_y_bf16, d_x_bf16, wd, chan_scales, d_bias, M, N, K, 0, device, st,
+                                  (path & NVQ_LINEAR_SINGLE_CTA) ? 1 : ((path & NVQ_LINEAR_CTA_PAIR) ? 2 : 0));
 }
 
 // ---------------------------------------------------------------- allocation-free variant

@@ -27,10 +27,11 @@ struct LinearParams {
 
 nvq_status nvq_status_word(int device, int** dev_ptr);
 
-// Y = scale_n * X @ Wd^T + bias_n with Wd (N x K) already 16-bit; Y bf16 or fp32 (out_f32)
+// Y = scale_n * X @ Wd^T + bias_n with Wd (N x K) already 16-bit; Y bf16 or fp32 (out_f32).
+// kernel: 0 = chosen by M, 1 = one CTA per 128 x 256 tile, 2 = CTA pair per 256 x 256 tile.
 nvq_status nvq_linear_bf16_launch(uint16_t* d_y, const uint16_t* d_x, const uint16_t* d_w_bf16,
                                   const float* d_scales, const float* d_bias, size_t M, size_t N,
-                                  size_t K, int out_f32, int device, cudaStream_t st);
+                                  size_t K, int out_f32, int device, cudaStream_t st, int kernel = 0);
 
 // launchers (gemm.cu: one CTA per 128 x 256 tile; gemm_pair.cu: CTA pair per 256 x 256 tile)
 nvq_status nvq_linear_launch_single(uint16_t* d_y, const uint16_t* d_x, const uint16_t* d_w,

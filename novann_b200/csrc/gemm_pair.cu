@@ -36,10 +36,7 @@ constexpr int TMEM_COLS = 512;
 constexpr int MAX_STAGES = 6;
 constexpr int EPI_WARPS = 8;               // warps 2 .. 9
 constexpr int FIRST_CONV_WARP = 2 + EPI_WARPS;
-#ifndef NVQ_PAIR_CONV_GROUPS
-#define NVQ_PAIR_CONV_GROUPS 2
-#endif
-constexpr int PAIR_CONV_GROUPS = NVQ_PAIR_CONV_GROUPS;   // fused variant: k-blocks expanded concurrently
+constexpr int PAIR_CONV_GROUPS = 2;        // fused variant: k-blocks expanded concurrently
 static_assert(PAIR_CONV_GROUPS == 1 || PAIR_CONV_GROUPS == 2, "the five-slot ring feeds at most two groups");
 
 // FUSED = 0: B comes expanded (bf16) from a workspace.  FUSED = NVQ_E4M3 / NVQ_E5M2: B comes as
@@ -464,7 +461,7 @@ static nvq_status launch_pair(uint16_t* d_y, const void* d_x, const void* d_w,
            : (FUSED ? nvq_make_tmap_2d(&map_b, d_w, N, K, 64, BK, 1, 0)
                     : nvq_make_tmap_2d(&map_b, d_w, N, K, 64, BK, 2, 1));
     if (s != NVQ_OK) return s;
-    static bool attr_set[64];
+    static std::atomic<bool> attr_set[64];   // per device; setting the attribute twice is harmless
     if (!attr_set[device]) {
         NVQ_CUDA(cudaFuncSetAttribute(linear_tc_pair_kernel<FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Cfg<FUSED>::SMEM_BYTES));
@@ -529,7 +526,7 @@ static nvq_status launch_implicit_conv(float* d_out, const uint16_t* d_x_nhwc, c
     if (s != NVQ_OK) return s;
     s = nvq_make_tmap_2d(&map_b, d_w, Cout, K, 64, BK, 2, 1);
     if (s != NVQ_OK) return s;
-    static bool attr_set[64];
+    static std::atomic<bool> attr_set[64];   // per device; setting the attribute twice is harmless
     if (!attr_set[device]) {
         NVQ_CUDA(cudaFuncSetAttribute(linear_tc_pair_kernel<kImplicitConv>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -398,7 +398,7 @@ nvq_status nvq_linear_launch_small_m(uint16_t* d_y, const uint16_t* d_x, const u
     if (s != NVQ_OK) return s;
     s = nvq_make_tmap_2d(&map_x, d_x, M, K, (uint32_t)p.MP, BK, 2, 1);  // bf16, 128-byte swizzle
     if (s != NVQ_OK) return s;
-    static bool attr_set[64][3];
+    static std::atomic<bool> attr_set[64][3];   // per device and format; setting twice is harmless
     const int fi = fmt == NVQ_E4M3 ? 0 : (fmt == NVQ_E5M2 ? 1 : 2);
     if (!attr_set[device][fi]) {
         if (fi == 0)

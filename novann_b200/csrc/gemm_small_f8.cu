@@ -441,7 +441,7 @@ nvq_status nvq_linear_launch_small_m_direct(uint16_t* d_y, const uint16_t* d_x, 
     if (s != NVQ_OK) return s;
     s = nvq_make_tmap_2d(&map_x, d_x8, (uint64_t)2 * g.MP, K, (uint32_t)(2 * g.MP), BKC, 1, 1);
     if (s != NVQ_OK) return s;
-    static bool attr_set[64];
+    static std::atomic<bool> attr_set[64];   // per device; setting the attribute twice is harmless
     if (!attr_set[device]) {
         NVQ_CUDA(cudaFuncSetAttribute(linear_small_m_direct_kernel<NVQ_E4M3>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));

@@ -39,6 +39,10 @@ nvq_status nvq_use_device(int device) {
     return NVQ_OK;
 }
 
+// lazily allocated per-device state of other translation units (see nvq_shutdown)
+nvq_status nvq_cast_release_staging();
+nvq_status nvq_gemm_release_status_words();
+
 int nvq_sm_count(int device) { return g_sm_count[device] > 0 ? g_sm_count[device] : 148; }
 
 extern "C" {
@@ -63,6 +67,12 @@ nvq_status nvq_device_info(int device, int* sm_count, size_t* total_bytes, int* 
     if (cc_major) *cc_major = p.major;
     if (cc_minor) *cc_minor = p.minor;
     return NVQ_OK;
+}
+
+nvq_status nvq_shutdown(void) {
+    nvq_status a = nvq_cast_release_staging();
+    nvq_status b = nvq_gemm_release_status_words();
+    return a != NVQ_OK ? a : b;
 }
 
 nvq_status nvq_malloc(int device, size_t bytes, void** d_ptr) {

@@ -29,20 +29,31 @@ def check_device_errors(device: int = 0) -> None:
         raise _lib.NvqError(_lib.ERR_TIMEOUT, f"device-side wait gave up (code {flag.value})")
 
 
+_LINEAR_PATHS = {None: _lib.LINEAR_AUTO, "auto": _lib.LINEAR_AUTO,
+                 "bf16_activations": _lib.LINEAR_BF16_ACTIVATIONS,
+                 "expand_in_kernel": _lib.LINEAR_EXPAND_IN_KERNEL,
+                 "single_cta": _lib.LINEAR_SINGLE_CTA, "cta_pair": _lib.LINEAR_CTA_PAIR}
+_CONV_PATHS = {None: _lib.CONV_AUTO, "auto": _lib.CONV_AUTO, "patch_matrix": _lib.CONV_PATCH_MATRIX,
+               "cta_pair": _lib.CONV_CTA_PAIR}
+
+
 def linear_q_device(y: DeviceBuffer, x: DeviceBuffer, wq: DeviceBuffer, fmt: str,
                     w_scales: DeviceBuffer, bias: DeviceBuffer | None, m: int, n: int, k: int,
-                    workspace: DeviceBuffer | None, stream=None) -> None:
-    """``workspace=None`` selects the in-kernel expansion of FP8 codes (M > 128, K % 16 == 0)."""
-    check(lib().nvq_linear_fwd(y.at(0), x.at(0), wq.at(0), _lib.DTYPE_IDS[fmt], w_scales.at(0),
-                               bias.at(0) if bias is not None else None, m, n, k,
-                               workspace.at(0) if workspace is not None else None,
-                               workspace.nbytes if workspace is not None else 0,
-                               x.device, _sptr(stream)))
+                    workspace: DeviceBuffer | None, stream=None, path: str | None = None) -> None:
+    """``workspace=None`` selects the in-kernel expansion of FP8 codes (M > 128, K % 16 == 0).
+    ``path`` names a kernel path of ``nvq_linear_fwd_opts``: ``"bf16_activations"`` (M <= 128:
+    activations taken as bf16, no two-piece E4M3 carrier), ``"expand_in_kernel"``,
+    ``"single_cta"``, ``"cta_pair"``; ``None`` lets the library choose."""
+    check(lib().nvq_linear_fwd_opts(y.at(0), x.at(0), wq.at(0), _lib.DTYPE_IDS[fmt], w_scales.at(0),
+                                    bias.at(0) if bias is not None else None, m, n, k,
+                                    workspace.at(0) if workspace is not None else None,
+                                    workspace.nbytes if workspace is not None else 0,
+                                    _LINEAR_PATHS[path], x.device, _sptr(stream)))
 
 
 def linear_q_host(x_bf16_bits: np.ndarray, wq: np.ndarray, w_scales: np.ndarray,
                   bias: np.ndarray | None, fmt: str = "e4m3", device: int = 0,
-                  use_workspace: bool = True) -> np.ndarray:
+                  use_workspace: bool = True, path: str | None = None) -> np.ndarray:
     """Host arrays in, bf16 bits (M, N) out."""
     x = np.ascontiguousarray(x_bf16_bits, np.uint16)
     m, k = x.shape
@@ -53,25 +64,79 @@ def linear_q_host(x_bf16_bits: np.ndarray, wq: np.ndarray, w_scales: np.ndarray,
     db = DeviceBuffer.from_numpy(np.ascontiguousarray(bias, np.float32), device) if bias is not None else None
     dy = DeviceBuffer(m * n * 2, device)
     ws = DeviceBuffer(linear_workspace_bytes(n, k, fmt), device) if use_workspace else None
-    linear_q_device(dy, dx, dw, fmt, ds, db, m, n, k, ws)
+    linear_q_device(dy, dx, dw, fmt, ds, db, m, n, k, ws, path=path)
     device_sync(device)
     check_device_errors(device)
     return dy.to_numpy(np.uint16, (m, n))
 
 
+# ------------------------------------------------------------------ the reference's signatures
+_default_device = 0
+
+
+def set_default_device(device: int) -> None:
+    """GPU used by ``linear`` / ``conv2d`` below when no ``device=`` is given."""
+    global _default_device
+    _default_device = int(device)
+
+
+def _data(p):
+    """``Parameters`` (anything with ``.data``) or a bare array."""
+    return p.data if hasattr(p, "data") else p
+
+
+def linear(input: np.ndarray, weight, bias=None, *, device: int | None = None) -> np.ndarray:
+    """``F.linear(input, weight, bias)`` with the reference's signature
+    (novann/functional.py:147-163): ``weight`` / ``bias`` are ``Parameters`` (their ``.data`` is
+    read; bare arrays are taken too), result ``input @ weight.data.T + bias.data`` as float32,
+    computed on the GPU."""
+    dev = _default_device if device is None else device
+    return linear_f32_host(input, _data(weight), None if bias is None else _data(bias), dev)
+
+
+def conv2d(input: np.ndarray, weight, kernel_size, stride=1, padding=0, *, bias=None,
+           padding_mode: str = "zeros", extras: bool = False, device: int | None = None):
+    """``F.conv2d`` with the reference's signature (novann/functional.py:275-385):
+    ``kernel_size`` / ``stride`` / ``padding`` ints or pairs (``"valid"`` = 0, ``"same"``
+    refused), ``padding_mode`` one of zeros / reflect / replicate / circular.  Returns ``out``
+    (N, Cout, OH, OW) float32, or ``(out, col, w_col)`` with ``extras`` - ``col`` the im2col
+    matrix (C*KH*KW, N*OH*OW) built on the GPU, ``w_col`` the weight viewed (Cout, C*KH*KW)."""
+    from .layers import _pair
+    dev = _default_device if device is None else device
+    kh, kw = _pair(kernel_size)
+    w = _data(weight)
+    if tuple(w.shape[2:]) != (kh, kw):
+        raise ValueError(f"kernel_size {(kh, kw)} does not match the weight's {tuple(w.shape[2:])}")
+    res = conv2d_f32_host(input, w, None if bias is None else _data(bias), _pair(stride), _pair(padding),
+                          padding_mode, dev, return_col=extras)
+    if extras:
+        out, col = res
+        return out, col, np.asarray(w).reshape(w.shape[0], -1)
+    return res
+
+
 # ------------------------------------------------------------------ fp32 layers (host arrays)
-def _f32(a):
+def _f32(a, device: int = 0):
+    """Contiguous float32 view of a host array.  float32 passes through; float64 / float16
+    arrays (a reference BatchNorm hands float64 to its neighbours) are converted by the GPU
+    cast, as the layers' ``astype(np.float32, copy=False)`` would on the CPU."""
+    a = np.asarray(a)
+    if a.dtype == np.float32:
+        return np.ascontiguousarray(a)
+    if a.dtype in (np.float64, np.float16) and a.size:
+        from . import quant
+        return quant.cast(a, np.float32, device=device)
     return np.ascontiguousarray(a, np.float32)
 
 
 def linear_f32_host(x, w, b=None, device: int = 0, relu: bool = False):
     """``F.linear`` (novann/functional.py:147-163) in fp32 on the GPU.  With ``relu`` the
     fused ``F.relu`` is applied and (out, mask) is returned."""
-    x, w = _f32(x), _f32(w)
+    x, w = _f32(x, device), _f32(w, device)
     m, k = x.shape
     n = w.shape[0]
     dx, dw = DeviceBuffer.from_numpy(x, device), DeviceBuffer.from_numpy(w, device)
-    db = DeviceBuffer.from_numpy(_f32(b).reshape(-1), device) if b is not None else None
+    db = DeviceBuffer.from_numpy(_f32(b, device).reshape(-1), device) if b is not None else None
     dy = DeviceBuffer(max(4, m * n * 4), device)
     dm = DeviceBuffer(max(4, m * n * 4), device) if relu else None
     check(lib().nvq_linear_fwd_f32(dy.at(0), dx.at(0), dw.at(0), db.at(0) if db else None, m, n, k,
@@ -83,12 +148,12 @@ def linear_f32_host(x, w, b=None, device: int = 0, relu: bool = False):
 def linear_bwd_f32_host(grad, x, w, with_bias: bool = True, device: int = 0, mask=None):
     """``Linear.backward`` (novann/layers/linear/linear.py:85-108): returns (dW (N,K),
     db (1,N) or None, dX (M,K)); ``mask`` (M,K) multiplies dX (``ReLU.backward``)."""
-    grad, x, w = _f32(grad), _f32(x), _f32(w)
+    grad, x, w = _f32(grad, device), _f32(x, device), _f32(w, device)
     m, n = grad.shape
     k = x.shape[1]
     dg, dx, dw = (DeviceBuffer.from_numpy(a, device) for a in (grad, x, w))
     o_dw, o_db, o_dx = DeviceBuffer(n * k * 4, device), DeviceBuffer(n * 4, device), DeviceBuffer(m * k * 4, device)
-    dmask = DeviceBuffer.from_numpy(_f32(mask), device) if mask is not None else None
+    dmask = DeviceBuffer.from_numpy(_f32(mask, device), device) if mask is not None else None
     check(lib().nvq_linear_bwd_f32(o_dw.at(0), o_db.at(0) if with_bias else None, o_dx.at(0), dg.at(0),
                                    dx.at(0), dw.at(0), dmask.at(0) if dmask else None, m, n, k,
                                    device, None))
@@ -99,7 +164,7 @@ def linear_bwd_f32_host(grad, x, w, with_bias: bool = True, device: int = 0, mas
 
 def relu_host(x, device: int = 0):
     """``F.relu(x, extras=True)`` (novann/functional.py:8-22): returns (out, mask)."""
-    x = _f32(x)
+    x = _f32(x, device)
     d = DeviceBuffer.from_numpy(x, device)
     o, mk = DeviceBuffer(max(4, x.nbytes), device), DeviceBuffer(max(4, x.nbytes), device)
     check(lib().nvq_relu_fwd_f32(o.at(0), mk.at(0), d.at(0), x.size, device, None))
@@ -108,7 +173,7 @@ def relu_host(x, device: int = 0):
 
 def softmax_ce_host(logits, labels, device: int = 0):
     """``CrossEntropyLoss.__call__`` (novann/losses/loss_functions.py:69-75): (loss, grad)."""
-    z = _f32(logits)
+    z = _f32(logits, device)
     m, c = z.shape
     lab = np.ascontiguousarray(labels, np.int32)
     dz, dl = DeviceBuffer.from_numpy(z, device), DeviceBuffer.from_numpy(lab, device)
@@ -133,13 +198,13 @@ def conv2d_f32_host(x, w, b=None, stride=(1, 1), padding=(0, 0), padding_mode: s
                     device: int = 0, return_col: bool = False):
     """``F.conv2d`` (novann/functional.py:275-385) in fp32 on the GPU: (N,Cout,OH,OW), and with
     ``return_col`` also the im2col matrix (C*KH*KW, N*OH*OW) the reference caches."""
-    x, w = _f32(x), _f32(w)
+    x, w = _f32(x, device), _f32(w, device)
     n, c, h, wd = x.shape
     cout, _, kh, kw = w.shape
     mode = _pad_mode(padding_mode)
     oh, ow = conv2d_out_size(h, wd, kh, kw, stride[0], stride[1], padding[0], padding[1])
     dx, dw = DeviceBuffer.from_numpy(x, device), DeviceBuffer.from_numpy(w, device)
-    db = DeviceBuffer.from_numpy(_f32(b).reshape(-1), device) if b is not None else None
+    db = DeviceBuffer.from_numpy(_f32(b, device).reshape(-1), device) if b is not None else None
     col = DeviceBuffer(max(4, c * kh * kw * n * oh * ow * 4), device)
     out = DeviceBuffer(max(4, n * cout * oh * ow * 4), device)
     check(lib().nvq_conv2d_fwd_f32(out.at(0), dx.at(0), dw.at(0), db.at(0) if db else None, col.at(0),
@@ -152,12 +217,13 @@ def conv2d_f32_host(x, w, b=None, stride=(1, 1), padding=(0, 0), padding_mode: s
 
 
 def conv2d_q_host(x, wq, w_scales, b, kernel, stride=(1, 1), padding=(0, 0),
-                  padding_mode: str = "zeros", fmt: str = "e4m3", device: int = 0):
+                  padding_mode: str = "zeros", fmt: str = "e4m3", device: int = 0,
+                  path: str | None = None):
     """Quantised-weight ``F.conv2d``: ``wq`` is (Cout, kpad) FP8 codes of the zero-padded
     ``w.reshape(Cout, C*KH*KW)`` with ``w_scales`` (Cout,), or for ``fmt="e2m1_b32"`` the packed
     (Cout, kpad/2) FP4 codes with block scales (Cout, kpad/32), kpad a multiple of 32.  Returns
     fp32 (N,Cout,OH,OW)."""
-    x = _f32(x)
+    x = _f32(x, device)
     n, c, h, wd = x.shape
     kh, kw = kernel
     cout = wq.shape[0]
@@ -174,16 +240,16 @@ def conv2d_q_host(x, wq, w_scales, b, kernel, stride=(1, 1), padding=(0, 0),
     oh, ow = conv2d_out_size(h, wd, kh, kw, stride[0], stride[1], padding[0], padding[1])
     dx = DeviceBuffer.from_numpy(x, device)
     dq = DeviceBuffer.from_numpy(np.ascontiguousarray(wq, np.uint8), device)
-    ds = DeviceBuffer.from_numpy(_f32(w_scales), device)
-    db = DeviceBuffer.from_numpy(_f32(b).reshape(-1), device) if b is not None else None
+    ds = DeviceBuffer.from_numpy(_f32(w_scales, device), device)
+    db = DeviceBuffer.from_numpy(_f32(b, device).reshape(-1), device) if b is not None else None
     col = DeviceBuffer(rows.value * kpad.value * 2, device)
     yb = DeviceBuffer(rows.value * cout * 2, device)
     ws = DeviceBuffer(linear_workspace_bytes(cout, kpad.value, fmt), device)
     out = DeviceBuffer(n * cout * oh * ow * 4, device)
-    check(lib().nvq_conv2d_fwd_q(out.at(0), dx.at(0), dq.at(0), _lib.DTYPE_IDS[fmt], ds.at(0),
-                                 db.at(0) if db else None, col.at(0), yb.at(0), ws.at(0), ws.nbytes,
-                                 n, c, h, wd, cout, kh, kw, stride[0], stride[1], padding[0], padding[1],
-                                 mode, device, None))
+    check(lib().nvq_conv2d_fwd_q_opts(out.at(0), dx.at(0), dq.at(0), _lib.DTYPE_IDS[fmt], ds.at(0),
+                                      db.at(0) if db else None, col.at(0), yb.at(0), ws.at(0), ws.nbytes,
+                                      n, c, h, wd, cout, kh, kw, stride[0], stride[1], padding[0],
+                                      padding[1], mode, _CONV_PATHS[path], device, None))
     device_sync(device)
     check_device_errors(device)
     return out.to_numpy(np.float32, (n, cout, oh, ow))
@@ -192,7 +258,7 @@ def conv2d_q_host(x, wq, w_scales, b, kernel, stride=(1, 1), padding=(0, 0),
 def conv2d_bwd_f32_host(grad, col, w, x_shape, stride, padding, with_bias: bool = True, device: int = 0):
     """``Conv2d.backward`` (novann/layers/convolutional/conv2d.py:179-207): returns
     (dW (Cout,C,KH,KW), db (Cout,1) or None, dX (N,C,H,W))."""
-    grad, col, w = _f32(grad), _f32(col), _f32(w)
+    grad, col, w = _f32(grad, device), _f32(col, device), _f32(w, device)
     n, c, h, wd = x_shape
     cout, _, kh, kw = w.shape
     oh, ow = grad.shape[2], grad.shape[3]
@@ -210,7 +276,7 @@ def conv2d_bwd_f32_host(grad, col, w, x_shape, stride, padding, with_bias: bool 
 
 def im2col_f32_host(x, kernel, stride, padding, padding_mode: str = "zeros", device: int = 0):
     """``_im2col`` (novann/functional.py:346-368): (C*KH*KW, N*OH*OW) fp32."""
-    x = _f32(x)
+    x = _f32(x, device)
     n, c, h, wd = x.shape
     kh, kw = kernel
     oh, ow = conv2d_out_size(h, wd, kh, kw, stride[0], stride[1], padding[0], padding[1])
@@ -224,14 +290,14 @@ def im2col_f32_host(x, kernel, stride, padding, padding_mode: str = "zeros", dev
 def linear_q_bwd_host(grad, x, wq, w_scales, fmt: str = "e4m3", with_bias: bool = True, device: int = 0):
     """Backward of the quantised Linear on the tensor cores: returns (dW (N,K) fp32, db (1,N) or
     None, dX (M,K) fp32) from the output gradient, the forward input and the weight codes."""
-    grad, x = _f32(grad), _f32(x)
+    grad, x = _f32(grad, device), _f32(x, device)
     m, n = grad.shape
     k = x.shape[1]
     need = C.c_size_t()
     check(lib().nvq_linear_bwd_q_workspace_bytes(m, n, k, C.byref(need)))
     dg, dx_in = DeviceBuffer.from_numpy(grad, device), DeviceBuffer.from_numpy(x, device)
     dq = DeviceBuffer.from_numpy(np.ascontiguousarray(wq, np.uint8), device)
-    ds = DeviceBuffer.from_numpy(_f32(w_scales), device)
+    ds = DeviceBuffer.from_numpy(_f32(w_scales, device), device)
     o_dx, o_dw, o_db = DeviceBuffer(m * k * 4, device), DeviceBuffer(n * k * 4, device), DeviceBuffer(n * 4, device)
     ws = DeviceBuffer(need.value, device)
     check(lib().nvq_linear_bwd_q(o_dx.at(0), o_dw.at(0), o_db.at(0) if with_bias else None, dg.at(0),
@@ -265,8 +331,8 @@ def linear_w8a8_host(x_bf16_bits, wq, w_scales, bias, device: int = 0) -> np.nda
     n = wq.shape[0]
     dx = DeviceBuffer.from_numpy(x, device)
     dw = DeviceBuffer.from_numpy(np.ascontiguousarray(wq, np.uint8), device)
-    ds = DeviceBuffer.from_numpy(_f32(w_scales), device)
-    db = DeviceBuffer.from_numpy(_f32(bias), device) if bias is not None else None
+    ds = DeviceBuffer.from_numpy(_f32(w_scales, device), device)
+    db = DeviceBuffer.from_numpy(_f32(bias, device), device) if bias is not None else None
     dy = DeviceBuffer(m * n * 2, device)
     ws = DeviceBuffer(linear_w8a8_workspace_bytes(m, k), device)
     linear_w8a8_device(dy, dx, dw, ds, db, m, n, k, ws)
@@ -293,7 +359,7 @@ def linear_expanded_device(y: DeviceBuffer, x: DeviceBuffer, wd: DeviceBuffer,
 
 def mul_host(a, b, device: int = 0) -> np.ndarray:
     """Elementwise fp32 product on the GPU (``ReLU.backward``: grad * mask)."""
-    a, b = _f32(a), _f32(b)
+    a, b = _f32(a, device), _f32(b, device)
     if a.shape != b.shape:
         raise ValueError("shapes differ")
     da, db = DeviceBuffer.from_numpy(a, device), DeviceBuffer.from_numpy(b, device)
@@ -321,7 +387,7 @@ def batchnorm_fwd_host(x, gamma, beta, running_mean, running_var, momentum: floa
     (y fp32, new_running_mean, new_running_var, save_stats): y is the float32 narrowing of the
     reference's float64 result; save_stats (2, C) fp32 holds the batch mean and the
     Bessel-corrected variance for ``batchnorm_bwd_host`` (None in evaluation mode)."""
-    x = _f32(x)
+    x = _f32(x, device)
     n, c, s = _ncs(x.shape)
     dx = DeviceBuffer.from_numpy(x, device)
     dg, db = DeviceBuffer.from_numpy(_f64(gamma).ravel(), device), DeviceBuffer.from_numpy(_f64(beta).ravel(), device)
@@ -340,10 +406,10 @@ def batchnorm_fwd_host(x, gamma, beta, running_mean, running_var, momentum: floa
 
 def batchnorm_bwd_host(grad, x, save_stats, gamma, eps: float = 1e-5, device: int = 0):
     """``BatchNorm2d.backward`` (batchnorm2d.py:104-146): returns (dx fp32, dgamma, dbeta float64 (C,))."""
-    grad, x = _f32(grad), _f32(x)
+    grad, x = _f32(grad, device), _f32(x, device)
     n, c, s = _ncs(x.shape)
     dgr, dx = DeviceBuffer.from_numpy(grad, device), DeviceBuffer.from_numpy(x, device)
-    dst = DeviceBuffer.from_numpy(_f32(save_stats), device)
+    dst = DeviceBuffer.from_numpy(_f32(save_stats, device), device)
     dg = DeviceBuffer.from_numpy(_f64(gamma).ravel(), device)
     o_dx = DeviceBuffer(max(4, x.nbytes), device)
     o_dg, o_db = DeviceBuffer(c * 8, device), DeviceBuffer(c * 8, device)
@@ -356,7 +422,7 @@ def batchnorm_bwd_host(grad, x, save_stats, gamma, eps: float = 1e-5, device: in
 
 def max_pool2d_host(x, kernel, stride, padding=(0, 0), padding_mode: str = "zeros", device: int = 0):
     """``F.max_pool2d`` (novann/functional.py:450-536): (N, C, OH, OW) fp32."""
-    x = _f32(x)
+    x = _f32(x, device)
     n, c, h, w = x.shape
     mode = _pad_mode(padding_mode)
     oh = (h + 2 * padding[0] - kernel[0]) // stride[0] + 1
@@ -371,7 +437,7 @@ def max_pool2d_host(x, kernel, stride, padding=(0, 0), padding_mode: str = "zero
 def max_pool2d_bwd_host(grad, x, kernel, stride, padding=(0, 0), padding_mode: str = "zeros",
                         device: int = 0):
     """``MaxPool2d.backward`` (novann/layers/pooling/maxpool/maxpool2d.py): dX (N, C, H, W)."""
-    grad, x = _f32(grad), _f32(x)
+    grad, x = _f32(grad, device), _f32(x, device)
     n, c, h, w = x.shape
     dg, dx = DeviceBuffer.from_numpy(grad, device), DeviceBuffer.from_numpy(x, device)
     o = DeviceBuffer(max(4, x.nbytes), device)
@@ -383,7 +449,7 @@ def max_pool2d_bwd_host(grad, x, kernel, stride, padding=(0, 0), padding_mode: s
 
 def avg_pool2d_host(x, device: int = 0):
     """``F.avg_pool2d`` (novann/functional.py:550-559): (N, C, 1, 1) fp32."""
-    x = _f32(x)
+    x = _f32(x, device)
     n, c, h, w = x.shape
     dx, o = DeviceBuffer.from_numpy(x, device), DeviceBuffer(max(4, n * c * 4), device)
     check(lib().nvq_gap2d_fwd_f32(o.at(0), dx.at(0), n * c, h * w, device, None))
@@ -392,7 +458,7 @@ def avg_pool2d_host(x, device: int = 0):
 
 def avg_pool2d_bwd_host(grad, x_shape, device: int = 0):
     """``GlobalAvgPool2d.backward``: (N, C, H, W) fp32."""
-    grad = _f32(grad)
+    grad = _f32(grad, device)
     n, c, h, w = x_shape
     dg, o = DeviceBuffer.from_numpy(grad, device), DeviceBuffer(max(4, n * c * h * w * 4), device)
     check(lib().nvq_gap2d_bwd_f32(o.at(0), dg.at(0), n * c, h * w, device, None))
@@ -401,7 +467,7 @@ def avg_pool2d_bwd_host(grad, x_shape, device: int = 0):
 
 def dropout_host(x, mask, keep_prob: float, device: int = 0):
     """``(x * mask) / keep_prob`` (novann/layers/regularization/dropout.py:52-54, :66)."""
-    x, mask = _f32(x), _f32(mask)
+    x, mask = _f32(x, device), _f32(mask, device)
     dx, dm = DeviceBuffer.from_numpy(x, device), DeviceBuffer.from_numpy(mask, device)
     o = DeviceBuffer(max(4, x.nbytes), device)
     check(lib().nvq_dropout_f32(o.at(0), dx.at(0), dm.at(0), x.size, C.c_float(keep_prob), device, None))

@@ -27,6 +27,21 @@ def kaiming_normal(shape) -> np.ndarray:
     return np.random.normal(0.0, np.sqrt(2.0 / fan_in), shape).astype(np.float32)
 
 
+def small_normal(shape) -> np.ndarray:
+    """0.001 * N(0, 1): the law a stand-alone reference ``Linear`` starts from
+    (novann/core/init.py:209-219), drawn with the same call on the global legacy NumPy
+    generator, so a seeded model gets the reference's weights."""
+    return np.random.randn(*shape).astype(np.float32) * 0.001
+
+
+def kaiming_uniform_relu(shape) -> np.ndarray:
+    """U(-l, l), l = sqrt(2) * sqrt(3 / fan_in): the law a stand-alone reference ``Conv2d``
+    starts from (novann/layers/convolutional/conv2d.py:62, novann/core/init.py:182-206)."""
+    fan_in = int(np.prod(shape[1:]))
+    limit = np.sqrt(2.0) * np.sqrt(3.0 / fan_in)
+    return np.random.uniform(-limit, limit, shape).astype(np.float32)
+
+
 def _pair(x):
     if isinstance(x, int):
         return (x, x)
@@ -41,6 +56,20 @@ def _pair(x):
 
 def _dev(a: np.ndarray, device: int) -> DeviceBuffer:
     return DeviceBuffer.from_numpy(np.ascontiguousarray(a), device)
+
+
+def _as_f32(x: np.ndarray, device: int) -> np.ndarray:
+    """The reference's layer-entry ``x.astype(np.float32, copy=False)``
+    (novann/layers/linear/linear.py:81): float32 passes through untouched; float64 (what a
+    reference BatchNorm emits) and float16 are narrowed / widened on the GPU by ``nvq_cast``.
+    Other dtypes are refused: nothing is converted on the CPU."""
+    x = np.asarray(x)
+    if x.dtype == np.float32:
+        return np.ascontiguousarray(x)
+    if x.dtype in (np.float64, np.float16):
+        from . import quant
+        return quant.cast(x, np.float32, device=device)
+    raise TypeError(f"layer input must be float32, float64 or float16, got {x.dtype}")
 
 
 class Linear(Layer):
@@ -59,7 +88,7 @@ class Linear(Layer):
         self.reset_parameters()
 
     def reset_parameters(self, initializer=None) -> None:
-        init = initializer or self.init_fn or kaiming_normal
+        init = initializer or self.init_fn or small_normal
         w = init((self.out_features, self.in_features))
         self.weight = Parameters(np.asarray(w, dtype=np.float32))
         self.weight.name = "linear weight"
@@ -70,13 +99,13 @@ class Linear(Layer):
             self.bias = None
 
     def forward(self, x: np.ndarray) -> np.ndarray:
-        x = np.ascontiguousarray(x.astype(np.float32, copy=False))
+        x = _as_f32(x, self.device)
         self._cache_input = x
         return F.linear_f32_host(x, self.weight.data, None if self.bias is None else self.bias.data,
                                  self.device)
 
     def backward(self, grad: np.ndarray) -> np.ndarray:
-        grad = np.ascontiguousarray(grad.astype(np.float32, copy=False))
+        grad = _as_f32(grad, self.device)
         dw, db, dx = F.linear_bwd_f32_host(grad, self._cache_input, self.weight.data,
                                            self.bias is not None, self.device)
         self.weight.grad = dw
@@ -92,13 +121,26 @@ class Linear(Layer):
 
 
 class ReLU(Layer):
+    """``novann/layers/activations/relu.py``.  ``name`` / ``affect_init`` / ``init_key`` are what
+    the reference's ``Sequential`` reads from an activation to choose the initialiser of the
+    weighted layers around it (novann/layers/activations/activations.py:19-38)."""
+
     def __init__(self, device: int = 0) -> None:
         super().__init__()
         self._mask = None
         self.device = device
+        self.name = "relu"
+        self.affect_init = True
+
+    def get_init_key(self):
+        return self.name if self.affect_init else None
+
+    @property
+    def init_key(self):
+        return self.get_init_key()
 
     def forward(self, x: np.ndarray) -> np.ndarray:
-        out, self._mask = F.relu_host(np.ascontiguousarray(x, np.float32), self.device)
+        out, self._mask = F.relu_host(_as_f32(x, self.device), self.device)
         return out
 
     def backward(self, grad: np.ndarray) -> np.ndarray:
@@ -125,17 +167,22 @@ class QuantLinear(Linear):
 
     def reset_parameters(self, initializer=None) -> None:
         super().reset_parameters(initializer)
-        self.requantize()
+        self._codes = self._scales = None      # quantised on the next forward
 
     def requantize(self) -> None:
-        """Recompute the weight codes from ``weight.data`` (call after an optimiser step)."""
+        """Recompute the weight codes from ``weight.data``."""
         from . import quant
         self._codes, self._scales = quant.quantize_weight(self.weight.data, self.fmt, self.device)
 
     def forward(self, x: np.ndarray) -> np.ndarray:
         from . import quant
-        x = np.ascontiguousarray(x.astype(np.float32, copy=False))
+        x = _as_f32(x, self.device)
         self._cache_input = x
+        # Optimisers update weight.data in place (novann/optim/sgd.py:62-82) and say nothing, so
+        # in training mode the codes are refreshed on every forward; in evaluation mode the
+        # codes of the last refresh are reused.
+        if self._training or self._codes is None:
+            self.requantize()
         xb = quant.cast(x, "bf16", device=self.device)
         b = None if self.bias is None else self.bias.data.reshape(-1)
         yb = F.linear_q_host(xb, self._codes, self._scales, b, self.fmt, self.device)
@@ -144,7 +191,7 @@ class QuantLinear(Linear):
     def backward(self, grad: np.ndarray) -> np.ndarray:
         if not (self.tensor_core_backward and self.fmt in ("e4m3", "e5m2")):
             return super().backward(grad)
-        grad = np.ascontiguousarray(grad.astype(np.float32, copy=False))
+        grad = _as_f32(grad, self.device)
         dw, db, dx = F.linear_q_bwd_host(grad, self._cache_input, self._codes, self._scales, self.fmt,
                                          self.bias is not None, self.device)
         self.weight.grad = dw
@@ -173,7 +220,7 @@ class Conv2d(Layer):
         self.reset_parameters()
 
     def reset_parameters(self, initializer=None):
-        init = initializer or self.init_fn or kaiming_normal
+        init = initializer or self.init_fn or kaiming_uniform_relu
         w = init((self.out_channels, self.in_channels, self.KH, self.KW))
         self.weight = Parameters(np.asarray(w, dtype=np.float32))
         self.weight.name = "conv2d weight"
@@ -184,7 +231,7 @@ class Conv2d(Layer):
             self.bias = None
 
     def forward(self, x: np.ndarray) -> np.ndarray:
-        x = np.ascontiguousarray(x.astype(np.float32, copy=False))
+        x = _as_f32(x, self.device)
         out, col = F.conv2d_f32_host(x, self.weight.data, None if self.bias is None else self.bias.data,
                                      (self.sh, self.sw), (self.ph, self.pw), self.pm, self.device,
                                      return_col=True)
@@ -193,7 +240,7 @@ class Conv2d(Layer):
         return out
 
     def backward(self, grad: np.ndarray) -> np.ndarray:
-        grad = np.ascontiguousarray(grad.astype(np.float32, copy=False))
+        grad = _as_f32(grad, self.device)
         dw, db, dx = F.conv2d_bwd_f32_host(grad, self._cache["col"], self.weight.data,
                                            self._cache["x_shape"], (self.sh, self.sw),
                                            (self.ph, self.pw), self.bias is not None, self.device)
@@ -221,7 +268,7 @@ class QuantConv2d(Conv2d):
 
     def reset_parameters(self, initializer=None):
         super().reset_parameters(initializer)
-        self.requantize()
+        self._codes = self._scales = None      # quantised on the next forward
 
     def requantize(self) -> None:
         from . import quant
@@ -233,7 +280,9 @@ class QuantConv2d(Conv2d):
         self._codes, self._scales = quant.quantize_weight(padded, self.fmt, self.device)
 
     def forward(self, x: np.ndarray) -> np.ndarray:
-        x = np.ascontiguousarray(x.astype(np.float32, copy=False))
+        x = _as_f32(x, self.device)
+        if self._training or self._codes is None:     # see QuantLinear.forward
+            self.requantize()
         # backward uses the fp32 master weight (straight-through), so it needs the fp32 patches
         self._cache = {"x_shape": x.shape, "col": F.im2col_f32_host(
             x, (self.KH, self.KW), (self.sh, self.sw), (self.ph, self.pw), self.pm, self.device)}
@@ -267,7 +316,7 @@ class _BatchNorm(Layer):
         raise NotImplementedError
 
     def forward(self, x: np.ndarray) -> np.ndarray:
-        x = np.ascontiguousarray(x.astype(np.float32, copy=False))
+        x = _as_f32(x, self.device)
         self._check(x)
         y, rm, rv, stats = F.batchnorm_fwd_host(x, self.gamma.data, self.beta.data, self.running_mean,
                                                 self.running_var, self.momentum, self.eps,
@@ -337,13 +386,13 @@ class MaxPool2d(Layer):
         self._x = None
 
     def forward(self, x: np.ndarray) -> np.ndarray:
-        x = np.ascontiguousarray(x.astype(np.float32, copy=False))
+        x = _as_f32(x, self.device)
         self._x = x
         return F.max_pool2d_host(x, (self.KH, self.KW), (self.sh, self.sw), (self.ph, self.pw), self.pm,
                                  self.device)
 
     def backward(self, grad_output: np.ndarray) -> np.ndarray:
-        grad_output = np.ascontiguousarray(grad_output.astype(np.float32, copy=False))
+        grad_output = _as_f32(grad_output, self.device)
         dx = F.max_pool2d_bwd_host(grad_output, self._x, (self.KH, self.KW), (self.sh, self.sw),
                                    (self.ph, self.pw), self.pm, self.device)
         self._x = None
@@ -362,12 +411,12 @@ class GlobalAvgPool2d(Layer):
         self._x_shape = None
 
     def forward(self, x: np.ndarray) -> np.ndarray:
-        x = np.ascontiguousarray(x.astype(np.float32, copy=False))
+        x = _as_f32(x, self.device)
         self._x_shape = x.shape
         return F.avg_pool2d_host(x, self.device)
 
     def backward(self, grad_output: np.ndarray) -> np.ndarray:
-        return F.avg_pool2d_bwd_host(grad_output.astype(np.float32, copy=False), self._x_shape, self.device)
+        return F.avg_pool2d_bwd_host(_as_f32(grad_output, self.device), self._x_shape, self.device)
 
     def __repr__(self):
         return "GlobalAvgPool2d()"

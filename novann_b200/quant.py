@@ -18,14 +18,14 @@ from . import _lib
 from ._lib import check, lib
 from .device import DeviceBuffer, _sptr
 
-_NP_OF = {"f32": np.float32, "f16": np.float16, "bf16": np.uint16}
+_NP_OF = {"f32": np.float32, "f16": np.float16, "bf16": np.uint16, "f64": np.float64}
 
 
 def _dtype_name(d) -> str:
     if isinstance(d, str):
         d = d.lower()
         alias = {"float32": "f32", "float16": "f16", "bfloat16": "bf16", "fp32": "f32",
-                 "fp16": "f16"}
+                 "fp16": "f16", "float64": "f64", "fp64": "f64"}
         d = alias.get(d, d)
         if d in _lib.DTYPE_IDS:
             return d
@@ -35,6 +35,8 @@ def _dtype_name(d) -> str:
         return "f32"
     if d == np.float16:
         return "f16"
+    if d == np.float64:
+        return "f64"
     if d.name == "bfloat16":
         return "bf16"
     raise ValueError(f"unsupported dtype {d}")
@@ -94,12 +96,14 @@ def dequantize_fp4_b32_device(dst: DeviceBuffer, packed: DeviceBuffer, scales: D
 # ------------------------------------------------------------------ host arrays
 def cast(x: np.ndarray, dtype, *, src_dtype=None, device: int = 0, out: np.ndarray | None = None
          ) -> np.ndarray:
-    """GPU replacement for ``x.astype(dtype)`` between fp32 and fp16 / bf16.
+    """GPU replacement for ``x.astype(dtype)`` between fp32 and fp16 / bf16 / fp64.
 
-    ``x`` float32 -> ``dtype`` in {float16, "bf16"}; or ``x`` float16 / bf16-bits
-    (``src_dtype="bf16"``, uint16 array) -> float32.  Like the reference's
-    ``astype(np.float32, copy=False)``, a float32 -> float32 request returns ``x``
-    itself.  Host arrays in pinned memory (``pinned_empty``) move at full PCIe rate.
+    ``x`` float32 -> ``dtype`` in {float16, "bf16", float64}; or ``x`` float16 / float64 /
+    bf16-bits (``src_dtype="bf16"``, uint16 array) -> float32.  float64 -> float32 is the
+    conversion the reference's layers perform on BatchNorm's float64 output
+    (``novann/layers/linear/linear.py:81``).  Like ``astype(np.float32, copy=False)``, a
+    request for the dtype ``x`` already has returns ``x`` itself.  Host arrays in pinned
+    memory (``pinned_empty``) move at full PCIe rate.
     """
     dst = _dtype_name(dtype)
     if src_dtype is None:

@@ -63,6 +63,20 @@ class Communicator:
         check(lib().nvq_allreduce_sum_f32(C.c_void_p(self.handle), buf.at(offset), n, self.device,
                                           _sptr(stream)))
 
+    def wait(self, stream, timeout_ms: int = 30000) -> None:
+        """Host-side watchdog around the collective: returns when ``stream`` has drained; raises
+        ``NvqError`` (``ERR_TIMEOUT`` / ``ERR_NCCL``) when the all-reduce is still pending after
+        ``timeout_ms`` or NCCL reported an asynchronous error.  The wait polls; it never blocks
+        inside the driver, so a peer that never joined cannot hold this thread.  After a
+        failure call ``abort()``."""
+        check(lib().nvq_comm_wait(C.c_void_p(self.handle), self.device, _sptr(stream), int(timeout_ms)))
+
+    def abort(self) -> None:
+        """``ncclCommAbort``: tear the communicator down without waiting for what is in flight."""
+        if self.handle:
+            lib().nvq_comm_abort(C.c_void_p(self.handle))
+            self.handle = None
+
     def close(self) -> None:
         if self.handle:
             lib().nvq_comm_destroy(C.c_void_p(self.handle))
@@ -74,11 +88,12 @@ class MLPTrainStep:
     results with ``logits()``, ``loss()``, ``grads()``, ``params()``."""
 
     def __init__(self, params, batch: int, lr: float, device: int = 0, comm: Communicator | None = None,
-                 gate=None):
+                 gate=None, collective_timeout_ms: int = 30000):
         self.dims = [params[0].shape[1]] + [params[2 * i].shape[0] for i in range(len(params) // 2)]
         self.nl = len(self.dims) - 1
         self.batch, self.lr, self.device, self.comm = batch, float(lr), device, comm
         self.gate = gate            # launch.StepGate: host rendezvous before each collective step
+        self.collective_timeout_ms = collective_timeout_ms
         self._step_no = 0
         self.stream = Stream(device)
         flat = flatten_params(params)
@@ -153,15 +168,23 @@ class MLPTrainStep:
         return self.nl + 1 + (2 * self.nl - 1) + 1
 
     def step(self, x: np.ndarray, labels: np.ndarray) -> None:
-        self._step_no += 1
         if self.gate is not None:
-            self.gate.enter(self._step_no)      # raises PeerLost before anything is launched
+            self.gate.enter(self._step_no + 1)  # raises PeerLost before anything is launched
+        self._step_no += 1
         self.upload(x, labels)
         if self._graph is not None:
             self.replay()
         else:
             self.launch()
-        self.stream.sync()
+        self.sync()
+
+    def sync(self) -> None:
+        """Waits for the step on the host; with a communicator the wait is the NCCL watchdog
+        (bounded, polls the communicator's asynchronous error state)."""
+        if self.comm is not None and self.comm.world > 1:
+            self.comm.wait(self.stream, self.collective_timeout_ms)
+        else:
+            self.stream.sync()
 
     # ---- results
     def logits(self) -> np.ndarray:

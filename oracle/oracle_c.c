@@ -187,6 +187,55 @@ void orc_bf16_to_f32(const uint16_t* b, float* out, size_t n) {
     for (ptrdiff_t i = 0; i < (ptrdiff_t)n; i++) o[i] = (uint32_t)b[i] << 16;
 }
 
+/* fp64 -> fp32, bit-identical to NumPy's astype(float32) (the narrowing NovaNN's layers apply
+ * to BatchNorm's float64 output, novann/layers/linear/linear.py:81): RNE on the 29 dropped
+ * mantissa bits, subnormal results kept, overflow to inf; NaN keeps sign and the top 22
+ * payload bits and comes out quiet. */
+static inline uint32_t f64_to_f32_1(uint64_t u) {
+    uint32_t sign = (uint32_t)(u >> 32) & 0x80000000u;
+    uint64_t a = u & 0x7FFFFFFFFFFFFFFFull;
+    if (a > 0x7FF0000000000000ull) return sign | 0x7FC00000u | (uint32_t)((a >> 29) & 0x3FFFFFu);
+    if (a >= 0x47F0000000000000ull) return sign | 0x7F800000u;
+    int e = (int)(a >> 52);
+    if (e >= 897) {
+        uint64_t h = rne_shift(a - (896ull << 52), 29);
+        if (h > 0x7F800000ull) h = 0x7F800000ull;
+        return sign | (uint32_t)h;
+    }
+    if (e == 0) return sign;
+    uint64_t m = (a & ((1ull << 52) - 1)) | (1ull << 52);
+    return sign | (uint32_t)rne_shift(m, 926 - e);
+}
+
+/* fp32 -> fp64: exact; NaN quiet, payload shifted left 29. */
+static inline uint64_t f32_to_f64_1(uint32_t u) {
+    uint64_t sign = (uint64_t)(u & 0x80000000u) << 32;
+    uint32_t e = (u >> 23) & 0xFFu;
+    uint64_t m = u & 0x7FFFFFu;
+    if (e == 0xFF) return sign | 0x7FF0000000000000ull | (m << 29) | (m ? 0x0008000000000000ull : 0);
+    if (e == 0) {
+        if (m == 0) return sign;
+        int s = 0;
+        while (!(m & 0x800000u)) { m <<= 1; s++; }
+        return sign | ((uint64_t)(897 - s) << 52) | ((m & 0x7FFFFFu) << 29);
+    }
+    return sign | ((uint64_t)(e + 896) << 52) | (m << 29);
+}
+
+void orc_f64_to_f32(const double* x, float* out, size_t n) {
+    const uint64_t* u = (const uint64_t*)x;
+    uint32_t* o = (uint32_t*)out;
+#pragma omp parallel for schedule(static)
+    for (ptrdiff_t i = 0; i < (ptrdiff_t)n; i++) o[i] = f64_to_f32_1(u[i]);
+}
+
+void orc_f32_to_f64(const float* x, double* out, size_t n) {
+    const uint32_t* u = (const uint32_t*)x;
+    uint64_t* o = (uint64_t*)out;
+#pragma omp parallel for schedule(static)
+    for (ptrdiff_t i = 0; i < (ptrdiff_t)n; i++) o[i] = f32_to_f64_1(u[i]);
+}
+
 /* max |x| with NaNs ignored; exact and order independent (integer max on the
  * magnitudes' bit patterns). */
 float orc_amax_f32(const float* x, size_t n) {

@@ -38,7 +38,8 @@ class OracleC:
         L.orc_amax_f32.restype = C.c_float
         L.orc_amax_f32.argtypes = [C.c_void_p, C.c_size_t]
         L.orc_max_threads.restype = C.c_int
-        for name in ("orc_f32_to_f16", "orc_f16_to_f32", "orc_f32_to_bf16", "orc_bf16_to_f32"):
+        for name in ("orc_f32_to_f16", "orc_f16_to_f32", "orc_f32_to_bf16", "orc_bf16_to_f32",
+                     "orc_f64_to_f32", "orc_f32_to_f64"):
             getattr(L, name).argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
             getattr(L, name).restype = None
         L.orc_quantize_fp8.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_float, C.c_int]
@@ -75,6 +76,12 @@ class OracleC:
 
     def bf16_bits_to_f32(self, b, out=None):
         return self._conv("orc_bf16_to_f32", b, np.uint16, np.float32, out)
+
+    def f64_to_f32(self, x, out=None):
+        return self._conv("orc_f64_to_f32", x, np.float64, np.float32, out)
+
+    def f32_to_f64(self, x, out=None):
+        return self._conv("orc_f32_to_f64", x, np.float32, np.float64, out)
 
     def amax_f32(self, x) -> np.float32:
         x = np.ascontiguousarray(x, np.float32)

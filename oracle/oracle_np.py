@@ -99,6 +99,65 @@ def f16_bits_to_f32(h: np.ndarray) -> np.ndarray:
 
 
 # ----------------------------------------------------------------------------
+# fp64 <-> fp32   (reference primitive: ndarray.astype(np.float32) on BatchNorm's float64
+# output, novann/layers/linear/linear.py:81 fed by novann/layers/batchnorm/batchnorm2d.py:40-41,87)
+# ----------------------------------------------------------------------------
+def f64_to_f32_bits(x: np.ndarray) -> np.ndarray:
+    """fp64 -> fp32 bit patterns (uint32), identical to ``x.astype(np.float32)``.
+
+    RNE on the 29 dropped mantissa bits, subnormal results honoured, |x| >= 2^128 (after
+    rounding) -> inf.  NaN: sign kept, top 22 payload bits kept, quiet bit set
+    (``sign | 0x7fc00000 | payload >> 29``; NumPy's behaviour, observed black-box).
+    """
+    u = np.ascontiguousarray(x, dtype=np.float64).view(np.uint64)
+    sign = ((u >> np.uint64(32)) & np.uint64(0x80000000)).astype(np.uint64)
+    a = u & np.uint64(0x7FFFFFFFFFFFFFFF)
+    e = (a >> np.uint64(52)).astype(np.int64)
+    m = a & np.uint64((1 << 52) - 1)
+    # normal range of the target (|x| >= 2^-126, biased fp64 exponent >= 897): rebias, drop 29 bits
+    v = a.astype(np.int64) - (np.int64(896) << 52)
+    h = v >> 29
+    r = v & ((1 << 29) - 1)
+    h = h + ((r > (1 << 28)) | ((r == (1 << 28)) & ((h & 1) == 1)))
+    h = np.minimum(h, 0x7F800000)
+    # subnormal range: value = (m | 2^52) * 2^(e - 1075); the target's unit is 2^-149
+    mm = (m | np.uint64(1 << 52)).astype(np.int64)
+    sh = np.clip(926 - e, 0, 62)
+    hs = mm >> sh
+    rs = mm & ((np.int64(1) << sh) - 1)
+    half = np.int64(1) << np.maximum(sh - 1, 0)
+    hs = hs + ((rs > half) | ((rs == half) & ((hs & 1) == 1)))
+    hs = np.where(e == 0, 0, hs)            # fp64 zeros and subnormals are far below 2^-150
+    out = np.where(e >= 897, h, hs)
+    out = np.where(a >= np.uint64(0x47F0000000000000), 0x7F800000, out)
+    nan = np.int64(0x7FC00000) | (m >> np.uint64(29)).astype(np.int64)
+    out = np.where(a > np.uint64(0x7FF0000000000000), nan, out)
+    return (out.astype(np.uint64) | sign).astype(np.uint32)
+
+
+def f32_bits_to_f64_bits(x: np.ndarray) -> np.ndarray:
+    """fp32 -> fp64 bit patterns (uint64), identical to ``x.astype(np.float64)``: exact;
+    a NaN comes out quiet with its payload shifted left 29."""
+    u = _u32(x).astype(np.uint64)
+    sign = (u & np.uint64(0x80000000)) << np.uint64(32)
+    e = (u >> np.uint64(23)) & np.uint64(0xFF)
+    m = u & np.uint64(0x7FFFFF)
+    out = ((e + np.uint64(896)) << np.uint64(52)) | (m << np.uint64(29))
+    out = np.where(e == 0xFF, np.uint64(0x7FF0000000000000) | (m << np.uint64(29)) |
+                   np.where(m != 0, np.uint64(0x0008000000000000), np.uint64(0)), out)
+    # fp32 subnormal m * 2^-149: normalise (the leading one of m moves to the hidden bit)
+    mi = m.astype(np.int64)
+    lead = np.zeros(m.shape, np.int64)
+    for b in range(23):
+        lead = np.where((mi >> b) > 0, b, lead)
+    sub = ((np.uint64(1023 - 149) + lead.astype(np.uint64)) << np.uint64(52)) | \
+          ((m << (np.uint64(52) - lead.astype(np.uint64))) & np.uint64((1 << 52) - 1))
+    out = np.where((e == 0) & (m != 0), sub, out)
+    out = np.where((e == 0) & (m == 0), np.uint64(0), out)
+    return (out | sign).astype(np.uint64)
+
+
+# ----------------------------------------------------------------------------
 # fp32 <-> bf16   (no reference code; spec: RNE, NaN -> sign|0x7fc0)
 # ----------------------------------------------------------------------------
 def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:

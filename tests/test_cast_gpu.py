@@ -169,3 +169,133 @@ def test_full_size_roundtrip_properties(gpu):
             man = b & (0x7F if name == "bf16" else 0x3FF)
             notnan = ~((exp == (0xFF if name == "bf16" else 0x1F)) & (man != 0))
             assert np.array_equal(a[notnan], b[notnan])
+
+
+# ---------------------------------------------------------------- float64 <-> float32
+# The narrowing NovaNN really performs: its BatchNorm layers emit float64 and the next layer's
+# astype(np.float32) narrows it (novann/layers/linear/linear.py:81).  Pinned against
+# ndarray.astype itself, the reference's primitive, and against the integer oracle.
+def _f64_edge_block() -> np.ndarray:
+    bits = [
+        0x0000000000000000, 0x0000000000000001, 0x000FFFFFFFFFFFFF, 0x0010000000000000,   # zero, fp64 denormals
+        0x3690000000000000, 0x3690000000000001, 0x368FFFFFFFFFFFFF, 0x36A0000000000000,   # half of fp32's least subnormal
+        0x36A8000000000000, 0x36B0000000000000, 0x36B8000000000000, 0x380FFFFFFFFFFFFF,   # subnormal ties, below min normal
+        0x380FFFFFF0000000, 0x3810000000000000, 0x380FFFFFE0000000,                       # rounds up into the normals
+        0x3FF0000010000000, 0x3FF0000030000000, 0x3FF000000FFFFFFF, 0x3FF0000010000001,   # ties at 1 + half ulp
+        0x3FF0000020000000, 0x3FF00000EFFFFFFF, 0x3FF00000F0000000,
+        0x47EFFFFFE0000000, 0x47EFFFFFEFFFFFFF, 0x47EFFFFFF0000000, 0x47F0000000000000,   # fp32 max / overflow tie
+        0x7FEFFFFFFFFFFFFF, 0x7FF0000000000000,                                           # fp64 max, inf
+        0x7FF0000000000001, 0x7FF8000000000000, 0x7FF0000020000000, 0x7FF4000000000000,   # NaNs: payload kept >> 29, quieted
+        0x7FF0000010000000, 0x7FF7FFFFFFFFFFFF, 0x7FF00000E0000000, 0x7FFFFFFFFFFFFFFF,
+    ]
+    base = np.array(bits, dtype=np.uint64)
+    return np.concatenate([base, base | np.uint64(1 << 63)]).view(np.float64)
+
+
+def _f64_source(n, seed):
+    """Doubles that land all over fp32's range, ties at fp32's half ulp, and the edge block."""
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal(n) * 10.0 ** rng.integers(-46, 39, n)
+    k = n // 4
+    if k:
+        f = rng.integers(0, 0x7F800000, k, dtype=np.uint64).astype(np.uint32).view(np.float32).astype(np.float64)
+        t = f.view(np.uint64) | np.uint64(1 << 28)                 # exactly half way between two fp32 values
+        t += rng.integers(-1, 2, k).astype(np.int64).view(np.uint64)  # ... or one fp64 ulp either side
+        x[:k] = t.view(np.float64) * rng.choice([-1.0, 1.0], k)
+    e = _f64_edge_block()
+    if n >= e.size:
+        x[n - e.size:] = e
+    return x
+
+
+def _device_cast_f64(x, src, dst, gpu, src_off=0, dst_off=0):
+    n = x.size
+    dsize = 8 if dst == "f64" else 4
+    d_in = DeviceBuffer(x.nbytes + 64, gpu)
+    d_out = DeviceBuffer(n * dsize + 128, gpu)
+    d_out.zero()
+    d_in.upload(x, offset=src_off)
+    quant.cast_device(d_out, dst, d_in, src, n, dst_offset=dst_off, src_offset=src_off)
+    out = d_out.download(np.empty(n, np.float64 if dst == "f64" else np.float32), offset=dst_off)
+    guard = d_out.download(np.empty(32, np.uint8), offset=dst_off + n * dsize)
+    assert not guard.any()
+    return out
+
+
+@pytest.mark.parametrize("n", [0, 1, 3, 4, 5, 31, 33, 1000, 4099, (1 << 20) + 3])
+@pytest.mark.parametrize("offs", [(0, 0), (8, 4), (16, 0), (0, 8), (24, 12)])
+def test_f64_to_f32_sizes_and_alignment(gpu, oracle_c, n, offs):
+    x = _f64_source(n, seed=n + offs[0])
+    got = _device_cast_f64(x, "f64", "f32", gpu, *offs)
+    with np.errstate(all="ignore"):
+        assert np.array_equal(got.view(np.uint32), x.astype(np.float32).view(np.uint32))
+    assert np.array_equal(got.view(np.uint32), o.f64_to_f32_bits(x))
+    assert np.array_equal(got.view(np.uint32), oracle_c.f64_to_f32(x).view(np.uint32))
+
+
+def test_f64_to_f32_2pow26_doubles_against_numpy(gpu, oracle_c):
+    """2^26 doubles (512 MiB in): random magnitudes, fp32 half-ulp ties and the edge block,
+    bit-compared with ndarray.astype(np.float32)."""
+    x = _f64_source(1 << 26, seed=7)
+    got = _device_cast_f64(x, "f64", "f32", gpu)
+    with np.errstate(all="ignore"):
+        want = x.astype(np.float32)
+    bad = np.flatnonzero(got.view(np.uint32) != want.view(np.uint32))
+    assert bad.size == 0, (hex(int(x.view(np.uint64)[bad[0]])), hex(int(got.view(np.uint32)[bad[0]])))
+    assert np.array_equal(oracle_c.f64_to_f32(x).view(np.uint32), want.view(np.uint32))
+
+
+def test_f64_every_fp32_neighbourhood(gpu):
+    """Every fp32 exponent (subnormals included) x the 5 doubles around each of 64 mantissa
+    ties per exponent: the rounding decision at every scale."""
+    e = np.arange(0, 255, dtype=np.uint32)[:, None] << 23
+    m = np.random.default_rng(3).integers(0, 1 << 23, (1, 64), dtype=np.uint64).astype(np.uint32)
+    f = (e | m).reshape(-1).view(np.float32).astype(np.float64)
+    half = np.spacing(f.astype(np.float32)).astype(np.float64) / 2
+    x = np.concatenate([f + half * k for k in (0.0, 0.5, 1.0, 1.5)] +
+                       [np.nextafter(f + half, np.inf), np.nextafter(f + half, -np.inf)])
+    x = np.concatenate([x, -x])
+    got = _device_cast_f64(x, "f64", "f32", gpu)
+    with np.errstate(all="ignore"):
+        assert np.array_equal(got.view(np.uint32), x.astype(np.float32).view(np.uint32))
+
+
+@pytest.mark.parametrize("n", [0, 1, 5, 1000, (1 << 20) + 1])
+def test_f32_to_f64_exact(gpu, oracle_c, n):
+    x = _source("f32", n, seed=n)
+    got = _device_cast_f64(x, "f32", "f64", gpu)
+    assert np.array_equal(got.view(np.uint64), x.astype(np.float64).view(np.uint64))
+    assert np.array_equal(got.view(np.uint64), o.f32_bits_to_f64_bits(x))
+    got2 = _device_cast_f64(x, "f32", "f64", gpu, 4, 8)
+    assert np.array_equal(got2.view(np.uint64), got.view(np.uint64))
+
+
+def test_f32_to_f64_all_exponents_and_nans(gpu):
+    """Every exponent with 2^15 mantissas, both signs, subnormals and NaN payloads included,
+    against ndarray.astype(np.float64)."""
+    u = (np.arange(256, dtype=np.uint32)[:, None] << 23) | \
+        (np.arange(1 << 15, dtype=np.uint32)[None, :] * np.uint32(257) & np.uint32(0x7FFFFF))
+    u = np.concatenate([u.reshape(-1), u.reshape(-1) | np.uint32(0x80000000)])
+    got = _device_cast_f64(u.view(np.float32), "f32", "f64", gpu)
+    assert np.array_equal(got.view(np.uint64), u.view(np.float32).astype(np.float64).view(np.uint64))
+
+
+def test_f64_host_api(gpu):
+    """quant.cast on host float64 arrays (several staging chunks), and the layer-entry helper."""
+    from novann_b200.layers import _as_f32
+    x = _f64_source((20 << 20) + 5, seed=11)
+    got = quant.cast(x, np.float32)
+    with np.errstate(all="ignore"):
+        want = x.astype(np.float32)
+    assert got.dtype == np.float32 and np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    back = quant.cast(got, np.float64)
+    assert back.dtype == np.float64
+    assert np.array_equal(back.view(np.uint64), got.astype(np.float64).view(np.uint64))
+    x2 = x[:1000].reshape(10, 100)
+    y = _as_f32(x2, gpu)
+    with np.errstate(all="ignore"):
+        assert y.shape == (10, 100) and np.array_equal(y.view(np.uint32), x2.astype(np.float32).view(np.uint32))
+    f = np.ones((3, 4), np.float32)
+    assert _as_f32(f, gpu) is f or np.shares_memory(_as_f32(f, gpu), f)
+    with pytest.raises(TypeError):
+        _as_f32(np.ones(4, np.int32), gpu)

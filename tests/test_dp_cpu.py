@@ -128,3 +128,31 @@ def test_step_gate_peer_that_left_right_after_a_step_still_counts_for_that_step(
     slow.enter(1)
     with pytest.raises(PeerLost, match="left before step 2"):
         slow.enter(2)
+
+
+def test_step_gate_ignores_what_an_earlier_run_left_in_the_directory(tmp_path):
+    """Restart in the same directory (the recovery case after PeerLost): the first run reached
+    step 3 and one rank even left cleanly; the second run has only rank 0 alive.  Neither the
+    stale ``3`` nor the stale ``left 3`` may let rank 0 pass step 1."""
+    from novann_b200.launch import PeerLost, StepGate, exchange_bytes
+    d = str(tmp_path)
+    a, b = StepGate(d, 0, 2, timeout_s=0.5, token="run1"), StepGate(d, 1, 2, timeout_s=0.5, token="run1")
+    for step in (1, 2, 3):
+        a._write(str(step)); a._last = step
+        b._write(str(step)); b._last = step
+        a.enter(step)
+        b.enter(step)
+    b.leave()
+    again = StepGate(d, 0, 2, timeout_s=0.5, token="run2")
+    with pytest.raises(PeerLost, match="did not reach step 1"):
+        again.enter(1)
+    # same token, new gate object (a worker restarted by the same launcher): its own stale
+    # announcement is removed on creation
+    a2 = StepGate(d, 0, 2, timeout_s=0.2, token="run1")
+    assert a2._read(0) is None
+    # the id side channel: a file of an earlier launch is not returned to the other ranks
+    exchange_bytes(b"old" * 8, 0, os.path.join(d, "nccl_id"), token="run1")
+    with pytest.raises(TimeoutError):
+        exchange_bytes(None, 1, os.path.join(d, "nccl_id"), timeout_s=0.3, token="run2")
+    exchange_bytes(b"new" * 8, 0, os.path.join(d, "nccl_id"), token="run2")
+    assert exchange_bytes(None, 1, os.path.join(d, "nccl_id"), timeout_s=0.3, token="run2") == b"new" * 8

@@ -50,7 +50,7 @@ def _fp8_shard_worker(rank, world, tmpdir):
     sys.path.insert(0, ROOT)
     from novann_b200 import quant, workloads
     from novann_b200.device import DeviceBuffer
-    from novann_b200.launch import exchange_bytes
+    from novann_b200.launch import publish, wait_for
     from novann_b200.train import shard_rows
     from oracle import oracle_np as o
 
@@ -59,10 +59,10 @@ def _fp8_shard_worker(rank, world, tmpdir):
     shard = np.ascontiguousarray(x[lo:hi])
     part = quant.amax(shard, device=rank)                     # this rank's partial amax (one float)
     # the one scalar exchange of the path: max-combine on the host, no collective
-    open(os.path.join(tmpdir, f"amax.{rank}"), "wb").write(np.float32(part).tobytes())
+    publish(os.path.join(tmpdir, f"amax.{rank}"), np.float32(part).tobytes())   # atomic: all 4 bytes or no file
     vals = []
     for r in range(world):
-        vals.append(np.frombuffer(exchange_bytes(None, 1, os.path.join(tmpdir, f"amax.{r}")), np.float32)[0])
+        vals.append(np.frombuffer(wait_for(os.path.join(tmpdir, f"amax.{r}")), np.float32)[0])
     amax = np.float32(max(vals))
     for fmt in ("e4m3", "e5m2"):
         d = DeviceBuffer.from_numpy(shard, rank)
@@ -87,3 +87,58 @@ def test_two_rank_fp8_row_shards_equal_whole_tensor(gpu, tmp_path):
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     mp.spawn(_fp8_shard_worker, args=(2, str(tmp_path)), nprocs=2, join=True)
+
+
+def _gated_worker(rank, world, tmpdir, q):
+    sys.path.insert(0, ROOT)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"        # a rank leaves in this test: no multicast bindings
+    from novann_b200 import _lib, workloads
+    from novann_b200.launch import PeerLost, StepGate, exchange_bytes
+    from novann_b200.train import Communicator, MLPTrainStep, shard_rows
+
+    uid = Communicator.make_unique_id() if rank == 0 else None
+    uid = exchange_bytes(uid, rank, os.path.join(tmpdir, "nccl_id"), token="gated")
+    comm = Communicator(uid, rank, world, device=rank)
+    gate = StepGate(tmpdir, rank, world, timeout_s=120.0, token="gated")
+    dims = (784, 256, 128, 10)
+    x, y, params = workloads.mlp_inputs(128, dims, seed=0)
+    lo, hi = shard_rows(128, rank, world)
+    st = MLPTrainStep(params, hi - lo, 0.01, device=rank, comm=comm, gate=gate, collective_timeout_ms=60000)
+    for _ in range(2):
+        st.step(x[lo:hi], y[lo:hi])             # both ranks: gate, all-reduce, watchdog wait
+    gate.timeout_s = 3.0
+    if rank == 1:
+        gate.leave()                            # between steps, nothing in flight
+        comm.close()
+        q.put((rank, "left"))
+        return
+    before = _lib.lib().nvq_launch_count()
+    try:
+        st.step(x[lo:hi], y[lo:hi])
+        q.put((rank, "no error"))
+    except PeerLost as e:
+        launched = _lib.lib().nvq_launch_count() - before
+        q.put((rank, f"PeerLost launched={launched} step_no={st._step_no}: {e}"))
+    comm.abort()                                # the partner is gone: tear down without waiting
+
+
+def test_gated_step_raises_before_anything_is_launched_when_a_rank_left(gpu, tmp_path):
+    """The ``gate=`` hook of the data-parallel step together with the collective: both ranks run
+    two gated steps, rank 1 leaves between steps (nothing in flight) and closes its
+    communicator, and rank 0's third step must raise PeerLost with no kernel launched and the
+    step counter unchanged - no kernel is left waiting for the partner."""
+    from novann_b200.device import device_count
+    if device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_gated_worker, args=(r, 2, str(tmp_path), q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    msgs = dict(q.get(timeout=240) for _ in range(2))
+    for p in ps:
+        p.join(60)
+        assert p.exitcode == 0
+    assert msgs[1] == "left"
+    assert msgs[0].startswith("PeerLost launched=0 step_no=2"), msgs

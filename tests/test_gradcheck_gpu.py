@@ -31,7 +31,7 @@ def _picks(shape, k, rng):
 
 def test_linear_gradients(gpu):
     rng = np.random.default_rng(0)
-    layer = nb.Linear(20, 12, device=gpu)
+    layer = nb.Linear(20, 12, device=gpu, init=nb.layers.kaiming_normal)
     x = rng.standard_normal((6, 20)).astype(np.float32)
     proj = rng.standard_normal((6, 12))
     layer.forward(x)
@@ -67,7 +67,9 @@ def test_relu_mask_and_sequential_shapes(gpu):
     r = nb.ReLU(device=gpu)
     y = r.forward(x)
     assert np.array_equal(r._mask, (x > 0).astype(np.float32)) and np.array_equal(y, x * (x > 0))
-    model = nb.Sequential(nb.Linear(9, 7, device=gpu), nb.ReLU(device=gpu), nb.Linear(7, 3, device=gpu))
+    init = nb.layers.kaiming_normal
+    model = nb.Sequential(nb.Linear(9, 7, device=gpu, init=init), nb.ReLU(device=gpu),
+                          nb.Linear(7, 3, device=gpu, init=init))
     out = model(x)
     assert out.shape == (5, 3) and out.dtype == np.float32
     model.backward(np.ones_like(out))

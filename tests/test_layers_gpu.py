@@ -15,6 +15,8 @@ from novann_b200 import functional as F, quant, workloads
 from novann_b200.train import MLPTrainStep
 from oracle import oracle_np as o
 
+from novann_b200.layers import kaiming_normal  # noqa: E402
+
 pytestmark = pytest.mark.gpu
 G = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
@@ -161,7 +163,7 @@ def test_weight_quantisation_per_channel_bit_exact(gpu):
 @pytest.mark.parametrize("fmt,tol", [("e4m3", 1e-2), ("e5m2", 1e-2), ("e2m1_b32", 5e-2)])
 def test_quant_linear_layer(gpu, fmt, tol):
     rng = np.random.default_rng(3)
-    layer = nb.QuantLinear(256, 192, fmt=fmt, device=gpu)
+    layer = nb.QuantLinear(256, 192, fmt=fmt, device=gpu, init=kaiming_normal)
     layer.bias.data = rng.standard_normal((1, 192)).astype(np.float32) * 0.01
     x = rng.standard_normal((160, 256)).astype(np.float32)
     y = layer(x)
@@ -206,7 +208,7 @@ def test_quant_linear_backward_on_tensor_cores(gpu, m, n, k):
 
 def test_quant_linear_layer_tensor_core_backward(gpu):
     rng = np.random.default_rng(1)
-    layer = nb.QuantLinear(128, 64, fmt="e4m3", device=gpu, tensor_core_backward=True)
+    layer = nb.QuantLinear(128, 64, fmt="e4m3", device=gpu, tensor_core_backward=True, init=kaiming_normal)
     x = rng.standard_normal((96, 128)).astype(np.float32)
     layer(x)
     g = rng.standard_normal((96, 64)).astype(np.float32)
@@ -378,7 +380,7 @@ def test_quant_mlp_inference_fused_relu(gpu):
     (3, 128, 10, 10, 96, 3, 1),       # at most 128 channels out, an even number of k-blocks
     (2, 64, 6, 200, 16, 3, 1),        # output rows of 200 positions: one row per tile (swapped kernel only)
 ])
-def test_implicit_gemm_conv_equals_patch_matrix_conv_and_oracle(gpu, case, monkeypatch):
+def test_implicit_gemm_conv_equals_patch_matrix_conv_and_oracle(gpu, case):
     """The tcgen05 implicit-GEMM convolution (4-D TMA boxes, no patch matrix) against the
     patch-matrix path of the same entry point (bit-identical inputs to the MMAs, so only the fp32
     accumulation order differs) and against the oracle within the FP8 bound."""
@@ -390,19 +392,17 @@ def test_implicit_gemm_conv_equals_patch_matrix_conv_and_oracle(gpu, case, monke
     w_col = wt.reshape(cout, -1)
     assert w_col.shape[1] % 16 == 0
     codes, scales = quant.quantize_weight(w_col, "e4m3", gpu)
-    monkeypatch.delenv("NVQ_CONV_MODE", raising=False)
     y_imp = F.conv2d_q_host(x, codes, scales, b, (k, k), (1, 1), (p, p), "zeros", "e4m3", gpu)
-    monkeypatch.setenv("NVQ_CONV_MODE", "explicit")
-    y_exp = F.conv2d_q_host(x, codes, scales, b, (k, k), (1, 1), (p, p), "zeros", "e4m3", gpu)
+    y_exp = F.conv2d_q_host(x, codes, scales, b, (k, k), (1, 1), (p, p), "zeros", "e4m3", gpu,
+                            path="patch_matrix")
     assert y_imp.shape == y_exp.shape == (n, cout, h + 2 * p - k + 1, w + 2 * p - k + 1)
     # both are bf16-rounded: equal up to one bf16 ulp where the fp32 sums differ in their last bits
     assert o.max_abs_rel(y_imp, y_exp) <= 2.0 ** -8
     assert np.mean(y_imp == y_exp) > 0.9
     # both implicit kernels, whichever the dispatch picks: the CTA-pair kernel and (for at most
     # 128 output channels) the operand-swapped kernel
-    for forced in ("pair", "swapped"):
-        monkeypatch.setenv("NVQ_CONV_MODE", forced)
-        y_f = F.conv2d_q_host(x, codes, scales, b, (k, k), (1, 1), (p, p), "zeros", "e4m3", gpu)
+    for forced in ("cta_pair", "auto"):
+        y_f = F.conv2d_q_host(x, codes, scales, b, (k, k), (1, 1), (p, p), "zeros", "e4m3", gpu, path=forced)
         assert o.max_abs_rel(y_f, y_exp) <= 2.0 ** -8, forced
         assert np.mean(y_f == y_exp) > 0.9, forced
     # oracle: bf16 activations x dequantised weight, float64 accumulation
@@ -423,7 +423,7 @@ def test_implicit_gemm_conv_equals_patch_matrix_conv_and_oracle(gpu, case, monke
     (2, 64, 17, 9, 24, 5, 2, 2, 1),       # stride 2 down only, 5 x 5 taps
     (37, 64, 28, 28, 128, 3, 1, 2, 2),    # several tiles per CTA pair
 ])
-def test_strided_implicit_gemm_conv(gpu, case, monkeypatch):
+def test_strided_implicit_gemm_conv(gpu, case):
     """Strides of 2: the 4-D TMA box walks the NHWC tensor with a traversal stride, so the box of
     a filter tap still lands as consecutive operand rows.  Against the patch-matrix path of the
     same call and against the oracle."""
@@ -433,17 +433,15 @@ def test_strided_implicit_gemm_conv(gpu, case, monkeypatch):
     wt = (rng.standard_normal((cout, c, k, k)) * 0.05).astype(np.float32)
     b = (rng.standard_normal(cout) * 0.1).astype(np.float32)
     codes, scales = quant.quantize_weight(wt.reshape(cout, -1), "e4m3", gpu)
-    monkeypatch.delenv("NVQ_CONV_MODE", raising=False)
     y_imp = F.conv2d_q_host(x, codes, scales, b, (k, k), (sh, sw), (p, p), "zeros", "e4m3", gpu)
-    monkeypatch.setenv("NVQ_CONV_MODE", "explicit")
-    y_exp = F.conv2d_q_host(x, codes, scales, b, (k, k), (sh, sw), (p, p), "zeros", "e4m3", gpu)
+    y_exp = F.conv2d_q_host(x, codes, scales, b, (k, k), (sh, sw), (p, p), "zeros", "e4m3", gpu,
+                            path="patch_matrix")
     oh, ow = (h + 2 * p - k) // sh + 1, (w + 2 * p - k) // sw + 1
     assert y_imp.shape == y_exp.shape == (n, cout, oh, ow)
     assert o.max_abs_rel(y_imp, y_exp) <= 2.0 ** -8
     assert np.mean(y_imp == y_exp) > 0.9
-    for forced in ("pair", "swapped"):
-        monkeypatch.setenv("NVQ_CONV_MODE", forced)
-        y_f = F.conv2d_q_host(x, codes, scales, b, (k, k), (sh, sw), (p, p), "zeros", "e4m3", gpu)
+    for forced in ("cta_pair", "auto"):
+        y_f = F.conv2d_q_host(x, codes, scales, b, (k, k), (sh, sw), (p, p), "zeros", "e4m3", gpu, path=forced)
         assert o.max_abs_rel(y_f, y_exp) <= 2.0 ** -8, forced
         assert np.mean(y_f == y_exp) > 0.9, forced
     wd = o.dequantize_fp8(codes, 1.0, "e4m3").reshape(cout, c, k, k) * scales.reshape(-1, 1, 1, 1)
@@ -461,7 +459,7 @@ def test_strided_implicit_gemm_conv(gpu, case, monkeypatch):
     (2, 16, 9, 9, 24, 3, 2, 1),        # patch-matrix path (stride 2, C = 16): kpad = 160
     (2, 3, 8, 8, 8, 5, 1, 2),          # patch-matrix path, K = 75 -> kpad = 96
 ])
-def test_fp4_weight_conv2d(gpu, case, monkeypatch):
+def test_fp4_weight_conv2d(gpu, case):
     """FP4 E2M1 block-32 weights through the quantised convolution (block scales folded into the
     expanded weight): both paths against the oracle within the FP4 bound, and against each other
     where both apply."""
@@ -476,7 +474,6 @@ def test_fp4_weight_conv2d(gpu, case, monkeypatch):
     w_col[:, :ckk] = wt.reshape(cout, -1)
     packed, scales = quant.quantize_weight(w_col, "e2m1_b32", gpu)
     assert packed.shape == (cout, kpad // 2) and scales.shape == (cout, kpad // 32)
-    monkeypatch.delenv("NVQ_CONV_MODE", raising=False)
     y = F.conv2d_q_host(x, packed, scales, b, (k, k), (s, s), (p, p), "zeros", "e2m1_b32", gpu)
     # oracle: the same codes and scales, bf16 activations, float64 contraction
     wd = o.dequantize_fp4_weight(packed, scales)
@@ -490,8 +487,8 @@ def test_fp4_weight_conv2d(gpu, case, monkeypatch):
     ref32 = o.conv2d_fwd_f32(xb, wt, b.reshape(-1, 1), (s, s), (p, p))
     assert o.max_abs_rel(y, ref32) <= 2.5e-1           # 4-bit weights; the spec's 5e-2 is for the codes' own GEMM
     if s == 1 and c % 64 == 0:
-        monkeypatch.setenv("NVQ_CONV_MODE", "explicit")
-        y2 = F.conv2d_q_host(x, packed, scales, b, (k, k), (s, s), (p, p), "zeros", "e2m1_b32", gpu)
+        y2 = F.conv2d_q_host(x, packed, scales, b, (k, k), (s, s), (p, p), "zeros", "e2m1_b32", gpu,
+                             path="patch_matrix")
         assert o.max_abs_rel(y, y2) <= 2.0 ** -8
     F.check_device_errors(gpu)
 

@@ -235,7 +235,7 @@ def test_linear_split_last_wave_and_deep_k(gpu, m, n, k):
     (4, 256, 16400),      # rows longer than the activation-splitting kernel keeps in registers
 ])
 @pytest.mark.parametrize("few_rows_mode", ["direct", "convert"])
-def test_linear_few_rows_weight_streaming_kernel(gpu, fmt, m, n, k, few_rows_mode, monkeypatch):
+def test_linear_few_rows_weight_streaming_kernel(gpu, fmt, m, n, k, few_rows_mode):
     """M <= 128 runs a weight-streaming kernel (codes read once, operands swapped, split along K
     with a deterministic reduction) - "direct": the codes are the tensor cores' operand and each
     activation row is two rows of E4M3 codes; "convert": the codes are expanded to bf16 in shared
@@ -243,32 +243,30 @@ def test_linear_few_rows_weight_streaming_kernel(gpu, fmt, m, n, k, few_rows_mod
     row (same bits)."""
     xb, w, b = workloads.linear_inputs(m, n, k, seed=m + n)
     wq, sc = o.quantize_weight_per_channel(w, fmt)
-    monkeypatch.delenv("NVQ_LINEAR_MODE", raising=False)
-    monkeypatch.setenv("NVQ_FEW_ROWS_MODE", few_rows_mode)
-    y = F.linear_q_host(xb, wq, sc, b, fmt, gpu)
-    y2 = F.linear_q_host(xb, wq, sc, b, fmt, gpu)
+    path = "bf16_activations" if few_rows_mode == "convert" else None
+    y = F.linear_q_host(xb, wq, sc, b, fmt, gpu, path=path)
+    y2 = F.linear_q_host(xb, wq, sc, b, fmt, gpu, path=path)
     assert np.array_equal(y, y2)
     want_bits, _ = o.linear_fwd_qweight(xb, wq, sc, b, fmt)
     err = o.max_abs_rel(o.bf16_bits_to_f32(y), o.bf16_bits_to_f32(want_bits))
     assert err <= 2.0 ** -7, err
-    monkeypatch.setenv("NVQ_LINEAR_MODE", "single")          # expansion pass + single-CTA kernel
-    y_old = F.linear_q_host(xb, wq, sc, b, fmt, gpu)
+    y_old = F.linear_q_host(xb, wq, sc, b, fmt, gpu, path="single_cta")   # expansion pass + single-CTA kernel
     assert o.max_abs_rel(o.bf16_bits_to_f32(y), o.bf16_bits_to_f32(y_old)) <= 2.0 ** -7
     assert np.mean(y == y_old) > 0.9
     F.check_device_errors(gpu)
 
 
 @pytest.mark.parametrize("m,fmt", [(8, "e4m3"), (8, "e5m2"), (256, "e4m3"), (256, "e5m2")])
-def test_linear_in_kernel_expansion_of_every_code(gpu, m, fmt, monkeypatch):
+def test_linear_in_kernel_expansion_of_every_code(gpu, m, fmt):
     """Every FP8 code (subnormals, NaN / inf codes, both zeros) through the in-kernel expansion:
     the converting few-rows kernel (m = 8) and the fused CTA-pair kernel (m = 256, no workspace).
     Row n of the weight holds code n repeated, x is all ones."""
-    monkeypatch.setenv("NVQ_FEW_ROWS_MODE", "convert")
     n, k = 256, 64
     wq = np.repeat(np.arange(256, dtype=np.uint8)[:, None], k, axis=1)
     xb = o.f32_to_bf16_bits(np.ones((m, k), np.float32))
     sc = np.ones(n, np.float32)
-    y = o.bf16_bits_to_f32(F.linear_q_host(xb, wq, sc, None, fmt, gpu, use_workspace=m <= 128))
+    y = o.bf16_bits_to_f32(F.linear_q_host(xb, wq, sc, None, fmt, gpu, use_workspace=m <= 128,
+                                           path="bf16_activations" if m <= 128 else None))
     table = o.E4M3_TABLE if fmt == "e4m3" else o.E5M2_TABLE
     with np.errstate(all="ignore"):
         vals = table[np.arange(256)].astype(np.float64) * k
@@ -281,15 +279,13 @@ def test_linear_in_kernel_expansion_of_every_code(gpu, m, fmt, monkeypatch):
 
 
 @pytest.mark.parametrize("fmt", ["e4m3", "e5m2"])
-def test_linear_few_rows_direct_every_code_and_activation_split(gpu, fmt, monkeypatch):
+def test_linear_few_rows_direct_every_code_and_activation_split(gpu, fmt):
     """The direct few-rows kernel (FP8 codes straight into kind::f8f6f4 MMAs).  (1) Every weight
     code against x = 1: finite codes bit-exact, NaN codes NaN; an E5M2 infinity code meets the
     zero low-order piece of the activation and gives NaN where the bf16 paths give infinity (the
     quantiser never emits those codes).  (2) Activations that use all eight significant bits and
     span 2^-20 .. 2^6 within a row against a float64 product: the two-piece split is exact down
     to 2^-13 of the row maximum."""
-    monkeypatch.delenv("NVQ_LINEAR_MODE", raising=False)
-    monkeypatch.setenv("NVQ_FEW_ROWS_MODE", "direct")
     n, k = 256, 64
     wq = np.repeat(np.arange(256, dtype=np.uint8)[:, None], k, axis=1)
     xb = o.f32_to_bf16_bits(np.ones((8, k), np.float32))
@@ -320,19 +316,17 @@ def test_linear_few_rows_direct_every_code_and_activation_split(gpu, fmt, monkey
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 128, 64), (16, 4096, 4096), (33, 1000, 352), (128, 264, 2048), (7, 136, 96)])
-def test_linear_few_rows_fp4_weights(gpu, m, n, k, monkeypatch):
+def test_linear_few_rows_fp4_weights(gpu, m, n, k):
     """FP4 block-32 weights through the few-rows kernel (codes and block scales read once, the
     scale folded in while the tile is expanded in shared memory): against the oracle and against
     the expansion-pass path of the same call."""
     xb, w, b = workloads.linear_inputs(m, n, k, seed=m * n)
     packed, scales = o.quantize_fp4_b32(o.f32_to_bf16_bits(w).reshape(w.shape))
-    monkeypatch.delenv("NVQ_LINEAR_MODE", raising=False)
     y = o.bf16_bits_to_f32(F.linear_q_host(xb, packed, scales, b, "e2m1_b32", gpu))
     wd = o.bf16_bits_to_f32(o.f32_to_bf16_bits(o.dequantize_fp4_weight(packed, scales))).reshape(n, k)
     ref = o.bf16_bits_to_f32(xb).astype(np.float64) @ wd.astype(np.float64).T + b
     assert o.max_abs_rel(y, ref) <= FP4_TOL
     assert o.max_abs_rel(y, ref) <= 2.0 ** -7
-    monkeypatch.setenv("NVQ_LINEAR_MODE", "single")
-    y_old = o.bf16_bits_to_f32(F.linear_q_host(xb, packed, scales, b, "e2m1_b32", gpu))
+    y_old = o.bf16_bits_to_f32(F.linear_q_host(xb, packed, scales, b, "e2m1_b32", gpu, path="single_cta"))
     assert o.max_abs_rel(y, y_old) <= 2.0 ** -7
     F.check_device_errors(gpu)

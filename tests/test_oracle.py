@@ -182,3 +182,44 @@ def test_two_piece_e4m3_split_of_bf16_activations():
         p1 = small.astype(ml_dtypes.float8_e4m3fn).astype(np.float32)
         p2 = ((small - p1) * 16).astype(ml_dtypes.float8_e4m3fn).astype(np.float32)
         assert np.max(np.abs(p1 + p2 / 16 - small)) <= 2.0 ** -14
+
+
+def _f64_patterns():
+    """Doubles across fp32's whole range, ties at fp32's half ulp (and one fp64 ulp either side),
+    every fp32 exponent, fp64 specials."""
+    rng = np.random.default_rng(5)
+    raw = rng.integers(0, 1 << 64, 1 << 21, dtype=np.uint64).view(np.float64)
+    spread = rng.standard_normal(1 << 21) * 10.0 ** rng.integers(-46, 39, 1 << 21)
+    f = rng.integers(0, 0x7F800000, 1 << 21, dtype=np.uint64).astype(np.uint32).view(np.float32)
+    t = f.astype(np.float64).view(np.uint64) | np.uint64(1 << 28)
+    ties = np.concatenate([t, t + np.uint64(1), t - np.uint64(1)]).view(np.float64)
+    spec = np.array([0, 1, 0x3690000000000000, 0x3690000000000001, 0x36A0000000000000, 0x380FFFFFF0000000,
+                     0x47EFFFFFEFFFFFFF, 0x47EFFFFFF0000000, 0x7FF0000000000000, 0x7FF0000000000001,
+                     0x7FF8000000000000, 0x7FF0000020000000, 0x7FF7FFFFFFFFFFFF, 0x7FF00000E0000000],
+                    np.uint64)
+    spec = np.concatenate([spec, spec | np.uint64(1 << 63)]).view(np.float64)
+    return np.concatenate([raw, spread, ties, -ties, spec])
+
+
+def test_f64_to_f32_equals_numpy_astype(oracle_c):
+    """float64 -> float32 is the narrowing the reference's layers apply to BatchNorm's float64
+    output (novann/layers/linear/linear.py:81): pinned against ndarray.astype itself."""
+    d = _f64_patterns()
+    with np.errstate(all="ignore"):
+        want = d.astype(np.float32).view(np.uint32)
+    assert np.array_equal(o.f64_to_f32_bits(d), want)
+    assert np.array_equal(oracle_c.f64_to_f32(d).view(np.uint32), want)
+    known = {0x7FF0000000000001: 0x7FC00000, 0xFFF0000020000000: 0xFFC00001, 0x7FF4000000000000: 0x7FE00000,
+             0x47EFFFFFEFFFFFFF: 0x7F7FFFFF, 0x47EFFFFFF0000000: 0x7F800000, 0x3690000000000000: 0x0,
+             0x3690000000000001: 0x1, 0x36A8000000000000: 0x2, 0x380FFFFFFFFFFFFF: 0x00800000}
+    got = o.f64_to_f32_bits(np.array(list(known), np.uint64).view(np.float64))
+    assert [int(g) for g in got] == list(known.values())
+
+
+def test_f32_to_f64_equals_numpy_astype(oracle_c):
+    want = X.astype(np.float64).view(np.uint64)
+    assert np.array_equal(o.f32_bits_to_f64_bits(X), want)
+    assert np.array_equal(oracle_c.f32_to_f64(X).view(np.uint64), want)
+    sub = np.arange(0, 1 << 23, 97, dtype=np.uint32).view(np.float32)      # fp32 subnormals normalise
+    assert np.array_equal(o.f32_bits_to_f64_bits(sub), sub.astype(np.float64).view(np.uint64))
+    assert np.array_equal(oracle_c.f32_to_f64(sub).view(np.uint64), sub.astype(np.float64).view(np.uint64))

@@ -15,6 +15,7 @@ import pytest
 
 from novann_b200 import _lib, functional as F, workloads
 from novann_b200.device import DeviceBuffer, device_sync
+from oracle import oracle_np as o
 
 pytestmark = pytest.mark.gpu
 
@@ -37,8 +38,12 @@ def _both_ways(gpu, m, n, k, seed):
     ds, db = DeviceBuffer.from_numpy(sc, gpu), DeviceBuffer.from_numpy(b, gpu)
     y_ref, y_new = DeviceBuffer(m * n * 2, gpu), DeviceBuffer(m * n * 2, gpu)
     status = DeviceBuffer.from_numpy(np.zeros(1, np.int32), gpu)
-    ws = DeviceBuffer(F.linear_workspace_bytes(n, k, "e4m3"), gpu)
-    F.linear_q_device(y_ref, dx, dw, "e4m3", ds, db, m, n, k, ws)
+    # the caller-workspace form gets exactly the bytes the built-in array has, so both calls
+    # take the same kernel path (few rows: the partial sums must fit the same 8 MiB)
+    ws = DeviceBuffer(max(STATIC_BYTES, F.linear_workspace_bytes(n, k, "e4m3")), gpu)
+    ws_bytes = C.c_size_t(STATIC_BYTES)
+    _lib.check(L.nvq_linear_fwd(y_ref.at(0), dx.at(0), dw.at(0), _lib.E4M3, ds.at(0), db.at(0), m, n, k,
+                                ws.at(0), ws_bytes, gpu, None))
     _lib.check(L.nvq_linear_fwd_static(y_new.at(0), dx.at(0), dw.at(0), _lib.E4M3, ds.at(0), db.at(0),
                                        m, n, k, status.at(0), gpu, None))
     device_sync(gpu)
@@ -46,6 +51,11 @@ def _both_ways(gpu, m, n, k, seed):
     assert status.to_numpy(np.int32, (1,))[0] == 0
     a = y_ref.to_numpy(np.uint16, (m, n))
     c = y_new.to_numpy(np.uint16, (m, n))
+    # and against the CPU oracle (float64 accumulation), within the FP8 bound of the other tests
+    rows = np.unique(np.concatenate([np.arange(0, m, max(1, m // 16)), [m - 1]]))
+    want, _ = o.linear_fwd_qweight(xb[rows], wq, sc, b, "e4m3")
+    err = o.max_abs_rel(o.bf16_bits_to_f32(c[rows]), o.bf16_bits_to_f32(want))
+    assert err <= 2.0 ** -7, err
     return a, c
 
 
@@ -58,6 +68,13 @@ def test_static_scratch_matches_workspace_form_twice_in_a_row(gpu):
     # multiple of 16, which also keeps this shape on the scratch path)
     a, c = _both_ways(gpu, 200, 264, 328, seed=2)
     assert np.array_equal(a, c)
+    # third call: few rows.  The same array now holds the few-rows kernels' fp32 partial sums,
+    # activation codes and row scales instead of an expanded weight, over the leftovers of the
+    # two calls before; bit for bit the caller-workspace form, and twice the same bits.
+    a, c = _both_ways(gpu, 16, 1024, 1024, seed=3)
+    assert np.array_equal(a, c)
+    a2, c2 = _both_ways(gpu, 16, 1024, 1024, seed=3)
+    assert np.array_equal(c, c2) and np.array_equal(a, a2)
 
 
 def test_static_scratch_rejects_oversized_weight(gpu):
