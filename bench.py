@@ -26,6 +26,7 @@ and the CPU oracle's C restatement on all cores for bf16 (the reference has no b
 from __future__ import annotations
 
 import argparse
+import faulthandler
 import json
 import os
 import statistics
@@ -120,6 +121,20 @@ def _dist_env():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     return rank, world, local
+
+
+_T0 = time.time()
+
+
+def phase(name: str, limit_s: int = 240) -> None:
+    """Marks the start of a phase on stderr and re-arms a watchdog: a phase that takes longer than
+    ``limit_s`` dumps every thread's stack and ends the process (a hung rank then costs minutes,
+    not the launcher's whole time limit, and the dump says where it stood)."""
+    rank = os.environ.get("RANK", "0")
+    sys.stderr.write(f"[bench rank {rank} +{time.time() - _T0:6.1f}s] {name}\n")
+    sys.stderr.flush()
+    faulthandler.cancel_dump_traceback_later()
+    faulthandler.dump_traceback_later(limit_s, exit=True)
 
 
 def _host_threads() -> int:
@@ -504,8 +519,9 @@ def measure_dp_step(dev, rank, world, dist, local):
     """The one collective of the project: the data-parallel MLP step, batch 128 split over the
     ranks, its flat 235 146-float gradient bucket summed by nvq_allreduce_sum_f32 (NCCL over
     NVLink), 1 / world folded into the SGD kernel.  Times are the max over ranks.
-    dp_step_us: eager steps (11 launches) with the all-reduce, device time per step;
-    dp_step_us_graph: the same step replayed from a CUDA graph; allreduce_us: the all-reduce alone."""
+    dp_step_us: eager steps (10 kernels + the all-reduce), device time per step, 50 steps
+    enqueued back to back; allreduce_us: the all-reduce alone.  The step is not replayed from a
+    CUDA graph here: a graph holding an NCCL collective is left out of the benchmark."""
     import torch
     from novann_b200 import workloads
     from novann_b200.device import DeviceBuffer
@@ -551,22 +567,6 @@ def measure_dp_step(dev, rank, world, dist, local):
     step.sync()
     out["allreduce_us"] = max_over_ranks(e0.elapsed_ms(e1) / 50 * 1e3)
     out["allreduce_floats"] = MLP_PARAMS
-    try:
-        step.capture()
-        for _ in range(3):
-            step.replay()
-        step.sync()
-        dist.barrier()
-        e0, e1 = T.events()
-        e0.record(step.stream)
-        for _ in range(50):
-            step.replay()
-        e1.record(step.stream)
-        step.sync()
-        out["dp_step_us_graph"] = max_over_ranks(e0.elapsed_ms(e1) / 50 * 1e3)
-    except Exception as e:          # a capture NCCL refuses is reported, not fatal
-        out["dp_step_us_graph"] = None
-        out["dp_graph_error"] = str(e)[:120]
     dist.barrier()
     buf.free()
     comm.close()
@@ -662,6 +662,7 @@ def run_ours(args):
         return float(t.item())
 
     # ---- inputs resident in HBM before the timed region
+    phase("cast sweep: inputs")
     tile = workloads.cast_input(TILE, seed=rank)
     d32 = DeviceBuffer(n * 4, dev)
     d16 = DeviceBuffer(n * 2, dev)
@@ -681,6 +682,7 @@ def run_ours(args):
             if events is not None:
                 events[i + 1].record(st)
 
+    phase("cast sweep: warm-up and timed steps")
     warm = max(3, args.warmup)
     for _ in range(warm):
         sweep()
@@ -708,14 +710,16 @@ def run_ours(args):
 
     T = Timing(dev, st)
     flat = {}
-    flat.update(measure_cast_sizes(T, rank))
-    flat.update(measure_quantisers(T, rank, world))
-    flat.update(measure_linear(T, rank, world))
-    flat.update(measure_conv(T, rank, world))
-    flat.update(measure_train_steps(T, rank, world))
+    for name, fn in (("other cast sizes", measure_cast_sizes), ("quantisers", measure_quantisers),
+                     ("linear", measure_linear), ("conv", measure_conv), ("train steps", measure_train_steps)):
+        phase(name)
+        flat.update(fn(T, rank) if fn is measure_cast_sizes else fn(T, rank, world))
     clocks = sampler.stop()   # sampled over the timed region and the other kernels
     if dist is not None:
+        phase("data-parallel step")
+        barrier()
         flat.update(measure_dp_step(dev, rank, world, dist, local))
+        barrier()
         # aggregate Linear throughput of the job: every rank multiplies its own row shard
         import torch
         t = torch.tensor([flat["linear_fp8_tflops_per_gpu"]], device=f"cuda:{local}", dtype=torch.float64)
@@ -728,12 +732,14 @@ def run_ours(args):
         flat["linear_fp8_tflops"] = flat["linear_fp8_tflops_per_gpu"]
 
     # ---- e2e: host arrays through the astype-replacement call
+    phase("e2e through host arrays", 400)
     e2e_steps = max(1, min(args.steps, 5))
     e = measure_e2e(dev, tile, n, e2e_steps, barrier, max_over_ranks)
     e2e_value = BYTES_PER_ELEM_STEP * n * e2e_steps * world / e["e2e_s"] / 1e9
     copy_ceiling = BYTES_PER_ELEM_STEP * n * world / e["copy_s"] / 1e9
     pageable = BYTES_PER_ELEM_STEP * e["pageable_elems"] * world / e["pageable_s"] / 1e9
 
+    phase("cpu baseline and report")
     if rank == 0:
         peak, peak_bf16, which = _peaks()
         dom = max(per_kernel, key=per_kernel.get)
@@ -788,7 +794,8 @@ def run_ours(args):
             "clocks": clocks,
         }
         line.update(flat)       # flat scalar keys: the Linear, the other cast sizes, the DP step ...
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
+    faulthandler.cancel_dump_traceback_later()
     if dist is not None:
         dist.destroy_process_group()
 
