@@ -468,10 +468,20 @@ def measure_conv(T, rank, world):
                                      chw, chw, cco, 3, 3, 1, 1, 1, 1, 0, dev, _sptr(st)))
     t = T.rotating(conv_call, [()], rounds=10)
     F.check_device_errors(dev)
-    for b in (d_xc, d_wc, d_col, d_yb, d_wsc, d_oc, d_sc):
+    # the same convolution between chained quantised layers: bf16 NHWC in and out, no layout pass
+    d_xh, d_yh = DeviceBuffer(cn * cc * chw * chw * 2, dev), DeviceBuffer(crows * cco * 2, dev)
+    F.nchw_f32_to_nhwc_bf16_device(d_xh, d_xc, cn, cc, chw * chw, stream=st)
+
+    def nhwc_call(*_):
+        F.conv2d_q_nhwc_device(d_yh, d_xh, d_wc, "e4m3", d_sc, None, d_wsc, cn, cc, chw, chw, cco, (3, 3),
+                               (1, 1), (1, 1), relu=True, stream=st)
+    t2 = T.rotating(nhwc_call, [()], rounds=10)
+    F.check_device_errors(dev)
+    for b in (d_xc, d_wc, d_col, d_yb, d_wsc, d_oc, d_sc, d_xh, d_yh):
         b.free()
-    return {"conv2d_fp8_ms": t, "conv2d_fp8_tflops_per_gpu": 2.0 * crows * cco * ckp / t / 1e9,
-            "conv2d_fp8_N_per_gpu": cn}
+    flops = 2.0 * crows * cco * ckp
+    return {"conv2d_fp8_ms": t, "conv2d_fp8_tflops_per_gpu": flops / t / 1e9, "conv2d_fp8_N_per_gpu": cn,
+            "conv2d_fp8_nhwc_ms": t2, "conv2d_fp8_nhwc_tflops_per_gpu": flops / t2 / 1e9}
 
 
 def measure_train_steps(T, rank, world):
@@ -809,7 +819,8 @@ def run_case(name: str, a: list[int]) -> None:
         cast [log2_elems=26 reps=3]      cast64 [log2_elems=26 reps=3]    fp8 [rows=8192 reps=3]
         fp4 [rows=8192 reps=3]           linear [M=4096 N=4096 K=4096 reps=3 in_kernel=0]
         w8a8 [M N K reps]                fewrows [M=16 N=8192 K=8192 reps=3]
-        conv [N=128 C=64 HW=56 Cout=128 reps=2]     mlp [batch=128 steps=3]     cnn [batch=128 steps=3]
+        conv [N=128 C=64 HW=56 Cout=128 reps=2]     convnhwc [N=128 C=64 HW=56 Cout=128 reps=3]
+        mlp [batch=128 steps=3]          cnn [batch=128 steps=3]
     """
     from novann_b200 import _lib, functional as F, quant, workloads
     from novann_b200._lib import check, lib
@@ -888,6 +899,18 @@ def run_case(name: str, a: list[int]) -> None:
             check(lib().nvq_conv2d_fwd_q(out.at(0), dx.at(0), dq.at(0), _lib.DTYPE_IDS["e4m3"], ds.at(0), None,
                                          col.at(0), yb.at(0), ws.at(0), ws.nbytes, n, c, hw, hw, cout, 3, 3,
                                          1, 1, 1, 1, 0, 0, _sptr(st)))
+    elif name == "convnhwc":
+        n, c, hw, cout, reps = arg(0, 128), arg(1, 64), arg(2, 56), arg(3, 128), arg(4, 3)
+        x = np.random.default_rng(0).standard_normal((n, c, hw, hw), dtype=np.float32)
+        wq = rng.integers(0, 0x7F, (cout, c * 9), dtype=np.uint64).astype(np.uint8)
+        dx32, dq = DeviceBuffer.from_numpy(x, 0), DeviceBuffer.from_numpy(wq, 0)
+        ds = DeviceBuffer.from_numpy(np.full(cout, 1e-3, np.float32), 0)
+        dxh, dyh = DeviceBuffer(x.size * 2, 0), DeviceBuffer(n * hw * hw * cout * 2, 0)
+        ws = DeviceBuffer(cout * c * 9 * 2, 0)
+        F.nchw_f32_to_nhwc_bf16_device(dxh, dx32, n, c, hw * hw, stream=st)
+        for _ in range(reps):
+            F.conv2d_q_nhwc_device(dyh, dxh, dq, "e4m3", ds, None, ws, n, c, hw, hw, cout, (3, 3), (1, 1), (1, 1),
+                                   relu=True, stream=st)
     elif name == "mlp":
         from novann_b200.train import MLPTrainStep
         batch, steps = arg(0, 128), arg(1, 3)

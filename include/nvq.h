@@ -397,6 +397,27 @@ nvq_status nvq_conv2d_fwd_q_opts(float* d_out, const float* d_x, const uint8_t* 
                                  int KH, int KW, int sh, int sw, int ph, int pw, nvq_pad_mode mode,
                                  uint32_t path, int device, void* stream);
 
+/* Quantised convolution between chained quantised layers: the activations stay in HBM as bf16
+ * NHWC ((N*H*W) x C, channels contiguous), which is the tensor cores' operand layout, so the
+ * per-call layout pass of nvq_conv2d_fwd_q and the fp32 NCHW output (four times the bytes) are
+ * gone.  Same contraction as F.conv2d (novann/functional.py:275-385) with zero padding:
+ *   out[(n, oh, ow), co] = bf16( act( s_co * sum x[n, oh*sh+kh-ph, ow*sw+kw-pw, c] * dequant(Wq)[co, (c,kh,kw)] + b_co ) )
+ * act = F.relu's v * (v > 0) when relu != 0 (novann/functional.py:8-22), identity otherwise.
+ * Wq / scales as for nvq_conv2d_fwd_q.  Strides 1 or 2, C % 64 == 0, OW * stride <= 256,
+ * Cout % 8 == 0; other shapes return NVQ_ERR_UNSUPPORTED (use nvq_conv2d_fwd_q).
+ * d_workspace: Cout * C * KH * KW * 2 bytes (the tap-ordered expanded weight), 16-byte aligned.
+ * The two converters sit at the ends of such a chain (S = H * W; C % 64 == 0 for the first,
+ * C % 8 == 0 for the second). */
+nvq_status nvq_conv2d_fwd_q_nhwc(uint16_t* d_out_bf16, const uint16_t* d_x_bf16, const uint8_t* d_wq,
+                                 nvq_dtype w_fmt, const float* d_w_scales, const float* d_bias,
+                                 void* d_workspace, size_t workspace_bytes, int N, int C, int H, int W,
+                                 int Cout, int KH, int KW, int sh, int sw, int ph, int pw, int relu,
+                                 int device, void* stream);
+nvq_status nvq_nchw_f32_to_nhwc_bf16(uint16_t* d_dst, const float* d_src, int N, int C, int S,
+                                     int device, void* stream);
+nvq_status nvq_nhwc_bf16_to_nchw_f32(float* d_dst, const uint16_t* d_src, int N, int C, int S,
+                                     int device, void* stream);
+
 /* ---------------------------------------------------------------- BatchNorm, pooling, Dropout
  * The layers either side of the GEMMs in NovaNN's CNN.  Activations are fp32 (N, C, S)
  * row-major with S = H*W (BatchNorm2d), the sequence length (BatchNorm1d, 3-D input) or 1

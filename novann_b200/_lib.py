@@ -102,6 +102,9 @@ SIGNATURES = {
     "nvq_conv2d_fwd_q": (i32, [vp, vp, vp, i32, vp, vp, vp, vp, vp, sz] + [i32] * 11 + [i32, i32, vp]),
     "nvq_conv2d_fwd_q_opts": (i32, [vp, vp, vp, i32, vp, vp, vp, vp, vp, sz] + [i32] * 11 +
                               [i32, C.c_uint32, i32, vp]),
+    "nvq_conv2d_fwd_q_nhwc": (i32, [vp, vp, vp, i32, vp, vp, vp, sz] + [i32] * 11 + [i32, i32, vp]),
+    "nvq_nchw_f32_to_nhwc_bf16": (i32, [vp, vp, i32, i32, i32, i32, vp]),
+    "nvq_nhwc_bf16_to_nchw_f32": (i32, [vp, vp, i32, i32, i32, i32, vp]),
     "nvq_comm_unique_id": (i32, [vp]),
     "nvq_comm_init": (i32, [vp, i32, i32, i32, pvp]),
     "nvq_comm_destroy": (i32, [vp]),

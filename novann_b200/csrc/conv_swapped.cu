@@ -16,7 +16,9 @@
 //   warp 1     TMEM allocation; one lane issues tcgen05.mma kind::f16 (128 x NP x 16) and commits
 //   warps 2-5  epilogue: TMEM -> scale, bias, bf16 rounding -> swizzled staging buffer -> TMA store
 //              of 32-channel x 32-position boxes into the fp32 NCHW output (register stores for
-//              ragged tails and unaligned shapes)
+//              ragged tails and unaligned shapes).  NHWC form (activations that stay bf16 NHWC
+//              between chained quantised layers): the box is staged position-major and stored
+//              into the bf16 (N*OH*OW) x Cout output, optional ReLU before the rounding
 // One CTA per SM, cta_group::1, persistent over (image, row block, channel block) tiles.
 // Every wait is bounded.
 #include "gemm_common.cuh"
@@ -40,7 +42,9 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 1024 + 4 * 2 * STG_BYTE
 enum { ERR_PRODUCER = 41, ERR_MMA_FULL = 42, ERR_MMA_TMEM = 43, ERR_EPILOGUE = 44 };
 
 struct ConvParams {
-    float* out;            // N x Cout x OH x OW fp32
+    float* out;            // N x Cout x OH x OW fp32 (NCHW form)
+    uint16_t* out16;       // (N*OH*OW) x Cout bf16 (NHWC form)
+    int relu;              // NHWC form: v * (v > 0) before the bf16 rounding
     const float* scales;   // Cout per-channel factors or nullptr (= 1)
     const float* bias;     // Cout or nullptr
     int images, Cout, OH, OW;
@@ -73,6 +77,7 @@ __device__ __forceinline__ Tile tile_of(const ConvParams& p, int t) {
     return r;
 }
 
+template <bool NHWC>
 __global__ void __launch_bounds__(THREADS, 1)
 conv_swapped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const __grid_constant__ CUtensorMap map_out, const ConvParams p) {
@@ -186,6 +191,55 @@ conv_swapped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             // column j of the accumulator is position oh0 * OW + j of the image's plane; rows of
             // the box below the image's last output row are not stored
             const int valid = min(p.bh, p.OH - tl.oh0) * p.OW;
+            if (NHWC) {
+                // row of the (N*OH*OW) x Cout output that holds position 0 of this tile
+                const size_t row0 = (size_t)tl.img * S + (size_t)tl.oh0 * p.OW;
+#pragma unroll 1
+                for (int c = 0; c < valid; c += 32) {
+                    uint32_t r[32];
+                    tc::tmem_ld_32x32(taddr + c, r);
+                    tc::tmem_ld_wait();
+                    uint32_t h[16];            // bf16 results of positions c + 2j (low half), c + 2j + 1 (high half)
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        float a = fmaf(__uint_as_float(r[2 * j]), sc, bi), b = fmaf(__uint_as_float(r[2 * j + 1]), sc, bi);
+                        if (p.relu) { a = a * (a > 0.f ? 1.f : 0.f); b = b * (b > 0.f ? 1.f : 0.f); }
+                        h[j] = pack_bf16(a, b);
+                    }
+                    if (p.tma_out && c + 32 <= valid) {
+                        // staged position-major: row = position (64 bytes: this warp's 32 channels),
+                        // so for one position the warp's 32 two-byte stores are one contiguous row
+                        const uint32_t stg = stg_base + (uint32_t)(chunk_no & 1) * STG_BYTES;
+                        chunk_no++;
+                        if (lane == 0) tc::bulk_wait_read<1>();
+                        __syncwarp();
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            asm volatile("st.shared.b16 [%0], %1;" ::"r"(stg + (uint32_t)(2 * j) * 64u + (uint32_t)lane * 2u),
+                                         "h"((uint16_t)(h[j] & 0xFFFFu)) : "memory");
+                            asm volatile("st.shared.b16 [%0], %1;" ::"r"(stg + (uint32_t)(2 * j + 1) * 64u + (uint32_t)lane * 2u),
+                                         "h"((uint16_t)(h[j] >> 16)) : "memory");
+                        }
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) {
+                            tc::tma_store_2d(&map_out, stg, tl.cb * CH_ROWS + quarter * 32, (int)(row0 + c));
+                            tc::bulk_commit();
+                        }
+                    } else if (ch_ok) {
+                        uint16_t* o = p.out16 + (row0 + c) * (size_t)p.Cout + ch;
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            if (c + 2 * j < valid) o[(size_t)(2 * j) * p.Cout] = (uint16_t)(h[j] & 0xFFFFu);
+                            if (c + 2 * j + 1 < valid) o[(size_t)(2 * j + 1) * p.Cout] = (uint16_t)(h[j] >> 16);
+                        }
+                    }
+                }
+                tc::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive(tc::smem_u32(&sh->tmem_empty[acc]));
+                continue;
+            }
             float* plane = p.out + ((size_t)tl.img * p.Cout + (ch_ok ? ch : 0)) * S + (size_t)tl.oh0 * p.OW;
             const bool vec = ((reinterpret_cast<uintptr_t>(plane) & 15) == 0);
 #pragma unroll 1
@@ -258,7 +312,8 @@ conv_swapped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 nvq_status nvq_conv_launch_swapped(float* d_out, const uint16_t* d_x_nhwc, const uint16_t* d_w,
                                    const float* d_scales, const float* d_bias, int N, int C, int H, int W,
                                    int Cout, int KH, int KW, int ph, int pw, int sh, int sw, int device,
-                                   cudaStream_t st) {
+                                   cudaStream_t st, uint16_t* d_out_nhwc, int relu) {
+    const bool nhwc = d_out_nhwc != nullptr;
     const int OH = (H + 2 * ph - KH) / sh + 1, OW = (W + 2 * pw - KW) / sw + 1;
     NVQ_REQUIRE(OH > 0 && OW > 0 && OW * sw <= 256 && C % 64 == 0 && Cout >= 1,
                 "swapped implicit convolution: needs OW * stride <= 256 and C %% 64 == 0");
@@ -279,8 +334,14 @@ nvq_status nvq_conv_launch_swapped(float* d_out, const uint16_t* d_x_nhwc, const
     // TMA stores need every box to start on a 16-byte boundary: planes and tiles of a multiple of
     // four positions; otherwise the epilogue stores from registers
     const size_t S = (size_t)OH * OW;
-    const bool tma_out = S % 4 == 0 && (bh * OW) % 4 == 0 && nvq_aligned(d_out, 16);
-    if (tma_out) {
+    // NHWC form: boxes of 32 channels x 32 rows of the (N*OH*OW) x Cout bf16 matrix; a box may start
+    // at any row, its channel offset is a multiple of 32 (64 bytes)
+    const bool tma_out = nhwc ? (Cout % 8 == 0 && nvq_aligned(d_out_nhwc, 16) && (size_t)N * S < (1u << 31))
+                              : (S % 4 == 0 && (bh * OW) % 4 == 0 && nvq_aligned(d_out, 16));
+    if (tma_out && nhwc) {
+        s = nvq_make_tmap_2d(&map_out, d_out_nhwc, (uint64_t)N * S, (uint64_t)Cout, 32, 32, 2, 0);
+        if (s != NVQ_OK) return s;
+    } else if (tma_out) {
         s = nvq_make_tmap_nchw_out(&map_out, d_out, N, Cout, S);
         if (s != NVQ_OK) return s;
     } else {
@@ -288,11 +349,14 @@ nvq_status nvq_conv_launch_swapped(float* d_out, const uint16_t* d_x_nhwc, const
     }
     static std::atomic<bool> attr_set[64];   // per device; setting the attribute twice is harmless
     if (!attr_set[device]) {
-        NVQ_CUDA(cudaFuncSetAttribute(conv_swapped_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        NVQ_CUDA(cudaFuncSetAttribute(conv_swapped_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        NVQ_CUDA(cudaFuncSetAttribute(conv_swapped_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         attr_set[device] = true;
     }
     ConvParams p = {};
     p.out = d_out;
+    p.out16 = d_out_nhwc;
+    p.relu = relu;
     p.scales = d_scales;
     p.bias = d_bias;
     p.images = N; p.Cout = Cout; p.OH = OH; p.OW = OW;
@@ -316,7 +380,8 @@ nvq_status nvq_conv_launch_swapped(float* d_out, const uint16_t* d_x_nhwc, const
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    NVQ_CUDA(cudaLaunchKernelEx(&cfg, conv_swapped_kernel, map_w, map_x, map_out, p));
+    if (nhwc) NVQ_CUDA(cudaLaunchKernelEx(&cfg, conv_swapped_kernel<true>, map_w, map_x, map_out, p));
+    else NVQ_CUDA(cudaLaunchKernelEx(&cfg, conv_swapped_kernel<false>, map_w, map_x, map_out, p));
     NVQ_LAUNCHED();
     return NVQ_OK;
 }

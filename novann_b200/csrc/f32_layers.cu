@@ -1104,6 +1104,82 @@ extern "C" nvq_status nvq_conv2d_fwd_q_opts(float* d_out, const float* d_x, cons
     return NVQ_OK;
 }
 
+// ---- activations kept bf16 NHWC between chained quantised layers -------------------------------
+extern "C" nvq_status nvq_nchw_f32_to_nhwc_bf16(uint16_t* d_dst, const float* d_src, int N, int C, int S,
+                                                int device, void* stream) {
+    NVQ_REQUIRE(d_dst && d_src && N > 0 && C > 0 && S > 0, "nvq_nchw_f32_to_nhwc_bf16: bad argument");
+    NVQ_REQUIRE(C % 64 == 0, "nvq_nchw_f32_to_nhwc_bf16: C (%d) must be a multiple of 64", C);
+    NVQ_REQUIRE(nvq_aligned(d_dst, 16), "nvq_nchw_f32_to_nhwc_bf16: destination must be 16-byte aligned");
+    nvq_status s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t cap = (size_t)nvq_sm_count(device) * 16;
+    if (S % 4 == 0 && nvq_aligned(d_src, 16)) {
+        const size_t want = (size_t)N * ((S + 63) / 64) * (C / 64);
+        nchw_f32_to_nhwc_bf16_v4_kernel<<<(unsigned)std::min(want, cap), 256, 0, st>>>(d_dst, d_src, N, C, S);
+    } else {
+        const size_t want = (size_t)N * ((S + 31) / 32) * (C / 64);
+        nchw_f32_to_nhwc_bf16_kernel<<<(unsigned)std::min(want, cap), 256, 0, st>>>(d_dst, d_src, N, C, S);
+    }
+    NVQ_LAUNCHED();
+    return NVQ_OK;
+}
+
+extern "C" nvq_status nvq_nhwc_bf16_to_nchw_f32(float* d_dst, const uint16_t* d_src, int N, int C, int S,
+                                                int device, void* stream) {
+    NVQ_REQUIRE(d_dst && d_src && N > 0 && C > 0 && S > 0, "nvq_nhwc_bf16_to_nchw_f32: bad argument");
+    NVQ_REQUIRE(C % 8 == 0 && nvq_aligned(d_src, 16), "nvq_nhwc_bf16_to_nchw_f32: C (%d) must be a multiple of 8, source 16-byte aligned", C);
+    nvq_status s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    const size_t want = (size_t)N * ((S + 31) / 32) * ((C + 63) / 64), cap = (size_t)nvq_sm_count(device) * 16;
+    rows_bf16_to_nchw_tiled_kernel<<<(unsigned)std::min(want, cap), 256, 0, (cudaStream_t)stream>>>(d_dst, d_src, N, C, S);
+    NVQ_LAUNCHED();
+    return NVQ_OK;
+}
+
+extern "C" nvq_status nvq_conv2d_fwd_q_nhwc(uint16_t* d_out_bf16, const uint16_t* d_x_bf16,
+                                            const uint8_t* d_wq, nvq_dtype w_fmt,
+                                            const float* d_w_scales, const float* d_bias,
+                                            void* d_workspace, size_t workspace_bytes, int N, int C,
+                                            int H, int W, int Cout, int KH, int KW, int sh, int sw,
+                                            int ph, int pw, int relu, int device, void* stream) {
+    ConvGeom g;
+    nvq_status s = geom(g, N, C, H, W, KH, KW, sh, sw, ph, pw, NVQ_PAD_ZEROS);
+    if (s != NVQ_OK) return s;
+    NVQ_REQUIRE(d_out_bf16 && d_x_bf16 && d_wq && d_w_scales && d_workspace, "nvq_conv2d_fwd_q_nhwc: null buffer");
+    NVQ_REQUIRE(Cout % 8 == 0, "nvq_conv2d_fwd_q_nhwc: Cout (%d) must be a multiple of 8", Cout);
+    NVQ_REQUIRE(w_fmt == NVQ_E4M3 || w_fmt == NVQ_E5M2 || w_fmt == NVQ_E2M1_B32,
+                "nvq_conv2d_fwd_q_nhwc: weight format must be E4M3, E5M2 or E2M1_B32");
+    NVQ_REQUIRE(nvq_aligned(d_out_bf16, 16) && nvq_aligned(d_x_bf16, 16) && nvq_aligned(d_workspace, 16),
+                "nvq_conv2d_fwd_q_nhwc: buffers must be 16-byte aligned");
+    const size_t L = (size_t)N * g.OH * g.OW;
+    if (!(sh >= 1 && sh <= 2 && sw >= 1 && sw <= 2 && C % 64 == 0 && g.OW * sw <= 256 && L < (1u << 31) &&
+          (size_t)Cout * C * KH * KW < (1u << 31)))
+        NVQ_FAIL(NVQ_ERR_UNSUPPORTED, "nvq_conv2d_fwd_q_nhwc: needs strides 1 or 2, C %% 64 == 0 and OW * stride <= 256 "
+                                      "(got stride %d x %d, C = %d, OW = %d); use nvq_conv2d_fwd_q", sh, sw, C, g.OW);
+    NVQ_REQUIRE(workspace_bytes >= (size_t)Cout * C * KH * KW * 2,
+                "nvq_conv2d_fwd_q_nhwc: workspace of %zu bytes required", (size_t)Cout * C * KH * KW * 2);
+    s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int kq = w_fmt == NVQ_E2M1_B32 ? 32 : 16;
+    const int Kpad = (C * KH * KW + kq - 1) / kq * kq;
+    const int wtotal = Cout * C * KH * KW;
+    if (w_fmt == NVQ_E4M3)
+        expand_permute_weight_kernel<NVQ_E4M3><<<ew_grid(wtotal, device), 256, 0, st>>>(
+            (uint16_t*)d_workspace, d_wq, Cout, C, KH, KW, Kpad);
+    else if (w_fmt == NVQ_E5M2)
+        expand_permute_weight_kernel<NVQ_E5M2><<<ew_grid(wtotal, device), 256, 0, st>>>(
+            (uint16_t*)d_workspace, d_wq, Cout, C, KH, KW, Kpad);
+    else
+        expand_permute_weight_fp4_kernel<<<ew_grid(wtotal, device), 256, 0, st>>>(
+            (uint16_t*)d_workspace, d_wq, d_w_scales, Cout, C, KH, KW, Kpad);
+    NVQ_LAUNCHED();
+    return nvq_conv_launch_swapped(nullptr, d_x_bf16, (const uint16_t*)d_workspace,
+                                   w_fmt == NVQ_E2M1_B32 ? nullptr : d_w_scales, d_bias, N, C, H, W, Cout, KH, KW,
+                                   ph, pw, sh, sw, device, st, d_out_bf16, relu ? 1 : 0);
+}
+
 extern "C" nvq_status nvq_conv2d_bwd_f32(float* d_dw, float* d_db, float* d_dx, const float* d_grad,
                                          const float* d_col, const float* d_w, float* d_gr,
                                          float* d_dcol, int N, int C, int H, int W, int Cout, int KH,

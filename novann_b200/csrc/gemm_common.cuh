@@ -74,10 +74,11 @@ nvq_status nvq_conv_launch_pair_implicit(float* d_out, const uint16_t* d_x_nhwc,
 
 // The same convolution with the operands swapped (output channels on the MMA's M side, up to 256
 // output positions on its N side): the form for few output channels.
+// With d_out_nhwc set the result goes there as bf16 (N*OH*OW) x Cout (NHWC) instead, ReLU optional.
 nvq_status nvq_conv_launch_swapped(float* d_out, const uint16_t* d_x_nhwc, const uint16_t* d_w,
                                    const float* d_scales, const float* d_bias, int N, int C, int H, int W,
                                    int Cout, int KH, int KW, int ph, int pw, int sh, int sw, int device,
-                                   cudaStream_t st);
+                                   cudaStream_t st, uint16_t* d_out_nhwc = nullptr, int relu = 0);
 
 #ifdef __CUDACC__
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {

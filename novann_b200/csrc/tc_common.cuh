@@ -107,6 +107,13 @@ __device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap
         "l"(map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n)
         : "memory");
 }
+// 2-D tiled store from this CTA's shared memory (bulk async group of the issuing thread)
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t smem_src, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+        "r"(smem_src), "r"(x), "r"(y)
+        : "memory");
+}
 // 3-D tiled store from this CTA's shared memory (bulk async group of the issuing thread)
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t smem_src, int x, int y, int z) {
     asm volatile(

@@ -255,6 +255,26 @@ def conv2d_q_host(x, wq, w_scales, b, kernel, stride=(1, 1), padding=(0, 0),
     return out.to_numpy(np.float32, (n, cout, oh, ow))
 
 
+def conv2d_q_nhwc_device(out: DeviceBuffer, x: DeviceBuffer, wq: DeviceBuffer, fmt: str,
+                         w_scales: DeviceBuffer, bias: DeviceBuffer | None, workspace: DeviceBuffer,
+                         n: int, c: int, h: int, w: int, cout: int, kernel, stride=(1, 1), padding=(0, 0),
+                         relu: bool = False, stream=None) -> None:
+    """Quantised convolution with bf16 NHWC activations in and out (``nvq_conv2d_fwd_q_nhwc``):
+    the form chained quantised layers use, nothing is converted or re-laid-out per call."""
+    check(lib().nvq_conv2d_fwd_q_nhwc(out.at(0), x.at(0), wq.at(0), _lib.DTYPE_IDS[fmt], w_scales.at(0),
+                                      bias.at(0) if bias is not None else None, workspace.at(0),
+                                      workspace.nbytes, n, c, h, w, cout, kernel[0], kernel[1], stride[0],
+                                      stride[1], padding[0], padding[1], int(relu), x.device, _sptr(stream)))
+
+
+def nchw_f32_to_nhwc_bf16_device(dst: DeviceBuffer, src: DeviceBuffer, n: int, c: int, s: int, stream=None) -> None:
+    check(lib().nvq_nchw_f32_to_nhwc_bf16(dst.at(0), src.at(0), n, c, s, src.device, _sptr(stream)))
+
+
+def nhwc_bf16_to_nchw_f32_device(dst: DeviceBuffer, src: DeviceBuffer, n: int, c: int, s: int, stream=None) -> None:
+    check(lib().nvq_nhwc_bf16_to_nchw_f32(dst.at(0), src.at(0), n, c, s, src.device, _sptr(stream)))
+
+
 def conv2d_bwd_f32_host(grad, col, w, x_shape, stride, padding, with_bias: bool = True, device: int = 0):
     """``Conv2d.backward`` (novann/layers/convolutional/conv2d.py:179-207): returns
     (dW (Cout,C,KH,KW), db (Cout,1) or None, dX (N,C,H,W))."""

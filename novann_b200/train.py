@@ -247,3 +247,71 @@ class QuantMLPInference:
         st.sync()
         self.F.check_device_errors(self.device)
         return out
+
+
+class QuantConvChain:
+    """A stack of quantised 3x3-style convolutions (optionally each followed by ReLU) whose
+    activations stay in HBM as bf16 NHWC from the first layer to the last: one layout conversion
+    at each end of the chain, none between layers (``nvq_conv2d_fwd_q_nhwc``).  The weights are
+    quantised once at construction; ``forward`` takes and returns fp32 NCHW host arrays like
+    ``F.conv2d`` (novann/functional.py:275-385), ``forward_device`` works on resident buffers.
+
+    ``layers``: list of dicts with ``weight`` (Cout, C, KH, KW) fp32, ``bias`` (Cout,) or None,
+    ``stride``, ``padding`` (pairs) and ``relu`` (bool).  Shape rules of the entry point apply
+    (strides 1 or 2, C % 64 == 0, Cout % 8 == 0, zero padding)."""
+
+    def __init__(self, layers, input_shape, fmt: str = "e4m3", device: int = 0):
+        from . import functional as F, quant
+        self.F, self.device, self.fmt = F, device, fmt
+        self.stream = Stream(device)
+        n, c, h, w = input_shape
+        self.shapes = [(n, c, h, w)]
+        self.layers = []
+        for spec in layers:
+            wt = np.ascontiguousarray(spec["weight"], np.float32)
+            cout, cin, kh, kw = wt.shape
+            if cin != c:
+                raise ValueError(f"layer expects {cin} input channels, got {c}")
+            sh, sw = spec.get("stride", (1, 1))
+            ph, pw = spec.get("padding", (0, 0))
+            w_col = wt.reshape(cout, -1)
+            q = 32 if fmt == "e2m1_b32" else 16
+            kpad = (w_col.shape[1] + q - 1) // q * q
+            padded = np.zeros((cout, kpad), np.float32)
+            padded[:, :w_col.shape[1]] = w_col
+            codes, scales = quant.quantize_weight(padded, fmt, device)
+            oh, ow = F.conv2d_out_size(h, w, kh, kw, sh, sw, ph, pw)
+            b = spec.get("bias")
+            self.layers.append(dict(
+                codes=DeviceBuffer.from_numpy(codes, device), scales=DeviceBuffer.from_numpy(scales, device),
+                bias=None if b is None else DeviceBuffer.from_numpy(np.ascontiguousarray(b, np.float32).ravel(), device),
+                ws=DeviceBuffer(cout * cin * kh * kw * 2, device), geom=(n, c, h, w, cout, (kh, kw), (sh, sw), (ph, pw)),
+                relu=bool(spec.get("relu", False))))
+            c, h, w = cout, oh, ow
+            self.shapes.append((n, c, h, w))
+        self.act = [DeviceBuffer(int(np.prod(s)) * 2, device) for s in self.shapes]
+        self.d_in32 = DeviceBuffer(int(np.prod(self.shapes[0])) * 4, device)
+        self.d_out32 = DeviceBuffer(int(np.prod(self.shapes[-1])) * 4, device)
+
+    def forward_device(self) -> None:
+        """act[0] (bf16 NHWC) -> act[-1] (bf16 NHWC), one kernel pair per layer on ``self.stream``."""
+        for i, L in enumerate(self.layers):
+            n, c, h, w, cout, k, s, p = L["geom"]
+            self.F.conv2d_q_nhwc_device(self.act[i + 1], self.act[i], L["codes"], self.fmt, L["scales"], L["bias"],
+                                        L["ws"], n, c, h, w, cout, k, s, p, relu=L["relu"], stream=self.stream)
+
+    def forward(self, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x, np.float32)
+        if x.shape != self.shapes[0]:
+            raise ValueError(f"expected input {self.shapes[0]}, got {x.shape}")
+        n, c, h, w = self.shapes[0]
+        self.d_in32.upload(x, stream=self.stream)
+        self.F.nchw_f32_to_nhwc_bf16_device(self.act[0], self.d_in32, n, c, h * w, stream=self.stream)
+        self.forward_device()
+        n, c, h, w = self.shapes[-1]
+        self.F.nhwc_bf16_to_nchw_f32_device(self.d_out32, self.act[-1], n, c, h * w, stream=self.stream)
+        out = np.empty(self.shapes[-1], np.float32)
+        self.d_out32.download(out, stream=self.stream)
+        self.stream.sync()
+        self.F.check_device_errors(self.device)
+        return out

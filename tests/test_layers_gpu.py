@@ -499,3 +499,88 @@ def test_quant_conv2d_layer_fp4(gpu):
     y = layer(x)
     ref = o.conv2d_fwd_f32(x, layer.weight.data, layer.bias.data, (1, 1), (1, 1))
     assert y.shape == ref.shape and o.max_abs_rel(y, ref) <= 2.5e-1
+
+
+@pytest.mark.parametrize("case", [
+    (2, 64, 16, 16, 64, 3, 1, 1),       # one channel block; quarters past Cout are clipped by the store
+    (3, 128, 15, 13, 72, 3, 1, 1),      # odd sizes: ragged tiles take the register-store tail
+    (2, 64, 12, 20, 40, 3, 0, 2),       # stride 2, no padding
+    (5, 64, 28, 28, 128, 3, 1, 1),      # whole tiles, TMA stores only
+    (2, 64, 9, 17, 264, 5, 2, 1),       # three channel blocks, 5 x 5 taps
+])
+@pytest.mark.parametrize("relu", [False, True])
+def test_nhwc_bf16_conv_equals_the_nchw_entry_point(gpu, case, relu):
+    """nvq_conv2d_fwd_q_nhwc (bf16 NHWC in and out, the contract between chained quantised
+    layers) against nvq_conv2d_fwd_q on the same codes: the same kernel does the contraction, so
+    the bf16 results are the same bits once both are laid out alike; ReLU is the reference's
+    v * (v > 0)."""
+    from novann_b200.device import DeviceBuffer
+    n, c, h, w, cout, k, p, s = case
+    rng = np.random.default_rng(sum(case))
+    x = rng.standard_normal((n, c, h, w)).astype(np.float32)
+    wt = (rng.standard_normal((cout, c, k, k)) * 0.05).astype(np.float32)
+    b = (rng.standard_normal(cout) * 0.1).astype(np.float32)
+    codes, scales = quant.quantize_weight(wt.reshape(cout, -1), "e4m3", gpu)
+    want = F.conv2d_q_host(x, codes, scales, b, (k, k), (s, s), (p, p), "zeros", "e4m3", gpu)
+    if relu:
+        want = want * (want > 0)
+    oh, ow = want.shape[2], want.shape[3]
+    dx32 = DeviceBuffer.from_numpy(x, gpu)
+    dx = DeviceBuffer(x.size * 2, gpu)
+    F.nchw_f32_to_nhwc_bf16_device(dx, dx32, n, c, h * w)
+    assert np.array_equal(dx.to_numpy(np.uint16, (n, h, w, c)),
+                          o.f32_to_bf16_bits(x).reshape(n, c, h, w).transpose(0, 2, 3, 1))
+    dq, ds, db = (DeviceBuffer.from_numpy(a, gpu) for a in (codes, scales, b))
+    ws = DeviceBuffer(cout * c * k * k * 2, gpu)
+    guard = 256
+    dy = DeviceBuffer(n * oh * ow * cout * 2 + guard, gpu)
+    dy.zero()
+    F.conv2d_q_nhwc_device(dy, dx, dq, "e4m3", ds, db, ws, n, c, h, w, cout, (k, k), (s, s), (p, p), relu=relu)
+    from novann_b200.device import device_sync
+    device_sync(gpu)
+    F.check_device_errors(gpu)
+    y = dy.to_numpy(np.uint16, (n * oh * ow * cout + guard // 2,))
+    assert not y[n * oh * ow * cout:].any()                       # nothing written past the end
+    got = o.bf16_bits_to_f32(y[:n * oh * ow * cout]).reshape(n, oh, ow, cout).transpose(0, 3, 1, 2)
+    assert np.array_equal(got.view(np.uint32), np.ascontiguousarray(want).view(np.uint32))
+    back = DeviceBuffer(n * oh * ow * cout * 4, gpu)
+    F.nhwc_bf16_to_nchw_f32_device(back, dy, n, cout, oh * ow)
+    assert np.array_equal(back.to_numpy(np.float32, want.shape).view(np.uint32), np.ascontiguousarray(want).view(np.uint32))
+
+
+def test_quant_conv_chain_keeps_activations_bf16_nhwc(gpu):
+    """Three chained quantised convolutions with ReLU between them: one layout conversion at each
+    end, none between layers; equal, bit for bit, to three separate calls of the NCHW entry
+    point with ReLU on the host in between."""
+    from novann_b200.train import QuantConvChain
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((4, 64, 20, 20)).astype(np.float32)
+    specs = []
+    for cin, cout, stride, relu in ((64, 128, 1, True), (128, 64, 2, True), (64, 72, 1, False)):
+        specs.append(dict(weight=(rng.standard_normal((cout, cin, 3, 3)) * (2.0 / (9 * cin)) ** 0.5).astype(np.float32),
+                          bias=(rng.standard_normal(cout) * 0.1).astype(np.float32),
+                          stride=(stride, stride), padding=(1, 1), relu=relu))
+    chain = QuantConvChain(specs, x.shape, "e4m3", gpu)
+    got = chain.forward(x)
+    cur = x
+    for sp in specs:
+        cout = sp["weight"].shape[0]
+        codes, scales = quant.quantize_weight(sp["weight"].reshape(cout, -1), "e4m3", gpu)
+        cur = F.conv2d_q_host(cur, codes, scales, sp["bias"], (3, 3), sp["stride"], sp["padding"], "zeros", "e4m3", gpu)
+        if sp["relu"]:
+            cur = cur * (cur > 0)
+    assert got.shape == cur.shape == (4, 72, 10, 10)
+    assert np.array_equal(got.view(np.uint32), np.ascontiguousarray(cur).view(np.uint32))
+    assert np.array_equal(chain.forward(x).view(np.uint32), got.view(np.uint32))     # same bits twice
+
+
+def test_nhwc_conv_refuses_shapes_outside_its_rule(gpu):
+    from novann_b200.device import DeviceBuffer
+    d = DeviceBuffer(1 << 16, gpu)
+    from novann_b200 import _lib
+    st = _lib.lib().nvq_conv2d_fwd_q_nhwc(d.at(0), d.at(0), d.at(0), _lib.E4M3, d.at(0), None, d.at(0), d.nbytes,
+                                          1, 48, 8, 8, 16, 3, 3, 1, 1, 1, 1, 0, gpu, None)      # C % 64 != 0
+    assert st == _lib.ERR_UNSUPPORTED and b"nvq_conv2d_fwd_q" in _lib.lib().nvq_last_error()
+    st = _lib.lib().nvq_conv2d_fwd_q_nhwc(d.at(0), d.at(0), d.at(0), _lib.E4M3, d.at(0), None, d.at(0), d.nbytes,
+                                          1, 64, 8, 8, 16, 3, 3, 3, 3, 1, 1, 0, gpu, None)      # stride 3
+    assert st == _lib.ERR_UNSUPPORTED
