@@ -192,8 +192,8 @@ nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf16, const ui
                           size_t M, size_t N, size_t K, void* d_workspace, size_t workspace_bytes,
                           int device, void* stream);
 /* nvq_linear_fwd with the kernel path chosen by the caller instead of by the shape rules above.
- * `path` is NVQ_LINEAR_AUTO (= nvq_linear_fwd) or NVQ_LINEAR_BF16_ACTIVATIONS, optionally
- * or-ed with at most one of the three kernel selectors.  A kernel selector switches the
+ * `path` is NVQ_LINEAR_AUTO (= nvq_linear_fwd), NVQ_LINEAR_BF16_ACTIVATIONS or
+ * NVQ_LINEAR_CLUSTER_REDUCE, optionally or-ed with at most one of the three kernel selectors.  A kernel selector switches the
  * few-rows kernels off; NVQ_LINEAR_EXPAND_IN_KERNEL falls back to the expansion pass where the
  * in-kernel form does not apply (FP4 weights, M <= 128, K % 16 != 0). */
 enum {
@@ -201,7 +201,13 @@ enum {
     NVQ_LINEAR_BF16_ACTIVATIONS = 1 << 0, /* M <= 128: no two-piece E4M3 carrier for the activations */
     NVQ_LINEAR_EXPAND_IN_KERNEL = 1 << 1, /* FP8 codes expanded in shared memory, nothing written to HBM */
     NVQ_LINEAR_SINGLE_CTA = 1 << 2,       /* expansion pass + one CTA per 128 x 256 tile */
-    NVQ_LINEAR_CTA_PAIR = 1 << 3          /* expansion pass + CTA pair per 256 x 256 tile */
+    NVQ_LINEAR_CTA_PAIR = 1 << 3,         /* expansion pass + CTA pair per 256 x 256 tile */
+    NVQ_LINEAR_CLUSTER_REDUCE = 1 << 4    /* M <= 32, FP8 codes, a weight that one wave of thread-block
+                                             clusters covers: the CTAs of a cluster split K and add
+                                             their partial sums through distributed shared memory
+                                             (two kernels, nothing through HBM) instead of the
+                                             split / stream / reduce kernels; same carrier, same
+                                             scales; measured no faster, so not the default */
 };
 nvq_status nvq_linear_fwd_opts(uint16_t* d_y_bf16, const uint16_t* d_x_bf16, const uint8_t* d_wq,
                                nvq_dtype w_fmt, const float* d_w_scales, const float* d_bias,

@@ -517,9 +517,10 @@ extern "C" nvq_status nvq_linear_fwd_opts(uint16_t* d_y_bf16, const uint16_t* d_
                                           size_t workspace_bytes, uint32_t path, int device,
                                           void* stream) {
     NVQ_REQUIRE(d_y_bf16 && d_x_bf16 && d_wq && d_w_scales, "nvq_linear_fwd: null buffer");
+    NVQ_REQUIRE(K % 8 == 0 && N % 8 == 0, "nvq_linear_fwd: K (%zu) and N (%zu) must be multiples of 8", K, N);
     const uint32_t kernel_bits = path & (NVQ_LINEAR_EXPAND_IN_KERNEL | NVQ_LINEAR_SINGLE_CTA | NVQ_LINEAR_CTA_PAIR);
     NVQ_REQUIRE((path & ~(uint32_t)(NVQ_LINEAR_BF16_ACTIVATIONS | NVQ_LINEAR_EXPAND_IN_KERNEL |
-                                    NVQ_LINEAR_SINGLE_CTA | NVQ_LINEAR_CTA_PAIR)) == 0 &&
+                                    NVQ_LINEAR_SINGLE_CTA | NVQ_LINEAR_CTA_PAIR | NVQ_LINEAR_CLUSTER_REDUCE)) == 0 &&
                     (kernel_bits & (kernel_bits - 1)) == 0,
                 "nvq_linear_fwd_opts: unknown or contradictory path selector 0x%x", path);
     NVQ_REQUIRE(M > 0 && N > 0 && K > 0, "nvq_linear_fwd: empty problem");
@@ -553,7 +554,8 @@ extern "C" nvq_status nvq_linear_fwd_opts(uint16_t* d_y_bf16, const uint16_t* d_
         if (w_fmt != NVQ_E2M1_B32 && !(path & NVQ_LINEAR_BF16_ACTIVATIONS) &&
             workspace_bytes >= nvq_linear_small_m_direct_workspace(M, N, K, device))
             return nvq_linear_launch_small_m_direct(d_y_bf16, d_x_bf16, d_wq, w_fmt, d_w_scales, d_bias, M, N,
-                                                    K, d_workspace, device, st);
+                                                    K, d_workspace, device, st,
+                                                    (path & NVQ_LINEAR_CLUSTER_REDUCE) != 0);
         return nvq_linear_launch_small_m(d_y_bf16, d_x_bf16, d_wq, w_fmt, d_w_scales, d_bias, M, N, K,
                                          (float*)d_workspace, device, st);
     }

@@ -56,10 +56,13 @@ size_t nvq_linear_small_m_workspace(size_t M, size_t N, size_t K, int device);
 // FP8 codes only: the weight codes are the MMA operand as they are (kind::f8f6f4) and each
 // activation row is split into two rows of E4M3 codes; workspace = partial sums + those codes.
 size_t nvq_linear_small_m_direct_workspace(size_t M, size_t N, size_t K, int device);
+// use_cluster: at most 32 rows and a weight that one wave of thread-block clusters covers run
+// as two kernels (split, then a clustered stream whose CTAs add their partial sums through
+// distributed shared memory) instead of three; other shapes ignore the request.
 nvq_status nvq_linear_launch_small_m_direct(uint16_t* d_y, const uint16_t* d_x, const uint8_t* d_wq,
                                             nvq_dtype fmt, const float* d_scales, const float* d_bias,
                                             size_t M, size_t N, size_t K, void* d_workspace, int device,
-                                            cudaStream_t st);
+                                            cudaStream_t st, bool use_cluster = false);
 nvq_status nvq_linear_launch_small_m(uint16_t* d_y, const uint16_t* d_x, const uint8_t* d_wq,
                                      nvq_dtype fmt, const float* d_scales, const float* d_bias,
                                      size_t M, size_t N, size_t K, float* d_partial, int device,

@@ -399,6 +399,331 @@ Geometry geometry(size_t M, size_t N, size_t K, int device) {
     return g;
 }
 
+
+// ---------------------------------------------------------------- clustered form (M <= 32)
+// For at most 32 rows and a weight that ONE wave of thread-block clusters covers, the fixed costs
+// of the call (kernel boundaries, partial sums through HBM) outweigh the weight stream: 16 MB of
+// codes stream in 2.5 us.  Here a cluster of S CTAs owns one 128-row weight block, each CTA
+// takes 1/S of K, and the partial sums meet in distributed shared memory: after a cluster
+// barrier CTA r of the cluster adds, in rank order, the S partial sums of the activation rows
+// m = r, r + S, ... (so the reduction is spread over the cluster and deterministic), applies
+// a_m, s_n, b_n and stores bf16.  No partial sum goes to HBM and no third kernel runs.
+//
+//   thread 0    barrier set-up, then at once the first ring of weight tiles (TMA); after the
+//               wait for the activation-splitting kernel, the activation tiles
+//   warp 1      TMEM allocation (off the producer's path), MMA issue (128 x 2 MP x 32), commit
+//   warps 2-5   epilogue: TMEM -> p1 sum + p2 sum / 16 -> own shared memory; after the cluster
+//               barrier the cross-CTA sums and the bf16 stores
+// Every mbarrier wait is bounded; both cluster barriers are reached by every thread of every CTA
+// whatever happened before them.
+constexpr int CL_MAX_MP = 32;
+constexpr int CL_STAGES = 8;                                 // ring slots at most; a CTA with fewer k-blocks takes fewer
+constexpr int CL_TMEM_COLS = 64;
+// Shared memory of a CTA: ring of `stages` slots (weight tile + activation tile), its partial sums
+// [MP][128] fp32, the barriers.
+__host__ __device__ constexpr int cl_slot_bytes(int MP) { return A_BYTES + 2 * MP * BKC; }
+__host__ __device__ constexpr int cl_smem_bytes(int MP, int stages) {
+    return 1024 + stages * cl_slot_bytes(MP) + MP * WROWS * 4 + 1024;
+}
+
+enum { ERR_CL_PRODUCER = 51, ERR_CL_MMA = 52, ERR_CL_EPILOGUE = 53 };
+
+struct ClusterParams {
+    uint16_t* y;            // M x N bf16
+    const float* xscale;    // a_m, MP floats
+    const float* scales;    // N or nullptr
+    const float* bias;      // N or nullptr
+    int M, MP, N, K;
+    int S;                  // CTAs per cluster = K ranges per weight block
+    int kb_per_cta, k_blocks;
+    int stages;             // ring slots of this launch
+    int* status;
+};
+
+struct ClusterShared {
+    uint64_t full[CL_STAGES];
+    uint64_t empty[CL_STAGES];
+    uint64_t tmem_full;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+// Not volatile on purpose: the loads of a thread's values are independent and must be in flight
+// together (a remote shared-memory load takes a few hundred cycles).  They stay behind the
+// cluster barrier through `token`, a zero that barrier's asm statement produces.
+__device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr, uint32_t token) {
+    float v;
+    asm("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr + token));
+    return v;
+}
+__device__ __forceinline__ uint32_t cluster_sync_token() {
+    uint32_t z;
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;\n\tmov.u32 %0, 0;" : "=r"(z)::"memory");
+    return z;
+}
+
+
+template <int FMT>
+__global__ void __launch_bounds__(THREADS, 1)
+linear_few_rows_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                               const ClusterParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = tc::smem_u32(smem_raw);
+    const uint32_t tiles = (raw + 1023u) & ~1023u;
+    const int CL_SLOT = cl_slot_bytes(p.MP), STAGES_RT = p.stages;
+    const uint32_t ring_bytes = (uint32_t)(STAGES_RT * CL_SLOT);
+    const uint32_t part = tiles + ring_bytes;
+    ClusterShared* sh = (ClusterShared*)(smem_raw + (tiles - raw) + ring_bytes + (uint32_t)p.MP * WROWS * 4u);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int* abort_flag = &sh->abort_flag;
+    const int rank = (int)tc::cluster_ctarank();          // this CTA's K range
+    const int nb = (int)blockIdx.x / p.S;                 // this cluster's weight block
+    const int kb0 = rank * p.kb_per_cta;
+    const int nkb = max(0, min(p.kb_per_cta, p.k_blocks - kb0));
+    const uint32_t NP = 2u * (uint32_t)p.MP;              // MMA N: p1 columns, then p2 columns
+    const uint32_t X_BYTES = NP * BKC;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < CL_STAGES; s++) {
+            tc::mbar_init(tc::smem_u32(&sh->full[s]), 1);
+            tc::mbar_init(tc::smem_u32(&sh->empty[s]), 1);
+        }
+        tc::mbar_init(tc::smem_u32(&sh->tmem_full), 1);
+        sh->abort_flag = 0;
+        tc::mbar_fence_init();
+        // The weight does not depend on the kernel that splits the activations, which may still
+        // be running: the first ring of weight tiles is requested right here, before anything
+        // else exists; the activation tiles of those slots follow after the wait for that kernel.
+        for (int i = 0; i < nkb && i < STAGES_RT; i++) {
+            const uint32_t fbar = tc::smem_u32(&sh->full[i]);
+            tc::mbar_arrive_expect_tx(fbar, A_BYTES + X_BYTES);
+            tc::tma_load_2d(tiles + i * CL_SLOT, &map_w, fbar, (kb0 + i) * BKC, nb * WROWS);
+        }
+    }
+    __syncthreads();                                      // the barriers exist
+
+    float sn = 1.f, bn = 0.f, xs_mine[8];     // epilogue threads: channel scale, bias, a_m of the rows this CTA closes
+#pragma unroll
+    for (int q = 0; q < 8; q++) xs_mine[q] = 0.f;
+    uint32_t tmem_base = 0;
+    if (warp >= 1) {
+        // TMEM allocation concerns the MMA warp and the epilogue warps only (named barrier 1, 160
+        // threads); the producer is not held up by it
+        if (warp == 1) {
+            tc::tmem_alloc(tc::smem_u32(&sh->tmem_base), CL_TMEM_COLS);
+            tc::tmem_relinquish();
+        }
+        tc::tc_fence_before();
+        asm volatile("bar.sync 1, 160;" ::: "memory");
+        tc::tc_fence_after();
+        tmem_base = sh->tmem_base;
+    }
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");   // the activation codes are complete and visible
+            for (int i = 0; i < nkb && i < STAGES_RT; i++)
+                tc::tma_load_2d(tiles + i * CL_SLOT + A_BYTES, &map_x, tc::smem_u32(&sh->full[i]), (kb0 + i) * BKC, 0);
+            for (int i = STAGES_RT; i < nkb; i++) {
+                const int stage = i % STAGES_RT;
+                if (!tc::mbar_wait(tc::smem_u32(&sh->empty[stage]), ((i / STAGES_RT) - 1) & 1, abort_flag, ERR_CL_PRODUCER))
+                    break;
+                const uint32_t fbar = tc::smem_u32(&sh->full[stage]);
+                tc::mbar_arrive_expect_tx(fbar, A_BYTES + X_BYTES);
+                tc::tma_load_2d(tiles + stage * CL_SLOT, &map_w, fbar, (kb0 + i) * BKC, nb * WROWS);
+                tc::tma_load_2d(tiles + stage * CL_SLOT + A_BYTES, &map_x, fbar, (kb0 + i) * BKC, 0);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0 && nkb > 0) {
+            // A = weight codes (E4M3 = 0, E5M2 = 1), B = activation codes (E4M3)
+            const uint32_t idesc = tc::idesc_f16(WROWS, NP, FMT == NVQ_E5M2 ? 1u : 0u, 0u);
+            bool ok = true;
+            // The MMAs of a k-block are tiny (128 x 2 MP x 32, four of them); what costs is the
+            // round around them (wait, fence, commit: ~250 ns).  The activation tiles arrive last
+            // and together, so the slots are taken four at a time: one round per four k-blocks,
+            // and a slot is only handed back when the ring will be walked again.
+            const bool reuse = nkb > STAGES_RT;
+            for (int i0 = 0; i0 < nkb && ok; i0 += 4) {
+                const int i1 = min(nkb, i0 + 4);
+                for (int i = i0; i < i1 && ok; i++)
+                    ok = tc::mbar_wait(tc::smem_u32(&sh->full[i % STAGES_RT]), (i / STAGES_RT) & 1, abort_flag, ERR_CL_MMA);
+                if (!ok) break;
+                tc::tc_fence_after();
+                for (int i = i0; i < i1; i++) {
+                    const int stage = i % STAGES_RT;
+                    const uint64_t a_desc = tc::smem_desc_k_sw128(tiles + stage * CL_SLOT);
+                    const uint64_t b_desc = tc::smem_desc_k_sw128(tiles + stage * CL_SLOT + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < 4; k++)      // four 32-byte k-steps of 32 codes
+                        tc::tc_mma_f8(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    if (reuse) tc::tc_commit(tc::smem_u32(&sh->empty[stage]));
+                }
+            }
+            if (ok) tc::tc_commit(tc::smem_u32(&sh->tmem_full));
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue: own partial sums
+        const int quarter = warp & 3;
+        const int wrow = quarter * 32 + lane;             // weight row of this thread within the block
+        // what the closing sums need from global memory is fetched now, while the MMAs run
+        {
+            const int n = nb * WROWS + wrow;
+            sn = (p.scales && n < p.N) ? p.scales[n] : 1.f;
+            bn = (p.bias && n < p.N) ? p.bias[n] : 0.f;
+            asm volatile("griddepcontrol.wait;" ::: "memory");   // xscale comes from the splitting kernel
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                const int m = rank + q * p.S;
+                xs_mine[q] = m < p.M ? p.xscale[m] : 0.f;
+            }
+        }
+        bool ok = nkb > 0 && tc::mbar_wait(tc::smem_u32(&sh->tmem_full), 0, abort_flag, ERR_CL_EPILOGUE);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (ok) tc::tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        // thread = weight row: for a fixed activation row a warp writes 32 consecutive floats
+#pragma unroll
+        for (int c = 0; c < CL_MAX_MP; c += 16) {
+            if (c < p.MP) {
+                uint32_t r1[16], r2[16];
+                if (ok) {
+                    tc::tmem_ld_32x16(taddr + c, r1);
+                    tc::tmem_ld_32x16(taddr + p.MP + c, r2);
+                    tc::tmem_ld_wait();
+                }
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const float v = ok ? fmaf(__uint_as_float(r2[j]), 0.0625f, __uint_as_float(r1[j])) : 0.f;
+                    asm volatile("st.shared.f32 [%0], %1;" ::"r"(part + (uint32_t)((c + j) * WROWS + wrow) * 4u), "f"(v) : "memory");
+                }
+            }
+        }
+        if (ok) tc::tc_fence_before();
+    }
+
+    const uint32_t token = cluster_sync_token();          // every CTA's partial sums are in its shared memory
+    if (warp >= 2) {
+        // ------------------------------------------------------------ cross-CTA sums: rows m = rank, rank + S, ...
+        const int wrow = (warp & 3) * 32 + lane;
+        const int n = nb * WROWS + wrow;
+        uint32_t peer[8];
+#pragma unroll
+        for (int r = 0; r < 8; r++) peer[r] = tc::mapa(part + (uint32_t)wrow * 4u, (uint32_t)(r < p.S ? r : 0));
+        // rows rank, rank + S, ...: at most 32 / S of them, i.e. at most 8 for S >= 4; four at a time,
+        // their S loads each all in flight together
+#pragma unroll
+        for (int q0 = 0; q0 < 8; q0 += 4) {
+            const int m0 = rank + q0 * p.S;
+            if (m0 >= p.M) break;
+            float v[4][8];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const int m = m0 + q * p.S;
+#pragma unroll
+                for (int r = 0; r < 8; r++)
+                    v[q][r] = (m < p.M && r < p.S) ? ld_cluster_f32(peer[r] + (uint32_t)(m * WROWS) * 4u, token) : 0.f;
+            }
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const int m = m0 + q * p.S;
+                if (m < p.M && n < p.N) {
+                    float s = v[q][0];
+#pragma unroll
+                    for (int r = 1; r < 8; r++)
+                        if (r < p.S) s = __fadd_rn(s, v[q][r]);          // rank order: the same sum on every run
+                    const float out = fmaf(__fmul_rn(s, xs_mine[q0 + q]), sn, bn);
+                    p.y[(size_t)m * p.N + n] = (uint16_t)(pack_bf16(out, 0.f) & 0xFFFFu);
+                }
+            }
+        }
+    }
+    if (warp >= 2) {
+        // rows past the eight handled above (only for S < 4 with more than 8 S rows): plain loop
+        const int wrow = (warp & 3) * 32 + lane;
+        const int n = nb * WROWS + wrow;
+        for (int m = rank + 8 * p.S; m < p.M; m += p.S) {
+            float s = 0.f;
+            for (int r = 0; r < p.S; r++) {
+                const float t = ld_cluster_f32(tc::mapa(part + (uint32_t)(m * WROWS + wrow) * 4u, (uint32_t)r), token);
+                s = r == 0 ? t : __fadd_rn(s, t);
+            }
+            if (n < p.N) p.y[(size_t)m * p.N + n] = (uint16_t)(pack_bf16(fmaf(__fmul_rn(s, p.xscale[m]), sn, bn), 0.f) & 0xFFFFu);
+        }
+    }
+    tc::cluster_sync_all();          // nobody leaves while another CTA still reads its memory
+
+    // ---------------------------------------------------------------- teardown
+    if (*abort_flag) {
+        for (int i = 0; i < 64; i++) __nanosleep(20000);   // let copies in flight land
+    }
+    if (warp >= 1) {
+        tc::tc_fence_before();
+        asm volatile("bar.sync 1, 160;" ::: "memory");
+        tc::tc_fence_after();
+        if (warp == 1) tc::tmem_dealloc(tmem_base, CL_TMEM_COLS);
+    }
+    if (threadIdx.x == 0 && *abort_flag && p.status) atomicCAS(p.status, 0, *abort_flag);
+}
+
+struct ClusterPlan { int S, kb_per_cta, stages, smem; };
+
+// CTAs of the clustered kernel that can be resident at once in clusters of S (per device).
+int cluster_resident_ctas(int S, int smem, int device) {
+    static std::atomic<int> cache[64][4][256];       // S = 1, 2, 4, 8; shared memory in KB
+    const int si = S == 1 ? 0 : (S == 2 ? 1 : (S == 4 ? 2 : 3));
+    std::atomic<int>& slot = cache[device][si][(smem + 1023) / 1024 & 255];
+    int v = slot.load(std::memory_order_relaxed);
+    if (v) return v;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = S;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(S * 64);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, linear_few_rows_cluster_kernel<NVQ_E4M3>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        clusters = 0;
+    }
+    v = clusters > 0 ? clusters * S : -1;
+    slot.store(v, std::memory_order_relaxed);
+    return v;
+}
+
+// The cluster size that puts the most CTAs to work in a single wave; S = 0 when the problem does
+// not fit (more than 32 rows, or more weight blocks than one wave of clusters holds).
+ClusterPlan cluster_plan(const Geometry& g, size_t M, int device) {
+    ClusterPlan best = {0, 0, 0, 0};
+    if (g.MP > CL_MAX_MP) return best;
+    int best_ctas = 0;
+    for (int S = 1; S <= 8; S *= 2) {
+        const int kb = (g.k_blocks + S - 1) / S;
+        if ((S - 1) * kb >= g.k_blocks) continue;            // every CTA gets at least one k-block
+        // Always the full ring, i.e. one CTA per SM: with half-size rings two CTAs share an SM and a
+        // cluster of 8 covers 4096 x 4096 in one wave, but that measured slower (10.9 against 9.7 us
+        // per call for 16 x 4096 x 4096 from a CUDA graph) - twice the CTAs to launch and a wider
+        // cluster barrier cost more than the halved MMA chain saves.
+        const int stages = CL_STAGES;
+        const int smem = cl_smem_bytes(g.MP, stages);
+        const int cap = cluster_resident_ctas(S, smem, device);
+        if (cap <= 0 || g.n_blocks * S > cap) continue;
+        if (g.n_blocks * S > best_ctas) {
+            best_ctas = g.n_blocks * S;
+            best.S = S; best.kb_per_cta = kb; best.stages = stages; best.smem = smem;
+        }
+    }
+    (void)M;
+    return best;
+}
+
 }  // namespace
 
 // workspace: [fp32 partial sums][activation codes, 2 MP x K bytes][a_m, MP floats]
@@ -410,7 +735,7 @@ size_t nvq_linear_small_m_direct_workspace(size_t M, size_t N, size_t K, int dev
 nvq_status nvq_linear_launch_small_m_direct(uint16_t* d_y, const uint16_t* d_x, const uint8_t* d_wq,
                                             nvq_dtype fmt, const float* d_scales, const float* d_bias,
                                             size_t M, size_t N, size_t K, void* d_workspace, int device,
-                                            cudaStream_t st) {
+                                            cudaStream_t st, bool use_cluster) {
     NVQ_REQUIRE(M >= 1 && M <= 128 && K % 16 == 0, "small-M Linear: needs 1 <= M <= 128 and K %% 16 == 0");
     NVQ_REQUIRE(fmt == NVQ_E4M3 || fmt == NVQ_E5M2, "small-M direct Linear: FP8 weight codes only");
     NVQ_REQUIRE(M * N < (1u << 31) && N < (1u << 24) && K < (1u << 24) && N * K < (1ull << 40),
@@ -447,13 +772,47 @@ nvq_status nvq_linear_launch_small_m_direct(uint16_t* d_y, const uint16_t* d_x, 
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         NVQ_CUDA(cudaFuncSetAttribute(linear_small_m_direct_kernel<NVQ_E5M2>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        NVQ_CUDA(cudaFuncSetAttribute(linear_few_rows_cluster_kernel<NVQ_E4M3>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, cl_smem_bytes(CL_MAX_MP, CL_STAGES)));
+        NVQ_CUDA(cudaFuncSetAttribute(linear_few_rows_cluster_kernel<NVQ_E5M2>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, cl_smem_bytes(CL_MAX_MP, CL_STAGES)));
         attr_set[device] = true;
     }
     split_activations_kernel<<<g.MP, 256, 0, st>>>(d_x8, d_xscale, d_x, (int)M, g.MP, (int)K);
     NVQ_LAUNCHED();
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // set up under the previous kernel's tail
     attr[0].val.programmaticStreamSerializationAllowed = 1;
+    const ClusterPlan cp = use_cluster ? cluster_plan(g, M, device) : ClusterPlan{0, 0, 0, 0};
+    if (cp.S > 0) {
+        // two kernels: the split above, then the clustered stream with the reduction inside
+        ClusterParams q;
+        q.y = d_y;
+        q.xscale = d_xscale;
+        q.scales = d_scales;
+        q.bias = d_bias;
+        q.M = (int)M; q.MP = g.MP; q.N = (int)N; q.K = (int)K;
+        q.S = cp.S; q.kb_per_cta = cp.kb_per_cta; q.k_blocks = g.k_blocks;
+        q.stages = cp.stages;
+        q.status = p.status;
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = cp.S;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        cudaLaunchConfig_t ccfg = {};
+        ccfg.gridDim = dim3(g.n_blocks * cp.S);
+        ccfg.blockDim = dim3(THREADS);
+        ccfg.dynamicSmemBytes = cp.smem;
+        ccfg.stream = st;
+        ccfg.attrs = attr;
+        ccfg.numAttrs = 2;
+        if (fmt == NVQ_E4M3)
+            NVQ_CUDA(cudaLaunchKernelEx(&ccfg, linear_few_rows_cluster_kernel<NVQ_E4M3>, map_w, map_x, q));
+        else
+            NVQ_CUDA(cudaLaunchKernelEx(&ccfg, linear_few_rows_cluster_kernel<NVQ_E5M2>, map_w, map_x, q));
+        NVQ_LAUNCHED();
+        return NVQ_OK;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(g.grid);
     cfg.blockDim = dim3(THREADS);

@@ -32,7 +32,8 @@ def check_device_errors(device: int = 0) -> None:
 _LINEAR_PATHS = {None: _lib.LINEAR_AUTO, "auto": _lib.LINEAR_AUTO,
                  "bf16_activations": _lib.LINEAR_BF16_ACTIVATIONS,
                  "expand_in_kernel": _lib.LINEAR_EXPAND_IN_KERNEL,
-                 "single_cta": _lib.LINEAR_SINGLE_CTA, "cta_pair": _lib.LINEAR_CTA_PAIR}
+                 "single_cta": _lib.LINEAR_SINGLE_CTA, "cta_pair": _lib.LINEAR_CTA_PAIR,
+                 "cluster_reduce": _lib.LINEAR_CLUSTER_REDUCE}
 _CONV_PATHS = {None: _lib.CONV_AUTO, "auto": _lib.CONV_AUTO, "patch_matrix": _lib.CONV_PATCH_MATRIX,
                "cta_pair": _lib.CONV_CTA_PAIR}
 
@@ -42,7 +43,8 @@ def linear_q_device(y: DeviceBuffer, x: DeviceBuffer, wq: DeviceBuffer, fmt: str
                     workspace: DeviceBuffer | None, stream=None, path: str | None = None) -> None:
     """``workspace=None`` selects the in-kernel expansion of FP8 codes (M > 128, K % 16 == 0).
     ``path`` names a kernel path of ``nvq_linear_fwd_opts``: ``"bf16_activations"`` (M <= 128:
-    activations taken as bf16, no two-piece E4M3 carrier), ``"expand_in_kernel"``,
+    activations taken as bf16, no two-piece E4M3 carrier), ``"cluster_reduce"`` (M <= 32: the
+    clustered stream that adds its partial sums through distributed shared memory), ``"expand_in_kernel"``,
     ``"single_cta"``, ``"cta_pair"``; ``None`` lets the library choose."""
     check(lib().nvq_linear_fwd_opts(y.at(0), x.at(0), wq.at(0), _lib.DTYPE_IDS[fmt], w_scales.at(0),
                                     bias.at(0) if bias is not None else None, m, n, k,

@@ -9,7 +9,7 @@ so the tests also assert a much tighter bound (a few bf16 ulps of the largest ou
 import numpy as np
 import pytest
 
-from novann_b200 import functional as F, workloads
+from novann_b200 import _lib, functional as F, workloads
 from oracle import oracle_np as o
 
 pytestmark = pytest.mark.gpu
@@ -234,7 +234,7 @@ def test_linear_split_last_wave_and_deep_k(gpu, m, n, k):
     (128, 4096, 1024), (128, 136, 4160), (31, 20000, 64),
     (4, 256, 16400),      # rows longer than the activation-splitting kernel keeps in registers
 ])
-@pytest.mark.parametrize("few_rows_mode", ["direct", "convert"])
+@pytest.mark.parametrize("few_rows_mode", ["direct", "cluster_reduce", "convert"])
 def test_linear_few_rows_weight_streaming_kernel(gpu, fmt, m, n, k, few_rows_mode):
     """M <= 128 runs a weight-streaming kernel (codes read once, operands swapped, split along K
     with a deterministic reduction) - "direct": the codes are the tensor cores' operand and each
@@ -243,7 +243,7 @@ def test_linear_few_rows_weight_streaming_kernel(gpu, fmt, m, n, k, few_rows_mod
     row (same bits)."""
     xb, w, b = workloads.linear_inputs(m, n, k, seed=m + n)
     wq, sc = o.quantize_weight_per_channel(w, fmt)
-    path = "bf16_activations" if few_rows_mode == "convert" else None
+    path = {"convert": "bf16_activations", "cluster_reduce": "cluster_reduce", "direct": None}[few_rows_mode]
     y = F.linear_q_host(xb, wq, sc, b, fmt, gpu, path=path)
     y2 = F.linear_q_host(xb, wq, sc, b, fmt, gpu, path=path)
     assert np.array_equal(y, y2)
@@ -279,8 +279,10 @@ def test_linear_in_kernel_expansion_of_every_code(gpu, m, fmt):
 
 
 @pytest.mark.parametrize("fmt", ["e4m3", "e5m2"])
-def test_linear_few_rows_direct_every_code_and_activation_split(gpu, fmt):
-    """The direct few-rows kernel (FP8 codes straight into kind::f8f6f4 MMAs).  (1) Every weight
+@pytest.mark.parametrize("path", [None, "cluster_reduce"])
+def test_linear_few_rows_direct_every_code_and_activation_split(gpu, fmt, path):
+    """The direct few-rows kernels (FP8 codes straight into kind::f8f6f4 MMAs): the single cluster
+    split / stream / reduce form and the clustered form (a request other shapes ignore).  (1) Every weight
     code against x = 1: finite codes bit-exact, NaN codes NaN; an E5M2 infinity code meets the
     zero low-order piece of the activation and gives NaN where the bf16 paths give infinity (the
     quantiser never emits those codes).  (2) Activations that use all eight significant bits and
@@ -289,7 +291,7 @@ def test_linear_few_rows_direct_every_code_and_activation_split(gpu, fmt):
     n, k = 256, 64
     wq = np.repeat(np.arange(256, dtype=np.uint8)[:, None], k, axis=1)
     xb = o.f32_to_bf16_bits(np.ones((8, k), np.float32))
-    y = o.bf16_bits_to_f32(F.linear_q_host(xb, wq, np.ones(n, np.float32), None, fmt, gpu))
+    y = o.bf16_bits_to_f32(F.linear_q_host(xb, wq, np.ones(n, np.float32), None, fmt, gpu, path=path))
     table = o.E4M3_TABLE if fmt == "e4m3" else o.E5M2_TABLE
     with np.errstate(all="ignore"):
         want = o.bf16_bits_to_f32(o.f32_to_bf16_bits((table[np.arange(256)].astype(np.float64) * k).astype(np.float32)))
@@ -307,7 +309,7 @@ def test_linear_few_rows_direct_every_code_and_activation_split(gpu, fmt):
     assert np.array_equal(o.bf16_bits_to_f32(xb).astype(np.float64), x)
     w = rng.standard_normal((n, k)).astype(np.float32)
     wq, sc = o.quantize_weight_per_channel(w, fmt)
-    y = o.bf16_bits_to_f32(F.linear_q_host(xb, wq, sc, None, fmt, gpu)).astype(np.float64)
+    y = o.bf16_bits_to_f32(F.linear_q_host(xb, wq, sc, None, fmt, gpu, path=path)).astype(np.float64)
     wd = o.dequantize_fp8(wq, 1.0, fmt).astype(np.float64) * sc.astype(np.float64)[:, None]
     ref = x @ wd.T
     assert np.all(y[3] == 0.0)
@@ -329,4 +331,34 @@ def test_linear_few_rows_fp4_weights(gpu, m, n, k):
     assert o.max_abs_rel(y, ref) <= 2.0 ** -7
     y_old = o.bf16_bits_to_f32(F.linear_q_host(xb, packed, scales, b, "e2m1_b32", gpu, path="single_cta"))
     assert o.max_abs_rel(y, y_old) <= 2.0 ** -7
+    F.check_device_errors(gpu)
+
+
+@pytest.mark.parametrize("m,n,k", [(16, 4096, 4096), (1, 4096, 4096), (32, 2048, 1024), (8, 16000, 256), (5, 520, 2064),
+                                   (16, 128, 16384), (30, 4096, 4096)])
+@pytest.mark.parametrize("fmt", ["e4m3", "e5m2"])
+def test_linear_very_few_rows_clustered_kernel(gpu, m, n, k, fmt):
+    """``path="cluster_reduce"``: at most 32 rows and a weight one wave of CTA clusters covers run
+    as two kernels (activation split, then a clustered stream whose CTAs split K and add their
+    partial sums in rank order through distributed shared memory; no partial sum goes to HBM, no
+    third kernel).  Against the oracle, against the default three-kernel form (same carrier and
+    scales), twice the same bits, and with a non-finite activation."""
+    xb, w, b = workloads.linear_inputs(m, n, k, seed=m * 7 + n)
+    wq, sc = o.quantize_weight_per_channel(w, fmt)
+    before = _lib.lib().nvq_launch_count()
+    y = F.linear_q_host(xb, wq, sc, b, fmt, gpu, path="cluster_reduce")
+    assert _lib.lib().nvq_launch_count() - before == 2           # split + clustered stream
+    assert np.array_equal(y, F.linear_q_host(xb, wq, sc, b, fmt, gpu, path="cluster_reduce"))
+    want_bits, _ = o.linear_fwd_qweight(xb, wq, sc, b, fmt)
+    assert o.max_abs_rel(o.bf16_bits_to_f32(y), o.bf16_bits_to_f32(want_bits)) <= 2.0 ** -7
+    before = _lib.lib().nvq_launch_count()
+    y3 = F.linear_q_host(xb, wq, sc, b, fmt, gpu)
+    assert _lib.lib().nvq_launch_count() - before == 3
+    assert o.max_abs_rel(o.bf16_bits_to_f32(y), o.bf16_bits_to_f32(y3)) <= 2.0 ** -7
+    assert np.mean(y == y3) > 0.9
+    if m > 1:
+        bad = xb.copy()
+        bad[1, k // 2] = 0x7F80                                     # +inf in row 1
+        yb = o.bf16_bits_to_f32(F.linear_q_host(bad, wq, sc, b, fmt, gpu, path="cluster_reduce"))
+        assert np.all(np.isnan(yb[1])) and np.array_equal(yb[0], o.bf16_bits_to_f32(y)[0])
     F.check_device_errors(gpu)
