@@ -115,11 +115,14 @@ uint64_t nvq_launch_count(void);
 nvq_status nvq_cast(void* d_dst, nvq_dtype dst_dtype, const void* d_src, nvq_dtype src_dtype,
                     size_t n, int device, void* stream);
 
-/* Host-buffer variant of nvq_cast: h_src/h_dst are host arrays (pinned memory
- * gives full PCIe rate); the data is streamed through device staging buffers in
- * chunks with H2D, kernel and D2H overlapped.  Synchronous.  This is the call that
+/* Host-buffer variant of nvq_cast: h_src/h_dst are host arrays; the data is streamed through
+ * device staging buffers in chunks with H2D, kernel and D2H overlapped.  Page-locked arrays
+ * (nvq_host_alloc) move at full PCIe rate; plain (pageable) arrays of 8 MiB and more are
+ * staged through page-locked buffers of the library by a few host threads (about half that
+ * rate, three times what the driver's own handling of pageable copies gives).  Synchronous.  This is the call that
  * sits exactly where ndarray.astype sat (host array in, host array out).  The staging
- * buffers (6 x 64 MiB per device) are allocated by the first call on a device and kept
+ * buffers (6 x 64 MiB per device, and as much page-locked host memory once a pageable array
+ * was seen) are allocated by the first call on a device and kept
  * until nvq_shutdown; calls on one device are serialised, calls on different devices
  * run concurrently. */
 nvq_status nvq_cast_host(void* h_dst, nvq_dtype dst_dtype, const void* h_src,

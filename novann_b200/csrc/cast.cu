@@ -7,7 +7,12 @@
 // Finite and infinite values go through the hardware converters (cvt.rn.*), which
 // implement round-to-nearest-even with subnormals; a packet that holds a NaN takes
 // the integer path so the NaN payload rules hold bit for bit.
+#include <sched.h>
+#include <string.h>
+
+#include <condition_variable>
 #include <mutex>
+#include <thread>
 
 #include "elementwise.cuh"
 
@@ -215,21 +220,109 @@ extern "C" nvq_status nvq_cast(void* d_dst, nvq_dtype dst_dtype, const void* d_s
 // each with its own stream, keep one chunk uploading, one converting and one
 // downloading at any time, so the PCIe link runs in both directions at once.  In-stream
 // ordering alone makes the reuse of a slot's buffers safe.
+//
+// Page-locked arrays (nvq_host_alloc) are the copies' source and destination as they are.
+// A plain (pageable) array - what ndarray.astype is handed - cannot be: the driver stages such
+// copies itself through one small buffer and one thread (about 15 GB/s here for the cast sweep).
+// Those arrays go through page-locked staging buffers of the library instead, filled and
+// drained by a few host threads while the previous chunk is on the link.
 namespace {
 constexpr int kSlots = 3;
 constexpr size_t kChunkBytes = (size_t)64 << 20;  // per staging buffer: 64 MiB on the wide side
 constexpr int kMaxDev = 64;
+constexpr size_t kStageMinBytes = (size_t)8 << 20;   // smaller pageable arrays: the plain path
 
 struct Staging {
     std::mutex mu;            // one transfer at a time per device; devices are independent
     bool ready = false;
+    bool host_ready = false;
     cudaStream_t stream[kSlots];
+    cudaEvent_t done[kSlots];
     void* d_in[kSlots];
     void* d_out[kSlots];
+    void* h_in[kSlots];       // page-locked staging for pageable arrays (allocated on first need)
+    void* h_out[kSlots];
 };
 Staging g_staging[kMaxDev];
 
 size_t dtype_size(nvq_dtype t) { return t == NVQ_F64 ? 8 : (t == NVQ_F32 ? 4 : 2); }
+
+// ---- a small pool of host threads that copy memory in parallel ------------------------
+// Never destroyed: the workers are detached and sleep on a condition variable between jobs, so
+// a process that exits without nvq_shutdown just ends them.
+class CopyPool {
+  public:
+    static CopyPool& get() {
+        static CopyPool* pool = new CopyPool();
+        return *pool;
+    }
+    // dst[0, bytes) = src[0, bytes), split over the workers and the calling thread
+    void copy(void* dst, const void* src, size_t bytes) {
+        if (bytes < ((size_t)1 << 20) || workers_ == 0) {
+            memcpy(dst, src, bytes);
+            return;
+        }
+        std::unique_lock<std::mutex> call_lock(call_mu_);      // one parallel copy at a time
+        const int parts = workers_ + 1;
+        const size_t piece = ((bytes + parts - 1) / parts + 4095) & ~(size_t)4095;
+        {
+            std::lock_guard<std::mutex> lk(mu_);
+            dst_ = (char*)dst; src_ = (const char*)src; bytes_ = bytes; piece_ = piece;
+            pending_ = workers_;
+            generation_++;
+        }
+        cv_.notify_all();
+        run_piece(workers_);                                    // the caller takes the last piece
+        std::unique_lock<std::mutex> lk(mu_);
+        done_cv_.wait(lk, [&] { return pending_ == 0; });
+    }
+
+  private:
+    CopyPool() {
+        int n = 8;
+        cpu_set_t set;
+        if (sched_getaffinity(0, sizeof(set), &set) == 0) {
+            const int avail = CPU_COUNT(&set);
+            if (avail - 1 < n) n = avail - 1;
+        }
+        if (n < 0) n = 0;
+        workers_ = n;
+        for (int w = 0; w < n; w++) std::thread([this, w] { loop(w); }).detach();
+    }
+    void run_piece(int idx) {
+        const size_t off = (size_t)idx * piece_;
+        if (off < bytes_) memcpy(dst_ + off, src_ + off, bytes_ - off < piece_ ? bytes_ - off : piece_);
+    }
+    void loop(int idx) {
+        uint64_t seen = 0;
+        for (;;) {
+            {
+                std::unique_lock<std::mutex> lk(mu_);
+                cv_.wait(lk, [&] { return generation_ != seen; });
+                seen = generation_;
+            }
+            run_piece(idx);
+            std::lock_guard<std::mutex> lk(mu_);
+            if (--pending_ == 0) done_cv_.notify_all();
+        }
+    }
+    std::mutex call_mu_, mu_;
+    std::condition_variable cv_, done_cv_;
+    uint64_t generation_ = 0;
+    int workers_ = 0, pending_ = 0;
+    char* dst_ = nullptr;
+    const char* src_ = nullptr;
+    size_t bytes_ = 0, piece_ = 0;
+};
+
+bool is_pinned(const void* p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return a.type == cudaMemoryTypeHost || a.type == cudaMemoryTypeManaged;
+}
 }  // namespace
 
 // Frees the staging buffers and streams of every device (nvq_shutdown).
@@ -243,9 +336,14 @@ nvq_status nvq_cast_release_staging() {
             NVQ_CUDA(cudaStreamSynchronize(sg.stream[i]));
             NVQ_CUDA(cudaFree(sg.d_in[i]));
             NVQ_CUDA(cudaFree(sg.d_out[i]));
+            if (sg.host_ready) {
+                NVQ_CUDA(cudaFreeHost(sg.h_in[i]));
+                NVQ_CUDA(cudaFreeHost(sg.h_out[i]));
+            }
+            NVQ_CUDA(cudaEventDestroy(sg.done[i]));
             NVQ_CUDA(cudaStreamDestroy(sg.stream[i]));
         }
-        sg.ready = false;
+        sg.ready = sg.host_ready = false;
     }
     return NVQ_OK;
 }
@@ -265,6 +363,7 @@ extern "C" nvq_status nvq_cast_host(void* h_dst, nvq_dtype dst_dtype, const void
     if (!sg.ready) {
         for (int i = 0; i < kSlots; i++) {
             NVQ_CUDA(cudaStreamCreateWithFlags(&sg.stream[i], cudaStreamNonBlocking));
+            NVQ_CUDA(cudaEventCreateWithFlags(&sg.done[i], cudaEventDisableTiming));
             NVQ_CUDA(cudaMalloc(&sg.d_in[i], kChunkBytes));
             NVQ_CUDA(cudaMalloc(&sg.d_out[i], kChunkBytes));
         }
@@ -272,17 +371,59 @@ extern "C" nvq_status nvq_cast_host(void* h_dst, nvq_dtype dst_dtype, const void
     }
     const size_t ss = dtype_size(src_dtype), ds = dtype_size(dst_dtype);
     const size_t chunk = kChunkBytes / (ss > ds ? ss : ds);
-    int slot = 0;
-    for (size_t off = 0; off < n; off += chunk, slot = (slot + 1) % kSlots) {
-        size_t m = n - off < chunk ? n - off : chunk;
-        cudaStream_t st = sg.stream[slot];
-        NVQ_CUDA(cudaMemcpyAsync(sg.d_in[slot], (const char*)h_src + off * ss, m * ss,
-                                 cudaMemcpyHostToDevice, st));
-        s = nvq_cast(sg.d_out[slot], dst_dtype, sg.d_in[slot], src_dtype, m, device, st);
-        if (s != NVQ_OK) return s;
-        NVQ_CUDA(cudaMemcpyAsync((char*)h_dst + off * ds, sg.d_out[slot], m * ds,
-                                 cudaMemcpyDeviceToHost, st));
+    const bool stage_in = n * ss >= kStageMinBytes && !is_pinned(h_src);
+    const bool stage_out = n * ds >= kStageMinBytes && !is_pinned(h_dst);
+    if ((stage_in || stage_out) && !sg.host_ready) {
+        for (int i = 0; i < kSlots; i++) {
+            NVQ_CUDA(cudaHostAlloc(&sg.h_in[i], kChunkBytes, cudaHostAllocPortable));
+            NVQ_CUDA(cudaHostAlloc(&sg.h_out[i], kChunkBytes, cudaHostAllocPortable));
+        }
+        sg.host_ready = true;
     }
-    for (int i = 0; i < kSlots; i++) NVQ_CUDA(cudaStreamSynchronize(sg.stream[i]));
+    if (!stage_in && !stage_out) {
+        int slot = 0;
+        for (size_t off = 0; off < n; off += chunk, slot = (slot + 1) % kSlots) {
+            size_t m = n - off < chunk ? n - off : chunk;
+            cudaStream_t st = sg.stream[slot];
+            NVQ_CUDA(cudaMemcpyAsync(sg.d_in[slot], (const char*)h_src + off * ss, m * ss,
+                                     cudaMemcpyHostToDevice, st));
+            s = nvq_cast(sg.d_out[slot], dst_dtype, sg.d_in[slot], src_dtype, m, device, st);
+            if (s != NVQ_OK) return s;
+            NVQ_CUDA(cudaMemcpyAsync((char*)h_dst + off * ds, sg.d_out[slot], m * ds,
+                                     cudaMemcpyDeviceToHost, st));
+        }
+        for (int i = 0; i < kSlots; i++) NVQ_CUDA(cudaStreamSynchronize(sg.stream[i]));
+        return NVQ_OK;
+    }
+    // Staged form.  Iteration i fills the staging buffer of chunk i and puts its copies and its
+    // kernel on the slot's stream, then drains chunk i - 1, whose transfer ran meanwhile; a slot
+    // comes round again only after its chunk was drained.
+    CopyPool& pool = CopyPool::get();
+    const size_t n_chunks = (n + chunk - 1) / chunk;
+    for (size_t i = 0; i <= n_chunks; i++) {
+        if (i < n_chunks) {
+            const int slot = (int)(i % kSlots);
+            const size_t off = i * chunk, m = n - off < chunk ? n - off : chunk;
+            cudaStream_t st = sg.stream[slot];
+            const void* src = (const char*)h_src + off * ss;
+            if (stage_in) {
+                pool.copy(sg.h_in[slot], src, m * ss);
+                src = sg.h_in[slot];
+            }
+            NVQ_CUDA(cudaMemcpyAsync(sg.d_in[slot], src, m * ss, cudaMemcpyHostToDevice, st));
+            s = nvq_cast(sg.d_out[slot], dst_dtype, sg.d_in[slot], src_dtype, m, device, st);
+            if (s != NVQ_OK) return s;
+            NVQ_CUDA(cudaMemcpyAsync(stage_out ? sg.h_out[slot] : (void*)((char*)h_dst + off * ds), sg.d_out[slot],
+                                     m * ds, cudaMemcpyDeviceToHost, st));
+            NVQ_CUDA(cudaEventRecord(sg.done[slot], st));
+        }
+        if (i >= 1) {
+            const size_t j = i - 1;
+            const int slot = (int)(j % kSlots);
+            const size_t off = j * chunk, m = n - off < chunk ? n - off : chunk;
+            NVQ_CUDA(cudaEventSynchronize(sg.done[slot]));
+            if (stage_out) pool.copy((char*)h_dst + off * ds, sg.h_out[slot], m * ds);
+        }
+    }
     return NVQ_OK;
 }

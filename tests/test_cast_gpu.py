@@ -299,3 +299,39 @@ def test_f64_host_api(gpu):
     assert _as_f32(f, gpu) is f or np.shares_memory(_as_f32(f, gpu), f)
     with pytest.raises(TypeError):
         _as_f32(np.ones(4, np.int32), gpu)
+
+
+@pytest.mark.parametrize("src_pinned,dst_pinned", [(False, False), (True, False), (False, True)])
+def test_cast_host_api_pageable_arrays_are_staged(gpu, oracle_c, src_pinned, dst_pinned):
+    """Plain (pageable) NumPy arrays - what ndarray.astype is handed - go through the library's
+    page-locked staging buffers, filled and drained by host threads: several chunks, a ragged
+    last chunk, either side pageable; same bits as the page-locked path and as the oracle."""
+    n = (16 << 20) * 3 + 12345                       # three full staging chunks and a tail (fp32 side)
+    x = pinned_empty(n, np.float32) if src_pinned else np.empty(n, np.float32)
+    workloads.cast_input(n, seed=8, out=x)
+    out = pinned_empty(n, np.uint16) if dst_pinned else np.empty(n, np.uint16)
+    out[:] = 0xFFFF
+    got = quant.cast(x, "bf16", out=out, device=gpu)
+    assert got is out
+    assert np.array_equal(got, oracle_c.f32_to_bf16_bits(x))
+    back = quant.cast(got, "f32", src_dtype="bf16", device=gpu)          # pageable result array
+    assert np.array_equal(back.view(np.uint32), got.astype(np.uint32) << 16)
+
+
+def test_cast_host_api_from_two_threads(gpu, oracle_c):
+    """Two host threads cast different arrays on one device at once: the calls are serialised
+    per device and both results are right."""
+    import threading
+    xs = [workloads.cast_input((9 << 20) + i, seed=20 + i) for i in range(2)]
+    outs = [None, None]
+
+    def work(i):
+        outs[i] = quant.cast(xs[i], np.float16, device=gpu)
+    ts = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    for x, h in zip(xs, outs):
+        with np.errstate(all="ignore"):
+            assert np.array_equal(h.view(np.uint16), x.astype(np.float16).view(np.uint16))
