@@ -205,6 +205,11 @@ enum {
     NVQ_LINEAR_EXPAND_IN_KERNEL = 1 << 1, /* FP8 codes expanded in shared memory, nothing written to HBM */
     NVQ_LINEAR_SINGLE_CTA = 1 << 2,       /* expansion pass + one CTA per 128 x 256 tile */
     NVQ_LINEAR_CTA_PAIR = 1 << 3,         /* expansion pass + CTA pair per 256 x 256 tile */
+    NVQ_LINEAR_CODES_FINITE = 1 << 5,     /* the caller vouches that no weight code is NaN or inf (true of
+                                             every code nvq_quantize_fp8_rows makes from finite weights):
+                                             the in-kernel expansion leaves its test for such codes out;
+                                             a NaN / inf code would then expand to the finite value its
+                                             bits spell */
     NVQ_LINEAR_CLUSTER_REDUCE = 1 << 4    /* M <= 32, FP8 codes, a weight that one wave of thread-block
                                              clusters covers: the CTAs of a cluster split K and add
                                              their partial sums through distributed shared memory

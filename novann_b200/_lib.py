@@ -20,6 +20,7 @@ DTYPE_SIZE = {F32: 4, F16: 2, BF16: 2, E4M3: 1, E5M2: 1, F64: 8}
 # path selectors of nvq_linear_fwd_opts / nvq_conv2d_fwd_q_opts
 LINEAR_AUTO, LINEAR_BF16_ACTIVATIONS, LINEAR_EXPAND_IN_KERNEL, LINEAR_SINGLE_CTA, LINEAR_CTA_PAIR = 0, 1, 2, 4, 8
 LINEAR_CLUSTER_REDUCE = 16
+LINEAR_CODES_FINITE = 32
 CONV_AUTO, CONV_PATCH_MATRIX, CONV_CTA_PAIR = 0, 1, 2
 PAD_MODES = {"zeros": 0, "reflect": 1, "replicate": 2, "circular": 3}
 

@@ -16,6 +16,7 @@ struct LinearParams {
     int num_items;            // items [num_big, num_items) are half-width tiles
     int group_m;              // rasterisation: m-blocks per group
     int* status;              // mapped host word: first non-zero give-up code
+    int codes_finite;         // fused kernels: the caller vouches that no weight code is NaN / inf
     // implicit-GEMM convolution (stride 1, zero padding): a CTA's 128-row operand tile is a box
     // of conv_bw x conv_bh output positions of one image; M tiles are numbered image-major
     int conv_bw, conv_bh;     // box (conv_bw = OW)
@@ -43,7 +44,8 @@ nvq_status nvq_linear_launch_pair(uint16_t* d_y, const uint16_t* d_x, const uint
 
 nvq_status nvq_linear_launch_pair_fused(uint16_t* d_y, const uint16_t* d_x, const uint8_t* d_wq,
                                         nvq_dtype fmt, const float* d_scales, const float* d_bias,
-                                        size_t M, size_t N, size_t K, int out_f32, int device, cudaStream_t st);
+                                        size_t M, size_t N, size_t K, int out_f32, int device, cudaStream_t st,
+                                        int codes_finite = 0);
 
 nvq_status nvq_linear_launch_pair_w8a8(uint16_t* d_y, const uint8_t* d_xq, const float* d_x_scales,
                                        const uint8_t* d_wq, const float* d_w_scales,
@@ -137,7 +139,10 @@ __device__ __forceinline__ uint32_t non_finite_flags(uint32_t w) {
     return FMT == NVQ_E4M3 ? __vcmpeq4(x, 0xFFFFFFFFu) : __vcmpgeu4(x, 0xFCFCFCFCu);
 }
 
-template <int FMT>
+// CHECK = false: the caller vouches for finite codes and the test (two operations per word, a
+// quarter of the converter warps' time) is left out; a NaN / inf code then expands to the finite
+// value its bits spell.
+template <int FMT, bool CHECK = true>
 __device__ __forceinline__ void expand16(const uint4& in, uint4& lo, uint4& hi) {
     const uint32_t w[4] = {in.x, in.y, in.z, in.w};
     uint32_t o[8];
@@ -146,9 +151,9 @@ __device__ __forceinline__ void expand16(const uint4& in, uint4& lo, uint4& hi) 
         o[2 * i] = expand2<FMT, 0>(w[i]);       // bytes 0, 1
         o[2 * i + 1] = expand2<FMT, 1>(w[i]);   // bytes 2, 3
     }
-    const uint32_t any = non_finite_flags<FMT>(w[0]) | non_finite_flags<FMT>(w[1]) |
-                         non_finite_flags<FMT>(w[2]) | non_finite_flags<FMT>(w[3]);
-    if (__builtin_expect(any != 0, 0)) {
+    const uint32_t any = !CHECK ? 0u : (non_finite_flags<FMT>(w[0]) | non_finite_flags<FMT>(w[1]) |
+                                        non_finite_flags<FMT>(w[2]) | non_finite_flags<FMT>(w[3]));
+    if (CHECK && __builtin_expect(any != 0, 0)) {
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const uint32_t fl = non_finite_flags<FMT>(w[i]) & 0x80808080u;

@@ -303,7 +303,8 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                         if (i < rows_b * 4) {
                             const int r = i >> 2, q = i & 3;
                             uint4 lo, hi;
-                            expand16<FUSED>(in[j], lo, hi);
+                            if (p.codes_finite) expand16<FUSED, false>(in[j], lo, hi);
+                            else expand16<FUSED, true>(in[j], lo, hi);
                             const uint32_t row_base = b_dst + (r >> 3) * 1024 + (r & 7) * 128;
                             const uint32_t c0 = (uint32_t)((2 * q) ^ (r & 7)), c1 = (uint32_t)((2 * q + 1) ^ (r & 7));
                             asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(row_base + c0 * 16),
@@ -449,7 +450,7 @@ template <int FUSED>
 static nvq_status launch_pair(uint16_t* d_y, const void* d_x, const void* d_w,
                               const float* d_scales, const float* d_bias, size_t M, size_t N,
                               size_t K, int out_f32, int device, cudaStream_t st,
-                              const float* row_scales = nullptr) {
+                              const float* row_scales = nullptr, int codes_finite = 0) {
     CUtensorMap map_a, map_b;
     constexpr bool F8 = Cfg<FUSED>::F8;
     // operand tiles: 128-byte rows with the 128-byte swizzle (64 bf16 or 128 FP8 codes)
@@ -472,6 +473,7 @@ static nvq_status launch_pair(uint16_t* d_y, const void* d_x, const void* d_w,
     p.out_f32 = out_f32;
     p.wq = nullptr;
     p.row_scales = row_scales;
+    p.codes_finite = codes_finite;
     p.scales = d_scales;
     p.bias = d_bias;
     p.M = (int)M;
@@ -585,11 +587,14 @@ nvq_status nvq_linear_launch_pair(uint16_t* d_y, const uint16_t* d_x, const uint
 
 nvq_status nvq_linear_launch_pair_fused(uint16_t* d_y, const uint16_t* d_x, const uint8_t* d_wq,
                                         nvq_dtype fmt, const float* d_scales, const float* d_bias,
-                                        size_t M, size_t N, size_t K, int out_f32, int device, cudaStream_t st) {
+                                        size_t M, size_t N, size_t K, int out_f32, int device, cudaStream_t st,
+                                        int codes_finite) {
     NVQ_REQUIRE(K % 16 == 0, "nvq_linear_fwd: K (%zu) must be a multiple of 16 for the fused FP8 path", K);
     if (fmt == NVQ_E4M3)
-        return launch_pair<NVQ_E4M3>(d_y, d_x, d_wq, d_scales, d_bias, M, N, K, out_f32, device, st);
-    return launch_pair<NVQ_E5M2>(d_y, d_x, d_wq, d_scales, d_bias, M, N, K, out_f32, device, st);
+        return launch_pair<NVQ_E4M3>(d_y, d_x, d_wq, d_scales, d_bias, M, N, K, out_f32, device, st, nullptr,
+                                     codes_finite);
+    return launch_pair<NVQ_E5M2>(d_y, d_x, d_wq, d_scales, d_bias, M, N, K, out_f32, device, st, nullptr,
+                                 codes_finite);
 }
 
 // W8A8: X and W both E4M3 codes, per-row and per-channel scales applied in the epilogue

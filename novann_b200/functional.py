@@ -40,17 +40,20 @@ _CONV_PATHS = {None: _lib.CONV_AUTO, "auto": _lib.CONV_AUTO, "patch_matrix": _li
 
 def linear_q_device(y: DeviceBuffer, x: DeviceBuffer, wq: DeviceBuffer, fmt: str,
                     w_scales: DeviceBuffer, bias: DeviceBuffer | None, m: int, n: int, k: int,
-                    workspace: DeviceBuffer | None, stream=None, path: str | None = None) -> None:
+                    workspace: DeviceBuffer | None, stream=None, path: str | None = None,
+                    codes_finite: bool = False) -> None:
     """``workspace=None`` selects the in-kernel expansion of FP8 codes (M > 128, K % 16 == 0).
     ``path`` names a kernel path of ``nvq_linear_fwd_opts``: ``"bf16_activations"`` (M <= 128:
     activations taken as bf16, no two-piece E4M3 carrier), ``"cluster_reduce"`` (M <= 32: the
     clustered stream that adds its partial sums through distributed shared memory), ``"expand_in_kernel"``,
-    ``"single_cta"``, ``"cta_pair"``; ``None`` lets the library choose."""
+    ``"single_cta"``, ``"cta_pair"``; ``None`` lets the library choose.  ``codes_finite``: the
+    caller vouches that no weight code is NaN / inf, which the in-kernel expansion then does not test."""
+    flags = _LINEAR_PATHS[path] | (_lib.LINEAR_CODES_FINITE if codes_finite else 0)
     check(lib().nvq_linear_fwd_opts(y.at(0), x.at(0), wq.at(0), _lib.DTYPE_IDS[fmt], w_scales.at(0),
                                     bias.at(0) if bias is not None else None, m, n, k,
                                     workspace.at(0) if workspace is not None else None,
                                     workspace.nbytes if workspace is not None else 0,
-                                    _LINEAR_PATHS[path], x.device, _sptr(stream)))
+                                    flags, x.device, _sptr(stream)))
 
 
 def linear_q_host(x_bf16_bits: np.ndarray, wq: np.ndarray, w_scales: np.ndarray,
