@@ -1,16 +1,16 @@
 """Locates an importable copy of the reference package (NovaNN) for the drop-in tests.
 
-The reference's checkout exists only where the fixtures were generated; a pip-installed copy
-under ``baseline/_ref`` (git-ignored, made with ``pip install --target baseline/_ref``) travels
-with the working tree.  Whichever is present is put on ``sys.path``; tests skip when neither is.
+A pip-installed copy under ``baseline/_ref`` (git-ignored, made with ``pip install --target
+baseline/_ref``) travels with the working tree; ``NOVANN_REFERENCE`` may name another directory
+that holds the ``novann`` package.  Whichever is present is put on ``sys.path``; tests skip when
+neither is.
 """
 import logging
 import os
 import sys
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-CANDIDATES = [os.path.join(ROOT, "baseline", "_ref"), os.environ.get("NOVANN_REFERENCE", ""),
-              os.path.join(os.sep, "root", "reference")]
+CANDIDATES = [os.path.join(ROOT, "baseline", "_ref"), os.environ.get("NOVANN_REFERENCE", "")]
 
 
 def import_novann():
