@@ -294,6 +294,22 @@ nvq_status nvq_linear_fwd_expanded(uint16_t* d_y_bf16, const uint16_t* d_x_bf16,
                                    const float* d_bias, size_t M, size_t N, size_t K, int relu,
                                    int device, void* stream);
 
+/* The same, with the expanded copy owned by a handle.  nvq_linear_cache_create allocates the
+ * N x K bf16 copy (nvq_linear_workspace_bytes) on `device`; nvq_linear_cache_fwd expands the codes
+ * only when (d_wq, d_w_scales, version) differ from what the copy was made from, then runs the
+ * contraction alone.  The caller bumps `version` whenever it rewrites the codes in place (a
+ * quantised layer does after every optimiser step); *expanded (may be NULL) reports whether this
+ * call ran the expansion pass.  M <= 128 without relu runs the few-rows kernels of nvq_linear_fwd
+ * on the codes (the buffer then holds partial sums and the next larger call expands again).
+ * Calls on one handle must be stream ordered.  With relu == 0 results equal nvq_linear_fwd's bit
+ * for bit. */
+typedef struct nvq_linear_cache nvq_linear_cache;
+nvq_status nvq_linear_cache_create(nvq_linear_cache** out, size_t N, size_t K, nvq_dtype w_fmt, int device);
+nvq_status nvq_linear_cache_fwd(nvq_linear_cache* cache, uint16_t* d_y_bf16, const uint16_t* d_x_bf16,
+                                const uint8_t* d_wq, const float* d_w_scales, const float* d_bias,
+                                size_t M, uint64_t version, int relu, int* expanded, void* stream);
+nvq_status nvq_linear_cache_destroy(nvq_linear_cache* cache);
+
 /* Tensor-core kernels bound every device-side wait; a wait that gives up records a
  * non-zero code here (read and cleared by this call) instead of hanging. */
 nvq_status nvq_device_error_flag(int device, int* flag);

@@ -74,6 +74,9 @@ SIGNATURES = {
     "nvq_linear_fwd_opts": (i32, [vp, vp, vp, i32, vp, vp, sz, sz, sz, vp, sz, C.c_uint32, i32, vp]),
     "nvq_linear_expand_weight": (i32, [vp, vp, i32, vp, sz, sz, i32, vp]),
     "nvq_linear_fwd_expanded": (i32, [vp, vp, vp, vp, vp, sz, sz, sz, i32, i32, vp]),
+    "nvq_linear_cache_create": (i32, [pvp, sz, sz, i32, i32]),
+    "nvq_linear_cache_fwd": (i32, [vp, vp, vp, vp, vp, vp, sz, u64, i32, C.POINTER(i32), vp]),
+    "nvq_linear_cache_destroy": (i32, [vp]),
     "nvq_linear_w8a8_workspace_bytes": (i32, [sz, sz, C.POINTER(sz)]),
     "nvq_linear_fwd_w8a8": (i32, [vp, vp, vp, vp, vp, sz, sz, sz, vp, sz, i32, vp]),
     "nvq_linear_bwd_q_workspace_bytes": (i32, [sz, sz, sz, C.POINTER(sz)]),

@@ -353,7 +353,7 @@ nvq_status nvq_linear_launch_single(uint16_t* d_y, const uint16_t* d_x, const ui
         NVQ_CUDA(cudaFuncSetAttribute(linear_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         attr_set[device] = true;
     }
-    LinearParams p;
+    LinearParams p = {};
     p.y = d_y;
     p.out_f32 = out_f32;
     p.wq = nullptr;
@@ -486,6 +486,73 @@ extern "C" nvq_status nvq_linear_fwd_expanded(uint16_t* d_y_bf16, const uint16_t
     if (s != NVQ_OK) return s;
     return nvq_linear_bf16_launch(d_y_bf16, d_x_bf16, d_wd_bf16, d_chan_scales, d_bias, M, N, K,
                                   relu ? 2 : 0, device, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------- expanded-weight cache
+// A weight that stays fixed over many forwards (inference, or several forwards between two
+// optimiser steps) is expanded once: the cache owns the N x K bf16 copy and remembers which
+// (codes pointer, scales pointer, version) it was made from.
+struct nvq_linear_cache {
+    size_t N, K, bytes;
+    nvq_dtype fmt;
+    int device;
+    void* d_buf;
+    const void* codes;
+    const void* scales;
+    uint64_t version;
+    bool valid;
+};
+
+extern "C" nvq_status nvq_linear_cache_create(nvq_linear_cache** out, size_t N, size_t K,
+                                              nvq_dtype w_fmt, int device) {
+    NVQ_REQUIRE(out && N > 0 && K > 0, "nvq_linear_cache_create: bad argument");
+    *out = nullptr;
+    size_t bytes = 0;
+    nvq_status s = nvq_linear_workspace_bytes(N, K, w_fmt, &bytes);
+    if (s != NVQ_OK) return s;
+    s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    void* buf = nullptr;
+    NVQ_CUDA(cudaMalloc(&buf, bytes));
+    *out = new nvq_linear_cache{N, K, bytes, w_fmt, device, buf, nullptr, nullptr, 0, false};
+    return NVQ_OK;
+}
+
+extern "C" nvq_status nvq_linear_cache_destroy(nvq_linear_cache* c) {
+    if (!c) return NVQ_OK;
+    nvq_status s = nvq_use_device(c->device);
+    if (s == NVQ_OK && c->d_buf) cudaFree(c->d_buf);
+    delete c;
+    return s;
+}
+
+extern "C" nvq_status nvq_linear_cache_fwd(nvq_linear_cache* c, uint16_t* d_y_bf16,
+                                           const uint16_t* d_x_bf16, const uint8_t* d_wq,
+                                           const float* d_w_scales, const float* d_bias, size_t M,
+                                           uint64_t version, int relu, int* expanded, void* stream) {
+    NVQ_REQUIRE(c && d_y_bf16 && d_x_bf16 && d_wq && d_w_scales && M > 0, "nvq_linear_cache_fwd: bad argument");
+    if (expanded) *expanded = 0;
+    const bool fp8 = c->fmt == NVQ_E4M3 || c->fmt == NVQ_E5M2;
+    if (M <= 128 && !relu) {
+        // few rows: the weight-streaming kernels of nvq_linear_fwd read the codes once and keep
+        // partial sums in the buffer, so the expanded copy (if any) is gone afterwards
+        c->valid = false;
+        return nvq_linear_fwd(d_y_bf16, d_x_bf16, d_wq, c->fmt, d_w_scales, d_bias, M, c->N, c->K, c->d_buf,
+                              c->bytes, c->device, stream);
+    }
+    if (!c->valid || c->codes != d_wq || c->scales != d_w_scales || c->version != version) {
+        c->valid = false;
+        nvq_status s = nvq_linear_expand_weight((uint16_t*)c->d_buf, d_wq, c->fmt, d_w_scales, c->N, c->K,
+                                                c->device, stream);
+        if (s != NVQ_OK) return s;
+        c->codes = d_wq;
+        c->scales = d_w_scales;
+        c->version = version;
+        c->valid = true;
+        if (expanded) *expanded = 1;
+    }
+    return nvq_linear_fwd_expanded(d_y_bf16, d_x_bf16, (const uint16_t*)c->d_buf, fp8 ? d_w_scales : nullptr,
+                                   d_bias, M, c->N, c->K, relu, c->device, stream);
 }
 
 extern "C" nvq_status nvq_linear_fwd(uint16_t* d_y_bf16, const uint16_t* d_x_bf16,

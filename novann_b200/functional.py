@@ -382,6 +382,70 @@ def linear_expanded_device(y: DeviceBuffer, x: DeviceBuffer, wd: DeviceBuffer,
                                         x.device, _sptr(stream)))
 
 
+class LinearWeightCache:
+    """Device-resident quantised weight of one Linear with its expanded bf16 copy cached
+    (``nvq_linear_cache_*``).  The codes are expanded on the first forward and again only
+    after ``update`` (which bumps the version the library compares); every other forward runs
+    the contraction alone.  ``forward_device`` works on device buffers, ``forward_host`` on
+    bf16 bit arrays; results equal ``linear_q_device``'s bit for bit."""
+
+    def __init__(self, wq: np.ndarray, w_scales: np.ndarray, bias: np.ndarray | None = None,
+                 fmt: str = "e4m3", device: int = 0) -> None:
+        import ctypes as C
+        self.fmt, self.device = fmt, device
+        self.n = int(wq.shape[0])
+        self.k = int(np.asarray(w_scales).size * 32 // self.n) if fmt == "e2m1_b32" else int(wq.shape[1])
+        self.version = 0
+        self.expansions = 0
+        self._h = C.c_void_p()
+        check(lib().nvq_linear_cache_create(C.byref(self._h), self.n, self.k, _lib.DTYPE_IDS[fmt], device))
+        self.d_codes = DeviceBuffer.from_numpy(np.ascontiguousarray(wq, np.uint8), device)
+        self.d_scales = DeviceBuffer.from_numpy(np.ascontiguousarray(w_scales, np.float32), device)
+        self.d_bias = None if bias is None else DeviceBuffer.from_numpy(
+            np.ascontiguousarray(bias, np.float32).reshape(-1), device)
+
+    def update(self, wq: np.ndarray | None = None, w_scales: np.ndarray | None = None,
+               bias: np.ndarray | None = None) -> None:
+        """New codes / scales / bias written into the same device buffers; the next forward
+        expands again."""
+        if wq is not None:
+            self.d_codes.upload(np.ascontiguousarray(wq, np.uint8))
+        if w_scales is not None:
+            self.d_scales.upload(np.ascontiguousarray(w_scales, np.float32))
+        if bias is not None and self.d_bias is not None:
+            self.d_bias.upload(np.ascontiguousarray(bias, np.float32).reshape(-1))
+        self.version += 1
+
+    def forward_device(self, y: DeviceBuffer, x: DeviceBuffer, m: int, stream=None, relu: bool = False) -> None:
+        import ctypes as C
+        ran = C.c_int(0)
+        check(lib().nvq_linear_cache_fwd(self._h, y.at(0), x.at(0), self.d_codes.at(0), self.d_scales.at(0),
+                                         self.d_bias.at(0) if self.d_bias is not None else None, m,
+                                         self.version, int(relu), C.byref(ran), _sptr(stream)))
+        self.expansions += ran.value
+
+    def forward_host(self, x_bf16_bits: np.ndarray, relu: bool = False) -> np.ndarray:
+        x = np.ascontiguousarray(x_bf16_bits, np.uint16)
+        m = x.shape[0]
+        dx = DeviceBuffer.from_numpy(x, self.device)
+        dy = DeviceBuffer(m * self.n * 2, self.device)
+        self.forward_device(dy, dx, m, relu=relu)
+        device_sync(self.device)
+        check_device_errors(self.device)
+        return dy.to_numpy(np.uint16, (m, self.n))
+
+    def close(self) -> None:
+        if self._h:
+            lib().nvq_linear_cache_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def mul_host(a, b, device: int = 0) -> np.ndarray:
     """Elementwise fp32 product on the GPU (``ReLU.backward``: grad * mask)."""
     a, b = _f32(a, device), _f32(b, device)

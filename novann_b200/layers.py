@@ -162,17 +162,19 @@ class QuantLinear(Linear):
                  fmt: str = "e4m3", device: int = 0, tensor_core_backward: bool = False) -> None:
         self.fmt = fmt
         self.tensor_core_backward = tensor_core_backward
-        self._codes = self._scales = None
+        self._codes = self._scales = self._resident = None
         super().__init__(in_features, out_features, bias, init, device)
 
     def reset_parameters(self, initializer=None) -> None:
         super().reset_parameters(initializer)
         self._codes = self._scales = None      # quantised on the next forward
+        self._resident = None
 
     def requantize(self) -> None:
         """Recompute the weight codes from ``weight.data``."""
         from . import quant
         self._codes, self._scales = quant.quantize_weight(self.weight.data, self.fmt, self.device)
+        self._resident = None                  # the device-resident copy follows the codes
 
     def forward(self, x: np.ndarray) -> np.ndarray:
         from . import quant
@@ -185,7 +187,14 @@ class QuantLinear(Linear):
             self.requantize()
         xb = quant.cast(x, "bf16", device=self.device)
         b = None if self.bias is None else self.bias.data.reshape(-1)
-        yb = F.linear_q_host(xb, self._codes, self._scales, b, self.fmt, self.device)
+        if self._training:
+            yb = F.linear_q_host(xb, self._codes, self._scales, b, self.fmt, self.device)
+        else:
+            # evaluation: codes, scales and bias stay on the device and the expanded weight is
+            # made once per requantize() instead of once per forward
+            if self._resident is None:
+                self._resident = F.LinearWeightCache(self._codes, self._scales, b, self.fmt, self.device)
+            yb = self._resident.forward_host(xb)
         return quant.cast(yb, "f32", src_dtype="bf16", device=self.device)
 
     def backward(self, grad: np.ndarray) -> np.ndarray:

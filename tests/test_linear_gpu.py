@@ -9,7 +9,7 @@ so the tests also assert a much tighter bound (a few bf16 ulps of the largest ou
 import numpy as np
 import pytest
 
-from novann_b200 import _lib, functional as F, workloads
+from novann_b200 import _lib, functional as F, quant, workloads
 from oracle import oracle_np as o
 
 pytestmark = pytest.mark.gpu
@@ -362,3 +362,46 @@ def test_linear_very_few_rows_clustered_kernel(gpu, m, n, k, fmt):
         yb = o.bf16_bits_to_f32(F.linear_q_host(bad, wq, sc, b, fmt, gpu, path="cluster_reduce"))
         assert np.all(np.isnan(yb[1])) and np.array_equal(yb[0], o.bf16_bits_to_f32(y)[0])
     F.check_device_errors(gpu)
+
+
+@pytest.mark.parametrize("fmt", ["e4m3", "e5m2", "e2m1_b32"])
+def test_weight_cache_expands_once_and_equals_the_plain_call(fmt):
+    """nvq_linear_cache_*: the expansion pass runs on the first forward and after update() only,
+    and every result equals nvq_linear_fwd's bit for bit (M above and below the few-rows bound)."""
+    rng = np.random.default_rng(91)
+    n, k = 384, 256
+    w = rng.standard_normal((n, k)).astype(np.float32) * 0.05
+    bias = rng.standard_normal(n).astype(np.float32)
+    wq, ws = quant.quantize_weight(w, fmt)
+    cache = F.LinearWeightCache(wq, ws, bias, fmt)
+    for i, m in enumerate((300, 160, 16, 300)):
+        x = quant.cast(rng.standard_normal((m, k)).astype(np.float32), "bf16")
+        want = F.linear_q_host(x, wq, ws, bias, fmt)
+        got = cache.forward_host(x)
+        np.testing.assert_array_equal(got, want)
+    # 300 and 160 share one expansion; M = 16 streams the codes and drops the copy
+    assert cache.expansions == 2
+    w2 = rng.standard_normal((n, k)).astype(np.float32) * 0.05
+    wq2, ws2 = quant.quantize_weight(w2, fmt)
+    cache.update(wq2, ws2)
+    x = quant.cast(rng.standard_normal((200, k)).astype(np.float32), "bf16")
+    before = cache.expansions
+    np.testing.assert_array_equal(cache.forward_host(x), F.linear_q_host(x, wq2, ws2, bias, fmt))
+    np.testing.assert_array_equal(cache.forward_host(x), F.linear_q_host(x, wq2, ws2, bias, fmt))
+    assert cache.expansions == before + 1
+    cache.close()
+
+
+def test_quant_linear_in_evaluation_mode_keeps_the_weight_on_the_device():
+    from novann_b200 import layers as L
+    rng = np.random.default_rng(92)
+    lin = L.QuantLinear(256, 384)
+    x = rng.standard_normal((200, 256)).astype(np.float32)
+    y_train = lin.forward(x)
+    lin.eval()
+    y1, y2 = lin.forward(x), lin.forward(x)
+    np.testing.assert_array_equal(y1, y_train)
+    np.testing.assert_array_equal(y2, y_train)
+    assert lin._resident is not None and lin._resident.expansions == 1
+    lin.requantize()
+    assert lin._resident is None
