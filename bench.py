@@ -536,9 +536,10 @@ def measure_dp_step(dev, rank, world, dist, local):
     """The one collective of the project: the data-parallel MLP step, batch 128 split over the
     ranks, its flat 235 146-float gradient bucket summed by nvq_allreduce_sum_f32 (NCCL over
     NVLink), 1 / world folded into the SGD kernel.  Times are the max over ranks.
-    dp_step_us: eager steps (10 kernels + the all-reduce), device time per step, 50 steps
-    enqueued back to back; allreduce_us: the all-reduce alone.  The step is not replayed from a
-    CUDA graph here: a graph holding an NCCL collective is left out of the benchmark."""
+    dp_step_us: device time per step, 50 steps enqueued back to back, each step = a CUDA graph of
+    the library's nine forward / loss / backward kernels, then the all-reduce and the SGD kernel
+    launched eagerly (the NCCL collective is never captured); dp_step_eager_us: all eleven launches
+    eager; allreduce_us: the all-reduce alone."""
     import torch
     from novann_b200 import workloads
     from novann_b200.device import DeviceBuffer
@@ -566,6 +567,18 @@ def measure_dp_step(dev, rank, world, dist, local):
     e0.record(step.stream)
     for _ in range(50):
         step.launch()
+    e1.record(step.stream)
+    step.sync()
+    out["dp_step_eager_us"] = max_over_ranks(e0.elapsed_ms(e1) / 50 * 1e3)
+    step.capture()
+    for _ in range(3):
+        step.replay()
+    step.sync()
+    dist.barrier()
+    e0, e1 = T.events()
+    e0.record(step.stream)
+    for _ in range(50):
+        step.replay()
     e1.record(step.stream)
     step.sync()
     out["dp_step_us"] = max_over_ranks(e0.elapsed_ms(e1) / 50 * 1e3)

@@ -115,6 +115,7 @@ class MLPTrainStep:
         self.d_yhat = DeviceBuffer(f4 * self.dims[-1], device)
         self.d_loss = DeviceBuffer(4, device)
         self._graph = None
+        self._graph_is_partial = False
 
     def upload(self, x: np.ndarray, labels: np.ndarray) -> None:
         self.d_x.upload(np.ascontiguousarray(x, np.float32), stream=self.stream)
@@ -122,6 +123,11 @@ class MLPTrainStep:
 
     def launch(self) -> None:
         """Enqueue one step on ``self.stream`` (inputs already uploaded)."""
+        self.launch_compute()
+        self.launch_update()
+
+    def launch_compute(self) -> None:
+        """Forward, loss and backward: the gradients of this rank's rows land in ``d_grads``."""
         L, dev, st, B = lib(), self.device, _sptr(self.stream), self.batch
         for i in range(self.nl):
             last = i == self.nl - 1
@@ -137,6 +143,10 @@ class MLPTrainStep:
                                        self.d_act[i].at(0), self.d_params.at(self.w_off[i]),
                                        self.d_mask[i - 1].at(0) if i > 0 else None,
                                        B, self.dims[i + 1], self.dims[i], dev, st))
+
+    def launch_update(self) -> None:
+        """The gradient all-reduce (data parallel) and the SGD update."""
+        L, dev, st = lib(), self.device, _sptr(self.stream)
         scale = 1.0
         if self.comm is not None and self.comm.world > 1:
             self.comm.allreduce_sum(self.d_grads, self.n_params, stream=self.stream)
@@ -147,12 +157,19 @@ class MLPTrainStep:
     def capture(self) -> None:
         """Record the step's launch sequence into a CUDA graph (after one eager step has run,
         so that first-call set-up is done).  ``replay()`` then issues the whole step as one
-        graph launch; the buffers it reads and writes are the same ones ``upload`` fills."""
+        graph launch; the buffers it reads and writes are the same ones ``upload`` fills.
+        With a communicator of more than one rank the graph holds forward, loss and backward
+        only: the NCCL all-reduce is never captured (it is enqueued after the graph, followed by
+        the SGD kernel), so a step costs three host calls instead of eleven."""
         if self._graph is not None:
             return
+        self._graph_is_partial = self.comm is not None and self.comm.world > 1
         check(lib().nvq_graph_begin_capture(self.device, _sptr(self.stream)))
         try:
-            self.launch()
+            if self._graph_is_partial:
+                self.launch_compute()
+            else:
+                self.launch()
         finally:
             h = C.c_void_p()
             check(lib().nvq_graph_end_capture(self.device, _sptr(self.stream), C.byref(h)))
@@ -161,6 +178,8 @@ class MLPTrainStep:
 
     def replay(self) -> None:
         check(lib().nvq_graph_launch(self.device, C.c_void_p(self._graph), _sptr(self.stream)))
+        if self._graph_is_partial:
+            self.launch_update()
 
     def kernels_per_step(self) -> int:
         """Kernel launches of this library in one step: nl forward, 1 loss, per layer one GEMM for

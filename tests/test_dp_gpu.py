@@ -35,6 +35,17 @@ def _worker(rank, world, tmpdir):
     for a, b in zip(st.params(), cur):
         err = np.max(np.abs(a - b)) / max(1e-30, np.max(np.abs(b)))
         assert err <= 1e-5, (rank, err)
+    # the same step with forward / loss / backward replayed from a CUDA graph and the all-reduce
+    # and the SGD kernel enqueued after it (the collective itself is never captured)
+    st.capture()
+    assert st._graph_is_partial
+    for s in range(2):
+        xs, ys, _ = workloads.mlp_inputs(128, dims, seed=40 + s)
+        st.step(xs[lo:hi], ys[lo:hi])
+        cur = o.mlp_train_step(cur, xs, ys, 0.01)["params"]
+    for a, b in zip(st.params(), cur):
+        err = np.max(np.abs(a - b)) / max(1e-30, np.max(np.abs(b)))
+        assert err <= 2e-5, (rank, err)
     comm.close()
 
 
