@@ -582,6 +582,36 @@ def measure_dp_step(dev, rank, world, dist, local):
     e1.record(step.stream)
     step.sync()
     out["dp_step_us"] = max_over_ranks(e0.elapsed_ms(e1) / 50 * 1e3)
+    # the same step with the all-reduce and the SGD update fused into one kernel over NVLink peer
+    # memory (no NCCL on the data path): graph of the nine compute kernels + that kernel
+    from novann_b200.train import PeerGroup
+
+    def gather(payload):
+        t = torch.zeros(64, dtype=torch.uint8, device=f"cuda:{local}")
+        t[:len(payload)] = torch.tensor(list(payload), dtype=torch.uint8)
+        outs = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(outs, t)
+        return [bytes(o.cpu().tolist())[:len(payload)] for o in outs]
+
+    peer = PeerGroup(rank, world, MLP_PARAMS, dev, allgather=gather, timeout_ms=20000)
+    pstep = MLPTrainStep(params, hi - lo, 0.01, dev, peer=peer)
+    Tp = Timing(dev, pstep.stream)
+    for _ in range(2):
+        pstep.step(x[lo:hi], y[lo:hi])
+    pstep.capture()
+    for _ in range(4):
+        pstep.replay()
+    pstep.sync()
+    dist.barrier()
+    e0, e1 = Tp.events()
+    e0.record(pstep.stream)
+    for _ in range(50):
+        pstep.replay()
+    e1.record(pstep.stream)
+    pstep.sync()
+    out["dp_step_peer_us"] = max_over_ranks(e0.elapsed_ms(e1) / 50 * 1e3)
+    dist.barrier()
+    peer.close()
     # the all-reduce alone, on the gradient bucket
     buf = DeviceBuffer(MLP_PARAMS * 4, dev)
     buf.zero(stream=step.stream)
@@ -813,7 +843,8 @@ def run_ours(args):
                          "linear_fp8_tflops_per_gpu": flat["linear_fp8_tflops_per_gpu"],
                          "linear_fp8_frac_bf16_peak": flat["linear_fp8_frac_bf16_peak"],
                          "linear_fp8_M_per_gpu": flat["linear_fp8_M_per_gpu"],
-                         "dp_step_us": flat.get("dp_step_us"), "allreduce_us": flat.get("allreduce_us")},
+                         "dp_step_us": flat.get("dp_step_us"), "allreduce_us": flat.get("allreduce_us"),
+                         "dp_step_peer_us": flat.get("dp_step_peer_us")},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 12 * n,
                     "d2h_bytes_per_step": 12 * n, "steps": e2e_steps,

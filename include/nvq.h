@@ -527,6 +527,33 @@ nvq_status nvq_comm_wait(void* comm, int device, void* stream, uint32_t timeout_
  * (nvq_comm_destroy waits for them).  The handle is invalid afterwards. */
 nvq_status nvq_comm_abort(void* comm);
 
+/* The same step without NCCL: gradient all-reduce fused with the SGD update over NVLink peer
+ * memory (CUDA IPC, plain peer loads and stores; one process per GPU, at most 8 ranks).
+ *   nvq_peer_create   allocates, on `device`, two gradient buffers of n_floats and a flag array;
+ *   nvq_peer_export   writes this rank's handle (nvq_peer_handle_bytes bytes) for the launcher's
+ *                     side channel; nvq_peer_connect takes the handles of all ranks, in rank order
+ *                     (an all-zero handle marks a rank that is absent: it is never heard from, which
+ *                     is how a test makes the bounded wait run out);
+ *   nvq_peer_grad_buffer  where the backward pass writes this rank's gradients; steps alternate
+ *                     between buffer 0 and buffer 1 (`parity`), starting with 0, on every rank alike;
+ *   nvq_peer_allreduce_sgd  one kernel: announces the step to every rank, waits (at most timeout_ms,
+ *                     default 2000) until every rank has announced it, adds the gradients of all
+ *                     ranks in rank order and applies p -= lr * (sum / world).  A wait that runs out
+ *                     leaves the parameters untouched and records code 61 for nvq_device_error_flag;
+ *                     nothing hangs.  The step number is kept on the device, so the launch can be
+ *                     captured into a CUDA graph (one graph per parity) and replayed.
+ * All ranks must call it the same number of times; destroy only after a host-side rendezvous
+ * (a peer may still be reading this rank's buffers until its own step has completed). */
+typedef struct nvq_peer_group nvq_peer_group;
+nvq_status nvq_peer_handle_bytes(size_t* bytes);
+nvq_status nvq_peer_create(nvq_peer_group** out, int rank, int world, size_t n_floats, uint32_t timeout_ms,
+                           int device);
+nvq_status nvq_peer_export(nvq_peer_group* group, void* handle);
+nvq_status nvq_peer_connect(nvq_peer_group* group, const void* handles);
+nvq_status nvq_peer_grad_buffer(nvq_peer_group* group, int parity, float** d_ptr);
+nvq_status nvq_peer_allreduce_sgd(nvq_peer_group* group, int parity, float* d_params, float lr, void* stream);
+nvq_status nvq_peer_destroy(nvq_peer_group* group);
+
 #ifdef __cplusplus
 }
 #endif

@@ -74,6 +74,13 @@ SIGNATURES = {
     "nvq_linear_fwd_opts": (i32, [vp, vp, vp, i32, vp, vp, sz, sz, sz, vp, sz, C.c_uint32, i32, vp]),
     "nvq_linear_expand_weight": (i32, [vp, vp, i32, vp, sz, sz, i32, vp]),
     "nvq_linear_fwd_expanded": (i32, [vp, vp, vp, vp, vp, sz, sz, sz, i32, i32, vp]),
+    "nvq_peer_handle_bytes": (i32, [C.POINTER(sz)]),
+    "nvq_peer_create": (i32, [pvp, i32, i32, sz, C.c_uint32, i32]),
+    "nvq_peer_export": (i32, [vp, vp]),
+    "nvq_peer_connect": (i32, [vp, vp]),
+    "nvq_peer_grad_buffer": (i32, [vp, i32, pvp]),
+    "nvq_peer_allreduce_sgd": (i32, [vp, i32, vp, f32c, vp]),
+    "nvq_peer_destroy": (i32, [vp]),
     "nvq_linear_cache_create": (i32, [pvp, sz, sz, i32, i32]),
     "nvq_linear_cache_fwd": (i32, [vp, vp, vp, vp, vp, vp, sz, u64, i32, C.POINTER(i32), vp]),
     "nvq_linear_cache_destroy": (i32, [vp]),

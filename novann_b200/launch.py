@@ -55,6 +55,17 @@ def exchange_bytes(payload: bytes | None, rank: int, path: str, timeout_s: float
     return wait_for(full, timeout_s, f"rank {rank}: ")
 
 
+def allgather_bytes(payload: bytes, rank: int, world: int, path: str, timeout_s: float = 60.0,
+                    token: str | None = None) -> list[bytes]:
+    """Every rank publishes ``payload`` at ``path.<token>.<rank>`` and returns the payloads of all
+    ranks in rank order (the side channel for the IPC handles of ``train.PeerGroup``, and a host
+    rendezvous when the payload is empty)."""
+    full = f"{path}.{run_token(token)}"
+    publish(f"{full}.{rank}", payload)
+    return [payload if r == rank else wait_for(f"{full}.{r}", timeout_s, f"rank {rank}: ")
+            for r in range(world)]
+
+
 class PeerLost(RuntimeError):
     """A rank did not announce the step in time, or announced that it left."""
 

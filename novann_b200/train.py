@@ -83,12 +83,94 @@ class Communicator:
             self.handle = None
 
 
+class _DeviceView:
+    """Device memory owned by someone else, with ``DeviceBuffer``'s addressing."""
+
+    def __init__(self, ptr: int, nbytes: int, device: int):
+        self.ptr, self.nbytes, self.device = ptr, nbytes, device
+
+    def at(self, offset: int) -> C.c_void_p:
+        return C.c_void_p(self.ptr + offset)
+
+    def to_numpy(self, dtype, shape) -> np.ndarray:
+        out = np.empty(shape, dtype)
+        check(lib().nvq_memcpy_d2h(out.ctypes.data_as(C.c_void_p), C.c_void_p(self.ptr), out.nbytes,
+                                   self.device, None))
+        check(lib().nvq_device_sync(self.device))
+        return out
+
+
+class PeerGroup:
+    """Gradient all-reduce fused with the SGD update over NVLink peer memory (``nvq_peer_*``):
+    one kernel per step and rank instead of an NCCL all-reduce plus the SGD kernel.
+
+    ``allgather(payload) -> [payload of rank 0, 1, ...]`` is the launcher's side channel for the
+    64-byte IPC handles (``launch.allgather_bytes`` over a shared directory, or a
+    ``torch.distributed`` gather).  ``absent`` lists ranks that are never connected - their
+    announcement never comes, so the step gives up after ``timeout_ms`` with an error flag;
+    tests use it to make the bounded wait run out on one GPU."""
+
+    def __init__(self, rank: int, world: int, n_floats: int, device: int, allgather=None,
+                 timeout_ms: int = 2000, absent=()):
+        self.rank, self.world, self.device, self.n = rank, world, device, int(n_floats)
+        self._allgather = allgather
+        h = C.c_void_p()
+        check(lib().nvq_peer_create(C.byref(h), rank, world, self.n, int(timeout_ms), device))
+        self.handle = h.value
+        hb = C.c_size_t()
+        check(lib().nvq_peer_handle_bytes(C.byref(hb)))
+        mine = (C.c_uint8 * hb.value)()
+        check(lib().nvq_peer_export(C.c_void_p(self.handle), mine))
+        if world > 1:
+            if allgather is not None:
+                blobs = allgather(bytes(mine))
+            else:
+                blobs = [bytes(mine) if r == rank else bytes(hb.value) for r in range(world)]
+            blobs = [bytes(hb.value) if r in absent else b for r, b in enumerate(blobs)]
+            allh = (C.c_uint8 * (hb.value * world)).from_buffer_copy(b"".join(blobs))
+            check(lib().nvq_peer_connect(C.c_void_p(self.handle), allh))
+        self.calls = 0
+        self.grad_views = []
+        for parity in (0, 1):
+            p = C.c_void_p()
+            check(lib().nvq_peer_grad_buffer(C.c_void_p(self.handle), parity, C.byref(p)))
+            self.grad_views.append(_DeviceView(p.value, self.n * 4, device))
+
+    def grads(self) -> _DeviceView:
+        """Where the backward pass of the NEXT step writes this rank's gradients."""
+        return self.grad_views[self.calls & 1]
+
+    def allreduce_sgd(self, d_params: DeviceBuffer, lr: float, stream=None, parity: int | None = None) -> None:
+        """Enqueue the fused all-reduce / update of the next step.  With ``parity`` given the
+        launch is only recorded (CUDA graph capture of the step that reads that buffer) and
+        ``advance()`` is called by whoever replays it."""
+        check(lib().nvq_peer_allreduce_sgd(C.c_void_p(self.handle),
+                                           self.calls & 1 if parity is None else parity,
+                                           d_params.at(0), C.c_float(lr), _sptr(stream)))
+        if parity is None:
+            self.calls += 1
+
+    def advance(self) -> None:
+        self.calls += 1
+
+    def close(self) -> None:
+        """Host rendezvous (a peer may still be reading this rank's buffers until its own last
+        step has completed and it has synchronised), then unmap and free."""
+        if self.handle:
+            if self._allgather is not None and self.world > 1:
+                self._allgather(b"closing")
+            lib().nvq_peer_destroy(C.c_void_p(self.handle))
+            self.handle = None
+
+
 class MLPTrainStep:
     """``step(x, labels)`` runs one training step on the device and returns nothing; read
-    results with ``logits()``, ``loss()``, ``grads()``, ``params()``."""
+    results with ``logits()``, ``loss()``, ``grads()``, ``params()``.  Data parallel: ``comm=``
+    (NCCL all-reduce, then the SGD kernel) or ``peer=`` (``PeerGroup``: all-reduce and update in
+    one kernel over NVLink peer memory)."""
 
     def __init__(self, params, batch: int, lr: float, device: int = 0, comm: Communicator | None = None,
-                 gate=None, collective_timeout_ms: int = 30000):
+                 gate=None, collective_timeout_ms: int = 30000, peer: PeerGroup | None = None):
         self.dims = [params[0].shape[1]] + [params[2 * i].shape[0] for i in range(len(params) // 2)]
         self.nl = len(self.dims) - 1
         self.batch, self.lr, self.device, self.comm = batch, float(lr), device, comm
@@ -99,7 +181,12 @@ class MLPTrainStep:
         flat = flatten_params(params)
         self.n_params = flat.size
         self.d_params = DeviceBuffer.from_numpy(flat, device)
-        self.d_grads = DeviceBuffer(flat.nbytes, device)
+        self.peer = peer
+        if peer is not None and comm is not None:
+            raise ValueError("comm= and peer= are alternatives")
+        if peer is not None and peer.n != flat.size:
+            raise ValueError("the peer group was made for another parameter count")
+        self.d_grads = DeviceBuffer(flat.nbytes, device) if peer is None else peer.grads()
         self.w_off, self.b_off, off = [], [], 0
         for fi, fo in zip(self.dims[:-1], self.dims[1:]):
             self.w_off.append(off * 4)
@@ -116,6 +203,7 @@ class MLPTrainStep:
         self.d_loss = DeviceBuffer(4, device)
         self._graph = None
         self._graph_is_partial = False
+        self._peer_graphs = [None, None]    # forward / loss / backward into gradient buffer 0 / 1
 
     def upload(self, x: np.ndarray, labels: np.ndarray) -> None:
         self.d_x.upload(np.ascontiguousarray(x, np.float32), stream=self.stream)
@@ -126,9 +214,14 @@ class MLPTrainStep:
         self.launch_compute()
         self.launch_update()
 
-    def launch_compute(self) -> None:
-        """Forward, loss and backward: the gradients of this rank's rows land in ``d_grads``."""
+    def launch_compute(self, grads=None) -> None:
+        """Forward, loss and backward: the gradients of this rank's rows land in ``d_grads``
+        (with a peer group: in the buffer the next fused update reads, or in ``grads``)."""
         L, dev, st, B = lib(), self.device, _sptr(self.stream), self.batch
+        if grads is not None:
+            self.d_grads = grads
+        elif self.peer is not None:
+            self.d_grads = self.peer.grads()
         for i in range(self.nl):
             last = i == self.nl - 1
             check(L.nvq_linear_fwd_f32(self.d_act[i + 1].at(0), self.d_act[i].at(0),
@@ -147,6 +240,9 @@ class MLPTrainStep:
     def launch_update(self) -> None:
         """The gradient all-reduce (data parallel) and the SGD update."""
         L, dev, st = lib(), self.device, _sptr(self.stream)
+        if self.peer is not None:
+            self.peer.allreduce_sgd(self.d_params, self.lr, stream=self.stream)
+            return
         scale = 1.0
         if self.comm is not None and self.comm.world > 1:
             self.comm.allreduce_sum(self.d_grads, self.n_params, stream=self.stream)
@@ -163,6 +259,21 @@ class MLPTrainStep:
         the SGD kernel), so a step costs three host calls instead of eleven."""
         if self._graph is not None:
             return
+        if self.peer is not None:
+            # the gradients alternate between the peer group's two buffers: one graph per buffer
+            for parity in (0, 1):
+                check(lib().nvq_graph_begin_capture(self.device, _sptr(self.stream)))
+                try:
+                    self.launch_compute(grads=self.peer.grad_views[parity])
+                    self.peer.allreduce_sgd(self.d_params, self.lr, stream=self.stream, parity=parity)
+                finally:
+                    h = C.c_void_p()
+                    check(lib().nvq_graph_end_capture(self.device, _sptr(self.stream), C.byref(h)))
+                self._peer_graphs[parity] = h.value
+            self._graph = self._peer_graphs[0]
+            self._graph_is_partial = False     # the fused all-reduce / update is the library's own kernel
+            self.launches_per_step = self.kernels_per_step()
+            return
         self._graph_is_partial = self.comm is not None and self.comm.world > 1
         check(lib().nvq_graph_begin_capture(self.device, _sptr(self.stream)))
         try:
@@ -177,7 +288,13 @@ class MLPTrainStep:
         self.launches_per_step = self.kernels_per_step()
 
     def replay(self) -> None:
-        check(lib().nvq_graph_launch(self.device, C.c_void_p(self._graph), _sptr(self.stream)))
+        graph = self._graph
+        if self.peer is not None:
+            graph = self._peer_graphs[self.peer.calls & 1]
+            self.d_grads = self.peer.grads()
+        check(lib().nvq_graph_launch(self.device, C.c_void_p(graph), _sptr(self.stream)))
+        if self.peer is not None:
+            self.peer.advance()
         if self._graph_is_partial:
             self.launch_update()
 
@@ -204,6 +321,10 @@ class MLPTrainStep:
             self.comm.wait(self.stream, self.collective_timeout_ms)
         else:
             self.stream.sync()
+        if self.peer is not None:
+            # a rank that never announced the step: the kernel gave up, the parameters are untouched
+            from .functional import check_device_errors
+            check_device_errors(self.device)
 
     # ---- results
     def logits(self) -> np.ndarray:

@@ -49,6 +49,99 @@ def _worker(rank, world, tmpdir):
     comm.close()
 
 
+def _peer_worker(rank, world, tmpdir):
+    sys.path.insert(0, ROOT)
+    import functools
+    from novann_b200 import workloads
+    from novann_b200.launch import allgather_bytes
+    from novann_b200.train import MLPTrainStep, PeerGroup, shard_rows
+    from oracle import oracle_np as o
+
+    dims = (784, 256, 128, 10)
+    x, y, params = workloads.mlp_inputs(128, dims, seed=0)
+    n = sum(p.size for p in params)
+    counter = [0]
+
+    def gather(payload):
+        counter[0] += 1
+        return allgather_bytes(payload, rank, world, os.path.join(tmpdir, f"peer{counter[0]}"), token="peer")
+
+    peer = PeerGroup(rank, world, n, device=rank, allgather=gather, timeout_ms=20000)
+    lo, hi = shard_rows(128, rank, world)
+    st = MLPTrainStep(params, hi - lo, 0.01, device=rank, peer=peer)
+    cur = params
+    for s in range(3):                       # eager: nine kernels + the fused all-reduce / update
+        xs, ys, _ = workloads.mlp_inputs(128, dims, seed=60 + s)
+        st.step(xs[lo:hi], ys[lo:hi])
+        cur = o.mlp_train_step(cur, xs, ys, 0.01)["params"]
+    st.capture()                             # two graphs, one per gradient buffer
+    for s in range(3):
+        xs, ys, _ = workloads.mlp_inputs(128, dims, seed=70 + s)
+        st.step(xs[lo:hi], ys[lo:hi])
+        cur = o.mlp_train_step(cur, xs, ys, 0.01)["params"]
+    mine = st.params()
+    for a, b in zip(mine, cur):
+        err = np.max(np.abs(a - b)) / max(1e-30, np.max(np.abs(b)))
+        assert err <= 2e-5, (rank, err)
+    # every rank adds the gradients in the same order: the parameters agree bit for bit
+    blob = np.concatenate([p.ravel() for p in mine]).tobytes()
+    everyone = gather(blob)
+    assert all(e == everyone[0] for e in everyone)
+    peer.close()
+
+
+def test_two_rank_peer_memory_step_equals_global_batch_step(gpu, tmp_path):
+    """The data-parallel step with the all-reduce and the SGD update fused into one kernel over
+    NVLink peer memory (no NCCL): equal to the whole-batch step, and bit-identical across ranks."""
+    from novann_b200.device import device_count
+    if device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_peer_worker, args=(2, str(tmp_path)), nprocs=2, join=True)
+
+
+def test_peer_step_on_one_rank_equals_the_plain_step(gpu):
+    """world = 1: the fused kernel is the SGD update (sum of one gradient, 1 / 1)."""
+    from novann_b200 import workloads
+    from novann_b200.train import MLPTrainStep, PeerGroup
+    dims = (784, 256, 128, 10)
+    x, y, params = workloads.mlp_inputs(128, dims, seed=3)
+    n = sum(p.size for p in params)
+    peer = PeerGroup(0, 1, n, device=gpu)
+    a = MLPTrainStep(params, 128, 0.01, device=gpu, peer=peer)
+    b = MLPTrainStep(params, 128, 0.01, device=gpu)
+    for s in range(3):
+        xs, ys, _ = workloads.mlp_inputs(128, dims, seed=80 + s)
+        a.step(xs, ys)
+        b.step(xs, ys)
+    for pa, pb in zip(a.params(), b.params()):
+        np.testing.assert_array_equal(pa, pb)
+    peer.close()
+
+
+def test_peer_step_gives_up_when_a_rank_never_announces(gpu):
+    """A group of two whose second rank is absent: nothing ever sets its flag, the kernel's wait
+    runs out after the time limit, the parameters stay as they were, the error flag reports it and
+    the context stays usable (no fault, no hang)."""
+    from novann_b200 import _lib, workloads
+    from novann_b200.train import MLPTrainStep, PeerGroup
+    dims = (784, 256, 128, 10)
+    x, y, params = workloads.mlp_inputs(128, dims, seed=4)
+    n = sum(p.size for p in params)
+    peer = PeerGroup(0, 2, n, device=gpu, timeout_ms=50, absent=(1,))
+    st = MLPTrainStep(params, 64, 0.01, device=gpu, peer=peer)
+    before = st.params()
+    with pytest.raises(_lib.NvqError):
+        st.step(x[:64], y[:64])
+    for pa, pb in zip(st.params(), before):
+        np.testing.assert_array_equal(pa, pb)
+    # the device still works
+    plain = MLPTrainStep(params, 64, 0.01, device=gpu)
+    plain.step(x[:64], y[:64])
+    assert np.isfinite(plain.loss())
+    peer.close()
+
+
 def test_two_rank_step_equals_global_batch_step(gpu, tmp_path):
     from novann_b200.device import device_count
     if device_count() < 2:
