@@ -156,3 +156,28 @@ def test_step_gate_ignores_what_an_earlier_run_left_in_the_directory(tmp_path):
         exchange_bytes(None, 1, os.path.join(d, "nccl_id"), timeout_s=0.3, token="run2")
     exchange_bytes(b"new" * 8, 0, os.path.join(d, "nccl_id"), token="run2")
     assert exchange_bytes(None, 1, os.path.join(d, "nccl_id"), timeout_s=0.3, token="run2") == b"new" * 8
+
+
+def _allgather_worker(rank, world, tmpdir, q):
+    sys.path.insert(0, ROOT)
+    from novann_b200.launch import allgather_bytes
+    got = allgather_bytes(bytes([rank]) * 64, rank, world, os.path.join(tmpdir, "handles"), token="t1")
+    again = allgather_bytes(b"", rank, world, os.path.join(tmpdir, "rendezvous"), token="t1")
+    q.put((rank, got, again))
+
+
+def test_allgather_bytes_returns_every_ranks_payload_in_rank_order(tmp_path):
+    """The side channel of the peer-memory step (64-byte IPC handles, and an empty payload as a
+    host rendezvous): three processes, every rank gets the same list."""
+    import multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_allgather_worker, args=(r, 3, str(tmp_path), q)) for r in range(3)]
+    for p in ps:
+        p.start()
+    res = sorted(q.get(timeout=60) for _ in range(3))
+    for p in ps:
+        p.join(timeout=30)
+    for rank, got, again in res:
+        assert got == [bytes([r]) * 64 for r in range(3)]
+        assert again == [b"", b"", b""]
