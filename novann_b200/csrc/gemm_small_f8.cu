@@ -123,7 +123,11 @@ split_activations_kernel(uint8_t* __restrict__ x8, float* __restrict__ xscale,
         return;
     }
     const uint4* xr = (const uint4*)(x + (size_t)m * K);
-    const bool in_regs = nvec <= SPLIT_KEEP * 256;
+    // The row is taken in batches of SPLIT_KEEP x 256 vectors whose loads are all in flight
+    // together; the first batch stays in registers between the two passes (rows up to 16384
+    // elements are read once), later batches are read again (from L2) by the second pass.
+    constexpr int BATCH = SPLIT_KEEP * 256;
+    const int n_batches = (nvec + BATCH - 1) / BATCH;
     uint4 keep[SPLIT_KEEP];
     float amax = 0.f;
     int bad = 0;
@@ -136,16 +140,22 @@ split_activations_kernel(uint8_t* __restrict__ x8, float* __restrict__ xscale,
             amax = fmaxf(amax, fmaxf(a, b));
         }
     };
-    if (in_regs) {
+#pragma unroll
+    for (int j = 0; j < SPLIT_KEEP; j++) {
+        const int i = threadIdx.x + 256 * j;
+        keep[j] = i < nvec ? xr[i] : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int j = 0; j < SPLIT_KEEP; j++) look(keep[j]);
+    for (int b = 1; b < n_batches; b++) {
+        uint4 t[SPLIT_KEEP];
 #pragma unroll
         for (int j = 0; j < SPLIT_KEEP; j++) {
-            const int i = threadIdx.x + 256 * j;
-            keep[j] = i < nvec ? xr[i] : make_uint4(0u, 0u, 0u, 0u);
+            const int i = b * BATCH + threadIdx.x + 256 * j;
+            t[j] = i < nvec ? xr[i] : make_uint4(0u, 0u, 0u, 0u);
         }
 #pragma unroll
-        for (int j = 0; j < SPLIT_KEEP; j++) look(keep[j]);
-    } else {
-        for (int i = threadIdx.x; i < nvec; i += blockDim.x) look(xr[i]);
+        for (int j = 0; j < SPLIT_KEEP; j++) look(t[j]);
     }
     if (threadIdx.x == 0) bad_s = 0;
     __syncthreads();
@@ -165,14 +175,23 @@ split_activations_kernel(uint8_t* __restrict__ x8, float* __restrict__ xscale,
     const float a = __uint_as_float((uint32_t)(e - 7 + 127) << 23);
     const float inv = __uint_as_float((uint32_t)(7 - e + 127) << 23);
     if (threadIdx.x == 0) xscale[m] = non_finite ? __uint_as_float(0x7FC00000u) : a;
-    if (in_regs) {
+#pragma unroll
+    for (int j = 0; j < SPLIT_KEEP; j++) {
+        const int i = threadIdx.x + 256 * j;
+        if (i < nvec) split8(keep[j], inv, non_finite, row1[i], row2[i]);
+    }
+    for (int b = 1; b < n_batches; b++) {
+        uint4 t[SPLIT_KEEP];
 #pragma unroll
         for (int j = 0; j < SPLIT_KEEP; j++) {
-            const int i = threadIdx.x + 256 * j;
-            if (i < nvec) split8(keep[j], inv, non_finite, row1[i], row2[i]);
+            const int i = b * BATCH + threadIdx.x + 256 * j;
+            t[j] = i < nvec ? xr[i] : make_uint4(0u, 0u, 0u, 0u);
         }
-    } else {
-        for (int i = threadIdx.x; i < nvec; i += blockDim.x) split8(xr[i], inv, non_finite, row1[i], row2[i]);
+#pragma unroll
+        for (int j = 0; j < SPLIT_KEEP; j++) {
+            const int i = b * BATCH + threadIdx.x + 256 * j;
+            if (i < nvec) split8(t[j], inv, non_finite, row1[i], row2[i]);
+        }
     }
 }
 

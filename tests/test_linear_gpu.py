@@ -233,6 +233,7 @@ def test_linear_split_last_wave_and_deep_k(gpu, m, n, k):
     (1, 128, 64), (3, 8, 16), (16, 4096, 4096), (17, 1000, 336), (64, 264, 8192), (100, 2048, 48),
     (128, 4096, 1024), (128, 136, 4160), (31, 20000, 64),
     (4, 256, 16400),      # rows longer than the activation-splitting kernel keeps in registers
+    (16, 256, 28672), (2, 128, 33808),    # two and three load batches per row
 ])
 @pytest.mark.parametrize("few_rows_mode", ["direct", "cluster_reduce", "convert"])
 def test_linear_few_rows_weight_streaming_kernel(gpu, fmt, m, n, k, few_rows_mode):
