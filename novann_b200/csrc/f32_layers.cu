@@ -43,33 +43,6 @@ struct GemmArgs {
     float* rowsum;
 };
 
-// Programmatic dependent launch for the latency-bound fp32 steps: a kernel launched with
-// launch_chained may be scheduled while the previous kernel of the stream is still running; its
-// first statement, chain_sync(), lets the NEXT kernel be scheduled in the same way and then waits
-// until the previous one has completed and its writes are visible.  Every thread executes it
-// before anything else (a block that returned without waiting would let the grid complete, and
-// its successor start, before the predecessor's writes have landed).  Launched without the
-// attribute, or after a kernel that is not part of such a chain, the two instructions do nothing.
-__device__ __forceinline__ void chain_sync() {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-}
-template <typename... KArgs, typename... Args>
-static void launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
-                           Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);   // the error, if any, is read by NVQ_LAUNCHED
-}
-
 constexpr int kSplitChunk = 64;   // split-k ranges are multiples of the deepest chunk
 
 // element e of a T x TK tile -> (row-in-tile, k-in-chunk); the index that has unit stride in
@@ -87,7 +60,7 @@ __device__ __forceinline__ void tile_coord(int e, bool k_contiguous, int& r, int
 // has k = 9; a 64-deep chunk would multiply 55 rows of zeros).
 template <int T, int TK = 64>
 __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
-    chain_sync();
+    nvq_chain_sync();
     constexpr int R = T / 16;                 // outputs per thread per dimension
     constexpr int LD = T * TK / 256;          // tile elements each thread stages per chunk
     // double-buffered tiles: chunk c+1 is fetched into registers while chunk c is multiplied
@@ -197,7 +170,7 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
 #endif
 template <int RI, int RJ>
 __global__ void __launch_bounds__(256) gemm_f32_big_kernel(const GemmArgs g) {
-    chain_sync();
+    nvq_chain_sync();
     constexpr int TI = 16 * RI, TJ = 16 * RJ, TKB = NVQ_GEMM_BIG_TK;
     constexpr int LDA = TI * TKB / 256, LDB = TJ * TKB / 256;
     __shared__ __align__(16) float As[2][TKB][TI + 4];
@@ -331,7 +304,7 @@ __global__ void __launch_bounds__(256) gemm_f32_big_kernel(const GemmArgs g) {
 // order and the 32 lane sums are combined by a fixed butterfly (same result on every run)
 __global__ void splitk_reduce_kernel(float* __restrict__ c, const float* __restrict__ partial,
                                      int n, int splits) {
-    chain_sync();
+    nvq_chain_sync();
     const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (e >= n) return;
     float s = 0.f;
@@ -356,10 +329,10 @@ nvq_status launch_gemm_splitk(GemmArgs g, float* scratch, size_t scratch_elems, 
     const dim3 tiles2((g.J + tj - 1) / tj, (g.I + ti - 1) / ti);
     auto launch = [&](unsigned z) {
         const dim3 grid(tiles2.x, tiles2.y, z);
-        if (kind == 44) launch_chained(gemm_f32_big_kernel<4, 4>, grid, 256, 0, st, g);
-        else if (kind == 28) launch_chained(gemm_f32_big_kernel<2, 8>, grid, 256, 0, st, g);
-        else if (kind == 18) launch_chained(gemm_f32_big_kernel<1, 8>, grid, 256, 0, st, g);
-        else launch_chained(gemm_f32_kernel<16>, grid, 256, 0, st, g);
+        if (kind == 44) nvq_launch_chained(gemm_f32_big_kernel<4, 4>, grid, 256, 0, st, g);
+        else if (kind == 28) nvq_launch_chained(gemm_f32_big_kernel<2, 8>, grid, 256, 0, st, g);
+        else if (kind == 18) nvq_launch_chained(gemm_f32_big_kernel<1, 8>, grid, 256, 0, st, g);
+        else nvq_launch_chained(gemm_f32_kernel<16>, grid, 256, 0, st, g);
     };
     const long long tiles = (long long)tiles2.x * tiles2.y;
     const long long out = (long long)g.I * g.J;
@@ -379,7 +352,7 @@ nvq_status launch_gemm_splitk(GemmArgs g, float* scratch, size_t scratch_elems, 
     g.partial = scratch;
     launch((unsigned)g.splits);
     NVQ_LAUNCHED();
-    launch_chained(splitk_reduce_kernel, dim3((unsigned)((out + 7) / 8)), 256, 0, st, g.c, (const float*)scratch, (int)out, g.splits);
+    nvq_launch_chained(splitk_reduce_kernel, dim3((unsigned)((out + 7) / 8)), 256, 0, st, g.c, (const float*)scratch, (int)out, g.splits);
     NVQ_LAUNCHED();
     return NVQ_OK;
 }
@@ -393,17 +366,17 @@ nvq_status launch_gemm(const GemmArgs& g, cudaStream_t st) {
         const long long b28 = (long long)((g.J + 127) / 128) * ((g.I + 31) / 32);
         const long long b18 = (long long)((g.J + 127) / 128) * ((g.I + 15) / 16);
         if (g.I > 32 && b44 >= 64) {
-            launch_chained(gemm_f32_big_kernel<4, 4>, dim3((g.J + 63) / 64, (g.I + 63) / 64), 256, 0, st, g);
+            nvq_launch_chained(gemm_f32_big_kernel<4, 4>, dim3((g.J + 63) / 64, (g.I + 63) / 64), 256, 0, st, g);
             NVQ_LAUNCHED();
             return NVQ_OK;
         }
         if (g.I > 16 && g.I <= 32 && b28 >= 64) {
-            launch_chained(gemm_f32_big_kernel<2, 8>, dim3((g.J + 127) / 128, (g.I + 31) / 32), 256, 0, st, g);
+            nvq_launch_chained(gemm_f32_big_kernel<2, 8>, dim3((g.J + 127) / 128, (g.I + 31) / 32), 256, 0, st, g);
             NVQ_LAUNCHED();
             return NVQ_OK;
         }
         if (g.I <= 16 && b18 >= 64) {
-            launch_chained(gemm_f32_big_kernel<1, 8>, dim3((g.J + 127) / 128, (g.I + 15) / 16), 256, 0, st, g);
+            nvq_launch_chained(gemm_f32_big_kernel<1, 8>, dim3((g.J + 127) / 128, (g.I + 15) / 16), 256, 0, st, g);
             NVQ_LAUNCHED();
             return NVQ_OK;
         }
@@ -413,17 +386,17 @@ nvq_status launch_gemm(const GemmArgs& g, cudaStream_t st) {
         // shallow contraction: 16-deep chunks; 16-row tiles when the output has few rows
         if (g.I <= 16) {
             dim3 grid((g.J + 15) / 16, (g.I + 15) / 16);
-            launch_chained(gemm_f32_kernel<16, 16>, grid, 256, 0, st, g);
+            nvq_launch_chained(gemm_f32_kernel<16, 16>, grid, 256, 0, st, g);
         } else {
             dim3 grid((g.J + 31) / 32, (g.I + 31) / 32);
-            launch_chained(gemm_f32_kernel<32, 16>, grid, 256, 0, st, g);
+            nvq_launch_chained(gemm_f32_kernel<32, 16>, grid, 256, 0, st, g);
         }
     } else if (big_blocks >= 148) {
         dim3 grid((g.J + 31) / 32, (g.I + 31) / 32);
-        launch_chained(gemm_f32_kernel<32>, grid, 256, 0, st, g);
+        nvq_launch_chained(gemm_f32_kernel<32>, grid, 256, 0, st, g);
     } else {
         dim3 grid((g.J + 15) / 16, (g.I + 15) / 16);
-        launch_chained(gemm_f32_kernel<16>, grid, 256, 0, st, g);
+        nvq_launch_chained(gemm_f32_kernel<16>, grid, 256, 0, st, g);
     }
     NVQ_LAUNCHED();
     return NVQ_OK;
@@ -433,7 +406,7 @@ nvq_status launch_gemm(const GemmArgs& g, cudaStream_t st) {
 // row groups; each thread adds its rows in order, the 8 partial sums are combined in order.
 __global__ void __launch_bounds__(256)
 colsum_kernel(const float* __restrict__ g, float* __restrict__ out, int M, int N) {
-    chain_sync();
+    nvq_chain_sync();
     __shared__ float part[8][33];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const int n = blockIdx.x * 32 + tx;
@@ -452,7 +425,7 @@ colsum_kernel(const float* __restrict__ g, float* __restrict__ out, int M, int N
 
 __global__ void relu_kernel(float* __restrict__ out, float* __restrict__ mask,
                             const float* __restrict__ x, size_t n) {
-    chain_sync();
+    nvq_chain_sync();
     size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         float v = x[i];
@@ -464,7 +437,7 @@ __global__ void relu_kernel(float* __restrict__ out, float* __restrict__ mask,
 
 __global__ void mul_kernel(float* __restrict__ out, const float* __restrict__ a,
                            const float* __restrict__ b, size_t n) {
-    chain_sync();
+    nvq_chain_sync();
     size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
         out[i] = __fmul_rn(a[i], b[i]);
@@ -477,7 +450,7 @@ __global__ void mul_kernel(float* __restrict__ out, const float* __restrict__ a,
 __global__ void softmax_ce_kernel(float* __restrict__ grad, float* __restrict__ loss,
                                   const float* __restrict__ logits, const int* __restrict__ labels,
                                   float* __restrict__ yhat_scratch, int M, int C) {
-    chain_sync();
+    nvq_chain_sync();
     extern __shared__ double red[];
     for (int m = threadIdx.x; m < M; m += blockDim.x) {
         const float* z = logits + (size_t)m * C;
@@ -529,7 +502,7 @@ __global__ void softmax_ce_kernel(float* __restrict__ grad, float* __restrict__ 
 
 __global__ void sgd_kernel(float* __restrict__ p, const float* __restrict__ g, size_t n, float lr,
                            float grad_scale) {
-    chain_sync();
+    nvq_chain_sync();
     size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         float gr = g[i];
@@ -922,7 +895,7 @@ extern "C" nvq_status nvq_linear_bwd_f32(float* d_dw, float* d_db, float* d_dx, 
         s = launch_gemm(g, st);
         if (s != NVQ_OK) return s;
     } else if (d_db) {
-        launch_chained(colsum_kernel, dim3((N + 31) / 32), 256, 0, st, d_g, d_db, M, N);
+        nvq_launch_chained(colsum_kernel, dim3((N + 31) / 32), 256, 0, st, d_g, d_db, M, N);
         NVQ_LAUNCHED();
     }
     if (d_dx) {   // dX[m,k] = sum_n G[m,n] W[n,k]
@@ -944,7 +917,7 @@ extern "C" nvq_status nvq_relu_fwd_f32(float* d_out, float* d_mask, const float*
     NVQ_REQUIRE(d_out && d_x, "nvq_relu_fwd_f32: null buffer");
     nvq_status s = nvq_use_device(device);
     if (s != NVQ_OK) return s;
-    launch_chained(relu_kernel, dim3(ew_grid(n, device)), 256, 0, (cudaStream_t)stream, d_out, d_mask, d_x, n);
+    nvq_launch_chained(relu_kernel, dim3(ew_grid(n, device)), 256, 0, (cudaStream_t)stream, d_out, d_mask, d_x, n);
     NVQ_LAUNCHED();
     return NVQ_OK;
 }
@@ -955,7 +928,7 @@ extern "C" nvq_status nvq_mul_f32(float* d_out, const float* d_a, const float* d
     NVQ_REQUIRE(d_out && d_a && d_b, "nvq_mul_f32: null buffer");
     nvq_status s = nvq_use_device(device);
     if (s != NVQ_OK) return s;
-    launch_chained(mul_kernel, dim3(ew_grid(n, device)), 256, 0, (cudaStream_t)stream, d_out, d_a, d_b, n);
+    nvq_launch_chained(mul_kernel, dim3(ew_grid(n, device)), 256, 0, (cudaStream_t)stream, d_out, d_a, d_b, n);
     NVQ_LAUNCHED();
     return NVQ_OK;
 }
@@ -967,7 +940,7 @@ extern "C" nvq_status nvq_softmax_ce_f32(float* d_grad, float* d_loss, const flo
                 "nvq_softmax_ce_f32: bad argument");
     nvq_status s = nvq_use_device(device);
     if (s != NVQ_OK) return s;
-    launch_chained(softmax_ce_kernel, dim3(1), 256, 256 * sizeof(double), (cudaStream_t)stream, d_grad, d_loss,
+    nvq_launch_chained(softmax_ce_kernel, dim3(1), 256, 256 * sizeof(double), (cudaStream_t)stream, d_grad, d_loss,
                    d_logits, (const int*)d_labels, d_yhat, M, C);
     NVQ_LAUNCHED();
     return NVQ_OK;
@@ -979,7 +952,7 @@ extern "C" nvq_status nvq_sgd_step_f32(float* d_param, const float* d_grad, size
     NVQ_REQUIRE(d_param && d_grad, "nvq_sgd_step_f32: null buffer");
     nvq_status s = nvq_use_device(device);
     if (s != NVQ_OK) return s;
-    launch_chained(sgd_kernel, dim3(ew_grid(n, device)), 256, 0, (cudaStream_t)stream, d_param, d_grad, n, lr, grad_scale);
+    nvq_launch_chained(sgd_kernel, dim3(ew_grid(n, device)), 256, 0, (cudaStream_t)stream, d_param, d_grad, n, lr, grad_scale);
     NVQ_LAUNCHED();
     return NVQ_OK;
 }
