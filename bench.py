@@ -593,25 +593,50 @@ def measure_dp_step(dev, rank, world, dist, local):
         dist.all_gather(outs, t)
         return [bytes(o.cpu().tolist())[:len(payload)] for o in outs]
 
-    peer = PeerGroup(rank, world, MLP_PARAMS, dev, allgather=gather, timeout_ms=20000)
-    pstep = MLPTrainStep(params, hi - lo, 0.01, dev, peer=peer)
-    Tp = Timing(dev, pstep.stream)
-    for _ in range(2):
-        pstep.step(x[lo:hi], y[lo:hi])
-    pstep.capture()
-    for _ in range(4):
-        pstep.replay()
-    pstep.sync()
+    def all_ranks_ok(flag):
+        t = torch.tensor([1.0 if flag else 0.0], device=f"cuda:{local}", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return t.item() > 0
+
+    # Every stage ends with an agreement over all ranks, so that a rank on which CUDA IPC or a
+    # step failed never leaves the others inside a collective: the figure is then reported as null.
+    peer, why = None, None
+    try:
+        peer = PeerGroup(rank, world, MLP_PARAMS, dev, allgather=gather, timeout_ms=20000)
+    except Exception as e:      # noqa: BLE001 - reported in the line
+        why = f"peer group: {e}"
+    if not all_ranks_ok(peer is not None):
+        out["dp_step_peer_us"] = None
+        out["dp_step_peer_skipped"] = (why or "another rank could not map peer memory")[:120]
+    else:
+        t_step = None
+        try:
+            pstep = MLPTrainStep(params, hi - lo, 0.01, dev, peer=peer)
+            Tp = Timing(dev, pstep.stream)
+            for _ in range(2):
+                pstep.step(x[lo:hi], y[lo:hi])
+            pstep.capture()
+            for _ in range(4):
+                pstep.replay()
+            pstep.sync()
+            e0, e1 = Tp.events()
+            e0.record(pstep.stream)
+            for _ in range(50):
+                pstep.replay()
+            e1.record(pstep.stream)
+            pstep.sync()
+            t_step = e0.elapsed_ms(e1) / 50 * 1e3
+        except Exception as e:      # noqa: BLE001
+            why = f"peer step: {e}"
+        if all_ranks_ok(t_step is not None):
+            out["dp_step_peer_us"] = max_over_ranks(t_step)
+        else:
+            out["dp_step_peer_us"] = None
+            out["dp_step_peer_skipped"] = (why or "the step failed on another rank")[:120]
     dist.barrier()
-    e0, e1 = Tp.events()
-    e0.record(pstep.stream)
-    for _ in range(50):
-        pstep.replay()
-    e1.record(pstep.stream)
-    pstep.sync()
-    out["dp_step_peer_us"] = max_over_ranks(e0.elapsed_ms(e1) / 50 * 1e3)
-    dist.barrier()
-    peer.close()
+    if peer is not None:
+        peer._allgather = None       # the barrier above was the rendezvous
+        peer.close()
     # the all-reduce alone, on the gradient bucket
     buf = DeviceBuffer(MLP_PARAMS * 4, dev)
     buf.zero(stream=step.stream)
