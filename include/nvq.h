@@ -85,6 +85,9 @@ nvq_status nvq_device_sync(int device);
 nvq_status nvq_event_create(int device, void** event);
 nvq_status nvq_event_destroy(int device, void* event);
 nvq_status nvq_event_record(int device, void* event, void* stream);
+/* work enqueued on `stream` after this call waits for what `event` recorded (also inside a stream
+ * capture, where it forks / joins branches of the graph) */
+nvq_status nvq_stream_wait_event(int device, void* stream, void* event);
 nvq_status nvq_event_sync(int device, void* event);
 nvq_status nvq_event_elapsed_ms(void* start, void* stop, float* ms);
 

@@ -53,6 +53,7 @@ SIGNATURES = {
     "nvq_event_create": (i32, [i32, pvp]),
     "nvq_event_destroy": (i32, [i32, vp]),
     "nvq_event_record": (i32, [i32, vp, vp]),
+    "nvq_stream_wait_event": (i32, [i32, vp, vp]),
     "nvq_event_sync": (i32, [i32, vp]),
     "nvq_event_elapsed_ms": (i32, [vp, vp, C.POINTER(f32c)]),
     "nvq_graph_begin_capture": (i32, [i32, vp]),

@@ -174,6 +174,11 @@ nvq_status nvq_event_record(int device, void* event, void* stream) {
     NVQ_CUDA(cudaEventRecord((cudaEvent_t)event, (cudaStream_t)stream));
     return NVQ_OK;
 }
+nvq_status nvq_stream_wait_event(int device, void* stream, void* event) {
+    NVQ_CUDA(cudaSetDevice(device));
+    NVQ_CUDA(cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)event, 0));
+    return NVQ_OK;
+}
 nvq_status nvq_event_sync(int device, void* event) {
     NVQ_CUDA(cudaSetDevice(device));
     NVQ_CUDA(cudaEventSynchronize((cudaEvent_t)event));

@@ -53,6 +53,10 @@ class Event:
     def sync(self) -> None:
         check(lib().nvq_event_sync(self.device, self.ptr))
 
+    def block(self, stream) -> None:
+        """Work enqueued on ``stream`` from now on waits for what this event recorded."""
+        check(lib().nvq_stream_wait_event(self.device, _sptr(stream), self.ptr))
+
     def elapsed_ms(self, later: "Event") -> float:
         ms = C.c_float()
         check(lib().nvq_event_elapsed_ms(self.ptr, later.ptr, C.byref(ms)))

@@ -17,7 +17,7 @@ import ctypes as C
 import numpy as np
 
 from ._lib import check, lib
-from .device import DeviceBuffer, Stream, _sptr
+from .device import DeviceBuffer, Event, Stream, _sptr
 
 
 def shard_rows(n_rows: int, rank: int, world: int) -> tuple[int, int]:
@@ -178,6 +178,7 @@ class MLPTrainStep:
         self.collective_timeout_ms = collective_timeout_ms
         self._step_no = 0
         self.stream = Stream(device)
+        self.side = Stream(device)          # weight-gradient GEMMs, beside the dX chain
         flat = flatten_params(params)
         self.n_params = flat.size
         self.d_params = DeviceBuffer.from_numpy(flat, device)
@@ -201,6 +202,8 @@ class MLPTrainStep:
         self.d_g = [DeviceBuffer(f4 * d, device) for d in self.dims]     # gradient w.r.t. each activation
         self.d_yhat = DeviceBuffer(f4 * self.dims[-1], device)
         self.d_loss = DeviceBuffer(4, device)
+        self.ev_fork = [Event(device) for _ in range(self.nl)]
+        self.ev_join = Event(device)
         self._graph = None
         self._graph_is_partial = False
         self._peer_graphs = [None, None]    # forward / loss / backward into gradient buffer 0 / 1
@@ -230,12 +233,22 @@ class MLPTrainStep:
                                        None if last else self.d_mask[i].at(0), dev, st))
         check(L.nvq_softmax_ce_f32(self.d_g[self.nl].at(0), self.d_loss.at(0), self.d_act[self.nl].at(0),
                                    self.d_labels.at(0), self.d_yhat.at(0), B, self.dims[-1], dev, st))
+        # Backward: the chain loss -> dX(nl-1) -> ... -> dX(1) runs on the step's stream; every
+        # weight gradient (with its bias gradient) depends on one link of that chain only and runs
+        # on a side stream, joined before the update - in a CUDA graph these are parallel branches.
+        side = _sptr(self.side)
         for i in reversed(range(self.nl)):
+            self.ev_fork[i].record(self.stream)          # d_g[i + 1] is complete
+            self.ev_fork[i].block(self.side)
             check(L.nvq_linear_bwd_f32(self.d_grads.at(self.w_off[i]), self.d_grads.at(self.b_off[i]),
-                                       self.d_g[i].at(0) if i > 0 else None, self.d_g[i + 1].at(0),
-                                       self.d_act[i].at(0), self.d_params.at(self.w_off[i]),
-                                       self.d_mask[i - 1].at(0) if i > 0 else None,
-                                       B, self.dims[i + 1], self.dims[i], dev, st))
+                                       None, self.d_g[i + 1].at(0), self.d_act[i].at(0), None, None,
+                                       B, self.dims[i + 1], self.dims[i], dev, side))
+            if i > 0:
+                check(L.nvq_linear_bwd_f32(None, None, self.d_g[i].at(0), self.d_g[i + 1].at(0),
+                                           None, self.d_params.at(self.w_off[i]), self.d_mask[i - 1].at(0),
+                                           B, self.dims[i + 1], self.dims[i], dev, st))
+        self.ev_join.record(self.side)
+        self.ev_join.block(self.stream)
 
     def launch_update(self) -> None:
         """The gradient all-reduce (data parallel) and the SGD update."""
