@@ -84,7 +84,6 @@ __global__ void __launch_bounds__(256) peer_allreduce_sgd_kernel(const PeerArgs 
     // every block leaves through here: the last one publishes the step number for the next launch
     auto leave = [&]() {
         if (threadIdx.x == 0) {
-            __threadfence();
             if (atomicAdd(a.arrived, 1u) == gridDim.x - 1) {
                 *a.arrived = 0;
                 *(volatile unsigned long long*)a.step_ctr = step;
@@ -100,7 +99,7 @@ __global__ void __launch_bounds__(256) peer_allreduce_sgd_kernel(const PeerArgs 
                 atomicExch(&s_abort, 1);
                 break;
             }
-            __nanosleep(200);
+            __nanosleep(100);
         }
     }
     __syncthreads();
