@@ -406,3 +406,25 @@ def test_quant_linear_in_evaluation_mode_keeps_the_weight_on_the_device():
     assert lin._resident is not None and lin._resident.expansions == 1
     lin.requantize()
     assert lin._resident is None
+
+
+def test_weight_cache_with_fused_relu():
+    """relu=True applies the reference's F.relu (v * (v > 0)) before the bf16 rounding: the same
+    values as the plain call followed by ReLU, for M above and below the few-rows bound."""
+    rng = np.random.default_rng(93)
+    n, k = 256, 192
+    w = rng.standard_normal((n, k)).astype(np.float32) * 0.05
+    bias = rng.standard_normal(n).astype(np.float32) * 0.1
+    wq, ws = quant.quantize_weight(w, "e4m3")
+    cache = F.LinearWeightCache(wq, ws, bias, "e4m3")
+    for m in (200, 24):
+        x = quant.cast(rng.standard_normal((m, k)).astype(np.float32), "bf16")
+        plain = o.bf16_bits_to_f32(cache.forward_host(x) if m > 128 else F.linear_q_host(x, wq, ws, bias, "e4m3",
+                                                                                         path="bf16_activations"))
+        got = o.bf16_bits_to_f32(cache.forward_host(x, relu=True))
+        want = plain * (plain > 0)
+        if m > 128:
+            np.testing.assert_array_equal(got, want)
+        else:   # few rows with ReLU take the expanded weight; the plain few-rows kernel sums in another order
+            assert np.max(np.abs(got - want)) <= 2.0 ** -7 * np.max(np.abs(want))
+    cache.close()
