@@ -352,6 +352,11 @@ nvq_status nvq_mul_f32(float* d_out, const float* d_a, const float* d_b, size_t 
 nvq_status nvq_softmax_ce_f32(float* d_grad, float* d_loss, const float* d_logits,
                               const int32_t* d_labels, float* d_yhat, int M, int C, int device,
                               void* stream);
+/* The loss value alone, from the y_hat that nvq_softmax_ce_f32 left in d_yhat (call that one with
+ * d_loss = NULL): nothing in a training step depends on the number, so a step can run this beside
+ * its backward pass.  Same arithmetic, same bits as the one-call form. */
+nvq_status nvq_ce_loss_f32(float* d_loss, const float* d_yhat, const int32_t* d_labels, int M, int C,
+                           int device, void* stream);
 /* SGD.step, vanilla path (novann/optim/sgd.py:58-82): p = p - lr * (g * grad_scale), each
  * product and the subtraction rounded separately (grad_scale == 1 skips its multiply). */
 nvq_status nvq_sgd_step_f32(float* d_param, const float* d_grad, size_t n, float lr,

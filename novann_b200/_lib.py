@@ -96,6 +96,7 @@ SIGNATURES = {
     "nvq_relu_fwd_f32": (i32, [vp, vp, vp, sz, i32, vp]),
     "nvq_mul_f32": (i32, [vp, vp, vp, sz, i32, vp]),
     "nvq_softmax_ce_f32": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, vp]),
+    "nvq_ce_loss_f32": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "nvq_sgd_step_f32": (i32, [vp, vp, sz, f32c, f32c, i32, vp]),
     "nvq_adamw_step_f32": (i32, [vp, vp, vp, vp, sz] + [f32c] * 9 + [i32, i32, vp]),
     "nvq_conv2d_out_size": (i32, [i32] * 8 + [C.POINTER(i32), C.POINTER(i32)]),

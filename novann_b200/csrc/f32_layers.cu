@@ -234,6 +234,75 @@ __global__ void __launch_bounds__(256 * kSliceGroups) gemm_f32_ksplit_kernel(con
     g.c[idx] = val;
 }
 
+// Linear forward with both operands contiguous along k (X (M, K), W (N, K)) and an output too small
+// to fill the GPU with shared-memory tiles: no shared memory at all.  A warp owns a 4 x 4 block of
+// outputs; its lanes split k (lane t takes elements 4 t .. 4 t + 3 of every 128), so the four rows
+// of X and the four rows of W are read as fully coalesced 128-bit loads (rows shared with the
+// block's other warps come from L1), 64 multiply-adds per eight loads, and the 16 sums are
+// combined over the lanes by a fixed butterfly at the end (the same bits on every run; another
+// order than the tile kernels, within their 1e-5 of the reference's sgemm).
+__global__ void __launch_bounds__(256) linear_fwd_klanes_kernel(const GemmArgs g) {
+    nvq_chain_sync();
+    const int lane = threadIdx.x & 31;
+    const int wj_count = (g.J + 3) / 4;
+    const int w = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int i0 = (w / wj_count) * 4, j0 = (w % wj_count) * 4;
+    if (i0 >= g.I) return;
+    float acc[4][4];
+#pragma unroll
+    for (int u = 0; u < 4; u++)
+#pragma unroll
+        for (int v = 0; v < 4; v++) acc[u][v] = 0.f;
+    const float* arow[4];
+    const float* brow[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+        arow[u] = g.a + (long long)min(i0 + u, g.I - 1) * g.a_si;     // rows past the end repeat the last one
+        brow[u] = g.b + (long long)min(j0 + u, g.J - 1) * g.b_sj;     // (their results are not stored)
+    }
+    for (int l = 4 * lane; l < g.L; l += 128) {
+        float4 a[4], b[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            a[u] = *reinterpret_cast<const float4*>(arow[u] + l);
+            b[u] = *reinterpret_cast<const float4*>(brow[u] + l);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+#pragma unroll
+            for (int v = 0; v < 4; v++) {
+                acc[u][v] = fmaf(a[u].x, b[v].x, acc[u][v]);
+                acc[u][v] = fmaf(a[u].y, b[v].y, acc[u][v]);
+                acc[u][v] = fmaf(a[u].z, b[v].z, acc[u][v]);
+                acc[u][v] = fmaf(a[u].w, b[v].w, acc[u][v]);
+            }
+    }
+    // all lanes end up with the 16 sums; lane 4 u + v stores output (i0 + u, j0 + v)
+    float mine = 0.f;
+#pragma unroll
+    for (int u = 0; u < 4; u++)
+#pragma unroll
+        for (int v = 0; v < 4; v++) {
+            float x = acc[u][v];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) x = __fadd_rn(x, __shfl_xor_sync(0xFFFFFFFFu, x, o));
+            if (lane == 4 * u + v) mine = x;
+        }
+    if (lane >= 16) return;
+    const int i = i0 + (lane >> 2), j = j0 + (lane & 3);
+    if (i >= g.I || j >= g.J) return;
+    float val = mine;
+    if (g.bias) val = __fadd_rn(val, g.bias_per_row ? g.bias[i] : g.bias[j]);
+    const size_t idx = (size_t)i * g.J + j;
+    if (g.relu) {
+        const float m = val > 0.f ? 1.f : 0.f;
+        if (g.mask_out) g.mask_out[idx] = m;
+        val = __fmul_rn(val, m);
+    }
+    if (g.mask_in) val = __fmul_rn(val, g.mask_in[idx]);
+    g.c[idx] = val;
+}
+
 // Register-tiled form for large outputs: a 16 x 16 thread grid, each thread RI x RJ outputs
 // (RJ consecutive columns, read from shared memory as float4), 16-deep chunks, double
 // buffered.  Per k step a thread issues RI + RJ/4 shared loads for RI * RJ multiply-adds,
@@ -470,7 +539,13 @@ nvq_status launch_gemm(const GemmArgs& g, cudaStream_t st) {
         nvq_launch_chained(gemm_f32_kernel<32>, grid, 256, 0, st, g);
     } else {
         dim3 grid((g.J + 15) / 16, (g.I + 15) / 16);
-        if (g.L >= 256 && !g.rowsum && g.splits <= 1)
+        const bool k_rows = g.a_sl == 1 && g.b_sl == 1 && g.L % 4 == 0 && g.a_si % 4 == 0 && g.b_sj % 4 == 0 &&
+                            nvq_aligned(g.a, 16) && nvq_aligned(g.b, 16) && g.out_mode == 0 && !g.rowsum &&
+                            g.splits <= 1;
+        if (k_rows && g.L >= 128) {
+            const long long warps = (long long)((g.I + 3) / 4) * ((g.J + 3) / 4);
+            nvq_launch_chained(linear_fwd_klanes_kernel, dim3((unsigned)((warps + 7) / 8)), 256, 0, st, g);
+        } else if (g.L >= 256 && !g.rowsum && g.splits <= 1)
             nvq_launch_chained(gemm_f32_ksplit_kernel, grid, 256 * kSliceGroups, 0, st, g);
         else
             nvq_launch_chained(gemm_f32_kernel<16>, grid, 256, 0, st, g);
@@ -524,6 +599,9 @@ __global__ void mul_kernel(float* __restrict__ out, const float* __restrict__ a,
 //   y_hat = softmax(logits, axis 1) in fp32; grad = float((double(y_hat) - onehot) / M)
 //   loss  = -sum(onehot * log(p2 + 1e-8)) / M with p2 = softmax(y_hat, axis 0): the value the
 //   reference reports (it applies softmax a second time, along the batch axis).
+__device__ void ce_loss_from_yhat(float* __restrict__ loss, const float* __restrict__ yhat_scratch,
+                                  const int* __restrict__ labels, int M, int C, double* red);
+
 __global__ void softmax_ce_kernel(float* __restrict__ grad, float* __restrict__ loss,
                                   const float* __restrict__ logits, const int* __restrict__ labels,
                                   float* __restrict__ yhat_scratch, int M, int C) {
@@ -545,6 +623,21 @@ __global__ void softmax_ce_kernel(float* __restrict__ grad, float* __restrict__ 
     }
     __syncthreads();
     if (!loss) return;
+    ce_loss_from_yhat(loss, yhat_scratch, labels, M, C, red);
+}
+
+// loss = -sum(onehot * log(p2 + 1e-8)) / M with p2 = softmax(y_hat, axis 0), from the y_hat the
+// kernel above left in yhat_scratch.  Nothing in the step depends on the value, so a training
+// step runs this beside its backward pass instead of in front of it.
+__global__ void ce_loss_kernel(float* __restrict__ loss, const float* __restrict__ yhat,
+                               const int* __restrict__ labels, int M, int C) {
+    nvq_chain_sync();
+    extern __shared__ double red[];
+    ce_loss_from_yhat(loss, yhat, labels, M, C, red);
+}
+
+__device__ void ce_loss_from_yhat(float* __restrict__ loss, const float* __restrict__ yhat_scratch,
+                                  const int* __restrict__ labels, int M, int C, double* red) {
     // second softmax along the batch axis: one warp per class column, lanes stride over the
     // rows; only the labelled entries enter the loss
     double part = 0.0;
@@ -1019,6 +1112,17 @@ extern "C" nvq_status nvq_softmax_ce_f32(float* d_grad, float* d_loss, const flo
     if (s != NVQ_OK) return s;
     nvq_launch_chained(softmax_ce_kernel, dim3(1), 256, 256 * sizeof(double), (cudaStream_t)stream, d_grad, d_loss,
                    d_logits, (const int*)d_labels, d_yhat, M, C);
+    NVQ_LAUNCHED();
+    return NVQ_OK;
+}
+
+extern "C" nvq_status nvq_ce_loss_f32(float* d_loss, const float* d_yhat, const int32_t* d_labels, int M,
+                                      int C, int device, void* stream) {
+    NVQ_REQUIRE(d_loss && d_yhat && d_labels && M > 0 && C > 0, "nvq_ce_loss_f32: bad argument");
+    nvq_status s = nvq_use_device(device);
+    if (s != NVQ_OK) return s;
+    nvq_launch_chained(ce_loss_kernel, dim3(1), 256, 256 * sizeof(double), (cudaStream_t)stream, d_loss, d_yhat,
+                       (const int*)d_labels, M, C);
     NVQ_LAUNCHED();
     return NVQ_OK;
 }

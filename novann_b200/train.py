@@ -179,6 +179,7 @@ class MLPTrainStep:
         self._step_no = 0
         self.stream = Stream(device)
         self.side = Stream(device)          # weight-gradient GEMMs, beside the dX chain
+        self.side2 = Stream(device)         # the loss value, beside both
         flat = flatten_params(params)
         self.n_params = flat.size
         self.d_params = DeviceBuffer.from_numpy(flat, device)
@@ -204,6 +205,8 @@ class MLPTrainStep:
         self.d_loss = DeviceBuffer(4, device)
         self.ev_fork = [Event(device) for _ in range(self.nl)]
         self.ev_join = Event(device)
+        self.ev_loss = Event(device)
+        self.ev_loss_done = Event(device)
         self._graph = None
         self._graph_is_partial = False
         self._peer_graphs = [None, None]    # forward / loss / backward into gradient buffer 0 / 1
@@ -231,8 +234,15 @@ class MLPTrainStep:
                                        self.d_params.at(self.w_off[i]), self.d_params.at(self.b_off[i]),
                                        B, self.dims[i + 1], self.dims[i], 0 if last else 1,
                                        None if last else self.d_mask[i].at(0), dev, st))
-        check(L.nvq_softmax_ce_f32(self.d_g[self.nl].at(0), self.d_loss.at(0), self.d_act[self.nl].at(0),
+        # the gradient of the loss on the step's stream; the loss VALUE (the reference's double
+        # softmax), which nothing downstream reads, beside the backward pass on the side stream
+        check(L.nvq_softmax_ce_f32(self.d_g[self.nl].at(0), None, self.d_act[self.nl].at(0),
                                    self.d_labels.at(0), self.d_yhat.at(0), B, self.dims[-1], dev, st))
+        self.ev_loss.record(self.stream)
+        self.ev_loss.block(self.side2)
+        check(L.nvq_ce_loss_f32(self.d_loss.at(0), self.d_yhat.at(0), self.d_labels.at(0), B, self.dims[-1],
+                                dev, _sptr(self.side2)))
+        self.ev_loss_done.record(self.side2)
         # Backward: the chain loss -> dX(nl-1) -> ... -> dX(1) runs on the step's stream; every
         # weight gradient (with its bias gradient) depends on one link of that chain only and runs
         # on a side stream, joined before the update - in a CUDA graph these are parallel branches.
@@ -249,6 +259,7 @@ class MLPTrainStep:
                                            B, self.dims[i + 1], self.dims[i], dev, st))
         self.ev_join.record(self.side)
         self.ev_join.block(self.stream)
+        self.ev_loss_done.block(self.stream)
 
     def launch_update(self) -> None:
         """The gradient all-reduce (data parallel) and the SGD update."""
